@@ -1,0 +1,177 @@
+/*
+ * b200conv.h - C ABI of the B200 (sm_100a) FP32 Conv2D / GEMM library.
+ *
+ * Plain C: pointers, sizes and POD structs only.  This is the boundary a host
+ * extension binds to; the PyTorch PrivateUse1 extension shipped next to it
+ * (csrc/torch_backend) and the ctypes binding (b200conv.py) call nothing else.
+ *
+ * The reference backend has no C plug-in interface of its own: its operators
+ * are C++ functions registered with the PyTorch dispatcher that record Vulkan
+ * compute dispatches.  Each entry point below therefore cites the reference
+ * function whose device work it replaces (paths are inside the reference tree).
+ *
+ * Conventions
+ *  - every function returns 0 on success or a negative B200_E* code; the text
+ *    of the most recent failure on the calling thread is b200_last_error().
+ *  - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream).
+ *    All compute entry points are asynchronous with respect to the host.
+ *  - tensors are FP32.  Inputs are described by b200_view4 (device pointer to
+ *    element [0,0,0,0] plus four element strides, which may be zero, negative
+ *    or non-monotone), so NCHW, channels-last, sliced, offset, transposed and
+ *    broadcast views are consumed in place; outputs are contiguous NCHW, as in
+ *    the reference (csrc/ops/convolution.cpp:662,685,689,693).
+ *  - there is no CPU fallback: with no usable device every call fails.
+ */
+#ifndef B200CONV_H
+#define B200CONV_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200_OK 0
+#define B200_EINVAL (-1)      /* invalid shapes or parameters */
+#define B200_ECUDA (-2)       /* a CUDA runtime/driver call failed */
+#define B200_EWORKSPACE (-3)  /* workspace too small / forced candidate exceeds the budget */
+#define B200_EUNSUPPORTED (-4)/* forced candidate not applicable to this geometry */
+#define B200_ENOMEM (-5)
+#define B200_ERANGE (-6)      /* int32 coordinate / uint32 element-count guards */
+#define B200_EDEVICE (-7)     /* a device-side bounded wait gave up (status word set) */
+
+/* The 16 push constants of the reference's ConvParams, same order
+ * (csrc/ops/convolution.cpp:45-52). */
+typedef struct {
+  int32_t n, cin, cout, h, w, kh, kw, oh, ow;
+  int32_t sh, sw, ph, pw, dh, dw, groups;
+} b200_conv_params;
+
+typedef struct {
+  const float* ptr;   /* device address of element [0,0,0,0] (storage offset already applied) */
+  int64_t stride[4];  /* element strides of the logical [N,C,H,W] / [Cout,Cin/g,kh,kw] view */
+} b200_view4;
+
+/* Phases and candidates: ConvPhase / ConvKind of csrc/ops/convolution.cpp:161-187. */
+enum { B200_PHASE_FORWARD = 0, B200_PHASE_DINPUT = 1, B200_PHASE_DWEIGHT = 2, B200_PHASE_DBIAS = 3 };
+enum {
+  B200_ALGO_AUTO = 0,    /* heuristic (replaces `heuristic`, convolution.cpp:423-482) */
+  B200_ALGO_DIRECT = 1,  /* one thread per output, loop order of the direct shaders (exact FP32 FMA) */
+  B200_ALGO_TILED = 2,   /* CUDA-core FP32 implicit GEMM, any geometry / strides */
+  B200_ALGO_TC = 3,      /* tcgen05 implicit GEMM, 3xTF32 split with FP32 accumulation in TMEM */
+  B200_ALGO_WINOGRAD = 4 /* Winograd-domain forward for 3x3 stride-1 (replaces winograd_f2) */
+};
+
+/* ---- runtime: replaces VulkanContext / VulkanAllocator --------------------------------- */
+
+/* Select the device and create the library state.  Idempotent.
+ * Replaces VulkanContext::instance() device pick, csrc/vulkan_context.cpp:59-83. */
+int b200_init(int device_ordinal);
+const char* b200_last_error(void);
+/* csrc/torch_vulkan.cpp:181-183 (device_name) */
+const char* b200_device_name(void);
+int b200_device_sm_count(void);
+
+/* Stream-ordered caching allocator: a block freed on a stream can be handed out
+ * again on that stream at once, and on another stream after the free point has
+ * been reached.  Replaces VulkanAllocator::allocate / free-list reuse,
+ * csrc/vulkan_allocator.cpp:33-47,123-154. */
+int b200_malloc(void** ptr, size_t bytes, void* stream);
+int b200_free(void* ptr, void* stream);
+int b200_empty_cache(void);
+/* out[0..3] = bytes in use, bytes cached, cudaMalloc calls, cache hits */
+int b200_mem_stats(uint64_t out[4]);
+/* pinned host memory for staged transfers */
+int b200_host_alloc(void** ptr, size_t bytes);
+int b200_host_free(void* ptr);
+
+enum { B200_H2D = 1, B200_D2H = 2, B200_D2D = 3 };
+/* Asynchronous on `stream`; replaces the upload/download recording of
+ * csrc/vulkan_context.cpp:98-112,172-211 and csrc/ops/device_copy.cpp. */
+int b200_memcpy(void* dst, const void* src, size_t bytes, int kind, void* stream);
+int b200_memset(void* dst, int value, size_t bytes, void* stream);
+/* dst (contiguous, numel elements of elem_bytes = 1,2,4 or 8) <- strided view;
+ * replaces conv2d_pack.comp / native_pack (csrc/ops/convolution.cpp:62-99) for the
+ * copy_/contiguous plumbing.  Convolution itself never packs. */
+int b200_gather_strided(void* dst, const void* src, int ndim, const int64_t* sizes,
+                        const int64_t* strides, int elem_bytes, void* stream);
+/* strided dst <- contiguous src (copy_ into a view) */
+int b200_scatter_strided(void* dst, const void* src, int ndim, const int64_t* sizes,
+                         const int64_t* strides, int elem_bytes, void* stream);
+
+/* Streams and events: replaces the single in-order queue and event sequences of
+ * csrc/torch_vulkan.cpp:34-103 and csrc/vulkan_context.cpp:493-523. */
+int b200_stream_create(void** stream);
+int b200_stream_destroy(void* stream);
+int b200_stream_sync(void* stream);
+int b200_stream_query(void* stream); /* 1 = idle, 0 = busy, <0 = error */
+int b200_device_sync(void);
+int b200_event_create(void** event, int enable_timing);
+int b200_event_destroy(void* event);
+int b200_event_record(void* event, void* stream);
+int b200_event_sync(void* event);
+int b200_event_query(void* event);   /* 1 = complete, 0 = pending */
+int b200_stream_wait_event(void* stream, void* event);
+int b200_event_elapsed_ms(void* first, void* second, float* ms);
+
+/* ---- convolution ----------------------------------------------------------------------- */
+
+/* Validate a geometry and derive OH/OW: convolution_params, csrc/ops/convolution.cpp:101-156,
+ * plus the element-count guards of dispatch (:559-560).  `wcin` is weight.size(1). */
+int b200_conv2d_geometry(b200_conv_params* out, int64_t n, int64_t cin, int64_t cout, int64_t h,
+                         int64_t w, int64_t wcin, int64_t kh, int64_t kw, int64_t sh, int64_t sw,
+                         int64_t ph, int64_t pw, int64_t dh, int64_t dw, int64_t groups);
+
+/* Candidate actually used for (geometry, phase) when `algo` is requested
+ * (AUTO resolves through the heuristic); <0 if the forced candidate is not applicable.
+ * Replaces applicable/candidates/heuristic, csrc/ops/convolution.cpp:357-482. */
+int b200_conv2d_select(const b200_conv_params* p, int phase, int algo, size_t workspace_bytes);
+/* Scratch bytes the selected candidate wants (0 = none).  For dWeight this is the
+ * split-K partial buffer of weight_split_plan, csrc/ops/convolution.cpp:204-238;
+ * a smaller non-zero budget yields fewer, longer splits. */
+size_t b200_conv2d_workspace(const b200_conv_params* p, int phase, int algo, size_t budget_bytes);
+
+/* y = conv(x, w) + bias.  Replaces convolution_overrideable's dispatch
+ * (csrc/ops/convolution.cpp:641-665) and the conv2d_forward, conv2d_tiled_<tile>,
+ * conv2d_depthwise and conv2d_winograd_<stage> shaders.  bias may be NULL (the reference binds
+ * a shared zero buffer, :660).  y: contiguous [n,cout,oh,ow]. */
+int b200_conv2d_forward(const b200_conv_params* p, b200_view4 x, b200_view4 w, const float* bias,
+                        int64_t bias_stride, float* y, void* workspace, size_t workspace_bytes,
+                        int algo, void* stream);
+/* dx = conv_transpose(dy, w).  Replaces dispatch(Input), csrc/ops/convolution.cpp:684-687 and
+ * the conv2d_backward_input shaders.  dx: contiguous [n,cin,h,w]. */
+int b200_conv2d_dinput(const b200_conv_params* p, b200_view4 dy, b200_view4 w, float* dx,
+                       void* workspace, size_t workspace_bytes, int algo, void* stream);
+/* dw = dy (*) x summed over batch and positions.  Replaces dispatch(Weight), :688-691,
+ * the conv2d_backward_weight shaders (direct, reduce, tiled, finalize).  The split-K partials are summed in
+ * ascending split order (no float atomics), so results are run-to-run identical.
+ * dw: contiguous [cout,cin/g,kh,kw]. */
+int b200_conv2d_dweight(const b200_conv_params* p, b200_view4 x, b200_view4 dy, float* dw,
+                        void* workspace, size_t workspace_bytes, int algo, void* stream);
+/* db[co] = sum dy.  Replaces dispatch(Bias), :692-695, conv2d_backward_bias{,_reduce}.
+ * workspace may be NULL (then a single pass per channel is used). */
+int b200_conv2d_dbias(const b200_conv_params* p, b200_view4 dy, float* db, void* workspace,
+                      size_t workspace_bytes, void* stream);
+
+/* ---- GEMM (nn.Linear neighbours of the conv path) -------------------------------------- */
+
+/* C[M,N] (contiguous) = alpha * A*B + (beta == 0 ? 0 : beta * bias[n]); A, B arbitrary 2-D
+ * element strides; bias NULL = plain mm.  Replaces mm_impl (csrc/ops/mm.cpp:244-343) and
+ * addmm_bias_vulkan (:835-879) with matmul_strided{,_reg}{,_bias}.comp. */
+int b200_gemm(int64_t M, int64_t N, int64_t K, const float* A, int64_t sa0, int64_t sa1,
+              const float* B, int64_t sb0, int64_t sb1, const float* bias, float alpha, float beta,
+              float* C, int algo, void* stream);
+
+/* ---- statistics ------------------------------------------------------------------------ */
+
+/* Number of kernels this library has launched since load (all streams). */
+uint64_t b200_launch_count(void);
+/* Name of the kernel family the last conv/gemm call on this thread launched
+ * (e.g. "tc_igemm_fwd", "simt_igemm_dweight+finalize"). */
+const char* b200_last_kernel(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200CONV_H */

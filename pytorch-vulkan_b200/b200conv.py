@@ -1,0 +1,282 @@
+"""ctypes binding of the C-ABI library (include/b200conv.h).
+
+Used by the tests and the benchmark to reach the CUDA kernels without PyTorch in the
+loop.  Every call goes to ``libb200conv.so``; there is no Python or CPU implementation
+behind these functions, and a missing library or device raises.
+
+The high-level helpers take numpy arrays (any strided float32 view: the bytes spanned by
+the view are uploaded as they are and the kernels consume the view in place through
+``b200_view4``), mirroring how the reference's operators accept transposed, sliced,
+offset, channels-last and broadcast tensors (csrc/ops/convolution.cpp:641-697).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import POINTER, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_uint64, c_void_p
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libb200conv.so")
+
+PHASE_FORWARD, PHASE_DINPUT, PHASE_DWEIGHT, PHASE_DBIAS = 0, 1, 2, 3
+ALGO_AUTO, ALGO_DIRECT, ALGO_TILED, ALGO_TC, ALGO_WINOGRAD = 0, 1, 2, 3, 4
+ALGO_NAMES = {"auto": 0, "direct": 1, "tiled": 2, "tc": 3, "winograd": 4}
+H2D, D2H, D2D = 1, 2, 3
+DEFAULT_WORKSPACE = 64 << 20  # TORCH_VULKAN_CONV_WORKSPACE_MB default, convolution.cpp:239-247
+
+
+class ConvParams(ctypes.Structure):
+    _fields_ = [(k, c_int32) for k in ("n", "cin", "cout", "h", "w", "kh", "kw", "oh", "ow",
+                                       "sh", "sw", "ph", "pw", "dh", "dw", "groups")]
+
+    def flops(self):
+        return 2 * self.n * self.oh * self.ow * self.cout * (self.cin // self.groups) * self.kh * self.kw
+
+
+class View4(ctypes.Structure):
+    _fields_ = [("ptr", c_void_p), ("stride", c_int64 * 4)]
+
+
+class B200Error(RuntimeError):
+    def __init__(self, code, text):
+        super().__init__(f"b200conv error {code}: {text}")
+        self.code = code
+
+
+# name -> (restype, argtypes): the complete list of symbols include/b200conv.h declares.
+SIGNATURES = {
+    "b200_init": (c_int, [c_int]),
+    "b200_last_error": (c_char_p, []),
+    "b200_device_name": (c_char_p, []),
+    "b200_device_sm_count": (c_int, []),
+    "b200_malloc": (c_int, [POINTER(c_void_p), c_size_t, c_void_p]),
+    "b200_free": (c_int, [c_void_p, c_void_p]),
+    "b200_empty_cache": (c_int, []),
+    "b200_mem_stats": (c_int, [POINTER(c_uint64)]),
+    "b200_host_alloc": (c_int, [POINTER(c_void_p), c_size_t]),
+    "b200_host_free": (c_int, [c_void_p]),
+    "b200_memcpy": (c_int, [c_void_p, c_void_p, c_size_t, c_int, c_void_p]),
+    "b200_memset": (c_int, [c_void_p, c_int, c_size_t, c_void_p]),
+    "b200_gather_strided": (c_int, [c_void_p, c_void_p, c_int, POINTER(c_int64), POINTER(c_int64), c_int, c_void_p]),
+    "b200_scatter_strided": (c_int, [c_void_p, c_void_p, c_int, POINTER(c_int64), POINTER(c_int64), c_int, c_void_p]),
+    "b200_stream_create": (c_int, [POINTER(c_void_p)]),
+    "b200_stream_destroy": (c_int, [c_void_p]),
+    "b200_stream_sync": (c_int, [c_void_p]),
+    "b200_stream_query": (c_int, [c_void_p]),
+    "b200_device_sync": (c_int, []),
+    "b200_event_create": (c_int, [POINTER(c_void_p), c_int]),
+    "b200_event_destroy": (c_int, [c_void_p]),
+    "b200_event_record": (c_int, [c_void_p, c_void_p]),
+    "b200_event_sync": (c_int, [c_void_p]),
+    "b200_event_query": (c_int, [c_void_p]),
+    "b200_stream_wait_event": (c_int, [c_void_p, c_void_p]),
+    "b200_event_elapsed_ms": (c_int, [c_void_p, c_void_p, POINTER(c_float)]),
+    "b200_conv2d_geometry": (c_int, [POINTER(ConvParams)] + [c_int64] * 15),
+    "b200_conv2d_select": (c_int, [POINTER(ConvParams), c_int, c_int, c_size_t]),
+    "b200_conv2d_workspace": (c_size_t, [POINTER(ConvParams), c_int, c_int, c_size_t]),
+    "b200_conv2d_forward": (c_int, [POINTER(ConvParams), View4, View4, c_void_p, c_int64, c_void_p, c_void_p,
+                                    c_size_t, c_int, c_void_p]),
+    "b200_conv2d_dinput": (c_int, [POINTER(ConvParams), View4, View4, c_void_p, c_void_p, c_size_t, c_int, c_void_p]),
+    "b200_conv2d_dweight": (c_int, [POINTER(ConvParams), View4, View4, c_void_p, c_void_p, c_size_t, c_int, c_void_p]),
+    "b200_conv2d_dbias": (c_int, [POINTER(ConvParams), View4, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "b200_gemm": (c_int, [c_int64, c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64,
+                          c_void_p, c_float, c_float, c_void_p, c_int, c_void_p]),
+    "b200_launch_count": (c_uint64, []),
+    "b200_last_kernel": (c_char_p, []),
+}
+
+_lib = None
+
+
+def lib():
+    """Load libb200conv.so and declare every prototype.  Raises if the library is absent:
+    build it with ``python pytorch-vulkan_b200/build.py``."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise OSError(f"{LIB_PATH} not found: the CUDA library must be built (no fallback exists)")
+        handle = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = handle
+    return _lib
+
+
+def check(rc):
+    if rc < 0:
+        raise B200Error(rc, lib().b200_last_error().decode())
+    return rc
+
+
+def init(device=-1):
+    check(lib().b200_init(device))
+
+
+def launch_count():
+    return int(lib().b200_launch_count())
+
+
+def last_kernel():
+    return lib().b200_last_kernel().decode()
+
+
+class DeviceBuffer:
+    """A block from the library's caching allocator."""
+
+    def __init__(self, nbytes, stream=None):
+        self.nbytes = int(nbytes)
+        self.stream = stream
+        p = c_void_p()
+        check(lib().b200_malloc(ctypes.byref(p), max(self.nbytes, 1), stream))
+        self.ptr = p.value
+
+    def free(self):
+        if self.ptr:
+            check(lib().b200_free(self.ptr, self.stream))
+            self.ptr = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+    def upload(self, host_bytes, stream=None):
+        check(lib().b200_memcpy(self.ptr, host_bytes, self.nbytes, H2D, stream))
+
+    def to_numpy(self, shape, dtype=np.float32, stream=None):
+        out = np.empty(shape, dtype)
+        assert out.nbytes <= self.nbytes
+        check(lib().b200_memcpy(out.ctypes.data, self.ptr, out.nbytes, D2H, stream))
+        check(lib().b200_stream_sync(stream))
+        return out
+
+
+def geometry(xshape, cout, kernel, stride=(1, 1), padding=(0, 0), dilation=(1, 1), groups=1, wcin=None):
+    pair = lambda v: (v, v) if isinstance(v, int) else tuple(v)
+    n, cin, h, w = xshape
+    (kh, kw), (sh, sw), (ph, pw), (dh, dw) = pair(kernel), pair(stride), pair(padding), pair(dilation)
+    if wcin is None:
+        wcin = cin // groups if groups > 0 else -1
+    p = ConvParams()
+    check(lib().b200_conv2d_geometry(ctypes.byref(p), n, cin, cout, h, w, wcin, kh, kw, sh, sw, ph, pw, dh, dw, groups))
+    return p
+
+
+def _byte_bounds(a):
+    lo = hi = a.ctypes.data
+    for dim, st in zip(a.shape, a.strides):
+        if dim == 0:
+            return a.ctypes.data, a.ctypes.data
+        if st > 0:
+            hi += (dim - 1) * st
+        else:
+            lo += (dim - 1) * st
+    return lo, hi + a.itemsize
+
+
+class DeviceView:
+    """A float32 numpy view uploaded byte-for-byte; `.view4()` describes it to the kernels."""
+
+    def __init__(self, arr, stream=None):
+        arr = np.asarray(arr)
+        assert arr.dtype == np.float32
+        self.shape = arr.shape
+        lo, hi = _byte_bounds(arr)
+        self.buf = DeviceBuffer(hi - lo, stream)
+        if hi > lo:
+            check(lib().b200_memcpy(self.buf.ptr, c_void_p(lo), hi - lo, H2D, stream))
+            check(lib().b200_stream_sync(stream))  # the numpy memory may be pageable
+        self.ptr = self.buf.ptr + (arr.ctypes.data - lo)
+        self.strides = [s // 4 for s in arr.strides]
+
+    def view4(self):
+        st = list(self.strides) + [0] * (4 - len(self.strides))
+        return View4(self.ptr, (c_int64 * 4)(*st))
+
+
+def contiguous_view4(ptr, shape):
+    st, acc = [], 1
+    for d in reversed(shape):
+        st.append(acc)
+        acc *= d
+    return View4(ptr, (c_int64 * 4)(*reversed(st)))
+
+
+def workspace_bytes(p, phase, algo=ALGO_AUTO, budget=DEFAULT_WORKSPACE):
+    return int(lib().b200_conv2d_workspace(ctypes.byref(p), phase, algo, budget))
+
+
+def select(p, phase, algo=ALGO_AUTO, budget=DEFAULT_WORKSPACE):
+    return check(lib().b200_conv2d_select(ctypes.byref(p), phase, algo, budget))
+
+
+def _algo(a):
+    return ALGO_NAMES[a] if isinstance(a, str) else int(a)
+
+
+def conv2d_forward(x, w, b=None, stride=(1, 1), padding=(0, 0), dilation=(1, 1), groups=1, algo="auto",
+                   budget=DEFAULT_WORKSPACE):
+    """y = conv2d(x, w) + b on the device; numpy in, numpy out (contiguous NCHW)."""
+    algo = _algo(algo)
+    p = geometry(x.shape, w.shape[0], w.shape[2:], stride, padding, dilation, groups, wcin=w.shape[1])
+    xv, wv = DeviceView(x), DeviceView(w)
+    bv = DeviceView(b) if b is not None else None
+    y = DeviceBuffer(4 * p.n * p.cout * p.oh * p.ow)
+    ws_n = workspace_bytes(p, PHASE_FORWARD, algo, budget)
+    ws = DeviceBuffer(ws_n) if ws_n else None
+    check(lib().b200_conv2d_forward(ctypes.byref(p), xv.view4(), wv.view4(), bv.ptr if bv else None,
+                                    bv.strides[0] if bv else 0, y.ptr, ws.ptr if ws else None, ws_n, algo, None))
+    return y.to_numpy((p.n, p.cout, p.oh, p.ow))
+
+
+def conv2d_backward(go, x, w, stride=(1, 1), padding=(0, 0), dilation=(1, 1), groups=1,
+                    mask=(True, True, True), algo="auto", budget=DEFAULT_WORKSPACE):
+    """(dx, dw, db) like aten::convolution_backward with an output mask; None where masked off
+    (csrc/ops/convolution.cpp:667-697)."""
+    algo = _algo(algo)
+    p = geometry(x.shape, w.shape[0], w.shape[2:], stride, padding, dilation, groups, wcin=w.shape[1])
+    if tuple(go.shape) != (p.n, p.cout, p.oh, p.ow):
+        raise ValueError("convolution backward: output gradient shape mismatch")
+    gv = DeviceView(go)
+    dx = dw = db = None
+    L = lib()
+    if mask[0]:
+        wv = DeviceView(w)
+        out = DeviceBuffer(4 * int(np.prod(x.shape)))
+        n = workspace_bytes(p, PHASE_DINPUT, algo, budget)
+        ws = DeviceBuffer(n) if n else None
+        check(L.b200_conv2d_dinput(ctypes.byref(p), gv.view4(), wv.view4(), out.ptr, ws.ptr if ws else None, n, algo, None))
+        dx = out.to_numpy(x.shape)
+    if mask[1]:
+        xv = DeviceView(x)
+        out = DeviceBuffer(4 * int(np.prod(w.shape)))
+        n = workspace_bytes(p, PHASE_DWEIGHT, algo, budget)
+        ws = DeviceBuffer(n) if n else None
+        check(L.b200_conv2d_dweight(ctypes.byref(p), xv.view4(), gv.view4(), out.ptr, ws.ptr if ws else None, n, algo, None))
+        dw = out.to_numpy(w.shape)
+    if mask[2]:
+        out = DeviceBuffer(4 * p.cout)
+        n = workspace_bytes(p, PHASE_DBIAS, algo, budget)
+        ws = DeviceBuffer(n) if n else None
+        check(L.b200_conv2d_dbias(ctypes.byref(p), gv.view4(), out.ptr, ws.ptr if ws else None, n, None))
+        db = out.to_numpy((p.cout,))
+    return dx, dw, db
+
+
+def gemm(a, b, bias=None, alpha=1.0, beta=0.0, algo="auto"):
+    """C = alpha*a@b + beta*bias[col] (bias None: plain mm); a and b any 2-D float32 views."""
+    M, K = a.shape
+    K2, N = b.shape
+    if K != K2:
+        raise ValueError("matrix shapes cannot be multiplied")
+    av, bv = DeviceView(a), DeviceView(b)
+    biasv = DeviceView(np.ascontiguousarray(bias, np.float32)) if bias is not None else None
+    out = DeviceBuffer(4 * M * N)
+    if M * N:
+        check(lib().b200_gemm(M, N, K, av.ptr, av.strides[0], av.strides[1], bv.ptr, bv.strides[0], bv.strides[1],
+                              biasv.ptr if biasv else None, alpha, beta, out.ptr, _algo(algo), None))
+    return out.to_numpy((M, N))

@@ -1,0 +1,81 @@
+// Shared host/device helpers of the B200 Conv2D library (internal; the public
+// surface is include/b200conv.h).
+#pragma once
+#include <cuda_runtime.h>
+#include <atomic>
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+#include "../../include/b200conv.h"
+
+namespace b200 {
+
+// ---- error reporting ---------------------------------------------------------------------
+void set_error(const char* fmt, ...);
+int fail(int code, const char* fmt, ...);
+int cuda_fail(cudaError_t e, const char* what);
+
+#define B200_CUDA(expr)                                         \
+  do {                                                          \
+    cudaError_t e__ = (expr);                                   \
+    if (e__ != cudaSuccess) return ::b200::cuda_fail(e__, #expr); \
+  } while (0)
+
+int ensure_init();
+int sm_count();
+extern std::atomic<uint64_t> g_launches;
+void note_kernel(const char* name);
+inline void count_launch(int n = 1) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
+
+// Checks the launch of the kernel named `what`; to be used right after <<<>>>.
+int launch_check(const char* what);
+
+// ---- device-side geometry ------------------------------------------------------------------
+struct View4 {
+  const float* ptr;
+  long long s0, s1, s2, s3;
+};
+inline View4 to_view(const b200_view4& v) { return {v.ptr, v.stride[0], v.stride[1], v.stride[2], v.stride[3]}; }
+inline View4 contiguous_view(const float* p, long long d1, long long d2, long long d3) {
+  return {p, d1 * d2 * d3, d2 * d3, d3, 1};
+}
+
+struct ConvGeom {
+  int n, cin, cout, h, w, kh, kw, oh, ow, sh, sw, ph, pw, dh, dw, groups;
+  int cig, cog;  // channels per group
+};
+inline ConvGeom to_geom(const b200_conv_params& p) {
+  return {p.n, p.cin, p.cout, p.h, p.w, p.kh, p.kw, p.oh, p.ow, p.sh, p.sw, p.ph, p.pw, p.dh, p.dw, p.groups,
+          p.cin / p.groups, p.cout / p.groups};
+}
+
+static inline int64_t div_up64(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// ---- kernel families (each returns a B200_* code) -------------------------------------------
+// CUDA-core paths (conv_simt.cu)
+int simt_direct(const ConvGeom& g, int phase, View4 a, View4 b, const float* bias, long long bias_stride,
+                float* out, cudaStream_t st);
+int simt_igemm_forward(const ConvGeom& g, View4 x, View4 w, const float* bias, long long bias_stride, float* y,
+                       cudaStream_t st);
+int simt_igemm_dinput(const ConvGeom& g, View4 dy, View4 w, float* dx, cudaStream_t st);
+// splits >= 1; when splits > 1 `partial` holds splits*numel(dw) floats and a finalize pass sums
+// them in ascending order into dw.
+int simt_igemm_dweight(const ConvGeom& g, View4 x, View4 dy, float* dw, float* partial, int splits, int span,
+                       cudaStream_t st);
+int finalize_splits(const float* partial, float* out, long long count, int splits, cudaStream_t st);
+int dbias_reduce(const ConvGeom& g, View4 dy, float* db, float* partial, int slabs, cudaStream_t st);
+int simt_gemm(long long M, long long N, long long K, const float* A, long long sa0, long long sa1, const float* B,
+              long long sb0, long long sb1, const float* bias, float alpha, float beta, float* C, cudaStream_t st);
+
+// tcgen05 paths (conv_tc.cu)
+bool tc_supported(const ConvGeom& g, int phase);
+size_t tc_workspace(const ConvGeom& g, int phase, size_t budget, int* splits_out, int* span_out);
+int tc_forward(const ConvGeom& g, View4 x, View4 w, const float* bias, long long bias_stride, float* y,
+               void* ws, size_t ws_bytes, cudaStream_t st);
+int tc_dinput(const ConvGeom& g, View4 dy, View4 w, float* dx, void* ws, size_t ws_bytes, cudaStream_t st);
+int tc_dweight(const ConvGeom& g, View4 x, View4 dy, float* dw, void* ws, size_t ws_bytes, cudaStream_t st);
+int tc_gemm(long long M, long long N, long long K, const float* A, long long sa0, long long sa1, const float* B,
+            long long sb0, long long sb1, const float* bias, float alpha, float beta, float* C, cudaStream_t st);
+
+}  // namespace b200

@@ -1,0 +1,76 @@
+"""Host-only checks of the C-ABI boundary: the library loads, exports every symbol the
+header declares, and its host logic (geometry validation, candidate selection, workspace
+planning) matches the oracle's restatement of the reference.  No device work is issued."""
+import ctypes
+import os
+import re
+
+import pytest
+
+import b200conv
+from oracle import oracle
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared():
+    text = open(os.path.join(ROOT, "include", "b200conv.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(b200_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    handle = ctypes.CDLL(b200conv.LIB_PATH)
+    names = _declared()
+    assert len(names) >= 30
+    for name in names:
+        assert hasattr(handle, name), name
+
+
+def test_binding_covers_the_header():
+    assert sorted(b200conv.SIGNATURES) == _declared()
+
+
+def test_geometry_matches_oracle_on_reference_cases():
+    from golden_cases import conv_cases
+    for c in conv_cases():
+        p = b200conv.geometry(c["xshape"], c["cout"], c["kernel"], c["stride"], c["padding"], c["dilation"],
+                              c["groups"])
+        g = oracle.geometry(c["xshape"], c["cout"], c["kernel"], c["stride"], c["padding"], c["dilation"],
+                            c["groups"])
+        assert (p.oh, p.ow) == (g.oh, g.ow)
+        assert p.flops() == g.flops()
+
+
+def test_geometry_rejections_carry_the_reference_messages():
+    with pytest.raises(b200conv.B200Error, match="effective kernel exceeds padded input"):
+        b200conv.geometry((1, 2, 2, 2), 3, (3, 3), stride=(2, 2))
+    with pytest.raises(b200conv.B200Error, match="int32 coordinates"):
+        b200conv.geometry((1, 1, 4, 4), 1, (1, 1), stride=(2 ** 31, 1))
+    with pytest.raises(b200conv.B200Error, match="invalid shapes or parameters"):
+        b200conv.geometry((1, 6, 4, 4), 4, (1, 1), groups=4)
+    with pytest.raises(b200conv.B200Error, match="invalid shapes or parameters"):
+        b200conv.geometry((1, 6, 4, 4), 6, (1, 1), groups=2, wcin=6)
+    with pytest.raises(b200conv.B200Error, match="indexing overflow"):
+        b200conv.geometry((70000, 1, 256, 256), 1, (1, 1))
+
+
+def test_workspace_plan_respects_budget_and_alignment():
+    p = b200conv.geometry((64, 256, 56, 56), 256, (3, 3), padding=(1, 1))
+    dw_bytes = 256 * 256 * 9 * 4
+    for budget in (0, dw_bytes, 3 * dw_bytes, 64 << 20, 1 << 30):
+        n = b200conv.workspace_bytes(p, b200conv.PHASE_DWEIGHT, b200conv.ALGO_TILED, budget)
+        assert n <= budget and n % dw_bytes == 0
+        assert n != dw_bytes  # a single partial is never materialised
+    assert b200conv.workspace_bytes(p, b200conv.PHASE_FORWARD, b200conv.ALGO_TILED) == 0
+    assert b200conv.workspace_bytes(p, b200conv.PHASE_DINPUT, b200conv.ALGO_DIRECT) == 0
+
+
+def test_forced_candidates_resolve_or_fail_loudly():
+    p = b200conv.geometry((1, 2, 14, 15), 3, (3, 5), stride=(2, 1), padding=(1, 2), dilation=(1, 2))
+    assert b200conv.select(p, b200conv.PHASE_FORWARD, b200conv.ALGO_DIRECT) == b200conv.ALGO_DIRECT
+    assert b200conv.select(p, b200conv.PHASE_FORWARD, b200conv.ALGO_TILED) == b200conv.ALGO_TILED
+    with pytest.raises(b200conv.B200Error, match="incompatible"):
+        b200conv.select(p, b200conv.PHASE_FORWARD, b200conv.ALGO_WINOGRAD)
+    # tiny geometry: the heuristic stays on the one-thread-per-output kernels (convolution.cpp:463-469)
+    assert b200conv.select(p, b200conv.PHASE_FORWARD) == b200conv.ALGO_DIRECT

@@ -1,0 +1,167 @@
+"""Parity of the CUDA path (through the C-ABI) against the golden vectors and the oracle.
+
+Gate: max over outputs of ||out - ref||_2 / ||ref||_2 <= 1e-4 (one norm per output tensor),
+plus the element-wise tolerances the reference's own tests use
+(tests/test_conv_dispatch.py:67,70: forward rtol 4e-4 / atol 3e-5, gradients 5e-4 / 5e-5)."""
+import numpy as np
+import pytest
+
+import b200conv
+from golden_cases import case_id, conv_cases, gemm_cases
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+CASES = conv_cases()
+GATE = 1e-4
+ALGOS = ["auto", "direct", "tiled"]
+
+
+def _args(c):
+    return dict(stride=c["stride"], padding=c["padding"], dilation=c["dilation"], groups=c["groups"])
+
+
+def _check(got, want, scale, grad):
+    assert oracle.rel_l2(got, want) <= GATE
+    rtol, atol = (5e-4, 5e-5) if grad else (4e-4, 3e-5)
+    np.testing.assert_allclose(got, want, rtol=rtol, atol=atol * scale)
+
+
+@pytest.mark.parametrize("algo", ALGOS)
+@pytest.mark.parametrize("c", CASES, ids=case_id)
+def test_forward_and_all_gradients_match_golden(c, algo):
+    scale = 1.0 if c["tag"] == "dispatch" else 10.0
+    before = b200conv.launch_count()
+    y = b200conv.conv2d_forward(c["x"], c["w"], c["b"], algo=algo, **_args(c))
+    dx, dw, db = b200conv.conv2d_backward(c["go"], c["x"], c["w"], algo=algo, **_args(c))
+    assert b200conv.launch_count() >= before + 4
+    _check(y, c["y"], scale, False)
+    _check(dx, c["dx"], scale, True)
+    _check(dw, c["dw"], scale, True)
+    _check(db, c["db"], scale, True)
+
+
+def test_known_answer_affine_forward_and_constant_dinput():
+    # tests/test_conv_dispatch.py:315-333 of the reference: more than 65535*128 outputs are not
+    # needed for a CUDA grid, but the closed form is: 1x1 weight 2, bias 1 -> exactly 2x+1;
+    # dX of a constant 0.25 gradient -> exactly 0.5.
+    n = 300000
+    x = ((np.arange(n) % 97) / 97.0).astype(np.float32).reshape(1, 1, 1, n)
+    w = np.full((1, 1, 1, 1), 2.0, np.float32)
+    b = np.ones(1, np.float32)
+    for algo in ALGOS:
+        np.testing.assert_array_equal(b200conv.conv2d_forward(x, w, b, algo=algo), 2 * x + 1)
+        go = np.full(x.shape, 0.25, np.float32)
+        dx, _, _ = b200conv.conv2d_backward(go, x, w, mask=(True, False, False), algo=algo)
+        np.testing.assert_array_equal(dx, np.full(x.shape, 0.5, np.float32))
+
+
+@pytest.mark.parametrize("algo", ALGOS)
+@pytest.mark.parametrize("layout", ["transpose", "channels_last", "slice", "offset", "broadcast"])
+def test_strided_views_are_consumed_in_place(layout, algo):
+    # View layouts and geometry of the reference's tests/test_conv_universality.py:47-81.
+    rng = np.random.default_rng(700)
+    base = rng.standard_normal((3, 6, 13, 15), dtype=np.float32)
+    def view(t):
+        if layout == "transpose": return t.transpose(0, 1, 3, 2)
+        if layout == "channels_last": return np.ascontiguousarray(t.transpose(0, 2, 3, 1)).transpose(0, 3, 1, 2)
+        if layout == "slice": return t[:, :, 1::2, ::2]
+        if layout == "offset": return t[1:]
+        return np.broadcast_to(t[:1], (3,) + t.shape[1:])
+    x = view(base)
+    w = rng.standard_normal((10, 3, 3, 5), dtype=np.float32).transpose(0, 1, 3, 2)
+    b = rng.standard_normal(20, dtype=np.float32)[1::2]
+    args = dict(stride=(1, 2), padding=(2, 1), dilation=(1, 1), groups=2)
+    g = oracle.geometry(x.shape, 10, w.shape[2:], **args)
+    xc, wc, bc = (np.ascontiguousarray(v) for v in (x, w, b))
+    y = b200conv.conv2d_forward(x, w, b, algo=algo, **args)
+    assert oracle.rel_l2(y, oracle.forward(g, xc, wc, bc, f64=True)) <= GATE
+    go = rng.standard_normal(g.y_shape[:-1] + (g.y_shape[-1] * 2,), dtype=np.float32)[..., 1::2]
+    goc = np.ascontiguousarray(go)
+    want = (oracle.dinput(g, goc, wc, f64=True), oracle.dweight(g, xc, goc, f64=True), oracle.dbias(g, goc, f64=True))
+    for mask in ((True, True, True), (True, False, False), (False, True, False), (False, False, True)):
+        got = b200conv.conv2d_backward(go, x, w, mask=mask, algo=algo, **args)
+        for enabled, a, e in zip(mask, got, want):
+            if enabled:
+                assert oracle.rel_l2(a, e) <= GATE
+            else:
+                assert a is None
+
+
+def test_headline_single_layer_config_matches_cpu_fp64():
+    # N=8, C=64, 56x56, 3x3 pad 1, nn.Conv2d default init, seed 0 (the reference-runnable config).
+    import torch
+    torch.manual_seed(0)
+    conv = torch.nn.Conv2d(64, 64, 3, padding=1)
+    x = torch.randn(8, 64, 56, 56)
+    go = torch.randn(8, 64, 56, 56)
+    w, b = conv.weight.detach().numpy(), conv.bias.detach().numpy()
+    want = oracle.torch_conv_all(x.numpy(), w, b, go.numpy(), (1, 1), (1, 1), (1, 1), 1)
+    y = b200conv.conv2d_forward(x.numpy(), w, b, padding=(1, 1))
+    dx, dw, db = b200conv.conv2d_backward(go.numpy(), x.numpy(), w, padding=(1, 1))
+    errs = [oracle.rel_l2(a, e) for a, e in zip((y, dx, dw, db), want)]
+    assert max(errs) <= GATE, errs
+
+
+def test_dweight_is_run_to_run_identical():
+    c = next(c for c in CASES if c["tag"] == "layer64")
+    a = b200conv.conv2d_backward(c["go"], c["x"], c["w"], mask=(False, True, True), **_args(c))
+    b = b200conv.conv2d_backward(c["go"], c["x"], c["w"], mask=(False, True, True), **_args(c))
+    np.testing.assert_array_equal(a[1], b[1])
+    np.testing.assert_array_equal(a[2], b[2])
+
+
+@pytest.mark.parametrize("algo", ["auto", "tiled"])
+def test_gemm_and_fused_addmm_match_golden(algo):
+    for case in gemm_cases():
+        for (beta, alpha), want in zip(case["scalars"], case["outs"]):
+            got = b200conv.gemm(case["a"], case["bt"].T, case["bias"], alpha=alpha, beta=beta, algo=algo)
+            assert oracle.rel_l2(got, want) <= GATE
+    a = np.array([[1, 2], [3, 4]], np.float32)
+    b = np.array([[5, 6], [7, 8]], np.float32)
+    np.testing.assert_array_equal(b200conv.gemm(a, b, algo=algo), np.array([[19, 22], [43, 50]], np.float32))
+
+
+def test_gemm_edge_shapes_and_beta_zero():
+    a = np.ones((3, 4), np.float32)
+    b = np.ones((4, 5), np.float32)
+    bias = np.full(5, np.nan, np.float32)
+    assert np.isfinite(b200conv.gemm(a, b, bias, alpha=1.0, beta=0.0)).all()
+    assert b200conv.gemm(np.zeros((0, 4), np.float32), b).shape == (0, 5)
+    # K == 0 -> zeros (mm) or beta*bias (addmm), mm.cpp:266-268,896-898
+    np.testing.assert_array_equal(b200conv.gemm(np.zeros((3, 0), np.float32), np.zeros((0, 5), np.float32)),
+                                  np.zeros((3, 5), np.float32))
+    bias = np.arange(5, dtype=np.float32)
+    np.testing.assert_array_equal(
+        b200conv.gemm(np.zeros((3, 0), np.float32), np.zeros((0, 5), np.float32), bias, alpha=1.0, beta=2.0),
+        np.broadcast_to(2 * bias, (3, 5)))
+
+
+def test_allocator_reuses_blocks_and_streams_events_work():
+    L = b200conv.lib()
+    stats = (ctypes_u64 * 4)()
+    a = b200conv.DeviceBuffer(3 << 20)
+    a.free()
+    L.b200_mem_stats(stats)
+    hits, device_allocs = stats[3], stats[2]
+    b = b200conv.DeviceBuffer(3 << 20)  # same stream: a cached block is handed out at once
+    L.b200_mem_stats(stats)
+    assert stats[3] == hits + 1 and stats[2] == device_allocs
+    import ctypes
+    s, e0, e1 = ctypes.c_void_p(), ctypes.c_void_p(), ctypes.c_void_p()
+    b200conv.check(L.b200_stream_create(ctypes.byref(s)))
+    b200conv.check(L.b200_event_create(ctypes.byref(e0), 1))
+    b200conv.check(L.b200_event_create(ctypes.byref(e1), 1))
+    b200conv.check(L.b200_event_record(e0, s))
+    b200conv.check(L.b200_memset(b.ptr, 0, 1 << 20, s))
+    b200conv.check(L.b200_event_record(e1, s))
+    b200conv.check(L.b200_event_sync(e1))
+    ms = ctypes.c_float()
+    b200conv.check(L.b200_event_elapsed_ms(e0, e1, ctypes.byref(ms)))
+    assert ms.value >= 0.0 and L.b200_event_query(e1) == 1 and L.b200_stream_query(s) == 1
+    for ev in (e0, e1):
+        b200conv.check(L.b200_event_destroy(ev))
+    b200conv.check(L.b200_stream_destroy(s))
+
+
+import ctypes as _ct
+ctypes_u64 = _ct.c_uint64

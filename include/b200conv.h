@@ -163,6 +163,12 @@ int b200_gemm(int64_t M, int64_t N, int64_t K, const float* A, int64_t sa0, int6
               const float* B, int64_t sb0, int64_t sb1, const float* bias, float alpha, float beta,
               float* C, int algo, void* stream);
 
+/* Device-side health word.  The tcgen05 kernels bound every wait on an mbarrier; a wait that
+ * gives up records (code << 24 | CTA index) here, frees its tensor memory and returns, so the
+ * context stays usable.  *status = 0 means no wait ever gave up.  Synchronises the device.
+ * (No counterpart in the reference: Vulkan fences time out on the host, csrc/vulkan_context.cpp:493-499.) */
+int b200_device_status(int* status, int clear);
+
 /* ---- statistics ------------------------------------------------------------------------ */
 
 /* Number of kernels this library has launched since load (all streams). */

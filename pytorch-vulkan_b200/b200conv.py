@@ -83,6 +83,7 @@ SIGNATURES = {
     "b200_conv2d_dbias": (c_int, [POINTER(ConvParams), View4, c_void_p, c_void_p, c_size_t, c_void_p]),
     "b200_gemm": (c_int, [c_int64, c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64,
                           c_void_p, c_float, c_float, c_void_p, c_int, c_void_p]),
+    "b200_device_status": (c_int, [POINTER(c_int), c_int]),
     "b200_launch_count": (c_uint64, []),
     "b200_last_kernel": (c_char_p, []),
 }
@@ -113,6 +114,13 @@ def check(rc):
 
 def init(device=-1):
     check(lib().b200_init(device))
+
+
+def device_status(clear=False):
+    """0 unless a bounded device-side wait gave up (synchronises the device)."""
+    v = c_int(0)
+    check(lib().b200_device_status(ctypes.byref(v), 1 if clear else 0))
+    return v.value
 
 
 def launch_count():

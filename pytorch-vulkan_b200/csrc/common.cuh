@@ -78,4 +78,8 @@ int tc_dweight(const ConvGeom& g, View4 x, View4 dy, float* dw, void* ws, size_t
 int tc_gemm(long long M, long long N, long long K, const float* A, long long sa0, long long sa1, const float* B,
             long long sb0, long long sb1, const float* bias, float alpha, float beta, float* C, cudaStream_t st);
 
+int* device_status_word();  // device memory, zero unless a bounded wait gave up
+int read_device_status(int* out);
+int clear_device_status();
+
 }  // namespace b200

@@ -239,6 +239,15 @@ int b200_conv2d_dbias(const b200_conv_params* p, b200_view4 dy, float* db, void*
   return dbias_reduce(g, to_view(dy), db, (float*)workspace, slabs, (cudaStream_t)stream);
 }
 
+int b200_device_status(int* status, int clear) {
+  if (int rc = ensure_init()) return rc;
+  B200_CUDA(cudaDeviceSynchronize());
+  if (status)
+    if (int rc = read_device_status(status)) return rc;
+  if (clear) return clear_device_status();
+  return B200_OK;
+}
+
 int b200_gemm(int64_t M, int64_t N, int64_t K, const float* A, int64_t sa0, int64_t sa1, const float* B,
               int64_t sb0, int64_t sb1, const float* bias, float alpha, float beta, float* C, int algo,
               void* stream) {

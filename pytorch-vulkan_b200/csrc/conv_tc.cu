@@ -1,10 +1,391 @@
-// tcgen05 (5th-generation tensor core) kernels: placeholder while the CUDA-core path is validated.
+// tcgen05 implicit-GEMM kernels for FP32 convolution on sm_100a.
+//
+// Numerics: every FP32 operand is split into two TF32 values (hi + lo) while it is staged into
+// shared memory; each K block is multiplied three times (hi*hi, hi*lo, lo*hi) by tcgen05.mma
+// kind::tf32 into one FP32 accumulator tile that lives in tensor memory (TMEM).
+//
+// Structure of one CTA (544 threads, one output tile of 128 rows x BN columns):
+//   warps 0-7  producer group 0  \  gather activations straight from the caller's strided view
+//   warps 8-15 producer group 1  /  (NCHW, channels-last, sliced ...), split them, and write the
+//                                   128-byte-swizzled K-major operand tiles; the two groups take
+//                                   alternate K blocks so global-load latency overlaps the MMAs
+//   warp 16    allocates TMEM, issues the tcgen05.mma stream, commits stages back to producers
+//   warps 0-15 afterwards read the accumulator with tcgen05.ld and store the result
+// Stages are handed over with mbarriers; every wait is bounded (tc_common.cuh).
+//
+// Replaces the reference's tiled shaders (paths inside the reference tree):
+//   forward  csrc/shaders/conv2d_tiled_body.glsl:53-86        (+ bias epilogue :19-25)
+//   dInput   csrc/shaders/conv2d_backward_input_tiled_body.glsl:49-93
+//   dWeight  csrc/shaders/conv2d_backward_weight_tiled_body.glsl:42-70 + conv2d_backward_weight_finalize.comp
+//   GEMM     csrc/shaders/matmul_strided_reg.comp / matmul_strided_reg_bias.comp
 #include "common.cuh"
+#include "tc_common.cuh"
+
+#include <algorithm>
+
 namespace b200 {
-bool tc_supported(const ConvGeom&, int) { return false; }
-size_t tc_workspace(const ConvGeom&, int, size_t, int*, int*) { return 0; }
-int tc_forward(const ConvGeom&, View4, View4, const float*, long long, float*, void*, size_t, cudaStream_t) { return fail(B200_EUNSUPPORTED, "tcgen05 path not built"); }
-int tc_dinput(const ConvGeom&, View4, View4, float*, void*, size_t, cudaStream_t) { return fail(B200_EUNSUPPORTED, "tcgen05 path not built"); }
-int tc_dweight(const ConvGeom&, View4, View4, float*, void*, size_t, cudaStream_t) { return fail(B200_EUNSUPPORTED, "tcgen05 path not built"); }
-int tc_gemm(long long, long long, long long, const float*, long long, long long, const float*, long long, long long, const float*, float, float, float*, cudaStream_t) { return B200_EUNSUPPORTED; }
+namespace tc {
+
+constexpr int BLOCK_M = 128;
+constexpr int KBLK = 32;  // FP32 elements per K block = one 128-byte swizzle row
+constexpr int PRODUCER_WARPS = 16, GROUP_THREADS = 256;
+constexpr int THREADS = (PRODUCER_WARPS + 1) * 32;
+
+template <int BN>
+struct TileCfg {
+  static constexpr int STAGES = BN == 256 ? 2 : (BN == 128 ? 3 : 4);
+  static constexpr int A_PLANE = BLOCK_M * 128;
+  static constexpr int B_PLANE = BN * 128;
+  static constexpr int STAGE_BYTES = 2 * A_PLANE + 2 * B_PLANE;
+  static constexpr int TILE_BYTES = STAGES * STAGE_BYTES;
+  static constexpr int SMEM_BYTES = TILE_BYTES + 1024 + 256;
+  static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+};
+
+struct Pipe {  // shared-memory addresses of the pipeline state
+  uint32_t tiles, full, empty, accum, tmem_slot;
+  volatile int* abort_flag;
+  volatile uint32_t* tmem_slot_ptr;
+  int* status;
+};
+
+template <int BN>
+__device__ __forceinline__ Pipe pipe_setup(unsigned char* smem_raw, int producer_arrivals, int* status) {
+  using Cfg = TileCfg<BN>;
+  Pipe p;
+  p.status = status;
+  const uint32_t raw = smem_u32(smem_raw);
+  p.tiles = (raw + 1023u) & ~1023u;
+  unsigned char* ctrl = smem_raw + (p.tiles - raw) + Cfg::TILE_BYTES;
+  p.full = smem_u32(ctrl);
+  p.empty = p.full + 8 * Cfg::STAGES;
+  p.accum = p.empty + 8 * Cfg::STAGES;
+  p.tmem_slot = p.accum + 8;
+  p.tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(ctrl + 8 * (2 * Cfg::STAGES + 1));
+  p.abort_flag = reinterpret_cast<volatile int*>(ctrl + 8 * (2 * Cfg::STAGES + 1) + 4);
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::STAGES; ++s) {
+      mbar_init(p.full + 8 * s, producer_arrivals);
+      mbar_init(p.empty + 8 * s, 1);
+    }
+    mbar_init(p.accum, 1);
+    *p.abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (threadIdx.x / 32 == PRODUCER_WARPS) tmem_alloc(p.tmem_slot, Cfg::TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  return p;
 }
+
+// The MMA warp: for every K block, three tcgen05.mma passes (hi*hi, hi*lo, lo*hi), four K=8
+// steps each, then hand the stage back.  Returns false if a bounded wait gave up.
+template <int BN>
+__device__ __forceinline__ void mma_loop(const Pipe& p, uint32_t tmem_acc, int kblocks) {
+  using Cfg = TileCfg<BN>;
+  constexpr uint32_t idesc = make_idesc_tf32(BLOCK_M, BN);
+  const int lane = threadIdx.x & 31;
+  for (int kb = 0; kb < kblocks; ++kb) {
+    const int s = kb % Cfg::STAGES;
+    const uint32_t it = (uint32_t)(kb / Cfg::STAGES);
+    if (!mbar_wait(p.full + 8 * s, it & 1, p.abort_flag, p.status, STATUS_TIMEOUT_FULL)) return;
+    tc_fence_after();
+    if (lane == 0) {
+      const uint32_t a_hi = p.tiles + s * Cfg::STAGE_BYTES, a_lo = a_hi + Cfg::A_PLANE;
+      const uint32_t b_hi = a_lo + Cfg::A_PLANE, b_lo = b_hi + Cfg::B_PLANE;
+      const uint64_t da_hi = make_kmajor_sw128_desc(a_hi), da_lo = make_kmajor_sw128_desc(a_lo);
+      const uint64_t db_hi = make_kmajor_sw128_desc(b_hi), db_lo = make_kmajor_sw128_desc(b_lo);
+      // small cross terms first, then the dominant term
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) umma_tf32(tmem_acc, da_lo + 2 * kk, db_hi + 2 * kk, idesc, (kb | kk) != 0);
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) umma_tf32(tmem_acc, da_hi + 2 * kk, db_lo + 2 * kk, idesc, 1);
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) umma_tf32(tmem_acc, da_hi + 2 * kk, db_hi + 2 * kk, idesc, 1);
+      umma_commit(p.empty + 8 * s);
+    }
+    __syncwarp();
+  }
+  if (lane == 0) umma_commit(p.accum);
+  __syncwarp();
+}
+
+template <int BN>
+__device__ __forceinline__ void pipe_teardown(const Pipe& p, uint32_t tmem_acc) {
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x / 32 == PRODUCER_WARPS) {
+    tc_fence_after();
+    tmem_dealloc(tmem_acc, TileCfg<BN>::TMEM_COLS);
+  }
+}
+
+// Copy one pre-split weight row block: lane = k.  Rows n0.. of the [rows_total][ktot] planes.
+template <int BN>
+__device__ __forceinline__ void produce_rows_kcontig(uint32_t plane_hi, uint32_t plane_lo, const float* __restrict__ hi,
+                                                     const float* __restrict__ lo, long long row0, int rows_valid,
+                                                     long long ktot, long long k0, int warp_in_group, int lane) {
+  constexpr int ROWS_PER_WARP = BN / (GROUP_THREADS / 32), BATCH = 8;
+#pragma unroll 1
+  for (int r0 = 0; r0 < ROWS_PER_WARP; r0 += BATCH) {
+    float vh[BATCH], vl[BATCH];
+#pragma unroll
+    for (int j = 0; j < BATCH; ++j) {  // all loads of the batch in flight before the first store
+      const int r = warp_in_group + (r0 + j) * (GROUP_THREADS / 32);
+      vh[j] = vl[j] = 0.f;
+      if (r < rows_valid) {
+        const long long off = (row0 + r) * ktot + k0 + lane;
+        vh[j] = __ldg(hi + off);
+        vl[j] = __ldg(lo + off);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < BATCH; ++j) {
+      const int r = warp_in_group + (r0 + j) * (GROUP_THREADS / 32);
+      const uint32_t o = sw128_offset(r, lane);
+      sts_f32(plane_hi + o, vh[j]);
+      sts_f32(plane_lo + o, vl[j]);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Forward and dInput: rows = pixels (128 per tile), columns = output channels of one group,
+// K = (tap, channel) with 32 consecutive channels of one filter tap per K block.
+// ---------------------------------------------------------------------------------------
+struct ConvTcArgs {
+  ConvGeom g;
+  View4 act;                // forward: x.  dInput: dy
+  const float* w_hi;        // [groups][nc][taps*kc] pre-split weights, K contiguous
+  const float* w_lo;
+  const float* bias;
+  long long bias_stride;
+  float* out;               // forward: y.  dInput: dx (contiguous NCHW)
+  long long rows_total;     // pixels of the output map: n*oh*ow (forward) or n*h*w (dInput)
+  int out_w, out_hw;        // width and plane size of the output map
+  int kc, nc;               // reduction / output channels per group
+  int cblocks, kblocks, tiles_n;
+  int out_channels;         // cout (forward) or cin (dInput)
+  int* status;
+};
+
+template <int BN, bool IS_DX>
+__global__ void __launch_bounds__(THREADS, 1) conv_tc_kernel(const ConvTcArgs a) {
+  using Cfg = TileCfg<BN>;
+  extern __shared__ unsigned char smem_raw[];
+  const Pipe p = pipe_setup<BN>(smem_raw, GROUP_THREADS, a.status);
+  const uint32_t tmem_acc = *p.tmem_slot_ptr;
+  const ConvGeom& g = a.g;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int group = blockIdx.y / a.tiles_n;
+  const int n0 = (blockIdx.y % a.tiles_n) * BN;
+  const long long row0 = (long long)blockIdx.x * BLOCK_M;
+  const int cols_valid = min(BN, a.nc - n0);
+
+  if (warp == PRODUCER_WARPS) {
+    mma_loop<BN>(p, tmem_acc, a.kblocks);
+  } else {
+    // ---- producers ----
+    const int grp = warp >> 3, t = threadIdx.x & (GROUP_THREADS - 1);
+    const int row = t & 127, khalf = t >> 7;  // this thread stages 16 channels of one pixel row
+    const long long pix = row0 + row;
+    const bool row_ok = pix < a.rows_total;
+    long long base = 0;
+    int y0 = 0, x0 = 0;
+    if (row_ok) {
+      const long long b = pix / a.out_hw;
+      const int pos = (int)(pix - b * a.out_hw);
+      const int py = pos / a.out_w, px = pos - py * a.out_w;
+      if (IS_DX) { y0 = py + g.ph; x0 = px + g.pw; }
+      else { y0 = py * g.sh - g.ph; x0 = px * g.sw - g.pw; }
+      base = b * a.act.s0 + (long long)group * a.kc * a.act.s1;
+    }
+    const long long ktot = (long long)g.kh * g.kw * a.kc;
+    const long long wrow0 = (long long)group * a.nc + n0;
+    for (int kb = grp; kb < a.kblocks; kb += 2) {
+      const int s = kb % Cfg::STAGES;
+      const uint32_t it = (uint32_t)(kb / Cfg::STAGES);
+      const int tap = kb / a.cblocks, c0 = (kb - tap * a.cblocks) * KBLK + khalf * 16;
+      const int ky = tap / g.kw, kx = tap - ky * g.kw;
+      bool ok = row_ok;
+      int iy, ix;
+      if (IS_DX) {
+        int yy = y0 - ky * g.dh, xx = x0 - kx * g.dw;
+        ok = ok && yy >= 0 && xx >= 0;
+        if (g.sh != 1 || g.sw != 1) {
+          ok = ok && (yy % g.sh == 0) && (xx % g.sw == 0);
+          yy /= g.sh;
+          xx /= g.sw;
+        }
+        ok = ok && yy < g.oh && xx < g.ow;
+        iy = yy; ix = xx;
+      } else {
+        iy = y0 + ky * g.dh; ix = x0 + kx * g.dw;
+        ok = ok && iy >= 0 && iy < g.h && ix >= 0 && ix < g.w;
+      }
+      // Issue the global loads before waiting for the stage: they only need registers.
+      float v[16];
+      const float* src = a.act.ptr + base + (long long)c0 * a.act.s1 + (long long)iy * a.act.s2 + (long long)ix * a.act.s3;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) v[j] = ok ? __ldg(src + j * a.act.s1) : 0.f;
+      if (!mbar_wait(p.empty + 8 * s, (it & 1) ^ 1, p.abort_flag, p.status, STATUS_TIMEOUT_EMPTY)) break;
+      const uint32_t a_hi = p.tiles + s * Cfg::STAGE_BYTES, a_lo = a_hi + Cfg::A_PLANE;
+      const uint32_t b_hi = a_lo + Cfg::A_PLANE, b_lo = b_hi + Cfg::B_PLANE;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        float h[4], l[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) split_tf32(v[q * 4 + j], h[j], l[j]);
+        const uint32_t o = sw128_offset(row, khalf * 16 + q * 4);
+        sts_f32x4(a_hi + o, h[0], h[1], h[2], h[3]);
+        sts_f32x4(a_lo + o, l[0], l[1], l[2], l[3]);
+      }
+      produce_rows_kcontig<BN>(b_hi, b_lo, a.w_hi, a.w_lo, wrow0, cols_valid, ktot, (long long)kb * KBLK, warp & 7, lane);
+      fence_proxy_async();
+      mbar_arrive(p.full + 8 * s);
+    }
+    // ---- epilogue: TMEM -> registers -> global ----
+    if (mbar_wait(p.accum, 0, p.abort_flag, p.status, STATUS_TIMEOUT_ACCUM)) {
+      tc_fence_after();
+      const int q = warp & 3, chunk = warp >> 2;  // lane quarter of this warp, column chunk
+      const long long opix = row0 + q * 32 + lane;
+      const bool orow_ok = opix < a.rows_total;
+      long long obase = 0;
+      if (orow_ok) {
+        const long long b = opix / a.out_hw;
+        obase = (b * a.out_channels + (long long)group * a.nc) * a.out_hw + (opix - b * a.out_hw);
+      }
+      constexpr int COLS_PER_WARP = BN / 4;
+#pragma unroll 1
+      for (int c = 0; c < COLS_PER_WARP; c += 32) {
+        const int col0 = chunk * COLS_PER_WARP + c;
+        if (col0 >= cols_valid) break;  // warp-uniform
+        float v[32];
+        tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)col0, v);
+        if (orow_ok) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int col = col0 + j;
+            if (col < cols_valid) {
+              float r = v[j];
+              if (!IS_DX && a.bias) r += __ldg(a.bias + ((long long)group * a.nc + n0 + col) * a.bias_stride);
+              a.out[obase + (long long)(n0 + col) * a.out_hw] = r;
+            }
+          }
+        }
+      }
+    }
+  }
+  pipe_teardown<BN>(p, tmem_acc);
+}
+
+// Weight staging: split W into TF32 hi/lo planes and reorder so that the reduction index of the
+// phase is contiguous.  forward: [g][co][tap][ci];  dInput: [g][ci][tap][co].
+__global__ void __launch_bounds__(256) prep_weights_kernel(ConvGeom g, View4 w, int is_dx, float* __restrict__ hi,
+                                                           float* __restrict__ lo, long long total) {
+  const long long i = blockIdx.x * 256ll + threadIdx.x;
+  if (i >= total) return;
+  const int taps = g.kh * g.kw;
+  const int kc = is_dx ? g.cog : g.cig, nc = is_dx ? g.cig : g.cog;
+  const int c = (int)(i % kc);
+  const int tap = (int)((i / kc) % taps);
+  const int r = (int)((i / ((long long)kc * taps)) % nc);
+  const int grp = (int)(i / ((long long)kc * taps * nc));
+  const int co = is_dx ? c : r, ci = is_dx ? r : c;
+  const float v = w.ptr[((long long)grp * g.cog + co) * w.s0 + ci * w.s1 + (tap / g.kw) * w.s2 + (tap % g.kw) * w.s3];
+  float h, l;
+  split_tf32(v, h, l);
+  hi[i] = h;
+  lo[i] = l;
+}
+
+}  // namespace tc
+
+using namespace tc;
+
+static int pick_bn(int nc) { return nc <= 64 ? 64 : (nc <= 128 ? 128 : 256); }
+
+bool tc_supported(const ConvGeom& g, int phase) {
+  if (phase == B200_PHASE_FORWARD) return g.cig % KBLK == 0 && g.cog >= 16;
+  if (phase == B200_PHASE_DINPUT) return g.cog % KBLK == 0 && g.cig >= 16;
+  return false;
+}
+
+size_t tc_workspace(const ConvGeom& g, int phase, size_t budget, int* splits_out, int* span_out) {
+  (void)budget;
+  if (splits_out) *splits_out = 1;
+  if (span_out) *span_out = 0;
+  if (phase == B200_PHASE_FORWARD || phase == B200_PHASE_DINPUT)
+    return 2 * sizeof(float) * (size_t)g.cout * g.cig * g.kh * g.kw;  // hi + lo planes
+  return 0;
+}
+
+template <int BN, bool IS_DX>
+static int launch_conv_tc(const ConvTcArgs& a, dim3 grid, cudaStream_t st) {
+  static bool configured = false;
+  if (!configured) {
+    B200_CUDA(cudaFuncSetAttribute(conv_tc_kernel<BN, IS_DX>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   TileCfg<BN>::SMEM_BYTES));
+    configured = true;
+  }
+  conv_tc_kernel<BN, IS_DX><<<grid, THREADS, TileCfg<BN>::SMEM_BYTES, st>>>(a);
+  count_launch();
+  return launch_check(IS_DX ? "conv_tc_kernel<dinput>" : "conv_tc_kernel<forward>");
+}
+
+static int conv_tc_run(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* bias, long long bias_stride,
+                       float* out, void* ws, size_t ws_bytes, cudaStream_t st) {
+  const size_t wcount = (size_t)g.cout * g.cig * g.kh * g.kw;
+  if (!ws || ws_bytes < 2 * sizeof(float) * wcount)
+    return fail(B200_EWORKSPACE, "tcgen05 convolution needs a workspace of %zu bytes (got %zu)",
+                2 * sizeof(float) * wcount, ws_bytes);
+  float* hi = (float*)ws;
+  float* lo = hi + wcount;
+  prep_weights_kernel<<<(unsigned)div_up64((long long)wcount, 256), 256, 0, st>>>(g, w, is_dx ? 1 : 0, hi, lo,
+                                                                                  (long long)wcount);
+  count_launch();
+  if (int rc = launch_check("prep_weights_kernel")) return rc;
+  ConvTcArgs a{};
+  a.g = g; a.act = act; a.w_hi = hi; a.w_lo = lo; a.bias = bias; a.bias_stride = bias_stride; a.out = out;
+  a.status = device_status_word();
+  if (!a.status) return fail(B200_ECUDA, "device status word is not allocated");
+  a.kc = is_dx ? g.cog : g.cig;
+  a.nc = is_dx ? g.cig : g.cog;
+  a.out_w = is_dx ? g.w : g.ow;
+  a.out_hw = is_dx ? g.h * g.w : g.oh * g.ow;
+  a.rows_total = (long long)g.n * a.out_hw;
+  a.out_channels = is_dx ? g.cin : g.cout;
+  a.cblocks = a.kc / KBLK;
+  a.kblocks = g.kh * g.kw * a.cblocks;
+  const int bn = pick_bn(a.nc);
+  a.tiles_n = (a.nc + bn - 1) / bn;
+  const long long gx = div_up64(a.rows_total, BLOCK_M), gy = (long long)g.groups * a.tiles_n;
+  if (gx > 2147483647ll || gy > 65535) return fail(B200_ERANGE, "tcgen05 convolution: grid exceeds launch limits");
+  const dim3 grid((unsigned)gx, (unsigned)gy);
+  if (is_dx) {
+    if (bn == 64) return launch_conv_tc<64, true>(a, grid, st);
+    if (bn == 128) return launch_conv_tc<128, true>(a, grid, st);
+    return launch_conv_tc<256, true>(a, grid, st);
+  }
+  if (bn == 64) return launch_conv_tc<64, false>(a, grid, st);
+  if (bn == 128) return launch_conv_tc<128, false>(a, grid, st);
+  return launch_conv_tc<256, false>(a, grid, st);
+}
+
+int tc_forward(const ConvGeom& g, View4 x, View4 w, const float* bias, long long bias_stride, float* y, void* ws,
+               size_t ws_bytes, cudaStream_t st) {
+  return conv_tc_run(g, false, x, w, bias, bias_stride, y, ws, ws_bytes, st);
+}
+int tc_dinput(const ConvGeom& g, View4 dy, View4 w, float* dx, void* ws, size_t ws_bytes, cudaStream_t st) {
+  return conv_tc_run(g, true, dy, w, nullptr, 0, dx, ws, ws_bytes, st);
+}
+int tc_dweight(const ConvGeom&, View4, View4, float*, void*, size_t, cudaStream_t) {
+  return fail(B200_EUNSUPPORTED, "tcgen05 dWeight not built yet");
+}
+int tc_gemm(long long, long long, long long, const float*, long long, long long, const float*, long long, long long,
+            const float*, float, float, float*, cudaStream_t) {
+  return B200_EUNSUPPORTED;
+}
+
+}  // namespace b200

@@ -56,6 +56,18 @@ static std::mutex g_init_mutex;
 static int g_device = -1;
 static int g_sms = 0;
 static char g_name[256] = "";
+static int* g_status_word = nullptr;
+
+int* device_status_word() { return g_status_word; }
+int read_device_status(int* out) {
+  if (!g_status_word) return fail(B200_ECUDA, "device status word is not allocated");
+  B200_CUDA(cudaMemcpy(out, g_status_word, sizeof(int), cudaMemcpyDeviceToHost));
+  return B200_OK;
+}
+int clear_device_status() {
+  if (g_status_word) B200_CUDA(cudaMemset(g_status_word, 0, sizeof(int)));
+  return B200_OK;
+}
 
 int ensure_init() {
   if (g_device >= 0) {
@@ -139,7 +151,8 @@ int b200_init(int device_ordinal) {
                 prop.major, prop.minor);
   snprintf(g_name, sizeof g_name, "%s", prop.name);
   g_sms = prop.multiProcessorCount;
-  B200_CUDA(cudaFree(nullptr));
+  B200_CUDA(cudaMalloc(&g_status_word, 256));
+  B200_CUDA(cudaMemset(g_status_word, 0, 256));
   g_device = dev;
   return B200_OK;
 }

@@ -1,0 +1,81 @@
+"""Parity of the tcgen05 (3xTF32) kernels, forced through the C-ABI, against the FP64 oracle.
+Gate: per-output L2-normalised error <= 1e-4; in practice the split keeps it near 1e-6."""
+import numpy as np
+import pytest
+
+import b200conv
+from golden_cases import conv_cases
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+GATE = 1e-4
+
+
+def _rand(shape, seed, scale=1.0):
+    return (np.random.default_rng(seed).standard_normal(shape, dtype=np.float32) * scale).astype(np.float32)
+
+
+def _reference(x, w, b, go, args):
+    return oracle.torch_conv_all(np.ascontiguousarray(x), np.ascontiguousarray(w), b, np.ascontiguousarray(go),
+                                 args["stride"], args["padding"], args["dilation"], args["groups"])
+
+
+def _run_case(xshape, cout, kernel, stride=(1, 1), padding=(0, 0), dilation=(1, 1), groups=1, seed=0,
+              channels_last=False, phases=("y", "dx"), algo="tc"):
+    args = dict(stride=stride, padding=padding, dilation=dilation, groups=groups)
+    g = oracle.geometry(xshape, cout, kernel, **args)
+    x, w = _rand(g.x_shape, seed), _rand(g.w_shape, seed + 1, 0.1)
+    b, go = _rand((cout,), seed + 2), _rand(g.y_shape, seed + 3)
+    if channels_last:
+        x = np.ascontiguousarray(x.transpose(0, 2, 3, 1)).transpose(0, 3, 1, 2)
+        go = np.ascontiguousarray(go.transpose(0, 2, 3, 1)).transpose(0, 3, 1, 2)
+    want = dict(zip(("y", "dx", "dw", "db"), _reference(x, w, b, go, args)))
+    got = {}
+    if "y" in phases:
+        got["y"] = b200conv.conv2d_forward(x, w, b, algo=algo, **args)
+        assert b200conv.last_kernel().startswith("tc_") or algo != "tc"
+    mask = ("dx" in phases, "dw" in phases, "db" in phases)
+    if any(mask):
+        dx, dw, db = b200conv.conv2d_backward(go, x, w, mask=mask, algo=algo, **args)
+        got.update({k: v for k, v in (("dx", dx), ("dw", dw), ("db", db)) if v is not None})
+    assert b200conv.device_status() == 0
+    errs = {k: oracle.rel_l2(got[k], want[k]) for k in got}
+    assert max(errs.values()) <= GATE, errs
+    return errs
+
+
+def test_tc_matches_golden_layer64():
+    c = next(c for c in conv_cases() if c["tag"] == "layer64")
+    args = dict(stride=c["stride"], padding=c["padding"], dilation=c["dilation"], groups=c["groups"])
+    y = b200conv.conv2d_forward(c["x"], c["w"], c["b"], algo="tc", **args)
+    assert b200conv.last_kernel() == "tc_igemm_forward"
+    dx, _, _ = b200conv.conv2d_backward(c["go"], c["x"], c["w"], mask=(True, False, False), algo="tc", **args)
+    assert b200conv.device_status() == 0
+    assert oracle.rel_l2(y, c["y"]) <= GATE
+    assert oracle.rel_l2(dx, c["dx"]) <= GATE
+    np.testing.assert_allclose(y, c["y"], rtol=4e-4, atol=3e-4)
+
+
+@pytest.mark.parametrize("shape", [
+    # (xshape, cout, kernel, kwargs): column tiles of 64/128/256, ragged pixel tiles, multi-tile N
+    ((2, 32, 9, 11), 48, (3, 3), dict(padding=(1, 1))),
+    ((3, 64, 17, 13), 128, (3, 3), dict(padding=(1, 1))),
+    ((2, 96, 14, 14), 256, (3, 3), dict(padding=(1, 1))),
+    ((1, 64, 20, 20), 320, (1, 1), dict()),
+    ((2, 64, 15, 15), 64, (3, 3), dict(stride=(2, 2), padding=(1, 1))),
+    ((2, 64, 12, 16), 64, (3, 3), dict(padding=(2, 2), dilation=(2, 2))),
+    ((1, 128, 10, 10), 64, (3, 5), dict(stride=(2, 1), padding=(1, 2), groups=2)),
+    ((2, 128, 8, 8), 128, (3, 3), dict(padding=(1, 1), groups=4)),
+], ids=lambda s: "x".join(map(str, s[0])) + f"-co{s[1]}-k{s[2][0]}x{s[2][1]}" if isinstance(s, tuple) and len(s) == 4 else None)
+@pytest.mark.parametrize("channels_last", [False, True], ids=["nchw", "nhwc"])
+def test_tc_forward_and_dinput_shapes(shape, channels_last):
+    xshape, cout, kernel, kw = shape
+    groups = kw.get("groups", 1)
+    # the tcgen05 dInput kernel reduces over 32-channel blocks of Cout/groups
+    phases = ("y", "dx") if (cout // groups) % 32 == 0 else ("y",)
+    _run_case(xshape, cout, kernel, channels_last=channels_last, seed=sum(xshape) + cout, phases=phases, **kw)
+
+
+def test_tc_headline_single_layer_config():
+    errs = _run_case((8, 64, 56, 56), 64, (3, 3), padding=(1, 1), seed=0)
+    assert max(errs.values()) < 2e-5, errs

@@ -154,6 +154,23 @@ int b200_conv2d_dweight(const b200_conv_params* p, b200_view4 x, b200_view4 dy, 
 int b200_conv2d_dbias(const b200_conv_params* p, b200_view4 dy, float* db, void* workspace,
                       size_t workspace_bytes, void* stream);
 
+/* dWeight for callers that cannot allocate device memory (no counterpart in the reference).
+ * Same result as b200_conv2d_dweight with the CUDA-core split-K kernel, but the split-K scratch
+ * is a fixed B200_STATIC_SCRATCH_BYTES array inside the library's device image, so the call
+ * performs no cudaMalloc/cudaFree and takes no workspace argument.  Meant for hosts whose
+ * device memory is entirely owned by their own pool, or whose hot loop cannot tolerate the
+ * implicit synchronisation of an allocation.  Requirements and limits:
+ *  - b200_init must have been called before (initialisation allocates; this call does not);
+ *  - fails with B200_EWORKSPACE when 2 * numel(dw) * 4 bytes exceed B200_STATIC_SCRATCH_BYTES;
+ *  - the array is shared by all calls and occupies device memory on every GPU that loads the
+ *    library until process exit; calls whose kernels may overlap on the GPU (different streams)
+ *    race on it and must be ordered by the caller; nothing needs clearing between calls;
+ *  - the first call on a device resolves the array's address and should be made outside any
+ *    stream capture. */
+#define B200_STATIC_SCRATCH_BYTES (16u << 20)
+int b200_conv2d_dweight_static(const b200_conv_params* p, b200_view4 x, b200_view4 dy, float* dw,
+                               void* stream);
+
 /* ---- GEMM (nn.Linear neighbours of the conv path) -------------------------------------- */
 
 /* C[M,N] (contiguous) = alpha * A*B + (beta == 0 ? 0 : beta * bias[n]); A, B arbitrary 2-D

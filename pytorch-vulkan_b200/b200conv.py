@@ -80,6 +80,7 @@ SIGNATURES = {
                                     c_size_t, c_int, c_void_p]),
     "b200_conv2d_dinput": (c_int, [POINTER(ConvParams), View4, View4, c_void_p, c_void_p, c_size_t, c_int, c_void_p]),
     "b200_conv2d_dweight": (c_int, [POINTER(ConvParams), View4, View4, c_void_p, c_void_p, c_size_t, c_int, c_void_p]),
+    "b200_conv2d_dweight_static": (c_int, [POINTER(ConvParams), View4, View4, c_void_p, c_void_p]),
     "b200_conv2d_dbias": (c_int, [POINTER(ConvParams), View4, c_void_p, c_void_p, c_size_t, c_void_p]),
     "b200_gemm": (c_int, [c_int64, c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64,
                           c_void_p, c_float, c_float, c_void_p, c_int, c_void_p]),
@@ -273,6 +274,20 @@ def conv2d_backward(go, x, w, stride=(1, 1), padding=(0, 0), dilation=(1, 1), gr
         check(L.b200_conv2d_dbias(ctypes.byref(p), gv.view4(), out.ptr, ws.ptr if ws else None, n, None))
         db = out.to_numpy((p.cout,))
     return dx, dw, db
+
+
+STATIC_SCRATCH_BYTES = 16 << 20
+
+
+def conv2d_dweight_static(go, x, w_shape, stride=(1, 1), padding=(0, 0), dilation=(1, 1), groups=1):
+    """dw through b200_conv2d_dweight_static: the split-K scratch lives inside the library, so the
+    call itself allocates nothing (the buffers for x, go and dw below are this helper's own)."""
+    init()
+    p = geometry(x.shape, w_shape[0], w_shape[2:], stride, padding, dilation, groups, wcin=w_shape[1])
+    xv, gv = DeviceView(x), DeviceView(go)
+    out = DeviceBuffer(4 * int(np.prod(w_shape)))
+    check(lib().b200_conv2d_dweight_static(ctypes.byref(p), xv.view4(), gv.view4(), out.ptr, None))
+    return out.to_numpy(tuple(w_shape))
 
 
 def gemm(a, b, bias=None, alpha=1.0, beta=0.0, algo="auto"):

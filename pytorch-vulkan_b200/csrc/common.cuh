@@ -23,6 +23,7 @@ int cuda_fail(cudaError_t e, const char* what);
   } while (0)
 
 int ensure_init();
+bool library_is_initialised();  // true once b200_init has bound a device
 int sm_count();
 extern std::atomic<uint64_t> g_launches;
 void note_kernel(const char* name);

@@ -78,6 +78,7 @@ int ensure_init() {
   }
   return b200_init(-1);
 }
+bool library_is_initialised() { return g_device >= 0; }
 // Planning code may run before a device is bound (host-only callers): assume a full B200.
 int sm_count() { return g_sms > 0 ? g_sms : 148; }
 

@@ -300,16 +300,189 @@ __global__ void __launch_bounds__(256) prep_weights_kernel(ConvGeom g, View4 w, 
   lo[i] = l;
 }
 
+
+// ---------------------------------------------------------------------------------------
+// dWeight: D[(tap,ci)][co] = sum over output positions of Xshifted[(tap,ci)][pos] * dY[co][pos].
+// rows  = 128 (tap, ci) pairs of one group, columns = BN output channels, K = positions of one
+// split (32 per K block, lane = position, so NCHW loads are coalesced).  Partials of the splits
+// go to [split][cout][cig*taps] and are summed in ascending order by finalize_kernel.
+// ---------------------------------------------------------------------------------------
+struct DwTcArgs {
+  ConvGeom g;
+  View4 x, dy;
+  float* out;            // dW itself (one split) or the partial buffer
+  long long positions;   // n*oh*ow
+  int span;              // positions per split (multiple of 32)
+  int m_total;           // taps * cig
+  int tiles_m, tiles_n;
+  int* status;
+};
+struct DwRow {
+  long long chan_off;  // (g*cig + ci) * x.s1, or -1 for a padding row
+  int ydelta, xdelta;  // ky*dh - ph, kx*dw - pw
+};
+constexpr int DW_TABLE_BYTES = BLOCK_M * (int)sizeof(DwRow);
+
+template <int BN>
+__global__ void __launch_bounds__(THREADS, 1) dweight_tc_kernel(const DwTcArgs a) {
+  using Cfg = TileCfg<BN>;
+  extern __shared__ unsigned char smem_raw[];
+  const Pipe p = pipe_setup<BN>(smem_raw, GROUP_THREADS, a.status);
+  const uint32_t tmem_acc = *p.tmem_slot_ptr;
+  const ConvGeom& g = a.g;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_per_group = a.tiles_m * a.tiles_n;
+  const int group = blockIdx.x / tiles_per_group;
+  const int tile = blockIdx.x - group * tiles_per_group;
+  const int m0 = (tile / a.tiles_n) * BLOCK_M, n0 = (tile % a.tiles_n) * BN;
+  const int split = blockIdx.y;
+  const long long k_begin = (long long)split * a.span;
+  const long long k_end = min(a.positions, k_begin + a.span);
+  const int kblocks = (int)((k_end - k_begin + KBLK - 1) / KBLK);
+  const int cols_valid = min(BN, g.cog - n0);
+  const int taps = g.kh * g.kw;
+  // row table, placed behind the pipeline control block
+  DwRow* rows = reinterpret_cast<DwRow*>(smem_raw + (p.full - smem_u32(smem_raw)) + 256);
+  if (threadIdx.x < BLOCK_M) {
+    const int m = m0 + threadIdx.x;
+    DwRow r;
+    r.chan_off = -1; r.ydelta = 0; r.xdelta = 0;
+    if (m < a.m_total) {
+      const int tap = m / g.cig, ci = m - tap * g.cig;
+      r.chan_off = ((long long)group * g.cig + ci) * a.x.s1;
+      r.ydelta = (tap / g.kw) * g.dh - g.ph;
+      r.xdelta = (tap % g.kw) * g.dw - g.pw;
+    }
+    rows[threadIdx.x] = r;
+  }
+  __syncthreads();
+
+  if (warp == PRODUCER_WARPS) {
+    mma_loop<BN>(p, tmem_acc, kblocks);
+  } else {
+    const int grp = warp >> 3, wi = warp & 7;
+    const int ohw = g.oh * g.ow;
+    for (int kb = grp; kb < kblocks; kb += 2) {
+      const int s = kb % Cfg::STAGES;
+      const uint32_t it = (uint32_t)(kb / Cfg::STAGES);
+      const long long pos = k_begin + (long long)kb * KBLK + lane;
+      const bool ok = pos < k_end;
+      long long xb = 0, yb = 0;
+      int iy0 = 0, ix0 = 0;
+      if (ok) {
+        const long long b = pos / ohw;
+        const int sp = (int)(pos - b * ohw);
+        const int oy = sp / g.ow, ox = sp - oy * g.ow;
+        iy0 = oy * g.sh; ix0 = ox * g.sw;
+        xb = b * a.x.s0;
+        yb = b * a.dy.s0 + (long long)oy * a.dy.s2 + (long long)ox * a.dy.s3;
+      }
+      if (!mbar_wait(p.empty + 8 * s, (it & 1) ^ 1, p.abort_flag, p.status, STATUS_TIMEOUT_EMPTY)) break;
+      const uint32_t a_hi = p.tiles + s * Cfg::STAGE_BYTES, a_lo = a_hi + Cfg::A_PLANE;
+      const uint32_t b_hi = a_lo + Cfg::A_PLANE, b_lo = b_hi + Cfg::B_PLANE;
+      // A rows: shifted input, 16 consecutive (tap, ci) rows per warp
+#pragma unroll 1
+      for (int r0 = 0; r0 < 16; r0 += 8) {
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const DwRow row = rows[wi * 16 + r0 + j];
+          const int iy = iy0 + row.ydelta, ix = ix0 + row.xdelta;
+          const bool in = ok && row.chan_off >= 0 && iy >= 0 && iy < g.h && ix >= 0 && ix < g.w;
+          v[j] = in ? __ldg(a.x.ptr + xb + row.chan_off + (long long)iy * a.x.s2 + (long long)ix * a.x.s3) : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float h, l;
+          split_tf32(v[j], h, l);
+          const uint32_t o = sw128_offset(wi * 16 + r0 + j, lane);
+          sts_f32(a_hi + o, h);
+          sts_f32(a_lo + o, l);
+        }
+      }
+      // B rows: output gradient, BN/8 consecutive channels per warp
+      constexpr int BROWS = BN / 8;
+#pragma unroll 1
+      for (int r0 = 0; r0 < BROWS; r0 += 8) {
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int r = wi * BROWS + r0 + j;
+          const bool in = ok && r < cols_valid;
+          v[j] = in ? __ldg(a.dy.ptr + yb + ((long long)group * g.cog + n0 + r) * a.dy.s1) : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float h, l;
+          split_tf32(v[j], h, l);
+          const uint32_t o = sw128_offset(wi * BROWS + r0 + j, lane);
+          sts_f32(b_hi + o, h);
+          sts_f32(b_lo + o, l);
+        }
+      }
+      fence_proxy_async();
+      mbar_arrive(p.full + 8 * s);
+    }
+    // ---- epilogue: lane = (tap, ci) row, registers = consecutive output channels ----
+    if (kblocks > 0 && mbar_wait(p.accum, 0, p.abort_flag, p.status, STATUS_TIMEOUT_ACCUM)) {
+      tc_fence_after();
+      const int q = warp & 3, chunk = warp >> 2;
+      const int m = m0 + q * 32 + lane;
+      const bool row_ok = m < a.m_total;
+      const int tap = row_ok ? m / g.cig : 0, ci = row_ok ? m - tap * g.cig : 0;
+      const long long cols = (long long)g.cig * taps;
+      float* out = a.out + ((long long)split * g.cout + (long long)group * g.cog + n0) * cols + (long long)ci * taps + tap;
+      constexpr int COLS_PER_WARP = BN / 4;
+#pragma unroll 1
+      for (int c = 0; c < COLS_PER_WARP; c += 32) {
+        const int col0 = chunk * COLS_PER_WARP + c;
+        if (col0 >= cols_valid) break;
+        float v[32];
+        tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)col0, v);
+        if (row_ok) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (col0 + j < cols_valid) out[(long long)(col0 + j) * cols] = v[j];
+        }
+      }
+    }
+  }
+  pipe_teardown<BN>(p, tmem_acc);
+}
+
 }  // namespace tc
 
 using namespace tc;
 
 static int pick_bn(int nc) { return nc <= 64 ? 64 : (nc <= 128 ? 128 : 256); }
+static void tc_dweight_plan(const ConvGeom& g, size_t budget, int* splits_out, int* span_out, size_t* bytes_out);
 
 bool tc_supported(const ConvGeom& g, int phase) {
   if (phase == B200_PHASE_FORWARD) return g.cig % KBLK == 0 && g.cog >= 16;
   if (phase == B200_PHASE_DINPUT) return g.cog % KBLK == 0 && g.cig >= 16;
+  if (phase == B200_PHASE_DWEIGHT) return g.cog >= 16 && g.cig * g.kh * g.kw >= 32;
   return false;
+}
+
+// Split plan of the tcgen05 dWeight kernel: enough (tile, split) CTAs for about two per SM, every
+// split at least eight K blocks long, partial buffer within the budget; spans are multiples of 32.
+static void tc_dweight_plan(const ConvGeom& g, size_t budget, int* splits_out, int* span_out, size_t* bytes_out) {
+  const long long positions = (long long)g.n * g.oh * g.ow;
+  const int bn = pick_bn(g.cog);
+  const long long tiles = div_up64((long long)g.cig * g.kh * g.kw, BLOCK_M) * div_up64(g.cog, bn) * g.groups;
+  const size_t dw_bytes = sizeof(float) * (size_t)g.cout * g.cig * g.kh * g.kw;
+  long long want = std::max<long long>(1, div_up64(2ll * sm_count(), tiles));
+  want = std::min<long long>(want, std::max<long long>(1, positions / (8 * KBLK)));
+  want = std::min<long long>(want, 65535);
+  want = std::min<long long>(want, (long long)(budget / dw_bytes));
+  long long span = positions, splits = 1;
+  if (want >= 2) {
+    span = div_up64(div_up64(positions, want), KBLK) * KBLK;
+    splits = div_up64(positions, span);
+  }
+  *splits_out = (int)splits;
+  *span_out = (int)std::min<long long>(span, 2147483616ll);
+  *bytes_out = splits > 1 ? (size_t)splits * dw_bytes : 0;
 }
 
 size_t tc_workspace(const ConvGeom& g, int phase, size_t budget, int* splits_out, int* span_out) {
@@ -318,6 +491,14 @@ size_t tc_workspace(const ConvGeom& g, int phase, size_t budget, int* splits_out
   if (span_out) *span_out = 0;
   if (phase == B200_PHASE_FORWARD || phase == B200_PHASE_DINPUT)
     return 2 * sizeof(float) * (size_t)g.cout * g.cig * g.kh * g.kw;  // hi + lo planes
+  if (phase == B200_PHASE_DWEIGHT) {
+    int splits, span;
+    size_t bytes;
+    tc_dweight_plan(g, budget, &splits, &span, &bytes);
+    if (splits_out) *splits_out = splits;
+    if (span_out) *span_out = span;
+    return bytes;
+  }
   return 0;
 }
 
@@ -380,8 +561,42 @@ int tc_forward(const ConvGeom& g, View4 x, View4 w, const float* bias, long long
 int tc_dinput(const ConvGeom& g, View4 dy, View4 w, float* dx, void* ws, size_t ws_bytes, cudaStream_t st) {
   return conv_tc_run(g, true, dy, w, nullptr, 0, dx, ws, ws_bytes, st);
 }
-int tc_dweight(const ConvGeom&, View4, View4, float*, void*, size_t, cudaStream_t) {
-  return fail(B200_EUNSUPPORTED, "tcgen05 dWeight not built yet");
+template <int BN>
+static int launch_dweight_tc(const DwTcArgs& a, dim3 grid, cudaStream_t st) {
+  constexpr int SMEM = TileCfg<BN>::SMEM_BYTES + DW_TABLE_BYTES;
+  static bool configured = false;
+  if (!configured) {
+    B200_CUDA(cudaFuncSetAttribute(dweight_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+    configured = true;
+  }
+  dweight_tc_kernel<BN><<<grid, THREADS, SMEM, st>>>(a);
+  count_launch();
+  return launch_check("dweight_tc_kernel");
+}
+
+int tc_dweight(const ConvGeom& g, View4 x, View4 dy, float* dw, void* ws, size_t ws_bytes, cudaStream_t st) {
+  int splits, span;
+  size_t bytes;
+  tc_dweight_plan(g, ws ? ws_bytes : 0, &splits, &span, &bytes);
+  DwTcArgs a{};
+  a.g = g; a.x = x; a.dy = dy;
+  a.positions = (long long)g.n * g.oh * g.ow;
+  a.span = span;
+  a.m_total = g.cig * g.kh * g.kw;
+  const int bn = pick_bn(g.cog);
+  a.tiles_m = (a.m_total + BLOCK_M - 1) / BLOCK_M;
+  a.tiles_n = (g.cog + bn - 1) / bn;
+  a.out = splits > 1 ? (float*)ws : dw;
+  a.status = device_status_word();
+  if (!a.status) return fail(B200_ECUDA, "device status word is not allocated");
+  const long long gx = (long long)a.tiles_m * a.tiles_n * g.groups;
+  if (gx > 2147483647ll) return fail(B200_ERANGE, "tcgen05 dWeight: grid exceeds launch limits");
+  const dim3 grid((unsigned)gx, (unsigned)splits);
+  int rc = bn == 64 ? launch_dweight_tc<64>(a, grid, st)
+         : bn == 128 ? launch_dweight_tc<128>(a, grid, st) : launch_dweight_tc<256>(a, grid, st);
+  if (rc) return rc;
+  if (splits > 1) return finalize_splits((const float*)ws, dw, (long long)g.cout * a.m_total, splits, st);
+  return B200_OK;
 }
 int tc_gemm(long long, long long, long long, const float*, long long, long long, const float*, long long, long long,
             const float*, float, float, float*, cudaStream_t) {

@@ -49,10 +49,12 @@ def test_tc_matches_golden_layer64():
     args = dict(stride=c["stride"], padding=c["padding"], dilation=c["dilation"], groups=c["groups"])
     y = b200conv.conv2d_forward(c["x"], c["w"], c["b"], algo="tc", **args)
     assert b200conv.last_kernel() == "tc_igemm_forward"
-    dx, _, _ = b200conv.conv2d_backward(c["go"], c["x"], c["w"], mask=(True, False, False), algo="tc", **args)
+    dx, dw, _ = b200conv.conv2d_backward(c["go"], c["x"], c["w"], mask=(True, True, False), algo="tc", **args)
+    assert b200conv.last_kernel() == "tc_igemm_dweight"
     assert b200conv.device_status() == 0
     assert oracle.rel_l2(y, c["y"]) <= GATE
     assert oracle.rel_l2(dx, c["dx"]) <= GATE
+    assert oracle.rel_l2(dw, c["dw"]) <= GATE
     np.testing.assert_allclose(y, c["y"], rtol=4e-4, atol=3e-4)
 
 
@@ -72,10 +74,24 @@ def test_tc_forward_and_dinput_shapes(shape, channels_last):
     xshape, cout, kernel, kw = shape
     groups = kw.get("groups", 1)
     # the tcgen05 dInput kernel reduces over 32-channel blocks of Cout/groups
-    phases = ("y", "dx") if (cout // groups) % 32 == 0 else ("y",)
+    phases = ("y", "dx", "dw") if (cout // groups) % 32 == 0 else ("y", "dw")
     _run_case(xshape, cout, kernel, channels_last=channels_last, seed=sum(xshape) + cout, phases=phases, **kw)
 
 
 def test_tc_headline_single_layer_config():
-    errs = _run_case((8, 64, 56, 56), 64, (3, 3), padding=(1, 1), seed=0)
+    errs = _run_case((8, 64, 56, 56), 64, (3, 3), padding=(1, 1), seed=0, phases=("y", "dx", "dw"))
     assert max(errs.values()) < 2e-5, errs
+
+
+def test_tc_dweight_split_boundaries_and_determinism():
+    # positions straddling K-block and split boundaries; two runs must agree bit for bit
+    for n, hw in ((1, 9), (2, 16), (5, 23), (16, 28)):
+        errs = _run_case((n, 24, hw, hw + 1), 40, (3, 3), padding=(1, 1), seed=n * hw, phases=("dw",))
+        assert errs["dw"] <= GATE
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((8, 32, 30, 30), dtype=np.float32)
+    go = rng.standard_normal((8, 64, 30, 30), dtype=np.float32)
+    w = np.zeros((64, 32, 3, 3), np.float32)
+    a = b200conv.conv2d_backward(go, x, w, padding=(1, 1), mask=(False, True, False), algo="tc")[1]
+    b = b200conv.conv2d_backward(go, x, w, padding=(1, 1), mask=(False, True, False), algo="tc")[1]
+    np.testing.assert_array_equal(a, b)

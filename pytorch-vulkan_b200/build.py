@@ -48,10 +48,42 @@ def build_lib(force=False, verbose=False):
     return LIB
 
 
+def build_torch_extension(force=False):
+    """g++ build of the PrivateUse1 extension torch_vulkan/_C.so (host code only; it links
+    libb200conv.so and the installed torch libraries)."""
+    import sysconfig
+    import torch
+    from torch.utils import cpp_extension
+    build_lib()
+    src_dir = os.path.join(CSRC, "torch_backend")
+    srcs = [os.path.join(src_dir, f) for f in sorted(os.listdir(src_dir)) if f.endswith(".cpp")]
+    deps = srcs + [os.path.join(src_dir, "backend.h"), os.path.join(HERE, "..", "include", "b200conv.h")]
+    out = os.path.join(HERE, "torch_vulkan", "_C.so")
+    if not (force or _newer(out, deps)):
+        return out
+    torch_lib = os.path.join(os.path.dirname(torch.__file__), "lib")
+    incs = [f"-I{p}" for p in cpp_extension.include_paths()] + [f"-I{sysconfig.get_paths()['include']}"]
+    abi = int(torch._C._GLIBCXX_USE_CXX11_ABI)
+    flags = ["-std=c++17", "-O2", "-fPIC", "-shared", "-w", f"-D_GLIBCXX_USE_CXX11_ABI={abi}",
+             "-DTORCH_EXTENSION_NAME=_C", "-DTORCH_API_INCLUDE_EXTENSION_H"]
+    os.makedirs(os.path.join(HERE, "build"), exist_ok=True)
+    objs, procs = [], []
+    for s in srcs:
+        o = os.path.join(HERE, "build", os.path.basename(s) + ".o")
+        objs.append(o)
+        if force or _newer(o, deps):
+            procs.append(subprocess.Popen(["/usr/bin/g++", *[f for f in flags if f != "-shared"], *incs, "-c", s, "-o", o]))
+    for p in procs:
+        if p.wait() != 0:
+            raise RuntimeError("g++ failed")
+    subprocess.check_call(["/usr/bin/g++", "-shared", "-o", out, *objs, f"-L{HERE}", "-lb200conv", f"-L{torch_lib}",
+                           "-ltorch", "-ltorch_cpu", "-lc10", "-ltorch_python",
+                           "-Wl,-rpath,$ORIGIN/..", f"-Wl,-rpath,{torch_lib}"])
+    return out
+
+
 if __name__ == "__main__":
     build_lib(force="--force" in sys.argv, verbose="-v" in sys.argv)
     if "--torch" in sys.argv:
-        sys.path.insert(0, HERE)
-        from torch_backend_build import build_torch_extension
-        build_torch_extension()
+        build_torch_extension(force="--force" in sys.argv)
     print("built", LIB)

@@ -1,0 +1,444 @@
+// ATen registrations on PrivateUse1 for the convolution path and the tensor plumbing its
+// callers need.  Host-side mirror of the reference's operator layer:
+//   convolution_overrideable / convolution_backward_overrideable  csrc/ops/convolution.cpp:641-702
+//   controls (env flags, re-read on every call)                  csrc/ops/convolution.cpp:402-422
+//   dispatch statistics                                          csrc/ops/convolution.cpp:523-538,625-635
+//   mm / mm.out / addmm                                          csrc/ops/mm.cpp:244-383,835-917,1092-1109
+//   empty / empty_strided / copies / views / resize_ / item      csrc/ops/mm.cpp:498-681,942-991,1054-1067
+// No operator here computes on the host: device work is the C ABI's, and there is no CPU
+// fallback registration (unregistered operators raise PyTorch's usual "not implemented" error).
+#include "backend.h"
+
+#include <ATen/EmptyTensor.h>
+#include <ATen/native/Resize.h>
+#include <ATen/ops/_reshape_alias_native.h>
+#include <ATen/ops/as_strided_native.h>
+#include <ATen/ops/view_native.h>
+#include <torch/library.h>
+
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+
+namespace torch_vulkan {
+
+static bool on_device(const at::Tensor& t) { return t.device().type() == c10::DeviceType::PrivateUse1; }
+static const c10::DispatchKeySet kKeys(c10::DispatchKey::PrivateUse1);
+
+// ---- allocation ------------------------------------------------------------------------------
+static at::Tensor empty_memory_format(c10::SymIntArrayRef size, std::optional<at::ScalarType> dtype,
+                                      std::optional<at::Layout>, std::optional<at::Device> device,
+                                      std::optional<bool>, std::optional<at::MemoryFormat> memory_format) {
+  if (device) validate_device(*device);
+  return at::detail::empty_generic(C10_AS_INTARRAYREF_SLOW(size), backend_allocator(), kKeys,
+                                   dtype.value_or(at::kFloat), memory_format);
+}
+static at::Tensor empty_strided(c10::SymIntArrayRef size, c10::SymIntArrayRef stride,
+                                std::optional<at::ScalarType> dtype, std::optional<at::Layout>,
+                                std::optional<at::Device> device, std::optional<bool>) {
+  if (device) validate_device(*device);
+  return at::detail::empty_strided_generic(C10_AS_INTARRAYREF_SLOW(size), C10_AS_INTARRAYREF_SLOW(stride),
+                                           backend_allocator(), kKeys, dtype.value_or(at::kFloat));
+}
+
+// ---- copies ------------------------------------------------------------------------------------
+static bool dense_standard(const at::Tensor& t) { return t.is_contiguous(); }
+
+static at::Tensor device_contiguous(const at::Tensor& t) {  // strided device view -> dense device tensor
+  if (dense_standard(t)) return t;
+  auto out = at::empty(t.sizes(), t.options());
+  if (t.numel())
+    B200_TORCH_CHECK(b200_gather_strided(out.data_ptr(), t.const_data_ptr(), (int)t.dim(), t.sizes().data(),
+                                         t.strides().data(), (int)t.element_size(), backend_stream()));
+  return out;
+}
+
+// dst (device, any strides) <- dense device tensor of the same dtype and shape
+static void device_assign(const at::Tensor& dst, const at::Tensor& dense) {
+  if (!dst.numel()) return;
+  if (dense_standard(dst))
+    B200_TORCH_CHECK(b200_memcpy(dst.data_ptr(), dense.const_data_ptr(), dst.nbytes(), B200_D2D, backend_stream()));
+  else
+    B200_TORCH_CHECK(b200_scatter_strided(dst.data_ptr(), dense.const_data_ptr(), (int)dst.dim(), dst.sizes().data(),
+                                          dst.strides().data(), (int)dst.element_size(), backend_stream()));
+}
+
+static at::Tensor copy_from(const at::Tensor& src, const at::Tensor& dst, bool /*non_blocking*/) {
+  TORCH_CHECK(src.element_size() <= 8 && dst.element_size() <= 8, "Vulkan copy: unsupported element size");
+  if (!on_device(src)) {  // host -> device
+    TORCH_CHECK(src.device().is_cpu() && on_device(dst), "Vulkan copy: unsupported device pair");
+    const auto host = src.to(dst.scalar_type()).expand(dst.sizes()).contiguous();
+    if (!host.numel()) return dst;
+    if (dense_standard(dst)) {
+      B200_TORCH_CHECK(b200_memcpy(dst.data_ptr(), host.const_data_ptr(), host.nbytes(), B200_H2D, backend_stream()));
+    } else {
+      auto staged = at::empty(dst.sizes(), dst.options());
+      B200_TORCH_CHECK(b200_memcpy(staged.data_ptr(), host.const_data_ptr(), host.nbytes(), B200_H2D, backend_stream()));
+      device_assign(dst, staged);
+    }
+    // the host tensor may be pageable and is released on return
+    B200_TORCH_CHECK(b200_stream_sync(backend_stream()));
+    return dst;
+  }
+  if (!on_device(dst)) {  // device -> host
+    TORCH_CHECK(dst.device().is_cpu(), "Vulkan copy: unsupported device pair");
+    const auto dense = device_contiguous(src.expand(dst.sizes()));
+    auto host = at::empty(dense.sizes(), dense.options().device(at::kCPU));
+    if (dense.numel()) {
+      B200_TORCH_CHECK(b200_memcpy(host.data_ptr(), dense.const_data_ptr(), dense.nbytes(), B200_D2H, backend_stream()));
+      B200_TORCH_CHECK(b200_stream_sync(backend_stream()));
+      note_host_read(dense.nbytes());
+    }
+    dst.copy_(host);
+    return dst;
+  }
+  // device -> device
+  if (src.scalar_type() != dst.scalar_type()) {  // dtype conversion is not part of this path: stage through the host
+    ++execution_stats().cpu_fallback_calls;
+    return copy_from(src.cpu().to(dst.scalar_type()), dst, false);
+  }
+  device_assign(dst, device_contiguous(src.expand(dst.sizes())));
+  return dst;
+}
+
+static void resize_storage(const at::Tensor& self, size_t bytes) {
+  auto* impl = self.storage().unsafeGetStorageImpl();
+  if (bytes <= impl->nbytes()) return;
+  auto next = backend_allocator()->allocate(bytes);
+  if (impl->nbytes() && impl->data())
+    B200_TORCH_CHECK(b200_memcpy(next.get(), impl->data(), impl->nbytes(), B200_D2D, backend_stream()));
+  impl->set_data_ptr_noswap(std::move(next));
+  impl->set_nbytes(bytes);
+}
+
+static const at::Tensor& resize_(const at::Tensor& self, c10::SymIntArrayRef size,
+                                 std::optional<at::MemoryFormat> memory_format) {
+  const auto sizes = C10_AS_INTARRAYREF_SLOW(size);
+  int64_t numel = 1;
+  for (auto s : sizes) numel *= s;
+  resize_storage(self, (size_t)(self.storage_offset() + numel) * self.element_size());
+  self.unsafeGetTensorImpl()->set_sizes_contiguous(sizes);
+  if (memory_format && *memory_format != at::MemoryFormat::Preserve && *memory_format != at::MemoryFormat::Contiguous)
+    self.unsafeGetTensorImpl()->empty_tensor_restride(*memory_format);
+  return self;
+}
+
+static at::Tensor copy_from_and_resize(const at::Tensor& src, const at::Tensor& dst) {
+  if (dst.sizes() != src.sizes()) {
+    std::vector<c10::SymInt> sz(src.sizes().begin(), src.sizes().end());
+    resize_(dst, sz, std::nullopt);
+  }
+  return copy_from(src, dst, false);
+}
+
+static at::Scalar local_scalar_dense(const at::Tensor& self) {
+  TORCH_CHECK(self.numel() == 1, "a Tensor with ", self.numel(), " elements cannot be converted to Scalar");
+  return self.cpu().item();
+}
+
+static at::Tensor& fill_scalar(at::Tensor& self, const at::Scalar& value) {
+  if (!self.numel()) return self;
+  if (value.toDouble() == 0.0 && dense_standard(self)) {
+    B200_TORCH_CHECK(b200_memset(self.data_ptr(), 0, self.nbytes(), backend_stream()));
+    return self;
+  }
+  copy_from(at::full(self.sizes(), value, self.options().device(at::kCPU)), self, false);
+  return self;
+}
+static at::Tensor& zero_(at::Tensor& self) { return fill_scalar(self, 0); }
+
+// ---- views -------------------------------------------------------------------------------------
+static at::Tensor view(const at::Tensor& self, c10::SymIntArrayRef size) {
+  return at::native::view(self, C10_AS_INTARRAYREF_SLOW(size));
+}
+static at::Tensor as_strided(const at::Tensor& self, c10::SymIntArrayRef size, c10::SymIntArrayRef stride,
+                             std::optional<c10::SymInt> storage_offset) {
+  std::optional<int64_t> off;
+  if (storage_offset) off = storage_offset->expect_int();
+  return at::native::as_strided_tensorimpl(self, C10_AS_INTARRAYREF_SLOW(size), C10_AS_INTARRAYREF_SLOW(stride), off);
+}
+static at::Tensor reshape_alias(const at::Tensor& self, c10::SymIntArrayRef size, c10::SymIntArrayRef stride) {
+  return at::native::_reshape_alias(self, C10_AS_INTARRAYREF_SLOW(size), C10_AS_INTARRAYREF_SLOW(stride));
+}
+
+// ---- convolution -------------------------------------------------------------------------------
+static std::mutex plan_mutex;
+static std::map<std::string, uint64_t> plan_stats;
+
+std::map<std::string, uint64_t> conv_dispatch_stats() {
+  std::lock_guard<std::mutex> lock(plan_mutex);
+  auto result = plan_stats;
+  for (const char* key : {"hits", "misses", "tunes", "evictions", "candidates_timed", "entries"}) result[key] += 0;
+  return result;
+}
+void clear_conv_dispatch_cache() {
+  std::lock_guard<std::mutex> lock(plan_mutex);
+  plan_stats.clear();
+}
+
+static size_t workspace_limit() {
+  const char* value = std::getenv("TORCH_VULKAN_CONV_WORKSPACE_MB");
+  if (!value || !*value) return 64ull * 1024 * 1024;
+  char* end = nullptr;
+  const auto mb = std::strtoull(value, &end, 10);
+  TORCH_CHECK(*value != '-' && end != value && *end == '\0' && mb <= 4096,
+              "TORCH_VULKAN_CONV_WORKSPACE_MB must be an integer in [0,4096]");
+  return mb * 1024 * 1024;
+}
+
+// Maps the reference's env controls onto this library's candidates.  forward: auto / direct /
+// tiled / depthwise / winograd; backward: auto / direct / optimized.  "tiled"/"optimized" force the
+// implicit-GEMM family (tcgen05 when the geometry allows, CUDA cores otherwise); the GLSL tile
+// menu (TORCH_VULKAN_CONV_TILE) has no meaning here and is validated, then ignored.
+static int requested_algo(int phase, const b200_conv_params& p) {
+  const char* name = phase == B200_PHASE_FORWARD ? "TORCH_VULKAN_CONV_ALGO" : "TORCH_VULKAN_CONV_BACKWARD_ALGO";
+  const char* raw = std::getenv(name);
+  const std::string algo = raw && *raw ? raw : "auto";
+  const bool fwd = phase == B200_PHASE_FORWARD;
+  TORCH_CHECK(algo == "auto" || algo == "direct" ||
+                  (fwd ? algo == "tiled" || algo == "depthwise" || algo == "winograd" : algo == "optimized"),
+              name, " has an invalid algorithm (forward: auto/direct/tiled/depthwise/winograd; backward: auto/direct/optimized)");
+  const char* tile = std::getenv("TORCH_VULKAN_CONV_TILE");
+  if (tile && *tile) {
+    bool known = false;
+    for (const char* t : {"auto", "base", "wide", "tall", "register", "register3", "register3_hoist"}) known |= !std::strcmp(tile, t);
+    TORCH_CHECK(known, "TORCH_VULKAN_CONV_TILE must be auto/base/wide/tall/register/register3/register3_hoist");
+  }
+  const char* tune = std::getenv("TORCH_VULKAN_CONV_AUTOTUNE");
+  TORCH_CHECK(!tune || !*tune || !std::strcmp(tune, "0") || !std::strcmp(tune, "1"),
+              "TORCH_VULKAN_CONV_AUTOTUNE must be 0 or 1");
+  if (algo == "direct") return B200_ALGO_DIRECT;
+  if (algo == "winograd") return B200_ALGO_WINOGRAD;
+  if (algo == "depthwise") {
+    TORCH_CHECK(p.groups == p.cin, "Forced Vulkan convolution forward candidate depthwise exceeds device limits, "
+                                   "workspace budget, or operator applicability");
+    return B200_ALGO_DIRECT;
+  }
+  if (algo == "tiled" || algo == "optimized") {
+    const int tc = b200_conv2d_select(&p, phase, B200_ALGO_TC, 0);
+    return tc == B200_ALGO_TC ? B200_ALGO_TC : B200_ALGO_TILED;
+  }
+  return B200_ALGO_AUTO;
+}
+
+static const char* phase_name(int phase) {
+  static const char* names[] = {"forward", "dinput", "dweight", "dbias"};
+  return names[phase];
+}
+static const char* candidate_name(int algo, int phase) {
+  switch (algo) {
+    case B200_ALGO_DIRECT: return "direct";
+    case B200_ALGO_TILED: return phase == B200_PHASE_DBIAS ? "reduce" : "tiled_simt";
+    case B200_ALGO_TC: return "tiled_tcgen05";
+    case B200_ALGO_WINOGRAD: return "winograd_f4";
+    default: return "auto";
+  }
+}
+
+struct Scratch {
+  at::Tensor tensor;
+  void* ptr = nullptr;
+  size_t bytes = 0;
+};
+// Resolves the candidate, enforces the workspace budget and allocates the scratch it needs.
+static int plan(const b200_conv_params& p, int phase, const at::TensorOptions& opts, Scratch& scratch) {
+  const size_t budget = workspace_limit();
+  const int requested = phase == B200_PHASE_DBIAS ? B200_ALGO_AUTO : requested_algo(phase, p);
+  const int chosen = b200_conv2d_select(&p, phase, requested, budget);
+  TORCH_CHECK(chosen >= 0, "Forced Vulkan convolution ", phase_name(phase), " candidate: ", b200_last_error());
+  int algo = requested;
+  size_t need = b200_conv2d_workspace(&p, phase, requested, budget);
+  if (chosen == B200_ALGO_TC && (phase == B200_PHASE_FORWARD || phase == B200_PHASE_DINPUT) && need > budget) {
+    // the staged weight planes do not fit the budget: a forced request fails like the reference's
+    // forced tiled dWeight with a zero budget, an automatic one takes the CUDA-core kernel
+    TORCH_CHECK(requested == B200_ALGO_AUTO, "Forced Vulkan convolution ", phase_name(phase),
+                " candidate exceeds device limits, workspace budget, or operator applicability");
+    algo = B200_ALGO_TILED;
+    need = 0;
+  }
+  if (phase == B200_PHASE_DWEIGHT && requested != B200_ALGO_AUTO && requested != B200_ALGO_DIRECT && need == 0 &&
+      (int64_t)p.n * p.oh * p.ow > 256 && budget == 0)
+    TORCH_CHECK(false, "Forced Vulkan convolution dweight candidate exceeds device limits, workspace budget, "
+                       "or operator applicability");
+  if (need) {
+    scratch.tensor = at::empty({(int64_t)need}, opts.dtype(at::kByte));
+    scratch.ptr = scratch.tensor.data_ptr();
+    scratch.bytes = need;
+  }
+  {
+    std::lock_guard<std::mutex> lock(plan_mutex);
+    const int shown = algo == B200_ALGO_AUTO ? chosen : b200_conv2d_select(&p, phase, algo, budget);
+    ++plan_stats[std::string("selected_") + phase_name(phase) + "_" + candidate_name(shown, phase)];
+    if (phase == B200_PHASE_DWEIGHT && need) {
+      const size_t dw_bytes = sizeof(float) * (size_t)p.cout * (p.cin / p.groups) * p.kh * p.kw;
+      plan_stats["dweight_tiled_split_count_total"] += need / dw_bytes;
+      plan_stats["dweight_tiled_workspace_bytes_total"] += need;
+      ++plan_stats["dweight_tiled_dispatches"];
+    }
+  }
+  return algo;
+}
+
+static b200_view4 view_of(const at::Tensor& t) {
+  b200_view4 v{t.const_data_ptr<float>(), {0, 0, 0, 0}};
+  for (int64_t d = 0; d < t.dim(); ++d) v.stride[d] = t.stride(d);
+  return v;
+}
+static void require_fp32_device(const at::Tensor& t) {
+  TORCH_CHECK(on_device(t) && t.scalar_type() == at::kFloat, "Vulkan convolution requires FP32 Vulkan tensors");
+}
+
+static b200_conv_params conv_params(const at::Tensor& input, const at::Tensor& weight, c10::SymIntArrayRef stride,
+                                    c10::SymIntArrayRef padding, c10::SymIntArrayRef dilation, bool transposed,
+                                    c10::SymIntArrayRef output_padding, const c10::SymInt& groups) {
+  TORCH_CHECK(!transposed, "Vulkan ConvTranspose is not implemented yet");
+  TORCH_CHECK(input.dim() == 4 && weight.dim() == 4, "Vulkan convolution supports NCHW tensors only");
+  TORCH_CHECK(stride.size() == 2 && padding.size() == 2 && dilation.size() == 2 && output_padding.size() == 2,
+              "Vulkan convolution requires two spatial dimensions");
+  TORCH_CHECK(output_padding[0].expect_int() == 0 && output_padding[1].expect_int() == 0,
+              "Vulkan convolution: output_padding requires transposed convolution");
+  require_fp32_device(input);
+  require_fp32_device(weight);
+  b200_conv_params p;
+  const int rc = b200_conv2d_geometry(&p, input.size(0), input.size(1), weight.size(0), input.size(2), input.size(3),
+                                      weight.size(1), weight.size(2), weight.size(3), stride[0].expect_int(),
+                                      stride[1].expect_int(), padding[0].expect_int(), padding[1].expect_int(),
+                                      dilation[0].expect_int(), dilation[1].expect_int(), groups.expect_int());
+  TORCH_CHECK(rc == 0, "Vulkan ", b200_last_error());
+  return p;
+}
+
+static at::Tensor convolution_overrideable(const at::Tensor& input, const at::Tensor& weight,
+                                           const std::optional<at::Tensor>& bias, c10::SymIntArrayRef stride,
+                                           c10::SymIntArrayRef padding, c10::SymIntArrayRef dilation, bool transposed,
+                                           c10::SymIntArrayRef output_padding, c10::SymInt groups) {
+  TORCH_CHECK(input.dim() != 5 && input.scalar_type() != at::kLong,
+              "Vulkan convolution: only FP32 Conv2D is implemented by this backend build");
+  const auto p = conv_params(input, weight, stride, padding, dilation, transposed, output_padding, groups);
+  const float* bias_ptr = nullptr;
+  int64_t bias_stride = 0;
+  if (bias && bias->defined()) {
+    TORCH_CHECK(bias->numel() == p.cout && bias->scalar_type() == at::kFloat && on_device(*bias),
+                "Vulkan convolution: bias shape/dtype mismatch");
+    bias_ptr = bias->const_data_ptr<float>();
+    bias_stride = bias->dim() ? bias->stride(bias->dim() - 1) : 0;
+  }
+  auto result = at::empty({p.n, p.cout, p.oh, p.ow}, input.options());  // always contiguous NCHW
+  Scratch scratch;
+  const int algo = plan(p, B200_PHASE_FORWARD, input.options(), scratch);
+  B200_TORCH_CHECK(b200_conv2d_forward(&p, view_of(input), view_of(weight), bias_ptr, bias_stride,
+                                       result.data_ptr<float>(), scratch.ptr, scratch.bytes, algo, backend_stream()));
+  return result;
+}
+
+static std::tuple<at::Tensor, at::Tensor, at::Tensor> convolution_backward_overrideable(
+    const at::Tensor& grad_output, const at::Tensor& input, const at::Tensor& weight, c10::SymIntArrayRef stride,
+    c10::SymIntArrayRef padding, c10::SymIntArrayRef dilation, bool transposed, c10::SymIntArrayRef output_padding,
+    c10::SymInt groups, std::array<bool, 3> output_mask) {
+  TORCH_CHECK(input.dim() != 5, "Vulkan convolution: only FP32 Conv2D is implemented by this backend build");
+  const auto p = conv_params(input, weight, stride, padding, dilation, transposed, output_padding, groups);
+  TORCH_CHECK(grad_output.dim() == 4 && grad_output.size(0) == p.n && grad_output.size(1) == p.cout &&
+                  grad_output.size(2) == p.oh && grad_output.size(3) == p.ow,
+              "Vulkan convolution backward: output gradient shape mismatch");
+  require_fp32_device(grad_output);
+  at::Tensor dx, dw, db;
+  if (output_mask[0]) {
+    dx = at::empty(input.sizes(), input.options().memory_format(at::MemoryFormat::Contiguous));
+    Scratch scratch;
+    const int algo = plan(p, B200_PHASE_DINPUT, input.options(), scratch);
+    B200_TORCH_CHECK(b200_conv2d_dinput(&p, view_of(grad_output), view_of(weight), dx.data_ptr<float>(), scratch.ptr,
+                                        scratch.bytes, algo, backend_stream()));
+  }
+  if (output_mask[1]) {
+    dw = at::empty(weight.sizes(), weight.options().memory_format(at::MemoryFormat::Contiguous));
+    Scratch scratch;
+    const int algo = plan(p, B200_PHASE_DWEIGHT, input.options(), scratch);
+    B200_TORCH_CHECK(b200_conv2d_dweight(&p, view_of(input), view_of(grad_output), dw.data_ptr<float>(), scratch.ptr,
+                                         scratch.bytes, algo, backend_stream()));
+  }
+  if (output_mask[2]) {
+    db = at::empty({p.cout}, weight.options());
+    Scratch scratch;
+    plan(p, B200_PHASE_DBIAS, input.options(), scratch);
+    B200_TORCH_CHECK(b200_conv2d_dbias(&p, view_of(grad_output), db.data_ptr<float>(), scratch.ptr, scratch.bytes,
+                                       backend_stream()));
+  }
+  return {dx, dw, db};
+}
+
+// ---- mm / addmm ----------------------------------------------------------------------------------
+static void gemm_into(const at::Tensor& a, const at::Tensor& b, const float* bias, float alpha, float beta,
+                      at::Tensor& out) {
+  B200_TORCH_CHECK(b200_gemm(a.size(0), b.size(1), a.size(1), a.const_data_ptr<float>(), a.stride(0), a.stride(1),
+                             b.const_data_ptr<float>(), b.stride(0), b.stride(1), bias, alpha, beta,
+                             out.data_ptr<float>(), B200_ALGO_AUTO, backend_stream()));
+}
+static void check_mm(const at::Tensor& a, const at::Tensor& b) {
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2, "mm: both arguments must be matrices");
+  TORCH_CHECK(a.size(1) == b.size(0), "mm: matrix shapes cannot be multiplied (", a.size(0), "x", a.size(1), " and ",
+              b.size(0), "x", b.size(1), ")");
+  TORCH_CHECK(on_device(a) && on_device(b) && a.scalar_type() == at::kFloat && b.scalar_type() == at::kFloat,
+              "Vulkan mm supports FP32 Vulkan tensors only");
+}
+static at::Tensor mm(const at::Tensor& a, const at::Tensor& b) {
+  check_mm(a, b);
+  auto out = at::empty({a.size(0), b.size(1)}, a.options());
+  if (!out.numel()) return out;
+  if (!a.size(1)) return torch_vulkan::zero_(out);
+  gemm_into(a, b, nullptr, 1.f, 0.f, out);
+  return out;
+}
+static at::Tensor& mm_out(const at::Tensor& a, const at::Tensor& b, at::Tensor& out) {
+  check_mm(a, b);
+  const std::vector<int64_t> shape = {a.size(0), b.size(1)};
+  if (out.sizes() != at::IntArrayRef(shape)) {
+    std::vector<c10::SymInt> sz(shape.begin(), shape.end());
+    resize_(out, sz, std::nullopt);
+  }
+  if (!out.numel()) return out;
+  // the output may alias an operand or be a strided view: compute into a fresh tensor first
+  auto result = torch_vulkan::mm(a, b);
+  copy_from(result, out, false);
+  return out;
+}
+static at::Tensor addmm(const at::Tensor& self, const at::Tensor& mat1, const at::Tensor& mat2, const at::Scalar& beta,
+                        const at::Scalar& alpha) {
+  TORCH_CHECK(mat1.dim() == 2 && mat2.dim() == 2, "addmm: mat1 and mat2 must be matrices");
+  TORCH_CHECK(mat1.size(1) == mat2.size(0), "addmm: matrix shapes cannot be multiplied");
+  TORCH_CHECK(self.device() == mat1.device() && self.device() == mat2.device(),
+              "addmm: all tensors must be on the same device");
+  TORCH_CHECK(self.scalar_type() == mat1.scalar_type() && self.scalar_type() == mat2.scalar_type(),
+              "addmm: all tensors must have the same dtype");
+  const std::vector<int64_t> shape = {mat1.size(0), mat2.size(1)};
+  const auto expanded = self.expand(shape);  // validates broadcasting even when beta is zero
+  check_mm(mat1, mat2);
+  auto out = at::empty(shape, mat1.options());
+  if (!out.numel()) return out;
+  const float b = beta.toFloat(), a = alpha.toFloat();
+  TORCH_CHECK(self.dim() <= 1 || (self.dim() == 2 && self.size(0) == 1) || b == 0.f,
+              "Vulkan addmm: only a bias broadcast along rows (1-D, or [1,N]) is fused by this backend build");
+  at::Tensor bias = device_contiguous(self.dim() == 0 ? self.expand({shape[1]}) : self.reshape({-1}).expand({shape[1]}));
+  gemm_into(mat1, mat2, bias.const_data_ptr<float>(), a, b, out);
+  return out;
+}
+
+TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
+  m.impl("empty.memory_format", &empty_memory_format);
+  m.impl("empty_strided", &empty_strided);
+  m.impl("_copy_from", &copy_from);
+  m.impl("_copy_from_and_resize", &copy_from_and_resize);
+  m.impl("_local_scalar_dense", &local_scalar_dense);
+  m.impl("fill_.Scalar", &fill_scalar);
+  m.impl("zero_", &zero_);
+  m.impl("resize_", &resize_);
+  m.impl("view", &view);
+  m.impl("as_strided", &as_strided);
+  m.impl("_reshape_alias", &reshape_alias);
+  m.impl("convolution_overrideable", &convolution_overrideable);
+  m.impl("convolution_backward_overrideable", &convolution_backward_overrideable);
+  m.impl("mm", &mm);
+  m.impl("mm.out", &mm_out);
+  m.impl("addmm", &addmm);
+}
+
+}  // namespace torch_vulkan

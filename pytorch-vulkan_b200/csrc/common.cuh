@@ -79,6 +79,11 @@ int tc_dweight(const ConvGeom& g, View4 x, View4 dy, float* dw, void* ws, size_t
 int tc_gemm(long long M, long long N, long long K, const float* A, long long sa0, long long sa1, const float* B,
             long long sb0, long long sb1, const float* bias, float alpha, float beta, float* C, cudaStream_t st);
 
+// persistent strip kernel for stride-1 "same" convolutions (conv_tc_strip.cu)
+bool strip_supported(const ConvGeom& g, int phase);
+int strip_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* bias, long long bias_stride, float* out,
+               void* ws, size_t ws_bytes, cudaStream_t st);
+
 int* device_status_word();  // device memory, zero unless a bounded wait gave up
 int read_device_status(int* out);
 int clear_device_status();

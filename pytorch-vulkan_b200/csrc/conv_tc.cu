@@ -22,6 +22,8 @@
 #include "tc_common.cuh"
 
 #include <algorithm>
+#include <cstdlib>
+#include <cstring>
 
 namespace b200 {
 namespace tc {
@@ -554,11 +556,26 @@ static int conv_tc_run(const ConvGeom& g, bool is_dx, View4 act, View4 w, const 
   return launch_conv_tc<256, false>(a, grid, st);
 }
 
+// B200_CONV_TC_VARIANT=gather forces the per-tap gather kernel where the strip kernel would run
+// (A/B measurements); anything else lets the strip kernel take the geometries it supports.
+static bool strip_allowed() {
+  const char* v = getenv("B200_CONV_TC_VARIANT");
+  return !(v && !strcmp(v, "gather"));
+}
+
 int tc_forward(const ConvGeom& g, View4 x, View4 w, const float* bias, long long bias_stride, float* y, void* ws,
                size_t ws_bytes, cudaStream_t st) {
+  if (strip_allowed() && strip_supported(g, B200_PHASE_FORWARD)) {
+    note_kernel("tc_strip_forward");
+    return strip_conv(g, false, x, w, bias, bias_stride, y, ws, ws_bytes, st);
+  }
   return conv_tc_run(g, false, x, w, bias, bias_stride, y, ws, ws_bytes, st);
 }
 int tc_dinput(const ConvGeom& g, View4 dy, View4 w, float* dx, void* ws, size_t ws_bytes, cudaStream_t st) {
+  if (strip_allowed() && strip_supported(g, B200_PHASE_DINPUT)) {
+    note_kernel("tc_strip_dinput");
+    return strip_conv(g, true, dy, w, nullptr, 0, dx, ws, ws_bytes, st);
+  }
   return conv_tc_run(g, true, dy, w, nullptr, 0, dx, ws, ws_bytes, st);
 }
 template <int BN>

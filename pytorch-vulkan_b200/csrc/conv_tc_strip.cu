@@ -1,0 +1,408 @@
+// Persistent tcgen05 implicit-GEMM kernel for stride-1 "same" convolutions (3x3 pad 1, 1x1,
+// 5x5 pad 2, dilated 3x3 with matching padding ...), forward and dInput, FP32 via 3xTF32.
+//
+// Idea: the nine (kh*kw) filter taps of one 32-channel block all read the same activations,
+// shifted by whole pixels.  The activations of a tile are therefore staged ONCE per channel
+// block as a "strip" in shared memory -- one 128-byte row (32 channels, TF32 hi and lo planes)
+// per pixel of a zero-padded pixel space -- and every tap's tcgen05.mma reads that strip through
+// a matrix descriptor whose start address is moved by `shift(tap)` rows.  (The 128-byte swizzle
+// is a function of the absolute shared-memory address, so a descriptor may start at any row.)
+// Compared with gathering an operand tile per tap this issues kh*kw times fewer global loads,
+// TF32 splits and shared-memory stores, which is what lets the tensor pipe stay busy.
+//
+// Padded pixel space: images are laid out with `pc` zero columns after every row and `pr` zero
+// rows after every image (pc = pad_w, pr = pad_h), q = (n*(H+pr) + y)*(W+pc) + x.  A tap offset
+// (dy, dx) is then the constant row shift dy*(W+pc) + dx for every pixel, and reads that leave the
+// image land on zero rows of the strip.  Accumulator rows that fall on padding are discarded.
+//
+// CTA roles (672 threads, persistent over tiles of 128 padded pixels x BN output channels):
+//   warps 0-3    epilogue: tcgen05.ld of a finished accumulator, bias, coalesced NCHW stores
+//   warps 4-11   strip producers: gather from the caller's strided view, split_tf32, swizzled stores
+//   warps 12-19  weight producers: K-contiguous staged weights -> split_tf32 -> swizzled stores
+//   warp 20      TMEM allocation and the tcgen05.mma stream (lo*hi, hi*lo, hi*hi per tap)
+// The accumulator is double-buffered in TMEM, so the epilogue of tile i overlaps the main loop of
+// tile i+1.  All hand-offs are mbarriers with bounded waits.
+//
+// Replaces csrc/shaders/conv2d_tiled_body.glsl:53-86 and
+// csrc/shaders/conv2d_backward_input_tiled_body.glsl:49-93 of the reference for these geometries.
+#include "common.cuh"
+#include "tc_common.cuh"
+
+#include <algorithm>
+
+namespace b200 {
+namespace tcs {
+using namespace tc;
+
+constexpr int BLOCK_M = 128, KBLK = 32;
+constexpr int EPI_WARPS = 4, A_WARPS = 8, W_WARPS = 8;
+constexpr int A_THREADS = A_WARPS * 32, W_THREADS = W_WARPS * 32;
+constexpr int MMA_WARP = EPI_WARPS + A_WARPS + W_WARPS;
+constexpr int THREADS = (MMA_WARP + 1) * 32;
+constexpr int MAX_TAPS = 64;
+constexpr int MAX_STAGES = 4;
+constexpr int SMEM_LIMIT = 232448 - 2048;  // 227 KB per CTA minus the control block and alignment slack
+
+struct StripArgs {
+  ConvGeom g;
+  View4 act;              // forward: x.  dInput: dy (same spatial size as the output)
+  const float* wp;        // staged weights [groups][nc][taps][kc], raw FP32
+  const float* bias;
+  long long bias_stride;
+  float* out;             // contiguous NCHW [n][out_channels][H][W]
+  int H, W, pr, pc;       // image size and padding rows/cols of the padded pixel space
+  int kc, nc, out_channels;
+  int cblocks, taps, tiles_n;
+  long long q_total, tiles_m, tiles_total;
+  int halo, strip_rows;   // strip_rows is a multiple of 8
+  int a_stages, w_stages;
+  int is_dx;
+  int* status;
+};
+
+struct Ctrl {  // lives behind the operand stages in shared memory
+  unsigned long long a_full[2], a_empty[2], w_full[MAX_STAGES], w_empty[MAX_STAGES], acc_full[2], acc_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+  int shift[MAX_TAPS];
+};
+
+template <int BN>
+__global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs a) {
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t tiles_base = (raw + 1023u) & ~1023u;
+  const uint32_t a_stage_bytes = (uint32_t)a.strip_rows * 256u, a_plane = (uint32_t)a.strip_rows * 128u;
+  constexpr uint32_t w_stage_bytes = BN * 256u, w_plane = BN * 128u;
+  const uint32_t w_base = tiles_base + a.a_stages * a_stage_bytes;
+  Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem_raw + (w_base - raw) + a.w_stages * w_stage_bytes);
+  volatile int* abort_flag = &ctrl->abort_flag;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const ConvGeom& g = a.g;
+  constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(smem_u32(&ctrl->a_full[s]), A_THREADS);
+      mbar_init(smem_u32(&ctrl->a_empty[s]), 1);
+      mbar_init(smem_u32(&ctrl->acc_full[s]), 1);
+      mbar_init(smem_u32(&ctrl->acc_empty[s]), EPI_WARPS * 32);
+    }
+    for (int s = 0; s < MAX_STAGES; ++s) {
+      mbar_init(smem_u32(&ctrl->w_full[s]), W_THREADS);
+      mbar_init(smem_u32(&ctrl->w_empty[s]), 1);
+    }
+    ctrl->abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (threadIdx.x < a.taps) {
+    const int ky = threadIdx.x / g.kw, kx = threadIdx.x - ky * g.kw;
+    const int s = (ky * g.dh - g.ph) * (a.W + a.pc) + (kx * g.dw - g.pw);
+    ctrl->shift[threadIdx.x] = a.is_dx ? -s : s;
+  }
+  if (warp == MMA_WARP) tmem_alloc(smem_u32(&ctrl->tmem_base), TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&ctrl->tmem_base);
+
+  const int row_pitch = a.W + a.pc;
+  const long long img_pitch = (long long)(a.H + a.pr) * row_pitch;
+
+  if (warp == MMA_WARP) {
+    // ------------------------------ MMA issuer ------------------------------
+    constexpr uint32_t idesc = make_idesc_tf32(BLOCK_M, BN);
+    uint32_t a_count = 0, w_count = 0, t_count = 0;
+    bool alive = true;
+    for (long long tile = blockIdx.x; tile < a.tiles_total && alive; tile += gridDim.x, ++t_count) {
+      const uint32_t ab = t_count & 1;
+      if (!mbar_wait(smem_u32(&ctrl->acc_empty[ab]), ((t_count >> 1) & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_ACCUM)) break;
+      const uint32_t tmem_acc = tmem_base + ab * BN;
+      for (int cb = 0; cb < a.cblocks && alive; ++cb, ++a_count) {
+        const uint32_t as = a_count % a.a_stages;
+        if (!mbar_wait(smem_u32(&ctrl->a_full[as]), (a_count / a.a_stages) & 1, abort_flag, a.status, STATUS_TIMEOUT_FULL)) { alive = false; break; }
+        const uint32_t strip = tiles_base + as * a_stage_bytes;
+        for (int tap = 0; tap < a.taps; ++tap, ++w_count) {
+          const uint32_t ws = w_count % a.w_stages;
+          if (!mbar_wait(smem_u32(&ctrl->w_full[ws]), (w_count / a.w_stages) & 1, abort_flag, a.status, STATUS_TIMEOUT_FULL)) { alive = false; break; }
+          tc_fence_after();
+          if (lane == 0) {
+            const uint32_t a_hi = strip + (uint32_t)(a.halo + ctrl->shift[tap]) * 128u, a_lo = a_hi + a_plane;
+            const uint32_t b_hi = w_base + ws * w_stage_bytes, b_lo = b_hi + w_plane;
+            const uint64_t da_hi = make_kmajor_sw128_desc(a_hi), da_lo = make_kmajor_sw128_desc(a_lo);
+            const uint64_t db_hi = make_kmajor_sw128_desc(b_hi), db_lo = make_kmajor_sw128_desc(b_lo);
+            const uint32_t first = (cb | tap) == 0 ? 0u : 1u;
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) umma_tf32(tmem_acc, da_lo + 2 * kk, db_hi + 2 * kk, idesc, first | (uint32_t)(kk != 0));
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) umma_tf32(tmem_acc, da_hi + 2 * kk, db_lo + 2 * kk, idesc, 1);
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) umma_tf32(tmem_acc, da_hi + 2 * kk, db_hi + 2 * kk, idesc, 1);
+            umma_commit(smem_u32(&ctrl->w_empty[ws]));
+          }
+          __syncwarp();
+        }
+        if (alive && lane == 0) umma_commit(smem_u32(&ctrl->a_empty[as]));
+        __syncwarp();
+      }
+      if (alive && lane == 0) umma_commit(smem_u32(&ctrl->acc_full[ab]));
+      __syncwarp();
+    }
+  } else if (warp >= EPI_WARPS + A_WARPS) {
+    // ------------------------------ weight producers ------------------------------
+    const int t = threadIdx.x - (EPI_WARPS + A_WARPS) * 32;
+    uint32_t w_count = 0;
+    bool alive = true;
+    for (long long tile = blockIdx.x; tile < a.tiles_total && alive; tile += gridDim.x) {
+      const int n_tile = (int)(tile % a.tiles_n);
+      const int group = (int)((tile / a.tiles_n) / a.tiles_m);
+      const int n0 = n_tile * BN;
+      const int rows_valid = min(BN, a.nc - n0);
+      const float* wrow = a.wp + ((long long)group * a.nc + n0) * a.taps * a.kc;
+      for (int cb = 0; cb < a.cblocks && alive; ++cb) {
+        for (int tap = 0; tap < a.taps; ++tap, ++w_count) {
+          const uint32_t ws = w_count % a.w_stages;
+          // loads first (registers only), then wait for the stage, then split and store
+          constexpr int TASKS = BN * 8 / W_THREADS;  // (row, 16-byte chunk) pairs per thread
+          float4 v[TASKS];
+#pragma unroll
+          for (int j = 0; j < TASKS; ++j) {
+            const int i = t + j * W_THREADS, row = i >> 3, chunk = i & 7;
+            v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (row < rows_valid)
+              v[j] = __ldg(reinterpret_cast<const float4*>(wrow + ((long long)row * a.taps + tap) * a.kc + cb * KBLK + chunk * 4));
+          }
+          if (!mbar_wait(smem_u32(&ctrl->w_empty[ws]), ((w_count / a.w_stages) & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_EMPTY)) { alive = false; break; }
+          const uint32_t b_hi = w_base + ws * w_stage_bytes, b_lo = b_hi + w_plane;
+#pragma unroll
+          for (int j = 0; j < TASKS; ++j) {
+            const int i = t + j * W_THREADS, row = i >> 3, chunk = i & 7;
+            float h[4], l[4];
+            split_tf32(v[j].x, h[0], l[0]);
+            split_tf32(v[j].y, h[1], l[1]);
+            split_tf32(v[j].z, h[2], l[2]);
+            split_tf32(v[j].w, h[3], l[3]);
+            const uint32_t o = sw128_offset(row, chunk * 4);
+            sts_f32x4(b_hi + o, h[0], h[1], h[2], h[3]);
+            sts_f32x4(b_lo + o, l[0], l[1], l[2], l[3]);
+          }
+          fence_proxy_async();
+          mbar_arrive(smem_u32(&ctrl->w_full[ws]));
+        }
+      }
+    }
+  } else if (warp >= EPI_WARPS) {
+    // ------------------------------ strip producers ------------------------------
+    const int t = threadIdx.x - EPI_WARPS * 32;
+    const bool vec_ok = a.act.s1 == 1 && ((reinterpret_cast<uintptr_t>(a.act.ptr) & 15) == 0) &&
+                        (a.act.s0 % 4 == 0) && (a.act.s2 % 4 == 0) && (a.act.s3 % 4 == 0);
+    uint32_t a_count = 0;
+    bool alive = true;
+    for (long long tile = blockIdx.x; tile < a.tiles_total && alive; tile += gridDim.x) {
+      const long long m_tile = (tile / a.tiles_n) % a.tiles_m;
+      const int group = (int)((tile / a.tiles_n) / a.tiles_m);
+      const long long q0 = m_tile * BLOCK_M;
+      for (int cb = 0; cb < a.cblocks && alive; ++cb, ++a_count) {
+        const uint32_t as = a_count % a.a_stages;
+        bool waited = false;
+        for (int r = t; r < a.strip_rows; r += A_THREADS) {
+          const long long q = q0 - a.halo + r;
+          bool ok = q >= 0 && q < a.q_total;
+          const float* src = a.act.ptr;
+          if (ok) {
+            const long long n = q / img_pitch;
+            const int rem = (int)(q - n * img_pitch);
+            const int y = rem / row_pitch, x = rem - y * row_pitch;
+            ok = y < a.H && x < a.W;
+            src += n * a.act.s0 + ((long long)group * a.kc + cb * KBLK) * a.act.s1 + (long long)y * a.act.s2 + (long long)x * a.act.s3;
+          }
+          float v[KBLK];
+          if (ok && vec_ok) {
+#pragma unroll
+            for (int j = 0; j < KBLK / 4; ++j) {
+              const float4 f = __ldg(reinterpret_cast<const float4*>(src) + j);
+              v[4 * j] = f.x; v[4 * j + 1] = f.y; v[4 * j + 2] = f.z; v[4 * j + 3] = f.w;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < KBLK; ++j) v[j] = ok ? __ldg(src + j * a.act.s1) : 0.f;
+          }
+          if (!waited) {
+            if (!mbar_wait(smem_u32(&ctrl->a_empty[as]), ((a_count / a.a_stages) & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_EMPTY)) { alive = false; break; }
+            waited = true;
+          }
+          const uint32_t p_hi = tiles_base + as * a_stage_bytes, p_lo = p_hi + a_plane;
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            float h[4], l[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) split_tf32(v[c * 4 + j], h[j], l[j]);
+            const uint32_t o = sw128_offset(r, c * 4);
+            sts_f32x4(p_hi + o, h[0], h[1], h[2], h[3]);
+            sts_f32x4(p_lo + o, l[0], l[1], l[2], l[3]);
+          }
+        }
+        if (!alive) break;
+        if (!waited && !mbar_wait(smem_u32(&ctrl->a_empty[as]), ((a_count / a.a_stages) & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_EMPTY)) { alive = false; break; }
+        fence_proxy_async();
+        mbar_arrive(smem_u32(&ctrl->a_full[as]));
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ------------------------------
+    uint32_t t_count = 0;
+    for (long long tile = blockIdx.x; tile < a.tiles_total; tile += gridDim.x, ++t_count) {
+      const int n_tile = (int)(tile % a.tiles_n);
+      const long long m_tile = (tile / a.tiles_n) % a.tiles_m;
+      const int group = (int)((tile / a.tiles_n) / a.tiles_m);
+      const int n0 = n_tile * BN;
+      const int cols_valid = min(BN, a.nc - n0);
+      const uint32_t ab = t_count & 1;
+      if (!mbar_wait(smem_u32(&ctrl->acc_full[ab]), (t_count >> 1) & 1, abort_flag, a.status, STATUS_TIMEOUT_ACCUM)) break;
+      tc_fence_after();
+      const long long q = m_tile * BLOCK_M + warp * 32 + lane;
+      bool ok = q < a.q_total;
+      long long obase = 0;
+      if (ok) {
+        const long long n = q / img_pitch;
+        const int rem = (int)(q - n * img_pitch);
+        const int y = rem / row_pitch, x = rem - y * row_pitch;
+        ok = y < a.H && x < a.W;
+        obase = ((n * a.out_channels + (long long)group * a.nc + n0) * a.H + y) * a.W + x;
+      }
+      const long long plane = (long long)a.H * a.W;
+      const uint32_t tmem_acc = tmem_base + ab * BN + ((uint32_t)(warp * 32) << 16);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        if (c0 >= cols_valid) break;
+        float v[32];
+        tmem_ld32(tmem_acc + (uint32_t)c0, v);
+        if (c0 + 32 >= cols_valid || c0 + 32 >= BN) {  // last read of this accumulator: hand it back early
+          tc_fence_before();
+          mbar_arrive(smem_u32(&ctrl->acc_empty[ab]));
+        }
+        if (ok) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int col = c0 + j;
+            if (col < cols_valid) {
+              float r = v[j];
+              if (a.bias) r += __ldg(a.bias + ((long long)group * a.nc + n0 + col) * a.bias_stride);
+              a.out[obase + (long long)col * plane] = r;
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == MMA_WARP) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// Reorder W[cout][cin/g][kh][kw] (any strides) into [g][row][tap][kchan] with the reduction channel
+// contiguous: forward row = co, kchan = ci; dInput row = ci, kchan = co.
+__global__ void __launch_bounds__(256) stage_weights_kernel(ConvGeom g, View4 w, int is_dx, float* __restrict__ out,
+                                                            long long total) {
+  const long long i = blockIdx.x * 256ll + threadIdx.x;
+  if (i >= total) return;
+  const int taps = g.kh * g.kw;
+  const int kc = is_dx ? g.cog : g.cig, nc = is_dx ? g.cig : g.cog;
+  const int c = (int)(i % kc);
+  const int tap = (int)((i / kc) % taps);
+  const int r = (int)((i / ((long long)kc * taps)) % nc);
+  const int grp = (int)(i / ((long long)kc * taps * nc));
+  const int co = is_dx ? c : r, ci = is_dx ? r : c;
+  out[i] = w.ptr[((long long)grp * g.cog + co) * w.s0 + ci * w.s1 + (tap / g.kw) * w.s2 + (tap % g.kw) * w.s3];
+}
+
+struct StripPlan {
+  bool ok = false;
+  int bn = 0, a_stages = 0, w_stages = 0, strip_rows = 0, halo = 0, smem = 0;
+};
+
+static StripPlan plan_strip(const ConvGeom& g, bool is_dx) {
+  StripPlan p;
+  const int kc = is_dx ? g.cog : g.cig, nc = is_dx ? g.cig : g.cog;
+  if (g.sh != 1 || g.sw != 1 || g.oh != g.h || g.ow != g.w) return p;
+  if (2 * g.ph != g.dh * (g.kh - 1) || 2 * g.pw != g.dw * (g.kw - 1)) return p;
+  if (kc % KBLK != 0 || nc < 16 || g.kh * g.kw > MAX_TAPS) return p;
+  p.halo = g.ph * (g.w + g.pw) + g.pw;
+  p.strip_rows = (BLOCK_M + 2 * p.halo + 7) / 8 * 8;
+  const int a_stage = p.strip_rows * 256;
+  for (int bn : {256, 128, 64}) {
+    if (bn > 64 && nc <= bn / 2) continue;  // do not pad the column tile by more than 2x
+    const int w_stage = bn * 256;
+    for (int a_stages : {2, 1}) {
+      const int left = SMEM_LIMIT - a_stages * a_stage;
+      if (left < 2 * w_stage) continue;
+      p.ok = true;
+      p.bn = bn;
+      p.a_stages = a_stages;
+      p.w_stages = std::min(MAX_STAGES, left / w_stage);
+      p.smem = a_stages * a_stage + p.w_stages * w_stage + 1024 + (int)sizeof(Ctrl) + 64;
+      return p;
+    }
+  }
+  return p;
+}
+
+}  // namespace tcs
+
+bool strip_supported(const ConvGeom& g, int phase) {
+  if (phase != B200_PHASE_FORWARD && phase != B200_PHASE_DINPUT) return false;
+  return tcs::plan_strip(g, phase == B200_PHASE_DINPUT).ok;
+}
+size_t strip_workspace(const ConvGeom& g) { return sizeof(float) * (size_t)g.cout * g.cig * g.kh * g.kw; }
+
+template <int BN>
+static int launch_strip(const tcs::StripArgs& a, int grid, int smem, cudaStream_t st) {
+  static int configured = 0;
+  if (configured < smem) {
+    B200_CUDA(cudaFuncSetAttribute(tcs::conv_strip_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    configured = smem;
+  }
+  tcs::conv_strip_kernel<BN><<<grid, tcs::THREADS, smem, st>>>(a);
+  count_launch();
+  return launch_check("conv_strip_kernel");
+}
+
+int strip_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* bias, long long bias_stride, float* out,
+               void* ws, size_t ws_bytes, cudaStream_t st) {
+  using namespace tcs;
+  const StripPlan plan = plan_strip(g, is_dx);
+  if (!plan.ok) return fail(B200_EUNSUPPORTED, "strip kernel does not take this geometry");
+  const size_t wcount = (size_t)g.cout * g.cig * g.kh * g.kw;
+  if (!ws || ws_bytes < sizeof(float) * wcount || (reinterpret_cast<uintptr_t>(ws) & 15))
+    return fail(B200_EWORKSPACE, "tcgen05 convolution needs a 16-byte aligned workspace of %zu bytes (got %zu)",
+                sizeof(float) * wcount, ws_bytes);
+  float* wp = (float*)ws;
+  stage_weights_kernel<<<(unsigned)div_up64((long long)wcount, 256), 256, 0, st>>>(g, w, is_dx ? 1 : 0, wp, (long long)wcount);
+  count_launch();
+  if (int rc = launch_check("stage_weights_kernel")) return rc;
+  StripArgs a{};
+  a.g = g; a.act = act; a.wp = wp; a.bias = is_dx ? nullptr : bias; a.bias_stride = bias_stride; a.out = out;
+  a.H = g.h; a.W = g.w; a.pr = g.ph; a.pc = g.pw;
+  a.kc = is_dx ? g.cog : g.cig;
+  a.nc = is_dx ? g.cig : g.cog;
+  a.out_channels = is_dx ? g.cin : g.cout;
+  a.cblocks = a.kc / KBLK;
+  a.taps = g.kh * g.kw;
+  a.tiles_n = (a.nc + plan.bn - 1) / plan.bn;
+  a.q_total = (long long)g.n * (a.H + a.pr) * (a.W + a.pc);
+  a.tiles_m = div_up64(a.q_total, BLOCK_M);
+  a.tiles_total = a.tiles_m * a.tiles_n * g.groups;
+  a.halo = plan.halo; a.strip_rows = plan.strip_rows; a.a_stages = plan.a_stages; a.w_stages = plan.w_stages;
+  a.is_dx = is_dx ? 1 : 0;
+  a.status = device_status_word();
+  if (!a.status) return fail(B200_ECUDA, "device status word is not allocated");
+  const int grid = (int)std::min<long long>(a.tiles_total, sm_count());
+  if (plan.bn == 64) return launch_strip<64>(a, grid, plan.smem, st);
+  if (plan.bn == 128) return launch_strip<128>(a, grid, plan.smem, st);
+  return launch_strip<256>(a, grid, plan.smem, st);
+}
+
+}  // namespace b200

@@ -48,7 +48,7 @@ def test_tc_matches_golden_layer64():
     c = next(c for c in conv_cases() if c["tag"] == "layer64")
     args = dict(stride=c["stride"], padding=c["padding"], dilation=c["dilation"], groups=c["groups"])
     y = b200conv.conv2d_forward(c["x"], c["w"], c["b"], algo="tc", **args)
-    assert b200conv.last_kernel() == "tc_igemm_forward"
+    assert b200conv.last_kernel() == "tc_strip_forward"
     dx, dw, _ = b200conv.conv2d_backward(c["go"], c["x"], c["w"], mask=(True, True, False), algo="tc", **args)
     assert b200conv.last_kernel() == "tc_igemm_dweight"
     assert b200conv.device_status() == 0
@@ -68,9 +68,16 @@ def test_tc_matches_golden_layer64():
     ((2, 64, 12, 16), 64, (3, 3), dict(padding=(2, 2), dilation=(2, 2))),
     ((1, 128, 10, 10), 64, (3, 5), dict(stride=(2, 1), padding=(1, 2), groups=2)),
     ((2, 128, 8, 8), 128, (3, 3), dict(padding=(1, 1), groups=4)),
+    ((3, 32, 7, 7), 64, (3, 3), dict(padding=(1, 1))),            # tiles spanning several small images
+    ((1, 32, 30, 41), 32, (5, 5), dict(padding=(2, 2))),          # 25 taps
+    ((2, 64, 9, 9), 512, (1, 1), dict()),                         # two column tiles of 256
 ], ids=lambda s: "x".join(map(str, s[0])) + f"-co{s[1]}-k{s[2][0]}x{s[2][1]}" if isinstance(s, tuple) and len(s) == 4 else None)
 @pytest.mark.parametrize("channels_last", [False, True], ids=["nchw", "nhwc"])
-def test_tc_forward_and_dinput_shapes(shape, channels_last):
+@pytest.mark.parametrize("variant", ["strip", "gather"])
+def test_tc_forward_and_dinput_shapes(shape, channels_last, variant, monkeypatch):
+    # "gather" pins the per-tap gather kernel; "strip" lets the persistent strip kernel take the
+    # stride-1 same-size geometries (the others run the gather kernel either way)
+    monkeypatch.setenv("B200_CONV_TC_VARIANT", variant)
     xshape, cout, kernel, kw = shape
     groups = kw.get("groups", 1)
     # the tcgen05 dInput kernel reduces over 32-channel blocks of Cout/groups

@@ -84,6 +84,11 @@ bool strip_supported(const ConvGeom& g, int phase);
 int strip_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* bias, long long bias_stride, float* out,
                void* ws, size_t ws_bytes, cudaStream_t st);
 
+// dWeight strip kernel (dweight_tc_strip.cu)
+bool dweight_strip_supported(const ConvGeom& g);
+size_t dweight_strip_workspace(const ConvGeom& g, size_t budget);
+int dweight_strip(const ConvGeom& g, View4 x, View4 dy, float* dw, void* ws, size_t ws_bytes, cudaStream_t st);
+
 int* device_status_word();  // device memory, zero unless a bounded wait gave up
 int read_device_status(int* out);
 int clear_device_status();

@@ -459,6 +459,13 @@ using namespace tc;
 static int pick_bn(int nc) { return nc <= 64 ? 64 : (nc <= 128 ? 128 : 256); }
 static void tc_dweight_plan(const ConvGeom& g, size_t budget, int* splits_out, int* span_out, size_t* bytes_out);
 
+// B200_CONV_TC_VARIANT=gather forces the per-tap gather kernel where the strip kernel would run
+// (A/B measurements); anything else lets the strip kernel take the geometries it supports.
+static bool strip_allowed() {
+  const char* v = getenv("B200_CONV_TC_VARIANT");
+  return !(v && !strcmp(v, "gather"));
+}
+
 bool tc_supported(const ConvGeom& g, int phase) {
   if (phase == B200_PHASE_FORWARD) return g.cig % KBLK == 0 && g.cog >= 16;
   if (phase == B200_PHASE_DINPUT) return g.cog % KBLK == 0 && g.cig >= 16;
@@ -493,6 +500,10 @@ size_t tc_workspace(const ConvGeom& g, int phase, size_t budget, int* splits_out
   if (span_out) *span_out = 0;
   if (phase == B200_PHASE_FORWARD || phase == B200_PHASE_DINPUT)
     return 2 * sizeof(float) * (size_t)g.cout * g.cig * g.kh * g.kw;  // hi + lo planes
+  if (phase == B200_PHASE_DWEIGHT && strip_allowed() && dweight_strip_supported(g)) {
+    if (splits_out) *splits_out = 0;
+    return dweight_strip_workspace(g, budget);
+  }
   if (phase == B200_PHASE_DWEIGHT) {
     int splits, span;
     size_t bytes;
@@ -556,13 +567,6 @@ static int conv_tc_run(const ConvGeom& g, bool is_dx, View4 act, View4 w, const 
   return launch_conv_tc<256, false>(a, grid, st);
 }
 
-// B200_CONV_TC_VARIANT=gather forces the per-tap gather kernel where the strip kernel would run
-// (A/B measurements); anything else lets the strip kernel take the geometries it supports.
-static bool strip_allowed() {
-  const char* v = getenv("B200_CONV_TC_VARIANT");
-  return !(v && !strcmp(v, "gather"));
-}
-
 int tc_forward(const ConvGeom& g, View4 x, View4 w, const float* bias, long long bias_stride, float* y, void* ws,
                size_t ws_bytes, cudaStream_t st) {
   if (strip_allowed() && strip_supported(g, B200_PHASE_FORWARD)) {
@@ -592,6 +596,10 @@ static int launch_dweight_tc(const DwTcArgs& a, dim3 grid, cudaStream_t st) {
 }
 
 int tc_dweight(const ConvGeom& g, View4 x, View4 dy, float* dw, void* ws, size_t ws_bytes, cudaStream_t st) {
+  if (strip_allowed() && dweight_strip_supported(g)) {
+    note_kernel("tc_strip_dweight");
+    return dweight_strip(g, x, dy, dw, ws, ws_bytes, st);
+  }
   int splits, span;
   size_t bytes;
   tc_dweight_plan(g, ws ? ws_bytes : 0, &splits, &span, &bytes);

@@ -29,6 +29,8 @@
 #include "tc_common.cuh"
 
 #include <algorithm>
+#include <cstdio>
+#include <cstdlib>
 
 namespace b200 {
 namespace tcs {
@@ -58,6 +60,7 @@ struct StripArgs {
   int a_stages, w_stages;
   int is_dx;
   int* status;
+  unsigned long long* prof;  // optional cycle counters of CTA 0 (B200_STRIP_PROFILE=1), else null
 };
 
 struct Ctrl {  // lives behind the operand stages in shared memory
@@ -66,6 +69,11 @@ struct Ctrl {  // lives behind the operand stages in shared memory
   int abort_flag;
   int shift[MAX_TAPS];
 };
+
+// Cycle accounting for one thread of each role in CTA 0 (diagnostics only).
+#define PROF_ON(leader) (a.prof != nullptr && blockIdx.x == 0 && (leader))
+#define PROF_T0(on) const long long prof_t0__ = (on) ? clock64() : 0
+#define PROF_ADD(on, slot) do { if (on) atomicAdd(a.prof + (slot), (unsigned long long)(clock64() - prof_t0__)); } while (0)
 
 template <int BN>
 __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs a) {
@@ -80,6 +88,9 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const ConvGeom& g = a.g;
   constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+  // Weight stages are short (one tap = 12 MMAs), so the weight producers work as WGROUPS
+  // independent groups on alternate stages: that many global-load round trips overlap.
+  constexpr int WGROUPS = BN == 64 ? 4 : (BN == 128 ? 2 : 1);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < 2; ++s) {
@@ -89,7 +100,7 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
       mbar_init(smem_u32(&ctrl->acc_empty[s]), EPI_WARPS * 32);
     }
     for (int s = 0; s < MAX_STAGES; ++s) {
-      mbar_init(smem_u32(&ctrl->w_full[s]), W_THREADS);
+      mbar_init(smem_u32(&ctrl->w_full[s]), W_THREADS / WGROUPS);
       mbar_init(smem_u32(&ctrl->w_empty[s]), 1);
     }
     ctrl->abort_flag = 0;
@@ -116,16 +127,24 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
     bool alive = true;
     for (long long tile = blockIdx.x; tile < a.tiles_total && alive; tile += gridDim.x, ++t_count) {
       const uint32_t ab = t_count & 1;
+      const bool pm = PROF_ON(lane == 0);
+      { PROF_T0(pm);
       if (!mbar_wait(smem_u32(&ctrl->acc_empty[ab]), ((t_count >> 1) & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_ACCUM)) break;
+      PROF_ADD(pm, 0); }
       const uint32_t tmem_acc = tmem_base + ab * BN;
       for (int cb = 0; cb < a.cblocks && alive; ++cb, ++a_count) {
         const uint32_t as = a_count % a.a_stages;
+        { PROF_T0(pm);
         if (!mbar_wait(smem_u32(&ctrl->a_full[as]), (a_count / a.a_stages) & 1, abort_flag, a.status, STATUS_TIMEOUT_FULL)) { alive = false; break; }
+        PROF_ADD(pm, 1); }
         const uint32_t strip = tiles_base + as * a_stage_bytes;
         for (int tap = 0; tap < a.taps; ++tap, ++w_count) {
           const uint32_t ws = w_count % a.w_stages;
+          { PROF_T0(pm);
           if (!mbar_wait(smem_u32(&ctrl->w_full[ws]), (w_count / a.w_stages) & 1, abort_flag, a.status, STATUS_TIMEOUT_FULL)) { alive = false; break; }
+          PROF_ADD(pm, 2); }
           tc_fence_after();
+          PROF_T0(pm);
           if (lane == 0) {
             const uint32_t a_hi = strip + (uint32_t)(a.halo + ctrl->shift[tap]) * 128u, a_lo = a_hi + a_plane;
             const uint32_t b_hi = w_base + ws * w_stage_bytes, b_lo = b_hi + w_plane;
@@ -141,6 +160,7 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
             umma_commit(smem_u32(&ctrl->w_empty[ws]));
           }
           __syncwarp();
+          PROF_ADD(pm, 3);
         }
         if (alive && lane == 0) umma_commit(smem_u32(&ctrl->a_empty[as]));
         __syncwarp();
@@ -150,7 +170,9 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
     }
   } else if (warp >= EPI_WARPS + A_WARPS) {
     // ------------------------------ weight producers ------------------------------
-    const int t = threadIdx.x - (EPI_WARPS + A_WARPS) * 32;
+    constexpr int WT = W_THREADS / WGROUPS;
+    const int t = (threadIdx.x - (EPI_WARPS + A_WARPS) * 32) % WT;
+    const uint32_t wgroup = (uint32_t)((threadIdx.x - (EPI_WARPS + A_WARPS) * 32) / WT);
     uint32_t w_count = 0;
     bool alive = true;
     for (long long tile = blockIdx.x; tile < a.tiles_total && alive; tile += gridDim.x) {
@@ -161,22 +183,27 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
       const float* wrow = a.wp + ((long long)group * a.nc + n0) * a.taps * a.kc;
       for (int cb = 0; cb < a.cblocks && alive; ++cb) {
         for (int tap = 0; tap < a.taps; ++tap, ++w_count) {
+          if (w_count % WGROUPS != wgroup) continue;
           const uint32_t ws = w_count % a.w_stages;
           // loads first (registers only), then wait for the stage, then split and store
-          constexpr int TASKS = BN * 8 / W_THREADS;  // (row, 16-byte chunk) pairs per thread
+          constexpr int TASKS = BN * 8 / WT;  // (row, 16-byte chunk) pairs per thread
           float4 v[TASKS];
 #pragma unroll
           for (int j = 0; j < TASKS; ++j) {
-            const int i = t + j * W_THREADS, row = i >> 3, chunk = i & 7;
+            const int i = t + j * WT, row = i >> 3, chunk = i & 7;
             v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
             if (row < rows_valid)
               v[j] = __ldg(reinterpret_cast<const float4*>(wrow + ((long long)row * a.taps + tap) * a.kc + cb * KBLK + chunk * 4));
           }
+          const bool pw = PROF_ON(threadIdx.x == (EPI_WARPS + A_WARPS) * 32);
+          { PROF_T0(pw);
           if (!mbar_wait(smem_u32(&ctrl->w_empty[ws]), ((w_count / a.w_stages) & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_EMPTY)) { alive = false; break; }
+          PROF_ADD(pw, 4); }
+          PROF_T0(pw);
           const uint32_t b_hi = w_base + ws * w_stage_bytes, b_lo = b_hi + w_plane;
 #pragma unroll
           for (int j = 0; j < TASKS; ++j) {
-            const int i = t + j * W_THREADS, row = i >> 3, chunk = i & 7;
+            const int i = t + j * WT, row = i >> 3, chunk = i & 7;
             float h[4], l[4];
             split_tf32(v[j].x, h[0], l[0]);
             split_tf32(v[j].y, h[1], l[1]);
@@ -188,6 +215,7 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
           }
           fence_proxy_async();
           mbar_arrive(smem_u32(&ctrl->w_full[ws]));
+          PROF_ADD(pw, 5);
         }
       }
     }
@@ -205,6 +233,8 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
       for (int cb = 0; cb < a.cblocks && alive; ++cb, ++a_count) {
         const uint32_t as = a_count % a.a_stages;
         bool waited = false;
+        const bool pa = PROF_ON(threadIdx.x == EPI_WARPS * 32);
+        PROF_T0(pa);
         for (int r = t; r < a.strip_rows; r += A_THREADS) {
           const long long q = q0 - a.halo + r;
           bool ok = q >= 0 && q < a.q_total;
@@ -228,7 +258,9 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
             for (int j = 0; j < KBLK; ++j) v[j] = ok ? __ldg(src + j * a.act.s1) : 0.f;
           }
           if (!waited) {
+            const long long tw = pa ? clock64() : 0;
             if (!mbar_wait(smem_u32(&ctrl->a_empty[as]), ((a_count / a.a_stages) & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_EMPTY)) { alive = false; break; }
+            if (pa) atomicAdd(a.prof + 6, (unsigned long long)(clock64() - tw));
             waited = true;
           }
           const uint32_t p_hi = tiles_base + as * a_stage_bytes, p_lo = p_hi + a_plane;
@@ -246,6 +278,7 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
         if (!waited && !mbar_wait(smem_u32(&ctrl->a_empty[as]), ((a_count / a.a_stages) & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_EMPTY)) { alive = false; break; }
         fence_proxy_async();
         mbar_arrive(smem_u32(&ctrl->a_full[as]));
+        PROF_ADD(pa, 7);
       }
     }
   } else {
@@ -258,7 +291,11 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
       const int n0 = n_tile * BN;
       const int cols_valid = min(BN, a.nc - n0);
       const uint32_t ab = t_count & 1;
+      const bool pe = PROF_ON(threadIdx.x == 0);
+      { PROF_T0(pe);
       if (!mbar_wait(smem_u32(&ctrl->acc_full[ab]), (t_count >> 1) & 1, abort_flag, a.status, STATUS_TIMEOUT_ACCUM)) break;
+      PROF_ADD(pe, 8); }
+      PROF_T0(pe);
       tc_fence_after();
       const long long q = m_tile * BLOCK_M + warp * 32 + lane;
       bool ok = q < a.q_total;
@@ -293,6 +330,8 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
           }
         }
       }
+      PROF_ADD(pe, 9);
+      if (pe) atomicAdd(a.prof + 10, 1ull);
     }
   }
   tc_fence_before();
@@ -399,7 +438,26 @@ int strip_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* b
   a.is_dx = is_dx ? 1 : 0;
   a.status = device_status_word();
   if (!a.status) return fail(B200_ECUDA, "device status word is not allocated");
+  static unsigned long long* prof_buf = nullptr;
+  const char* prof_env = getenv("B200_STRIP_PROFILE");
+  const bool profiling = prof_env && prof_env[0] == '1';
+  if (profiling) {
+    if (!prof_buf) B200_CUDA(cudaMalloc(&prof_buf, 16 * sizeof(unsigned long long)));
+    B200_CUDA(cudaMemsetAsync(prof_buf, 0, 16 * sizeof(unsigned long long), st));
+    a.prof = prof_buf;
+  }
   const int grid = (int)std::min<long long>(a.tiles_total, sm_count());
+  if (profiling) {
+    const int rc = plan.bn == 64 ? launch_strip<64>(a, grid, plan.smem, st)
+                 : plan.bn == 128 ? launch_strip<128>(a, grid, plan.smem, st) : launch_strip<256>(a, grid, plan.smem, st);
+    unsigned long long h[16];
+    B200_CUDA(cudaStreamSynchronize(st));
+    B200_CUDA(cudaMemcpy(h, prof_buf, sizeof h, cudaMemcpyDeviceToHost));
+    fprintf(stderr, "[strip profile, CTA 0, cycles] bn=%d a_stages=%d w_stages=%d tiles=%llu | mma: wait_acc %llu wait_a %llu wait_w %llu issue %llu | "
+            "w: wait_empty %llu convert %llu | a: wait_empty %llu stage_total %llu | epi: wait_acc %llu drain %llu\n",
+            plan.bn, plan.a_stages, plan.w_stages, h[10], h[0], h[1], h[2], h[3], h[4], h[5], h[6], h[7], h[8], h[9]);
+    return rc;
+  }
   if (plan.bn == 64) return launch_strip<64>(a, grid, plan.smem, st);
   if (plan.bn == 128) return launch_strip<128>(a, grid, plan.smem, st);
   return launch_strip<256>(a, grid, plan.smem, st);

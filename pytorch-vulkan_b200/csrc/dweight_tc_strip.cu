@@ -1,0 +1,353 @@
+// tcgen05 dWeight kernel for stride-1 "same" convolutions with kw <= 4 (3x3 pad 1, dilated 3x3,
+// 1x1 ...), FP32 via 3xTF32.
+//
+//   dW[co][ci][ky][kx] = sum over padded pixels q of  dY[q][co] * X[q + shift(ky,kx)][ci]
+//
+// The contraction runs over pixels, so both operands are staged pixel-major ("MN-major" for the
+// tensor core): one 128-byte shared-memory row per pixel holding 32 channels, TF32 hi and lo
+// planes, written in the 128-byte/32-byte-base swizzle that tcgen05 requires for 32-bit MN-major
+// operands.  Two properties of the matrix descriptor make the filter taps free:
+//   * a descriptor may start at any row, so the vertical tap (ky) is a start-address offset;
+//   * the blocks of 32 rows that make up the M dimension sit at a programmable byte stride, so
+//     with a stride of `dilation_w` rows the four M blocks of ONE staged input strip are the
+//     horizontal taps kx = 0..3: a single tcgen05.mma of shape 128 x BN x 8 accumulates up to four
+//     taps of a 32-channel block at once.  (For 1x1 filters the four M blocks are four channel
+//     blocks instead.)
+// Every CTA owns one (channel block, ky, column tile, pixel split) and a single accumulator in
+// TMEM; its 16 producer warps stream the input strip (32 + halo rows per K block) and the dY
+// strip (32 rows x BN channels) straight from the caller's strided views, one 32-row block per
+// warp, several K blocks in flight.  Split partials land in [split][cout][cin/g*kh*kw] and are
+// summed in ascending order by finalize_kernel (no atomics, run-to-run identical).
+//
+// Replaces csrc/shaders/conv2d_backward_weight_tiled_body.glsl:42-70 and
+// conv2d_backward_weight_finalize.comp:9-18 of the reference for these geometries.
+#include "common.cuh"
+#include "tc_common.cuh"
+
+#include <algorithm>
+
+namespace b200 {
+namespace tcdw {
+using namespace tc;
+
+constexpr int KP = 32;          // pixels per K block (four K=8 MMA steps)
+constexpr int XR = 48;          // rows of one staged input block: KP + margin for the horizontal taps
+constexpr int XOFF = 4;         // row of the strip that corresponds to the first pixel of the K block
+constexpr int PRODUCER_WARPS = 16;
+constexpr int MMA_WARP = PRODUCER_WARPS;
+constexpr int THREADS = (PRODUCER_WARPS + 1) * 32;
+constexpr int MAX_STAGES = 6;
+constexpr int SMEM_LIMIT = 232448 - 2048;
+
+struct DwStripArgs {
+  ConvGeom g;
+  View4 x, dy;
+  float* out;            // dW (one split) or the partial buffer [split][cout][cig*taps]
+  int H, W, pr, pc;      // padded pixel space (see conv_tc_strip.cu)
+  long long q_total;
+  int span, splits;      // padded pixels per split (multiple of KP)
+  int xblocks;           // staged input blocks per CTA: 1 (taps in M) or 4 (1x1: channel blocks in M)
+  int ci_tiles, co_tiles;
+  int stages;
+  int* status;
+};
+
+struct Ctrl {
+  unsigned long long full[MAX_STAGES], empty[MAX_STAGES], accum;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+// byte offset of channel e (0..31) of row `row` in a plane using the 128B swizzle with 32-byte base
+__device__ __forceinline__ uint32_t sw32b_offset(int row, int e) {
+  return (uint32_t)(row * 128 + ((((e >> 3) ^ (row & 3)) << 5) | ((e & 7) << 2)));
+}
+// MN-major operand descriptor: blocks of 32 channels `lbo` bytes apart, 4-row groups 512 bytes apart
+__device__ __forceinline__ uint64_t make_mn_desc(uint32_t addr, uint32_t lbo) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)(lbo >> 4) << 16;
+  d |= (uint64_t)(512u >> 4) << 32;
+  d |= (uint64_t)1 << 46;   // descriptor version of sm_100
+  d |= (uint64_t)1 << 61;   // SWIZZLE_128B with 32-byte base
+  return d;
+}
+
+// One warp stages `rows` (<= 32, lane = row) x 32 channels of a pixel-major block: gather from
+// the strided view, split into TF32 hi/lo, swizzled stores.  `q_first` is the padded pixel of row 0;
+// rows outside [q_lo, q_hi) or on padding are written as zeros.
+__device__ __forceinline__ void stage_block(const View4& v, long long chan0, int chans, int H, int W, int row_pitch,
+                                            long long img_pitch, long long q_first, long long q_lo, long long q_hi,
+                                            int rows, int row0, uint32_t plane_hi, uint32_t plane_lo, int lane,
+                                            bool vec_ok, float (&val)[32]) {
+  (void)plane_hi; (void)plane_lo; (void)row0;
+  const long long q = q_first + lane;
+  bool ok = lane < rows && q >= q_lo && q < q_hi;
+  const float* src = v.ptr;
+  if (ok) {
+    const long long n = q / img_pitch;
+    const int rem = (int)(q - n * img_pitch);
+    const int y = rem / row_pitch, x = rem - y * row_pitch;
+    ok = y < H && x < W;
+    src += n * v.s0 + chan0 * v.s1 + (long long)y * v.s2 + (long long)x * v.s3;
+  }
+  if (ok && vec_ok && chans == 32) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float4 f = __ldg(reinterpret_cast<const float4*>(src) + j);
+      val[4 * j] = f.x; val[4 * j + 1] = f.y; val[4 * j + 2] = f.z; val[4 * j + 3] = f.w;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) val[j] = (ok && j < chans) ? __ldg(src + j * v.s1) : 0.f;
+  }
+}
+__device__ __forceinline__ void store_block(const float (&val)[32], int rows, int row0, uint32_t plane_hi,
+                                            uint32_t plane_lo, int lane) {
+  if (lane >= rows) return;
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    float h[4], l[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) split_tf32(val[c * 4 + j], h[j], l[j]);
+    const uint32_t o = sw32b_offset(row0 + lane, c * 4);
+    sts_f32x4(plane_hi + o, h[0], h[1], h[2], h[3]);
+    sts_f32x4(plane_lo + o, l[0], l[1], l[2], l[3]);
+  }
+}
+
+template <int BN>
+__global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStripArgs a) {
+  extern __shared__ unsigned char smem_raw[];
+  const ConvGeom& g = a.g;
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  constexpr int NB = BN / 32;                                  // dY blocks per stage
+  const uint32_t x_plane = XR * 128u, x_bytes = (uint32_t)a.xblocks * 2u * x_plane;
+  constexpr uint32_t y_plane = NB * KP * 128u;                 // all dY blocks of one plane
+  const uint32_t stage_bytes = x_bytes + 2u * y_plane;
+  Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem_raw + (base - raw) + a.stages * stage_bytes);
+  volatile int* abort_flag = &ctrl->abort_flag;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int x_tasks = a.xblocks * 2;                           // an input block = rows 0..31 and 32..47
+  const int tasks = x_tasks + NB;                              // warp-sized staging jobs per K block
+  constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < MAX_STAGES; ++s) {
+      mbar_init(smem_u32(&ctrl->full[s]), (uint32_t)tasks * 32u);
+      mbar_init(smem_u32(&ctrl->empty[s]), 1);
+    }
+    mbar_init(smem_u32(&ctrl->accum), 1);
+    ctrl->abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == MMA_WARP) tmem_alloc(smem_u32(&ctrl->tmem_base), TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_acc = *reinterpret_cast<volatile uint32_t*>(&ctrl->tmem_base);
+
+  // ---- which piece of dW this CTA owns ----
+  int id = blockIdx.x;
+  const int ci_tile = id % a.ci_tiles; id /= a.ci_tiles;
+  const int ky = id % g.kh;            id /= g.kh;
+  const int co_tile = id % a.co_tiles; id /= a.co_tiles;
+  const int group = id;
+  const int split = blockIdx.y;
+  const int ci_per_tile = a.xblocks * 32;
+  const int ci0 = ci_tile * ci_per_tile, co0 = co_tile * BN;
+  const int cols_valid = min(BN, g.cog - co0);
+  const int row_pitch = a.W + a.pc;
+  const long long img_pitch = (long long)(a.H + a.pr) * row_pitch;
+  const long long k_begin = (long long)split * a.span, k_end = min(a.q_total, k_begin + a.span);
+  const int kblocks = (int)((k_end - k_begin + KP - 1) / KP);
+  const long long yshift = (long long)(ky * g.dh - g.ph) * row_pitch;
+
+  if (warp == MMA_WARP) {
+    constexpr uint32_t idesc = make_idesc_tf32(128, BN) | (1u << 15) | (1u << 16);  // both operands MN-major
+    const uint32_t a_lbo = a.xblocks == 1 ? (uint32_t)g.dw * 128u : 2u * x_plane;
+    for (int kb = 0; kb < kblocks; ++kb) {
+      const int s = kb % a.stages;
+      if (!mbar_wait(smem_u32(&ctrl->full[s]), (uint32_t)(kb / a.stages) & 1, abort_flag, a.status, STATUS_TIMEOUT_FULL)) break;
+      tc_fence_after();
+      if (lane == 0) {
+        const uint32_t xs = base + s * stage_bytes, ys = xs + x_bytes;
+        // input rows start at the pixel shifted by -pad_w; hi plane then lo plane of each block
+        const uint32_t a_hi = xs + (uint32_t)(XOFF - g.pw) * 128u, a_lo = a_hi + x_plane;
+        const uint32_t b_hi = ys, b_lo = ys + y_plane;
+#pragma unroll
+        for (int kg = 0; kg < KP / 8; ++kg) {
+          const uint64_t da_hi = make_mn_desc(a_hi + kg * 1024u, a_lbo), da_lo = make_mn_desc(a_lo + kg * 1024u, a_lbo);
+          const uint64_t db_hi = make_mn_desc(b_hi + kg * 1024u, KP * 128u), db_lo = make_mn_desc(b_lo + kg * 1024u, KP * 128u);
+          umma_tf32(tmem_acc, da_lo, db_hi, idesc, (kb | kg) != 0);
+          umma_tf32(tmem_acc, da_hi, db_lo, idesc, 1);
+          umma_tf32(tmem_acc, da_hi, db_hi, idesc, 1);
+        }
+        umma_commit(smem_u32(&ctrl->empty[s]));
+      }
+      __syncwarp();
+    }
+    if (lane == 0) umma_commit(smem_u32(&ctrl->accum));
+    __syncwarp();
+  } else {
+    // ---- producers: job j of K block kb goes to warp (kb*tasks + j) % 16 ----
+    const bool x_vec = a.x.s1 == 1 && ((reinterpret_cast<uintptr_t>(a.x.ptr) & 15) == 0) && a.x.s0 % 4 == 0 &&
+                       a.x.s2 % 4 == 0 && a.x.s3 % 4 == 0;
+    const bool y_vec = a.dy.s1 == 1 && ((reinterpret_cast<uintptr_t>(a.dy.ptr) & 15) == 0) && a.dy.s0 % 4 == 0 &&
+                       a.dy.s2 % 4 == 0 && a.dy.s3 % 4 == 0;
+    const long long total_jobs = (long long)kblocks * tasks;
+    bool alive = true;
+    for (long long job = warp; job < total_jobs && alive; job += PRODUCER_WARPS) {
+      const int kb = (int)(job / tasks), j = (int)(job - (long long)kb * tasks);
+      const int s = kb % a.stages;
+      const long long k0 = k_begin + (long long)kb * KP;
+      const uint32_t xs = base + s * stage_bytes, ys = xs + x_bytes;
+      float val[32];
+      int rows, row0;
+      uint32_t p_hi, p_lo;
+      if (j < x_tasks) {
+        const int blk = j >> 1, half = j & 1;
+        rows = half ? XR - 32 : 32;
+        row0 = half * 32;
+        p_hi = xs + (uint32_t)blk * 2u * x_plane;
+        p_lo = p_hi + x_plane;
+        const int c0 = ci0 + blk * 32;
+        const int chans = max(0, min(32, g.cig - c0));
+        // the input is needed wherever it exists: no split-range clipping, only image bounds
+        stage_block(a.x, (long long)group * g.cig + c0, chans, a.H, a.W, row_pitch, img_pitch,
+                    k0 + yshift - XOFF + row0, 0, a.q_total, rows, row0, p_hi, p_lo, lane, x_vec, val);
+      } else {
+        const int blk = j - x_tasks;
+        rows = 32;
+        row0 = blk * KP;
+        p_hi = ys;
+        p_lo = ys + y_plane;
+        const int c0 = co0 + blk * 32;
+        const int chans = max(0, min(32, g.cog - c0));
+        // dY outside this split's pixel range must read as zero so that splits do not overlap
+        stage_block(a.dy, (long long)group * g.cog + c0, chans, a.H, a.W, row_pitch, img_pitch, k0, k_begin, k_end,
+                    rows, row0, p_hi, p_lo, lane, y_vec, val);
+      }
+      if (!mbar_wait(smem_u32(&ctrl->empty[s]), ((uint32_t)(kb / a.stages) & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_EMPTY)) { alive = false; break; }
+      store_block(val, rows, row0, p_hi, p_lo, lane);
+      fence_proxy_async();
+      mbar_arrive(smem_u32(&ctrl->full[s]));
+    }
+    // ---- epilogue (warps 0-3): lane = row of the accumulator = (block, channel) ----
+    if (warp < 4 && mbar_wait(smem_u32(&ctrl->accum), 0, abort_flag, a.status, STATUS_TIMEOUT_ACCUM)) {
+      tc_fence_after();
+      const int taps = g.kh * g.kw;
+      const long long cols = (long long)g.cig * taps;
+      // block index: horizontal tap (taps-in-M mode) or channel block (1x1 mode)
+      const int kx = a.xblocks == 1 ? warp : 0;
+      const int ci = ci0 + (a.xblocks == 1 ? lane : warp * 32 + lane);
+      const bool row_ok = kx < g.kw && ci < g.cig;
+      float* out = a.out + ((long long)split * g.cout + (long long)group * g.cog + co0) * cols + (long long)ci * taps + ky * g.kw + kx;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        if (c0 >= cols_valid) break;
+        float v[32];
+        tmem_ld32(tmem_acc + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, v);
+        if (row_ok) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (c0 + j < cols_valid) out[(long long)(c0 + j) * cols] = v[j];
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == MMA_WARP) {
+    tc_fence_after();
+    tmem_dealloc(tmem_acc, TMEM_COLS);
+  }
+}
+
+struct DwStripPlan {
+  bool ok = false;
+  int bn = 0, xblocks = 1, stages = 0, smem = 0, ci_tiles = 0, co_tiles = 0, splits = 1, span = 0;
+  size_t bytes = 0;
+};
+
+static DwStripPlan plan_dw_strip(const ConvGeom& g, size_t budget) {
+  DwStripPlan p;
+  if (g.sh != 1 || g.sw != 1 || g.oh != g.h || g.ow != g.w) return p;
+  if (2 * g.ph != g.dh * (g.kh - 1) || 2 * g.pw != g.dw * (g.kw - 1)) return p;
+  if (g.kw > 4 || g.pw > XOFF || 3 * g.dw - g.pw + XOFF + KP > XR) return p;
+  if (g.cog < 16 || g.cig < 16) return p;
+  p.xblocks = (g.kw == 1 && g.cig >= 64) ? 4 : 1;
+  p.bn = g.cog <= 64 ? 64 : (g.cog <= 128 ? 128 : 256);
+  const int stage = p.xblocks * 2 * XR * 128 + 2 * (p.bn / 32) * KP * 128;
+  p.stages = std::min(MAX_STAGES, SMEM_LIMIT / stage);
+  if (p.stages < 2) return p;
+  p.smem = p.stages * stage + 1024 + (int)sizeof(Ctrl) + 64;
+  p.ci_tiles = (g.cig + p.xblocks * 32 - 1) / (p.xblocks * 32);
+  p.co_tiles = (g.cog + p.bn - 1) / p.bn;
+  const long long q_total = (long long)g.n * (g.h + g.ph) * (g.w + g.pw);
+  const long long tiles = (long long)p.ci_tiles * g.kh * p.co_tiles * g.groups;
+  const size_t dw_bytes = sizeof(float) * (size_t)g.cout * g.cig * g.kh * g.kw;
+  // two full waves of CTAs (one CTA per SM is resident), never a few CTAs more than that; every
+  // split at least 16 K blocks long; partials within budget
+  long long want = std::max<long long>(1, 2ll * sm_count() / tiles);
+  want = std::min<long long>(want, std::max<long long>(1, q_total / (16 * KP)));
+  want = std::min<long long>(want, 65535);
+  want = std::min<long long>(want, (long long)(budget / dw_bytes));
+  long long span = div_up64(q_total, KP) * KP, splits = 1;
+  if (want >= 2) {
+    span = div_up64(div_up64(q_total, want), KP) * KP;
+    splits = div_up64(q_total, span);
+  }
+  if (span > 2147483616ll) return p;
+  p.splits = (int)splits;
+  p.span = (int)span;
+  p.bytes = splits > 1 ? (size_t)splits * dw_bytes : 0;
+  p.ok = true;
+  return p;
+}
+
+}  // namespace tcdw
+
+bool dweight_strip_supported(const ConvGeom& g) { return tcdw::plan_dw_strip(g, 0).ok; }
+size_t dweight_strip_workspace(const ConvGeom& g, size_t budget) { return tcdw::plan_dw_strip(g, budget).bytes; }
+
+template <int BN>
+static int launch_dw_strip(const tcdw::DwStripArgs& a, dim3 grid, int smem, cudaStream_t st) {
+  static int configured = 0;
+  if (configured < smem) {
+    B200_CUDA(cudaFuncSetAttribute(tcdw::dweight_strip_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    configured = smem;
+  }
+  tcdw::dweight_strip_kernel<BN><<<grid, tcdw::THREADS, smem, st>>>(a);
+  count_launch();
+  return launch_check("dweight_strip_kernel");
+}
+
+int dweight_strip(const ConvGeom& g, View4 x, View4 dy, float* dw, void* ws, size_t ws_bytes, cudaStream_t st) {
+  using namespace tcdw;
+  const DwStripPlan plan = plan_dw_strip(g, ws ? ws_bytes : 0);
+  if (!plan.ok) return fail(B200_EUNSUPPORTED, "dWeight strip kernel does not take this geometry");
+  DwStripArgs a{};
+  a.g = g; a.x = x; a.dy = dy;
+  a.H = g.h; a.W = g.w; a.pr = g.ph; a.pc = g.pw;
+  a.q_total = (long long)g.n * (a.H + a.pr) * (a.W + a.pc);
+  a.span = plan.span; a.splits = plan.splits; a.xblocks = plan.xblocks;
+  a.ci_tiles = plan.ci_tiles; a.co_tiles = plan.co_tiles; a.stages = plan.stages;
+  a.out = plan.splits > 1 ? (float*)ws : dw;
+  a.status = device_status_word();
+  if (!a.status) return fail(B200_ECUDA, "device status word is not allocated");
+  const long long gx = (long long)plan.ci_tiles * g.kh * plan.co_tiles * g.groups;
+  if (gx > 2147483647ll) return fail(B200_ERANGE, "dWeight strip kernel: grid exceeds launch limits");
+  // rows of dW that no CTA writes (channel blocks beyond kw taps) do not exist: every (co, ci, ky, kx)
+  // is covered because kx < kw <= 4 blocks and all ci tiles are enumerated
+  const dim3 grid((unsigned)gx, (unsigned)plan.splits);
+  int rc = plan.bn == 64 ? launch_dw_strip<64>(a, grid, plan.smem, st)
+         : plan.bn == 128 ? launch_dw_strip<128>(a, grid, plan.smem, st) : launch_dw_strip<256>(a, grid, plan.smem, st);
+  if (rc) return rc;
+  if (plan.splits > 1)
+    return finalize_splits((const float*)ws, dw, (long long)g.cout * g.cig * g.kh * g.kw, plan.splits, st);
+  return B200_OK;
+}
+
+}  // namespace b200

@@ -50,7 +50,7 @@ def test_tc_matches_golden_layer64():
     y = b200conv.conv2d_forward(c["x"], c["w"], c["b"], algo="tc", **args)
     assert b200conv.last_kernel() == "tc_strip_forward"
     dx, dw, _ = b200conv.conv2d_backward(c["go"], c["x"], c["w"], mask=(True, True, False), algo="tc", **args)
-    assert b200conv.last_kernel() == "tc_igemm_dweight"
+    assert b200conv.last_kernel() == "tc_strip_dweight"
     assert b200conv.device_status() == 0
     assert oracle.rel_l2(y, c["y"]) <= GATE
     assert oracle.rel_l2(dx, c["dx"]) <= GATE

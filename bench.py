@@ -14,7 +14,7 @@ far larger than L2, so no explicit L2 flush is needed between iterations.
 
 N>1 (torchrun, one rank per GPU): every rank runs the same sweep on its own batch of 64
 (weak scaling, global batch 64*N) and the weight gradients of each layer are summed over
-ranks with one NCCL all-reduce per step on the compute stream.
+ranks with ONE NCCL all-reduce per step (all layers' dW in a single fused buffer) on the compute stream.
 
 Prints ONE JSON line.  `--impl reference` times the reference's CPU path instead (PyTorch's CPU
 convolution, which is what the reference falls back to and tests against) on a bounded sample.
@@ -169,8 +169,10 @@ class Layer:
         self.x, self.w, self.go = self.hx.to(device), self.hw_.to(device), self.hgo.to(device)
         self.y = torch.empty(BATCH, cout, self.p.oh, self.p.ow, device=device)
         self.dx = torch.empty(BATCH, cin, hw, hw, device=device)
-        self.dw = torch.empty(cout, cin, k, k, device=device)
-        self.hy, self.hdx, self.hdw = (torch.empty(t.shape).pin_memory() for t in (self.y, self.dx, self.dw))
+        self.dw = None  # a view into the step's fused gradient buffer (set by main)
+        self.w_shape = (cout, cin, k, k)
+        self.hy, self.hdx = (torch.empty(t.shape).pin_memory() for t in (self.y, self.dx))
+        self.hdw = torch.empty(self.w_shape).pin_memory()
         self.flops = 3 * self.p.flops()
         self.ws_bytes = max(b200conv.workspace_bytes(self.p, ph) for ph in (0, 1, 2))
         self.h2d = sum(t.numel() * 4 for t in (self.hx, self.hw_, self.hgo))
@@ -221,7 +223,13 @@ def main():
     ws_bytes = max(max(l.ws_bytes for l in layers), 1)
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=device)
     step_flops = sum(l.flops for l in layers)
-    grads = [l.dw for l in layers]
+    # all weight gradients of a step live in one buffer: the data-parallel exchange is ONE all-reduce
+    grad_flat = torch.empty(sum(int(torch.tensor(l.w_shape).prod()) for l in layers), device=device)
+    off = 0
+    for l in layers:
+        n = int(torch.tensor(l.w_shape).prod())
+        l.dw = grad_flat[off:off + n].view(l.w_shape)
+        off += n
 
     families = {}  # kernel family -> [flops, [event pairs]]
 
@@ -250,8 +258,7 @@ def main():
         for l in layers:
             run_layer(l, timed)
         if dist is not None:
-            for gten in grads:  # data-parallel exchange: sum of the weight gradients
-                dist.all_reduce(gten)
+            dist.all_reduce(grad_flat)  # data-parallel exchange: sum of the weight gradients
 
     def barrier():
         torch.cuda.synchronize()
@@ -286,8 +293,9 @@ def main():
             run_layer(l, False)
             l.hy.copy_(l.y, non_blocking=True)
             l.hdx.copy_(l.dx, non_blocking=True)
-            if dist is not None:
-                dist.all_reduce(l.dw)
+        if dist is not None:
+            dist.all_reduce(grad_flat)
+        for l in layers:
             l.hdw.copy_(l.dw, non_blocking=True)
     e2e_steps = max(2, min(args.steps, 5))
     e2e_step()

@@ -87,7 +87,13 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
   volatile int* abort_flag = &ctrl->abort_flag;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const ConvGeom& g = a.g;
-  constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+  // For BN <= 128 the weight stage's hi and lo planes (adjacent in shared memory) are fed to the
+  // tensor core as ONE operand of 2*BN rows: a single MMA of width 2*BN yields a_hi*b_hi in columns
+  // [0,BN) and a_hi*b_lo in [BN,2BN), a second one of width BN adds a_lo*b_hi to [0,BN); the epilogue
+  // sums the two halves.  Two MMAs read 14/18 of the shared-memory bytes that three do.
+  constexpr bool FUSE_HILO = BN <= 128;
+  constexpr uint32_t ACC_COLS = FUSE_HILO ? 2 * BN : BN;
+  constexpr uint32_t TMEM_COLS = 2 * ACC_COLS;
   // Weight stages are short (one tap = 12 MMAs), so the weight producers work as WGROUPS
   // independent groups on alternate stages: that many global-load round trips overlap.
   constexpr int WGROUPS = BN == 64 ? 4 : (BN == 128 ? 2 : 1);
@@ -123,6 +129,7 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
   if (warp == MMA_WARP) {
     // ------------------------------ MMA issuer ------------------------------
     constexpr uint32_t idesc = make_idesc_tf32(BLOCK_M, BN);
+    constexpr uint32_t idesc_wide = make_idesc_tf32(BLOCK_M, FUSE_HILO ? 2 * BN : BN);
     uint32_t a_count = 0, w_count = 0, t_count = 0;
     bool alive = true;
     for (long long tile = blockIdx.x; tile < a.tiles_total && alive; tile += gridDim.x, ++t_count) {
@@ -131,7 +138,7 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
       { PROF_T0(pm);
       if (!mbar_wait(smem_u32(&ctrl->acc_empty[ab]), ((t_count >> 1) & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_ACCUM)) break;
       PROF_ADD(pm, 0); }
-      const uint32_t tmem_acc = tmem_base + ab * BN;
+      const uint32_t tmem_acc = tmem_base + ab * ACC_COLS;
       for (int cb = 0; cb < a.cblocks && alive; ++cb, ++a_count) {
         const uint32_t as = a_count % a.a_stages;
         { PROF_T0(pm);
@@ -151,12 +158,19 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
             const uint64_t da_hi = make_kmajor_sw128_desc(a_hi), da_lo = make_kmajor_sw128_desc(a_lo);
             const uint64_t db_hi = make_kmajor_sw128_desc(b_hi), db_lo = make_kmajor_sw128_desc(b_lo);
             const uint32_t first = (cb | tap) == 0 ? 0u : 1u;
+            if (FUSE_HILO) {
 #pragma unroll
-            for (int kk = 0; kk < 4; ++kk) umma_tf32(tmem_acc, da_lo + 2 * kk, db_hi + 2 * kk, idesc, first | (uint32_t)(kk != 0));
+              for (int kk = 0; kk < 4; ++kk) umma_tf32(tmem_acc, da_hi + 2 * kk, db_hi + 2 * kk, idesc_wide, first | (uint32_t)(kk != 0));
 #pragma unroll
-            for (int kk = 0; kk < 4; ++kk) umma_tf32(tmem_acc, da_hi + 2 * kk, db_lo + 2 * kk, idesc, 1);
+              for (int kk = 0; kk < 4; ++kk) umma_tf32(tmem_acc, da_lo + 2 * kk, db_hi + 2 * kk, idesc, 1);
+            } else {
 #pragma unroll
-            for (int kk = 0; kk < 4; ++kk) umma_tf32(tmem_acc, da_hi + 2 * kk, db_hi + 2 * kk, idesc, 1);
+              for (int kk = 0; kk < 4; ++kk) umma_tf32(tmem_acc, da_lo + 2 * kk, db_hi + 2 * kk, idesc, first | (uint32_t)(kk != 0));
+#pragma unroll
+              for (int kk = 0; kk < 4; ++kk) umma_tf32(tmem_acc, da_hi + 2 * kk, db_lo + 2 * kk, idesc, 1);
+#pragma unroll
+              for (int kk = 0; kk < 4; ++kk) umma_tf32(tmem_acc, da_hi + 2 * kk, db_hi + 2 * kk, idesc, 1);
+            }
             umma_commit(smem_u32(&ctrl->w_empty[ws]));
           }
           __syncwarp();
@@ -308,12 +322,18 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
         obase = ((n * a.out_channels + (long long)group * a.nc + n0) * a.H + y) * a.W + x;
       }
       const long long plane = (long long)a.H * a.W;
-      const uint32_t tmem_acc = tmem_base + ab * BN + ((uint32_t)(warp * 32) << 16);
+      const uint32_t tmem_acc = tmem_base + ab * ACC_COLS + ((uint32_t)(warp * 32) << 16);
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         if (c0 >= cols_valid) break;
         float v[32];
         tmem_ld32(tmem_acc + (uint32_t)c0, v);
+        if (FUSE_HILO) {
+          float v2[32];
+          tmem_ld32(tmem_acc + (uint32_t)(BN + c0), v2);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] += v2[j];
+        }
         if (c0 + 32 >= cols_valid || c0 + 32 >= BN) {  // last read of this accumulator: hand it back early
           tc_fence_before();
           mbar_arrive(smem_u32(&ctrl->acc_empty[ab]));

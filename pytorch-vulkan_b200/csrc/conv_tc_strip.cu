@@ -64,7 +64,7 @@ struct StripArgs {
 };
 
 struct Ctrl {  // lives behind the operand stages in shared memory
-  unsigned long long a_full[2], a_empty[2], w_full[MAX_STAGES], w_empty[MAX_STAGES], acc_full[2], acc_empty[2];
+  unsigned long long a_full[MAX_STAGES], a_empty[MAX_STAGES], w_full[MAX_STAGES], w_empty[MAX_STAGES], acc_full[2], acc_empty[2];
   uint32_t tmem_base;
   int abort_flag;
   int shift[MAX_TAPS];
@@ -99,9 +99,11 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
   constexpr int WGROUPS = BN == 64 ? 4 : (BN == 128 ? 2 : 1);
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(smem_u32(&ctrl->a_full[s]), A_THREADS);
+    for (int s = 0; s < MAX_STAGES; ++s) {
+      mbar_init(smem_u32(&ctrl->a_full[s]), (uint32_t)((a.strip_rows + 31) / 32) * 32u);
       mbar_init(smem_u32(&ctrl->a_empty[s]), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
       mbar_init(smem_u32(&ctrl->acc_full[s]), 1);
       mbar_init(smem_u32(&ctrl->acc_empty[s]), EPI_WARPS * 32);
     }
@@ -235,65 +237,66 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
     }
   } else if (warp >= EPI_WARPS) {
     // ------------------------------ strip producers ------------------------------
-    const int t = threadIdx.x - EPI_WARPS * 32;
+    // A stage is staged as chunks of 32 rows, one warp per chunk (lane = row); chunk c of stage n
+    // goes to warp (n*chunks + c) % 8, so short strips (1x1 filters) keep several stages in flight.
+    const int aw = warp - EPI_WARPS;
+    const int chunks = (a.strip_rows + 31) / 32;
     const bool vec_ok = a.act.s1 == 1 && ((reinterpret_cast<uintptr_t>(a.act.ptr) & 15) == 0) &&
                         (a.act.s0 % 4 == 0) && (a.act.s2 % 4 == 0) && (a.act.s3 % 4 == 0);
-    uint32_t a_count = 0;
-    bool alive = true;
-    for (long long tile = blockIdx.x; tile < a.tiles_total && alive; tile += gridDim.x) {
+    const long long my_tiles = a.tiles_total > blockIdx.x ? (a.tiles_total - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const long long total_jobs = my_tiles * a.cblocks * chunks;
+    for (long long job = aw; job < total_jobs; job += A_WARPS) {
+      const uint32_t a_count = (uint32_t)(job / chunks);
+      const int chunk = (int)(job - (long long)a_count * chunks);
+      const long long tile = blockIdx.x + (long long)(a_count / a.cblocks) * gridDim.x;
+      const int cb = (int)(a_count % a.cblocks);
       const long long m_tile = (tile / a.tiles_n) % a.tiles_m;
       const int group = (int)((tile / a.tiles_n) / a.tiles_m);
-      const long long q0 = m_tile * BLOCK_M;
-      for (int cb = 0; cb < a.cblocks && alive; ++cb, ++a_count) {
-        const uint32_t as = a_count % a.a_stages;
-        bool waited = false;
-        const bool pa = PROF_ON(threadIdx.x == EPI_WARPS * 32);
-        PROF_T0(pa);
-        for (int r = t; r < a.strip_rows; r += A_THREADS) {
-          const long long q = q0 - a.halo + r;
-          bool ok = q >= 0 && q < a.q_total;
-          const float* src = a.act.ptr;
-          if (ok) {
-            const long long n = q / img_pitch;
-            const int rem = (int)(q - n * img_pitch);
-            const int y = rem / row_pitch, x = rem - y * row_pitch;
-            ok = y < a.H && x < a.W;
-            src += n * a.act.s0 + ((long long)group * a.kc + cb * KBLK) * a.act.s1 + (long long)y * a.act.s2 + (long long)x * a.act.s3;
-          }
-          float v[KBLK];
-          if (ok && vec_ok) {
-#pragma unroll
-            for (int j = 0; j < KBLK / 4; ++j) {
-              const float4 f = __ldg(reinterpret_cast<const float4*>(src) + j);
-              v[4 * j] = f.x; v[4 * j + 1] = f.y; v[4 * j + 2] = f.z; v[4 * j + 3] = f.w;
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < KBLK; ++j) v[j] = ok ? __ldg(src + j * a.act.s1) : 0.f;
-          }
-          if (!waited) {
-            const long long tw = pa ? clock64() : 0;
-            if (!mbar_wait(smem_u32(&ctrl->a_empty[as]), ((a_count / a.a_stages) & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_EMPTY)) { alive = false; break; }
-            if (pa) atomicAdd(a.prof + 6, (unsigned long long)(clock64() - tw));
-            waited = true;
-          }
-          const uint32_t p_hi = tiles_base + as * a_stage_bytes, p_lo = p_hi + a_plane;
-#pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            float h[4], l[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) split_tf32(v[c * 4 + j], h[j], l[j]);
-            const uint32_t o = sw128_offset(r, c * 4);
-            sts_f32x4(p_hi + o, h[0], h[1], h[2], h[3]);
-            sts_f32x4(p_lo + o, l[0], l[1], l[2], l[3]);
-          }
-        }
-        if (!alive) break;
-        if (!waited && !mbar_wait(smem_u32(&ctrl->a_empty[as]), ((a_count / a.a_stages) & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_EMPTY)) { alive = false; break; }
-        fence_proxy_async();
-        mbar_arrive(smem_u32(&ctrl->a_full[as]));
-        PROF_ADD(pa, 7);
+      const uint32_t as = a_count % a.a_stages;
+      const bool pa = PROF_ON(threadIdx.x == EPI_WARPS * 32);
+      PROF_T0(pa);
+      const int r = chunk * 32 + lane;
+      const long long q = m_tile * BLOCK_M - a.halo + r;
+      bool ok = r < a.strip_rows && q >= 0 && q < a.q_total;
+      const float* src = a.act.ptr;
+      if (ok) {
+        const long long n = q / img_pitch;
+        const int rem = (int)(q - n * img_pitch);
+        const int y = rem / row_pitch, x = rem - y * row_pitch;
+        ok = y < a.H && x < a.W;
+        src += n * a.act.s0 + ((long long)group * a.kc + cb * KBLK) * a.act.s1 + (long long)y * a.act.s2 + (long long)x * a.act.s3;
       }
+      float v[KBLK];
+      if (ok && vec_ok) {
+#pragma unroll
+        for (int j = 0; j < KBLK / 4; ++j) {
+          const float4 f = __ldg(reinterpret_cast<const float4*>(src) + j);
+          v[4 * j] = f.x; v[4 * j + 1] = f.y; v[4 * j + 2] = f.z; v[4 * j + 3] = f.w;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < KBLK; ++j) v[j] = ok ? __ldg(src + j * a.act.s1) : 0.f;
+      }
+      {
+        const long long tw = pa ? clock64() : 0;
+        if (!mbar_wait(smem_u32(&ctrl->a_empty[as]), ((a_count / a.a_stages) & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_EMPTY)) break;
+        if (pa) atomicAdd(a.prof + 6, (unsigned long long)(clock64() - tw));
+      }
+      if (r < a.strip_rows) {
+        const uint32_t p_hi = tiles_base + as * a_stage_bytes, p_lo = p_hi + a_plane;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          float h[4], l[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) split_tf32(v[c * 4 + j], h[j], l[j]);
+          const uint32_t o = sw128_offset(r, c * 4);
+          sts_f32x4(p_hi + o, h[0], h[1], h[2], h[3]);
+          sts_f32x4(p_lo + o, l[0], l[1], l[2], l[3]);
+        }
+      }
+      fence_proxy_async();
+      mbar_arrive(smem_u32(&ctrl->a_full[as]));
+      PROF_ADD(pa, 7);
     }
   } else {
     // ------------------------------ epilogue ------------------------------
@@ -395,7 +398,8 @@ static StripPlan plan_strip(const ConvGeom& g, bool is_dx) {
   for (int bn : {256, 128, 64}) {
     if (bn > 64 && nc <= bn / 2) continue;  // do not pad the column tile by more than 2x
     const int w_stage = bn * 256;
-    for (int a_stages : {2, 1}) {
+    for (int a_stages : {4, 3, 2, 1}) {
+      if (a_stages > 2 && a_stages * a_stage > SMEM_LIMIT / 2) continue;  // deep strip pipelines only while cheap
       const int left = SMEM_LIMIT - a_stages * a_stage;
       if (left < 2 * w_stage) continue;
       p.ok = true;

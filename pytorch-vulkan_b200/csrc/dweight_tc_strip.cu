@@ -131,7 +131,10 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int x_tasks = a.xblocks * 2;                           // an input block = rows 0..31 and 32..47
   const int tasks = x_tasks + NB;                              // warp-sized staging jobs per K block
-  constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+  // BN <= 128: the dY hi and lo planes (their 32-channel blocks are equally spaced) form ONE operand
+  // of 2*BN columns, so x_hi*[dy_hi | dy_lo] is a single MMA; the epilogue adds the two halves.
+  constexpr bool FUSE_HILO = BN <= 128;
+  constexpr uint32_t TMEM_COLS = FUSE_HILO ? 2 * BN : BN;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < MAX_STAGES; ++s) {
@@ -166,6 +169,7 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
 
   if (warp == MMA_WARP) {
     constexpr uint32_t idesc = make_idesc_tf32(128, BN) | (1u << 15) | (1u << 16);  // both operands MN-major
+    constexpr uint32_t idesc_wide = make_idesc_tf32(128, FUSE_HILO ? 2 * BN : BN) | (1u << 15) | (1u << 16);
     const uint32_t a_lbo = a.xblocks == 1 ? (uint32_t)g.dw * 128u : 2u * x_plane;
     for (int kb = 0; kb < kblocks; ++kb) {
       const int s = kb % a.stages;
@@ -180,9 +184,14 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
         for (int kg = 0; kg < KP / 8; ++kg) {
           const uint64_t da_hi = make_mn_desc(a_hi + kg * 1024u, a_lbo), da_lo = make_mn_desc(a_lo + kg * 1024u, a_lbo);
           const uint64_t db_hi = make_mn_desc(b_hi + kg * 1024u, KP * 128u), db_lo = make_mn_desc(b_lo + kg * 1024u, KP * 128u);
-          umma_tf32(tmem_acc, da_lo, db_hi, idesc, (kb | kg) != 0);
-          umma_tf32(tmem_acc, da_hi, db_lo, idesc, 1);
-          umma_tf32(tmem_acc, da_hi, db_hi, idesc, 1);
+          if (FUSE_HILO) {
+            umma_tf32(tmem_acc, da_hi, db_hi, idesc_wide, (kb | kg) != 0);
+            umma_tf32(tmem_acc, da_lo, db_hi, idesc, 1);
+          } else {
+            umma_tf32(tmem_acc, da_lo, db_hi, idesc, (kb | kg) != 0);
+            umma_tf32(tmem_acc, da_hi, db_lo, idesc, 1);
+            umma_tf32(tmem_acc, da_hi, db_hi, idesc, 1);
+          }
         }
         umma_commit(smem_u32(&ctrl->empty[s]));
       }
@@ -249,6 +258,12 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
         if (c0 >= cols_valid) break;
         float v[32];
         tmem_ld32(tmem_acc + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, v);
+        if (FUSE_HILO) {
+          float v2[32];
+          tmem_ld32(tmem_acc + ((uint32_t)(warp * 32) << 16) + (uint32_t)(BN + c0), v2);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] += v2[j];
+        }
         if (row_ok) {
 #pragma unroll
           for (int j = 0; j < 32; ++j)

@@ -170,6 +170,44 @@ struct ConvTcArgs {
   int cblocks, kblocks, tiles_n;
   int out_channels;         // cout (forward) or cin (dInput)
   int* status;
+  // dInput with stride > 1: the rows of the implicit GEMM are ordered by input-pixel parity class
+  // ("phase" (y % sh, x % sw)).  Every pixel of a phase is reached by the same subset of filter taps,
+  // so a tile only runs the K blocks of those taps: no MMA is spent on the structurally-zero taps
+  // (for stride 2 and a 3x3 filter that is 9/4 taps per pixel instead of 9).
+  int phases;                          // 1 = plain row order
+  int phase_tile_start[17];            // first M tile of each phase (prefix sums)
+  unsigned long long phase_taps[16];   // bit t set: filter tap t contributes to this phase
+};
+
+__device__ __forceinline__ int nth_set_bit(unsigned long long mask, int n) {
+  for (int i = 0; i < n; ++i) mask &= mask - 1;
+  return __ffsll((long long)mask) - 1;
+}
+
+// Row r of M tile `tile` -> output pixel (batch, y, x); false if the row is padding.
+struct RowMap {
+  int phases, sh, sw, p, q, hp, wq, out_w, out_hw;
+  long long rows_total, tile0;
+  __device__ __forceinline__ bool decode(long long tile, int r, long long& b, int& py, int& px) const {
+    if (phases == 1) {
+      const long long pix = tile * BLOCK_M + r;
+      if (pix >= rows_total) return false;
+      b = pix / out_hw;
+      const int pos = (int)(pix - b * out_hw);
+      py = pos / out_w;
+      px = pos - py * out_w;
+      return true;
+    }
+    const long long idx = (tile - tile0) * BLOCK_M + r;
+    const long long per = (long long)hp * wq;
+    if (per == 0 || idx >= rows_total) return false;
+    b = idx / per;
+    const int pos = (int)(idx - b * per);
+    const int yy = pos / wq;
+    py = yy * sh + p;
+    px = (pos - yy * wq) * sw + q;
+    return true;
+  }
 };
 
 template <int BN, bool IS_DX>
@@ -182,33 +220,48 @@ __global__ void __launch_bounds__(THREADS, 1) conv_tc_kernel(const ConvTcArgs a)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int group = blockIdx.y / a.tiles_n;
   const int n0 = (blockIdx.y % a.tiles_n) * BN;
-  const long long row0 = (long long)blockIdx.x * BLOCK_M;
   const int cols_valid = min(BN, a.nc - n0);
+  RowMap rm;
+  rm.phases = 1; rm.out_w = a.out_w; rm.out_hw = a.out_hw; rm.rows_total = a.rows_total; rm.tile0 = 0;
+  rm.sh = rm.sw = 1; rm.p = rm.q = 0; rm.hp = rm.wq = 0;
+  unsigned long long tapmask = ~0ull;
+  int kblocks = a.kblocks;
+  if (IS_DX && a.phases > 1) {
+    int ph = 0;
+    while (ph + 1 < a.phases && (int)blockIdx.x >= a.phase_tile_start[ph + 1]) ++ph;
+    rm.phases = a.phases; rm.sh = g.sh; rm.sw = g.sw; rm.p = ph / g.sw; rm.q = ph % g.sw;
+    rm.hp = (g.h - rm.p + g.sh - 1) / g.sh;
+    rm.wq = (g.w - rm.q + g.sw - 1) / g.sw;
+    rm.rows_total = (long long)g.n * rm.hp * rm.wq;
+    rm.tile0 = a.phase_tile_start[ph];
+    tapmask = a.phase_taps[ph];
+    kblocks = __popcll(tapmask) * a.cblocks;
+  }
 
   if (warp == PRODUCER_WARPS) {
-    mma_loop<BN>(p, tmem_acc, a.kblocks);
+    mma_loop<BN>(p, tmem_acc, kblocks);
   } else {
     // ---- producers ----
     const int grp = warp >> 3, t = threadIdx.x & (GROUP_THREADS - 1);
     const int row = t & 127, khalf = t >> 7;  // this thread stages 16 channels of one pixel row
-    const long long pix = row0 + row;
-    const bool row_ok = pix < a.rows_total;
-    long long base = 0;
-    int y0 = 0, x0 = 0;
+    long long base = 0, b = 0;
+    int y0 = 0, x0 = 0, py = 0, px = 0;
+    const bool row_ok = rm.decode(blockIdx.x, row, b, py, px);
+    const bool vec_ok = a.act.s1 == 1 && ((reinterpret_cast<uintptr_t>(a.act.ptr) & 15) == 0) && a.act.s0 % 4 == 0 &&
+                        a.act.s2 % 4 == 0 && a.act.s3 % 4 == 0;
     if (row_ok) {
-      const long long b = pix / a.out_hw;
-      const int pos = (int)(pix - b * a.out_hw);
-      const int py = pos / a.out_w, px = pos - py * a.out_w;
       if (IS_DX) { y0 = py + g.ph; x0 = px + g.pw; }
       else { y0 = py * g.sh - g.ph; x0 = px * g.sw - g.pw; }
       base = b * a.act.s0 + (long long)group * a.kc * a.act.s1;
     }
     const long long ktot = (long long)g.kh * g.kw * a.kc;
     const long long wrow0 = (long long)group * a.nc + n0;
-    for (int kb = grp; kb < a.kblocks; kb += 2) {
+    for (int kb = grp; kb < kblocks; kb += 2) {
       const int s = kb % Cfg::STAGES;
       const uint32_t it = (uint32_t)(kb / Cfg::STAGES);
-      const int tap = kb / a.cblocks, c0 = (kb - tap * a.cblocks) * KBLK + khalf * 16;
+      const int tap_slot = kb / a.cblocks, cblk = kb - tap_slot * a.cblocks;
+      const int tap = (IS_DX && a.phases > 1) ? nth_set_bit(tapmask, tap_slot) : tap_slot;
+      const int c0 = cblk * KBLK + khalf * 16;
       const int ky = tap / g.kw, kx = tap - ky * g.kw;
       bool ok = row_ok;
       int iy, ix;
@@ -229,8 +282,16 @@ __global__ void __launch_bounds__(THREADS, 1) conv_tc_kernel(const ConvTcArgs a)
       // Issue the global loads before waiting for the stage: they only need registers.
       float v[16];
       const float* src = a.act.ptr + base + (long long)c0 * a.act.s1 + (long long)iy * a.act.s2 + (long long)ix * a.act.s3;
+      if (ok && vec_ok) {
 #pragma unroll
-      for (int j = 0; j < 16; ++j) v[j] = ok ? __ldg(src + j * a.act.s1) : 0.f;
+        for (int j = 0; j < 4; ++j) {
+          const float4 f = __ldg(reinterpret_cast<const float4*>(src) + j);
+          v[4 * j] = f.x; v[4 * j + 1] = f.y; v[4 * j + 2] = f.z; v[4 * j + 3] = f.w;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = ok ? __ldg(src + j * a.act.s1) : 0.f;
+      }
       if (!mbar_wait(p.empty + 8 * s, (it & 1) ^ 1, p.abort_flag, p.status, STATUS_TIMEOUT_EMPTY)) break;
       const uint32_t a_hi = p.tiles + s * Cfg::STAGE_BYTES, a_lo = a_hi + Cfg::A_PLANE;
       const uint32_t b_hi = a_lo + Cfg::A_PLANE, b_lo = b_hi + Cfg::B_PLANE;
@@ -243,7 +304,7 @@ __global__ void __launch_bounds__(THREADS, 1) conv_tc_kernel(const ConvTcArgs a)
         sts_f32x4(a_hi + o, h[0], h[1], h[2], h[3]);
         sts_f32x4(a_lo + o, l[0], l[1], l[2], l[3]);
       }
-      produce_rows_kcontig<BN>(b_hi, b_lo, a.w_hi, a.w_lo, wrow0, cols_valid, ktot, (long long)kb * KBLK, warp & 7, lane);
+      produce_rows_kcontig<BN>(b_hi, b_lo, a.w_hi, a.w_lo, wrow0, cols_valid, ktot, (long long)tap * a.kc + cblk * KBLK, warp & 7, lane);
       fence_proxy_async();
       mbar_arrive(p.full + 8 * s);
     }
@@ -251,13 +312,10 @@ __global__ void __launch_bounds__(THREADS, 1) conv_tc_kernel(const ConvTcArgs a)
     if (mbar_wait(p.accum, 0, p.abort_flag, p.status, STATUS_TIMEOUT_ACCUM)) {
       tc_fence_after();
       const int q = warp & 3, chunk = warp >> 2;  // lane quarter of this warp, column chunk
-      const long long opix = row0 + q * 32 + lane;
-      const bool orow_ok = opix < a.rows_total;
-      long long obase = 0;
-      if (orow_ok) {
-        const long long b = opix / a.out_hw;
-        obase = (b * a.out_channels + (long long)group * a.nc) * a.out_hw + (opix - b * a.out_hw);
-      }
+      long long ob = 0, obase = 0;
+      int opy = 0, opx = 0;
+      const bool orow_ok = rm.decode(blockIdx.x, q * 32 + lane, ob, opy, opx);
+      if (orow_ok) obase = (ob * a.out_channels + (long long)group * a.nc) * a.out_hw + (long long)opy * a.out_w + opx;
       constexpr int COLS_PER_WARP = BN / 4;
 #pragma unroll 1
       for (int c = 0; c < COLS_PER_WARP; c += 32) {
@@ -270,7 +328,7 @@ __global__ void __launch_bounds__(THREADS, 1) conv_tc_kernel(const ConvTcArgs a)
           for (int j = 0; j < 32; ++j) {
             const int col = col0 + j;
             if (col < cols_valid) {
-              float r = v[j];
+              float r = kblocks > 0 ? v[j] : 0.f;  // a phase no tap reaches has a zero gradient
               if (!IS_DX && a.bias) r += __ldg(a.bias + ((long long)group * a.nc + n0 + col) * a.bias_stride);
               a.out[obase + (long long)(n0 + col) * a.out_hw] = r;
             }
@@ -554,7 +612,27 @@ static int conv_tc_run(const ConvGeom& g, bool is_dx, View4 act, View4 w, const 
   a.kblocks = g.kh * g.kw * a.cblocks;
   const int bn = pick_bn(a.nc);
   a.tiles_n = (a.nc + bn - 1) / bn;
-  const long long gx = div_up64(a.rows_total, BLOCK_M), gy = (long long)g.groups * a.tiles_n;
+  long long gx = div_up64(a.rows_total, BLOCK_M);
+  const long long gy = (long long)g.groups * a.tiles_n;
+  a.phases = 1;
+  if (is_dx && (g.sh > 1 || g.sw > 1) && g.sh * g.sw <= 16 && g.kh * g.kw <= 64) {
+    a.phases = g.sh * g.sw;
+    long long tiles = 0;
+    for (int ph = 0; ph < a.phases; ++ph) {
+      const int p = ph / g.sw, q = ph % g.sw;
+      const long long hp = (g.h - p + g.sh - 1) / g.sh, wq = (g.w - q + g.sw - 1) / g.sw;
+      unsigned long long mask = 0;
+      for (int ky = 0; ky < g.kh; ++ky)
+        for (int kx = 0; kx < g.kw; ++kx)
+          if (((p + g.ph - ky * g.dh) % g.sh + g.sh) % g.sh == 0 && ((q + g.pw - kx * g.dw) % g.sw + g.sw) % g.sw == 0)
+            mask |= 1ull << (ky * g.kw + kx);
+      a.phase_taps[ph] = mask;
+      a.phase_tile_start[ph] = (int)tiles;
+      tiles += div_up64((long long)g.n * hp * wq, BLOCK_M);
+    }
+    a.phase_tile_start[a.phases] = (int)tiles;
+    gx = tiles;
+  }
   if (gx > 2147483647ll || gy > 65535) return fail(B200_ERANGE, "tcgen05 convolution: grid exceeds launch limits");
   const dim3 grid((unsigned)gx, (unsigned)gy);
   if (is_dx) {

@@ -71,6 +71,8 @@ def test_tc_matches_golden_layer64():
     ((3, 32, 7, 7), 64, (3, 3), dict(padding=(1, 1))),            # tiles spanning several small images
     ((1, 32, 30, 41), 32, (5, 5), dict(padding=(2, 2))),          # 25 taps
     ((2, 64, 9, 9), 512, (1, 1), dict()),                         # two column tiles of 256
+    ((2, 32, 10, 11), 32, (2, 2), dict(stride=(3, 3))),           # input pixels that no filter tap reaches
+    ((2, 32, 13, 12), 64, (3, 3), dict(stride=(2, 3), padding=(1, 0), dilation=(2, 1))),
 ], ids=lambda s: "x".join(map(str, s[0])) + f"-co{s[1]}-k{s[2][0]}x{s[2][1]}" if isinstance(s, tuple) and len(s) == 4 else None)
 @pytest.mark.parametrize("channels_last", [False, True], ids=["nchw", "nhwc"])
 @pytest.mark.parametrize("variant", ["strip", "gather"])

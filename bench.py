@@ -9,7 +9,7 @@ Workload (N=1): the ResNet-50-style layer sweep, batch 64: 3x3 pad-1 layers
 One "step" is one pass over all 12 layer instances.  Inputs are seeded synthetic tensors
 (N(0,1) activations, kaiming-uniform weights) and stay resident in HBM for `value`; the
 `e2e` figure repeats the step through the C-ABI with pinned HOST buffers, host->device and
-device->host copies inside the timed region.  The working set of a step (about 1.7 GB) is
+device->host copies inside the timed region (uploads, kernels and downloads pipelined on three streams).  The working set of a step (about 1.7 GB) is
 far larger than L2, so no explicit L2 flush is needed between iterations.
 
 N>1 (torchrun, one rank per GPU): every rank runs the same sweep on its own batch of 64
@@ -285,25 +285,56 @@ def main():
         raise SystemExit(f"device status word is {status:#x}: a bounded wait gave up; numbers are invalid")
 
     # ---- end-to-end leg: host buffers in, host buffers out, copies inside the timed region ----
+    # Three streams pipeline the step over its layers: uploads of layer i+1, compute of layer i and
+    # downloads of layer i-1 overlap (PCIe is full duplex); events order the hand-offs, including the
+    # reuse of each layer's device buffers by the next step.
+    main = torch.cuda.current_stream()
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+    ev_in = [torch.cuda.Event() for _ in layers]
+    ev_comp = [torch.cuda.Event() for _ in layers]
+    ev_out = [torch.cuda.Event() for _ in layers]
+    ev_grads = torch.cuda.Event()
+
     def e2e_step():
-        for l in layers:
-            l.x.copy_(l.hx, non_blocking=True)
-            l.w.copy_(l.hw_, non_blocking=True)
-            l.go.copy_(l.hgo, non_blocking=True)
+        for i, l in enumerate(layers):
+            with torch.cuda.stream(s_in):
+                s_in.wait_event(ev_comp[i])  # previous step's kernels have finished reading these inputs
+                l.x.copy_(l.hx, non_blocking=True)
+                l.w.copy_(l.hw_, non_blocking=True)
+                l.go.copy_(l.hgo, non_blocking=True)
+                ev_in[i].record(s_in)
+            main.wait_event(ev_in[i])
+            main.wait_event(ev_out[i])      # previous step's downloads of y/dx/dw have left the buffers
             run_layer(l, False)
-            l.hy.copy_(l.y, non_blocking=True)
-            l.hdx.copy_(l.dx, non_blocking=True)
+            ev_comp[i].record(main)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_comp[i])
+                l.hy.copy_(l.y, non_blocking=True)
+                l.hdx.copy_(l.dx, non_blocking=True)
+                if dist is None:
+                    l.hdw.copy_(l.dw, non_blocking=True)
+                ev_out[i].record(s_out)
         if dist is not None:
             dist.all_reduce(grad_flat)
-        for l in layers:
-            l.hdw.copy_(l.dw, non_blocking=True)
+            ev_grads.record(main)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_grads)
+                for i, l in enumerate(layers):
+                    l.hdw.copy_(l.dw, non_blocking=True)
+                    ev_out[i].record(s_out)
+
+    def e2e_join():
+        main.wait_stream(s_in)
+        main.wait_stream(s_out)
     e2e_steps = max(2, min(args.steps, 5))
     e2e_step()
+    e2e_join()
     barrier()
     e_start, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e_start.record()
     for _ in range(e2e_steps):
         e2e_step()
+    e2e_join()
     e_end.record()
     barrier()
     e2e_ms = e_start.elapsed_time(e_end) / e2e_steps

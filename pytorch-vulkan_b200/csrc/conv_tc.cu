@@ -701,9 +701,6 @@ int tc_dweight(const ConvGeom& g, View4 x, View4 dy, float* dw, void* ws, size_t
   if (splits > 1) return finalize_splits((const float*)ws, dw, (long long)g.cout * a.m_total, splits, st);
   return B200_OK;
 }
-int tc_gemm(long long, long long, long long, const float*, long long, long long, const float*, long long, long long,
-            const float*, float, float, float*, cudaStream_t) {
-  return B200_EUNSUPPORTED;
-}
+
 
 }  // namespace b200

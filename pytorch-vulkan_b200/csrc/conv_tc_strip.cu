@@ -59,6 +59,9 @@ struct StripArgs {
   int halo, strip_rows;   // strip_rows is a multiple of 8
   int a_stages, w_stages;
   int is_dx;
+  int out_rowmajor;       // 0: NCHW planes.  1: [pixel][channel] rows (channels-last / GEMM C)
+  int out_vec4;           // row-major rows may be written with 16-byte stores
+  float alpha, beta;      // out = alpha * acc + beta * bias
   int* status;
   unsigned long long* prof;  // optional cycle counters of CTA 0 (B200_STRIP_PROFILE=1), else null
 };
@@ -322,7 +325,8 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
         const int rem = (int)(q - n * img_pitch);
         const int y = rem / row_pitch, x = rem - y * row_pitch;
         ok = y < a.H && x < a.W;
-        obase = ((n * a.out_channels + (long long)group * a.nc + n0) * a.H + y) * a.W + x;
+        obase = a.out_rowmajor ? (((n * a.H + y) * a.W + x) * (long long)a.out_channels + (long long)group * a.nc + n0)
+                               : (((n * a.out_channels + (long long)group * a.nc + n0) * a.H + y) * a.W + x);
       }
       const long long plane = (long long)a.H * a.W;
       const uint32_t tmem_acc = tmem_base + ab * ACC_COLS + ((uint32_t)(warp * 32) << 16);
@@ -345,10 +349,19 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             const int col = c0 + j;
-            if (col < cols_valid) {
-              float r = v[j];
-              if (a.bias) r += __ldg(a.bias + ((long long)group * a.nc + n0 + col) * a.bias_stride);
-              a.out[obase + (long long)col * plane] = r;
+            float r = a.alpha * v[j];
+            if (a.bias && col < cols_valid) r += a.beta * __ldg(a.bias + ((long long)group * a.nc + n0 + col) * a.bias_stride);
+            v[j] = r;
+          }
+          if (a.out_rowmajor && a.out_vec4 && c0 + 32 <= cols_valid) {
+            float4* dst = reinterpret_cast<float4*>(a.out + obase + c0);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) dst[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int col = c0 + j;
+              if (col < cols_valid) a.out[a.out_rowmajor ? obase + col : obase + (long long)col * plane] = v[j];
             }
           }
         }
@@ -434,7 +447,7 @@ static int launch_strip(const tcs::StripArgs& a, int grid, int smem, cudaStream_
 }
 
 int strip_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* bias, long long bias_stride, float* out,
-               void* ws, size_t ws_bytes, cudaStream_t st) {
+               void* ws, size_t ws_bytes, cudaStream_t st, bool rowmajor, float alpha, float beta) {
   using namespace tcs;
   const StripPlan plan = plan_strip(g, is_dx);
   if (!plan.ok) return fail(B200_EUNSUPPORTED, "strip kernel does not take this geometry");
@@ -460,6 +473,9 @@ int strip_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* b
   a.tiles_total = a.tiles_m * a.tiles_n * g.groups;
   a.halo = plan.halo; a.strip_rows = plan.strip_rows; a.a_stages = plan.a_stages; a.w_stages = plan.w_stages;
   a.is_dx = is_dx ? 1 : 0;
+  a.out_rowmajor = rowmajor ? 1 : 0;
+  a.alpha = alpha; a.beta = beta;
+  a.out_vec4 = rowmajor && a.out_channels % 4 == 0 && plan.bn % 4 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 && a.nc % 4 == 0;
   a.status = device_status_word();
   if (!a.status) return fail(B200_ECUDA, "device status word is not allocated");
   static unsigned long long* prof_buf = nullptr;
@@ -485,6 +501,29 @@ int strip_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* b
   if (plan.bn == 64) return launch_strip<64>(a, grid, plan.smem, st);
   if (plan.bn == 128) return launch_strip<128>(a, grid, plan.smem, st);
   return launch_strip<256>(a, grid, plan.smem, st);
+}
+
+
+// C[M,N] = alpha * A*B + beta * bias[n] as a 1x1 convolution over an M-pixel image with K input and N
+// output channels, written row-major.  Takes K % 32 == 0 and N >= 16; anything else is the caller's
+// CUDA-core kernel.  The staged copy of B comes from the caching allocator and is released on `st`.
+int tc_gemm(long long M, long long N, long long K, const float* A, long long sa0, long long sa1, const float* B,
+            long long sb0, long long sb1, const float* bias, float alpha, float beta, float* C, cudaStream_t st) {
+  if (K % tcs::KBLK != 0 || K < tcs::KBLK || N < 16 || M > 2147483647ll || N > 2147483647ll || K > 2147483647ll)
+    return fail(B200_EUNSUPPORTED, "tcgen05 GEMM is incompatible with this shape (needs K %% 32 == 0 and N >= 16)");
+  ConvGeom g{};
+  g.n = 1; g.cin = (int)K; g.cout = (int)N; g.h = 1; g.w = (int)M; g.kh = g.kw = 1; g.oh = 1; g.ow = (int)M;
+  g.sh = g.sw = 1; g.ph = g.pw = 0; g.dh = g.dw = 1; g.groups = 1; g.cig = (int)K; g.cog = (int)N;
+  if (!tcs::plan_strip(g, false).ok) return fail(B200_EUNSUPPORTED, "tcgen05 GEMM is incompatible with this shape");
+  const View4 act{A, 0, sa1, 0, sa0};   // [n=1][c=k][h=1][w=m]
+  const View4 wv{B, sb1, sb0, 0, 0};    // [co=n][ci=k][1][1]
+  void* ws = nullptr;
+  const size_t ws_bytes = sizeof(float) * (size_t)K * (size_t)N;
+  if (int rc = b200_malloc(&ws, ws_bytes, st)) return rc;
+  if (!bias || beta == 0.f) { bias = nullptr; beta = 0.f; }
+  const int rc = strip_conv(g, false, act, wv, bias, 1, C, ws, ws_bytes, st, true, alpha, beta);
+  b200_free(ws, st);
+  return rc;
 }
 
 }  // namespace b200

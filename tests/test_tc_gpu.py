@@ -104,3 +104,26 @@ def test_tc_dweight_split_boundaries_and_determinism():
     a = b200conv.conv2d_backward(go, x, w, padding=(1, 1), mask=(False, True, False), algo="tc")[1]
     b = b200conv.conv2d_backward(go, x, w, padding=(1, 1), mask=(False, True, False), algo="tc")[1]
     np.testing.assert_array_equal(a, b)
+
+
+@pytest.mark.parametrize("M,K,N", [(300, 96, 200), (128, 32, 16), (1000, 256, 64), (77, 64, 513)])
+def test_tc_gemm_strided_operands_and_addmm_epilogue(M, K, N):
+    rng = np.random.default_rng(M + K + N)
+    a = rng.standard_normal((M, K), dtype=np.float32)
+    bt = rng.standard_normal((N, K), dtype=np.float32)   # consumed as a transposed (stride-swapped) view
+    b = np.ascontiguousarray(bt.T)
+    bias = rng.standard_normal(N, dtype=np.float32)
+    for rhs in (bt.T, b, b[:, ::-1][:, ::-1]):
+        got = b200conv.gemm(a, rhs, algo="tc")
+        assert b200conv.last_kernel() == "tc_gemm"
+        assert oracle.rel_l2(got, oracle.gemm(a, rhs, f64=True)) <= GATE
+    at = np.ascontiguousarray(a.T).T                      # column-major A
+    assert oracle.rel_l2(b200conv.gemm(at, b, algo="tc"), oracle.gemm(a, b, f64=True)) <= GATE
+    for beta, alpha in ((1.0, 1.0), (0.0, 1.0), (0.5, -2.0)):
+        got = b200conv.gemm(a, bt.T, bias, alpha=alpha, beta=beta, algo="tc")
+        assert oracle.rel_l2(got, oracle.gemm(a, bt.T, bias, alpha=alpha, beta=beta, f64=True)) <= GATE
+    nan_bias = np.full(N, np.nan, np.float32)
+    assert np.isfinite(b200conv.gemm(a, b, nan_bias, alpha=1.0, beta=0.0, algo="tc")).all()
+    assert b200conv.device_status() == 0
+    with pytest.raises(b200conv.B200Error, match="incompatible"):
+        b200conv.gemm(a[:, :K - 1], b[:K - 1], algo="tc")

@@ -408,6 +408,11 @@ static StripPlan plan_strip(const ConvGeom& g, bool is_dx) {
   p.halo = g.ph * (g.w + g.pw) + g.pw;
   p.strip_rows = (BLOCK_M + 2 * p.halo + 7) / 8 * 8;
   const int a_stage = p.strip_rows * 256;
+  // Column tile: the widest tile makes the best use of shared-memory bandwidth per MMA, but a small
+  // image gives few 128-pixel row tiles; pick the width with the lowest modelled time
+  // waves(tiles / SMs) * width / efficiency(width).
+  const long long tiles_m = div_up64((long long)g.n * (g.h + g.ph) * (g.w + g.pw), BLOCK_M);
+  double best_cost = 0.0;
   for (int bn : {256, 128, 64}) {
     if (bn > 64 && nc <= bn / 2) continue;  // do not pad the column tile by more than 2x
     const int w_stage = bn * 256;
@@ -415,12 +420,18 @@ static StripPlan plan_strip(const ConvGeom& g, bool is_dx) {
       if (a_stages > 2 && a_stages * a_stage > SMEM_LIMIT / 2) continue;  // deep strip pipelines only while cheap
       const int left = SMEM_LIMIT - a_stages * a_stage;
       if (left < 2 * w_stage) continue;
-      p.ok = true;
-      p.bn = bn;
-      p.a_stages = a_stages;
-      p.w_stages = std::min(MAX_STAGES, left / w_stage);
-      p.smem = a_stages * a_stage + p.w_stages * w_stage + 1024 + (int)sizeof(Ctrl) + 64;
-      return p;
+      const long long tiles = tiles_m * ((nc + bn - 1) / bn) * g.groups;
+      const double eff = bn == 256 ? 1.0 : (bn == 128 ? 0.85 : 0.55);
+      const double cost = (double)div_up64(tiles, sm_count()) * bn / eff;
+      if (!p.ok || cost < best_cost) {
+        best_cost = cost;
+        p.ok = true;
+        p.bn = bn;
+        p.a_stages = a_stages;
+        p.w_stages = std::min(MAX_STAGES, left / w_stage);
+        p.smem = a_stages * a_stage + p.w_stages * w_stage + 1024 + (int)sizeof(Ctrl) + 64;
+      }
+      break;  // the deepest strip pipeline that fits is the one to use for this width
     }
   }
   return p;

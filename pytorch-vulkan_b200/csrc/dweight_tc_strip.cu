@@ -105,14 +105,24 @@ __device__ __forceinline__ void stage_block(const View4& v, long long chan0, int
 __device__ __forceinline__ void store_block(const float (&val)[32], int rows, int row0, uint32_t plane_hi,
                                             uint32_t plane_lo, int lane) {
   if (lane >= rows) return;
+  // With the 32-byte-base swizzle rows r and r+4 put the same 16-byte chunk into the same banks.
+  // Lanes 4-7 of every group of eight therefore write the two chunks of a 32-byte pair in the
+  // opposite order, which makes each 8-lane store wavefront conflict-free.
+  const bool swap = (lane >> 2) & 1;
 #pragma unroll
-  for (int c = 0; c < 8; ++c) {
-    float h[4], l[4];
+  for (int m = 0; m < 4; ++m) {
+    float h0[4], l0[4], h1[4], l1[4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) split_tf32(val[c * 4 + j], h[j], l[j]);
-    const uint32_t o = sw32b_offset(row0 + lane, c * 4);
-    sts_f32x4(plane_hi + o, h[0], h[1], h[2], h[3]);
-    sts_f32x4(plane_lo + o, l[0], l[1], l[2], l[3]);
+    for (int j = 0; j < 4; ++j) {
+      split_tf32(val[m * 8 + j], h0[j], l0[j]);
+      split_tf32(val[m * 8 + 4 + j], h1[j], l1[j]);
+    }
+    const uint32_t o0 = sw32b_offset(row0 + lane, m * 8), o1 = o0 + 16;
+    const uint32_t oa = swap ? o1 : o0, ob = swap ? o0 : o1;
+    sts_f32x4(plane_hi + oa, swap ? h1[0] : h0[0], swap ? h1[1] : h0[1], swap ? h1[2] : h0[2], swap ? h1[3] : h0[3]);
+    sts_f32x4(plane_lo + oa, swap ? l1[0] : l0[0], swap ? l1[1] : l0[1], swap ? l1[2] : l0[2], swap ? l1[3] : l0[3]);
+    sts_f32x4(plane_hi + ob, swap ? h0[0] : h1[0], swap ? h0[1] : h1[1], swap ? h0[2] : h1[2], swap ? h0[3] : h1[3]);
+    sts_f32x4(plane_lo + ob, swap ? l0[0] : l1[0], swap ? l0[1] : l1[1], swap ? l0[2] : l1[2], swap ? l0[3] : l1[3]);
   }
 }
 

@@ -193,7 +193,9 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
     const int t = (threadIdx.x - (EPI_WARPS + A_WARPS) * 32) % WT;
     const uint32_t wgroup = (uint32_t)((threadIdx.x - (EPI_WARPS + A_WARPS) * 32) / WT);
     uint32_t w_count = 0;
-    bool alive = true;
+    // no more groups than stages (same parity argument as for the strip producers)
+    const uint32_t wgroups_active = (uint32_t)min(WGROUPS, a.w_stages);
+    bool alive = wgroup < wgroups_active;
     for (long long tile = blockIdx.x; tile < a.tiles_total && alive; tile += gridDim.x) {
       const int n_tile = (int)(tile % a.tiles_n);
       const int group = (int)((tile / a.tiles_n) / a.tiles_m);
@@ -202,7 +204,7 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
       const float* wrow = a.wp + ((long long)group * a.nc + n0) * a.taps * a.kc;
       for (int cb = 0; cb < a.cblocks && alive; ++cb) {
         for (int tap = 0; tap < a.taps; ++tap, ++w_count) {
-          if (w_count % WGROUPS != wgroup) continue;
+          if (w_count % wgroups_active != wgroup) continue;
           const uint32_t ws = w_count % a.w_stages;
           // loads first (registers only), then wait for the stage, then split and store
           constexpr int TASKS = BN * 8 / WT;  // (row, 16-byte chunk) pairs per thread
@@ -248,7 +250,10 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
                         (a.act.s0 % 4 == 0) && (a.act.s2 % 4 == 0) && (a.act.s3 % 4 == 0);
     const long long my_tiles = a.tiles_total > blockIdx.x ? (a.tiles_total - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
     const long long total_jobs = my_tiles * a.cblocks * chunks;
-    for (long long job = aw; job < total_jobs; job += A_WARPS) {
+    // A warp's consecutive jobs must not be more than a_stages stages apart: a waiter that skips a
+    // whole phase of a stage's mbarrier would see the parity of an older phase and run ahead.
+    const int a_warps = min(A_WARPS, chunks * a.a_stages);
+    for (long long job = aw; job < total_jobs && aw < a_warps; job += a_warps) {
       const uint32_t a_count = (uint32_t)(job / chunks);
       const int chunk = (int)(job - (long long)a_count * chunks);
       const long long tile = blockIdx.x + (long long)(a_count / a.cblocks) * gridDim.x;

@@ -216,8 +216,11 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
     const bool y_vec = a.dy.s1 == 1 && ((reinterpret_cast<uintptr_t>(a.dy.ptr) & 15) == 0) && a.dy.s0 % 4 == 0 &&
                        a.dy.s2 % 4 == 0 && a.dy.s3 % 4 == 0;
     const long long total_jobs = (long long)kblocks * tasks;
-    bool alive = true;
-    for (long long job = warp; job < total_jobs && alive; job += PRODUCER_WARPS) {
+    // consecutive jobs of a warp stay within `stages` K blocks of each other (a waiter that skipped
+    // a whole phase of a stage's mbarrier would see the parity of an older phase and run ahead)
+    const int warps_active = min(PRODUCER_WARPS, tasks * a.stages);
+    bool alive = warp < warps_active;
+    for (long long job = warp; job < total_jobs && alive; job += warps_active) {
       const int kb = (int)(job / tasks), j = (int)(job - (long long)kb * tasks);
       const int s = kb % a.stages;
       const long long k0 = k_begin + (long long)kb * KP;

@@ -127,3 +127,11 @@ def test_tc_gemm_strided_operands_and_addmm_epilogue(M, K, N):
     assert b200conv.device_status() == 0
     with pytest.raises(b200conv.B200Error, match="incompatible"):
         b200conv.gemm(a[:, :K - 1], b[:K - 1], algo="tc")
+
+
+@pytest.mark.parametrize("n,c,hw", [(4, 256, 32), (2, 64, 112), (1, 32, 150)])
+def test_tc_strip_pipeline_depth_corner_cases(n, c, hw):
+    # wide images leave room for a single strip stage / fewer weight stages than producer groups:
+    # the producer job assignment must keep every warp within one phase of each stage's barrier
+    errs = _run_case((n, c, hw, hw), c, (3, 3), padding=(1, 1), seed=n + c + hw, phases=("y", "dx", "dw"))
+    assert max(errs.values()) < 2e-5, errs

@@ -174,7 +174,8 @@ class Layer:
         self.hy, self.hdx = (torch.empty(t.shape).pin_memory() for t in (self.y, self.dx))
         self.hdw = torch.empty(self.w_shape).pin_memory()
         self.flops = 3 * self.p.flops()
-        self.ws_bytes = max(b200conv.workspace_bytes(self.p, ph) for ph in (0, 1, 2))
+        # scratch budget per call: 512 MiB (the operator's default is 64 MiB; Winograd chunks less with more)
+        self.ws_bytes = max(b200conv.workspace_bytes(self.p, ph, budget=512 << 20) for ph in (0, 1, 2))
         self.h2d = sum(t.numel() * 4 for t in (self.hx, self.hw_, self.hgo))
         self.d2h = sum(t.numel() * 4 for t in (self.hy, self.hdx, self.hdw))
 

@@ -82,7 +82,14 @@ int tc_gemm(long long M, long long N, long long K, const float* A, long long sa0
 // persistent strip kernel for stride-1 "same" convolutions (conv_tc_strip.cu)
 bool strip_supported(const ConvGeom& g, int phase);
 int strip_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* bias, long long bias_stride, float* out,
-               void* ws, size_t ws_bytes, cudaStream_t st, bool rowmajor = false, float alpha = 1.f, float beta = 1.f);
+               void* ws, size_t ws_bytes, cudaStream_t st, bool rowmajor = false, float alpha = 1.f, float beta = 1.f,
+               const float* staged_weights = nullptr);
+
+// Winograd F(4x4,3x3) forward / dInput (winograd.cu)
+bool winograd_supported(const ConvGeom& g, int phase);
+size_t winograd_workspace(const ConvGeom& g, int phase, size_t budget);
+int winograd_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* bias, long long bias_stride, float* out,
+                  void* ws, size_t ws_bytes, cudaStream_t st);
 
 // dWeight strip kernel (dweight_tc_strip.cu)
 bool dweight_strip_supported(const ConvGeom& g);

@@ -68,7 +68,7 @@ static int check_params(const b200_conv_params* p) {
 }
 
 // Returns the candidate to run, or a negative code when a forced one is not applicable.
-static int select(const ConvGeom& g, int phase, int algo) {
+static int select(const ConvGeom& g, int phase, int algo, size_t workspace) {
   const long long rows = (long long)g.n * g.oh * g.ow, cols = (long long)g.cig * g.kh * g.kw;
   if (phase == B200_PHASE_DBIAS) return algo == B200_ALGO_DIRECT ? B200_ALGO_DIRECT : B200_ALGO_TILED;
   switch (algo) {
@@ -80,12 +80,19 @@ static int select(const ConvGeom& g, int phase, int algo) {
         return fail(B200_EUNSUPPORTED, "forced tcgen05 candidate is incompatible with this geometry");
       return algo;
     case B200_ALGO_WINOGRAD:
-      return fail(B200_EUNSUPPORTED, "forced Winograd candidate is incompatible with this geometry");
+      if (!winograd_supported(g, phase))
+        return fail(B200_EUNSUPPORTED, "forced Winograd candidate is incompatible with this geometry or phase");
+      return algo;
     case B200_ALGO_AUTO:
       break;
     default:
       return fail(B200_EINVAL, "unknown algorithm id %d", algo);
   }
+  // Winograd F(4x4,3x3) pays for its transform passes once the channel contraction is long:
+  // measured faster than the direct tcgen05 kernels from 256 channels per group on both sides.
+  if ((phase == B200_PHASE_FORWARD || phase == B200_PHASE_DINPUT) && g.cig >= 256 && g.cog >= 256 &&
+      winograd_supported(g, phase) && winograd_workspace(g, phase, workspace) > 0)
+    return B200_ALGO_WINOGRAD;
   if (tc_supported(g, phase)) return B200_ALGO_TC;
   // Thresholds of the reference heuristic for leaving the one-thread-per-output kernels.
   if (phase == B200_PHASE_FORWARD) return (g.cog >= 8 && cols >= 16 && rows >= 32) ? B200_ALGO_TILED : B200_ALGO_DIRECT;
@@ -133,15 +140,14 @@ int b200_conv2d_geometry(b200_conv_params* out, int64_t n, int64_t cin, int64_t 
 }
 
 int b200_conv2d_select(const b200_conv_params* p, int phase, int algo, size_t workspace_bytes) {
-  (void)workspace_bytes;
   if (int rc = check_params(p)) return rc;
-  return select(to_geom(*p), phase, algo);
+  return select(to_geom(*p), phase, algo, workspace_bytes);
 }
 
 size_t b200_conv2d_workspace(const b200_conv_params* p, int phase, int algo, size_t budget_bytes) {
   if (check_params(p) != B200_OK) return 0;
   const ConvGeom g = to_geom(*p);
-  const int chosen = select(g, phase, algo);
+  const int chosen = select(g, phase, algo, budget_bytes);
   if (chosen < 0) return 0;
   if (phase == B200_PHASE_DBIAS) {
     const int slabs = dbias_slabs(g, contiguous_view(nullptr, g.cout, g.oh, g.ow), budget_bytes);
@@ -152,6 +158,7 @@ size_t b200_conv2d_workspace(const b200_conv_params* p, int phase, int algo, siz
     return s > 1 ? (size_t)s * g.cout * sizeof(float) : 0;
   }
   if (chosen == B200_ALGO_TC) return tc_workspace(g, phase, budget_bytes, nullptr, nullptr);
+  if (chosen == B200_ALGO_WINOGRAD) return winograd_workspace(g, phase, budget_bytes);
   if (chosen == B200_ALGO_TILED && phase == B200_PHASE_DWEIGHT) return simt_dweight_plan(g, budget_bytes).bytes;
   return 0;
 }
@@ -163,11 +170,14 @@ int b200_conv2d_forward(const b200_conv_params* p, b200_view4 x, b200_view4 w, c
   if (int rc = ensure_init()) return rc;
   if (!x.ptr || !w.ptr || !y) return fail(B200_EINVAL, "convolution forward: null tensor");
   const ConvGeom g = to_geom(*p);
-  const int chosen = select(g, B200_PHASE_FORWARD, algo);
+  const int chosen = select(g, B200_PHASE_FORWARD, algo, workspace ? workspace_bytes : 0);
   if (chosen < 0) return chosen;
   cudaStream_t st = (cudaStream_t)stream;
   if (!bias) bias_stride = 0;
   switch (chosen) {
+    case B200_ALGO_WINOGRAD:
+      note_kernel("winograd_f4_forward");
+      return winograd_conv(g, false, to_view(x), to_view(w), bias, bias_stride, y, workspace, workspace_bytes, st);
     case B200_ALGO_TC:
       note_kernel("tc_igemm_forward");
       return tc_forward(g, to_view(x), to_view(w), bias, bias_stride, y, workspace, workspace_bytes, st);
@@ -186,10 +196,13 @@ int b200_conv2d_dinput(const b200_conv_params* p, b200_view4 dy, b200_view4 w, f
   if (int rc = ensure_init()) return rc;
   if (!dy.ptr || !w.ptr || !dx) return fail(B200_EINVAL, "convolution dInput: null tensor");
   const ConvGeom g = to_geom(*p);
-  const int chosen = select(g, B200_PHASE_DINPUT, algo);
+  const int chosen = select(g, B200_PHASE_DINPUT, algo, workspace ? workspace_bytes : 0);
   if (chosen < 0) return chosen;
   cudaStream_t st = (cudaStream_t)stream;
   switch (chosen) {
+    case B200_ALGO_WINOGRAD:
+      note_kernel("winograd_f4_dinput");
+      return winograd_conv(g, true, to_view(dy), to_view(w), nullptr, 0, dx, workspace, workspace_bytes, st);
     case B200_ALGO_TC:
       note_kernel("tc_igemm_dinput");
       return tc_dinput(g, to_view(dy), to_view(w), dx, workspace, workspace_bytes, st);
@@ -208,7 +221,7 @@ int b200_conv2d_dweight(const b200_conv_params* p, b200_view4 x, b200_view4 dy, 
   if (int rc = ensure_init()) return rc;
   if (!x.ptr || !dy.ptr || !dw) return fail(B200_EINVAL, "convolution dWeight: null tensor");
   const ConvGeom g = to_geom(*p);
-  const int chosen = select(g, B200_PHASE_DWEIGHT, algo);
+  const int chosen = select(g, B200_PHASE_DWEIGHT, algo, workspace ? workspace_bytes : 0);
   if (chosen < 0) return chosen;
   cudaStream_t st = (cudaStream_t)stream;
   if (!workspace) workspace_bytes = 0;

@@ -463,18 +463,21 @@ static int launch_strip(const tcs::StripArgs& a, int grid, int smem, cudaStream_
 }
 
 int strip_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* bias, long long bias_stride, float* out,
-               void* ws, size_t ws_bytes, cudaStream_t st, bool rowmajor, float alpha, float beta) {
+               void* ws, size_t ws_bytes, cudaStream_t st, bool rowmajor, float alpha, float beta, const float* staged_weights) {
   using namespace tcs;
   const StripPlan plan = plan_strip(g, is_dx);
   if (!plan.ok) return fail(B200_EUNSUPPORTED, "strip kernel does not take this geometry");
   const size_t wcount = (size_t)g.cout * g.cig * g.kh * g.kw;
-  if (!ws || ws_bytes < sizeof(float) * wcount || (reinterpret_cast<uintptr_t>(ws) & 15))
-    return fail(B200_EWORKSPACE, "tcgen05 convolution needs a 16-byte aligned workspace of %zu bytes (got %zu)",
-                sizeof(float) * wcount, ws_bytes);
-  float* wp = (float*)ws;
-  stage_weights_kernel<<<(unsigned)div_up64((long long)wcount, 256), 256, 0, st>>>(g, w, is_dx ? 1 : 0, wp, (long long)wcount);
-  count_launch();
-  if (int rc = launch_check("stage_weights_kernel")) return rc;
+  const float* wp = staged_weights;  // already [groups][nc][taps][kc]
+  if (!wp) {
+    if (!ws || ws_bytes < sizeof(float) * wcount || (reinterpret_cast<uintptr_t>(ws) & 15))
+      return fail(B200_EWORKSPACE, "tcgen05 convolution needs a 16-byte aligned workspace of %zu bytes (got %zu)",
+                  sizeof(float) * wcount, ws_bytes);
+    stage_weights_kernel<<<(unsigned)div_up64((long long)wcount, 256), 256, 0, st>>>(g, w, is_dx ? 1 : 0, (float*)ws, (long long)wcount);
+    count_launch();
+    if (int rc = launch_check("stage_weights_kernel")) return rc;
+    wp = (const float*)ws;
+  }
   StripArgs a{};
   a.g = g; a.act = act; a.wp = wp; a.bias = is_dx ? nullptr : bias; a.bias_stride = bias_stride; a.out = out;
   a.H = g.h; a.W = g.w; a.pr = g.ph; a.pc = g.pw;

@@ -135,3 +135,38 @@ def test_tc_strip_pipeline_depth_corner_cases(n, c, hw):
     # the producer job assignment must keep every warp within one phase of each stage's barrier
     errs = _run_case((n, c, hw, hw), c, (3, 3), padding=(1, 1), seed=n + c + hw, phases=("y", "dx", "dw"))
     assert max(errs.values()) < 2e-5, errs
+
+
+@pytest.mark.parametrize("shape", [
+    ((2, 32, 9, 11), 48, dict(padding=(1, 1))),
+    ((2, 64, 33, 33), 64, dict(padding=(1, 1))),        # ragged edge tiles
+    ((1, 64, 16, 20), 96, dict(padding=(0, 0))),        # valid convolution: output smaller than input
+    ((2, 32, 12, 12), 32, dict(padding=(2, 2))),        # output larger than input
+    ((2, 128, 14, 14), 128, dict(padding=(1, 1), groups=4)),
+    ((3, 256, 7, 7), 256, dict(padding=(1, 1))),
+], ids=lambda s: "x".join(map(str, s[0])) + f"-co{s[1]}" if isinstance(s, tuple) and len(s) == 3 else None)
+@pytest.mark.parametrize("budget", [1 << 30, 3 << 20], ids=["one-chunk", "chunked"])
+def test_winograd_f4_forward_and_dinput(shape, budget):
+    xshape, cout, kw = shape
+    args = dict(stride=(1, 1), padding=kw.get("padding", (0, 0)), dilation=(1, 1), groups=kw.get("groups", 1))
+    g = oracle.geometry(xshape, cout, (3, 3), **args)
+    x, w = _rand(g.x_shape, 11), _rand(g.w_shape, 12, 0.1)
+    b, go = _rand((cout,), 13), _rand(g.y_shape, 14)
+    want = _reference(x, w, b, go, args)
+    p = b200conv.geometry(xshape, cout, (3, 3), **args)
+    if b200conv.workspace_bytes(p, b200conv.PHASE_FORWARD, b200conv.ALGO_WINOGRAD, budget) == 0:
+        with pytest.raises(b200conv.B200Error, match="[Ww]orkspace"):
+            b200conv.conv2d_forward(x, w, b, algo="winograd", budget=budget, **args)
+        return
+    y = b200conv.conv2d_forward(x, w, b, algo="winograd", budget=budget, **args)
+    assert b200conv.last_kernel() == "winograd_f4_forward"
+    errs = [oracle.rel_l2(y, want[0])]
+    if (cout // args["groups"]) % 32 == 0:   # dInput contracts over 32-channel blocks of Cout/groups
+        dx, _, _ = b200conv.conv2d_backward(go, x, w, mask=(True, False, False), algo="winograd", budget=budget, **args)
+        assert b200conv.last_kernel() == "winograd_f4_dinput"
+        errs.append(oracle.rel_l2(dx, want[1]))
+    else:
+        with pytest.raises(b200conv.B200Error, match="incompatible"):
+            b200conv.conv2d_backward(go, x, w, mask=(True, False, False), algo="winograd", budget=budget, **args)
+    assert b200conv.device_status() == 0
+    assert max(errs) <= GATE, errs

@@ -422,6 +422,7 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_tc_kernel(const DwTcArgs a
   } else {
     const int grp = warp >> 3, wi = warp & 7;
     const int ohw = g.oh * g.ow;
+    const bool channels_last = a.x.s1 == 1 && a.dy.s1 == 1 && a.x.s3 != 1 && a.dy.s3 != 1;
     for (int kb = grp; kb < kblocks; kb += 2) {
       const int s = kb % Cfg::STAGES;
       const uint32_t it = (uint32_t)(kb / Cfg::STAGES);
@@ -440,6 +441,55 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_tc_kernel(const DwTcArgs a
       if (!mbar_wait(p.empty + 8 * s, (it & 1) ^ 1, p.abort_flag, p.status, STATUS_TIMEOUT_EMPTY)) break;
       const uint32_t a_hi = p.tiles + s * Cfg::STAGE_BYTES, a_lo = a_hi + Cfg::A_PLANE;
       const uint32_t b_hi = a_lo + Cfg::A_PLANE, b_lo = b_hi + Cfg::B_PLANE;
+      if (channels_last) {
+        // Channels-last operands: lane = row (32 consecutive channels are contiguous in memory), the
+        // 32 pixels of the K block are walked four at a time; each pixel's coordinates come from the
+        // lane that decoded it.  One 16-byte swizzled store per lane per four pixels.
+        constexpr int ROW_BLOCKS = 4 + BN / 32;
+#pragma unroll 1
+        for (int rb = wi; rb < ROW_BLOCKS; rb += 8) {
+          const bool is_a = rb < 4;
+          const int r = (is_a ? rb : rb - 4) * 32 + lane;
+          DwRow row;
+          row.chan_off = -1; row.ydelta = 0; row.xdelta = 0;
+          if (is_a) row = rows[r];
+          const long long ychan = ((long long)group * g.cog + n0 + r) * a.dy.s1;
+          const bool brow_ok = r < cols_valid;
+          const uint32_t p_hi = is_a ? a_hi : b_hi, p_lo = is_a ? a_lo : b_lo;
+#pragma unroll 1
+          for (int kq = 0; kq < 8; kq += 2) {
+            float v[8];
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk) {
+              const int k = kq * 4 + kk;
+              const bool kok = __shfl_sync(0xffffffffu, ok ? 1 : 0, k) != 0;
+              const long long kxb = __shfl_sync(0xffffffffu, xb, k), kyb = __shfl_sync(0xffffffffu, yb, k);
+              const int kiy = __shfl_sync(0xffffffffu, iy0, k), kix = __shfl_sync(0xffffffffu, ix0, k);
+              float val = 0.f;
+              if (is_a) {
+                const int iy = kiy + row.ydelta, ix = kix + row.xdelta;
+                if (kok && row.chan_off >= 0 && iy >= 0 && iy < g.h && ix >= 0 && ix < g.w)
+                  val = __ldg(a.x.ptr + kxb + row.chan_off + (long long)iy * a.x.s2 + (long long)ix * a.x.s3);
+              } else if (kok && brow_ok) {
+                val = __ldg(a.dy.ptr + kyb + ychan);
+              }
+              v[kk] = val;
+            }
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+              float h[4], l[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) split_tf32(v[half * 4 + j], h[j], l[j]);
+              const uint32_t o = sw128_offset(r, (kq + half) * 4);
+              sts_f32x4(p_hi + o, h[0], h[1], h[2], h[3]);
+              sts_f32x4(p_lo + o, l[0], l[1], l[2], l[3]);
+            }
+          }
+        }
+        fence_proxy_async();
+        mbar_arrive(p.full + 8 * s);
+        continue;
+      }
       // A rows: shifted input, 16 consecutive (tap, ci) rows per warp
 #pragma unroll 1
       for (int r0 = 0; r0 < 16; r0 += 8) {

@@ -83,7 +83,9 @@ int tc_gemm(long long M, long long N, long long K, const float* A, long long sa0
 bool strip_supported(const ConvGeom& g, int phase);
 int strip_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* bias, long long bias_stride, float* out,
                void* ws, size_t ws_bytes, cudaStream_t st, bool rowmajor = false, float alpha = 1.f, float beta = 1.f,
-               const float* staged_weights = nullptr);
+               const float* staged_images = nullptr);  // images already written for strip_column_tile()
+int strip_column_tile(const ConvGeom& g, bool is_dx);   // column tile the plan picks, 0 if unsupported
+size_t strip_workspace(const ConvGeom& g, int phase);  // bytes of the weight stage images
 
 // Winograd F(4x4,3x3) forward / dInput (winograd.cu)
 bool winograd_supported(const ConvGeom& g, int phase);

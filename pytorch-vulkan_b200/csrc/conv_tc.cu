@@ -606,8 +606,10 @@ size_t tc_workspace(const ConvGeom& g, int phase, size_t budget, int* splits_out
   (void)budget;
   if (splits_out) *splits_out = 1;
   if (span_out) *span_out = 0;
-  if (phase == B200_PHASE_FORWARD || phase == B200_PHASE_DINPUT)
-    return 2 * sizeof(float) * (size_t)g.cout * g.cig * g.kh * g.kw;  // hi + lo planes
+  if (phase == B200_PHASE_FORWARD || phase == B200_PHASE_DINPUT) {
+    const size_t planes = 2 * sizeof(float) * (size_t)g.cout * g.cig * g.kh * g.kw;  // hi + lo
+    return strip_allowed() && strip_supported(g, phase) ? std::max(planes, strip_workspace(g, phase)) : planes;
+  }
   if (phase == B200_PHASE_DWEIGHT && strip_allowed() && dweight_strip_supported(g)) {
     if (splits_out) *splits_out = 0;
     return dweight_strip_workspace(g, budget);

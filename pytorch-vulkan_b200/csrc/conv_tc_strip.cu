@@ -15,11 +15,12 @@
 // (dy, dx) is then the constant row shift dy*(W+pc) + dx for every pixel, and reads that leave the
 // image land on zero rows of the strip.  Accumulator rows that fall on padding are discarded.
 //
-// CTA roles (672 threads, persistent over tiles of 128 padded pixels x BN output channels):
+// CTA roles (448 threads, persistent over tiles of 128 padded pixels x BN output channels):
 //   warps 0-3    epilogue: tcgen05.ld of a finished accumulator, bias, coalesced NCHW stores
 //   warps 4-11   strip producers: gather from the caller's strided view, split_tf32, swizzled stores
-//   warps 12-19  weight producers: K-contiguous staged weights -> split_tf32 -> swizzled stores
-//   warp 20      TMEM allocation and the tcgen05.mma stream (lo*hi, hi*lo, hi*hi per tap)
+//   warp 12      weight stages: one bulk copy (cp.async.bulk -> mbarrier complete_tx) of a pre-split,
+//                pre-swizzled image per stage (stage_weights_kernel writes the images once per call)
+//   warp 13      TMEM allocation and the tcgen05.mma stream (lo*hi, hi*lo, hi*hi per tap)
 // The accumulator is double-buffered in TMEM, so the epilogue of tile i overlaps the main loop of
 // tile i+1.  All hand-offs are mbarriers with bounded waits.
 //
@@ -37,8 +38,7 @@ namespace tcs {
 using namespace tc;
 
 constexpr int BLOCK_M = 128, KBLK = 32;
-constexpr int EPI_WARPS = 4, A_WARPS = 8, W_WARPS = 8;
-constexpr int A_THREADS = A_WARPS * 32, W_THREADS = W_WARPS * 32;
+constexpr int EPI_WARPS = 4, A_WARPS = 8, W_WARPS = 1;
 constexpr int MMA_WARP = EPI_WARPS + A_WARPS + W_WARPS;
 constexpr int THREADS = (MMA_WARP + 1) * 32;
 constexpr int MAX_TAPS = 64;
@@ -48,7 +48,7 @@ constexpr int SMEM_LIMIT = 232448 - 2048;  // 227 KB per CTA minus the control b
 struct StripArgs {
   ConvGeom g;
   View4 act;              // forward: x.  dInput: dy (same spatial size as the output)
-  const float* wp;        // staged weights [groups][nc][taps][kc], raw FP32
+  const float* wp;        // weight stage images [groups][tiles_n][cblocks][taps] of BN*256 bytes (stage_weights_kernel)
   const float* bias;
   long long bias_stride;
   float* out;             // contiguous NCHW [n][out_channels][H][W]
@@ -97,9 +97,6 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
   constexpr bool FUSE_HILO = BN <= 128;
   constexpr uint32_t ACC_COLS = FUSE_HILO ? 2 * BN : BN;
   constexpr uint32_t TMEM_COLS = 2 * ACC_COLS;
-  // Weight stages are short (one tap = 12 MMAs), so the weight producers work as WGROUPS
-  // independent groups on alternate stages: that many global-load round trips overlap.
-  constexpr int WGROUPS = BN == 64 ? 4 : (BN == 128 ? 2 : 1);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < MAX_STAGES; ++s) {
@@ -111,7 +108,7 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
       mbar_init(smem_u32(&ctrl->acc_empty[s]), EPI_WARPS * 32);
     }
     for (int s = 0; s < MAX_STAGES; ++s) {
-      mbar_init(smem_u32(&ctrl->w_full[s]), W_THREADS / WGROUPS);
+      mbar_init(smem_u32(&ctrl->w_full[s]), 1);  // the issuing thread's arrive.expect_tx; the copy completes the bytes
       mbar_init(smem_u32(&ctrl->w_empty[s]), 1);
     }
     ctrl->abort_flag = 0;
@@ -187,58 +184,32 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
       if (alive && lane == 0) umma_commit(smem_u32(&ctrl->acc_full[ab]));
       __syncwarp();
     }
-  } else if (warp >= EPI_WARPS + A_WARPS) {
-    // ------------------------------ weight producers ------------------------------
-    constexpr int WT = W_THREADS / WGROUPS;
-    const int t = (threadIdx.x - (EPI_WARPS + A_WARPS) * 32) % WT;
-    const uint32_t wgroup = (uint32_t)((threadIdx.x - (EPI_WARPS + A_WARPS) * 32) / WT);
-    uint32_t w_count = 0;
-    // no more groups than stages (same parity argument as for the strip producers)
-    const uint32_t wgroups_active = (uint32_t)min(WGROUPS, a.w_stages);
-    bool alive = wgroup < wgroups_active;
-    for (long long tile = blockIdx.x; tile < a.tiles_total && alive; tile += gridDim.x) {
-      const int n_tile = (int)(tile % a.tiles_n);
-      const int group = (int)((tile / a.tiles_n) / a.tiles_m);
-      const int n0 = n_tile * BN;
-      const int rows_valid = min(BN, a.nc - n0);
-      const float* wrow = a.wp + ((long long)group * a.nc + n0) * a.taps * a.kc;
-      for (int cb = 0; cb < a.cblocks && alive; ++cb) {
-        for (int tap = 0; tap < a.taps; ++tap, ++w_count) {
-          if (w_count % wgroups_active != wgroup) continue;
+  } else if (warp == EPI_WARPS + A_WARPS) {
+    // ------------------------------ weight stages ------------------------------
+    // One thread: each stage is a single bulk copy of a ready-made (split, swizzled) image.
+    if (lane == 0) {
+      uint32_t w_count = 0;
+      bool alive = true;
+      const bool pw = PROF_ON(true);
+      for (long long tile = blockIdx.x; tile < a.tiles_total && alive; tile += gridDim.x) {
+        const long long n_tile = tile % a.tiles_n;
+        const long long group = (tile / a.tiles_n) / a.tiles_m;
+        const float* img = a.wp + (group * a.tiles_n + n_tile) * a.cblocks * a.taps * (long long)(BN * 64);
+        for (int i = 0; i < a.cblocks * a.taps; ++i, ++w_count, img += BN * 64) {
           const uint32_t ws = w_count % a.w_stages;
-          // loads first (registers only), then wait for the stage, then split and store
-          constexpr int TASKS = BN * 8 / WT;  // (row, 16-byte chunk) pairs per thread
-          float4 v[TASKS];
-#pragma unroll
-          for (int j = 0; j < TASKS; ++j) {
-            const int i = t + j * WT, row = i >> 3, chunk = i & 7;
-            v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (row < rows_valid)
-              v[j] = __ldg(reinterpret_cast<const float4*>(wrow + ((long long)row * a.taps + tap) * a.kc + cb * KBLK + chunk * 4));
-          }
-          const bool pw = PROF_ON(threadIdx.x == (EPI_WARPS + A_WARPS) * 32);
           { PROF_T0(pw);
           if (!mbar_wait(smem_u32(&ctrl->w_empty[ws]), ((w_count / a.w_stages) & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_EMPTY)) { alive = false; break; }
           PROF_ADD(pw, 4); }
-          PROF_T0(pw);
-          const uint32_t b_hi = w_base + ws * w_stage_bytes, b_lo = b_hi + w_plane;
-#pragma unroll
-          for (int j = 0; j < TASKS; ++j) {
-            const int i = t + j * WT, row = i >> 3, chunk = i & 7;
-            float h[4], l[4];
-            split_tf32(v[j].x, h[0], l[0]);
-            split_tf32(v[j].y, h[1], l[1]);
-            split_tf32(v[j].z, h[2], l[2]);
-            split_tf32(v[j].w, h[3], l[3]);
-            const uint32_t o = sw128_offset(row, chunk * 4);
-            sts_f32x4(b_hi + o, h[0], h[1], h[2], h[3]);
-            sts_f32x4(b_lo + o, l[0], l[1], l[2], l[3]);
-          }
-          fence_proxy_async();
-          mbar_arrive(smem_u32(&ctrl->w_full[ws]));
-          PROF_ADD(pw, 5);
+          const uint32_t full = smem_u32(&ctrl->w_full[ws]);
+          mbar_expect_tx(full, w_stage_bytes);
+          bulk_g2s(w_base + ws * w_stage_bytes, img, w_stage_bytes, full);
         }
       }
+      // After an abort the MMA warp no longer consumes stages: wait (bounded) for the copies still
+      // in flight so that none lands in shared memory of a finished CTA.
+      if (!alive)
+        for (uint32_t j = w_count > (uint32_t)a.w_stages ? w_count - a.w_stages : 0; j < w_count; ++j)
+          mbar_wait(smem_u32(&ctrl->w_full[j % a.w_stages]), (j / a.w_stages) & 1, nullptr, a.status, STATUS_TIMEOUT_FULL);
     }
   } else if (warp >= EPI_WARPS) {
     // ------------------------------ strip producers ------------------------------
@@ -308,6 +279,12 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
     }
   } else {
     // ------------------------------ epilogue ------------------------------
+    // A warp reads the TMEM lane quarter (warp & 3); with 8 warps the 32-column chunks alternate
+    // between warps w and w + 4.  One warp per scheduler runs at the latency of its dependent
+    // instructions, so the per-element work is kept to a multiply-add and a store through a
+    // running pointer; everything uniform (bias present, ragged last tile) is decided per chunk.
+    const int quarter = warp & 3, half = warp >> 2;
+    constexpr int HALVES = EPI_WARPS / 4;
     uint32_t t_count = 0;
     for (long long tile = blockIdx.x; tile < a.tiles_total; tile += gridDim.x, ++t_count) {
       const int n_tile = (int)(tile % a.tiles_n);
@@ -317,12 +294,7 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
       const int cols_valid = min(BN, a.nc - n0);
       const uint32_t ab = t_count & 1;
       const bool pe = PROF_ON(threadIdx.x == 0);
-      { PROF_T0(pe);
-      if (!mbar_wait(smem_u32(&ctrl->acc_full[ab]), (t_count >> 1) & 1, abort_flag, a.status, STATUS_TIMEOUT_ACCUM)) break;
-      PROF_ADD(pe, 8); }
-      PROF_T0(pe);
-      tc_fence_after();
-      const long long q = m_tile * BLOCK_M + warp * 32 + lane;
+      const long long q = m_tile * BLOCK_M + quarter * 32 + lane;
       bool ok = q < a.q_total;
       long long obase = 0;
       if (ok) {
@@ -333,11 +305,18 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
         obase = a.out_rowmajor ? (((n * a.H + y) * a.W + x) * (long long)a.out_channels + (long long)group * a.nc + n0)
                                : (((n * a.out_channels + (long long)group * a.nc + n0) * a.H + y) * a.W + x);
       }
-      const long long plane = (long long)a.H * a.W;
-      const uint32_t tmem_acc = tmem_base + ab * ACC_COLS + ((uint32_t)(warp * 32) << 16);
+      const long long col_stride = a.out_rowmajor ? 1 : (long long)a.H * a.W;
+      { PROF_T0(pe);
+      if (!mbar_wait(smem_u32(&ctrl->acc_full[ab]), (t_count >> 1) & 1, abort_flag, a.status, STATUS_TIMEOUT_ACCUM)) break;
+      PROF_ADD(pe, 8); }
+      PROF_T0(pe);
+      tc_fence_after();
+      const uint32_t tmem_acc = tmem_base + ab * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
+      const int chunks = (cols_valid + 31) / 32;
+      bool released = false;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        if (c0 >= cols_valid) break;
+      for (int ch = half; ch < chunks; ch += HALVES) {
+        const int c0 = ch * 32;
         float v[32];
         tmem_ld32(tmem_acc + (uint32_t)c0, v);
         if (FUSE_HILO) {
@@ -346,30 +325,39 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] += v2[j];
         }
-        if (c0 + 32 >= cols_valid || c0 + 32 >= BN) {  // last read of this accumulator: hand it back early
+        if (ch + HALVES >= chunks) {  // this warp's last read of the accumulator: hand it back early
           tc_fence_before();
           mbar_arrive(smem_u32(&ctrl->acc_empty[ab]));
+          released = true;
+        }
+        const int nvalid = min(32, cols_valid - c0);
+        if (a.bias) {
+          float bv = 0.f;  // lane j holds the bias of column c0 + j
+          if (lane < nvalid) bv = a.beta * __ldg(a.bias + ((long long)group * a.nc + n0 + c0 + lane) * a.bias_stride);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = fmaf(a.alpha, v[j], __shfl_sync(0xffffffffu, bv, j));
+        } else if (a.alpha != 1.f) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] *= a.alpha;
         }
         if (ok) {
+          float* p = a.out + obase + c0 * col_stride;
+          if (a.out_rowmajor && a.out_vec4 && nvalid == 32) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int col = c0 + j;
-            float r = a.alpha * v[j];
-            if (a.bias && col < cols_valid) r += a.beta * __ldg(a.bias + ((long long)group * a.nc + n0 + col) * a.bias_stride);
-            v[j] = r;
-          }
-          if (a.out_rowmajor && a.out_vec4 && c0 + 32 <= cols_valid) {
-            float4* dst = reinterpret_cast<float4*>(a.out + obase + c0);
+            for (int j = 0; j < 8; ++j) reinterpret_cast<float4*>(p)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          } else if (nvalid == 32) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) dst[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            for (int j = 0; j < 32; ++j, p += col_stride) *p = v[j];
           } else {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const int col = c0 + j;
-              if (col < cols_valid) a.out[a.out_rowmajor ? obase + col : obase + (long long)col * plane] = v[j];
-            }
+            for (int j = 0; j < 32; ++j, p += col_stride)
+              if (j < nvalid) *p = v[j];
           }
         }
+      }
+      if (!released) {  // no chunk for this warp in a narrow last tile
+        tc_fence_before();
+        mbar_arrive(smem_u32(&ctrl->acc_empty[ab]));
       }
       PROF_ADD(pe, 9);
       if (pe) atomicAdd(a.prof + 10, 1ull);
@@ -383,20 +371,35 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
   }
 }
 
-// Reorder W[cout][cin/g][kh][kw] (any strides) into [g][row][tap][kchan] with the reduction channel
-// contiguous: forward row = co, kchan = ci; dInput row = ci, kchan = co.
-__global__ void __launch_bounds__(256) stage_weights_kernel(ConvGeom g, View4 w, int is_dx, float* __restrict__ out,
-                                                            long long total) {
+// Split W[cout][cin/g][kh][kw] (any strides) into TF32 hi/lo parts laid out as the shared-memory
+// images the MMA reads: image (group, n_tile, cb, tap) = [hi: bn rows x 128 B, SWIZZLE_128B][lo: same],
+// row = output column of the tile (forward: co, dInput: ci; zero beyond nc), 32 reduction channels
+// per row.  A weight stage of the main kernel is then one bulk copy.
+__global__ void __launch_bounds__(256) stage_weights_kernel(ConvGeom g, View4 w, int is_dx, int bn, int tiles_n,
+                                                            float* __restrict__ out, long long total) {
   const long long i = blockIdx.x * 256ll + threadIdx.x;
   if (i >= total) return;
   const int taps = g.kh * g.kw;
   const int kc = is_dx ? g.cog : g.cig, nc = is_dx ? g.cig : g.cog;
-  const int c = (int)(i % kc);
-  const int tap = (int)((i / kc) % taps);
-  const int r = (int)((i / ((long long)kc * taps)) % nc);
-  const int grp = (int)(i / ((long long)kc * taps * nc));
-  const int co = is_dx ? c : r, ci = is_dx ? r : c;
-  out[i] = w.ptr[((long long)grp * g.cog + co) * w.s0 + ci * w.s1 + (tap / g.kw) * w.s2 + (tap % g.kw) * w.s3];
+  const int cblocks = kc / KBLK;
+  const int k = (int)(i % KBLK);
+  const int row = (int)((i / KBLK) % bn);
+  const long long image = i / ((long long)KBLK * bn);
+  const int tap = (int)(image % taps);
+  const int cb = (int)((image / taps) % cblocks);
+  const int n_tile = (int)((image / ((long long)taps * cblocks)) % tiles_n);
+  const int grp = (int)(image / ((long long)taps * cblocks * tiles_n));
+  const int r = n_tile * bn + row, c = cb * KBLK + k;
+  float v = 0.f;
+  if (r < nc) {
+    const int co = is_dx ? c : r, ci = is_dx ? r : c;
+    v = w.ptr[((long long)grp * g.cog + co) * w.s0 + ci * w.s1 + (tap / g.kw) * w.s2 + (tap % g.kw) * w.s3];
+  }
+  float hi, lo;
+  split_tf32(v, hi, lo);
+  float* dst = out + image * (bn * 64ll) + sw128_offset(row, k) / 4;
+  dst[0] = hi;
+  dst[bn * 32] = lo;
 }
 
 struct StripPlan {
@@ -448,7 +451,19 @@ bool strip_supported(const ConvGeom& g, int phase) {
   if (phase != B200_PHASE_FORWARD && phase != B200_PHASE_DINPUT) return false;
   return tcs::plan_strip(g, phase == B200_PHASE_DINPUT).ok;
 }
-size_t strip_workspace(const ConvGeom& g) { return sizeof(float) * (size_t)g.cout * g.cig * g.kh * g.kw; }
+int strip_column_tile(const ConvGeom& g, bool is_dx) {
+  const tcs::StripPlan p = tcs::plan_strip(g, is_dx);
+  return p.ok ? p.bn : 0;
+}
+// Bytes of the weight stage images: hi and lo planes with the column count padded to the tile width.
+// The width depends on the image count, so take the largest over the widths the plan may pick.
+size_t strip_workspace(const ConvGeom& g, int phase) {
+  const bool is_dx = phase == B200_PHASE_DINPUT;
+  const size_t kc = is_dx ? g.cog : g.cig, nc = is_dx ? g.cig : g.cog;
+  size_t cols = 0;
+  for (size_t bn : {256, 128, 64}) cols = std::max(cols, (nc + bn - 1) / bn * bn);
+  return 2 * sizeof(float) * (size_t)g.groups * cols * kc * g.kh * g.kw;
+}
 
 template <int BN>
 static int launch_strip(const tcs::StripArgs& a, int grid, int smem, cudaStream_t st) {
@@ -463,21 +478,24 @@ static int launch_strip(const tcs::StripArgs& a, int grid, int smem, cudaStream_
 }
 
 int strip_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* bias, long long bias_stride, float* out,
-               void* ws, size_t ws_bytes, cudaStream_t st, bool rowmajor, float alpha, float beta, const float* staged_weights) {
+               void* ws, size_t ws_bytes, cudaStream_t st, bool rowmajor, float alpha, float beta, const float* staged_images) {
   using namespace tcs;
   const StripPlan plan = plan_strip(g, is_dx);
   if (!plan.ok) return fail(B200_EUNSUPPORTED, "strip kernel does not take this geometry");
-  const size_t wcount = (size_t)g.cout * g.cig * g.kh * g.kw;
-  const float* wp = staged_weights;  // already [groups][nc][taps][kc]
+  const int kc = is_dx ? g.cog : g.cig, nc = is_dx ? g.cig : g.cog;
+  const int tiles_n = (nc + plan.bn - 1) / plan.bn;
+  const long long wcount = (long long)g.groups * tiles_n * plan.bn * kc * g.kh * g.kw;  // per plane
+  const float* wp = staged_images;
   if (!wp) {
-    if (!ws || ws_bytes < sizeof(float) * wcount || (reinterpret_cast<uintptr_t>(ws) & 15))
+    if (!ws || ws_bytes < 2 * sizeof(float) * (size_t)wcount || (reinterpret_cast<uintptr_t>(ws) & 15))
       return fail(B200_EWORKSPACE, "tcgen05 convolution needs a 16-byte aligned workspace of %zu bytes (got %zu)",
-                  sizeof(float) * wcount, ws_bytes);
-    stage_weights_kernel<<<(unsigned)div_up64((long long)wcount, 256), 256, 0, st>>>(g, w, is_dx ? 1 : 0, (float*)ws, (long long)wcount);
+                  2 * sizeof(float) * (size_t)wcount, ws_bytes);
+    stage_weights_kernel<<<(unsigned)div_up64(wcount, 256), 256, 0, st>>>(g, w, is_dx ? 1 : 0, plan.bn, tiles_n, (float*)ws, wcount);
     count_launch();
     if (int rc = launch_check("stage_weights_kernel")) return rc;
     wp = (const float*)ws;
   }
+  if (reinterpret_cast<uintptr_t>(wp) & 15) return fail(B200_EINVAL, "weight stage images must be 16-byte aligned");
   StripArgs a{};
   a.g = g; a.act = act; a.wp = wp; a.bias = is_dx ? nullptr : bias; a.bias_stride = bias_stride; a.out = out;
   a.H = g.h; a.W = g.w; a.pr = g.ph; a.pc = g.pw;
@@ -537,7 +555,7 @@ int tc_gemm(long long M, long long N, long long K, const float* A, long long sa0
   const View4 act{A, 0, sa1, 0, sa0};   // [n=1][c=k][h=1][w=m]
   const View4 wv{B, sb1, sb0, 0, 0};    // [co=n][ci=k][1][1]
   void* ws = nullptr;
-  const size_t ws_bytes = sizeof(float) * (size_t)K * (size_t)N;
+  const size_t ws_bytes = strip_workspace(g, B200_PHASE_FORWARD);
   if (int rc = b200_malloc(&ws, ws_bytes, st)) return rc;
   if (!bias || beta == 0.f) { bias = nullptr; beta = 0.f; }
   const int rc = strip_conv(g, false, act, wv, bias, 1, C, ws, ws_bytes, st, true, alpha, beta);

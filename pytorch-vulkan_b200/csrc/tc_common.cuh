@@ -27,6 +27,12 @@ __device__ __forceinline__ unsigned long long global_ns() {
 }
 
 // ---- mbarrier ----------------------------------------------------------------------------
+#ifndef B200_WAIT_SLEEP_NS
+#define B200_WAIT_SLEEP_NS 0
+#endif
+#ifndef B200_WAIT_HINT_NS
+#define B200_WAIT_HINT_NS 1000
+#endif
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
@@ -47,28 +53,50 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// The same with a suspend-time hint: the hardware may park the thread for up to `ns` nanoseconds
+// and wakes it when the phase completes.  Waiting warps then stay out of the shared-memory pipe,
+// which the working roles of the CTA (epilogue stores, producer stores) need.
+__device__ __forceinline__ bool mbar_try_hint(uint32_t bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
 // Wait with a wall-clock bound.  On expiry the status word and the CTA's abort flag are set and
 // false is returned; every role then falls through to the common teardown (TMEM is freed, the
 // kernel returns, the context stays usable).  Other waiters notice the abort flag and leave too.
+constexpr uint32_t WAIT_HINT_NS = B200_WAIT_HINT_NS;
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // 2 s: no legitimate wait is near this
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
                                           int code) {
   if (mbar_try(bar, parity)) return true;
   unsigned long long t0 = 0;
   uint32_t spins = 0;
-  while (!mbar_try(bar, parity)) {
+  while (!mbar_try_hint(bar, parity, WAIT_HINT_NS)) {
+    if (B200_WAIT_SLEEP_NS) __nanosleep(B200_WAIT_SLEEP_NS);
     if (((++spins) & 63u) == 0) {
-      if (*abort_flag) return false;
+      if (abort_flag && *abort_flag) return false;
       const unsigned long long now = global_ns();
       if (t0 == 0) t0 = now;
       else if (now - t0 > WAIT_LIMIT_NS) {
         atomicCAS(status, 0, (code << 24) | (int)(blockIdx.x & 0xFFFFFF));
-        *abort_flag = 1;
+        if (abort_flag) *abort_flag = 1;
         return false;
       }
     }
   }
   return true;
+}
+// Bulk copy global -> shared memory of this CTA; completion is counted in bytes on `bar`
+// (pair it with mbar_expect_tx).  Both addresses 16-byte aligned, size a multiple of 16.
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 __device__ __forceinline__ void fence_barrier_init() {
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");

@@ -17,6 +17,7 @@
 // Replaces the reference's F(2x2,3x3) path: csrc/ops/convolution.cpp:257-335 (eligibility, three
 // dispatches) and csrc/shaders/conv2d_winograd_{weights,input,gemm_output}.comp.
 #include "common.cuh"
+#include "tc_common.cuh"
 
 #include <algorithm>
 
@@ -55,8 +56,11 @@ struct Tiling {
 };
 
 // U[p][co][ci] = (G g G^T)[p].  transposed: g'(ci -> row, co -> column) = g rotated by 180 degrees.
+// U is written directly as the strip kernel's weight stage images for the grouped 1x1 product
+// (group = p*groups + grp; TF32 hi and lo planes of bn rows x 32 channels, SWIZZLE_128B); rows that
+// pad the last column tile are zeroed by the caller.
 __global__ void __launch_bounds__(256) filter_transform_kernel(ConvGeom g, View4 w, int transposed, float* __restrict__ U,
-                                                               long long pairs) {
+                                                               long long pairs, int bn, int tiles_n) {
   const long long i = blockIdx.x * 256ll + threadIdx.x;
   if (i >= pairs) return;
   const int kc = transposed ? g.cog : g.cig, nc = transposed ? g.cig : g.cog;
@@ -82,13 +86,21 @@ __global__ void __launch_bounds__(256) filter_transform_kernel(ConvGeom g, View4
 #pragma unroll
     for (int y = 0; y < 6; ++y) t[y][x] = o[y];
   }
-  const long long plane = pairs;  // rows(all groups) * kc
+  const int cblocks = kc / 32;
+  const long long within = ((long long)(r / bn) * cblocks + k / 32) * (bn * 64ll) + tc::sw128_offset(r % bn, k % 32) / 4;
+  const long long per_group = (long long)tiles_n * cblocks * (bn * 64ll);
 #pragma unroll
   for (int y = 0; y < 6; ++y) {
     float o[6];
     g6(t[y], o);
 #pragma unroll
-    for (int x = 0; x < 6; ++x) U[(long long)(y * 6 + x) * plane + i] = o[x];
+    for (int x = 0; x < 6; ++x) {
+      float hi, lo;
+      tc::split_tf32(o[x], hi, lo);
+      float* dst = U + ((long long)(y * 6 + x) * g.groups + grp) * per_group + within;
+      dst[0] = hi;
+      dst[bn * 32] = lo;
+    }
   }
 }
 
@@ -236,7 +248,10 @@ static Plan make_plan(const ConvGeom& g, bool is_dx) {
   if (p.kc % 32 != 0 || p.nc < 16 || p.nc % 4 != 0) return p;
   const int oh = is_dx ? g.h : g.oh, ow = is_dx ? g.w : g.ow;
   p.tiles = (long long)g.n * ((oh + 3) / 4) * ((ow + 3) / 4);
-  p.u_bytes = sizeof(float) * 36ull * g.cout * g.cig;
+  // the transformed filter is kept as the strip kernel's weight stage images
+  ConvGeom gg{};
+  gg.groups = 36 * g.groups; gg.cig = p.kc; gg.cog = p.nc; gg.kh = gg.kw = 1;
+  p.u_bytes = (strip_workspace(gg, B200_PHASE_FORWARD) + 255) / 256 * 256;
   p.per_tile = sizeof(float) * 36ull * ((size_t)p.kc + p.nc) * g.groups;
   if (36ll * g.groups > 65535) return p;
   p.ok = true;
@@ -279,8 +294,8 @@ int winograd_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float
   tl.tiles = p.tiles;
   const int ctot_in = p.kc * g.groups, ctot_out = p.nc * g.groups;
   float* U = (float*)ws;
-  const size_t u_floats = (p.u_bytes / sizeof(float) + 63) / 64 * 64;
-  long long chunk = (long long)((ws_bytes - u_floats * sizeof(float)) / p.per_tile);
+  const size_t u_floats = p.u_bytes / sizeof(float);
+  long long chunk = (long long)((ws_bytes - p.u_bytes) / p.per_tile);
   chunk = std::min(chunk, p.tiles);
   if (chunk < p.tiles) chunk = chunk / 128 * 128;
   if (chunk <= 0) return fail(B200_EWORKSPACE, "Winograd convolution exceeds the workspace budget");
@@ -288,9 +303,7 @@ int winograd_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float
   float* M = V + (size_t)chunk * 36 * ctot_in;
 
   const long long pairs = (long long)g.cout * g.cig;
-  filter_transform_kernel<<<(unsigned)div_up64(pairs, 256), 256, 0, st>>>(g, w, is_dx ? 1 : 0, U, pairs);
-  count_launch();
-  if (int rc = launch_check("filter_transform_kernel")) return rc;
+  int staged_bn = 0;  // column tile the images in U were written for
 
   // the 36 plane products as one grouped 1x1 convolution: group index = plane * groups + group
   ConvGeom gg{};
@@ -304,8 +317,18 @@ int winograd_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float
     count_launch();
     if (int rc = launch_check("input_transform_kernel")) return rc;
     gg.w = (int)cnt; gg.ow = (int)cnt;
+    const int bn = strip_column_tile(gg, false);  // depends on the number of tiles in the chunk
+    if (bn <= 0) return fail(B200_EUNSUPPORTED, "Winograd plane product does not fit the strip kernel");
+    if (bn != staged_bn) {
+      const int tiles_n = (p.nc + bn - 1) / bn;
+      if (p.nc % bn != 0) B200_CUDA(cudaMemsetAsync(U, 0, p.u_bytes, st));
+      filter_transform_kernel<<<(unsigned)div_up64(pairs, 256), 256, 0, st>>>(g, w, is_dx ? 1 : 0, U, pairs, bn, tiles_n);
+      count_launch();
+      if (int rc = launch_check("filter_transform_kernel")) return rc;
+      staged_bn = bn;
+    }
     const View4 vact{V, 0, 1, 0, 36ll * ctot_in};
-    if (int rc = strip_conv(gg, false, vact, View4{U, 0, 0, 0, 0}, nullptr, 0, M, nullptr, 0, st, true, 1.f, 0.f, U)) return rc;
+    if (int rc = strip_conv(gg, false, vact, View4{}, nullptr, 0, M, nullptr, 0, st, true, 1.f, 0.f, U)) return rc;
     output_transform_kernel<<<dim3((unsigned)div_up64(cnt, 8), (unsigned)div_up64(ctot_out, 32)), 256, 0, st>>>(
         tl, M, ctot_out, is_dx ? nullptr : bias, bias_stride, out, t0, t1);
     count_launch();

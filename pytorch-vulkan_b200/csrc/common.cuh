@@ -53,6 +53,27 @@ inline ConvGeom to_geom(const b200_conv_params& p) {
 
 static inline int64_t div_up64(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
+// Division of 0 <= n < 2^31 by a divisor fixed at launch time as one multiply-high and a shift:
+// with s = ceil(log2 d) and m = ceil(2^(31+s) / d), floor(n / d) = (n * m) >> (31 + s) because the
+// excess m*d - 2^(31+s) is below d <= 2^s and n is below 2^31.  Kernels use it to turn a padded
+// pixel index into (image, row, column) without the long division sequence.
+struct FastDiv {
+  uint32_t d = 1, mul = 0, shr = 0;
+  FastDiv() = default;
+  explicit FastDiv(uint32_t divisor) : d(divisor) {
+    if (d > 1) {
+      uint32_t s = 0;
+      while ((1ull << s) < d) ++s;
+      mul = (uint32_t)(((1ull << (31 + s)) + d - 1) / d);
+      shr = s - 1;  // after taking the high 32 bits of the product
+    }
+  }
+#ifdef __CUDACC__
+  __device__ __forceinline__ uint32_t div(uint32_t n) const { return d == 1 ? n : (__umulhi(n, mul) >> shr); }
+#endif
+  uint32_t host_div(uint32_t n) const { return d == 1 ? n : (uint32_t)(((uint64_t)n * mul) >> 32) >> shr; }
+};
+
 // ---- kernel families (each returns a B200_* code) -------------------------------------------
 // CUDA-core paths (conv_simt.cu)
 int simt_direct(const ConvGeom& g, int phase, View4 a, View4 b, const float* bias, long long bias_stride,

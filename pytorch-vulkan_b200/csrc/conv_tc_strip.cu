@@ -32,6 +32,7 @@
 #include <algorithm>
 #include <cstdio>
 #include <cstdlib>
+#include <cstring>
 
 namespace b200 {
 namespace tcs {
@@ -41,29 +42,49 @@ constexpr int BLOCK_M = 128, KBLK = 32;
 constexpr int EPI_WARPS = 4, A_WARPS = 8, W_WARPS = 1;
 constexpr int MMA_WARP = EPI_WARPS + A_WARPS + W_WARPS;
 constexpr int THREADS = (MMA_WARP + 1) * 32;
-constexpr int MAX_TAPS = 64;
+constexpr int MAX_TAPS = 64, MAX_PHASES = 16;
 constexpr int MAX_STAGES = 4;
 constexpr int SMEM_LIMIT = 232448 - 2048;  // 227 KB per CTA minus the control block and alignment slack
 
+// Filter taps grouped by the input phase they read.  With stride s the input row of output row oy
+// and tap ky is s*oy + ky*d - pad = s*(oy + dr) + a with a = (ky*d - pad) mod s: tap ky reads the
+// sub-image made of rows = a (mod s) ("phase a") at the whole-pixel offset dr.  Channel blocks are
+// therefore enumerated per phase, and each phase runs only its own taps (stride 1: one phase, all taps).
+struct TapTable {
+  int n_phase = 0, taps_total = 0;
+  unsigned char a[MAX_PHASES], b[MAX_PHASES];  // row / column phase of active phase i
+  unsigned char start[MAX_PHASES + 1];         // taps of phase i: [start[i], start[i+1])
+  unsigned char ky[MAX_TAPS], kx[MAX_TAPS];    // filter position of tap t
+  int shift[MAX_TAPS];                         // strip row offset of tap t
+};
+
 struct StripArgs {
   ConvGeom g;
-  View4 act;              // forward: x.  dInput: dy (same spatial size as the output)
-  const float* wp;        // weight stage images [groups][tiles_n][cblocks][taps] of BN*256 bytes (stage_weights_kernel)
+  View4 act;              // forward: x.  dInput: dy
+  const float* wp;        // weight stage images [groups][tiles_n][phase][cblock][tap of phase] of BN*256 bytes
   const float* bias;
   long long bias_stride;
-  float* out;             // contiguous NCHW [n][out_channels][H][W]
-  int H, W, pr, pc;       // image size and padding rows/cols of the padded pixel space
+  float* out;             // contiguous NCHW [n][out_channels][out_h][out_w] (or row-major, see below)
+  int H, W, pr, pc;       // pixel grid shared by the strip and the accumulator rows, and its zero padding
+  int act_h, act_w;       // extent of the activation tensor; grid pixel (r, c) of phase (a, b) reads (r*sph + a, c*spw + b)
+  int out_h, out_w;       // extent of the output tensor (grid pixels beyond it are discarded)
+  int sph, spw;
   int kc, nc, out_channels;
-  int cblocks, taps, tiles_n;
-  long long q_total, tiles_m, tiles_total;
-  int halo, strip_rows;   // strip_rows is a multiple of 8
+  int cb_per_phase;       // kc / 32
+  int cblocks;            // strips per tile: n_phase * cb_per_phase
+  int images_per_tile;    // weight stages per tile: cb_per_phase * taps_total
+  int tiles_n;
+  int q_total;            // grid pixels incl. padding (below 2^31 - 2^20)
+  FastDiv img_div, row_div;
+  long long tiles_m, tiles_total;
+  int halo, strip_rows;   // rows staged before the tile's first pixel; strip_rows is a multiple of 8
   int a_stages, w_stages;
-  int is_dx;
   int out_rowmajor;       // 0: NCHW planes.  1: [pixel][channel] rows (channels-last / GEMM C)
   int out_vec4;           // row-major rows may be written with 16-byte stores
   float alpha, beta;      // out = alpha * acc + beta * bias
   int* status;
   unsigned long long* prof;  // optional cycle counters of CTA 0 (B200_STRIP_PROFILE=1), else null
+  TapTable tt;
 };
 
 struct Ctrl {  // lives behind the operand stages in shared memory
@@ -71,6 +92,7 @@ struct Ctrl {  // lives behind the operand stages in shared memory
   uint32_t tmem_base;
   int abort_flag;
   int shift[MAX_TAPS];
+  unsigned char ph_a[MAX_PHASES], ph_b[MAX_PHASES], tap_start[MAX_PHASES + 1];
 };
 
 // Cycle accounting for one thread of each role in CTA 0 (diagnostics only).
@@ -114,11 +136,10 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
     ctrl->abort_flag = 0;
     fence_barrier_init();
   }
-  if (threadIdx.x < a.taps) {
-    const int ky = threadIdx.x / g.kw, kx = threadIdx.x - ky * g.kw;
-    const int s = (ky * g.dh - g.ph) * (a.W + a.pc) + (kx * g.dw - g.pw);
-    ctrl->shift[threadIdx.x] = a.is_dx ? -s : s;
-  }
+  // the tap table moves to shared memory: kernel parameters are not indexed dynamically
+  if (threadIdx.x < MAX_TAPS) ctrl->shift[threadIdx.x] = a.tt.shift[threadIdx.x];
+  if (threadIdx.x < MAX_PHASES) { ctrl->ph_a[threadIdx.x] = a.tt.a[threadIdx.x]; ctrl->ph_b[threadIdx.x] = a.tt.b[threadIdx.x]; }
+  if (threadIdx.x <= MAX_PHASES) ctrl->tap_start[threadIdx.x] = a.tt.start[threadIdx.x];
   if (warp == MMA_WARP) tmem_alloc(smem_u32(&ctrl->tmem_base), TMEM_COLS);
   tc_fence_before();
   __syncthreads();
@@ -126,7 +147,7 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&ctrl->tmem_base);
 
   const int row_pitch = a.W + a.pc;
-  const long long img_pitch = (long long)(a.H + a.pr) * row_pitch;
+  const int img_pitch = (a.H + a.pr) * row_pitch;
 
   if (warp == MMA_WARP) {
     // ------------------------------ MMA issuer ------------------------------
@@ -141,13 +162,16 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
       if (!mbar_wait(smem_u32(&ctrl->acc_empty[ab]), ((t_count >> 1) & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_ACCUM)) break;
       PROF_ADD(pm, 0); }
       const uint32_t tmem_acc = tmem_base + ab * ACC_COLS;
+      uint32_t accumulate = 0;  // the tile's first MMA overwrites the accumulator
       for (int cb = 0; cb < a.cblocks && alive; ++cb, ++a_count) {
         const uint32_t as = a_count % a.a_stages;
         { PROF_T0(pm);
         if (!mbar_wait(smem_u32(&ctrl->a_full[as]), (a_count / a.a_stages) & 1, abort_flag, a.status, STATUS_TIMEOUT_FULL)) { alive = false; break; }
         PROF_ADD(pm, 1); }
         const uint32_t strip = tiles_base + as * a_stage_bytes;
-        for (int tap = 0; tap < a.taps; ++tap, ++w_count) {
+        const int phase = cb / a.cb_per_phase;
+        const int tap_end = ctrl->tap_start[phase + 1];
+        for (int tap = ctrl->tap_start[phase]; tap < tap_end; ++tap, ++w_count) {
           const uint32_t ws = w_count % a.w_stages;
           { PROF_T0(pm);
           if (!mbar_wait(smem_u32(&ctrl->w_full[ws]), (w_count / a.w_stages) & 1, abort_flag, a.status, STATUS_TIMEOUT_FULL)) { alive = false; break; }
@@ -159,7 +183,8 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
             const uint32_t b_hi = w_base + ws * w_stage_bytes, b_lo = b_hi + w_plane;
             const uint64_t da_hi = make_kmajor_sw128_desc(a_hi), da_lo = make_kmajor_sw128_desc(a_lo);
             const uint64_t db_hi = make_kmajor_sw128_desc(b_hi), db_lo = make_kmajor_sw128_desc(b_lo);
-            const uint32_t first = (cb | tap) == 0 ? 0u : 1u;
+            const uint32_t first = accumulate;
+            accumulate = 1;
             if (FUSE_HILO) {
 #pragma unroll
               for (int kk = 0; kk < 4; ++kk) umma_tf32(tmem_acc, da_hi + 2 * kk, db_hi + 2 * kk, idesc_wide, first | (uint32_t)(kk != 0));
@@ -194,8 +219,8 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
       for (long long tile = blockIdx.x; tile < a.tiles_total && alive; tile += gridDim.x) {
         const long long n_tile = tile % a.tiles_n;
         const long long group = (tile / a.tiles_n) / a.tiles_m;
-        const float* img = a.wp + (group * a.tiles_n + n_tile) * a.cblocks * a.taps * (long long)(BN * 64);
-        for (int i = 0; i < a.cblocks * a.taps; ++i, ++w_count, img += BN * 64) {
+        const float* img = a.wp + (group * a.tiles_n + n_tile) * a.images_per_tile * (long long)(BN * 64);
+        for (int i = 0; i < a.images_per_tile; ++i, ++w_count, img += BN * 64) {
           const uint32_t ws = w_count % a.w_stages;
           { PROF_T0(pw);
           if (!mbar_wait(smem_u32(&ctrl->w_empty[ws]), ((w_count / a.w_stages) & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_EMPTY)) { alive = false; break; }
@@ -235,15 +260,17 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
       const bool pa = PROF_ON(threadIdx.x == EPI_WARPS * 32);
       PROF_T0(pa);
       const int r = chunk * 32 + lane;
-      const long long q = m_tile * BLOCK_M - a.halo + r;
+      const int q = (int)m_tile * BLOCK_M - a.halo + r;
       bool ok = r < a.strip_rows && q >= 0 && q < a.q_total;
       const float* src = a.act.ptr;
       if (ok) {
-        const long long n = q / img_pitch;
-        const int rem = (int)(q - n * img_pitch);
-        const int y = rem / row_pitch, x = rem - y * row_pitch;
-        ok = y < a.H && x < a.W;
-        src += n * a.act.s0 + ((long long)group * a.kc + cb * KBLK) * a.act.s1 + (long long)y * a.act.s2 + (long long)x * a.act.s3;
+        const int n = (int)a.img_div.div((uint32_t)q);
+        const int rem = q - n * img_pitch;
+        const int y = (int)a.row_div.div((uint32_t)rem), x = rem - y * row_pitch;
+        const int phase = cb / a.cb_per_phase, cbl = cb - phase * a.cb_per_phase;
+        const int iy = y * a.sph + ctrl->ph_a[phase], ix = x * a.spw + ctrl->ph_b[phase];
+        ok = y < a.H && x < a.W && iy < a.act_h && ix < a.act_w;
+        src += n * a.act.s0 + ((long long)group * a.kc + cbl * KBLK) * a.act.s1 + (long long)iy * a.act.s2 + (long long)ix * a.act.s3;
       }
       float v[KBLK];
       if (ok && vec_ok) {
@@ -267,7 +294,7 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
         for (int c = 0; c < 8; ++c) {
           float h[4], l[4];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) split_tf32(v[c * 4 + j], h[j], l[j]);
+          for (int j = 0; j < 4; ++j) split_tf32_fast(v[c * 4 + j], h[j], l[j]);
           const uint32_t o = sw128_offset(r, c * 4);
           sts_f32x4(p_hi + o, h[0], h[1], h[2], h[3]);
           sts_f32x4(p_lo + o, l[0], l[1], l[2], l[3]);
@@ -294,18 +321,18 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
       const int cols_valid = min(BN, a.nc - n0);
       const uint32_t ab = t_count & 1;
       const bool pe = PROF_ON(threadIdx.x == 0);
-      const long long q = m_tile * BLOCK_M + quarter * 32 + lane;
+      const int q = (int)m_tile * BLOCK_M + quarter * 32 + lane;
       bool ok = q < a.q_total;
       long long obase = 0;
       if (ok) {
-        const long long n = q / img_pitch;
-        const int rem = (int)(q - n * img_pitch);
-        const int y = rem / row_pitch, x = rem - y * row_pitch;
-        ok = y < a.H && x < a.W;
-        obase = a.out_rowmajor ? (((n * a.H + y) * a.W + x) * (long long)a.out_channels + (long long)group * a.nc + n0)
-                               : (((n * a.out_channels + (long long)group * a.nc + n0) * a.H + y) * a.W + x);
+        const long long n = a.img_div.div((uint32_t)q);
+        const int rem = q - (int)n * img_pitch;
+        const int y = (int)a.row_div.div((uint32_t)rem), x = rem - y * row_pitch;
+        ok = y < a.out_h && x < a.out_w;
+        obase = a.out_rowmajor ? (((n * a.out_h + y) * a.out_w + x) * (long long)a.out_channels + (long long)group * a.nc + n0)
+                               : (((n * a.out_channels + (long long)group * a.nc + n0) * a.out_h + y) * a.out_w + x);
       }
-      const long long col_stride = a.out_rowmajor ? 1 : (long long)a.H * a.W;
+      const long long col_stride = a.out_rowmajor ? 1 : (long long)a.out_h * a.out_w;
       { PROF_T0(pe);
       if (!mbar_wait(smem_u32(&ctrl->acc_full[ab]), (t_count >> 1) & 1, abort_flag, a.status, STATUS_TIMEOUT_ACCUM)) break;
       PROF_ADD(pe, 8); }
@@ -372,28 +399,31 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
 }
 
 // Split W[cout][cin/g][kh][kw] (any strides) into TF32 hi/lo parts laid out as the shared-memory
-// images the MMA reads: image (group, n_tile, cb, tap) = [hi: bn rows x 128 B, SWIZZLE_128B][lo: same],
-// row = output column of the tile (forward: co, dInput: ci; zero beyond nc), 32 reduction channels
-// per row.  A weight stage of the main kernel is then one bulk copy.
+// images the MMA reads: image = [hi: bn rows x 128 B, SWIZZLE_128B][lo: same], row = output column of
+// the tile (forward: co, dInput: ci; zero beyond nc), 32 reduction channels per row.  Images are
+// ordered as the main loop consumes them: [group][n_tile][phase][channel block][tap of the phase],
+// so a weight stage of the main kernel is one bulk copy from a running pointer.
 __global__ void __launch_bounds__(256) stage_weights_kernel(ConvGeom g, View4 w, int is_dx, int bn, int tiles_n,
-                                                            float* __restrict__ out, long long total) {
+                                                            TapTable tt, float* __restrict__ out, long long total) {
   const long long i = blockIdx.x * 256ll + threadIdx.x;
   if (i >= total) return;
-  const int taps = g.kh * g.kw;
   const int kc = is_dx ? g.cog : g.cig, nc = is_dx ? g.cig : g.cog;
-  const int cblocks = kc / KBLK;
+  const int cpp = kc / KBLK, per_tile = cpp * tt.taps_total;
   const int k = (int)(i % KBLK);
   const int row = (int)((i / KBLK) % bn);
   const long long image = i / ((long long)KBLK * bn);
-  const int tap = (int)(image % taps);
-  const int cb = (int)((image / taps) % cblocks);
-  const int n_tile = (int)((image / ((long long)taps * cblocks)) % tiles_n);
-  const int grp = (int)(image / ((long long)taps * cblocks * tiles_n));
-  const int r = n_tile * bn + row, c = cb * KBLK + k;
+  const int local = (int)(image % per_tile);
+  const int n_tile = (int)((image / per_tile) % tiles_n);
+  const int grp = (int)(image / ((long long)per_tile * tiles_n));
+  int phase = 0;
+  while (phase + 1 < tt.n_phase && local >= cpp * tt.start[phase + 1]) ++phase;
+  const int rel = local - cpp * tt.start[phase], ntap = tt.start[phase + 1] - tt.start[phase];
+  const int cbl = rel / ntap, tap = tt.start[phase] + rel % ntap;
+  const int r = n_tile * bn + row, c = cbl * KBLK + k;
   float v = 0.f;
   if (r < nc) {
     const int co = is_dx ? c : r, ci = is_dx ? r : c;
-    v = w.ptr[((long long)grp * g.cog + co) * w.s0 + ci * w.s1 + (tap / g.kw) * w.s2 + (tap % g.kw) * w.s3];
+    v = w.ptr[((long long)grp * g.cog + co) * w.s0 + ci * w.s1 + tt.ky[tap] * w.s2 + tt.kx[tap] * w.s3];
   }
   float hi, lo;
   split_tf32(v, hi, lo);
@@ -402,24 +432,71 @@ __global__ void __launch_bounds__(256) stage_weights_kernel(ConvGeom g, View4 w,
   dst[bn * 32] = lo;
 }
 
+static inline int floor_div(int a, int b) { return a >= 0 ? a / b : -((-a + b - 1) / b); }
+
 struct StripPlan {
   bool ok = false;
   int bn = 0, a_stages = 0, w_stages = 0, strip_rows = 0, halo = 0, smem = 0;
+  int gh = 0, gw = 0, pr = 0, pc = 0;  // pixel grid and its padding
+  int act_h = 0, act_w = 0, out_h = 0, out_w = 0, sph = 1, spw = 1;
+  TapTable tt;
 };
 
+// Forward takes any stride / padding / dilation; dInput stride 1 with any padding / dilation.  Both
+// need the reduction channels in blocks of 32 and at least 16 output columns.
 static StripPlan plan_strip(const ConvGeom& g, bool is_dx) {
   StripPlan p;
   const int kc = is_dx ? g.cog : g.cig, nc = is_dx ? g.cig : g.cog;
-  if (g.sh != 1 || g.sw != 1 || g.oh != g.h || g.ow != g.w) return p;
-  if (2 * g.ph != g.dh * (g.kh - 1) || 2 * g.pw != g.dw * (g.kw - 1)) return p;
   if (kc % KBLK != 0 || nc < 16 || g.kh * g.kw > MAX_TAPS) return p;
-  p.halo = g.ph * (g.w + g.pw) + g.pw;
-  p.strip_rows = (BLOCK_M + 2 * p.halo + 7) / 8 * 8;
+  if (is_dx && (g.sh != 1 || g.sw != 1)) return p;
+  if (g.sh * g.sw > MAX_PHASES || g.sh > 255 || g.sw > 255) return p;
+  p.sph = g.sh; p.spw = g.sw;
+  p.act_h = is_dx ? g.oh : g.h; p.act_w = is_dx ? g.ow : g.w;
+  p.out_h = is_dx ? g.h : g.oh; p.out_w = is_dx ? g.w : g.ow;
+  // the grid covers the output and every phase sub-image of the activations
+  p.gh = std::max(p.out_h, (p.act_h + p.sph - 1) / p.sph);
+  p.gw = std::max(p.out_w, (p.act_w + p.spw - 1) / p.spw);
+  // taps -> (phase, whole-pixel offset); forward reads x at s*o - pad + k*d, dInput reads dy at i + pad - k*d
+  struct Tap { int phase, dr, dc, ky, kx; };
+  Tap taps[MAX_TAPS];
+  int ntaps = 0, dr_lo = 0, dr_hi = 0, dc_lo = 0, dc_hi = 0;
+  for (int ky = 0; ky < g.kh; ++ky)
+    for (int kx = 0; kx < g.kw; ++kx) {
+      const int oy = is_dx ? g.ph - ky * g.dh : ky * g.dh - g.ph, ox = is_dx ? g.pw - kx * g.dw : kx * g.dw - g.pw;
+      const int dr = floor_div(oy, p.sph), dc = floor_div(ox, p.spw);
+      taps[ntaps++] = Tap{(oy - dr * p.sph) * p.spw + (ox - dc * p.spw), dr, dc, ky, kx};
+      dr_lo = std::min(dr_lo, dr); dr_hi = std::max(dr_hi, dr);
+      dc_lo = std::min(dc_lo, dc); dc_hi = std::max(dc_hi, dc);
+    }
+  p.pr = std::max(-dr_lo, dr_hi);
+  p.pc = std::max(-dc_lo, dc_hi);
+  if ((long long)g.n * (p.gh + p.pr) * (p.gw + p.pc) > 2147483647ll - (1 << 20)) return p;  // 32-bit pixel indices
+  const int row_pitch = p.gw + p.pc;
+  TapTable& tt = p.tt;
+  memset(&tt, 0, sizeof tt);
+  int lo = 0, hi = 0;
+  for (int phase = 0; phase < p.sph * p.spw; ++phase) {
+    int count = 0;
+    for (int t = 0; t < ntaps; ++t)
+      if (taps[t].phase == phase) {
+        const int i = tt.taps_total++;
+        tt.ky[i] = (unsigned char)taps[t].ky; tt.kx[i] = (unsigned char)taps[t].kx;
+        tt.shift[i] = taps[t].dr * row_pitch + taps[t].dc;
+        lo = std::min(lo, tt.shift[i]); hi = std::max(hi, tt.shift[i]);
+        ++count;
+      }
+    if (count == 0) continue;  // no tap reads this phase: its channel blocks are never staged
+    tt.a[tt.n_phase] = (unsigned char)(phase / p.spw); tt.b[tt.n_phase] = (unsigned char)(phase % p.spw);
+    tt.start[tt.n_phase + 1] = (unsigned char)tt.taps_total;
+    ++tt.n_phase;
+  }
+  p.halo = -lo;
+  p.strip_rows = (BLOCK_M + hi - lo + 7) / 8 * 8;
   const int a_stage = p.strip_rows * 256;
   // Column tile: the widest tile makes the best use of shared-memory bandwidth per MMA, but a small
   // image gives few 128-pixel row tiles; pick the width with the lowest modelled time
   // waves(tiles / SMs) * width / efficiency(width).
-  const long long tiles_m = div_up64((long long)g.n * (g.h + g.ph) * (g.w + g.pw), BLOCK_M);
+  const long long tiles_m = div_up64((long long)g.n * (p.gh + p.pr) * (p.gw + p.pc), BLOCK_M);
   double best_cost = 0.0;
   for (int bn : {256, 128, 64}) {
     if (bn > 64 && nc <= bn / 2) continue;  // do not pad the column tile by more than 2x
@@ -490,7 +567,7 @@ int strip_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* b
     if (!ws || ws_bytes < 2 * sizeof(float) * (size_t)wcount || (reinterpret_cast<uintptr_t>(ws) & 15))
       return fail(B200_EWORKSPACE, "tcgen05 convolution needs a 16-byte aligned workspace of %zu bytes (got %zu)",
                   2 * sizeof(float) * (size_t)wcount, ws_bytes);
-    stage_weights_kernel<<<(unsigned)div_up64(wcount, 256), 256, 0, st>>>(g, w, is_dx ? 1 : 0, plan.bn, tiles_n, (float*)ws, wcount);
+    stage_weights_kernel<<<(unsigned)div_up64(wcount, 256), 256, 0, st>>>(g, w, is_dx ? 1 : 0, plan.bn, tiles_n, plan.tt, (float*)ws, wcount);
     count_launch();
     if (int rc = launch_check("stage_weights_kernel")) return rc;
     wp = (const float*)ws;
@@ -498,18 +575,23 @@ int strip_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* b
   if (reinterpret_cast<uintptr_t>(wp) & 15) return fail(B200_EINVAL, "weight stage images must be 16-byte aligned");
   StripArgs a{};
   a.g = g; a.act = act; a.wp = wp; a.bias = is_dx ? nullptr : bias; a.bias_stride = bias_stride; a.out = out;
-  a.H = g.h; a.W = g.w; a.pr = g.ph; a.pc = g.pw;
-  a.kc = is_dx ? g.cog : g.cig;
-  a.nc = is_dx ? g.cig : g.cog;
+  a.H = plan.gh; a.W = plan.gw; a.pr = plan.pr; a.pc = plan.pc;
+  a.act_h = plan.act_h; a.act_w = plan.act_w; a.out_h = plan.out_h; a.out_w = plan.out_w;
+  a.sph = plan.sph; a.spw = plan.spw;
+  a.tt = plan.tt;
+  a.kc = kc;
+  a.nc = nc;
   a.out_channels = is_dx ? g.cin : g.cout;
-  a.cblocks = a.kc / KBLK;
-  a.taps = g.kh * g.kw;
-  a.tiles_n = (a.nc + plan.bn - 1) / plan.bn;
-  a.q_total = (long long)g.n * (a.H + a.pr) * (a.W + a.pc);
+  a.cb_per_phase = kc / KBLK;
+  a.cblocks = plan.tt.n_phase * a.cb_per_phase;
+  a.images_per_tile = a.cb_per_phase * plan.tt.taps_total;
+  a.tiles_n = tiles_n;
+  a.q_total = (int)((long long)g.n * (a.H + a.pr) * (a.W + a.pc));
+  a.img_div = FastDiv((uint32_t)((a.H + a.pr) * (a.W + a.pc)));
+  a.row_div = FastDiv((uint32_t)(a.W + a.pc));
   a.tiles_m = div_up64(a.q_total, BLOCK_M);
   a.tiles_total = a.tiles_m * a.tiles_n * g.groups;
   a.halo = plan.halo; a.strip_rows = plan.strip_rows; a.a_stages = plan.a_stages; a.w_stages = plan.w_stages;
-  a.is_dx = is_dx ? 1 : 0;
   a.out_rowmajor = rowmajor ? 1 : 0;
   a.alpha = alpha; a.beta = beta;
   a.out_vec4 = rowmajor && a.out_channels % 4 == 0 && plan.bn % 4 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 && a.nc % 4 == 0;

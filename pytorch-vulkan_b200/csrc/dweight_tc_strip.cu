@@ -25,6 +25,8 @@
 #include "tc_common.cuh"
 
 #include <algorithm>
+#include <cstdio>
+#include <cstdlib>
 
 namespace b200 {
 namespace tcdw {
@@ -44,13 +46,19 @@ struct DwStripArgs {
   View4 x, dy;
   float* out;            // dW (one split) or the partial buffer [split][cout][cig*taps]
   int H, W, pr, pc;      // padded pixel space (see conv_tc_strip.cu)
-  long long q_total;
+  int q_total;           // padded pixels (below 2^31 - 64)
+  FastDiv img_div, row_div;
   int span, splits;      // padded pixels per split (multiple of KP)
   int xblocks;           // staged input blocks per CTA: 1 (taps in M) or 4 (1x1: channel blocks in M)
   int ci_tiles, co_tiles;
   int stages;
   int* status;
+  unsigned long long* prof;  // optional cycle counters of CTA (0,0) (B200_STRIP_PROFILE=1), else null
 };
+
+#define DPROF_ON(leader) (a.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && (leader))
+#define DPROF_T0(on) const long long prof_t0__ = (on) ? clock64() : 0
+#define DPROF_ADD(on, slot) do { if (on) atomicAdd(a.prof + (slot), (unsigned long long)(clock64() - prof_t0__)); } while (0)
 
 struct Ctrl {
   unsigned long long full[MAX_STAGES], empty[MAX_STAGES], accum;
@@ -76,53 +84,63 @@ __device__ __forceinline__ uint64_t make_mn_desc(uint32_t addr, uint32_t lbo) {
 // One warp stages `rows` (<= 32, lane = row) x 32 channels of a pixel-major block: gather from
 // the strided view, split into TF32 hi/lo, swizzled stores.  `q_first` is the padded pixel of row 0;
 // rows outside [q_lo, q_hi) or on padding are written as zeros.
+//
+// With the 32-byte-base swizzle rows r and r+4 put the same 16-byte chunk into the same banks, so
+// lanes 4-7 of every group of eight write the two chunks of a 32-byte pair in the opposite order
+// (every 8-lane store wavefront is then conflict-free).  To keep that free of per-value selects the
+// swapped lanes already LOAD their channels in swapped order: val[j] holds channel j ^ 4 there.
 __device__ __forceinline__ void stage_block(const View4& v, long long chan0, int chans, int H, int W, int row_pitch,
-                                            long long img_pitch, long long q_first, long long q_lo, long long q_hi,
-                                            int rows, int row0, uint32_t plane_hi, uint32_t plane_lo, int lane,
-                                            bool vec_ok, float (&val)[32]) {
-  (void)plane_hi; (void)plane_lo; (void)row0;
-  const long long q = q_first + lane;
+                                            int img_pitch, const FastDiv& img_div, const FastDiv& row_div, int q_first,
+                                            int q_lo, int q_hi, int rows, int lane, bool vec_ok, float (&val)[32]) {
+  const int q = q_first + lane;
   bool ok = lane < rows && q >= q_lo && q < q_hi;
   const float* src = v.ptr;
   if (ok) {
-    const long long n = q / img_pitch;
-    const int rem = (int)(q - n * img_pitch);
-    const int y = rem / row_pitch, x = rem - y * row_pitch;
+    const int n = (int)img_div.div((uint32_t)q);
+    const int rem = q - n * img_pitch;
+    const int y = (int)row_div.div((uint32_t)rem), x = rem - y * row_pitch;
     ok = y < H && x < W;
     src += n * v.s0 + chan0 * v.s1 + (long long)y * v.s2 + (long long)x * v.s3;
   }
-  if (ok && vec_ok && chans == 32) {
+  const int sw = (lane >> 2) & 1;
+  if (ok && chans == 32) {
+    if (vec_ok) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float4 f = __ldg(reinterpret_cast<const float4*>(src) + j);
-      val[4 * j] = f.x; val[4 * j + 1] = f.y; val[4 * j + 2] = f.z; val[4 * j + 3] = f.w;
+      for (int j = 0; j < 8; ++j) {
+        const float4 f = __ldg(reinterpret_cast<const float4*>(src) + (j ^ sw));
+        val[4 * j] = f.x; val[4 * j + 1] = f.y; val[4 * j + 2] = f.z; val[4 * j + 3] = f.w;
+      }
+    } else {
+      const float* pa = src + 4 * sw * v.s1;  // for j with bit 2 clear
+      const float* pb = src - 4 * sw * v.s1;  // for j with bit 2 set
+#pragma unroll
+      for (int j = 0; j < 32; ++j) val[j] = __ldg(((j & 4) ? pb : pa) + j * v.s1);
     }
   } else {
 #pragma unroll
-    for (int j = 0; j < 32; ++j) val[j] = (ok && j < chans) ? __ldg(src + j * v.s1) : 0.f;
+    for (int j = 0; j < 32; ++j) {
+      const int c = j ^ (sw << 2);
+      val[j] = (ok && c < chans) ? __ldg(src + c * v.s1) : 0.f;
+    }
   }
 }
 __device__ __forceinline__ void store_block(const float (&val)[32], int rows, int row0, uint32_t plane_hi,
                                             uint32_t plane_lo, int lane) {
   if (lane >= rows) return;
-  // With the 32-byte-base swizzle rows r and r+4 put the same 16-byte chunk into the same banks.
-  // Lanes 4-7 of every group of eight therefore write the two chunks of a 32-byte pair in the
-  // opposite order, which makes each 8-lane store wavefront conflict-free.
-  const bool swap = (lane >> 2) & 1;
+  const uint32_t sw16 = (uint32_t)((lane >> 2) & 1) << 4;
 #pragma unroll
   for (int m = 0; m < 4; ++m) {
     float h0[4], l0[4], h1[4], l1[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      split_tf32(val[m * 8 + j], h0[j], l0[j]);
-      split_tf32(val[m * 8 + 4 + j], h1[j], l1[j]);
+      split_tf32_fast(val[m * 8 + j], h0[j], l0[j]);
+      split_tf32_fast(val[m * 8 + 4 + j], h1[j], l1[j]);
     }
-    const uint32_t o0 = sw32b_offset(row0 + lane, m * 8), o1 = o0 + 16;
-    const uint32_t oa = swap ? o1 : o0, ob = swap ? o0 : o1;
-    sts_f32x4(plane_hi + oa, swap ? h1[0] : h0[0], swap ? h1[1] : h0[1], swap ? h1[2] : h0[2], swap ? h1[3] : h0[3]);
-    sts_f32x4(plane_lo + oa, swap ? l1[0] : l0[0], swap ? l1[1] : l0[1], swap ? l1[2] : l0[2], swap ? l1[3] : l0[3]);
-    sts_f32x4(plane_hi + ob, swap ? h0[0] : h1[0], swap ? h0[1] : h1[1], swap ? h0[2] : h1[2], swap ? h0[3] : h1[3]);
-    sts_f32x4(plane_lo + ob, swap ? l0[0] : l1[0], swap ? l0[1] : l1[1], swap ? l0[2] : l1[2], swap ? l0[3] : l1[3]);
+    const uint32_t oa = sw32b_offset(row0 + lane, m * 8) ^ sw16, ob = oa ^ 16u;
+    sts_f32x4(plane_hi + oa, h0[0], h0[1], h0[2], h0[3]);
+    sts_f32x4(plane_lo + oa, l0[0], l0[1], l0[2], l0[3]);
+    sts_f32x4(plane_hi + ob, h1[0], h1[1], h1[2], h1[3]);
+    sts_f32x4(plane_lo + ob, l1[0], l1[1], l1[2], l1[3]);
   }
 }
 
@@ -172,10 +190,11 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
   const int ci0 = ci_tile * ci_per_tile, co0 = co_tile * BN;
   const int cols_valid = min(BN, g.cog - co0);
   const int row_pitch = a.W + a.pc;
-  const long long img_pitch = (long long)(a.H + a.pr) * row_pitch;
-  const long long k_begin = (long long)split * a.span, k_end = min(a.q_total, k_begin + a.span);
-  const int kblocks = (int)((k_end - k_begin + KP - 1) / KP);
-  const long long yshift = (long long)(ky * g.dh - g.ph) * row_pitch;
+  const int img_pitch = (a.H + a.pr) * row_pitch;
+  const int k_begin = split * a.span;  // < q_total
+  const int k_end = a.q_total - k_begin > a.span ? k_begin + a.span : a.q_total;
+  const int kblocks = (k_end - k_begin + KP - 1) / KP;
+  const int yshift = (ky * g.dh - g.ph) * row_pitch;
 
   if (warp == MMA_WARP) {
     constexpr uint32_t idesc = make_idesc_tf32(128, BN) | (1u << 15) | (1u << 16);  // both operands MN-major
@@ -183,8 +202,12 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
     const uint32_t a_lbo = a.xblocks == 1 ? (uint32_t)g.dw * 128u : 2u * x_plane;
     for (int kb = 0; kb < kblocks; ++kb) {
       const int s = kb % a.stages;
+      const bool pm = DPROF_ON(lane == 0);
+      { DPROF_T0(pm);
       if (!mbar_wait(smem_u32(&ctrl->full[s]), (uint32_t)(kb / a.stages) & 1, abort_flag, a.status, STATUS_TIMEOUT_FULL)) break;
+      DPROF_ADD(pm, 0); }
       tc_fence_after();
+      DPROF_T0(pm);
       if (lane == 0) {
         const uint32_t xs = base + s * stage_bytes, ys = xs + x_bytes;
         // input rows start at the pixel shifted by -pad_w; hi plane then lo plane of each block
@@ -206,6 +229,7 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
         umma_commit(smem_u32(&ctrl->empty[s]));
       }
       __syncwarp();
+      DPROF_ADD(pm, 1);
     }
     if (lane == 0) umma_commit(smem_u32(&ctrl->accum));
     __syncwarp();
@@ -223,11 +247,13 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
     for (long long job = warp; job < total_jobs && alive; job += warps_active) {
       const int kb = (int)(job / tasks), j = (int)(job - (long long)kb * tasks);
       const int s = kb % a.stages;
-      const long long k0 = k_begin + (long long)kb * KP;
+      const int k0 = k_begin + kb * KP;
       const uint32_t xs = base + s * stage_bytes, ys = xs + x_bytes;
       float val[32];
       int rows, row0;
       uint32_t p_hi, p_lo;
+      const bool pp = DPROF_ON(threadIdx.x == 0);
+      DPROF_T0(pp);
       if (j < x_tasks) {
         const int blk = j >> 1, half = j & 1;
         rows = half ? XR - 32 : 32;
@@ -237,8 +263,8 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
         const int c0 = ci0 + blk * 32;
         const int chans = max(0, min(32, g.cig - c0));
         // the input is needed wherever it exists: no split-range clipping, only image bounds
-        stage_block(a.x, (long long)group * g.cig + c0, chans, a.H, a.W, row_pitch, img_pitch,
-                    k0 + yshift - XOFF + row0, 0, a.q_total, rows, row0, p_hi, p_lo, lane, x_vec, val);
+        stage_block(a.x, (long long)group * g.cig + c0, chans, a.H, a.W, row_pitch, img_pitch, a.img_div, a.row_div,
+                    k0 + yshift - XOFF + row0, 0, a.q_total, rows, lane, x_vec, val);
       } else {
         const int blk = j - x_tasks;
         rows = 32;
@@ -248,16 +274,24 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
         const int c0 = co0 + blk * 32;
         const int chans = max(0, min(32, g.cog - c0));
         // dY outside this split's pixel range must read as zero so that splits do not overlap
-        stage_block(a.dy, (long long)group * g.cog + c0, chans, a.H, a.W, row_pitch, img_pitch, k0, k_begin, k_end,
-                    rows, row0, p_hi, p_lo, lane, y_vec, val);
+        stage_block(a.dy, (long long)group * g.cog + c0, chans, a.H, a.W, row_pitch, img_pitch, a.img_div, a.row_div,
+                    k0, k_begin, k_end, rows, lane, y_vec, val);
       }
+      DPROF_ADD(pp, 2);
+      { const long long tw = pp ? clock64() : 0;
       if (!mbar_wait(smem_u32(&ctrl->empty[s]), ((uint32_t)(kb / a.stages) & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_EMPTY)) { alive = false; break; }
+      if (pp) atomicAdd(a.prof + 3, (unsigned long long)(clock64() - tw)); }
+      { const long long tw = pp ? clock64() : 0;
       store_block(val, rows, row0, p_hi, p_lo, lane);
       fence_proxy_async();
       mbar_arrive(smem_u32(&ctrl->full[s]));
+      if (pp) { atomicAdd(a.prof + 4, (unsigned long long)(clock64() - tw)); atomicAdd(a.prof + 5, 1ull); } }
     }
     // ---- epilogue (warps 0-3): lane = row of the accumulator = (block, channel) ----
+    const bool pe = DPROF_ON(threadIdx.x == 0);
+    DPROF_T0(pe);
     if (warp < 4 && mbar_wait(smem_u32(&ctrl->accum), 0, abort_flag, a.status, STATUS_TIMEOUT_ACCUM)) {
+      DPROF_ADD(pe, 6);
       tc_fence_after();
       const int taps = g.kh * g.kw;
       const long long cols = (long long)g.cig * taps;
@@ -278,11 +312,19 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
           for (int j = 0; j < 32; ++j) v[j] += v2[j];
         }
         if (row_ok) {
+          float* p = out + c0 * cols;
+          const int nvalid = cols_valid - c0;
+          if (nvalid >= 32) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (c0 + j < cols_valid) out[(long long)(c0 + j) * cols] = v[j];
+            for (int j = 0; j < 32; ++j, p += cols) *p = v[j];
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j, p += cols)
+              if (j < nvalid) *p = v[j];
+          }
         }
       }
+      DPROF_ADD(pe, 7);
     }
   }
   tc_fence_before();
@@ -327,7 +369,7 @@ static DwStripPlan plan_dw_strip(const ConvGeom& g, size_t budget) {
     span = div_up64(div_up64(q_total, want), KP) * KP;
     splits = div_up64(q_total, span);
   }
-  if (span > 2147483616ll) return p;
+  if (q_total > 2147483647ll - (1 << 20)) return p;  // pixel indices are 32-bit in the kernel
   p.splits = (int)splits;
   p.span = (int)span;
   p.bytes = splits > 1 ? (size_t)splits * dw_bytes : 0;
@@ -359,7 +401,9 @@ int dweight_strip(const ConvGeom& g, View4 x, View4 dy, float* dw, void* ws, siz
   DwStripArgs a{};
   a.g = g; a.x = x; a.dy = dy;
   a.H = g.h; a.W = g.w; a.pr = g.ph; a.pc = g.pw;
-  a.q_total = (long long)g.n * (a.H + a.pr) * (a.W + a.pc);
+  a.q_total = (int)((long long)g.n * (a.H + a.pr) * (a.W + a.pc));
+  a.img_div = FastDiv((uint32_t)((a.H + a.pr) * (a.W + a.pc)));
+  a.row_div = FastDiv((uint32_t)(a.W + a.pc));
   a.span = plan.span; a.splits = plan.splits; a.xblocks = plan.xblocks;
   a.ci_tiles = plan.ci_tiles; a.co_tiles = plan.co_tiles; a.stages = plan.stages;
   a.out = plan.splits > 1 ? (float*)ws : dw;
@@ -370,9 +414,25 @@ int dweight_strip(const ConvGeom& g, View4 x, View4 dy, float* dw, void* ws, siz
   // rows of dW that no CTA writes (channel blocks beyond kw taps) do not exist: every (co, ci, ky, kx)
   // is covered because kx < kw <= 4 blocks and all ci tiles are enumerated
   const dim3 grid((unsigned)gx, (unsigned)plan.splits);
+  static unsigned long long* prof_buf = nullptr;
+  const char* prof_env = getenv("B200_STRIP_PROFILE");
+  const bool profiling = prof_env && prof_env[0] == '1';
+  if (profiling) {
+    if (!prof_buf) B200_CUDA(cudaMalloc(&prof_buf, 16 * sizeof(unsigned long long)));
+    B200_CUDA(cudaMemsetAsync(prof_buf, 0, 16 * sizeof(unsigned long long), st));
+    a.prof = prof_buf;
+  }
   int rc = plan.bn == 64 ? launch_dw_strip<64>(a, grid, plan.smem, st)
          : plan.bn == 128 ? launch_dw_strip<128>(a, grid, plan.smem, st) : launch_dw_strip<256>(a, grid, plan.smem, st);
   if (rc) return rc;
+  if (profiling) {
+    unsigned long long h[16];
+    B200_CUDA(cudaStreamSynchronize(st));
+    B200_CUDA(cudaMemcpy(h, prof_buf, sizeof h, cudaMemcpyDeviceToHost));
+    fprintf(stderr, "[dweight strip profile, CTA 0, cycles] bn=%d xblocks=%d stages=%d grid=%lldx%d kblocks/cta=%d | mma: wait_full %llu issue %llu | "
+            "warp 0: jobs %llu load %llu wait_empty %llu store %llu | epilogue: wait_accum(total) %llu drain %llu\n",
+            plan.bn, plan.xblocks, plan.stages, gx, plan.splits, plan.span / KP, h[0], h[1], h[5], h[2], h[3], h[4], h[6], h[7]);
+  }
   if (plan.splits > 1)
     return finalize_splits((const float*)ws, dw, (long long)g.cout * g.cig * g.kh * g.kw, plan.splits, st);
   return B200_OK;

@@ -166,6 +166,11 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+#ifdef B200_SPLIT_MASK_LO
+#define B200_SPLIT_LO(r) __uint_as_float(__float_as_uint(r) & 0xFFFFE000u)
+#else
+#define B200_SPLIT_LO(r) (r)
+#endif
 // ---- 3xTF32 split --------------------------------------------------------------------------
 // x = hi + lo with hi the TF32 value nearest to x (10 explicit mantissa bits, low 13 bits zero)
 // and lo the TF32 truncation of the exact FP32 remainder.  a*b is then evaluated as
@@ -179,6 +184,14 @@ __device__ __forceinline__ void split_tf32(float x, float& hi, float& lo) {
   const float rem = x - hi;
   // |hi| = inf or NaN (overflowing round-up, or non-finite input): keep hi alone.
   lo = ((h & 0x7F800000u) == 0x7F800000u) ? 0.f : __uint_as_float(__float_as_uint(rem) & 0xFFFFE000u);
+}
+
+// Producer-side split (three instructions per value): same hi; lo is the exact remainder, of which
+// the tensor core reads the TF32 bits only.  An operand that rounds up past the largest finite TF32
+// value (|x| >= 2^128 - 2^115) or is not finite yields NaN where the full split keeps hi alone.
+__device__ __forceinline__ void split_tf32_fast(float x, float& hi, float& lo) {
+  hi = __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u);
+  lo = B200_SPLIT_LO(x - hi);
 }
 
 // Byte offset of element (row, k) inside a 128B-swizzled K-major tile plane (k in [0,32)).

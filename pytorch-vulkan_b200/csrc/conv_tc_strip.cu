@@ -68,15 +68,20 @@ struct StripArgs {
   int H, W, pr, pc;       // pixel grid shared by the strip and the accumulator rows, and its zero padding
   int act_h, act_w;       // extent of the activation tensor; grid pixel (r, c) of phase (a, b) reads (r*sph + a, c*spw + b)
   int out_h, out_w;       // extent of the output tensor (grid pixels beyond it are discarded)
-  int sph, spw;
+  int sph, spw;           // forward: phases live on the reduction side (channel block -> phase)
+  int osh, osw;           // dInput: phases live on the output side: column tile -> phase (a, b), grid pixel (r, c)
+                          // is the output pixel (r*osh + a, c*osw + b); all phases read the same dY strip
+  int phase_on_n;         // 1 in the dInput arrangement
+  int tiles_pp;           // column tiles per phase (dInput), else tiles_n
   int kc, nc, out_channels;
   int cb_per_phase;       // kc / 32
-  int cblocks;            // strips per tile: n_phase * cb_per_phase
-  int images_per_tile;    // weight stages per tile: cb_per_phase * taps_total
+  int cblocks;            // strips per tile: forward n_phase * cb_per_phase, dInput cb_per_phase
+  int images_per_tile;    // forward: weight stages per tile = cb_per_phase * taps_total
   int tiles_n;
   int q_total;            // grid pixels incl. padding (below 2^31 - 2^20)
   FastDiv img_div, row_div;
-  long long tiles_m, tiles_total;
+  int tiles_m, tiles_total;
+  FastDiv div_tiles_n, div_tiles_m, div_tiles_pp, div_chunks, div_cblocks, div_cbpp, div_a_stages;
   int halo, strip_rows;   // rows staged before the tile's first pixel; strip_rows is a multiple of 8
   int a_stages, w_stages;
   int out_rowmajor;       // 0: NCHW planes.  1: [pixel][channel] rows (channels-last / GEMM C)
@@ -103,6 +108,7 @@ struct Ctrl {  // lives behind the operand stages in shared memory
 template <int BN>
 __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs a) {
   extern __shared__ unsigned char smem_raw[];
+  const unsigned long long prof_start = a.prof ? global_ns() : 0;
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t tiles_base = (raw + 1023u) & ~1023u;
   const uint32_t a_stage_bytes = (uint32_t)a.strip_rows * 256u, a_plane = (uint32_t)a.strip_rows * 128u;
@@ -151,38 +157,44 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
 
   if (warp == MMA_WARP) {
     // ------------------------------ MMA issuer ------------------------------
-    constexpr uint32_t idesc = make_idesc_tf32(BLOCK_M, BN);
-    constexpr uint32_t idesc_wide = make_idesc_tf32(BLOCK_M, FUSE_HILO ? 2 * BN : BN);
-    uint32_t a_count = 0, w_count = 0, t_count = 0;
-    bool alive = true;
-    for (long long tile = blockIdx.x; tile < a.tiles_total && alive; tile += gridDim.x, ++t_count) {
-      const uint32_t ab = t_count & 1;
-      const bool pm = PROF_ON(lane == 0);
-      { PROF_T0(pm);
-      if (!mbar_wait(smem_u32(&ctrl->acc_empty[ab]), ((t_count >> 1) & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_ACCUM)) break;
-      PROF_ADD(pm, 0); }
-      const uint32_t tmem_acc = tmem_base + ab * ACC_COLS;
-      uint32_t accumulate = 0;  // the tile's first MMA overwrites the accumulator
-      for (int cb = 0; cb < a.cblocks && alive; ++cb, ++a_count) {
-        const uint32_t as = a_count % a.a_stages;
+    // One thread.  The tensor pipe accepts only a few instructions ahead of the one it executes, so
+    // whatever this thread does between two tcgen05.mma shows up as idle tensor time: stage indices
+    // and parities are counted, not divided, and descriptors are the stage's base plus an offset.
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_tf32(BLOCK_M, BN);
+      constexpr uint32_t idesc_wide = make_idesc_tf32(BLOCK_M, FUSE_HILO ? 2 * BN : BN);
+      const uint64_t da_base = make_kmajor_sw128_desc(tiles_base + (uint32_t)a.halo * 128u);
+      const uint64_t db_base = make_kmajor_sw128_desc(w_base);
+      const uint32_t a_stage_d = a_stage_bytes >> 4, a_plane_d = a_plane >> 4;
+      constexpr uint32_t w_stage_d = w_stage_bytes >> 4, w_plane_d = w_plane >> 4;
+      uint32_t as = 0, a_par = 0, ws = 0, w_par = 0, t_count = 0;
+      const bool pm = PROF_ON(true);
+      bool alive = true;
+      for (int tile = blockIdx.x; tile < a.tiles_total && alive; tile += gridDim.x, ++t_count) {
+        const uint32_t ab = t_count & 1;
         { PROF_T0(pm);
-        if (!mbar_wait(smem_u32(&ctrl->a_full[as]), (a_count / a.a_stages) & 1, abort_flag, a.status, STATUS_TIMEOUT_FULL)) { alive = false; break; }
-        PROF_ADD(pm, 1); }
-        const uint32_t strip = tiles_base + as * a_stage_bytes;
-        const int phase = cb / a.cb_per_phase;
-        const int tap_end = ctrl->tap_start[phase + 1];
-        for (int tap = ctrl->tap_start[phase]; tap < tap_end; ++tap, ++w_count) {
-          const uint32_t ws = w_count % a.w_stages;
+        if (!mbar_wait(smem_u32(&ctrl->acc_empty[ab]), ((t_count >> 1) & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_ACCUM)) break;
+        PROF_ADD(pm, 0); }
+        const uint32_t tmem_acc = tmem_base + ab * ACC_COLS;
+        const int n_tile = tile - (int)a.div_tiles_n.div((uint32_t)tile) * a.tiles_n;
+        int phase = a.phase_on_n ? (int)a.div_tiles_pp.div((uint32_t)n_tile) : 0;  // dInput: the phase of this column tile
+        int cbl = 0;
+        uint32_t accumulate = 0;  // the tile's first MMA overwrites the accumulator
+        for (int cb = 0; cb < a.cblocks && alive; ++cb) {
           { PROF_T0(pm);
-          if (!mbar_wait(smem_u32(&ctrl->w_full[ws]), (w_count / a.w_stages) & 1, abort_flag, a.status, STATUS_TIMEOUT_FULL)) { alive = false; break; }
-          PROF_ADD(pm, 2); }
-          tc_fence_after();
-          PROF_T0(pm);
-          if (lane == 0) {
-            const uint32_t a_hi = strip + (uint32_t)(a.halo + ctrl->shift[tap]) * 128u, a_lo = a_hi + a_plane;
-            const uint32_t b_hi = w_base + ws * w_stage_bytes, b_lo = b_hi + w_plane;
-            const uint64_t da_hi = make_kmajor_sw128_desc(a_hi), da_lo = make_kmajor_sw128_desc(a_lo);
-            const uint64_t db_hi = make_kmajor_sw128_desc(b_hi), db_lo = make_kmajor_sw128_desc(b_lo);
+          if (!mbar_wait(smem_u32(&ctrl->a_full[as]), a_par, abort_flag, a.status, STATUS_TIMEOUT_FULL)) { alive = false; break; }
+          PROF_ADD(pm, 1); }
+          const uint64_t da_strip = da_base + as * a_stage_d;
+          const int tap_end = ctrl->tap_start[phase + 1];
+          for (int tap = ctrl->tap_start[phase]; tap < tap_end; ++tap) {
+            const int sh = ctrl->shift[tap];
+            { PROF_T0(pm);
+            if (!mbar_wait(smem_u32(&ctrl->w_full[ws]), w_par, abort_flag, a.status, STATUS_TIMEOUT_FULL)) { alive = false; break; }
+            PROF_ADD(pm, 2); }
+            tc_fence_after();
+            PROF_T0(pm);
+            const uint64_t da_hi = da_strip + (uint64_t)(long long)(sh * 8), da_lo = da_hi + a_plane_d;
+            const uint64_t db_hi = db_base + ws * w_stage_d, db_lo = db_hi + w_plane_d;
             const uint32_t first = accumulate;
             accumulate = 1;
             if (FUSE_HILO) {
@@ -199,41 +211,53 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
               for (int kk = 0; kk < 4; ++kk) umma_tf32(tmem_acc, da_hi + 2 * kk, db_hi + 2 * kk, idesc, 1);
             }
             umma_commit(smem_u32(&ctrl->w_empty[ws]));
+            if (++ws == (uint32_t)a.w_stages) { ws = 0; w_par ^= 1; }
+            PROF_ADD(pm, 3);
           }
-          __syncwarp();
-          PROF_ADD(pm, 3);
+          if (alive) umma_commit(smem_u32(&ctrl->a_empty[as]));
+          if (++as == (uint32_t)a.a_stages) { as = 0; a_par ^= 1; }
+          if (!a.phase_on_n && ++cbl == a.cb_per_phase) { cbl = 0; ++phase; }
         }
-        if (alive && lane == 0) umma_commit(smem_u32(&ctrl->a_empty[as]));
-        __syncwarp();
+        if (alive) umma_commit(smem_u32(&ctrl->acc_full[ab]));
       }
-      if (alive && lane == 0) umma_commit(smem_u32(&ctrl->acc_full[ab]));
-      __syncwarp();
     }
   } else if (warp == EPI_WARPS + A_WARPS) {
     // ------------------------------ weight stages ------------------------------
     // One thread: each stage is a single bulk copy of a ready-made (split, swizzled) image.
     if (lane == 0) {
-      uint32_t w_count = 0;
+      uint32_t ws = 0, w_par = 1, issued = 0;
       bool alive = true;
       const bool pw = PROF_ON(true);
-      for (long long tile = blockIdx.x; tile < a.tiles_total && alive; tile += gridDim.x) {
-        const long long n_tile = tile % a.tiles_n;
-        const long long group = (tile / a.tiles_n) / a.tiles_m;
-        const float* img = a.wp + (group * a.tiles_n + n_tile) * a.images_per_tile * (long long)(BN * 64);
-        for (int i = 0; i < a.images_per_tile; ++i, ++w_count, img += BN * 64) {
-          const uint32_t ws = w_count % a.w_stages;
+      for (int tile = blockIdx.x; tile < a.tiles_total && alive; tile += gridDim.x) {
+        const int tn = (int)a.div_tiles_n.div((uint32_t)tile), n_tile = tile - tn * a.tiles_n;
+        const long long group = a.div_tiles_m.div((uint32_t)tn);
+        long long first_image;
+        int images;
+        if (a.phase_on_n) {  // images of a group: [phase][tile of the phase][channel block][tap of the phase]
+          const int phase = (int)a.div_tiles_pp.div((uint32_t)n_tile), in_phase = n_tile - phase * a.tiles_pp;
+          const int t0 = ctrl->tap_start[phase], ntap = ctrl->tap_start[phase + 1] - t0;
+          images = a.cb_per_phase * ntap;
+          first_image = ((group * a.tt.taps_total + t0) * a.tiles_pp + (long long)in_phase * ntap) * a.cb_per_phase;
+        } else {
+          images = a.images_per_tile;
+          first_image = (group * a.tiles_n + n_tile) * a.images_per_tile;
+        }
+        const float* img = a.wp + first_image * (long long)(BN * 64);
+        for (int i = 0; i < images; ++i, img += BN * 64) {
           { PROF_T0(pw);
-          if (!mbar_wait(smem_u32(&ctrl->w_empty[ws]), ((w_count / a.w_stages) & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_EMPTY)) { alive = false; break; }
+          if (!mbar_wait(smem_u32(&ctrl->w_empty[ws]), w_par, abort_flag, a.status, STATUS_TIMEOUT_EMPTY)) { alive = false; break; }
           PROF_ADD(pw, 4); }
           const uint32_t full = smem_u32(&ctrl->w_full[ws]);
           mbar_expect_tx(full, w_stage_bytes);
           bulk_g2s(w_base + ws * w_stage_bytes, img, w_stage_bytes, full);
+          ++issued;
+          if (++ws == (uint32_t)a.w_stages) { ws = 0; w_par ^= 1; }
         }
       }
-      // After an abort the MMA warp no longer consumes stages: wait (bounded) for the copies still
+      // After an abort the MMA thread no longer consumes stages: wait (bounded) for the copies still
       // in flight so that none lands in shared memory of a finished CTA.
       if (!alive)
-        for (uint32_t j = w_count > (uint32_t)a.w_stages ? w_count - a.w_stages : 0; j < w_count; ++j)
+        for (uint32_t j = issued > (uint32_t)a.w_stages ? issued - a.w_stages : 0; j < issued; ++j)
           mbar_wait(smem_u32(&ctrl->w_full[j % a.w_stages]), (j / a.w_stages) & 1, nullptr, a.status, STATUS_TIMEOUT_FULL);
     }
   } else if (warp >= EPI_WARPS) {
@@ -244,31 +268,34 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
     const int chunks = (a.strip_rows + 31) / 32;
     const bool vec_ok = a.act.s1 == 1 && ((reinterpret_cast<uintptr_t>(a.act.ptr) & 15) == 0) &&
                         (a.act.s0 % 4 == 0) && (a.act.s2 % 4 == 0) && (a.act.s3 % 4 == 0);
-    const long long my_tiles = a.tiles_total > blockIdx.x ? (a.tiles_total - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-    const long long total_jobs = my_tiles * a.cblocks * chunks;
+    const int my_tiles = a.tiles_total > (int)blockIdx.x ? (a.tiles_total - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+    const int total_jobs = my_tiles * a.cblocks * chunks;  // below 2^31 (checked by the host)
     // A warp's consecutive jobs must not be more than a_stages stages apart: a waiter that skips a
     // whole phase of a stage's mbarrier would see the parity of an older phase and run ahead.
     const int a_warps = min(A_WARPS, chunks * a.a_stages);
-    for (long long job = aw; job < total_jobs && aw < a_warps; job += a_warps) {
-      const uint32_t a_count = (uint32_t)(job / chunks);
-      const int chunk = (int)(job - (long long)a_count * chunks);
-      const long long tile = blockIdx.x + (long long)(a_count / a.cblocks) * gridDim.x;
-      const int cb = (int)(a_count % a.cblocks);
-      const long long m_tile = (tile / a.tiles_n) % a.tiles_m;
-      const int group = (int)((tile / a.tiles_n) / a.tiles_m);
-      const uint32_t as = a_count % a.a_stages;
+    for (int job = aw; job < total_jobs && aw < a_warps; job += a_warps) {
+      const uint32_t a_count = a.div_chunks.div((uint32_t)job);
+      const int chunk = job - (int)a_count * chunks;
+      const uint32_t tile_iter = a.div_cblocks.div(a_count);
+      const int cb = (int)(a_count - tile_iter * a.cblocks);
+      const uint32_t tile = blockIdx.x + tile_iter * gridDim.x;
+      const uint32_t tn = a.div_tiles_n.div(tile);
+      const int group = (int)a.div_tiles_m.div(tn);
+      const int m_tile = (int)tn - group * (int)a.tiles_m;
+      const uint32_t a_round = a.div_a_stages.div(a_count);
+      const uint32_t as = a_count - a_round * a.a_stages;
       const bool pa = PROF_ON(threadIdx.x == EPI_WARPS * 32);
       PROF_T0(pa);
       const int r = chunk * 32 + lane;
-      const int q = (int)m_tile * BLOCK_M - a.halo + r;
+      const int q = m_tile * BLOCK_M - a.halo + r;
       bool ok = r < a.strip_rows && q >= 0 && q < a.q_total;
       const float* src = a.act.ptr;
       if (ok) {
         const int n = (int)a.img_div.div((uint32_t)q);
         const int rem = q - n * img_pitch;
         const int y = (int)a.row_div.div((uint32_t)rem), x = rem - y * row_pitch;
-        const int phase = cb / a.cb_per_phase, cbl = cb - phase * a.cb_per_phase;
-        const int iy = y * a.sph + ctrl->ph_a[phase], ix = x * a.spw + ctrl->ph_b[phase];
+        const int phase = a.phase_on_n ? 0 : (int)a.div_cbpp.div((uint32_t)cb), cbl = cb - phase * a.cb_per_phase;
+        const int iy = a.phase_on_n ? y : y * a.sph + ctrl->ph_a[phase], ix = a.phase_on_n ? x : x * a.spw + ctrl->ph_b[phase];
         ok = y < a.H && x < a.W && iy < a.act_h && ix < a.act_w;
         src += n * a.act.s0 + ((long long)group * a.kc + cbl * KBLK) * a.act.s1 + (long long)iy * a.act.s2 + (long long)ix * a.act.s3;
       }
@@ -285,7 +312,7 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
       }
       {
         const long long tw = pa ? clock64() : 0;
-        if (!mbar_wait(smem_u32(&ctrl->a_empty[as]), ((a_count / a.a_stages) & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_EMPTY)) break;
+        if (!mbar_wait(smem_u32(&ctrl->a_empty[as]), (a_round & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_EMPTY)) break;
         if (pa) atomicAdd(a.prof + 6, (unsigned long long)(clock64() - tw));
       }
       if (r < a.strip_rows) {
@@ -313,22 +340,27 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
     const int quarter = warp & 3, half = warp >> 2;
     constexpr int HALVES = EPI_WARPS / 4;
     uint32_t t_count = 0;
-    for (long long tile = blockIdx.x; tile < a.tiles_total; tile += gridDim.x, ++t_count) {
-      const int n_tile = (int)(tile % a.tiles_n);
-      const long long m_tile = (tile / a.tiles_n) % a.tiles_m;
-      const int group = (int)((tile / a.tiles_n) / a.tiles_m);
-      const int n0 = n_tile * BN;
+    for (int tile = blockIdx.x; tile < a.tiles_total; tile += gridDim.x, ++t_count) {
+      const int tn = (int)a.div_tiles_n.div((uint32_t)tile), n_tile = tile - tn * a.tiles_n;
+      const int group = (int)a.div_tiles_m.div((uint32_t)tn);
+      const int m_tile = tn - group * (int)a.tiles_m;
+      const int phase_n = (int)a.div_tiles_pp.div((uint32_t)n_tile);
+      const int n0 = (n_tile - phase_n * a.tiles_pp) * BN;
       const int cols_valid = min(BN, a.nc - n0);
       const uint32_t ab = t_count & 1;
       const bool pe = PROF_ON(threadIdx.x == 0);
-      const int q = (int)m_tile * BLOCK_M + quarter * 32 + lane;
+      // a dInput phase that no tap reaches (e.g. 1x1 filter with stride 2) gets zeros
+      const bool has_taps = !a.phase_on_n || ctrl->tap_start[phase_n + 1] > ctrl->tap_start[phase_n];
+      const int q = m_tile * BLOCK_M + quarter * 32 + lane;
       bool ok = q < a.q_total;
       long long obase = 0;
       if (ok) {
         const long long n = a.img_div.div((uint32_t)q);
         const int rem = q - (int)n * img_pitch;
-        const int y = (int)a.row_div.div((uint32_t)rem), x = rem - y * row_pitch;
-        ok = y < a.out_h && x < a.out_w;
+        int y = (int)a.row_div.div((uint32_t)rem), x = rem - y * row_pitch;
+        ok = y < a.H && x < a.W;
+        if (a.phase_on_n) { y = y * a.osh + ctrl->ph_a[phase_n]; x = x * a.osw + ctrl->ph_b[phase_n]; }
+        ok = ok && y < a.out_h && x < a.out_w;
         obase = a.out_rowmajor ? (((n * a.out_h + y) * a.out_w + x) * (long long)a.out_channels + (long long)group * a.nc + n0)
                                : (((n * a.out_channels + (long long)group * a.nc + n0) * a.out_h + y) * a.out_w + x);
       }
@@ -358,6 +390,10 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
           released = true;
         }
         const int nvalid = min(32, cols_valid - c0);
+        if (!has_taps) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = 0.f;
+        }
         if (a.bias) {
           float bv = 0.f;  // lane j holds the bias of column c0 + j
           if (lane < nvalid) bv = a.beta * __ldg(a.bias + ((long long)group * a.nc + n0 + c0 + lane) * a.bias_stride);
@@ -396,6 +432,14 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
+  if (a.prof && threadIdx.x == 0) {  // spread of CTA start times and lifetimes (ns)
+    const unsigned long long now = global_ns();
+    atomicMin(a.prof + 11, prof_start);
+    atomicMax(a.prof + 12, prof_start);
+    atomicMax(a.prof + 13, now);
+    atomicMin(a.prof + 14, now - prof_start);
+    atomicMax(a.prof + 15, now - prof_start);
+  }
 }
 
 // Split W[cout][cin/g][kh][kw] (any strides) into TF32 hi/lo parts laid out as the shared-memory
@@ -403,22 +447,38 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
 // the tile (forward: co, dInput: ci; zero beyond nc), 32 reduction channels per row.  Images are
 // ordered as the main loop consumes them: [group][n_tile][phase][channel block][tap of the phase],
 // so a weight stage of the main kernel is one bulk copy from a running pointer.
-__global__ void __launch_bounds__(256) stage_weights_kernel(ConvGeom g, View4 w, int is_dx, int bn, int tiles_n,
+__global__ void __launch_bounds__(256) stage_weights_kernel(ConvGeom g, View4 w, int is_dx, int bn, int tiles_pp,
                                                             TapTable tt, float* __restrict__ out, long long total) {
   const long long i = blockIdx.x * 256ll + threadIdx.x;
   if (i >= total) return;
   const int kc = is_dx ? g.cog : g.cig, nc = is_dx ? g.cig : g.cog;
-  const int cpp = kc / KBLK, per_tile = cpp * tt.taps_total;
+  const int cpp = kc / KBLK;
   const int k = (int)(i % KBLK);
   const int row = (int)((i / KBLK) % bn);
   const long long image = i / ((long long)KBLK * bn);
-  const int local = (int)(image % per_tile);
-  const int n_tile = (int)((image / per_tile) % tiles_n);
-  const int grp = (int)(image / ((long long)per_tile * tiles_n));
-  int phase = 0;
-  while (phase + 1 < tt.n_phase && local >= cpp * tt.start[phase + 1]) ++phase;
-  const int rel = local - cpp * tt.start[phase], ntap = tt.start[phase + 1] - tt.start[phase];
-  const int cbl = rel / ntap, tap = tt.start[phase] + rel % ntap;
+  int grp, n_tile, cbl, tap;
+  if (is_dx) {  // [group][phase][tile of the phase][channel block][tap of the phase]
+    const int per_group = tiles_pp * cpp * tt.taps_total;
+    grp = (int)(image / per_group);
+    const int local = (int)(image - (long long)grp * per_group);
+    int phase = 0;
+    while (phase + 1 < tt.n_phase && local >= tiles_pp * cpp * tt.start[phase + 1]) ++phase;
+    const int rel = local - tiles_pp * cpp * tt.start[phase], ntap = tt.start[phase + 1] - tt.start[phase];
+    n_tile = rel / (cpp * ntap);
+    const int rel2 = rel - n_tile * cpp * ntap;
+    cbl = rel2 / ntap;
+    tap = tt.start[phase] + rel2 % ntap;
+  } else {      // [group][tile][phase][channel block][tap of the phase]
+    const int per_tile = cpp * tt.taps_total;
+    const int local = (int)(image % per_tile);
+    n_tile = (int)((image / per_tile) % tiles_pp);
+    grp = (int)(image / ((long long)per_tile * tiles_pp));
+    int phase = 0;
+    while (phase + 1 < tt.n_phase && local >= cpp * tt.start[phase + 1]) ++phase;
+    const int rel = local - cpp * tt.start[phase], ntap = tt.start[phase + 1] - tt.start[phase];
+    cbl = rel / ntap;
+    tap = tt.start[phase] + rel % ntap;
+  }
   const int r = n_tile * bn + row, c = cbl * KBLK + k;
   float v = 0.f;
   if (r < nc) {
@@ -442,29 +502,31 @@ struct StripPlan {
   TapTable tt;
 };
 
-// Forward takes any stride / padding / dilation; dInput stride 1 with any padding / dilation.  Both
-// need the reduction channels in blocks of 32 and at least 16 output columns.
+// Any stride / padding / dilation in both directions; the reduction channels must come in blocks of
+// 32 and there must be at least 16 output columns.  Forward groups the taps by the phase of the
+// INPUT pixel they read; dInput by the phase of the OUTPUT (dX) pixel they contribute to: dX pixel
+// s*r + a receives tap ky iff (ky*d - pad) = a (mod s), from dY row r - floor((ky*d - pad) / s).
 static StripPlan plan_strip(const ConvGeom& g, bool is_dx) {
   StripPlan p;
   const int kc = is_dx ? g.cog : g.cig, nc = is_dx ? g.cig : g.cog;
   if (kc % KBLK != 0 || nc < 16 || g.kh * g.kw > MAX_TAPS) return p;
-  if (is_dx && (g.sh != 1 || g.sw != 1)) return p;
   if (g.sh * g.sw > MAX_PHASES || g.sh > 255 || g.sw > 255) return p;
   p.sph = g.sh; p.spw = g.sw;
   p.act_h = is_dx ? g.oh : g.h; p.act_w = is_dx ? g.ow : g.w;
   p.out_h = is_dx ? g.h : g.oh; p.out_w = is_dx ? g.w : g.ow;
-  // the grid covers the output and every phase sub-image of the activations
-  p.gh = std::max(p.out_h, (p.act_h + p.sph - 1) / p.sph);
-  p.gw = std::max(p.out_w, (p.act_w + p.spw - 1) / p.spw);
+  // the grid covers the unstrided tensor and every phase sub-image of the strided one
+  p.gh = std::max(g.oh, (g.h + p.sph - 1) / p.sph);
+  p.gw = std::max(g.ow, (g.w + p.spw - 1) / p.spw);
   // taps -> (phase, whole-pixel offset); forward reads x at s*o - pad + k*d, dInput reads dy at i + pad - k*d
   struct Tap { int phase, dr, dc, ky, kx; };
   Tap taps[MAX_TAPS];
   int ntaps = 0, dr_lo = 0, dr_hi = 0, dc_lo = 0, dc_hi = 0;
   for (int ky = 0; ky < g.kh; ++ky)
     for (int kx = 0; kx < g.kw; ++kx) {
-      const int oy = is_dx ? g.ph - ky * g.dh : ky * g.dh - g.ph, ox = is_dx ? g.pw - kx * g.dw : kx * g.dw - g.pw;
-      const int dr = floor_div(oy, p.sph), dc = floor_div(ox, p.spw);
-      taps[ntaps++] = Tap{(oy - dr * p.sph) * p.spw + (ox - dc * p.spw), dr, dc, ky, kx};
+      const int oy = ky * g.dh - g.ph, ox = kx * g.dw - g.pw;
+      const int fr = floor_div(oy, p.sph), fc = floor_div(ox, p.spw);
+      const int dr = is_dx ? -fr : fr, dc = is_dx ? -fc : fc;
+      taps[ntaps++] = Tap{(oy - fr * p.sph) * p.spw + (ox - fc * p.spw), dr, dc, ky, kx};
       dr_lo = std::min(dr_lo, dr); dr_hi = std::max(dr_hi, dr);
       dc_lo = std::min(dc_lo, dc); dc_hi = std::max(dc_hi, dc);
     }
@@ -485,7 +547,7 @@ static StripPlan plan_strip(const ConvGeom& g, bool is_dx) {
         lo = std::min(lo, tt.shift[i]); hi = std::max(hi, tt.shift[i]);
         ++count;
       }
-    if (count == 0) continue;  // no tap reads this phase: its channel blocks are never staged
+    if (count == 0 && !is_dx) continue;  // forward: a phase no tap reads is never staged (dInput: it is zero-filled)
     tt.a[tt.n_phase] = (unsigned char)(phase / p.spw); tt.b[tt.n_phase] = (unsigned char)(phase % p.spw);
     tt.start[tt.n_phase + 1] = (unsigned char)tt.taps_total;
     ++tt.n_phase;
@@ -505,7 +567,7 @@ static StripPlan plan_strip(const ConvGeom& g, bool is_dx) {
       if (a_stages > 2 && a_stages * a_stage > SMEM_LIMIT / 2) continue;  // deep strip pipelines only while cheap
       const int left = SMEM_LIMIT - a_stages * a_stage;
       if (left < 2 * w_stage) continue;
-      const long long tiles = tiles_m * ((nc + bn - 1) / bn) * g.groups;
+      const long long tiles = tiles_m * ((nc + bn - 1) / bn) * g.groups * (is_dx ? p.sph * p.spw : 1);
       const double eff = bn == 256 ? 1.0 : (bn == 128 ? 0.85 : 0.55);
       const double cost = (double)div_up64(tiles, sm_count()) * bn / eff;
       if (!p.ok || cost < best_cost) {
@@ -560,14 +622,15 @@ int strip_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* b
   const StripPlan plan = plan_strip(g, is_dx);
   if (!plan.ok) return fail(B200_EUNSUPPORTED, "strip kernel does not take this geometry");
   const int kc = is_dx ? g.cog : g.cig, nc = is_dx ? g.cig : g.cog;
-  const int tiles_n = (nc + plan.bn - 1) / plan.bn;
-  const long long wcount = (long long)g.groups * tiles_n * plan.bn * kc * g.kh * g.kw;  // per plane
+  const int tiles_pp = (nc + plan.bn - 1) / plan.bn;  // column tiles (per output phase in dInput)
+  const int tiles_n = is_dx ? tiles_pp * plan.tt.n_phase : tiles_pp;
+  const long long wcount = (long long)g.groups * tiles_pp * plan.bn * kc * g.kh * g.kw;  // per plane
   const float* wp = staged_images;
   if (!wp) {
     if (!ws || ws_bytes < 2 * sizeof(float) * (size_t)wcount || (reinterpret_cast<uintptr_t>(ws) & 15))
       return fail(B200_EWORKSPACE, "tcgen05 convolution needs a 16-byte aligned workspace of %zu bytes (got %zu)",
                   2 * sizeof(float) * (size_t)wcount, ws_bytes);
-    stage_weights_kernel<<<(unsigned)div_up64(wcount, 256), 256, 0, st>>>(g, w, is_dx ? 1 : 0, plan.bn, tiles_n, plan.tt, (float*)ws, wcount);
+    stage_weights_kernel<<<(unsigned)div_up64(wcount, 256), 256, 0, st>>>(g, w, is_dx ? 1 : 0, plan.bn, tiles_pp, plan.tt, (float*)ws, wcount);
     count_launch();
     if (int rc = launch_check("stage_weights_kernel")) return rc;
     wp = (const float*)ws;
@@ -577,21 +640,32 @@ int strip_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* b
   a.g = g; a.act = act; a.wp = wp; a.bias = is_dx ? nullptr : bias; a.bias_stride = bias_stride; a.out = out;
   a.H = plan.gh; a.W = plan.gw; a.pr = plan.pr; a.pc = plan.pc;
   a.act_h = plan.act_h; a.act_w = plan.act_w; a.out_h = plan.out_h; a.out_w = plan.out_w;
-  a.sph = plan.sph; a.spw = plan.spw;
+  a.sph = is_dx ? 1 : plan.sph; a.spw = is_dx ? 1 : plan.spw;
+  a.osh = is_dx ? plan.sph : 1; a.osw = is_dx ? plan.spw : 1;
+  a.phase_on_n = is_dx ? 1 : 0;
+  a.tiles_pp = tiles_pp;
   a.tt = plan.tt;
   a.kc = kc;
   a.nc = nc;
   a.out_channels = is_dx ? g.cin : g.cout;
   a.cb_per_phase = kc / KBLK;
-  a.cblocks = plan.tt.n_phase * a.cb_per_phase;
+  a.cblocks = (is_dx ? 1 : plan.tt.n_phase) * a.cb_per_phase;
   a.images_per_tile = a.cb_per_phase * plan.tt.taps_total;
   a.tiles_n = tiles_n;
   a.q_total = (int)((long long)g.n * (a.H + a.pr) * (a.W + a.pc));
   a.img_div = FastDiv((uint32_t)((a.H + a.pr) * (a.W + a.pc)));
   a.row_div = FastDiv((uint32_t)(a.W + a.pc));
-  a.tiles_m = div_up64(a.q_total, BLOCK_M);
-  a.tiles_total = a.tiles_m * a.tiles_n * g.groups;
+  a.tiles_m = (int)div_up64(a.q_total, BLOCK_M);
   a.halo = plan.halo; a.strip_rows = plan.strip_rows; a.a_stages = plan.a_stages; a.w_stages = plan.w_stages;
+  const int chunks = (a.strip_rows + 31) / 32;
+  const long long tiles_total = (long long)a.tiles_m * a.tiles_n * g.groups;
+  if (tiles_total * a.cblocks * chunks > 2147483647ll - (1 << 20))
+    return fail(B200_EUNSUPPORTED, "strip kernel: tile count exceeds 32-bit job indices");
+  a.tiles_total = (int)tiles_total;
+  a.div_tiles_n = FastDiv((uint32_t)a.tiles_n); a.div_tiles_m = FastDiv((uint32_t)a.tiles_m);
+  a.div_tiles_pp = FastDiv((uint32_t)a.tiles_pp); a.div_chunks = FastDiv((uint32_t)chunks);
+  a.div_cblocks = FastDiv((uint32_t)a.cblocks); a.div_cbpp = FastDiv((uint32_t)a.cb_per_phase);
+  a.div_a_stages = FastDiv((uint32_t)a.a_stages);
   a.out_rowmajor = rowmajor ? 1 : 0;
   a.alpha = alpha; a.beta = beta;
   a.out_vec4 = rowmajor && a.out_channels % 4 == 0 && plan.bn % 4 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 && a.nc % 4 == 0;
@@ -603,9 +677,11 @@ int strip_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* b
   if (profiling) {
     if (!prof_buf) B200_CUDA(cudaMalloc(&prof_buf, 16 * sizeof(unsigned long long)));
     B200_CUDA(cudaMemsetAsync(prof_buf, 0, 16 * sizeof(unsigned long long), st));
+    B200_CUDA(cudaMemsetAsync(prof_buf + 11, 0xFF, sizeof(unsigned long long), st));
+    B200_CUDA(cudaMemsetAsync(prof_buf + 14, 0xFF, sizeof(unsigned long long), st));
     a.prof = prof_buf;
   }
-  const int grid = (int)std::min<long long>(a.tiles_total, sm_count());
+  const int grid = std::min(a.tiles_total, sm_count());
   if (profiling) {
     const int rc = plan.bn == 64 ? launch_strip<64>(a, grid, plan.smem, st)
                  : plan.bn == 128 ? launch_strip<128>(a, grid, plan.smem, st) : launch_strip<256>(a, grid, plan.smem, st);
@@ -613,8 +689,8 @@ int strip_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* b
     B200_CUDA(cudaStreamSynchronize(st));
     B200_CUDA(cudaMemcpy(h, prof_buf, sizeof h, cudaMemcpyDeviceToHost));
     fprintf(stderr, "[strip profile, CTA 0, cycles] bn=%d a_stages=%d w_stages=%d tiles=%llu | mma: wait_acc %llu wait_a %llu wait_w %llu issue %llu | "
-            "w: wait_empty %llu convert %llu | a: wait_empty %llu stage_total %llu | epi: wait_acc %llu drain %llu\n",
-            plan.bn, plan.a_stages, plan.w_stages, h[10], h[0], h[1], h[2], h[3], h[4], h[5], h[6], h[7], h[8], h[9]);
+            "w: wait_empty %llu convert %llu | a: wait_empty %llu stage_total %llu | epi: wait_acc %llu drain %llu | ns: CTA starts spread %llu, first start to last end %llu, CTA lifetime min %llu max %llu\n",
+            plan.bn, plan.a_stages, plan.w_stages, h[10], h[0], h[1], h[2], h[3], h[4], h[5], h[6], h[7], h[8], h[9], h[12] - h[11], h[13] - h[11], h[14], h[15]);
     return rc;
   }
   if (plan.bn == 64) return launch_strip<64>(a, grid, plan.smem, st);

@@ -73,12 +73,17 @@ def test_tc_matches_golden_layer64():
     ((2, 64, 9, 9), 512, (1, 1), dict()),                         # two column tiles of 256
     ((2, 32, 10, 11), 32, (2, 2), dict(stride=(3, 3))),           # input pixels that no filter tap reaches
     ((2, 32, 13, 12), 64, (3, 3), dict(stride=(2, 3), padding=(1, 0), dilation=(2, 1))),
+    ((2, 64, 14, 14), 64, (1, 1), dict(stride=(2, 2))),           # dInput phases that receive no tap (zero-filled)
+    ((2, 32, 12, 12), 32, (3, 3), dict()),                        # no padding: output smaller than the pixel grid
+    ((2, 32, 9, 10), 32, (3, 3), dict(padding=(2, 2))),           # more padding than the filter needs
+    ((2, 64, 16, 16), 32, (4, 4), dict(stride=(2, 2), padding=(1, 1))),
+    ((1, 32, 17, 19), 64, (3, 3), dict(stride=(3, 2), padding=(0, 2))),
 ], ids=lambda s: "x".join(map(str, s[0])) + f"-co{s[1]}-k{s[2][0]}x{s[2][1]}" if isinstance(s, tuple) and len(s) == 4 else None)
 @pytest.mark.parametrize("channels_last", [False, True], ids=["nchw", "nhwc"])
 @pytest.mark.parametrize("variant", ["strip", "gather"])
 def test_tc_forward_and_dinput_shapes(shape, channels_last, variant, monkeypatch):
-    # "gather" pins the per-tap gather kernel; "strip" lets the persistent strip kernel take the
-    # stride-1 same-size geometries (the others run the gather kernel either way)
+    # "gather" pins the per-tap gather kernel; "strip" lets the persistent strip kernel take every
+    # geometry whose reduction channels come in blocks of 32 (the others run the gather kernel either way)
     monkeypatch.setenv("B200_CONV_TC_VARIANT", variant)
     xshape, cout, kernel, kw = shape
     groups = kw.get("groups", 1)

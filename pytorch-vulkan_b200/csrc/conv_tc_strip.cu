@@ -81,7 +81,8 @@ struct StripArgs {
   int q_total;            // grid pixels incl. padding (below 2^31 - 2^20)
   FastDiv img_div, row_div;
   int tiles_m, tiles_total;
-  FastDiv div_tiles_n, div_tiles_m, div_tiles_pp, div_chunks, div_cblocks, div_cbpp, div_a_stages;
+  int unit, units;        // tiles per scheduling unit, number of units (tiles_total = unit * units)
+  FastDiv div_tiles_n, div_tiles_m, div_tiles_pp, div_chunks, div_cblocks, div_cbpp, div_a_stages, div_unit;
   int halo, strip_rows;   // rows staged before the tile's first pixel; strip_rows is a multiple of 8
   int a_stages, w_stages;
   int out_rowmajor;       // 0: NCHW planes.  1: [pixel][channel] rows (channels-last / GEMM C)
@@ -104,6 +105,18 @@ struct Ctrl {  // lives behind the operand stages in shared memory
 #define PROF_ON(leader) (a.prof != nullptr && blockIdx.x == 0 && (leader))
 #define PROF_T0(on) const long long prof_t0__ = (on) ? clock64() : 0
 #define PROF_ADD(on, slot) do { if (on) atomicAdd(a.prof + (slot), (unsigned long long)(clock64() - prof_t0__)); } while (0)
+
+// Tiles are dealt to CTAs in units of `unit` consecutive tiles, unit u to CTA u mod gridDim.  At any
+// moment the CTAs then work on neighbouring pixel rows (their strips share DRAM pages and L2 lines),
+// and with unit = all column tiles of a pixel-row tile a strided dInput gives every CTA the same mix
+// of output phases, whose tap counts differ.
+struct TileIter {
+  int u, t, unit, units, step;
+  __device__ explicit TileIter(const StripArgs& a) : u(blockIdx.x), t(0), unit(a.unit), units(a.units), step(gridDim.x) {}
+  __device__ bool valid() const { return u < units; }
+  __device__ int tile() const { return u * unit + t; }
+  __device__ void next() { if (++t == unit) { t = 0; u += step; } }
+};
 
 template <int BN>
 __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs a) {
@@ -170,7 +183,8 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
       uint32_t as = 0, a_par = 0, ws = 0, w_par = 0, t_count = 0;
       const bool pm = PROF_ON(true);
       bool alive = true;
-      for (int tile = blockIdx.x; tile < a.tiles_total && alive; tile += gridDim.x, ++t_count) {
+      for (TileIter it(a); it.valid() && alive; it.next(), ++t_count) {
+        const int tile = it.tile();
         const uint32_t ab = t_count & 1;
         { PROF_T0(pm);
         if (!mbar_wait(smem_u32(&ctrl->acc_empty[ab]), ((t_count >> 1) & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_ACCUM)) break;
@@ -228,7 +242,8 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
       uint32_t ws = 0, w_par = 1, issued = 0;
       bool alive = true;
       const bool pw = PROF_ON(true);
-      for (int tile = blockIdx.x; tile < a.tiles_total && alive; tile += gridDim.x) {
+      for (TileIter it(a); it.valid() && alive; it.next()) {
+        const int tile = it.tile();
         const int tn = (int)a.div_tiles_n.div((uint32_t)tile), n_tile = tile - tn * a.tiles_n;
         const long long group = a.div_tiles_m.div((uint32_t)tn);
         long long first_image;
@@ -268,7 +283,8 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
     const int chunks = (a.strip_rows + 31) / 32;
     const bool vec_ok = a.act.s1 == 1 && ((reinterpret_cast<uintptr_t>(a.act.ptr) & 15) == 0) &&
                         (a.act.s0 % 4 == 0) && (a.act.s2 % 4 == 0) && (a.act.s3 % 4 == 0);
-    const int my_tiles = a.tiles_total > (int)blockIdx.x ? (a.tiles_total - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+    const int my_units = a.units > (int)blockIdx.x ? (a.units - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+    const int my_tiles = my_units * a.unit;
     const int total_jobs = my_tiles * a.cblocks * chunks;  // below 2^31 (checked by the host)
     // A warp's consecutive jobs must not be more than a_stages stages apart: a waiter that skips a
     // whole phase of a stage's mbarrier would see the parity of an older phase and run ahead.
@@ -278,7 +294,8 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
       const int chunk = job - (int)a_count * chunks;
       const uint32_t tile_iter = a.div_cblocks.div(a_count);
       const int cb = (int)(a_count - tile_iter * a.cblocks);
-      const uint32_t tile = blockIdx.x + tile_iter * gridDim.x;
+      const uint32_t unit_iter = a.div_unit.div(tile_iter);
+      const uint32_t tile = (blockIdx.x + unit_iter * gridDim.x) * a.unit + (tile_iter - unit_iter * a.unit);
       const uint32_t tn = a.div_tiles_n.div(tile);
       const int group = (int)a.div_tiles_m.div(tn);
       const int m_tile = (int)tn - group * (int)a.tiles_m;
@@ -340,7 +357,8 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
     const int quarter = warp & 3, half = warp >> 2;
     constexpr int HALVES = EPI_WARPS / 4;
     uint32_t t_count = 0;
-    for (int tile = blockIdx.x; tile < a.tiles_total; tile += gridDim.x, ++t_count) {
+    for (TileIter it(a); it.valid(); it.next(), ++t_count) {
+      const int tile = it.tile();
       const int tn = (int)a.div_tiles_n.div((uint32_t)tile), n_tile = tile - tn * a.tiles_n;
       const int group = (int)a.div_tiles_m.div((uint32_t)tn);
       const int m_tile = tn - group * (int)a.tiles_m;
@@ -662,6 +680,10 @@ int strip_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* b
   if (tiles_total * a.cblocks * chunks > 2147483647ll - (1 << 20))
     return fail(B200_EUNSUPPORTED, "strip kernel: tile count exceeds 32-bit job indices");
   a.tiles_total = (int)tiles_total;
+  // units of all column tiles of a pixel-row tile while that still leaves every SM two or more units
+  a.unit = (tiles_total / a.tiles_n >= 2ll * sm_count()) ? a.tiles_n : 1;
+  a.units = a.tiles_total / a.unit;
+  a.div_unit = FastDiv((uint32_t)a.unit);
   a.div_tiles_n = FastDiv((uint32_t)a.tiles_n); a.div_tiles_m = FastDiv((uint32_t)a.tiles_m);
   a.div_tiles_pp = FastDiv((uint32_t)a.tiles_pp); a.div_chunks = FastDiv((uint32_t)chunks);
   a.div_cblocks = FastDiv((uint32_t)a.cblocks); a.div_cbpp = FastDiv((uint32_t)a.cb_per_phase);
@@ -681,7 +703,7 @@ int strip_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* b
     B200_CUDA(cudaMemsetAsync(prof_buf + 14, 0xFF, sizeof(unsigned long long), st));
     a.prof = prof_buf;
   }
-  const int grid = std::min(a.tiles_total, sm_count());
+  const int grid = std::min(a.units, sm_count());
   if (profiling) {
     const int rc = plan.bn == 64 ? launch_strip<64>(a, grid, plan.smem, st)
                  : plan.bn == 128 ? launch_strip<128>(a, grid, plan.smem, st) : launch_strip<256>(a, grid, plan.smem, st);

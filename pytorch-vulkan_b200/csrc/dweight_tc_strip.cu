@@ -47,7 +47,7 @@ struct DwStripArgs {
   float* out;            // dW (one split) or the partial buffer [split][cout][cig*taps]
   int H, W, pr, pc;      // padded pixel space (see conv_tc_strip.cu)
   int q_total;           // padded pixels (below 2^31 - 64)
-  FastDiv img_div, row_div;
+  FastDiv img_div, row_div, div_tasks, div_stages;
   int span, splits;      // padded pixels per split (multiple of KP)
   int xblocks;           // staged input blocks per CTA: 1 (taps in M) or 4 (1x1: channel blocks in M)
   int ci_tiles, co_tiles;
@@ -197,56 +197,59 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
   const int yshift = (ky * g.dh - g.ph) * row_pitch;
 
   if (warp == MMA_WARP) {
-    constexpr uint32_t idesc = make_idesc_tf32(128, BN) | (1u << 15) | (1u << 16);  // both operands MN-major
-    constexpr uint32_t idesc_wide = make_idesc_tf32(128, FUSE_HILO ? 2 * BN : BN) | (1u << 15) | (1u << 16);
-    const uint32_t a_lbo = a.xblocks == 1 ? (uint32_t)g.dw * 128u : 2u * x_plane;
-    for (int kb = 0; kb < kblocks; ++kb) {
-      const int s = kb % a.stages;
-      const bool pm = DPROF_ON(lane == 0);
-      { DPROF_T0(pm);
-      if (!mbar_wait(smem_u32(&ctrl->full[s]), (uint32_t)(kb / a.stages) & 1, abort_flag, a.status, STATUS_TIMEOUT_FULL)) break;
-      DPROF_ADD(pm, 0); }
-      tc_fence_after();
-      DPROF_T0(pm);
-      if (lane == 0) {
-        const uint32_t xs = base + s * stage_bytes, ys = xs + x_bytes;
-        // input rows start at the pixel shifted by -pad_w; hi plane then lo plane of each block
-        const uint32_t a_hi = xs + (uint32_t)(XOFF - g.pw) * 128u, a_lo = a_hi + x_plane;
-        const uint32_t b_hi = ys, b_lo = ys + y_plane;
+    // One thread; stage indices are counted and descriptors are base + offset, because everything
+    // this thread does between two tcgen05.mma is idle time of the tensor pipe.
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_tf32(128, BN) | (1u << 15) | (1u << 16);  // both operands MN-major
+      constexpr uint32_t idesc_wide = make_idesc_tf32(128, FUSE_HILO ? 2 * BN : BN) | (1u << 15) | (1u << 16);
+      const uint32_t a_lbo = a.xblocks == 1 ? (uint32_t)g.dw * 128u : 2u * x_plane;
+      // input rows start at the pixel shifted by -pad_w; hi plane then lo plane of each block
+      const uint64_t da_base = make_mn_desc(base + (uint32_t)(XOFF - g.pw) * 128u, a_lbo);
+      const uint64_t db_base = make_mn_desc(base + x_bytes, KP * 128u);
+      const uint32_t stage_d = stage_bytes >> 4, x_plane_d = x_plane >> 4;
+      constexpr uint32_t y_plane_d = y_plane >> 4;
+      const bool pm = DPROF_ON(true);
+      uint32_t s = 0, par = 0;
+      for (int kb = 0; kb < kblocks; ++kb) {
+        { DPROF_T0(pm);
+        if (!mbar_wait(smem_u32(&ctrl->full[s]), par, abort_flag, a.status, STATUS_TIMEOUT_FULL)) break;
+        DPROF_ADD(pm, 0); }
+        tc_fence_after();
+        DPROF_T0(pm);
+        const uint64_t da_hi = da_base + s * stage_d, da_lo = da_hi + x_plane_d;
+        const uint64_t db_hi = db_base + s * stage_d, db_lo = db_hi + y_plane_d;
 #pragma unroll
-        for (int kg = 0; kg < KP / 8; ++kg) {
-          const uint64_t da_hi = make_mn_desc(a_hi + kg * 1024u, a_lbo), da_lo = make_mn_desc(a_lo + kg * 1024u, a_lbo);
-          const uint64_t db_hi = make_mn_desc(b_hi + kg * 1024u, KP * 128u), db_lo = make_mn_desc(b_lo + kg * 1024u, KP * 128u);
+        for (int kg = 0; kg < KP / 8; ++kg) {  // 8 pixels = 8 rows of 128 bytes per MMA
           if (FUSE_HILO) {
-            umma_tf32(tmem_acc, da_hi, db_hi, idesc_wide, (kb | kg) != 0);
-            umma_tf32(tmem_acc, da_lo, db_hi, idesc, 1);
+            umma_tf32(tmem_acc, da_hi + kg * 64, db_hi + kg * 64, idesc_wide, (kb | kg) != 0);
+            umma_tf32(tmem_acc, da_lo + kg * 64, db_hi + kg * 64, idesc, 1);
           } else {
-            umma_tf32(tmem_acc, da_lo, db_hi, idesc, (kb | kg) != 0);
-            umma_tf32(tmem_acc, da_hi, db_lo, idesc, 1);
-            umma_tf32(tmem_acc, da_hi, db_hi, idesc, 1);
+            umma_tf32(tmem_acc, da_lo + kg * 64, db_hi + kg * 64, idesc, (kb | kg) != 0);
+            umma_tf32(tmem_acc, da_hi + kg * 64, db_lo + kg * 64, idesc, 1);
+            umma_tf32(tmem_acc, da_hi + kg * 64, db_hi + kg * 64, idesc, 1);
           }
         }
         umma_commit(smem_u32(&ctrl->empty[s]));
+        if (++s == (uint32_t)a.stages) { s = 0; par ^= 1; }
+        DPROF_ADD(pm, 1);
       }
-      __syncwarp();
-      DPROF_ADD(pm, 1);
+      umma_commit(smem_u32(&ctrl->accum));
     }
-    if (lane == 0) umma_commit(smem_u32(&ctrl->accum));
-    __syncwarp();
   } else {
     // ---- producers: job j of K block kb goes to warp (kb*tasks + j) % 16 ----
     const bool x_vec = a.x.s1 == 1 && ((reinterpret_cast<uintptr_t>(a.x.ptr) & 15) == 0) && a.x.s0 % 4 == 0 &&
                        a.x.s2 % 4 == 0 && a.x.s3 % 4 == 0;
     const bool y_vec = a.dy.s1 == 1 && ((reinterpret_cast<uintptr_t>(a.dy.ptr) & 15) == 0) && a.dy.s0 % 4 == 0 &&
                        a.dy.s2 % 4 == 0 && a.dy.s3 % 4 == 0;
-    const long long total_jobs = (long long)kblocks * tasks;
+    const int total_jobs = kblocks * tasks;  // kblocks <= 2^26, tasks <= 16
     // consecutive jobs of a warp stay within `stages` K blocks of each other (a waiter that skipped
     // a whole phase of a stage's mbarrier would see the parity of an older phase and run ahead)
     const int warps_active = min(PRODUCER_WARPS, tasks * a.stages);
     bool alive = warp < warps_active;
-    for (long long job = warp; job < total_jobs && alive; job += warps_active) {
-      const int kb = (int)(job / tasks), j = (int)(job - (long long)kb * tasks);
-      const int s = kb % a.stages;
+    for (int job = warp; job < total_jobs && alive; job += warps_active) {
+      const int kb = (int)a.div_tasks.div((uint32_t)job), j = job - kb * tasks;
+      const uint32_t round = a.div_stages.div((uint32_t)kb);
+      const int s = kb - (int)round * a.stages;
       const int k0 = k_begin + kb * KP;
       const uint32_t xs = base + s * stage_bytes, ys = xs + x_bytes;
       float val[32];
@@ -279,7 +282,7 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
       }
       DPROF_ADD(pp, 2);
       { const long long tw = pp ? clock64() : 0;
-      if (!mbar_wait(smem_u32(&ctrl->empty[s]), ((uint32_t)(kb / a.stages) & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_EMPTY)) { alive = false; break; }
+      if (!mbar_wait(smem_u32(&ctrl->empty[s]), (round & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_EMPTY)) { alive = false; break; }
       if (pp) atomicAdd(a.prof + 3, (unsigned long long)(clock64() - tw)); }
       { const long long tw = pp ? clock64() : 0;
       store_block(val, rows, row0, p_hi, p_lo, lane);
@@ -406,6 +409,8 @@ int dweight_strip(const ConvGeom& g, View4 x, View4 dy, float* dw, void* ws, siz
   a.row_div = FastDiv((uint32_t)(a.W + a.pc));
   a.span = plan.span; a.splits = plan.splits; a.xblocks = plan.xblocks;
   a.ci_tiles = plan.ci_tiles; a.co_tiles = plan.co_tiles; a.stages = plan.stages;
+  a.div_tasks = FastDiv((uint32_t)(plan.xblocks * 2 + plan.bn / 32));
+  a.div_stages = FastDiv((uint32_t)plan.stages);
   a.out = plan.splits > 1 ? (float*)ws : dw;
   a.status = device_status_word();
   if (!a.status) return fail(B200_ECUDA, "device status word is not allocated");

@@ -49,7 +49,13 @@ struct DwStripArgs {
   int q_total;           // padded pixels (below 2^31 - 64)
   FastDiv img_div, row_div, div_tasks, div_stages;
   int span, splits;      // padded pixels per split (multiple of KP)
-  int xblocks;           // staged input blocks per CTA: 1 (taps in M) or 4 (1x1: channel blocks in M)
+  int xblocks;           // staged input blocks per CTA: 1 (one strip, taps in M through the block stride) or 4
+  int xr;                // rows staged per input block: XR (strip with tap margin) or KP (exact blocks)
+  int blocks_are_taps;   // xblocks == 4: block j is tap kx = j of one channel block (strided filters) rather than
+                         // channel block j of a 1x1 filter
+  int sph, spw;          // stride: grid pixel (r, c) of phase (a, b) is the input pixel (r*sph + a, c*spw + b)
+  int in_h, in_w, out_h, out_w;  // extents of x and of dY (the grid H x W covers both)
+  unsigned blk_b, blk_dc;        // per tap kx: column phase and whole-pixel column offset (signed), 8 bits each
   int ci_tiles, co_tiles;
   int stages;
   int* status;
@@ -91,7 +97,9 @@ __device__ __forceinline__ uint64_t make_mn_desc(uint32_t addr, uint32_t lbo) {
 // swapped lanes already LOAD their channels in swapped order: val[j] holds channel j ^ 4 there.
 __device__ __forceinline__ void stage_block(const View4& v, long long chan0, int chans, int H, int W, int row_pitch,
                                             int img_pitch, const FastDiv& img_div, const FastDiv& row_div, int q_first,
-                                            int q_lo, int q_hi, int rows, int lane, bool vec_ok, float (&val)[32]) {
+                                            int q_lo, int q_hi, int rows, int lane, bool vec_ok, float (&val)[32],
+                                            int sph = 1, int spw = 1, int pa = 0, int pb = 0, int lim_h = 1 << 30,
+                                            int lim_w = 1 << 30) {
   const int q = q_first + lane;
   bool ok = lane < rows && q >= q_lo && q < q_hi;
   const float* src = v.ptr;
@@ -99,8 +107,9 @@ __device__ __forceinline__ void stage_block(const View4& v, long long chan0, int
     const int n = (int)img_div.div((uint32_t)q);
     const int rem = q - n * img_pitch;
     const int y = (int)row_div.div((uint32_t)rem), x = rem - y * row_pitch;
-    ok = y < H && x < W;
-    src += n * v.s0 + chan0 * v.s1 + (long long)y * v.s2 + (long long)x * v.s3;
+    const int ty = y * sph + pa, tx = x * spw + pb;  // position in the tensor
+    ok = y < H && x < W && ty < lim_h && tx < lim_w;
+    src += n * v.s0 + chan0 * v.s1 + (long long)ty * v.s2 + (long long)tx * v.s3;
   }
   const int sw = (lane >> 2) & 1;
   if (ok && chans == 32) {
@@ -151,13 +160,14 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   constexpr int NB = BN / 32;                                  // dY blocks per stage
-  const uint32_t x_plane = XR * 128u, x_bytes = (uint32_t)a.xblocks * 2u * x_plane;
+  const uint32_t x_plane = (uint32_t)a.xr * 128u, x_bytes = (uint32_t)a.xblocks * 2u * x_plane;
   constexpr uint32_t y_plane = NB * KP * 128u;                 // all dY blocks of one plane
   const uint32_t stage_bytes = x_bytes + 2u * y_plane;
   Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem_raw + (base - raw) + a.stages * stage_bytes);
   volatile int* abort_flag = &ctrl->abort_flag;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int x_tasks = a.xblocks * 2;                           // an input block = rows 0..31 and 32..47
+  const int x_halves = a.xr > 32 ? 2 : 1;                      // a strip = rows 0..31 and 32..47; an exact block = 32 rows
+  const int x_tasks = a.xblocks * x_halves;
   const int tasks = x_tasks + NB;                              // warp-sized staging jobs per K block
   // BN <= 128: the dY hi and lo planes (their 32-channel blocks are equally spaced) form ONE operand
   // of 2*BN columns, so x_hi*[dy_hi | dy_lo] is a single MMA; the epilogue adds the two halves.
@@ -186,7 +196,7 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
   const int co_tile = id % a.co_tiles; id /= a.co_tiles;
   const int group = id;
   const int split = blockIdx.y;
-  const int ci_per_tile = a.xblocks * 32;
+  const int ci_per_tile = a.blocks_are_taps ? 32 : a.xblocks * 32;
   const int ci0 = ci_tile * ci_per_tile, co0 = co_tile * BN;
   const int cols_valid = min(BN, g.cog - co0);
   const int row_pitch = a.W + a.pc;
@@ -194,7 +204,10 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
   const int k_begin = split * a.span;  // < q_total
   const int k_end = a.q_total - k_begin > a.span ? k_begin + a.span : a.q_total;
   const int kblocks = (k_end - k_begin + KP - 1) / KP;
-  const int yshift = (ky * g.dh - g.ph) * row_pitch;
+  // vertical tap: input row sph*(r + dr) + pa
+  const int oy = ky * g.dh - g.ph;
+  const int dr = oy >= 0 ? oy / a.sph : -((-oy + a.sph - 1) / a.sph), pa = oy - dr * a.sph;
+  const int yshift = dr * row_pitch;
 
   if (warp == MMA_WARP) {
     // One thread; stage indices are counted and descriptors are base + offset, because everything
@@ -204,7 +217,7 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
       constexpr uint32_t idesc_wide = make_idesc_tf32(128, FUSE_HILO ? 2 * BN : BN) | (1u << 15) | (1u << 16);
       const uint32_t a_lbo = a.xblocks == 1 ? (uint32_t)g.dw * 128u : 2u * x_plane;
       // input rows start at the pixel shifted by -pad_w; hi plane then lo plane of each block
-      const uint64_t da_base = make_mn_desc(base + (uint32_t)(XOFF - g.pw) * 128u, a_lbo);
+      const uint64_t da_base = make_mn_desc(base + (a.xblocks == 1 ? (uint32_t)(XOFF - g.pw) * 128u : 0u), a_lbo);
       const uint64_t db_base = make_mn_desc(base + x_bytes, KP * 128u);
       const uint32_t stage_d = stage_bytes >> 4, x_plane_d = x_plane >> 4;
       constexpr uint32_t y_plane_d = y_plane >> 4;
@@ -258,16 +271,26 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
       const bool pp = DPROF_ON(threadIdx.x == 0);
       DPROF_T0(pp);
       if (j < x_tasks) {
-        const int blk = j >> 1, half = j & 1;
+        const int blk = x_halves == 2 ? j >> 1 : j, half = x_halves == 2 ? j & 1 : 0;
         rows = half ? XR - 32 : 32;
         row0 = half * 32;
         p_hi = xs + (uint32_t)blk * 2u * x_plane;
         p_lo = p_hi + x_plane;
-        const int c0 = ci0 + blk * 32;
-        const int chans = max(0, min(32, g.cig - c0));
-        // the input is needed wherever it exists: no split-range clipping, only image bounds
-        stage_block(a.x, (long long)group * g.cig + c0, chans, a.H, a.W, row_pitch, img_pitch, a.img_div, a.row_div,
-                    k0 + yshift - XOFF + row0, 0, a.q_total, rows, lane, x_vec, val);
+        if (a.xblocks == 1) {
+          // one strip; the horizontal taps are its row offsets.  The input is needed wherever it
+          // exists: no split-range clipping, only image bounds
+          const int chans = max(0, min(32, g.cig - ci0));
+          stage_block(a.x, (long long)group * g.cig + ci0, chans, a.H, a.W, row_pitch, img_pitch, a.img_div, a.row_div,
+                      k0 + yshift - XOFF + row0, 0, a.q_total, rows, lane, x_vec, val);
+        } else {
+          // exact 32-pixel blocks: tap kx = blk of one channel block, or channel block blk of a 1x1 filter
+          const int c0 = ci0 + (a.blocks_are_taps ? 0 : blk * 32);
+          const int chans = (a.blocks_are_taps && blk >= g.kw) ? 0 : max(0, min(32, g.cig - c0));
+          const int pb = a.blocks_are_taps ? (int)((a.blk_b >> (8 * blk)) & 0xFFu) : 0;
+          const int dc = a.blocks_are_taps ? (int)(signed char)((a.blk_dc >> (8 * blk)) & 0xFFu) : 0;
+          stage_block(a.x, (long long)group * g.cig + c0, chans, a.H, a.W, row_pitch, img_pitch, a.img_div, a.row_div,
+                      k0 + yshift + dc, 0, a.q_total, rows, lane, x_vec, val, a.sph, a.spw, pa, pb, a.in_h, a.in_w);
+        }
       } else {
         const int blk = j - x_tasks;
         rows = 32;
@@ -278,7 +301,7 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
         const int chans = max(0, min(32, g.cog - c0));
         // dY outside this split's pixel range must read as zero so that splits do not overlap
         stage_block(a.dy, (long long)group * g.cog + c0, chans, a.H, a.W, row_pitch, img_pitch, a.img_div, a.row_div,
-                    k0, k_begin, k_end, rows, lane, y_vec, val);
+                    k0, k_begin, k_end, rows, lane, y_vec, val, 1, 1, 0, 0, a.out_h, a.out_w);
       }
       DPROF_ADD(pp, 2);
       { const long long tw = pp ? clock64() : 0;
@@ -299,8 +322,9 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
       const int taps = g.kh * g.kw;
       const long long cols = (long long)g.cig * taps;
       // block index: horizontal tap (taps-in-M mode) or channel block (1x1 mode)
-      const int kx = a.xblocks == 1 ? warp : 0;
-      const int ci = ci0 + (a.xblocks == 1 ? lane : warp * 32 + lane);
+      const bool taps_in_m = a.xblocks == 1 || a.blocks_are_taps;
+      const int kx = taps_in_m ? warp : 0;
+      const int ci = ci0 + (taps_in_m ? lane : warp * 32 + lane);
       const bool row_ok = kx < g.kw && ci < g.cig;
       float* out = a.out + ((long long)split * g.cout + (long long)group * g.cog + co0) * cols + (long long)ci * taps + ky * g.kw + kx;
 #pragma unroll 1
@@ -340,25 +364,54 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
 
 struct DwStripPlan {
   bool ok = false;
-  int bn = 0, xblocks = 1, stages = 0, smem = 0, ci_tiles = 0, co_tiles = 0, splits = 1, span = 0;
+  int bn = 0, xblocks = 1, xr = XR, blocks_are_taps = 0, stages = 0, smem = 0, ci_tiles = 0, co_tiles = 0, splits = 1, span = 0;
+  int gh = 0, gw = 0, pr = 0, pc = 0;  // pixel grid (covers dY and every phase sub-image of x) and its zero padding
+  unsigned blk_b = 0, blk_dc = 0;
   size_t bytes = 0;
 };
 
+static inline int floor_div(int a, int b) { return a >= 0 ? a / b : -((-a + b - 1) / b); }
+
+// Two arrangements of the M dimension (4 blocks of 32 rows):
+//   strip:  stride 1, output as large as the input, 2 <= kw <= 4 (or few channels): one staged input
+//           strip per K block, the horizontal taps are its row offsets;
+//   blocks: everything else with kw <= 4 -- strides, any padding, 1x1: four exact 32-pixel blocks per K
+//           block, either the taps kx = 0..3 of one channel block (each with its own column phase and
+//           offset) or, for a 1x1 filter, four channel blocks.
 static DwStripPlan plan_dw_strip(const ConvGeom& g, size_t budget) {
   DwStripPlan p;
-  if (g.sh != 1 || g.sw != 1 || g.oh != g.h || g.ow != g.w) return p;
-  if (2 * g.ph != g.dh * (g.kh - 1) || 2 * g.pw != g.dw * (g.kw - 1)) return p;
-  if (g.kw > 4 || g.pw > XOFF || 3 * g.dw - g.pw + XOFF + KP > XR) return p;
-  if (g.cog < 16 || g.cig < 16) return p;
-  p.xblocks = (g.kw == 1 && g.cig >= 64) ? 4 : 1;
+  if (g.kw > 4 || g.cog < 16 || g.cig < 16) return p;
+  const bool same = g.sh == 1 && g.sw == 1 && g.oh == g.h && g.ow == g.w && 2 * g.ph == g.dh * (g.kh - 1) &&
+                    2 * g.pw == g.dw * (g.kw - 1);
+  const bool strip_fits = same && g.pw <= XOFF && 3 * g.dw - g.pw + XOFF + KP <= XR;
+  const bool pointwise = same && g.kh == 1 && g.kw == 1;
+  if (strip_fits && !(pointwise && g.cig >= 64)) {
+    p.xblocks = 1; p.xr = XR;
+    p.gh = g.h; p.gw = g.w; p.pr = g.ph; p.pc = g.pw;
+  } else {
+    if (g.sh > 255 || g.sw > 255) return p;
+    p.xblocks = 4; p.xr = KP;
+    p.blocks_are_taps = pointwise ? 0 : 1;
+    p.gh = std::max(g.oh, (g.h + g.sh - 1) / g.sh);
+    p.gw = std::max(g.ow, (g.w + g.sw - 1) / g.sw);
+    for (int ky = 0; ky < g.kh; ++ky) p.pr = std::max(p.pr, std::abs(floor_div(ky * g.dh - g.ph, g.sh)));
+    for (int kx = 0; kx < g.kw; ++kx) {
+      const int ox = kx * g.dw - g.pw, dc = floor_div(ox, g.sw);
+      if (dc < -127 || dc > 127) return p;
+      p.pc = std::max(p.pc, std::abs(dc));
+      p.blk_b |= (unsigned)(ox - dc * g.sw) << (8 * kx);
+      p.blk_dc |= ((unsigned)dc & 0xFFu) << (8 * kx);
+    }
+  }
   p.bn = g.cog <= 64 ? 64 : (g.cog <= 128 ? 128 : 256);
-  const int stage = p.xblocks * 2 * XR * 128 + 2 * (p.bn / 32) * KP * 128;
+  const int stage = p.xblocks * 2 * p.xr * 128 + 2 * (p.bn / 32) * KP * 128;
   p.stages = std::min(MAX_STAGES, SMEM_LIMIT / stage);
   if (p.stages < 2) return p;
   p.smem = p.stages * stage + 1024 + (int)sizeof(Ctrl) + 64;
-  p.ci_tiles = (g.cig + p.xblocks * 32 - 1) / (p.xblocks * 32);
+  const int ci_per_tile = p.blocks_are_taps ? 32 : p.xblocks * 32;
+  p.ci_tiles = (g.cig + ci_per_tile - 1) / ci_per_tile;
   p.co_tiles = (g.cog + p.bn - 1) / p.bn;
-  const long long q_total = (long long)g.n * (g.h + g.ph) * (g.w + g.pw);
+  const long long q_total = (long long)g.n * (p.gh + p.pr) * (p.gw + p.pc);
   const long long tiles = (long long)p.ci_tiles * g.kh * p.co_tiles * g.groups;
   const size_t dw_bytes = sizeof(float) * (size_t)g.cout * g.cig * g.kh * g.kw;
   // two full waves of CTAs (one CTA per SM is resident), never a few CTAs more than that; every
@@ -403,13 +456,16 @@ int dweight_strip(const ConvGeom& g, View4 x, View4 dy, float* dw, void* ws, siz
   if (!plan.ok) return fail(B200_EUNSUPPORTED, "dWeight strip kernel does not take this geometry");
   DwStripArgs a{};
   a.g = g; a.x = x; a.dy = dy;
-  a.H = g.h; a.W = g.w; a.pr = g.ph; a.pc = g.pw;
+  a.H = plan.gh; a.W = plan.gw; a.pr = plan.pr; a.pc = plan.pc;
+  a.xr = plan.xr; a.blocks_are_taps = plan.blocks_are_taps;
+  a.sph = g.sh; a.spw = g.sw; a.in_h = g.h; a.in_w = g.w; a.out_h = g.oh; a.out_w = g.ow;
+  a.blk_b = plan.blk_b; a.blk_dc = plan.blk_dc;
   a.q_total = (int)((long long)g.n * (a.H + a.pr) * (a.W + a.pc));
   a.img_div = FastDiv((uint32_t)((a.H + a.pr) * (a.W + a.pc)));
   a.row_div = FastDiv((uint32_t)(a.W + a.pc));
   a.span = plan.span; a.splits = plan.splits; a.xblocks = plan.xblocks;
   a.ci_tiles = plan.ci_tiles; a.co_tiles = plan.co_tiles; a.stages = plan.stages;
-  a.div_tasks = FastDiv((uint32_t)(plan.xblocks * 2 + plan.bn / 32));
+  a.div_tasks = FastDiv((uint32_t)(plan.xblocks * (plan.xr > 32 ? 2 : 1) + plan.bn / 32));
   a.div_stages = FastDiv((uint32_t)plan.stages);
   a.out = plan.splits > 1 ? (float*)ws : dw;
   a.status = device_status_word();

@@ -50,6 +50,7 @@ struct DwStripArgs {
   FastDiv img_div, row_div, div_tasks, div_stages;
   int span, splits;      // padded pixels per split (multiple of KP)
   int xblocks;           // staged input blocks per CTA: 1 (one strip, taps in M through the block stride) or 4
+  int nacc;              // accumulators per CTA (strip arrangement: 1 or 2 channel blocks sharing the dY operand)
   int xr;                // rows staged per input block: XR (strip with tap margin) or KP (exact blocks)
   int blocks_are_taps;   // xblocks == 4: block j is tap kx = j of one channel block (strided filters) rather than
                          // channel block j of a 1x1 filter
@@ -156,23 +157,25 @@ __device__ __forceinline__ void store_block(const float (&val)[32], int rows, in
 template <int BN>
 __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStripArgs a) {
   extern __shared__ unsigned char smem_raw[];
+  const unsigned long long prof_start = a.prof ? global_ns() : 0;
   const ConvGeom& g = a.g;
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   constexpr int NB = BN / 32;                                  // dY blocks per stage
-  const uint32_t x_plane = (uint32_t)a.xr * 128u, x_bytes = (uint32_t)a.xblocks * 2u * x_plane;
+  const uint32_t x_plane = (uint32_t)a.xr * 128u, x_bytes = (uint32_t)(a.nacc * a.xblocks) * 2u * x_plane;
   constexpr uint32_t y_plane = NB * KP * 128u;                 // all dY blocks of one plane
   const uint32_t stage_bytes = x_bytes + 2u * y_plane;
   Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem_raw + (base - raw) + a.stages * stage_bytes);
   volatile int* abort_flag = &ctrl->abort_flag;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int x_halves = a.xr > 32 ? 2 : 1;                      // a strip = rows 0..31 and 32..47; an exact block = 32 rows
-  const int x_tasks = a.xblocks * x_halves;
+  const int x_tasks = a.nacc * a.xblocks * x_halves;
   const int tasks = x_tasks + NB;                              // warp-sized staging jobs per K block
   // BN <= 128: the dY hi and lo planes (their 32-channel blocks are equally spaced) form ONE operand
   // of 2*BN columns, so x_hi*[dy_hi | dy_lo] is a single MMA; the epilogue adds the two halves.
   constexpr bool FUSE_HILO = BN <= 128;
-  constexpr uint32_t TMEM_COLS = FUSE_HILO ? 2 * BN : BN;
+  constexpr uint32_t ACC_COLS = FUSE_HILO ? 2 * BN : BN;
+  const uint32_t tmem_cols = ACC_COLS * (uint32_t)a.nacc;  // 64..512, a power of two
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < MAX_STAGES; ++s) {
@@ -183,7 +186,7 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
     ctrl->abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp == MMA_WARP) tmem_alloc(smem_u32(&ctrl->tmem_base), TMEM_COLS);
+  if (warp == MMA_WARP) tmem_alloc(smem_u32(&ctrl->tmem_base), tmem_cols);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -196,7 +199,7 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
   const int co_tile = id % a.co_tiles; id /= a.co_tiles;
   const int group = id;
   const int split = blockIdx.y;
-  const int ci_per_tile = a.blocks_are_taps ? 32 : a.xblocks * 32;
+  const int ci_per_tile = a.blocks_are_taps ? 32 : a.nacc * a.xblocks * 32;
   const int ci0 = ci_tile * ci_per_tile, co0 = co_tile * BN;
   const int cols_valid = min(BN, g.cog - co0);
   const int row_pitch = a.W + a.pc;
@@ -229,17 +232,21 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
         DPROF_ADD(pm, 0); }
         tc_fence_after();
         DPROF_T0(pm);
-        const uint64_t da_hi = da_base + s * stage_d, da_lo = da_hi + x_plane_d;
+        const uint64_t da_hi = da_base + s * stage_d;
         const uint64_t db_hi = db_base + s * stage_d, db_lo = db_hi + y_plane_d;
+        for (int u = 0; u < a.nacc; ++u) {  // channel blocks that share this dY block
+          const uint32_t acc = tmem_acc + (uint32_t)u * ACC_COLS;
+          const uint64_t ua_hi = da_hi + (uint64_t)u * (2 * x_plane_d), ua_lo = ua_hi + x_plane_d;
 #pragma unroll
-        for (int kg = 0; kg < KP / 8; ++kg) {  // 8 pixels = 8 rows of 128 bytes per MMA
-          if (FUSE_HILO) {
-            umma_tf32(tmem_acc, da_hi + kg * 64, db_hi + kg * 64, idesc_wide, (kb | kg) != 0);
-            umma_tf32(tmem_acc, da_lo + kg * 64, db_hi + kg * 64, idesc, 1);
-          } else {
-            umma_tf32(tmem_acc, da_lo + kg * 64, db_hi + kg * 64, idesc, (kb | kg) != 0);
-            umma_tf32(tmem_acc, da_hi + kg * 64, db_lo + kg * 64, idesc, 1);
-            umma_tf32(tmem_acc, da_hi + kg * 64, db_hi + kg * 64, idesc, 1);
+          for (int kg = 0; kg < KP / 8; ++kg) {  // 8 pixels = 8 rows of 128 bytes per MMA
+            if (FUSE_HILO) {
+              umma_tf32(acc, ua_hi + kg * 64, db_hi + kg * 64, idesc_wide, (kb | kg) != 0);
+              umma_tf32(acc, ua_lo + kg * 64, db_hi + kg * 64, idesc, 1);
+            } else {
+              umma_tf32(acc, ua_lo + kg * 64, db_hi + kg * 64, idesc, (kb | kg) != 0);
+              umma_tf32(acc, ua_hi + kg * 64, db_lo + kg * 64, idesc, 1);
+              umma_tf32(acc, ua_hi + kg * 64, db_hi + kg * 64, idesc, 1);
+            }
           }
         }
         umma_commit(smem_u32(&ctrl->empty[s]));
@@ -279,8 +286,9 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
         if (a.xblocks == 1) {
           // one strip; the horizontal taps are its row offsets.  The input is needed wherever it
           // exists: no split-range clipping, only image bounds
-          const int chans = max(0, min(32, g.cig - ci0));
-          stage_block(a.x, (long long)group * g.cig + ci0, chans, a.H, a.W, row_pitch, img_pitch, a.img_div, a.row_div,
+          const int c0 = ci0 + blk * 32;  // strip blk of this CTA
+          const int chans = max(0, min(32, g.cig - c0));
+          stage_block(a.x, (long long)group * g.cig + c0, chans, a.H, a.W, row_pitch, img_pitch, a.img_div, a.row_div,
                       k0 + yshift - XOFF + row0, 0, a.q_total, rows, lane, x_vec, val);
         } else {
           // exact 32-pixel blocks: tap kx = blk of one channel block, or channel block blk of a 1x1 filter
@@ -316,25 +324,28 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
     // ---- epilogue (warps 0-3): lane = row of the accumulator = (block, channel) ----
     const bool pe = DPROF_ON(threadIdx.x == 0);
     DPROF_T0(pe);
-    if (warp < 4 && mbar_wait(smem_u32(&ctrl->accum), 0, abort_flag, a.status, STATUS_TIMEOUT_ACCUM)) {
+    // warp w reads TMEM lanes 32*(w & 3); warps 4-7 take the second accumulator
+    if (warp < 4 * a.nacc && mbar_wait(smem_u32(&ctrl->accum), 0, abort_flag, a.status, STATUS_TIMEOUT_ACCUM)) {
       DPROF_ADD(pe, 6);
       tc_fence_after();
       const int taps = g.kh * g.kw;
       const long long cols = (long long)g.cig * taps;
-      // block index: horizontal tap (taps-in-M mode) or channel block (1x1 mode)
+      const int quarter = warp & 3, u = warp >> 2;
+      // block index: horizontal tap (taps in M) or channel block (1x1 filter in the block arrangement)
       const bool taps_in_m = a.xblocks == 1 || a.blocks_are_taps;
-      const int kx = taps_in_m ? warp : 0;
-      const int ci = ci0 + (taps_in_m ? lane : warp * 32 + lane);
+      const int kx = taps_in_m ? quarter : 0;
+      const int ci = ci0 + u * 32 + (taps_in_m ? lane : quarter * 32 + lane);
       const bool row_ok = kx < g.kw && ci < g.cig;
       float* out = a.out + ((long long)split * g.cout + (long long)group * g.cog + co0) * cols + (long long)ci * taps + ky * g.kw + kx;
+      const uint32_t acc = tmem_acc + (uint32_t)u * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         if (c0 >= cols_valid) break;
         float v[32];
-        tmem_ld32(tmem_acc + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, v);
+        tmem_ld32(acc + (uint32_t)c0, v);
         if (FUSE_HILO) {
           float v2[32];
-          tmem_ld32(tmem_acc + ((uint32_t)(warp * 32) << 16) + (uint32_t)(BN + c0), v2);
+          tmem_ld32(acc + (uint32_t)(BN + c0), v2);
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] += v2[j];
         }
@@ -358,13 +369,21 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
   __syncthreads();
   if (warp == MMA_WARP) {
     tc_fence_after();
-    tmem_dealloc(tmem_acc, TMEM_COLS);
+    tmem_dealloc(tmem_acc, tmem_cols);
+  }
+  if (a.prof && threadIdx.x == 0) {  // spread of CTA start times and lifetimes (ns)
+    const unsigned long long now = global_ns();
+    atomicMin(a.prof + 11, prof_start);
+    atomicMax(a.prof + 12, prof_start);
+    atomicMax(a.prof + 13, now);
+    atomicMin(a.prof + 14, now - prof_start);
+    atomicMax(a.prof + 15, now - prof_start);
   }
 }
 
 struct DwStripPlan {
   bool ok = false;
-  int bn = 0, xblocks = 1, xr = XR, blocks_are_taps = 0, stages = 0, smem = 0, ci_tiles = 0, co_tiles = 0, splits = 1, span = 0;
+  int bn = 0, xblocks = 1, nacc = 1, xr = XR, blocks_are_taps = 0, stages = 0, smem = 0, ci_tiles = 0, co_tiles = 0, splits = 1, span = 0;
   int gh = 0, gw = 0, pr = 0, pc = 0;  // pixel grid (covers dY and every phase sub-image of x) and its zero padding
   unsigned blk_b = 0, blk_dc = 0;
   size_t bytes = 0;
@@ -403,12 +422,21 @@ static DwStripPlan plan_dw_strip(const ConvGeom& g, size_t budget) {
       p.blk_dc |= ((unsigned)dc & 0xFFu) << (8 * kx);
     }
   }
-  p.bn = g.cog <= 64 ? 64 : (g.cog <= 128 ? 128 : 256);
-  const int stage = p.xblocks * 2 * p.xr * 128 + 2 * (p.bn / 32) * KP * 128;
+  // Two channel blocks per CTA share every staged dY block (two accumulators in TMEM): the kernel is
+  // bound by the bytes its producers pull from L2, and this halves the dY bytes per MMA.  With two
+  // accumulators the column tile stays at 128 (TMEM holds 512 columns; four stages fit).
+  if (p.xblocks == 1 && g.cig >= 64) {
+    p.nacc = 2;
+    p.bn = g.cog <= 64 ? 64 : 128;
+  } else {
+    p.bn = g.cog <= 64 ? 64 : (g.cog <= 128 ? 128 : 256);
+  }
+  const int y_stage = 2 * (p.bn / 32) * KP * 128;
+  const int stage = p.nacc * p.xblocks * 2 * p.xr * 128 + y_stage;
   p.stages = std::min(MAX_STAGES, SMEM_LIMIT / stage);
   if (p.stages < 2) return p;
   p.smem = p.stages * stage + 1024 + (int)sizeof(Ctrl) + 64;
-  const int ci_per_tile = p.blocks_are_taps ? 32 : p.xblocks * 32;
+  const int ci_per_tile = p.blocks_are_taps ? 32 : p.nacc * p.xblocks * 32;
   p.ci_tiles = (g.cig + ci_per_tile - 1) / ci_per_tile;
   p.co_tiles = (g.cog + p.bn - 1) / p.bn;
   const long long q_total = (long long)g.n * (p.gh + p.pr) * (p.gw + p.pc);
@@ -457,7 +485,7 @@ int dweight_strip(const ConvGeom& g, View4 x, View4 dy, float* dw, void* ws, siz
   DwStripArgs a{};
   a.g = g; a.x = x; a.dy = dy;
   a.H = plan.gh; a.W = plan.gw; a.pr = plan.pr; a.pc = plan.pc;
-  a.xr = plan.xr; a.blocks_are_taps = plan.blocks_are_taps;
+  a.xr = plan.xr; a.blocks_are_taps = plan.blocks_are_taps; a.nacc = plan.nacc;
   a.sph = g.sh; a.spw = g.sw; a.in_h = g.h; a.in_w = g.w; a.out_h = g.oh; a.out_w = g.ow;
   a.blk_b = plan.blk_b; a.blk_dc = plan.blk_dc;
   a.q_total = (int)((long long)g.n * (a.H + a.pr) * (a.W + a.pc));
@@ -465,7 +493,7 @@ int dweight_strip(const ConvGeom& g, View4 x, View4 dy, float* dw, void* ws, siz
   a.row_div = FastDiv((uint32_t)(a.W + a.pc));
   a.span = plan.span; a.splits = plan.splits; a.xblocks = plan.xblocks;
   a.ci_tiles = plan.ci_tiles; a.co_tiles = plan.co_tiles; a.stages = plan.stages;
-  a.div_tasks = FastDiv((uint32_t)(plan.xblocks * (plan.xr > 32 ? 2 : 1) + plan.bn / 32));
+  a.div_tasks = FastDiv((uint32_t)(plan.nacc * plan.xblocks * (plan.xr > 32 ? 2 : 1) + plan.bn / 32));
   a.div_stages = FastDiv((uint32_t)plan.stages);
   a.out = plan.splits > 1 ? (float*)ws : dw;
   a.status = device_status_word();
@@ -481,6 +509,8 @@ int dweight_strip(const ConvGeom& g, View4 x, View4 dy, float* dw, void* ws, siz
   if (profiling) {
     if (!prof_buf) B200_CUDA(cudaMalloc(&prof_buf, 16 * sizeof(unsigned long long)));
     B200_CUDA(cudaMemsetAsync(prof_buf, 0, 16 * sizeof(unsigned long long), st));
+    B200_CUDA(cudaMemsetAsync(prof_buf + 11, 0xFF, sizeof(unsigned long long), st));
+    B200_CUDA(cudaMemsetAsync(prof_buf + 14, 0xFF, sizeof(unsigned long long), st));
     a.prof = prof_buf;
   }
   int rc = plan.bn == 64 ? launch_dw_strip<64>(a, grid, plan.smem, st)
@@ -491,8 +521,8 @@ int dweight_strip(const ConvGeom& g, View4 x, View4 dy, float* dw, void* ws, siz
     B200_CUDA(cudaStreamSynchronize(st));
     B200_CUDA(cudaMemcpy(h, prof_buf, sizeof h, cudaMemcpyDeviceToHost));
     fprintf(stderr, "[dweight strip profile, CTA 0, cycles] bn=%d xblocks=%d stages=%d grid=%lldx%d kblocks/cta=%d | mma: wait_full %llu issue %llu | "
-            "warp 0: jobs %llu load %llu wait_empty %llu store %llu | epilogue: wait_accum(total) %llu drain %llu\n",
-            plan.bn, plan.xblocks, plan.stages, gx, plan.splits, plan.span / KP, h[0], h[1], h[5], h[2], h[3], h[4], h[6], h[7]);
+            "warp 0: jobs %llu load %llu wait_empty %llu store %llu | epilogue: wait_accum(total) %llu drain %llu | ns: last CTA start %llu, first start to last end %llu, CTA lifetime min %llu max %llu\n",
+            plan.bn, plan.xblocks, plan.stages, gx, plan.splits, plan.span / KP, h[0], h[1], h[5], h[2], h[3], h[4], h[6], h[7], h[12] - h[11], h[13] - h[11], h[14], h[15]);
   }
   if (plan.splits > 1)
     return finalize_splits((const float*)ws, dw, (long long)g.cout * g.cig * g.kh * g.kw, plan.splits, st);

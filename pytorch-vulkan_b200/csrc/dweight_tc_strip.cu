@@ -50,6 +50,8 @@ struct DwStripArgs {
   FastDiv img_div, row_div, div_tasks, div_stages;
   int span, splits;      // padded pixels per split (multiple of KP)
   int xblocks;           // staged input blocks per CTA: 1 (one strip, taps in M through the block stride) or 4
+  int partial_layout;    // 1: `out` is the split buffer [split][cout][kh*kw][cig] (channel fastest, so the epilogue's
+                         // lanes store neighbouring floats); 0: dW itself, [cout][cig][kh*kw]
   int nacc;              // accumulators per CTA (strip arrangement: 1 or 2 channel blocks sharing the dY operand)
   int xr;                // rows staged per input block: XR (strip with tap margin) or KP (exact blocks)
   int blocks_are_taps;   // xblocks == 4: block j is tap kx = j of one channel block (strided filters) rather than
@@ -336,7 +338,8 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
       const int kx = taps_in_m ? quarter : 0;
       const int ci = ci0 + u * 32 + (taps_in_m ? lane : quarter * 32 + lane);
       const bool row_ok = kx < g.kw && ci < g.cig;
-      float* out = a.out + ((long long)split * g.cout + (long long)group * g.cog + co0) * cols + (long long)ci * taps + ky * g.kw + kx;
+      float* out = a.out + ((long long)split * g.cout + (long long)group * g.cog + co0) * cols +
+                   (a.partial_layout ? (long long)(ky * g.kw + kx) * g.cig + ci : (long long)ci * taps + ky * g.kw + kx);
       const uint32_t acc = tmem_acc + (uint32_t)u * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -379,6 +382,21 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
     atomicMin(a.prof + 14, now - prof_start);
     atomicMax(a.prof + 15, now - prof_start);
   }
+}
+
+// Sum the split partials [split][cout][taps][cig] in ascending split order (run-to-run identical)
+// and write dW[cout][cig][taps].  Threads follow the partial layout, so the reads, which are
+// `splits` times the writes, are coalesced.
+__global__ void __launch_bounds__(256) finalize_partials_kernel(const float* __restrict__ partial, float* __restrict__ dw,
+                                                               long long count, int splits, int cig, int taps) {
+  const long long i = blockIdx.x * 256ll + threadIdx.x;
+  if (i >= count) return;
+  float sum = 0.f;
+  for (int s = 0; s < splits; ++s) sum += partial[(long long)s * count + i];
+  const int ci = (int)(i % cig);
+  const int tap = (int)((i / cig) % taps);
+  const long long co = i / ((long long)cig * taps);
+  dw[(co * cig + ci) * taps + tap] = sum;
 }
 
 struct DwStripPlan {
@@ -496,6 +514,7 @@ int dweight_strip(const ConvGeom& g, View4 x, View4 dy, float* dw, void* ws, siz
   a.div_tasks = FastDiv((uint32_t)(plan.nacc * plan.xblocks * (plan.xr > 32 ? 2 : 1) + plan.bn / 32));
   a.div_stages = FastDiv((uint32_t)plan.stages);
   a.out = plan.splits > 1 ? (float*)ws : dw;
+  a.partial_layout = plan.splits > 1 ? 1 : 0;
   a.status = device_status_word();
   if (!a.status) return fail(B200_ECUDA, "device status word is not allocated");
   const long long gx = (long long)plan.ci_tiles * g.kh * plan.co_tiles * g.groups;
@@ -524,8 +543,13 @@ int dweight_strip(const ConvGeom& g, View4 x, View4 dy, float* dw, void* ws, siz
             "warp 0: jobs %llu load %llu wait_empty %llu store %llu | epilogue: wait_accum(total) %llu drain %llu | ns: last CTA start %llu, first start to last end %llu, CTA lifetime min %llu max %llu\n",
             plan.bn, plan.xblocks, plan.stages, gx, plan.splits, plan.span / KP, h[0], h[1], h[5], h[2], h[3], h[4], h[6], h[7], h[12] - h[11], h[13] - h[11], h[14], h[15]);
   }
-  if (plan.splits > 1)
-    return finalize_splits((const float*)ws, dw, (long long)g.cout * g.cig * g.kh * g.kw, plan.splits, st);
+  if (plan.splits > 1) {
+    const long long count = (long long)g.cout * g.cig * g.kh * g.kw;
+    finalize_partials_kernel<<<(unsigned)div_up64(count, 256), 256, 0, st>>>((const float*)ws, dw, count, plan.splits, g.cig,
+                                                                            g.kh * g.kw);
+    count_launch();
+    return launch_check("finalize_partials_kernel");
+  }
   return B200_OK;
 }
 

@@ -283,6 +283,7 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
     const int chunks = (a.strip_rows + 31) / 32;
     const bool vec_ok = a.act.s1 == 1 && ((reinterpret_cast<uintptr_t>(a.act.ptr) & 15) == 0) &&
                         (a.act.s0 % 4 == 0) && (a.act.s2 % 4 == 0) && (a.act.s3 % 4 == 0);
+    const bool chunked = vec_ok && a.act.s3 < 256;  // eight lanes per pixel (see below)
     const int my_units = a.units > (int)blockIdx.x ? (a.units - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
     const int my_tiles = my_units * a.unit;
     const int total_jobs = my_tiles * a.cblocks * chunks;  // below 2^31 (checked by the host)
@@ -317,10 +318,22 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
         src += n * a.act.s0 + ((long long)group * a.kc + cbl * KBLK) * a.act.s1 + (long long)iy * a.act.s2 + (long long)ix * a.act.s3;
       }
       float v[KBLK];
-      if (ok && vec_ok) {
+      if (chunked) {
+        // Channels-last: the 32 channels of a pixel are 128 contiguous bytes.  Eight lanes fetch one
+        // pixel (16 bytes each), so a load instruction covers four whole rows; lane r computed row r's
+        // address above and hands it to the lanes that fetch it.
+        const unsigned long long mine = ok ? reinterpret_cast<unsigned long long>(src) : 0ull;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float4* ps = reinterpret_cast<const float4*>(__shfl_sync(0xffffffffu, mine, 4 * i + (lane >> 3)));
+          const float4 f = ps ? __ldg(ps + (lane & 7)) : make_float4(0.f, 0.f, 0.f, 0.f);
+          v[4 * i] = f.x; v[4 * i + 1] = f.y; v[4 * i + 2] = f.z; v[4 * i + 3] = f.w;
+        }
+      } else if (vec_ok) {
+        // wide pixels (1 KB apart and more): measured faster with one pixel per lane
 #pragma unroll
         for (int j = 0; j < KBLK / 4; ++j) {
-          const float4 f = __ldg(reinterpret_cast<const float4*>(src) + j);
+          const float4 f = ok ? __ldg(reinterpret_cast<const float4*>(src) + j) : make_float4(0.f, 0.f, 0.f, 0.f);
           v[4 * j] = f.x; v[4 * j + 1] = f.y; v[4 * j + 2] = f.z; v[4 * j + 3] = f.w;
         }
       } else {
@@ -332,8 +345,21 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
         if (!mbar_wait(smem_u32(&ctrl->a_empty[as]), (a_round & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_EMPTY)) break;
         if (pa) atomicAdd(a.prof + 6, (unsigned long long)(clock64() - tw));
       }
-      if (r < a.strip_rows) {
-        const uint32_t p_hi = tiles_base + as * a_stage_bytes, p_lo = p_hi + a_plane;
+      const uint32_t p_hi = tiles_base + as * a_stage_bytes, p_lo = p_hi + a_plane;
+      if (chunked) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int ri = chunk * 32 + 4 * i + (lane >> 3);  // strip_rows is a multiple of 8
+          if (ri < a.strip_rows) {
+            float h[4], l[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) split_tf32_fast(v[4 * i + j], h[j], l[j]);
+            const uint32_t o = sw128_offset(ri, (lane & 7) * 4);
+            sts_f32x4(p_hi + o, h[0], h[1], h[2], h[3]);
+            sts_f32x4(p_lo + o, l[0], l[1], l[2], l[3]);
+          }
+        }
+      } else if (r < a.strip_rows) {
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
           float h[4], l[4];

@@ -98,7 +98,7 @@ __device__ __forceinline__ uint64_t make_mn_desc(uint32_t addr, uint32_t lbo) {
 // lanes 4-7 of every group of eight write the two chunks of a 32-byte pair in the opposite order
 // (every 8-lane store wavefront is then conflict-free).  To keep that free of per-value selects the
 // swapped lanes already LOAD their channels in swapped order: val[j] holds channel j ^ 4 there.
-__device__ __forceinline__ void stage_block(const View4& v, long long chan0, int chans, int H, int W, int row_pitch,
+__device__ __forceinline__ bool stage_block(const View4& v, long long chan0, int chans, int H, int W, int row_pitch,
                                             int img_pitch, const FastDiv& img_div, const FastDiv& row_div, int q_first,
                                             int q_lo, int q_hi, int rows, int lane, bool vec_ok, float (&val)[32],
                                             int sph = 1, int spw = 1, int pa = 0, int pb = 0, int lim_h = 1 << 30,
@@ -115,14 +115,21 @@ __device__ __forceinline__ void stage_block(const View4& v, long long chan0, int
     src += n * v.s0 + chan0 * v.s1 + (long long)ty * v.s2 + (long long)tx * v.s3;
   }
   const int sw = (lane >> 2) & 1;
-  if (ok && chans == 32) {
-    if (vec_ok) {
+  if (vec_ok && chans == 32) {
+    // Channels-last: eight lanes fetch the 128 contiguous bytes of one pixel, four pixels per load
+    // instruction; lane r computed the address of row r above and hands it to the lanes that fetch
+    // it.  val[4i..4i+3] is then the 16-byte chunk (lane & 7) of row 4i + (lane >> 3): see
+    // store_block_chunks.
+    const unsigned long long mine = ok ? reinterpret_cast<unsigned long long>(src) : 0ull;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float4 f = __ldg(reinterpret_cast<const float4*>(src) + (j ^ sw));
-        val[4 * j] = f.x; val[4 * j + 1] = f.y; val[4 * j + 2] = f.z; val[4 * j + 3] = f.w;
-      }
-    } else {
+    for (int i = 0; i < 8; ++i) {
+      const float4* ps = reinterpret_cast<const float4*>(__shfl_sync(0xffffffffu, mine, 4 * i + (lane >> 3)));
+      const float4 f = ps ? __ldg(ps + (lane & 7)) : make_float4(0.f, 0.f, 0.f, 0.f);
+      val[4 * i] = f.x; val[4 * i + 1] = f.y; val[4 * i + 2] = f.z; val[4 * i + 3] = f.w;
+    }
+    return true;
+  } else if (ok && chans == 32) {
+    {
       const float* pa = src + 4 * sw * v.s1;  // for j with bit 2 clear
       const float* pb = src - 4 * sw * v.s1;  // for j with bit 2 set
 #pragma unroll
@@ -133,6 +140,24 @@ __device__ __forceinline__ void stage_block(const View4& v, long long chan0, int
     for (int j = 0; j < 32; ++j) {
       const int c = j ^ (sw << 2);
       val[j] = (ok && c < chans) ? __ldg(src + c * v.s1) : 0.f;
+    }
+  }
+  return false;
+}
+// Store for the channels-last load pattern: eight lanes write the eight 16-byte chunks of one row
+// (a whole 128-byte row per quarter warp: conflict-free in any swizzle).
+__device__ __forceinline__ void store_block_chunks(const float (&val)[32], int rows, int row0, uint32_t plane_hi,
+                                                   uint32_t plane_lo, int lane) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = 4 * i + (lane >> 3);
+    if (r < rows) {
+      float h[4], l[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) split_tf32_fast(val[4 * i + j], h[j], l[j]);
+      const uint32_t o = sw32b_offset(row0 + r, (lane & 7) * 4);
+      sts_f32x4(plane_hi + o, h[0], h[1], h[2], h[3]);
+      sts_f32x4(plane_lo + o, l[0], l[1], l[2], l[3]);
     }
   }
 }
@@ -275,6 +300,7 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
       const int k0 = k_begin + kb * KP;
       const uint32_t xs = base + s * stage_bytes, ys = xs + x_bytes;
       float val[32];
+      bool chunked;  // which register pattern stage_block used
       int rows, row0;
       uint32_t p_hi, p_lo;
       const bool pp = DPROF_ON(threadIdx.x == 0);
@@ -290,7 +316,7 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
           // exists: no split-range clipping, only image bounds
           const int c0 = ci0 + blk * 32;  // strip blk of this CTA
           const int chans = max(0, min(32, g.cig - c0));
-          stage_block(a.x, (long long)group * g.cig + c0, chans, a.H, a.W, row_pitch, img_pitch, a.img_div, a.row_div,
+          chunked = stage_block(a.x, (long long)group * g.cig + c0, chans, a.H, a.W, row_pitch, img_pitch, a.img_div, a.row_div,
                       k0 + yshift - XOFF + row0, 0, a.q_total, rows, lane, x_vec, val);
         } else {
           // exact 32-pixel blocks: tap kx = blk of one channel block, or channel block blk of a 1x1 filter
@@ -298,7 +324,7 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
           const int chans = (a.blocks_are_taps && blk >= g.kw) ? 0 : max(0, min(32, g.cig - c0));
           const int pb = a.blocks_are_taps ? (int)((a.blk_b >> (8 * blk)) & 0xFFu) : 0;
           const int dc = a.blocks_are_taps ? (int)(signed char)((a.blk_dc >> (8 * blk)) & 0xFFu) : 0;
-          stage_block(a.x, (long long)group * g.cig + c0, chans, a.H, a.W, row_pitch, img_pitch, a.img_div, a.row_div,
+          chunked = stage_block(a.x, (long long)group * g.cig + c0, chans, a.H, a.W, row_pitch, img_pitch, a.img_div, a.row_div,
                       k0 + yshift + dc, 0, a.q_total, rows, lane, x_vec, val, a.sph, a.spw, pa, pb, a.in_h, a.in_w);
         }
       } else {
@@ -310,7 +336,7 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
         const int c0 = co0 + blk * 32;
         const int chans = max(0, min(32, g.cog - c0));
         // dY outside this split's pixel range must read as zero so that splits do not overlap
-        stage_block(a.dy, (long long)group * g.cog + c0, chans, a.H, a.W, row_pitch, img_pitch, a.img_div, a.row_div,
+        chunked = stage_block(a.dy, (long long)group * g.cog + c0, chans, a.H, a.W, row_pitch, img_pitch, a.img_div, a.row_div,
                     k0, k_begin, k_end, rows, lane, y_vec, val, 1, 1, 0, 0, a.out_h, a.out_w);
       }
       DPROF_ADD(pp, 2);
@@ -318,7 +344,8 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
       if (!mbar_wait(smem_u32(&ctrl->empty[s]), (round & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_EMPTY)) { alive = false; break; }
       if (pp) atomicAdd(a.prof + 3, (unsigned long long)(clock64() - tw)); }
       { const long long tw = pp ? clock64() : 0;
-      store_block(val, rows, row0, p_hi, p_lo, lane);
+      if (chunked) store_block_chunks(val, rows, row0, p_hi, p_lo, lane);
+      else store_block(val, rows, row0, p_hi, p_lo, lane);
       fence_proxy_async();
       mbar_arrive(smem_u32(&ctrl->full[s]));
       if (pp) { atomicAdd(a.prof + 4, (unsigned long long)(clock64() - tw)); atomicAdd(a.prof + 5, 1ull); } }

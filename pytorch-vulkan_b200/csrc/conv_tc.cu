@@ -701,14 +701,18 @@ int tc_forward(const ConvGeom& g, View4 x, View4 w, const float* bias, long long
                size_t ws_bytes, cudaStream_t st) {
   if (strip_allowed() && strip_supported(g, B200_PHASE_FORWARD)) {
     note_kernel("tc_strip_forward");
-    return strip_conv(g, false, x, w, bias, bias_stride, y, ws, ws_bytes, st);
+    const int rc = strip_conv(g, false, x, w, bias, bias_stride, y, ws, ws_bytes, st);
+    if (rc != B200_EUNSUPPORTED) return rc;  // tensors beyond 32-bit element offsets take the gather kernel
+    note_kernel("tc_igemm_forward");
   }
   return conv_tc_run(g, false, x, w, bias, bias_stride, y, ws, ws_bytes, st);
 }
 int tc_dinput(const ConvGeom& g, View4 dy, View4 w, float* dx, void* ws, size_t ws_bytes, cudaStream_t st) {
   if (strip_allowed() && strip_supported(g, B200_PHASE_DINPUT)) {
     note_kernel("tc_strip_dinput");
-    return strip_conv(g, true, dy, w, nullptr, 0, dx, ws, ws_bytes, st);
+    const int rc = strip_conv(g, true, dy, w, nullptr, 0, dx, ws, ws_bytes, st);
+    if (rc != B200_EUNSUPPORTED) return rc;
+    note_kernel("tc_igemm_dinput");
   }
   return conv_tc_run(g, true, dy, w, nullptr, 0, dx, ws, ws_bytes, st);
 }
@@ -728,7 +732,9 @@ static int launch_dweight_tc(const DwTcArgs& a, dim3 grid, cudaStream_t st) {
 int tc_dweight(const ConvGeom& g, View4 x, View4 dy, float* dw, void* ws, size_t ws_bytes, cudaStream_t st) {
   if (strip_allowed() && dweight_strip_supported(g)) {
     note_kernel("tc_strip_dweight");
-    return dweight_strip(g, x, dy, dw, ws, ws_bytes, st);
+    const int rc = dweight_strip(g, x, dy, dw, ws, ws_bytes, st);
+    if (rc != B200_EUNSUPPORTED) return rc;  // tensors beyond 32-bit element offsets take the gather kernel
+    note_kernel("tc_igemm_dweight");
   }
   int splits, span;
   size_t bytes;

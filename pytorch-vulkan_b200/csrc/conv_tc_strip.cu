@@ -284,6 +284,7 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
     const bool vec_ok = a.act.s1 == 1 && ((reinterpret_cast<uintptr_t>(a.act.ptr) & 15) == 0) &&
                         (a.act.s0 % 4 == 0) && (a.act.s2 % 4 == 0) && (a.act.s3 % 4 == 0);
     const bool chunked = vec_ok && a.act.s3 < 256;  // eight lanes per pixel (see below)
+    const int s1 = (int)a.act.s1;
     const int my_units = a.units > (int)blockIdx.x ? (a.units - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
     const int my_tiles = my_units * a.unit;
     const int total_jobs = my_tiles * a.cblocks * chunks;  // below 2^31 (checked by the host)
@@ -338,7 +339,7 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
         }
       } else {
 #pragma unroll
-        for (int j = 0; j < KBLK; ++j) v[j] = ok ? __ldg(src + j * a.act.s1) : 0.f;
+        for (int j = 0; j < KBLK; ++j) v[j] = ok ? __ldg(src + j * s1) : 0.f;  // 32-bit offsets: two instructions per value
       }
       {
         const long long tw = pa ? clock64() : 0;
@@ -680,6 +681,13 @@ int strip_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* b
     wp = (const float*)ws;
   }
   if (reinterpret_cast<uintptr_t>(wp) & 15) return fail(B200_EINVAL, "weight stage images must be 16-byte aligned");
+  {  // the kernel forms element offsets inside the activation tensor in 32 bits
+    const long long an = g.n, ac = is_dx ? g.cout : g.cin, ah = is_dx ? g.oh : g.h, aw = is_dx ? g.ow : g.w;
+    const long long span = (an - 1) * std::llabs(act.s0) + (ac - 1) * std::llabs(act.s1) +
+                           (ah - 1) * std::llabs(act.s2) + (aw - 1) * std::llabs(act.s3);
+    if (span > 2147483647ll - 64 * std::llabs(act.s1))
+      return fail(B200_EUNSUPPORTED, "strip kernel: activation tensor too large for 32-bit element offsets");
+  }
   StripArgs a{};
   a.g = g; a.act = act; a.wp = wp; a.bias = is_dx ? nullptr : bias; a.bias_stride = bias_stride; a.out = out;
   a.H = plan.gh; a.W = plan.gw; a.pr = plan.pr; a.pc = plan.pc;

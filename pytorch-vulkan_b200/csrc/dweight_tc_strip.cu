@@ -128,18 +128,25 @@ __device__ __forceinline__ bool stage_block(const View4& v, long long chan0, int
       val[4 * i] = f.x; val[4 * i + 1] = f.y; val[4 * i + 2] = f.z; val[4 * i + 3] = f.w;
     }
     return true;
-  } else if (ok && chans == 32) {
-    {
-      const float* pa = src + 4 * sw * v.s1;  // for j with bit 2 clear
-      const float* pb = src - 4 * sw * v.s1;  // for j with bit 2 set
+  } else if (chans == 32) {
+    // lane = pixel, one coalesced load per channel; 32-bit element offsets (the host checks that the
+    // tensor is addressable with them) keep this at two instructions per value
+    const int s1 = (int)v.s1;
+    const float* pa = src + 4 * sw * s1;  // for j with bit 2 clear
+    const float* pb = src - 4 * sw * s1;  // for j with bit 2 set
+    if (__all_sync(0xffffffffu, ok)) {  // the common case away from padding: no predication
 #pragma unroll
-      for (int j = 0; j < 32; ++j) val[j] = __ldg(((j & 4) ? pb : pa) + j * v.s1);
+      for (int j = 0; j < 32; ++j) val[j] = __ldg(((j & 4) ? pb : pa) + j * s1);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) val[j] = ok ? __ldg(((j & 4) ? pb : pa) + j * s1) : 0.f;
     }
   } else {
+    const int s1 = (int)v.s1;
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
       const int c = j ^ (sw << 2);
-      val[j] = (ok && c < chans) ? __ldg(src + c * v.s1) : 0.f;
+      val[j] = (ok && c < chans) ? __ldg(src + c * s1) : 0.f;
     }
   }
   return false;
@@ -527,6 +534,12 @@ int dweight_strip(const ConvGeom& g, View4 x, View4 dy, float* dw, void* ws, siz
   using namespace tcdw;
   const DwStripPlan plan = plan_dw_strip(g, ws ? ws_bytes : 0);
   if (!plan.ok) return fail(B200_EUNSUPPORTED, "dWeight strip kernel does not take this geometry");
+  // the kernel forms element offsets inside a tensor in 32 bits
+  auto span = [](const View4& v, long long n, long long c, long long h, long long w) {
+    return (n - 1) * std::llabs(v.s0) + (c - 1) * std::llabs(v.s1) + (h - 1) * std::llabs(v.s2) + (w - 1) * std::llabs(v.s3);
+  };
+  if (span(x, g.n, g.cin, g.h, g.w) > 2147483647ll - 64 * std::llabs(x.s1) || span(dy, g.n, g.cout, g.oh, g.ow) > 2147483647ll - 64 * std::llabs(dy.s1))
+    return fail(B200_EUNSUPPORTED, "dWeight strip kernel: tensor too large for 32-bit element offsets");
   DwStripArgs a{};
   a.g = g; a.x = x; a.dy = dy;
   a.H = plan.gh; a.W = plan.gw; a.pr = plan.pr; a.pc = plan.pc;

@@ -185,6 +185,20 @@ class Layer:
         return v(self.x), v(self.w), v(self.go)
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture summarised in
+# profiles/tc_strip_kernels_resnet_sweep.md (one layer of the sweep; bytes, not a live measurement)
+NCU_TRAFFIC = {
+    "tc_strip_dweight": {"bytes_per_launch": 53.9e6,
+                         "note": "ncu, layer 128->128 28x28 3x3 batch 64 NCHW: 51.4 MB read + 2.5 MB written per "
+                                 "launch against 51.9 MB algorithmic (x + dy + dW)"},
+    "tc_strip_forward": {"bytes_per_launch": 26.9e6,
+                         "note": "ncu, layer 128->128 28x28 3x3 batch 64: 26.9 MB read per launch (x + filter); the "
+                                 "25.7 MB output was still in L2 when the capture ended"},
+    "tc_strip_dinput": {"bytes_per_launch": 26.9e6,
+                        "note": "ncu, layer 128->128 28x28 3x3 batch 64: 26.9 MB read per launch (dy + filter)"},
+}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -356,7 +370,9 @@ def main():
         tf32_peak = pk["bf16_sustained"] / 2.0  # kind::tf32 runs at half the dense bf16 rate
         ach = fam_stats[dominant]["tflops"]
         roofline = {"bound": "tensor", "kernel": dominant, "achieved": ach, "peak": tf32_peak, "unit": "TFLOP/s",
-                    "frac": ach / tf32_peak, "frac_of_3xtf32_ceiling": ach / (tf32_peak / 3.0), "traffic": None,
+                    "frac": ach / tf32_peak, "frac_of_3xtf32_ceiling": ach / (tf32_peak / 3.0),
+                    "traffic": NCU_TRAFFIC.get(dominant, {}).get("bytes_per_launch"),
+                    "traffic_note": NCU_TRAFFIC.get(dominant, {}).get("note"),
                     "peak_source": f"{pk['source']}: sustained bf16 {pk['bf16_sustained']} TFLOP/s / 2 (TF32 rate); "
                                    "3xTF32 issues 3 MMAs per algorithmic MAC, ceiling = peak/3",
                     "families": fam_stats}

@@ -88,6 +88,7 @@ struct StripArgs {
   int out_rowmajor;       // 0: NCHW planes.  1: [pixel][channel] rows (channels-last / GEMM C)
   int out_vec4;           // row-major rows may be written with 16-byte stores
   float alpha, beta;      // out = alpha * acc + beta * bias
+  int wait_for_images;    // launched with programmatic stream serialisation behind stage_weights_kernel
   int* status;
   unsigned long long* prof;  // optional cycle counters of CTA 0 (B200_STRIP_PROFILE=1), else null
   TapTable tt;
@@ -242,6 +243,9 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
       uint32_t ws = 0, w_par = 1, issued = 0;
       bool alive = true;
       const bool pw = PROF_ON(true);
+      // The kernel may have started while the staging kernel ahead of it was still running: only
+      // this thread reads what that kernel writes, so only it waits for that kernel to finish.
+      if (a.wait_for_images) asm volatile("griddepcontrol.wait;" ::: "memory");
       for (TileIter it(a); it.valid() && alive; it.next()) {
         const int tile = it.tile();
         const int tn = (int)a.div_tiles_n.div((uint32_t)tile), n_tile = tile - tn * a.tiles_n;
@@ -494,6 +498,8 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
 // so a weight stage of the main kernel is one bulk copy from a running pointer.
 __global__ void __launch_bounds__(256) stage_weights_kernel(ConvGeom g, View4 w, int is_dx, int bn, int tiles_pp,
                                                             TapTable tt, float* __restrict__ out, long long total) {
+  // let the convolution kernel behind this one start its prologue and its activation strips now
+  asm volatile("griddepcontrol.launch_dependents;");
   const long long i = blockIdx.x * 256ll + threadIdx.x;
   if (i >= total) return;
   const int kc = is_dx ? g.cog : g.cig, nc = is_dx ? g.cig : g.cog;
@@ -656,7 +662,13 @@ static int launch_strip(const tcs::StripArgs& a, int grid, int smem, cudaStream_
     B200_CUDA(cudaFuncSetAttribute(tcs::conv_strip_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured = smem;
   }
-  tcs::conv_strip_kernel<BN><<<grid, tcs::THREADS, smem, st>>>(a);
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3((unsigned)grid); cfg.blockDim = dim3(tcs::THREADS); cfg.dynamicSmemBytes = (size_t)smem; cfg.stream = st;
+  cudaLaunchAttribute attr{};
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  if (a.wait_for_images) { cfg.attrs = &attr; cfg.numAttrs = 1; }
+  B200_CUDA(cudaLaunchKernelEx(&cfg, tcs::conv_strip_kernel<BN>, a));
   count_launch();
   return launch_check("conv_strip_kernel");
 }
@@ -671,6 +683,7 @@ int strip_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* b
   const int tiles_n = is_dx ? tiles_pp * plan.tt.n_phase : tiles_pp;
   const long long wcount = (long long)g.groups * tiles_pp * plan.bn * kc * g.kh * g.kw;  // per plane
   const float* wp = staged_images;
+  bool staged_here = false;
   if (!wp) {
     if (!ws || ws_bytes < 2 * sizeof(float) * (size_t)wcount || (reinterpret_cast<uintptr_t>(ws) & 15))
       return fail(B200_EWORKSPACE, "tcgen05 convolution needs a 16-byte aligned workspace of %zu bytes (got %zu)",
@@ -679,6 +692,7 @@ int strip_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* b
     count_launch();
     if (int rc = launch_check("stage_weights_kernel")) return rc;
     wp = (const float*)ws;
+    staged_here = true;
   }
   if (reinterpret_cast<uintptr_t>(wp) & 15) return fail(B200_EINVAL, "weight stage images must be 16-byte aligned");
   {  // the kernel forms element offsets inside the activation tensor in 32 bits
@@ -722,6 +736,7 @@ int strip_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* b
   a.div_tiles_pp = FastDiv((uint32_t)a.tiles_pp); a.div_chunks = FastDiv((uint32_t)chunks);
   a.div_cblocks = FastDiv((uint32_t)a.cblocks); a.div_cbpp = FastDiv((uint32_t)a.cb_per_phase);
   a.div_a_stages = FastDiv((uint32_t)a.a_stages);
+  a.wait_for_images = staged_here ? 1 : 0;
   a.out_rowmajor = rowmajor ? 1 : 0;
   a.alpha = alpha; a.beta = beta;
   a.out_vec4 = rowmajor && a.out_channels % 4 == 0 && plan.bn % 4 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 && a.nc % 4 == 0;

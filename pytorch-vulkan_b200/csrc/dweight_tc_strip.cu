@@ -203,7 +203,8 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
   volatile int* abort_flag = &ctrl->abort_flag;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int x_halves = a.xr > 32 ? 2 : 1;                      // a strip = rows 0..31 and 32..47; an exact block = 32 rows
-  const int x_tasks = a.nacc * a.xblocks * x_halves;
+  // taps beyond the filter width are not staged: their accumulator rows are never stored
+  const int x_tasks = a.nacc * (a.blocks_are_taps ? g.kw : a.xblocks) * x_halves;
   const int tasks = x_tasks + NB;                              // warp-sized staging jobs per K block
   // BN <= 128: the dY hi and lo planes (their 32-channel blocks are equally spaced) form ONE operand
   // of 2*BN columns, so x_hi*[dy_hi | dy_lo] is a single MMA; the epilogue adds the two halves.
@@ -328,7 +329,7 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
         } else {
           // exact 32-pixel blocks: tap kx = blk of one channel block, or channel block blk of a 1x1 filter
           const int c0 = ci0 + (a.blocks_are_taps ? 0 : blk * 32);
-          const int chans = (a.blocks_are_taps && blk >= g.kw) ? 0 : max(0, min(32, g.cig - c0));
+          const int chans = max(0, min(32, g.cig - c0));
           const int pb = a.blocks_are_taps ? (int)((a.blk_b >> (8 * blk)) & 0xFFu) : 0;
           const int dc = a.blocks_are_taps ? (int)(signed char)((a.blk_dc >> (8 * blk)) & 0xFFu) : 0;
           chunked = stage_block(a.x, (long long)group * g.cig + c0, chans, a.H, a.W, row_pitch, img_pitch, a.img_div, a.row_div,
@@ -551,7 +552,7 @@ int dweight_strip(const ConvGeom& g, View4 x, View4 dy, float* dw, void* ws, siz
   a.row_div = FastDiv((uint32_t)(a.W + a.pc));
   a.span = plan.span; a.splits = plan.splits; a.xblocks = plan.xblocks;
   a.ci_tiles = plan.ci_tiles; a.co_tiles = plan.co_tiles; a.stages = plan.stages;
-  a.div_tasks = FastDiv((uint32_t)(plan.nacc * plan.xblocks * (plan.xr > 32 ? 2 : 1) + plan.bn / 32));
+  a.div_tasks = FastDiv((uint32_t)(plan.nacc * (plan.blocks_are_taps ? g.kw : plan.xblocks) * (plan.xr > 32 ? 2 : 1) + plan.bn / 32));
   a.div_stages = FastDiv((uint32_t)plan.stages);
   a.out = plan.splits > 1 ? (float*)ws : dw;
   a.partial_layout = plan.splits > 1 ? 1 : 0;

@@ -1,31 +1,40 @@
-// Persistent tcgen05 implicit-GEMM kernel for stride-1 "same" convolutions (3x3 pad 1, 1x1,
-// 5x5 pad 2, dilated 3x3 with matching padding ...), forward and dInput, FP32 via 3xTF32.
+// Persistent tcgen05 implicit-GEMM kernel for convolution forward and dInput (any stride, padding,
+// dilation and grouping; reduction channels in blocks of 32), FP32 via 3xTF32.  The same kernel is
+// the GEMM behind mm/addmm and the plane product of the Winograd path.
 //
-// Idea: the nine (kh*kw) filter taps of one 32-channel block all read the same activations,
-// shifted by whole pixels.  The activations of a tile are therefore staged ONCE per channel
-// block as a "strip" in shared memory -- one 128-byte row (32 channels, TF32 hi and lo planes)
-// per pixel of a zero-padded pixel space -- and every tap's tcgen05.mma reads that strip through
-// a matrix descriptor whose start address is moved by `shift(tap)` rows.  (The 128-byte swizzle
-// is a function of the absolute shared-memory address, so a descriptor may start at any row.)
+// Idea: the kh*kw filter taps of one 32-channel block all read the same activations, shifted by
+// whole pixels.  The activations of a tile are therefore staged ONCE per channel block as a
+// "strip" in shared memory -- one 128-byte row (32 channels, TF32 hi and lo planes) per pixel of
+// a zero-padded pixel grid -- and every tap's tcgen05.mma reads that strip through a matrix
+// descriptor whose start address is moved by `shift(tap)` rows.  (The 128-byte swizzle is a
+// function of the absolute shared-memory address, so a descriptor may start at any row.)
 // Compared with gathering an operand tile per tap this issues kh*kw times fewer global loads,
 // TF32 splits and shared-memory stores, which is what lets the tensor pipe stay busy.
 //
-// Padded pixel space: images are laid out with `pc` zero columns after every row and `pr` zero
-// rows after every image (pc = pad_w, pr = pad_h), q = (n*(H+pr) + y)*(W+pc) + x.  A tap offset
-// (dy, dx) is then the constant row shift dy*(W+pc) + dx for every pixel, and reads that leave the
-// image land on zero rows of the strip.  Accumulator rows that fall on padding are discarded.
+// Padded pixel grid: `pc` zero columns after every row and `pr` zero rows after every image,
+// q = (n*(H+pr) + y)*(W+pc) + x.  A tap offset (dr, dc) is then the constant row shift
+// dr*(W+pc) + dc for every pixel, and reads that leave the image land on zero rows of the strip.
+// Accumulator rows that fall on padding (or outside a smaller output) are discarded.
 //
-// CTA roles (448 threads, persistent over tiles of 128 padded pixels x BN output channels):
-//   warps 0-3    epilogue: tcgen05.ld of a finished accumulator, bias, coalesced NCHW stores
-//   warps 4-11   strip producers: gather from the caller's strided view, split_tf32, swizzled stores
-//   warp 12      weight stages: one bulk copy (cp.async.bulk -> mbarrier complete_tx) of a pre-split,
-//                pre-swizzled image per stage (stage_weights_kernel writes the images once per call)
-//   warp 13      TMEM allocation and the tcgen05.mma stream (lo*hi, hi*lo, hi*hi per tap)
+// Strides: with stride s the taps are grouped by the phase (row mod s, column mod s) of the pixels
+// they touch -- input phases in forward (channel blocks are enumerated per phase, each with its own
+// taps), output phases in dInput (column tiles are enumerated per phase; all read one dY strip).
+// See TapTable and plan_strip.
+//
+// CTA roles (448 threads, persistent over tiles of 128 grid pixels x BN output channels):
+//   warps 0-3    epilogue: tcgen05.ld of a finished accumulator, bias, coalesced stores
+//   warps 4-11   strip producers: gather from the caller's strided view, TF32 split, swizzled stores
+//   warp 12      (one thread) weight stages: one bulk copy (cp.async.bulk -> mbarrier complete_tx)
+//                of a pre-split, pre-swizzled image per stage; stage_weights_kernel writes the
+//                images once per call
+//   warp 13      TMEM allocation; one thread issues the tcgen05.mma stream
 // The accumulator is double-buffered in TMEM, so the epilogue of tile i overlaps the main loop of
 // tile i+1.  All hand-offs are mbarriers with bounded waits.
 //
 // Replaces csrc/shaders/conv2d_tiled_body.glsl:53-86 and
-// csrc/shaders/conv2d_backward_input_tiled_body.glsl:49-93 of the reference for these geometries.
+// csrc/shaders/conv2d_backward_input_tiled_body.glsl:49-93 of the reference.
+#include <cuda_bf16.h>
+
 #include "common.cuh"
 #include "tc_common.cuh"
 
@@ -136,7 +145,7 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
   // tensor core as ONE operand of 2*BN rows: a single MMA of width 2*BN yields a_hi*b_hi in columns
   // [0,BN) and a_hi*b_lo in [BN,2BN), a second one of width BN adds a_lo*b_hi to [0,BN); the epilogue
   // sums the two halves.  Two MMAs read 14/18 of the shared-memory bytes that three do.
-  constexpr bool FUSE_HILO = BN <= 128;
+  constexpr bool FUSE_HILO = BN <= 128 && !CROSS_BF16;
   constexpr uint32_t ACC_COLS = FUSE_HILO ? 2 * BN : BN;
   constexpr uint32_t TMEM_COLS = 2 * ACC_COLS;
 
@@ -177,6 +186,7 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc_tf32(BLOCK_M, BN);
       constexpr uint32_t idesc_wide = make_idesc_tf32(BLOCK_M, FUSE_HILO ? 2 * BN : BN);
+      constexpr uint32_t idesc_cross = make_idesc_bf16(BLOCK_M, BN);
       const uint64_t da_base = make_kmajor_sw128_desc(tiles_base + (uint32_t)a.halo * 128u);
       const uint64_t db_base = make_kmajor_sw128_desc(w_base);
       const uint32_t a_stage_d = a_stage_bytes >> 4, a_plane_d = a_plane >> 4;
@@ -212,7 +222,12 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
             const uint64_t db_hi = db_base + ws * w_stage_d, db_lo = db_hi + w_plane_d;
             const uint32_t first = accumulate;
             accumulate = 1;
-            if (FUSE_HILO) {
+            if (CROSS_BF16) {  // hi x hi in TF32, then both cross terms as one BF16 product over the second planes
+#pragma unroll
+              for (int kk = 0; kk < 4; ++kk) umma_tf32(tmem_acc, da_hi + 2 * kk, db_hi + 2 * kk, idesc, first | (uint32_t)(kk != 0));
+#pragma unroll
+              for (int kk = 0; kk < 4; ++kk) umma_bf16(tmem_acc, da_lo + 2 * kk, db_lo + 2 * kk, idesc_cross, 1);
+            } else if (FUSE_HILO) {
 #pragma unroll
               for (int kk = 0; kk < 4; ++kk) umma_tf32(tmem_acc, da_hi + 2 * kk, db_hi + 2 * kk, idesc_wide, first | (uint32_t)(kk != 0));
 #pragma unroll
@@ -359,20 +374,40 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
             float h[4], l[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) split_tf32_fast(v[4 * i + j], h[j], l[j]);
-            const uint32_t o = sw128_offset(ri, (lane & 7) * 4);
-            sts_f32x4(p_hi + o, h[0], h[1], h[2], h[3]);
-            sts_f32x4(p_lo + o, l[0], l[1], l[2], l[3]);
+            const int c4 = (lane & 7) * 4;  // first of this lane's four channels
+            sts_f32x4(p_hi + sw128_offset(ri, c4), h[0], h[1], h[2], h[3]);
+            if (CROSS_BF16) {
+              sts_b32x2(p_lo + sw128_offset_bf16(ri, c4), pack_bf16x2(h[0], h[1]), pack_bf16x2(h[2], h[3]));
+              sts_b32x2(p_lo + sw128_offset_bf16(ri, 32 + c4), pack_bf16x2(l[0], l[1]), pack_bf16x2(l[2], l[3]));
+            } else {
+              sts_f32x4(p_lo + sw128_offset(ri, c4), l[0], l[1], l[2], l[3]);
+            }
           }
         }
       } else if (r < a.strip_rows) {
+        if (CROSS_BF16) {
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          float h[4], l[4];
+          for (int c = 0; c < 4; ++c) {  // eight channels: two 16-byte chunks of the hi plane, one each of bf16(hi), bf16(lo)
+            float h[8], l[8];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) split_tf32_fast(v[c * 4 + j], h[j], l[j]);
-          const uint32_t o = sw128_offset(r, c * 4);
-          sts_f32x4(p_hi + o, h[0], h[1], h[2], h[3]);
-          sts_f32x4(p_lo + o, l[0], l[1], l[2], l[3]);
+            for (int j = 0; j < 8; ++j) split_tf32_fast(v[c * 8 + j], h[j], l[j]);
+            sts_f32x4(p_hi + sw128_offset(r, c * 8), h[0], h[1], h[2], h[3]);
+            sts_f32x4(p_hi + sw128_offset(r, c * 8 + 4), h[4], h[5], h[6], h[7]);
+            sts_b32x4(p_lo + sw128_offset_bf16(r, c * 8), pack_bf16x2(h[0], h[1]), pack_bf16x2(h[2], h[3]),
+                      pack_bf16x2(h[4], h[5]), pack_bf16x2(h[6], h[7]));
+            sts_b32x4(p_lo + sw128_offset_bf16(r, 32 + c * 8), pack_bf16x2(l[0], l[1]), pack_bf16x2(l[2], l[3]),
+                      pack_bf16x2(l[4], l[5]), pack_bf16x2(l[6], l[7]));
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            float h[4], l[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) split_tf32_fast(v[c * 4 + j], h[j], l[j]);
+            const uint32_t o = sw128_offset(r, c * 4);
+            sts_f32x4(p_hi + o, h[0], h[1], h[2], h[3]);
+            sts_f32x4(p_lo + o, l[0], l[1], l[2], l[3]);
+          }
         }
       }
       fence_proxy_async();
@@ -538,9 +573,15 @@ __global__ void __launch_bounds__(256) stage_weights_kernel(ConvGeom g, View4 w,
   }
   float hi, lo;
   split_tf32(v, hi, lo);
-  float* dst = out + image * (bn * 64ll) + sw128_offset(row, k) / 4;
-  dst[0] = hi;
-  dst[bn * 32] = lo;
+  float* plane = out + image * (bn * 64ll);
+  plane[sw128_offset(row, k) / 4] = hi;
+  if (CROSS_BF16) {  // second plane: [bf16(lo) x32 | bf16(hi) x32] per row, pairing with the activations' [hi | lo]
+    __nv_bfloat16* cross = reinterpret_cast<__nv_bfloat16*>(plane + bn * 32);
+    cross[sw128_offset_bf16(row, k) / 2] = __float2bfloat16_rn(lo);
+    cross[sw128_offset_bf16(row, 32 + k) / 2] = __float2bfloat16_rn(hi);
+  } else {
+    plane[bn * 32 + sw128_offset(row, k) / 4] = lo;
+  }
 }
 
 static inline int floor_div(int a, int b) { return a >= 0 ? a / b : -((-a + b - 1) / b); }

@@ -1,23 +1,26 @@
-// tcgen05 dWeight kernel for stride-1 "same" convolutions with kw <= 4 (3x3 pad 1, dilated 3x3,
-// 1x1 ...), FP32 via 3xTF32.
+// tcgen05 dWeight kernel for filters up to four taps wide (any stride, padding, dilation, groups;
+// at least 16 channels on both sides), FP32 via 3xTF32.
 //
-//   dW[co][ci][ky][kx] = sum over padded pixels q of  dY[q][co] * X[q + shift(ky,kx)][ci]
+//   dW[co][ci][ky][kx] = sum over grid pixels q of  dY[q][co] * X_phase(ky,kx)[q + shift(ky,kx)][ci]
 //
 // The contraction runs over pixels, so both operands are staged pixel-major ("MN-major" for the
 // tensor core): one 128-byte shared-memory row per pixel holding 32 channels, TF32 hi and lo
 // planes, written in the 128-byte/32-byte-base swizzle that tcgen05 requires for 32-bit MN-major
-// operands.  Two properties of the matrix descriptor make the filter taps free:
-//   * a descriptor may start at any row, so the vertical tap (ky) is a start-address offset;
-//   * the blocks of 32 rows that make up the M dimension sit at a programmable byte stride, so
-//     with a stride of `dilation_w` rows the four M blocks of ONE staged input strip are the
-//     horizontal taps kx = 0..3: a single tcgen05.mma of shape 128 x BN x 8 accumulates up to four
-//     taps of a 32-channel block at once.  (For 1x1 filters the four M blocks are four channel
-//     blocks instead.)
-// Every CTA owns one (channel block, ky, column tile, pixel split) and a single accumulator in
-// TMEM; its 16 producer warps stream the input strip (32 + halo rows per K block) and the dY
-// strip (32 rows x BN channels) straight from the caller's strided views, one 32-row block per
-// warp, several K blocks in flight.  Split partials land in [split][cout][cin/g*kh*kw] and are
-// summed in ascending order by finalize_kernel (no atomics, run-to-run identical).
+// operands.  The M dimension of the MMA (4 blocks of 32 rows, at a programmable byte stride) is
+// filled in one of two ways (plan_dw_strip):
+//   strip   stride 1, output as large as the input: the vertical tap (ky) is a start-address
+//           offset of ONE staged input strip and, with a block stride of `dilation_w` rows, its
+//           four M blocks are the horizontal taps kx = 0..3: a single tcgen05.mma of shape
+//           128 x BN x 8 accumulates up to four taps of a 32-channel block at once.  Two channel
+//           blocks per CTA (two accumulators in TMEM) share every staged dY block.
+//   blocks  everything else: four exact 32-pixel blocks per K block, the taps kx of one channel
+//           block (each read from its own column phase and offset of a strided input) or four
+//           channel blocks of a 1x1 filter.
+// Every CTA owns one (channel tile, ky, column tile, pixel split); its 16 producer warps stream the
+// input and dY blocks straight from the caller's strided views, one 32-row block per warp, several
+// K blocks in flight.  Split partials land in [split][cout][kh*kw][cin/g] (channel fastest: the
+// epilogue's lanes store neighbouring floats) and finalize_partials_kernel sums them in ascending
+// split order (no atomics, run-to-run identical) while transposing into dW.
 //
 // Replaces csrc/shaders/conv2d_backward_weight_tiled_body.glsl:42-70 and
 // conv2d_backward_weight_finalize.comp:9-18 of the reference for these geometries.

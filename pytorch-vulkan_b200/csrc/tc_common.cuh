@@ -27,9 +27,6 @@ __device__ __forceinline__ unsigned long long global_ns() {
 }
 
 // ---- mbarrier ----------------------------------------------------------------------------
-#ifndef B200_WAIT_SLEEP_NS
-#define B200_WAIT_SLEEP_NS 0
-#endif
 #ifndef B200_WAIT_HINT_NS
 #define B200_WAIT_HINT_NS 1000
 #endif
@@ -78,7 +75,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   unsigned long long t0 = 0;
   uint32_t spins = 0;
   while (!mbar_try_hint(bar, parity, WAIT_HINT_NS)) {
-    if (B200_WAIT_SLEEP_NS) __nanosleep(B200_WAIT_SLEEP_NS);
     if (((++spins) & 63u) == 0) {
       if (abort_flag && *abort_flag) return false;
       const unsigned long long now = global_ns();
@@ -144,6 +140,19 @@ __device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t adesc, uint6
       ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// kind::f16 with BF16 operands, FP32 accumulate, both operands K-major (K = 16 per instruction).
+__host__ __device__ constexpr uint32_t make_idesc_bf16(int M, int N) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // Arrive on `bar` once every tcgen05.mma issued so far by this thread has completed.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -192,6 +201,34 @@ __device__ __forceinline__ void split_tf32(float x, float& hi, float& lo) {
 __device__ __forceinline__ void split_tf32_fast(float x, float& hi, float& lo) {
   hi = __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u);
   lo = B200_SPLIT_LO(x - hi);
+}
+
+// ---- split precision with BF16 cross terms ---------------------------------------------------
+// x*w = xh*wh + (xh*wl + xl*wh) + xl*wl with xh = TF32 nearest to x and xl = x - xh.  The first
+// product runs as kind::tf32 on the hi planes.  The bracket is 2^-11 of the result, so 8-bit
+// operands carry it to 2^-20: it runs as ONE kind::f16 (BF16) product of twice the depth over
+// "cross" planes that hold, per 32 channels, [bf16(xh) x32 | bf16(xl) x32] for activations and
+// [bf16(wl) x32 | bf16(wh) x32] for weights (a 128-byte row either way).  That is one TF32 pass
+// plus one BF16 pass of the same duration per K block instead of three TF32 passes.
+#ifndef B200_CROSS_BF16
+#define B200_CROSS_BF16 1
+#endif
+constexpr bool CROSS_BF16 = B200_CROSS_BF16 != 0;
+// two floats -> packed bf16x2 (first argument in the low half = lower address)
+__device__ __forceinline__ uint32_t pack_bf16x2(float first, float second) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(second), "f"(first));
+  return r;
+}
+// Byte offset of bf16 element k (0..63) of `row` in a 128B-swizzled K-major plane.
+__device__ __forceinline__ uint32_t sw128_offset_bf16(int row, int k) {
+  return (uint32_t)(row * 128 + ((((k >> 3) ^ (row & 7)) << 4) | ((k & 7) << 1)));
+}
+__device__ __forceinline__ void sts_b32x4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ void sts_b32x2(uint32_t addr, uint32_t a, uint32_t b) {
+  asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(a), "r"(b) : "memory");
 }
 
 // Byte offset of element (row, k) inside a 128B-swizzled K-major tile plane (k in [0,32)).

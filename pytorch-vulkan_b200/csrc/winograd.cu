@@ -16,6 +16,8 @@
 //
 // Replaces the reference's F(2x2,3x3) path: csrc/ops/convolution.cpp:257-335 (eligibility, three
 // dispatches) and csrc/shaders/conv2d_winograd_{weights,input,gemm_output}.comp.
+#include <cuda_bf16.h>
+
 #include "common.cuh"
 #include "tc_common.cuh"
 
@@ -87,7 +89,7 @@ __global__ void __launch_bounds__(256) filter_transform_kernel(ConvGeom g, View4
     for (int y = 0; y < 6; ++y) t[y][x] = o[y];
   }
   const int cblocks = kc / 32;
-  const long long within = ((long long)(r / bn) * cblocks + k / 32) * (bn * 64ll) + tc::sw128_offset(r % bn, k % 32) / 4;
+  const long long within_image = ((long long)(r / bn) * cblocks + k / 32) * (bn * 64ll);  // start of the stage image
   const long long per_group = (long long)tiles_n * cblocks * (bn * 64ll);
 #pragma unroll
   for (int y = 0; y < 6; ++y) {
@@ -97,9 +99,15 @@ __global__ void __launch_bounds__(256) filter_transform_kernel(ConvGeom g, View4
     for (int x = 0; x < 6; ++x) {
       float hi, lo;
       tc::split_tf32(o[x], hi, lo);
-      float* dst = U + ((long long)(y * 6 + x) * g.groups + grp) * per_group + within;
-      dst[0] = hi;
-      dst[bn * 32] = lo;
+      float* plane = U + ((long long)(y * 6 + x) * g.groups + grp) * per_group + within_image;
+      plane[tc::sw128_offset(r % bn, k % 32) / 4] = hi;
+      if (tc::CROSS_BF16) {
+        __nv_bfloat16* cross = reinterpret_cast<__nv_bfloat16*>(plane + bn * 32);
+        cross[tc::sw128_offset_bf16(r % bn, k % 32) / 2] = __float2bfloat16_rn(lo);
+        cross[tc::sw128_offset_bf16(r % bn, 32 + k % 32) / 2] = __float2bfloat16_rn(hi);
+      } else {
+        plane[bn * 32 + tc::sw128_offset(r % bn, k % 32) / 4] = lo;
+      }
     }
   }
 }

@@ -59,7 +59,7 @@ enum {
   B200_ALGO_AUTO = 0,    /* heuristic (replaces `heuristic`, convolution.cpp:423-482) */
   B200_ALGO_DIRECT = 1,  /* one thread per output, loop order of the direct shaders (exact FP32 FMA) */
   B200_ALGO_TILED = 2,   /* CUDA-core FP32 implicit GEMM, any geometry / strides */
-  B200_ALGO_TC = 3,      /* tcgen05 implicit GEMM, 3xTF32 split with FP32 accumulation in TMEM */
+  B200_ALGO_TC = 3,      /* tcgen05 implicit GEMM, split-precision FP32 (TF32 hi*hi + cross terms) with FP32 accumulation in TMEM */
   B200_ALGO_WINOGRAD = 4 /* Winograd F(4x4,3x3) forward and dInput for 3x3 stride-1 dilation-1 filters (replaces winograd_f2) */
 };
 

@@ -1,5 +1,6 @@
 // Persistent tcgen05 implicit-GEMM kernel for convolution forward and dInput (any stride, padding,
-// dilation and grouping; reduction channels in blocks of 32), FP32 via 3xTF32.  The same kernel is
+// dilation and grouping; reduction channels in blocks of 32), FP32 by split precision (one TF32 pass
+// for hi x hi, one BF16 pass for the cross terms: tc_common.cuh).  The same kernel is
 // the GEMM behind mm/addmm and the plane product of the Winograd path.
 //
 // Idea: the kh*kw filter taps of one 32-channel block all read the same activations, shifted by

@@ -35,6 +35,15 @@ namespace b200 {
 namespace tcdw {
 using namespace tc;
 
+// BF16 cross terms (tc_common.cuh) are implemented for this kernel too (bf16 planes of 64-byte rows,
+// SWIZZLE_64B, same row-shift and block-stride tricks) and pass the parity tests, but dWeight is bound
+// by its producers' instruction issue, not by the tensor pipe: with them the 64-channel layers ran
+// 2-8 % slower and the others within 1 %.  They stay off here; -DB200_DW_CROSS_BF16=1 turns them on.
+#ifndef B200_DW_CROSS_BF16
+#define B200_DW_CROSS_BF16 0
+#endif
+constexpr bool DW_CROSS = B200_DW_CROSS_BF16 != 0;
+
 constexpr int KP = 32;          // pixels per K block (four K=8 MMA steps)
 constexpr int XR = 48;          // rows of one staged input block: KP + margin for the horizontal taps
 constexpr int XOFF = 4;         // row of the strip that corresponds to the first pixel of the K block
@@ -90,6 +99,22 @@ __device__ __forceinline__ uint64_t make_mn_desc(uint32_t addr, uint32_t lbo) {
   d |= (uint64_t)(512u >> 4) << 32;
   d |= (uint64_t)1 << 46;   // descriptor version of sm_100
   d |= (uint64_t)1 << 61;   // SWIZZLE_128B with 32-byte base
+  return d;
+}
+
+// byte offset of channel e (0..31) of row `row` in a bf16 plane of 64-byte rows, SWIZZLE_64B
+__device__ __forceinline__ uint32_t sw64_offset(int row, int e) {
+  return (uint32_t)(row * 64 + ((((e >> 3) ^ ((row >> 1) & 3)) << 4) | ((e & 7) << 1)));
+}
+// MN-major descriptor of a bf16 plane (64-byte rows): blocks of 32 channels `lbo` bytes apart, 8-row
+// groups 512 bytes apart, SWIZZLE_64B
+__device__ __forceinline__ uint64_t make_mn_desc16(uint32_t addr, uint32_t lbo) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)(lbo >> 4) << 16;
+  d |= (uint64_t)(512u >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)4 << 61;   // SWIZZLE_64B
   return d;
 }
 
@@ -154,10 +179,14 @@ __device__ __forceinline__ bool stage_block(const View4& v, long long chan0, int
   }
   return false;
 }
+// Where one staged block lives: the TF32 hi plane (128-byte rows) and either the FP32 lo plane or,
+// with BF16 cross terms, the two bf16 planes (64-byte rows) of bf16(hi) and bf16(lo).
+struct BlockPlanes {
+  uint32_t hi, lo, h16, l16;
+};
 // Store for the channels-last load pattern: eight lanes write the eight 16-byte chunks of one row
-// (a whole 128-byte row per quarter warp: conflict-free in any swizzle).
-__device__ __forceinline__ void store_block_chunks(const float (&val)[32], int rows, int row0, uint32_t plane_hi,
-                                                   uint32_t plane_lo, int lane) {
+// (a whole row per quarter warp: conflict-free in any swizzle).
+__device__ __forceinline__ void store_block_chunks(const float (&val)[32], int rows, int row0, const BlockPlanes& pl, int lane) {
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     const int r = 4 * i + (lane >> 3);
@@ -165,16 +194,22 @@ __device__ __forceinline__ void store_block_chunks(const float (&val)[32], int r
       float h[4], l[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) split_tf32_fast(val[4 * i + j], h[j], l[j]);
-      const uint32_t o = sw32b_offset(row0 + r, (lane & 7) * 4);
-      sts_f32x4(plane_hi + o, h[0], h[1], h[2], h[3]);
-      sts_f32x4(plane_lo + o, l[0], l[1], l[2], l[3]);
+      const int c4 = (lane & 7) * 4;
+      sts_f32x4(pl.hi + sw32b_offset(row0 + r, c4), h[0], h[1], h[2], h[3]);
+      if (DW_CROSS) {
+        const uint32_t o = sw64_offset(row0 + r, c4);
+        sts_b32x2(pl.h16 + o, pack_bf16x2(h[0], h[1]), pack_bf16x2(h[2], h[3]));
+        sts_b32x2(pl.l16 + o, pack_bf16x2(l[0], l[1]), pack_bf16x2(l[2], l[3]));
+      } else {
+        sts_f32x4(pl.lo + sw32b_offset(row0 + r, c4), l[0], l[1], l[2], l[3]);
+      }
     }
   }
 }
-__device__ __forceinline__ void store_block(const float (&val)[32], int rows, int row0, uint32_t plane_hi,
-                                            uint32_t plane_lo, int lane) {
+// Store for the lane = row pattern; val[j] holds channel j ^ 4 in lanes 4-7 of every eight (see stage_block).
+__device__ __forceinline__ void store_block(const float (&val)[32], int rows, int row0, const BlockPlanes& pl, int lane) {
   if (lane >= rows) return;
-  const uint32_t sw16 = (uint32_t)((lane >> 2) & 1) << 4;
+  const uint32_t sw = (uint32_t)((lane >> 2) & 1);
 #pragma unroll
   for (int m = 0; m < 4; ++m) {
     float h0[4], l0[4], h1[4], l1[4];
@@ -183,11 +218,21 @@ __device__ __forceinline__ void store_block(const float (&val)[32], int rows, in
       split_tf32_fast(val[m * 8 + j], h0[j], l0[j]);
       split_tf32_fast(val[m * 8 + 4 + j], h1[j], l1[j]);
     }
-    const uint32_t oa = sw32b_offset(row0 + lane, m * 8) ^ sw16, ob = oa ^ 16u;
-    sts_f32x4(plane_hi + oa, h0[0], h0[1], h0[2], h0[3]);
-    sts_f32x4(plane_lo + oa, l0[0], l0[1], l0[2], l0[3]);
-    sts_f32x4(plane_hi + ob, h1[0], h1[1], h1[2], h1[3]);
-    sts_f32x4(plane_lo + ob, l1[0], l1[1], l1[2], l1[3]);
+    const uint32_t oa = sw32b_offset(row0 + lane, m * 8) ^ (sw << 4), ob = oa ^ 16u;
+    sts_f32x4(pl.hi + oa, h0[0], h0[1], h0[2], h0[3]);
+    sts_f32x4(pl.hi + ob, h1[0], h1[1], h1[2], h1[3]);
+    if (DW_CROSS) {
+      // the eight channels of this group are one 16-byte chunk of a bf16 row; its two 8-byte halves
+      // go where this lane's channel order puts them (64-byte rows need no bank-conflict swap)
+      const uint32_t qa = sw64_offset(row0 + lane, m * 8) ^ (sw << 3), qb = qa ^ 8u;
+      sts_b32x2(pl.h16 + qa, pack_bf16x2(h0[0], h0[1]), pack_bf16x2(h0[2], h0[3]));
+      sts_b32x2(pl.h16 + qb, pack_bf16x2(h1[0], h1[1]), pack_bf16x2(h1[2], h1[3]));
+      sts_b32x2(pl.l16 + qa, pack_bf16x2(l0[0], l0[1]), pack_bf16x2(l0[2], l0[3]));
+      sts_b32x2(pl.l16 + qb, pack_bf16x2(l1[0], l1[1]), pack_bf16x2(l1[2], l1[3]));
+    } else {
+      sts_f32x4(pl.lo + oa, l0[0], l0[1], l0[2], l0[3]);
+      sts_f32x4(pl.lo + ob, l1[0], l1[1], l1[2], l1[3]);
+    }
   }
 }
 
@@ -211,7 +256,7 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
   const int tasks = x_tasks + NB;                              // warp-sized staging jobs per K block
   // BN <= 128: the dY hi and lo planes (their 32-channel blocks are equally spaced) form ONE operand
   // of 2*BN columns, so x_hi*[dy_hi | dy_lo] is a single MMA; the epilogue adds the two halves.
-  constexpr bool FUSE_HILO = BN <= 128;
+  constexpr bool FUSE_HILO = BN <= 128 && !DW_CROSS;
   constexpr uint32_t ACC_COLS = FUSE_HILO ? 2 * BN : BN;
   const uint32_t tmem_cols = ACC_COLS * (uint32_t)a.nacc;  // 64..512, a power of two
 
@@ -262,6 +307,12 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
       const uint64_t db_base = make_mn_desc(base + x_bytes, KP * 128u);
       const uint32_t stage_d = stage_bytes >> 4, x_plane_d = x_plane >> 4;
       constexpr uint32_t y_plane_d = y_plane >> 4;
+      // BF16 cross terms: the second plane of every block is split into bf16(hi) and bf16(lo) halves
+      // of 64-byte rows; x_hi16 pairs with dy_lo16 and x_lo16 with dy_hi16
+      constexpr uint32_t idesc16 = make_idesc_bf16(128, BN) | (1u << 15) | (1u << 16);
+      const uint32_t a_lbo16 = a.xblocks == 1 ? (uint32_t)g.dw * 64u : 2u * x_plane;
+      const uint64_t da16_base = make_mn_desc16(base + x_plane + (a.xblocks == 1 ? (uint32_t)(XOFF - g.pw) * 64u : 0u), a_lbo16);
+      const uint64_t db16_base = make_mn_desc16(base + x_bytes + y_plane, KP * 64u);
       const bool pm = DPROF_ON(true);
       uint32_t s = 0, par = 0;
       for (int kb = 0; kb < kblocks; ++kb) {
@@ -275,6 +326,17 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
         for (int u = 0; u < a.nacc; ++u) {  // channel blocks that share this dY block
           const uint32_t acc = tmem_acc + (uint32_t)u * ACC_COLS;
           const uint64_t ua_hi = da_hi + (uint64_t)u * (2 * x_plane_d), ua_lo = ua_hi + x_plane_d;
+          if (DW_CROSS) {
+#pragma unroll
+            for (int kg = 0; kg < KP / 8; ++kg) umma_tf32(acc, ua_hi + kg * 64, db_hi + kg * 64, idesc, (kb | kg) != 0);
+            const uint64_t a_h16 = da16_base + s * stage_d + (uint64_t)u * (2 * x_plane_d), a_l16 = a_h16 + (x_plane_d >> 1);
+            const uint64_t b_l16 = db16_base + s * stage_d, b_h16 = b_l16 + (y_plane_d >> 1);
+#pragma unroll
+            for (int kg = 0; kg < KP / 16; ++kg) umma_bf16(acc, a_h16 + kg * 64, b_l16 + kg * 64, idesc16, 1);  // 16 rows of 64 bytes
+#pragma unroll
+            for (int kg = 0; kg < KP / 16; ++kg) umma_bf16(acc, a_l16 + kg * 64, b_h16 + kg * 64, idesc16, 1);
+            continue;
+          }
 #pragma unroll
           for (int kg = 0; kg < KP / 8; ++kg) {  // 8 pixels = 8 rows of 128 bytes per MMA
             if (FUSE_HILO) {
@@ -313,15 +375,17 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
       float val[32];
       bool chunked;  // which register pattern stage_block used
       int rows, row0;
-      uint32_t p_hi, p_lo;
+      BlockPlanes pl;
       const bool pp = DPROF_ON(threadIdx.x == 0);
       DPROF_T0(pp);
       if (j < x_tasks) {
         const int blk = x_halves == 2 ? j >> 1 : j, half = x_halves == 2 ? j & 1 : 0;
         rows = half ? XR - 32 : 32;
         row0 = half * 32;
-        p_hi = xs + (uint32_t)blk * 2u * x_plane;
-        p_lo = p_hi + x_plane;
+        pl.hi = xs + (uint32_t)blk * 2u * x_plane;
+        pl.lo = pl.hi + x_plane;
+        pl.h16 = pl.lo;
+        pl.l16 = pl.lo + x_plane / 2;
         if (a.xblocks == 1) {
           // one strip; the horizontal taps are its row offsets.  The input is needed wherever it
           // exists: no split-range clipping, only image bounds
@@ -342,8 +406,10 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
         const int blk = j - x_tasks;
         rows = 32;
         row0 = blk * KP;
-        p_hi = ys;
-        p_lo = ys + y_plane;
+        pl.hi = ys;
+        pl.lo = ys + y_plane;
+        pl.l16 = pl.lo;                 // [bf16(lo) blocks][bf16(hi) blocks]: x_hi16 meets dy_lo16
+        pl.h16 = pl.lo + y_plane / 2;
         const int c0 = co0 + blk * 32;
         const int chans = max(0, min(32, g.cog - c0));
         // dY outside this split's pixel range must read as zero so that splits do not overlap
@@ -355,8 +421,8 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
       if (!mbar_wait(smem_u32(&ctrl->empty[s]), (round & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_EMPTY)) { alive = false; break; }
       if (pp) atomicAdd(a.prof + 3, (unsigned long long)(clock64() - tw)); }
       { const long long tw = pp ? clock64() : 0;
-      if (chunked) store_block_chunks(val, rows, row0, p_hi, p_lo, lane);
-      else store_block(val, rows, row0, p_hi, p_lo, lane);
+      if (chunked) store_block_chunks(val, rows, row0, pl, lane);
+      else store_block(val, rows, row0, pl, lane);
       fence_proxy_async();
       mbar_arrive(smem_u32(&ctrl->full[s]));
       if (pp) { atomicAdd(a.prof + 4, (unsigned long long)(clock64() - tw)); atomicAdd(a.prof + 5, 1ull); } }

@@ -7,7 +7,7 @@
 // of the tensor-core peak.  Three stages per chunk of tiles, all on the device:
 //   1. input_transform_kernel   d (strided view, zero padded) -> V[tile][36][Cin]
 //   2. the 36 channel contractions as ONE grouped 1x1 convolution over a `tiles`-pixel image
-//      (36*groups groups) on the persistent tcgen05 strip kernel, 3xTF32, row-major output
+//      (36*groups groups) on the persistent tcgen05 strip kernel (split-precision FP32), row-major output
 //      M[tile][36][Cout]
 //   3. output_transform_kernel  A^T m A + bias -> y (contiguous NCHW, ragged edge tiles guarded)
 // plus filter_transform_kernel  g -> U[36][Cout][Cin/groups] once per call (weights may change

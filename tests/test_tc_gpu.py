@@ -1,4 +1,4 @@
-"""Parity of the tcgen05 (3xTF32) kernels, forced through the C-ABI, against the FP64 oracle.
+"""Parity of the tcgen05 (split-precision FP32) kernels, forced through the C-ABI, against the FP64 oracle.
 Gate: per-output L2-normalised error <= 1e-4; in practice the split keeps it near 1e-6."""
 import numpy as np
 import pytest

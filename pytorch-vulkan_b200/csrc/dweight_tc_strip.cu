@@ -35,17 +35,20 @@ namespace b200 {
 namespace tcdw {
 using namespace tc;
 
-// BF16 cross terms (tc_common.cuh) are implemented for this kernel too (bf16 planes of 64-byte rows,
-// SWIZZLE_64B, same row-shift and block-stride tricks) and pass the parity tests, but dWeight is bound
-// by its producers' instruction issue, not by the tensor pipe: with them the 64-channel layers ran
-// 2-8 % slower and the others within 1 %.  They stay off here; -DB200_DW_CROSS_BF16=1 turns them on.
+// BF16 cross terms (tc_common.cuh) are implemented for this kernel too: bf16 planes of 64-byte rows
+// (SWIZZLE_64B) with the same row-shift and block-stride tricks, an accumulator of BN instead of 2*BN
+// TMEM columns and therefore up to four channel blocks sharing every staged dY block.  They pass the
+// parity tests but do not pay: the kernel is bound by its producers' global loads (about 15 bytes per
+// clock and SM with 4-byte loads in flight), not by the tensor pipe -- measured 0-5 % faster on the
+// 256/512-channel layers and 5-12 % slower on the 64-channel, 1x1 and strided ones.  Off by default;
+// -DB200_DW_CROSS_BF16=1 turns them on.
 #ifndef B200_DW_CROSS_BF16
 #define B200_DW_CROSS_BF16 0
 #endif
 constexpr bool DW_CROSS = B200_DW_CROSS_BF16 != 0;
 
 constexpr int KP = 32;          // pixels per K block (four K=8 MMA steps)
-constexpr int XR = 48;          // rows of one staged input block: KP + margin for the horizontal taps
+constexpr int XR = 40;          // rows of one staged input strip: KP + margin for the horizontal taps
 constexpr int XOFF = 4;         // row of the strip that corresponds to the first pixel of the K block
 constexpr int PRODUCER_WARPS = 16;
 constexpr int MMA_WARP = PRODUCER_WARPS;
@@ -544,11 +547,10 @@ static DwStripPlan plan_dw_strip(const ConvGeom& g, size_t budget) {
       p.blk_dc |= ((unsigned)dc & 0xFFu) << (8 * kx);
     }
   }
-  // Two channel blocks per CTA share every staged dY block (two accumulators in TMEM): the kernel is
-  // bound by the bytes its producers pull from L2, and this halves the dY bytes per MMA.  With two
-  // accumulators the column tile stays at 128 (TMEM holds 512 columns; four stages fit).
+  // Several channel blocks per CTA share every staged dY block (one TMEM accumulator each): less dY
+  // staging per MMA.  The column tile then stays at 128 (TMEM holds 512 columns).
   if (p.xblocks == 1 && g.cig >= 64) {
-    p.nacc = 2;
+    p.nacc = (DW_CROSS && g.cig >= 128) ? 4 : 2;
     p.bn = g.cog <= 64 ? 64 : 128;
   } else {
     p.bn = g.cog <= 64 ? 64 : (g.cog <= 128 ? 128 : 256);

@@ -16,9 +16,16 @@
 #include <ATen/ops/view_native.h>
 #include <torch/library.h>
 
+#include <algorithm>
+#include <array>
+#include <chrono>
 #include <cstdlib>
 #include <cstring>
+#include <deque>
+#include <functional>
 #include <mutex>
+#include <sstream>
+#include <unordered_map>
 
 namespace torch_vulkan {
 
@@ -164,15 +171,24 @@ static at::Tensor reshape_alias(const at::Tensor& self, c10::SymIntArrayRef size
 // ---- convolution -------------------------------------------------------------------------------
 static std::mutex plan_mutex;
 static std::map<std::string, uint64_t> plan_stats;
+// Plans found by the opt-in autotuner (TORCH_VULKAN_CONV_AUTOTUNE=1), FIFO of at most 256, keyed by
+// phase, budget, the sixteen geometry parameters and the memory layout class of each operand -- never
+// by addresses (csrc/ops/convolution.cpp:523-554 of the reference).
+static std::unordered_map<std::string, int> plan_cache;
+static std::deque<std::string> plan_fifo;
+static constexpr size_t kMaxConvPlans = 256;
 
 std::map<std::string, uint64_t> conv_dispatch_stats() {
   std::lock_guard<std::mutex> lock(plan_mutex);
   auto result = plan_stats;
-  for (const char* key : {"hits", "misses", "tunes", "evictions", "candidates_timed", "entries"}) result[key] += 0;
+  for (const char* key : {"hits", "misses", "tunes", "evictions", "candidates_timed"}) result[key] += 0;
+  result["entries"] = plan_cache.size();
   return result;
 }
 void clear_conv_dispatch_cache() {
   std::lock_guard<std::mutex> lock(plan_mutex);
+  plan_cache.clear();
+  plan_fifo.clear();
   plan_stats.clear();
 }
 
@@ -221,6 +237,11 @@ static int requested_algo(int phase, const b200_conv_params& p) {
   return B200_ALGO_AUTO;
 }
 
+static bool autotune_enabled() {
+  const char* tune = std::getenv("TORCH_VULKAN_CONV_AUTOTUNE");
+  return tune && !std::strcmp(tune, "1");
+}
+
 static const char* phase_name(int phase) {
   static const char* names[] = {"forward", "dinput", "dweight", "dbias"};
   return names[phase];
@@ -235,21 +256,106 @@ static const char* candidate_name(int algo, int phase) {
   }
 }
 
-struct Scratch {
-  at::Tensor tensor;
-  void* ptr = nullptr;
-  size_t bytes = 0;
-};
-// Resolves the candidate, enforces the workspace budget and allocates the scratch it needs.
-static int plan(const b200_conv_params& p, int phase, const at::TensorOptions& opts, Scratch& scratch) {
+// Runs one candidate: (algorithm id, workspace pointer, workspace bytes) -> B200_* code.
+using ConvRunner = std::function<int(int, void*, size_t)>;
+
+// Memory layout class of an operand for the plan key: 0 contiguous NCHW, 1 channels-last, 2 other.
+static int layout_class(const at::Tensor& t) {
+  if (t.is_contiguous()) return 0;
+  if (t.dim() == 4 && t.is_contiguous(at::MemoryFormat::ChannelsLast)) return 1;
+  return 2;
+}
+
+// Opt-in autotuner (csrc/ops/convolution.cpp:570-624 of the reference): on a cache miss every
+// shortlisted candidate is warmed once and timed five times in rotated order with the stream
+// synchronised around each run; the heuristic's choice is replaced only by a candidate whose median
+// is more than 5 % faster.  Returns the algorithm id to run (B200_ALGO_AUTO keeps the heuristic).
+static int tuned_algo(const b200_conv_params& p, int phase, size_t budget, const std::string& layouts,
+                      const at::TensorOptions& opts, const ConvRunner& run) {
+  const int heuristic = b200_conv2d_select(&p, phase, B200_ALGO_AUTO, budget);
+  std::vector<int> available;
+  for (int c : {B200_ALGO_DIRECT, B200_ALGO_TILED, B200_ALGO_TC, B200_ALGO_WINOGRAD})
+    if (b200_conv2d_select(&p, phase, c, budget) == c && b200_conv2d_workspace(&p, phase, c, budget) <= budget)
+      available.push_back(c);
+  if (std::find(available.begin(), available.end(), heuristic) == available.end()) return B200_ALGO_AUTO;
+  std::ostringstream key;
+  key << b200_device_name() << ':' << phase << ':' << budget << ':' << layouts;
+  for (const int v : {p.n, p.cin, p.cout, p.h, p.w, p.kh, p.kw, p.oh, p.ow, p.sh, p.sw, p.ph, p.pw, p.dh, p.dw, p.groups})
+    key << ':' << v;
+  {
+    std::lock_guard<std::mutex> lock(plan_mutex);
+    const auto it = plan_cache.find(key.str());
+    if (it != plan_cache.end() && std::find(available.begin(), available.end(), it->second) != available.end()) {
+      ++plan_stats["hits"];
+      return it->second;
+    }
+    ++plan_stats["misses"];
+  }
+  // bound the tuning cost: the one-thread-per-output kernels are only timed on small problems
+  const long double work = (long double)p.n * p.cout * p.oh * p.ow * (p.cin / p.groups) * p.kh * p.kw;
+  std::vector<int> shortlist;
+  for (int c : available)
+    if (c != B200_ALGO_DIRECT || work <= 8000000 || c == heuristic) shortlist.push_back(c);
+  const auto trial = [&](int c) {
+    // candidate-specific scratch allocation and release are part of what is timed
+    const size_t need = b200_conv2d_workspace(&p, phase, c, budget);
+    at::Tensor scratch;
+    if (need) scratch = at::empty({(int64_t)need}, opts.dtype(at::kByte));
+    B200_TORCH_CHECK(run(c, need ? scratch.data_ptr() : nullptr, need));
+    B200_TORCH_CHECK(b200_stream_sync(backend_stream()));
+  };
+  B200_TORCH_CHECK(b200_stream_sync(backend_stream()));
+  for (int c : shortlist) trial(c);
+  std::vector<std::array<double, 5>> samples(shortlist.size());
+  for (int repeat = 0; repeat < 5; ++repeat)
+    for (size_t j = 0; j < shortlist.size(); ++j) {
+      const size_t i = (j + repeat) % shortlist.size();
+      const auto start = std::chrono::steady_clock::now();
+      trial(shortlist[i]);
+      samples[i][repeat] = std::chrono::duration<double, std::nano>(std::chrono::steady_clock::now() - start).count();
+    }
+  for (auto& sample : samples) std::sort(sample.begin(), sample.end());
+  const size_t incumbent = std::find(shortlist.begin(), shortlist.end(), heuristic) - shortlist.begin();
+  int selected = heuristic;
+  double best = samples[incumbent][2];
+  for (size_t i = 0; i < shortlist.size(); ++i)
+    if (samples[i][2] < best * 0.95) {  // marginal differences are timing noise: keep the heuristic
+      best = samples[i][2];
+      selected = shortlist[i];
+    }
+  {
+    std::lock_guard<std::mutex> lock(plan_mutex);
+    ++plan_stats["tunes"];
+    plan_stats["candidates_timed"] += shortlist.size();
+    for (int c : shortlist) ++plan_stats[std::string("candidates_timed_") + phase_name(phase) + "_" + candidate_name(c, phase)];
+    if (!plan_cache.count(key.str())) {
+      if (plan_cache.size() >= kMaxConvPlans) {
+        plan_cache.erase(plan_fifo.front());
+        plan_fifo.pop_front();
+        ++plan_stats["evictions"];
+      }
+      plan_fifo.push_back(key.str());
+    }
+    plan_cache[key.str()] = selected;
+  }
+  return selected;
+}
+
+// Resolves the candidate (env controls, autotuner, heuristic), enforces the workspace budget,
+// allocates the scratch and runs it.  The tuner's trial runs write the same output; the winner is
+// executed again afterwards so that the visible result always belongs to the recorded plan.
+static void plan_and_run(const b200_conv_params& p, int phase, const at::TensorOptions& opts, const std::string& layouts,
+                         const ConvRunner& run) {
   const size_t budget = workspace_limit();
-  const int requested = phase == B200_PHASE_DBIAS ? B200_ALGO_AUTO : requested_algo(phase, p);
+  int requested = phase == B200_PHASE_DBIAS ? B200_ALGO_AUTO : requested_algo(phase, p);
+  if (requested == B200_ALGO_AUTO && phase != B200_PHASE_DBIAS && autotune_enabled())
+    requested = tuned_algo(p, phase, budget, layouts, opts, run);
   const int chosen = b200_conv2d_select(&p, phase, requested, budget);
   TORCH_CHECK(chosen >= 0, "Forced Vulkan convolution ", phase_name(phase), " candidate: ", b200_last_error());
   int algo = requested;
   size_t need = b200_conv2d_workspace(&p, phase, requested, budget);
   if (chosen == B200_ALGO_TC && (phase == B200_PHASE_FORWARD || phase == B200_PHASE_DINPUT) && need > budget) {
-    // the staged weight planes do not fit the budget: a forced request fails like the reference's
+    // the weight stage images do not fit the budget: a forced request fails like the reference's
     // forced tiled dWeight with a zero budget, an automatic one takes the CUDA-core kernel
     TORCH_CHECK(requested == B200_ALGO_AUTO, "Forced Vulkan convolution ", phase_name(phase),
                 " candidate exceeds device limits, workspace budget, or operator applicability");
@@ -260,11 +366,8 @@ static int plan(const b200_conv_params& p, int phase, const at::TensorOptions& o
       (int64_t)p.n * p.oh * p.ow > 256 && budget == 0)
     TORCH_CHECK(false, "Forced Vulkan convolution dweight candidate exceeds device limits, workspace budget, "
                        "or operator applicability");
-  if (need) {
-    scratch.tensor = at::empty({(int64_t)need}, opts.dtype(at::kByte));
-    scratch.ptr = scratch.tensor.data_ptr();
-    scratch.bytes = need;
-  }
+  at::Tensor scratch;
+  if (need) scratch = at::empty({(int64_t)need}, opts.dtype(at::kByte));
   {
     std::lock_guard<std::mutex> lock(plan_mutex);
     const int shown = algo == B200_ALGO_AUTO ? chosen : b200_conv2d_select(&p, phase, algo, budget);
@@ -276,7 +379,7 @@ static int plan(const b200_conv_params& p, int phase, const at::TensorOptions& o
       ++plan_stats["dweight_tiled_dispatches"];
     }
   }
-  return algo;
+  B200_TORCH_CHECK(run(algo, need ? scratch.data_ptr() : nullptr, need));
 }
 
 static b200_view4 view_of(const at::Tensor& t) {
@@ -324,10 +427,11 @@ static at::Tensor convolution_overrideable(const at::Tensor& input, const at::Te
     bias_stride = bias->dim() ? bias->stride(bias->dim() - 1) : 0;
   }
   auto result = at::empty({p.n, p.cout, p.oh, p.ow}, input.options());  // always contiguous NCHW
-  Scratch scratch;
-  const int algo = plan(p, B200_PHASE_FORWARD, input.options(), scratch);
-  B200_TORCH_CHECK(b200_conv2d_forward(&p, view_of(input), view_of(weight), bias_ptr, bias_stride,
-                                       result.data_ptr<float>(), scratch.ptr, scratch.bytes, algo, backend_stream()));
+  const std::string layouts = std::to_string(layout_class(input)) + std::to_string(layout_class(weight));
+  plan_and_run(p, B200_PHASE_FORWARD, input.options(), layouts, [&](int algo, void* ws, size_t ws_bytes) {
+    return b200_conv2d_forward(&p, view_of(input), view_of(weight), bias_ptr, bias_stride, result.data_ptr<float>(), ws,
+                               ws_bytes, algo, backend_stream());
+  });
   return result;
 }
 
@@ -341,27 +445,28 @@ static std::tuple<at::Tensor, at::Tensor, at::Tensor> convolution_backward_overr
                   grad_output.size(2) == p.oh && grad_output.size(3) == p.ow,
               "Vulkan convolution backward: output gradient shape mismatch");
   require_fp32_device(grad_output);
+  const std::string layouts = std::to_string(layout_class(input)) + std::to_string(layout_class(weight)) +
+                              std::to_string(layout_class(grad_output));
   at::Tensor dx, dw, db;
   if (output_mask[0]) {
     dx = at::empty(input.sizes(), input.options().memory_format(at::MemoryFormat::Contiguous));
-    Scratch scratch;
-    const int algo = plan(p, B200_PHASE_DINPUT, input.options(), scratch);
-    B200_TORCH_CHECK(b200_conv2d_dinput(&p, view_of(grad_output), view_of(weight), dx.data_ptr<float>(), scratch.ptr,
-                                        scratch.bytes, algo, backend_stream()));
+    plan_and_run(p, B200_PHASE_DINPUT, input.options(), layouts, [&](int algo, void* ws, size_t ws_bytes) {
+      return b200_conv2d_dinput(&p, view_of(grad_output), view_of(weight), dx.data_ptr<float>(), ws, ws_bytes, algo,
+                                backend_stream());
+    });
   }
   if (output_mask[1]) {
     dw = at::empty(weight.sizes(), weight.options().memory_format(at::MemoryFormat::Contiguous));
-    Scratch scratch;
-    const int algo = plan(p, B200_PHASE_DWEIGHT, input.options(), scratch);
-    B200_TORCH_CHECK(b200_conv2d_dweight(&p, view_of(input), view_of(grad_output), dw.data_ptr<float>(), scratch.ptr,
-                                         scratch.bytes, algo, backend_stream()));
+    plan_and_run(p, B200_PHASE_DWEIGHT, input.options(), layouts, [&](int algo, void* ws, size_t ws_bytes) {
+      return b200_conv2d_dweight(&p, view_of(input), view_of(grad_output), dw.data_ptr<float>(), ws, ws_bytes, algo,
+                                 backend_stream());
+    });
   }
   if (output_mask[2]) {
     db = at::empty({p.cout}, weight.options());
-    Scratch scratch;
-    plan(p, B200_PHASE_DBIAS, input.options(), scratch);
-    B200_TORCH_CHECK(b200_conv2d_dbias(&p, view_of(grad_output), db.data_ptr<float>(), scratch.ptr, scratch.bytes,
-                                       backend_stream()));
+    plan_and_run(p, B200_PHASE_DBIAS, input.options(), layouts, [&](int, void* ws, size_t ws_bytes) {
+      return b200_conv2d_dbias(&p, view_of(grad_output), db.data_ptr<float>(), ws, ws_bytes, backend_stream());
+    });
   }
   return {dx, dw, db};
 }

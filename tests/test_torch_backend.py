@@ -130,6 +130,41 @@ def test_dispatch_stats_env_controls_and_rejections(monkeypatch):
 
 
 @gpu
+def test_autotuner_times_candidates_once_and_reuses_the_plan(monkeypatch):
+    # tests/test_conv_dispatch.py:115-160 of the reference: the first call of a geometry tunes and caches,
+    # repeats hit the cache, a different memory layout is a different plan, results stay correct
+    monkeypatch.setenv("TORCH_VULKAN_CONV_AUTOTUNE", "1")
+    torch.manual_seed(3)
+    xc, wc = torch.randn(2, 32, 12, 12) * 0.2, torch.randn(32, 32, 3, 3) * 0.2
+    x = xc.to("vulkan").requires_grad_()
+    w = wc.to("vulkan").requires_grad_()
+    torch_vulkan.clear_conv_dispatch_cache()
+    y = F.conv2d(x, w, padding=1)
+    stats = torch_vulkan.conv_dispatch_stats()
+    assert stats["misses"] == 1 and stats["tunes"] == 1 and stats["hits"] == 0 and stats["entries"] == 1, stats
+    assert stats["candidates_timed"] >= 2, stats
+    assert stats.get("candidates_timed_forward_tiled_tcgen05", 0) == 1, stats
+    F.conv2d(x, w, padding=1)
+    stats = torch_vulkan.conv_dispatch_stats()
+    assert stats["hits"] == 1 and stats["tunes"] == 1 and stats["entries"] == 1, stats
+    go = torch.randn(2, 32, 12, 12) * 0.3
+    y.backward(go.to("vulkan"))   # dInput and dWeight tune separately
+    stats = torch_vulkan.conv_dispatch_stats()
+    assert stats["tunes"] == 3 and stats["entries"] == 3, stats
+    torch.testing.assert_close(y.cpu(), F.conv2d(xc, wc, padding=1), atol=3e-5, rtol=4e-4)
+    xr, wr = xc.clone().requires_grad_(), wc.clone().requires_grad_()
+    F.conv2d(xr, wr, padding=1).backward(go)
+    torch.testing.assert_close(x.grad.cpu(), xr.grad, atol=5e-5, rtol=5e-4)
+    torch.testing.assert_close(w.grad.cpu(), wr.grad, atol=5e-5, rtol=5e-4)
+    F.conv2d(x.detach().contiguous(memory_format=torch.channels_last), w.detach(), padding=1)
+    stats = torch_vulkan.conv_dispatch_stats()
+    assert stats["misses"] == 4 and stats["entries"] == 4, stats   # another layout class: another plan
+    monkeypatch.setenv("TORCH_VULKAN_CONV_AUTOTUNE", "2")
+    with pytest.raises(RuntimeError, match="AUTOTUNE"):
+        F.conv2d(x, w, padding=1)
+
+
+@gpu
 def test_mm_addmm_and_copies():
     torch.manual_seed(3)
     a, b = torch.randn(70, 33), torch.randn(50, 33)

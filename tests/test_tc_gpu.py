@@ -78,6 +78,16 @@ def test_tc_matches_golden_layer64():
     ((2, 32, 9, 10), 32, (3, 3), dict(padding=(2, 2))),           # more padding than the filter needs
     ((2, 64, 16, 16), 32, (4, 4), dict(stride=(2, 2), padding=(1, 1))),
     ((1, 32, 17, 19), 64, (3, 3), dict(stride=(3, 2), padding=(0, 2))),
+    ((2, 32, 21, 18), 32, (5, 5), dict(stride=(4, 4), padding=(2, 2))),           # sixteen phases
+    ((2, 64, 11, 23), 32, (3, 3), dict(stride=(1, 2), padding=(1, 1))),           # stride in one direction only
+    ((1, 32, 16, 16), 32, (3, 3), dict(stride=(2, 2), padding=(2, 2), dilation=(3, 3))),
+    ((2, 64, 9, 9), 64, (3, 3), dict(stride=(2, 2), padding=(1, 1), groups=2)),
+    ((2, 32, 6, 7), 32, (3, 3), dict(padding=(3, 3))),                            # padding wider than the filter reach
+    ((1, 32, 2, 2), 32, (3, 3), dict(padding=(1, 1))),                            # image smaller than the filter
+    ((3, 32, 1, 40), 32, (1, 3), dict(padding=(0, 1))),                           # one-row images
+    ((1, 32, 40, 1), 32, (3, 1), dict(stride=(2, 1), padding=(1, 0))),            # one-column images
+    ((2, 32, 8, 8), 32, (4, 4), dict(stride=(4, 4))),                             # non-overlapping patches
+    ((1, 96, 12, 12), 96, (3, 3), dict(stride=(2, 2), padding=(1, 1), groups=3)),
 ], ids=lambda s: "x".join(map(str, s[0])) + f"-co{s[1]}-k{s[2][0]}x{s[2][1]}" if isinstance(s, tuple) and len(s) == 4 else None)
 @pytest.mark.parametrize("channels_last", [False, True], ids=["nchw", "nhwc"])
 @pytest.mark.parametrize("variant", ["strip", "gather"])

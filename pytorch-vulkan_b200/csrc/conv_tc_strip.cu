@@ -40,6 +40,7 @@
 #include "tc_common.cuh"
 
 #include <algorithm>
+#include <mutex>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -699,11 +700,11 @@ size_t strip_workspace(const ConvGeom& g, int phase) {
 
 template <int BN>
 static int launch_strip(const tcs::StripArgs& a, int grid, int smem, cudaStream_t st) {
-  static int configured = 0;
-  if (configured < smem) {
-    B200_CUDA(cudaFuncSetAttribute(tcs::conv_strip_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    configured = smem;
-  }
+  // opt in once (thread-safe) to the full 227 KB of dynamic shared memory for this instantiation
+  static std::once_flag once;
+  static cudaError_t opt_in = cudaSuccess;
+  std::call_once(once, [] { opt_in = cudaFuncSetAttribute(tcs::conv_strip_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448); });
+  B200_CUDA(opt_in);
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3((unsigned)grid); cfg.blockDim = dim3(tcs::THREADS); cfg.dynamicSmemBytes = (size_t)smem; cfg.stream = st;
   cudaLaunchAttribute attr{};

@@ -28,6 +28,7 @@
 #include "tc_common.cuh"
 
 #include <algorithm>
+#include <mutex>
 #include <cstdio>
 #include <cstdlib>
 
@@ -566,12 +567,23 @@ static DwStripPlan plan_dw_strip(const ConvGeom& g, size_t budget) {
   const long long q_total = (long long)g.n * (p.gh + p.pr) * (p.gw + p.pc);
   const long long tiles = (long long)p.ci_tiles * g.kh * p.co_tiles * g.groups;
   const size_t dw_bytes = sizeof(float) * (size_t)g.cout * g.cig * g.kh * g.kw;
-  // two full waves of CTAs (one CTA per SM is resident), never a few CTAs more than that; every
-  // split at least 16 K blocks long; partials within budget
-  long long want = std::max<long long>(1, 2ll * sm_count() / tiles);
-  want = std::min<long long>(want, std::max<long long>(1, q_total / (16 * KP)));
-  want = std::min<long long>(want, 65535);
-  want = std::min<long long>(want, (long long)(budget / dw_bytes));
+  // Number of pixel splits: the one that minimises a small model of the run time in K-block units --
+  // waves of CTAs (one CTA per SM is resident) x (K blocks per split + a fixed cost per CTA for
+  // pipeline fill and the epilogue) + the finalize pass over the partials.  Every split at least 16
+  // K blocks long; partials within budget.
+  const long long kblocks_total = div_up64(q_total, KP);
+  long long most = std::max<long long>(1, kblocks_total / 16);
+  most = std::min<long long>(most, 65535);
+  most = std::min<long long>(most, (long long)(budget / dw_bytes));
+  most = std::min<long long>(most, 4ll * sm_count() / tiles + 1);
+  const double cta_fixed = 10.0, finalize_per_split = (double)dw_bytes / 3.3e6;  // ~3 TB/s against ~1.1 us per K block
+  long long want = 1;
+  double best = 0.0;
+  for (long long sp = 1; sp <= std::max<long long>(1, most); ++sp) {
+    const double waves = (double)div_up64(tiles * sp, sm_count());
+    const double cost = waves * ((double)div_up64(kblocks_total, sp) + cta_fixed) + (sp > 1 ? finalize_per_split * (double)sp : 0.0);
+    if (sp == 1 || cost < best) { best = cost; want = sp; }
+  }
   long long span = div_up64(q_total, KP) * KP, splits = 1;
   if (want >= 2) {
     span = div_up64(div_up64(q_total, want), KP) * KP;
@@ -592,11 +604,11 @@ size_t dweight_strip_workspace(const ConvGeom& g, size_t budget) { return tcdw::
 
 template <int BN>
 static int launch_dw_strip(const tcdw::DwStripArgs& a, dim3 grid, int smem, cudaStream_t st) {
-  static int configured = 0;
-  if (configured < smem) {
-    B200_CUDA(cudaFuncSetAttribute(tcdw::dweight_strip_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    configured = smem;
-  }
+  // opt in once (thread-safe) to the full 227 KB of dynamic shared memory for this instantiation
+  static std::once_flag once;
+  static cudaError_t opt_in = cudaSuccess;
+  std::call_once(once, [] { opt_in = cudaFuncSetAttribute(tcdw::dweight_strip_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448); });
+  B200_CUDA(opt_in);
   tcdw::dweight_strip_kernel<BN><<<grid, tcdw::THREADS, smem, st>>>(a);
   count_launch();
   return launch_check("dweight_strip_kernel");

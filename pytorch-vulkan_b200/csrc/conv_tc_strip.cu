@@ -113,8 +113,13 @@ struct Ctrl {  // lives behind the operand stages in shared memory
   unsigned char ph_a[MAX_PHASES], ph_b[MAX_PHASES], tap_start[MAX_PHASES + 1];
 };
 
-// Cycle accounting for one thread of each role in CTA 0 (diagnostics only).
-#define PROF_ON(leader) (a.prof != nullptr && blockIdx.x == 0 && (leader))
+// Cycle accounting for one thread of each role in CTA 0 (diagnostics only).  The probes sit in the
+// issuing loops, where every extra instruction costs tensor time, so they are compiled in only with
+// -DB200_ROLE_PROFILE=1 (then B200_STRIP_PROFILE=1 in the environment prints them).
+#ifndef B200_ROLE_PROFILE
+#define B200_ROLE_PROFILE 0
+#endif
+#define PROF_ON(leader) (B200_ROLE_PROFILE && a.prof != nullptr && blockIdx.x == 0 && (leader))
 #define PROF_T0(on) const long long prof_t0__ = (on) ? clock64() : 0
 #define PROF_ADD(on, slot) do { if (on) atomicAdd(a.prof + (slot), (unsigned long long)(clock64() - prof_t0__)); } while (0)
 
@@ -787,7 +792,7 @@ int strip_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* b
   if (!a.status) return fail(B200_ECUDA, "device status word is not allocated");
   static unsigned long long* prof_buf = nullptr;
   const char* prof_env = getenv("B200_STRIP_PROFILE");
-  const bool profiling = prof_env && prof_env[0] == '1';
+  const bool profiling = B200_ROLE_PROFILE && prof_env && prof_env[0] == '1';
   if (profiling) {
     if (!prof_buf) B200_CUDA(cudaMalloc(&prof_buf, 16 * sizeof(unsigned long long)));
     B200_CUDA(cudaMemsetAsync(prof_buf, 0, 16 * sizeof(unsigned long long), st));

@@ -81,7 +81,11 @@ struct DwStripArgs {
   unsigned long long* prof;  // optional cycle counters of CTA (0,0) (B200_STRIP_PROFILE=1), else null
 };
 
-#define DPROF_ON(leader) (a.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && (leader))
+// role cycle probes: compiled in only with -DB200_ROLE_PROFILE=1 (see conv_tc_strip.cu)
+#ifndef B200_ROLE_PROFILE
+#define B200_ROLE_PROFILE 0
+#endif
+#define DPROF_ON(leader) (B200_ROLE_PROFILE && a.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && (leader))
 #define DPROF_T0(on) const long long prof_t0__ = (on) ? clock64() : 0
 #define DPROF_ADD(on, slot) do { if (on) atomicAdd(a.prof + (slot), (unsigned long long)(clock64() - prof_t0__)); } while (0)
 
@@ -648,7 +652,7 @@ int dweight_strip(const ConvGeom& g, View4 x, View4 dy, float* dw, void* ws, siz
   const dim3 grid((unsigned)gx, (unsigned)plan.splits);
   static unsigned long long* prof_buf = nullptr;
   const char* prof_env = getenv("B200_STRIP_PROFILE");
-  const bool profiling = prof_env && prof_env[0] == '1';
+  const bool profiling = B200_ROLE_PROFILE && prof_env && prof_env[0] == '1';
   if (profiling) {
     if (!prof_buf) B200_CUDA(cudaMalloc(&prof_buf, 16 * sizeof(unsigned long long)));
     B200_CUDA(cudaMemsetAsync(prof_buf, 0, 16 * sizeof(unsigned long long), st));

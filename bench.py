@@ -186,7 +186,7 @@ class Layer:
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture summarised in
-# profiles/tc_strip_kernels_resnet_sweep.md (one layer of the sweep; bytes, not a live measurement)
+# the strip-kernel summary under profiles/ (one layer of the sweep; bytes, not a live measurement)
 NCU_TRAFFIC = {
     "tc_strip_dweight": {"bytes_per_launch": 53.9e6,
                          "note": "ncu, layer 128->128 28x28 3x3 batch 64 NCHW: 51.4 MB read + 2.5 MB written per "

@@ -374,8 +374,8 @@ def main():
                     "traffic": NCU_TRAFFIC.get(dominant, {}).get("bytes_per_launch"),
                     "traffic_note": NCU_TRAFFIC.get(dominant, {}).get("note"),
                     "peak_source": f"{pk['source']}: sustained bf16 {pk['bf16_sustained']} TFLOP/s / 2 (TF32 rate); "
-                                   "3xTF32 (dWeight) issues 3 TF32 passes per algorithmic MAC, ceiling = peak/3; forward/dInput issue one TF32 and "
-                                   "one BF16 pass of equal duration, ceiling = peak/2",
+                                   "3xTF32 issues 3 TF32 passes per algorithmic MAC, ceiling = peak/3; with BF16 cross terms (forward, dInput, "
+                                   "dWeight from 128 channels) one TF32 and one BF16 pass of equal duration, ceiling = peak/2",
                     "families": fam_stats}
         cpu = None if args.no_cpu else cpu_sample(3, 1)
         line = {
@@ -385,7 +385,7 @@ def main():
             "config": {"workload": WORKLOAD, "global_batch": BATCH * world, "parallelism": f"dp{world}",
                        "l2": "inputs larger than L2 (1.7 GB working set per step), no flush needed",
                        "numerics": "split-precision FP32 on tcgen05, FP32 accumulate: forward/dInput TF32 hi*hi + BF16 cross terms, "
-                                   "dWeight 3xTF32; FP32 FMA on the CUDA-core paths"},
+                                   "dWeight the same from 128 input channels, else 3xTF32; FP32 FMA on the CUDA-core paths"},
             "clocks": clocks,
             "e2e": {"value": world * step_flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                     "h2d_bytes_per_step": sum(l.h2d for l in layers), "d2h_bytes_per_step": sum(l.d2h for l in layers),

@@ -36,17 +36,13 @@ namespace b200 {
 namespace tcdw {
 using namespace tc;
 
-// BF16 cross terms (tc_common.cuh) are implemented for this kernel too: bf16 planes of 64-byte rows
-// (SWIZZLE_64B) with the same row-shift and block-stride tricks, an accumulator of BN instead of 2*BN
-// TMEM columns and therefore up to four channel blocks sharing every staged dY block.  They pass the
-// parity tests but do not pay: the kernel is bound by its producers' global loads (about 15 bytes per
-// clock and SM with 4-byte loads in flight), not by the tensor pipe -- measured 0-5 % faster on the
-// 256/512-channel layers and 5-12 % slower on the 64-channel, 1x1 and strided ones.  Off by default;
-// -DB200_DW_CROSS_BF16=1 turns them on.
-#ifndef B200_DW_CROSS_BF16
-#define B200_DW_CROSS_BF16 0
-#endif
-constexpr bool DW_CROSS = B200_DW_CROSS_BF16 != 0;
+// BF16 cross terms (tc_common.cuh) in this kernel: bf16 planes of 64-byte rows (SWIZZLE_64B) with the
+// same row-shift and block-stride tricks as the TF32 planes.  The kernel is bound by what its producers
+// pull from L2 (about 15-20 bytes per clock and SM for 128-byte pieces, loads or bulk copies alike), so
+// the cross terms pay only where they cut that traffic: an accumulator then takes BN instead of 2*BN
+// TMEM columns, and FOUR channel blocks can share every staged dY block.  Measured: 128/256/512-channel
+// 3x3 layers 12-20 % faster, 64-channel, 1x1 and strided ones 2-8 % slower -- so the plan turns them
+// on exactly when it can use four accumulators (plan_dw_strip); everything else runs 3xTF32.
 
 constexpr int KP = 32;          // pixels per K block (four K=8 MMA steps)
 constexpr int XR = 40;          // rows of one staged input strip: KP + margin for the horizontal taps
@@ -194,6 +190,7 @@ struct BlockPlanes {
 };
 // Store for the channels-last load pattern: eight lanes write the eight 16-byte chunks of one row
 // (a whole row per quarter warp: conflict-free in any swizzle).
+template <bool DW_CROSS>
 __device__ __forceinline__ void store_block_chunks(const float (&val)[32], int rows, int row0, const BlockPlanes& pl, int lane) {
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
@@ -215,6 +212,7 @@ __device__ __forceinline__ void store_block_chunks(const float (&val)[32], int r
   }
 }
 // Store for the lane = row pattern; val[j] holds channel j ^ 4 in lanes 4-7 of every eight (see stage_block).
+template <bool DW_CROSS>
 __device__ __forceinline__ void store_block(const float (&val)[32], int rows, int row0, const BlockPlanes& pl, int lane) {
   if (lane >= rows) return;
   const uint32_t sw = (uint32_t)((lane >> 2) & 1);
@@ -244,7 +242,7 @@ __device__ __forceinline__ void store_block(const float (&val)[32], int rows, in
   }
 }
 
-template <int BN>
+template <int BN, bool DW_CROSS>
 __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStripArgs a) {
   extern __shared__ unsigned char smem_raw[];
   const unsigned long long prof_start = a.prof ? global_ns() : 0;
@@ -429,8 +427,8 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
       if (!mbar_wait(smem_u32(&ctrl->empty[s]), (round & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_EMPTY)) { alive = false; break; }
       if (pp) atomicAdd(a.prof + 3, (unsigned long long)(clock64() - tw)); }
       { const long long tw = pp ? clock64() : 0;
-      if (chunked) store_block_chunks(val, rows, row0, pl, lane);
-      else store_block(val, rows, row0, pl, lane);
+      if (chunked) store_block_chunks<DW_CROSS>(val, rows, row0, pl, lane);
+      else store_block<DW_CROSS>(val, rows, row0, pl, lane);
       fence_proxy_async();
       mbar_arrive(smem_u32(&ctrl->full[s]));
       if (pp) { atomicAdd(a.prof + 4, (unsigned long long)(clock64() - tw)); atomicAdd(a.prof + 5, 1ull); } }
@@ -513,6 +511,7 @@ __global__ void __launch_bounds__(256) finalize_partials_kernel(const float* __r
 
 struct DwStripPlan {
   bool ok = false;
+  bool cross = false;  // BF16 cross terms (four accumulators)
   int bn = 0, xblocks = 1, nacc = 1, xr = XR, blocks_are_taps = 0, stages = 0, smem = 0, ci_tiles = 0, co_tiles = 0, splits = 1, span = 0;
   int gh = 0, gw = 0, pr = 0, pc = 0;  // pixel grid (covers dY and every phase sub-image of x) and its zero padding
   unsigned blk_b = 0, blk_dc = 0;
@@ -555,7 +554,8 @@ static DwStripPlan plan_dw_strip(const ConvGeom& g, size_t budget) {
   // Several channel blocks per CTA share every staged dY block (one TMEM accumulator each): less dY
   // staging per MMA.  The column tile then stays at 128 (TMEM holds 512 columns).
   if (p.xblocks == 1 && g.cig >= 64) {
-    p.nacc = (DW_CROSS && g.cig >= 128) ? 4 : 2;
+    p.cross = g.cig >= 128;
+    p.nacc = p.cross ? 4 : 2;
     p.bn = g.cog <= 64 ? 64 : 128;
   } else {
     p.bn = g.cog <= 64 ? 64 : (g.cog <= 128 ? 128 : 256);
@@ -606,14 +606,14 @@ static DwStripPlan plan_dw_strip(const ConvGeom& g, size_t budget) {
 bool dweight_strip_supported(const ConvGeom& g) { return tcdw::plan_dw_strip(g, 0).ok; }
 size_t dweight_strip_workspace(const ConvGeom& g, size_t budget) { return tcdw::plan_dw_strip(g, budget).bytes; }
 
-template <int BN>
+template <int BN, bool CROSS>
 static int launch_dw_strip(const tcdw::DwStripArgs& a, dim3 grid, int smem, cudaStream_t st) {
   // opt in once (thread-safe) to the full 227 KB of dynamic shared memory for this instantiation
   static std::once_flag once;
   static cudaError_t opt_in = cudaSuccess;
-  std::call_once(once, [] { opt_in = cudaFuncSetAttribute(tcdw::dweight_strip_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448); });
+  std::call_once(once, [] { opt_in = cudaFuncSetAttribute(tcdw::dweight_strip_kernel<BN, CROSS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448); });
   B200_CUDA(opt_in);
-  tcdw::dweight_strip_kernel<BN><<<grid, tcdw::THREADS, smem, st>>>(a);
+  tcdw::dweight_strip_kernel<BN, CROSS><<<grid, tcdw::THREADS, smem, st>>>(a);
   count_launch();
   return launch_check("dweight_strip_kernel");
 }
@@ -660,8 +660,9 @@ int dweight_strip(const ConvGeom& g, View4 x, View4 dy, float* dw, void* ws, siz
     B200_CUDA(cudaMemsetAsync(prof_buf + 14, 0xFF, sizeof(unsigned long long), st));
     a.prof = prof_buf;
   }
-  int rc = plan.bn == 64 ? launch_dw_strip<64>(a, grid, plan.smem, st)
-         : plan.bn == 128 ? launch_dw_strip<128>(a, grid, plan.smem, st) : launch_dw_strip<256>(a, grid, plan.smem, st);
+  int rc = plan.cross ? (plan.bn == 64 ? launch_dw_strip<64, true>(a, grid, plan.smem, st) : launch_dw_strip<128, true>(a, grid, plan.smem, st))
+         : plan.bn == 64 ? launch_dw_strip<64, false>(a, grid, plan.smem, st)
+         : plan.bn == 128 ? launch_dw_strip<128, false>(a, grid, plan.smem, st) : launch_dw_strip<256, false>(a, grid, plan.smem, st);
   if (rc) return rc;
   if (profiling) {
     unsigned long long h[16];

@@ -188,8 +188,8 @@ class Layer:
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture summarised in
 # the strip-kernel summary under profiles/ (one layer of the sweep; bytes, not a live measurement)
 NCU_TRAFFIC = {
-    "tc_strip_dweight": {"bytes_per_launch": 53.9e6,
-                         "note": "ncu, layer 128->128 28x28 3x3 batch 64 NCHW: 51.4 MB read + 2.5 MB written per "
+    "tc_strip_dweight": {"bytes_per_launch": 53.7e6,
+                         "note": "ncu, layer 128->128 28x28 3x3 batch 64 NCHW: 51.5 MB read + 2.2 MB written per "
                                  "launch against 51.9 MB algorithmic (x + dy + dW)"},
     "tc_strip_forward": {"bytes_per_launch": 26.9e6,
                          "note": "ncu, layer 128->128 28x28 3x3 batch 64: 26.9 MB read per launch (x + filter); the "

@@ -88,6 +88,8 @@ def test_tc_matches_golden_layer64():
     ((1, 32, 40, 1), 32, (3, 1), dict(stride=(2, 1), padding=(1, 0))),            # one-column images
     ((2, 32, 8, 8), 32, (4, 4), dict(stride=(4, 4))),                             # non-overlapping patches
     ((1, 96, 12, 12), 96, (3, 3), dict(stride=(2, 2), padding=(1, 1), groups=3)),
+    ((2, 160, 10, 10), 64, (3, 3), dict(padding=(1, 1))),         # dWeight: four channel blocks per CTA, second CTA one block
+    ((2, 256, 6, 6), 96, (3, 3), dict(padding=(1, 1), groups=2)),  # ... per group
 ], ids=lambda s: "x".join(map(str, s[0])) + f"-co{s[1]}-k{s[2][0]}x{s[2][1]}" if isinstance(s, tuple) and len(s) == 4 else None)
 @pytest.mark.parametrize("channels_last", [False, True], ids=["nchw", "nhwc"])
 @pytest.mark.parametrize("variant", ["strip", "gather"])
@@ -119,6 +121,14 @@ def test_tc_dweight_split_boundaries_and_determinism():
     a = b200conv.conv2d_backward(go, x, w, padding=(1, 1), mask=(False, True, False), algo="tc")[1]
     b = b200conv.conv2d_backward(go, x, w, padding=(1, 1), mask=(False, True, False), algo="tc")[1]
     np.testing.assert_array_equal(a, b)
+
+
+def test_tc_dweight_four_accumulators_with_ragged_channel_blocks():
+    # 136 and 200 input channels: the last 32-channel block of the last CTA is partly / wholly empty
+    for cin, cout in ((136, 32), (200, 48)):
+        errs = _run_case((1, cin, 9, 12), cout, (3, 3), padding=(1, 1), seed=cin, phases=("dw",))
+        assert errs["dw"] <= GATE
+        assert b200conv.last_kernel() == "tc_strip_dweight"
 
 
 @pytest.mark.parametrize("M,K,N", [(300, 96, 200), (128, 32, 16), (1000, 256, 64), (77, 64, 513)])

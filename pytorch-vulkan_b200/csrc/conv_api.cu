@@ -52,7 +52,9 @@ static int dbias_slabs(const ConvGeom& g, View4 dy, size_t budget) {
   const bool channels_inner = dy.s1 == 1 && dy.s3 != 1;
   const long long ctas = channels_inner ? div_up64(g.cout, 32) : g.cout;
   long long slabs = div_up64(4ll * std::max(1, sm_count()), ctas);
-  const long long limit = channels_inner ? div_up64((long long)g.n * g.oh * g.ow, 256) : g.n;
+  // channels-last: a CTA pass covers 32 pixels, give every slab at least eight passes;
+  // planes: a warp takes an image, a CTA eight of them
+  const long long limit = channels_inner ? div_up64((long long)g.n * g.oh * g.ow, 256) : div_up64(g.n, 8);
   slabs = std::max<long long>(1, std::min<long long>(slabs, limit));
   slabs = std::min<long long>(slabs, (long long)(budget / (sizeof(float) * g.cout)));
   return (int)std::max<long long>(1, slabs);

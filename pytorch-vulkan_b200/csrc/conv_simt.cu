@@ -401,34 +401,43 @@ __device__ __forceinline__ float warp_sum(float v) {
   return v;
 }
 
+// Planes contiguous (NCHW): one CTA per (channel, slab of images); each warp takes whole image
+// planes (8 in flight per CTA), lanes stream the plane with 16-byte loads where it is aligned.
 __global__ void __launch_bounds__(256) dbias_rows_kernel(ConvGeom g, View4 go, float* out, int slabs) {
   const int oc = blockIdx.x, slab = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int per = (g.n + slabs - 1) / slabs;
   const int b0 = slab * per, b1 = min(g.n, b0 + per);
   const int sp = g.oh * g.ow;
   const bool dense = go.s3 == 1 && go.s2 == g.ow;
   float sum = 0.f;
-  for (long long b = b0; b < b1; ++b) {
+  for (long long b = b0 + warp; b < b1; b += 8) {
     const float* base = go.ptr + b * go.s0 + oc * go.s1;
     if (dense) {
-      const bool vec = ((reinterpret_cast<uintptr_t>(base) & 15) == 0);
       int i = 0;
-      if (vec) {
+      if ((reinterpret_cast<uintptr_t>(base) & 15) == 0) {
         const float4* v4 = reinterpret_cast<const float4*>(base);
-        for (int q = threadIdx.x; q < sp / 4; q += 256) {
+        const int quads = sp / 4;
+        int q = lane;
+        for (; q + 96 < quads; q += 128) {  // four independent loads in flight per lane
+          const float4 a0 = __ldg(v4 + q), a1 = __ldg(v4 + q + 32), a2 = __ldg(v4 + q + 64), a3 = __ldg(v4 + q + 96);
+          sum += ((a0.x + a0.y) + (a0.z + a0.w)) + ((a1.x + a1.y) + (a1.z + a1.w)) + ((a2.x + a2.y) + (a2.z + a2.w)) +
+                 ((a3.x + a3.y) + (a3.z + a3.w));
+        }
+        for (; q < quads; q += 32) {
           const float4 v = __ldg(v4 + q);
           sum += (v.x + v.y) + (v.z + v.w);
         }
-        i = (sp / 4) * 4;
+        i = quads * 4;
       }
-      for (int q = i + threadIdx.x; q < sp; q += 256) sum += base[q];
+      for (int q = i + lane; q < sp; q += 32) sum += __ldg(base + q);
     } else {
-      for (int q = threadIdx.x; q < sp; q += 256) sum += base[(q / g.ow) * go.s2 + (q % g.ow) * go.s3];
+      for (int q = lane; q < sp; q += 32) sum += __ldg(base + (q / g.ow) * go.s2 + (q % g.ow) * go.s3);
     }
   }
   __shared__ float warp_part[8];
   sum = warp_sum(sum);
-  if ((threadIdx.x & 31) == 0) warp_part[threadIdx.x >> 5] = sum;
+  if (lane == 0) warp_part[warp] = sum;
   __syncthreads();
   if (threadIdx.x < 32) {
     float v = threadIdx.x < 8 ? warp_part[threadIdx.x] : 0.f;
@@ -437,27 +446,60 @@ __global__ void __launch_bounds__(256) dbias_rows_kernel(ConvGeom g, View4 go, f
   }
 }
 
-__global__ void __launch_bounds__(256) dbias_channels_kernel(ConvGeom g, View4 go, float* out, int slabs) {
-  const int oc = blockIdx.x * 32 + (threadIdx.x & 31), py = threadIdx.x >> 5, slab = blockIdx.y;
+// Channels contiguous (channels-last): one CTA per (block of 32 channels, slab of pixels); eight lanes
+// cover the 32 channels of a pixel with one 16-byte load each, so a warp reads four whole 128-byte
+// pieces per instruction and the CTA 32 pixels.  `dense` = pixels at a constant stride (true
+// channels-last); otherwise the pixel index is split into (image, row, column).
+__global__ void __launch_bounds__(256) dbias_channels_kernel(ConvGeom g, View4 go, float* out, int slabs, int dense) {
+  const int c4 = (threadIdx.x & 7) * 4, prow = threadIdx.x >> 3, slab = blockIdx.y;  // 32 pixel rows per CTA pass
+  const int oc0 = blockIdx.x * 32 + c4;
   const long long P = (long long)g.n * g.oh * g.ow;
   const long long per = (P + slabs - 1) / slabs;
   const long long p0 = slab * per, p1 = min(P, p0 + per);
   const int sp = g.oh * g.ow;
-  float sum = 0.f;
-  if (oc < g.cout)
-    for (long long q = p0 + py; q < p1; q += 8) {
-      const long long b = q / sp;
-      const int pos = (int)(q % sp);
-      sum += go.ptr[b * go.s0 + oc * go.s1 + (pos / g.ow) * go.s2 + (pos % g.ow) * go.s3];
+  const bool vec = oc0 + 3 < g.cout && ((reinterpret_cast<uintptr_t>(go.ptr) & 15) == 0) && go.s0 % 4 == 0 && go.s2 % 4 == 0 &&
+                   go.s3 % 4 == 0;
+  float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+  long long q = p0 + prow;
+  if (dense && vec) {  // four independent 16-byte loads in flight per thread
+    const float* src = go.ptr + oc0;
+    for (; q + 96 < p1; q += 128) {
+      const float4 a0 = __ldg(reinterpret_cast<const float4*>(src + q * go.s3));
+      const float4 a1 = __ldg(reinterpret_cast<const float4*>(src + (q + 32) * go.s3));
+      const float4 a2 = __ldg(reinterpret_cast<const float4*>(src + (q + 64) * go.s3));
+      const float4 a3 = __ldg(reinterpret_cast<const float4*>(src + (q + 96) * go.s3));
+      sum.x += (a0.x + a1.x) + (a2.x + a3.x); sum.y += (a0.y + a1.y) + (a2.y + a3.y);
+      sum.z += (a0.z + a1.z) + (a2.z + a3.z); sum.w += (a0.w + a1.w) + (a2.w + a3.w);
     }
-  __shared__ float part[8][33];
-  part[py][threadIdx.x & 31] = sum;
+  }
+  for (; q < p1; q += 32) {
+    long long off;
+    if (dense) off = q * go.s3;
+    else {
+      const long long b = q / sp;
+      const int pos = (int)(q - b * sp);
+      off = b * go.s0 + (pos / g.ow) * go.s2 + (pos % g.ow) * go.s3;
+    }
+    const float* src = go.ptr + off + oc0;
+    if (vec) {
+      const float4 v = __ldg(reinterpret_cast<const float4*>(src));
+      sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+    } else {
+      if (oc0 < g.cout) sum.x += __ldg(src);
+      if (oc0 + 1 < g.cout) sum.y += __ldg(src + 1);
+      if (oc0 + 2 < g.cout) sum.z += __ldg(src + 2);
+      if (oc0 + 3 < g.cout) sum.w += __ldg(src + 3);
+    }
+  }
+  __shared__ float4 part[32][9];
+  part[prow][threadIdx.x & 7] = sum;
   __syncthreads();
-  if (py == 0 && oc < g.cout) {
+  if (threadIdx.x < 32) {  // thread t sums channel t of the block over the 32 pixel rows, in order
     float v = 0.f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) v += part[i][threadIdx.x];
-    out[(long long)slab * g.cout + oc] = v;
+#pragma unroll 8
+    for (int i = 0; i < 32; ++i) v += reinterpret_cast<const float*>(&part[i][threadIdx.x >> 2])[threadIdx.x & 3];
+    const int oc = blockIdx.x * 32 + threadIdx.x;
+    if (oc < g.cout) out[(long long)slab * g.cout + oc] = v;
   }
 }
 
@@ -466,7 +508,9 @@ int dbias_reduce(const ConvGeom& g, View4 dy, float* db, float* partial, int sla
   float* out = slabs > 1 ? partial : db;
   const bool channels_inner = dy.s1 == 1 && dy.s3 != 1;
   if (channels_inner) {
-    dbias_channels_kernel<<<dim3((unsigned)div_up64(g.cout, 32), (unsigned)slabs), 256, 0, st>>>(g, dy, out, slabs);
+    // true channels-last: consecutive pixels of the whole batch sit at one constant stride
+    const int dense = dy.s2 == (long long)g.ow * dy.s3 && dy.s0 == (long long)g.oh * dy.s2;
+    dbias_channels_kernel<<<dim3((unsigned)div_up64(g.cout, 32), (unsigned)slabs), 256, 0, st>>>(g, dy, out, slabs, dense);
   } else {
     if (slabs > g.n) slabs = g.n;
     out = slabs > 1 ? partial : db;

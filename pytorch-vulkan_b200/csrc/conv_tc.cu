@@ -575,8 +575,10 @@ static bool strip_allowed() {
 }
 
 bool tc_supported(const ConvGeom& g, int phase) {
-  if (phase == B200_PHASE_FORWARD) return g.cig % KBLK == 0 && g.cog >= 16;
-  if (phase == B200_PHASE_DINPUT) return g.cog % KBLK == 0 && g.cig >= 16;
+  // the gather kernels need the reduction channels in blocks of 32; the strip kernel pads a ragged block
+  const bool strip = (phase == B200_PHASE_FORWARD || phase == B200_PHASE_DINPUT) && strip_allowed() && strip_supported(g, phase);
+  if (phase == B200_PHASE_FORWARD) return g.cog >= 16 && (g.cig % KBLK == 0 || strip);
+  if (phase == B200_PHASE_DINPUT) return g.cig >= 16 && (g.cog % KBLK == 0 || strip);
   if (phase == B200_PHASE_DWEIGHT) return g.cog >= 16 && g.cig * g.kh * g.kw >= 32;
   return false;
 }

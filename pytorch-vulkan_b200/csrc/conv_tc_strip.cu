@@ -307,9 +307,9 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
     // goes to warp (n*chunks + c) % 8, so short strips (1x1 filters) keep several stages in flight.
     const int aw = warp - EPI_WARPS;
     const int chunks = (a.strip_rows + 31) / 32;
-    const bool vec_ok = a.act.s1 == 1 && ((reinterpret_cast<uintptr_t>(a.act.ptr) & 15) == 0) &&
+    const bool vec_layout = a.act.s1 == 1 && a.kc % 4 == 0 && ((reinterpret_cast<uintptr_t>(a.act.ptr) & 15) == 0) &&
                         (a.act.s0 % 4 == 0) && (a.act.s2 % 4 == 0) && (a.act.s3 % 4 == 0);
-    const bool chunked = vec_ok && a.act.s3 < 256;  // eight lanes per pixel (see below)
+    const bool chunked_layout = vec_layout && a.act.s3 < 256;  // eight lanes per pixel (see below)
     const int s1 = (int)a.act.s1;
     const int my_units = a.units > (int)blockIdx.x ? (a.units - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
     const int my_tiles = my_units * a.unit;
@@ -335,11 +335,15 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
       const int q = m_tile * BLOCK_M - a.halo + r;
       bool ok = r < a.strip_rows && q >= 0 && q < a.q_total;
       const float* src = a.act.ptr;
+      const int phase = a.phase_on_n ? 0 : (int)a.div_cbpp.div((uint32_t)cb), cbl = cb - phase * a.cb_per_phase;
+      // the last channel block of a group may be ragged (channel counts that are no multiple of 32):
+      // it takes the masked one-value-per-load path, channels beyond the group read as zero
+      const int nvalid = min(KBLK, a.kc - cbl * KBLK);
+      const bool chunked = chunked_layout && nvalid == KBLK, vec_ok = vec_layout && nvalid == KBLK;
       if (ok) {
         const int n = (int)a.img_div.div((uint32_t)q);
         const int rem = q - n * img_pitch;
         const int y = (int)a.row_div.div((uint32_t)rem), x = rem - y * row_pitch;
-        const int phase = a.phase_on_n ? 0 : (int)a.div_cbpp.div((uint32_t)cb), cbl = cb - phase * a.cb_per_phase;
         const int iy = a.phase_on_n ? y : y * a.sph + ctrl->ph_a[phase], ix = a.phase_on_n ? x : x * a.spw + ctrl->ph_b[phase];
         ok = y < a.H && x < a.W && iy < a.act_h && ix < a.act_w;
         src += n * a.act.s0 + ((long long)group * a.kc + cbl * KBLK) * a.act.s1 + (long long)iy * a.act.s2 + (long long)ix * a.act.s3;
@@ -365,7 +369,7 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
         }
       } else {
 #pragma unroll
-        for (int j = 0; j < KBLK; ++j) v[j] = ok ? __ldg(src + j * s1) : 0.f;  // 32-bit offsets: two instructions per value
+        for (int j = 0; j < KBLK; ++j) v[j] = (ok && j < nvalid) ? __ldg(src + j * s1) : 0.f;  // 32-bit offsets: two instructions per value
       }
       {
         const long long tw = pa ? clock64() : 0;
@@ -545,7 +549,7 @@ __global__ void __launch_bounds__(256) stage_weights_kernel(ConvGeom g, View4 w,
   const long long i = blockIdx.x * 256ll + threadIdx.x;
   if (i >= total) return;
   const int kc = is_dx ? g.cog : g.cig, nc = is_dx ? g.cig : g.cog;
-  const int cpp = kc / KBLK;
+  const int cpp = (kc + KBLK - 1) / KBLK;
   const int k = (int)(i % KBLK);
   const int row = (int)((i / KBLK) % bn);
   const long long image = i / ((long long)KBLK * bn);
@@ -574,7 +578,7 @@ __global__ void __launch_bounds__(256) stage_weights_kernel(ConvGeom g, View4 w,
   }
   const int r = n_tile * bn + row, c = cbl * KBLK + k;
   float v = 0.f;
-  if (r < nc) {
+  if (r < nc && c < kc) {  // rows beyond the column count and channels beyond a ragged last block are zero
     const int co = is_dx ? c : r, ci = is_dx ? r : c;
     v = w.ptr[((long long)grp * g.cog + co) * w.s0 + ci * w.s1 + tt.ky[tap] * w.s2 + tt.kx[tap] * w.s3];
   }
@@ -608,7 +612,9 @@ struct StripPlan {
 static StripPlan plan_strip(const ConvGeom& g, bool is_dx) {
   StripPlan p;
   const int kc = is_dx ? g.cog : g.cig, nc = is_dx ? g.cig : g.cog;
-  if (kc % KBLK != 0 || nc < 16 || g.kh * g.kw > MAX_TAPS) return p;
+  // a ragged last channel block is padded with zeros; below 16 channels the padding would more than
+  // double the work and the CUDA-core kernels are the better choice
+  if (kc < 16 || nc < 16 || g.kh * g.kw > MAX_TAPS) return p;
   if (g.sh * g.sw > MAX_PHASES || g.sh > 255 || g.sw > 255) return p;
   p.sph = g.sh; p.spw = g.sw;
   p.act_h = is_dx ? g.oh : g.h; p.act_w = is_dx ? g.ow : g.w;
@@ -700,7 +706,7 @@ size_t strip_workspace(const ConvGeom& g, int phase) {
   const size_t kc = is_dx ? g.cog : g.cig, nc = is_dx ? g.cig : g.cog;
   size_t cols = 0;
   for (size_t bn : {256, 128, 64}) cols = std::max(cols, (nc + bn - 1) / bn * bn);
-  return 2 * sizeof(float) * (size_t)g.groups * cols * kc * g.kh * g.kw;
+  return 2 * sizeof(float) * (size_t)g.groups * cols * ((kc + 31) / 32 * 32) * g.kh * g.kw;  // ragged last channel block padded
 }
 
 template <int BN>
@@ -729,7 +735,8 @@ int strip_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* b
   const int kc = is_dx ? g.cog : g.cig, nc = is_dx ? g.cig : g.cog;
   const int tiles_pp = (nc + plan.bn - 1) / plan.bn;  // column tiles (per output phase in dInput)
   const int tiles_n = is_dx ? tiles_pp * plan.tt.n_phase : tiles_pp;
-  const long long wcount = (long long)g.groups * tiles_pp * plan.bn * kc * g.kh * g.kw;  // per plane
+  const int cpp = (kc + KBLK - 1) / KBLK;  // channel blocks per group, the last one possibly ragged
+  const long long wcount = (long long)g.groups * tiles_pp * plan.bn * cpp * KBLK * g.kh * g.kw;  // per plane
   const float* wp = staged_images;
   bool staged_here = false;
   if (!wp) {
@@ -762,7 +769,7 @@ int strip_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* b
   a.kc = kc;
   a.nc = nc;
   a.out_channels = is_dx ? g.cin : g.cout;
-  a.cb_per_phase = kc / KBLK;
+  a.cb_per_phase = cpp;
   a.cblocks = (is_dx ? 1 : plan.tt.n_phase) * a.cb_per_phase;
   a.images_per_tile = a.cb_per_phase * plan.tt.taps_total;
   a.tiles_n = tiles_n;
@@ -819,12 +826,12 @@ int strip_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* b
 
 
 // C[M,N] = alpha * A*B + beta * bias[n] as a 1x1 convolution over an M-pixel image with K input and N
-// output channels, written row-major.  Takes K % 32 == 0 and N >= 16; anything else is the caller's
-// CUDA-core kernel.  The staged copy of B comes from the caching allocator and is released on `st`.
+// output channels, written row-major.  Takes K >= 16 and N >= 16 (a ragged last block of K is padded
+// with zeros); anything else is the caller's CUDA-core kernel.  The staged copy of B comes from the caching allocator and is released on `st`.
 int tc_gemm(long long M, long long N, long long K, const float* A, long long sa0, long long sa1, const float* B,
             long long sb0, long long sb1, const float* bias, float alpha, float beta, float* C, cudaStream_t st) {
-  if (K % tcs::KBLK != 0 || K < tcs::KBLK || N < 16 || M > 2147483647ll || N > 2147483647ll || K > 2147483647ll)
-    return fail(B200_EUNSUPPORTED, "tcgen05 GEMM is incompatible with this shape (needs K %% 32 == 0 and N >= 16)");
+  if (K < 16 || N < 16 || M > 2147483647ll || N > 2147483647ll || K > 2147483647ll)
+    return fail(B200_EUNSUPPORTED, "tcgen05 GEMM is incompatible with this shape (needs K >= 16 and N >= 16)");
   ConvGeom g{};
   g.n = 1; g.cin = (int)K; g.cout = (int)N; g.h = 1; g.w = (int)M; g.kh = g.kw = 1; g.oh = 1; g.ow = (int)M;
   g.sh = g.sw = 1; g.ph = g.pw = 0; g.dh = g.dw = 1; g.groups = 1; g.cig = (int)K; g.cog = (int)N;

@@ -123,6 +123,21 @@ def test_tc_dweight_split_boundaries_and_determinism():
     np.testing.assert_array_equal(a, b)
 
 
+@pytest.mark.parametrize("shape", [
+    ((2, 48, 9, 11), 40, (3, 3), dict(padding=(1, 1))),                   # 48 -> 40 channels: ragged second block both ways
+    ((1, 20, 14, 14), 24, (3, 3), dict(padding=(1, 1))),                  # a single ragged block
+    ((2, 33, 8, 8), 17, (1, 1), dict()),                                  # one channel into the second block
+    ((2, 48, 10, 10), 80, (3, 3), dict(stride=(2, 2), padding=(1, 1), groups=2)),   # 24 -> 40 per group, strided
+    ((1, 70, 7, 9), 70, (3, 3), dict(padding=(1, 1))),
+], ids=lambda s: "x".join(map(str, s[0])) + f"-co{s[1]}" if isinstance(s, tuple) and len(s) == 4 else None)
+@pytest.mark.parametrize("channels_last", [False, True], ids=["nchw", "nhwc"])
+def test_tc_strip_pads_ragged_channel_blocks(shape, channels_last):
+    # channel counts that are no multiple of 32 (from 16 up) stay on the tcgen05 strip kernels
+    xshape, cout, kernel, kw = shape
+    _run_case(xshape, cout, kernel, channels_last=channels_last, seed=sum(xshape) + cout, phases=("y", "dx", "dw"), **kw)
+    assert b200conv.last_kernel().startswith("tc_strip")
+
+
 def test_tc_dweight_four_accumulators_with_ragged_channel_blocks():
     # 136 and 200 input channels: the last 32-channel block of the last CTA is partly / wholly empty
     for cin, cout in ((136, 32), (200, 48)):
@@ -150,8 +165,11 @@ def test_tc_gemm_strided_operands_and_addmm_epilogue(M, K, N):
     nan_bias = np.full(N, np.nan, np.float32)
     assert np.isfinite(b200conv.gemm(a, b, nan_bias, alpha=1.0, beta=0.0, algo="tc")).all()
     assert b200conv.device_status() == 0
+    # a reduction length that is no multiple of 32 is padded with zeros; below 16 the kernel declines
+    ragged = b200conv.gemm(np.ascontiguousarray(a[:, :K - 1]), np.ascontiguousarray(b[:K - 1]), algo="tc")
+    assert oracle.rel_l2(ragged, oracle.gemm(a[:, :K - 1], b[:K - 1], f64=True)) <= GATE
     with pytest.raises(b200conv.B200Error, match="incompatible"):
-        b200conv.gemm(a[:, :K - 1], b[:K - 1], algo="tc")
+        b200conv.gemm(np.ascontiguousarray(a[:, :8]), np.ascontiguousarray(b[:8]), algo="tc")
 
 
 @pytest.mark.parametrize("n,c,hw", [(4, 256, 32), (2, 64, 112), (1, 32, 150)])

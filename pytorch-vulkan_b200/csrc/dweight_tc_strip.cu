@@ -1,4 +1,4 @@
-// tcgen05 dWeight kernel for filters up to four taps wide (any stride, padding, dilation, groups;
+// tcgen05 dWeight kernel for filters up to eight taps wide (any stride, padding, dilation, groups;
 // at least 16 channels on both sides), FP32 via 3xTF32.
 //
 //   dW[co][ci][ky][kx] = sum over grid pixels q of  dY[q][co] * X_phase(ky,kx)[q + shift(ky,kx)][ci]
@@ -70,7 +70,8 @@ struct DwStripArgs {
                          // channel block j of a 1x1 filter
   int sph, spw;          // stride: grid pixel (r, c) of phase (a, b) is the input pixel (r*sph + a, c*spw + b)
   int in_h, in_w, out_h, out_w;  // extents of x and of dY (the grid H x W covers both)
-  unsigned blk_b, blk_dc;        // per tap kx: column phase and whole-pixel column offset (signed), 8 bits each
+  unsigned blk_b[2], blk_dc[2];  // per tap kx (up to 8): column phase and whole-pixel column offset (signed), 8 bits each
+  int kx_groups;                 // filters wider than four taps take ceil(kw / 4) CTAs, four taps each
   int ci_tiles, co_tiles;
   int stages;
   int* status;
@@ -257,8 +258,10 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
   volatile int* abort_flag = &ctrl->abort_flag;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int x_halves = a.xr > 32 ? 2 : 1;                      // a strip = rows 0..31 and 32..47; an exact block = 32 rows
-  // taps beyond the filter width are not staged: their accumulator rows are never stored
-  const int x_tasks = a.nacc * (a.blocks_are_taps ? g.kw : a.xblocks) * x_halves;
+  const int kx0 = (int)(blockIdx.x % (unsigned)a.kx_groups) * 4;  // first horizontal tap of this CTA
+  // taps beyond the filter width of a narrow filter are not staged (their accumulator rows are never
+  // stored); the last group of a wide filter stages zeros for them so that every CTA has the same jobs
+  const int x_tasks = a.nacc * (a.blocks_are_taps ? min(4, g.kw) : a.xblocks) * x_halves;
   const int tasks = x_tasks + NB;                              // warp-sized staging jobs per K block
   // BN <= 128: the dY hi and lo planes (their 32-channel blocks are equally spaced) form ONE operand
   // of 2*BN columns, so x_hi*[dy_hi | dy_lo] is a single MMA; the epilogue adds the two halves.
@@ -282,7 +285,7 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
   const uint32_t tmem_acc = *reinterpret_cast<volatile uint32_t*>(&ctrl->tmem_base);
 
   // ---- which piece of dW this CTA owns ----
-  int id = blockIdx.x;
+  int id = blockIdx.x / a.kx_groups;
   const int ci_tile = id % a.ci_tiles; id /= a.ci_tiles;
   const int ky = id % g.kh;            id /= g.kh;
   const int co_tile = id % a.co_tiles; id /= a.co_tiles;
@@ -309,7 +312,7 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
       constexpr uint32_t idesc_wide = make_idesc_tf32(128, FUSE_HILO ? 2 * BN : BN) | (1u << 15) | (1u << 16);
       const uint32_t a_lbo = a.xblocks == 1 ? (uint32_t)g.dw * 128u : 2u * x_plane;
       // input rows start at the pixel shifted by -pad_w; hi plane then lo plane of each block
-      const uint64_t da_base = make_mn_desc(base + (a.xblocks == 1 ? (uint32_t)(XOFF - g.pw) * 128u : 0u), a_lbo);
+      const uint64_t da_base = make_mn_desc(base + (a.xblocks == 1 ? (uint32_t)(XOFF - g.pw + kx0 * g.dw) * 128u : 0u), a_lbo);
       const uint64_t db_base = make_mn_desc(base + x_bytes, KP * 128u);
       const uint32_t stage_d = stage_bytes >> 4, x_plane_d = x_plane >> 4;
       constexpr uint32_t y_plane_d = y_plane >> 4;
@@ -317,7 +320,7 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
       // of 64-byte rows; x_hi16 pairs with dy_lo16 and x_lo16 with dy_hi16
       constexpr uint32_t idesc16 = make_idesc_bf16(128, BN) | (1u << 15) | (1u << 16);
       const uint32_t a_lbo16 = a.xblocks == 1 ? (uint32_t)g.dw * 64u : 2u * x_plane;
-      const uint64_t da16_base = make_mn_desc16(base + x_plane + (a.xblocks == 1 ? (uint32_t)(XOFF - g.pw) * 64u : 0u), a_lbo16);
+      const uint64_t da16_base = make_mn_desc16(base + x_plane + (a.xblocks == 1 ? (uint32_t)(XOFF - g.pw + kx0 * g.dw) * 64u : 0u), a_lbo16);
       const uint64_t db16_base = make_mn_desc16(base + x_bytes + y_plane, KP * 64u);
       const bool pm = DPROF_ON(true);
       uint32_t s = 0, par = 0;
@@ -402,9 +405,12 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
         } else {
           // exact 32-pixel blocks: tap kx = blk of one channel block, or channel block blk of a 1x1 filter
           const int c0 = ci0 + (a.blocks_are_taps ? 0 : blk * 32);
-          const int chans = max(0, min(32, g.cig - c0));
-          const int pb = a.blocks_are_taps ? (int)((a.blk_b >> (8 * blk)) & 0xFFu) : 0;
-          const int dc = a.blocks_are_taps ? (int)(signed char)((a.blk_dc >> (8 * blk)) & 0xFFu) : 0;
+          const int kx = kx0 + blk;  // tap of this block (blocks_are_taps)
+          const int chans = (a.blocks_are_taps && kx >= g.kw) ? 0 : max(0, min(32, g.cig - c0));
+          const unsigned tb = kx < 4 ? a.blk_b[0] >> (8 * kx) : a.blk_b[1] >> (8 * (kx - 4));
+          const unsigned td = kx < 4 ? a.blk_dc[0] >> (8 * kx) : a.blk_dc[1] >> (8 * (kx - 4));
+          const int pb = a.blocks_are_taps ? (int)(tb & 0xFFu) : 0;
+          const int dc = a.blocks_are_taps ? (int)(signed char)(td & 0xFFu) : 0;
           chunked = stage_block(a.x, (long long)group * g.cig + c0, chans, a.H, a.W, row_pitch, img_pitch, a.img_div, a.row_div,
                       k0 + yshift + dc, 0, a.q_total, rows, lane, x_vec, val, a.sph, a.spw, pa, pb, a.in_h, a.in_w);
         }
@@ -445,7 +451,7 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
       const int quarter = warp & 3, u = warp >> 2;
       // block index: horizontal tap (taps in M) or channel block (1x1 filter in the block arrangement)
       const bool taps_in_m = a.xblocks == 1 || a.blocks_are_taps;
-      const int kx = taps_in_m ? quarter : 0;
+      const int kx = taps_in_m ? kx0 + quarter : 0;
       const int ci = ci0 + u * 32 + (taps_in_m ? lane : quarter * 32 + lane);
       const bool row_ok = kx < g.kw && ci < g.cig;
       float* out = a.out + ((long long)split * g.cout + (long long)group * g.cog + co0) * cols +
@@ -514,24 +520,28 @@ struct DwStripPlan {
   bool cross = false;  // BF16 cross terms (four accumulators)
   int bn = 0, xblocks = 1, nacc = 1, xr = XR, blocks_are_taps = 0, stages = 0, smem = 0, ci_tiles = 0, co_tiles = 0, splits = 1, span = 0;
   int gh = 0, gw = 0, pr = 0, pc = 0;  // pixel grid (covers dY and every phase sub-image of x) and its zero padding
-  unsigned blk_b = 0, blk_dc = 0;
+  unsigned blk_b[2] = {0, 0}, blk_dc[2] = {0, 0};
+  int kx_groups = 1;
   size_t bytes = 0;
 };
 
 static inline int floor_div(int a, int b) { return a >= 0 ? a / b : -((-a + b - 1) / b); }
 
 // Two arrangements of the M dimension (4 blocks of 32 rows):
-//   strip:  stride 1, output as large as the input, 2 <= kw <= 4 (or few channels): one staged input
+//   strip:  stride 1, output as large as the input, kw >= 2 (or few channels): one staged input
 //           strip per K block, the horizontal taps are its row offsets;
-//   blocks: everything else with kw <= 4 -- strides, any padding, 1x1: four exact 32-pixel blocks per K
+//   blocks: everything else -- strides, any padding, 1x1: four exact 32-pixel blocks per K
 //           block, either the taps kx = 0..3 of one channel block (each with its own column phase and
 //           offset) or, for a 1x1 filter, four channel blocks.
 static DwStripPlan plan_dw_strip(const ConvGeom& g, size_t budget) {
   DwStripPlan p;
-  if (g.kw > 4 || g.cog < 16 || g.cig < 16) return p;
+  if (g.kw > 8 || g.cog < 16 || g.cig < 16) return p;
+  p.kx_groups = (g.kw + 3) / 4;
   const bool same = g.sh == 1 && g.sw == 1 && g.oh == g.h && g.ow == g.w && 2 * g.ph == g.dh * (g.kh - 1) &&
                     2 * g.pw == g.dw * (g.kw - 1);
-  const bool strip_fits = same && g.pw <= XOFF && 3 * g.dw - g.pw + XOFF + KP <= XR;
+  // the last row a VALID tap's M block reads must be inside the strip (the unused blocks of the last
+  // tap group read whatever follows in the stage; their accumulator rows are never stored)
+  const bool strip_fits = same && g.pw <= XOFF && (g.kw - 1) * g.dw - g.pw + XOFF + KP <= XR;
   const bool pointwise = same && g.kh == 1 && g.kw == 1;
   if (strip_fits && !(pointwise && g.cig >= 64)) {
     p.xblocks = 1; p.xr = XR;
@@ -547,8 +557,8 @@ static DwStripPlan plan_dw_strip(const ConvGeom& g, size_t budget) {
       const int ox = kx * g.dw - g.pw, dc = floor_div(ox, g.sw);
       if (dc < -127 || dc > 127) return p;
       p.pc = std::max(p.pc, std::abs(dc));
-      p.blk_b |= (unsigned)(ox - dc * g.sw) << (8 * kx);
-      p.blk_dc |= ((unsigned)dc & 0xFFu) << (8 * kx);
+      p.blk_b[kx / 4] |= (unsigned)(ox - dc * g.sw) << (8 * (kx % 4));
+      p.blk_dc[kx / 4] |= ((unsigned)dc & 0xFFu) << (8 * (kx % 4));
     }
   }
   // Several channel blocks per CTA share every staged dY block (one TMEM accumulator each): less dY
@@ -569,7 +579,7 @@ static DwStripPlan plan_dw_strip(const ConvGeom& g, size_t budget) {
   p.ci_tiles = (g.cig + ci_per_tile - 1) / ci_per_tile;
   p.co_tiles = (g.cog + p.bn - 1) / p.bn;
   const long long q_total = (long long)g.n * (p.gh + p.pr) * (p.gw + p.pc);
-  const long long tiles = (long long)p.ci_tiles * g.kh * p.co_tiles * g.groups;
+  const long long tiles = (long long)p.ci_tiles * g.kh * p.kx_groups * p.co_tiles * g.groups;
   const size_t dw_bytes = sizeof(float) * (size_t)g.cout * g.cig * g.kh * g.kw;
   // Number of pixel splits: the one that minimises a small model of the run time in K-block units --
   // waves of CTAs (one CTA per SM is resident) x (K blocks per split + a fixed cost per CTA for
@@ -633,22 +643,23 @@ int dweight_strip(const ConvGeom& g, View4 x, View4 dy, float* dw, void* ws, siz
   a.H = plan.gh; a.W = plan.gw; a.pr = plan.pr; a.pc = plan.pc;
   a.xr = plan.xr; a.blocks_are_taps = plan.blocks_are_taps; a.nacc = plan.nacc;
   a.sph = g.sh; a.spw = g.sw; a.in_h = g.h; a.in_w = g.w; a.out_h = g.oh; a.out_w = g.ow;
-  a.blk_b = plan.blk_b; a.blk_dc = plan.blk_dc;
+  a.blk_b[0] = plan.blk_b[0]; a.blk_b[1] = plan.blk_b[1]; a.blk_dc[0] = plan.blk_dc[0]; a.blk_dc[1] = plan.blk_dc[1];
+  a.kx_groups = plan.kx_groups;
   a.q_total = (int)((long long)g.n * (a.H + a.pr) * (a.W + a.pc));
   a.img_div = FastDiv((uint32_t)((a.H + a.pr) * (a.W + a.pc)));
   a.row_div = FastDiv((uint32_t)(a.W + a.pc));
   a.span = plan.span; a.splits = plan.splits; a.xblocks = plan.xblocks;
   a.ci_tiles = plan.ci_tiles; a.co_tiles = plan.co_tiles; a.stages = plan.stages;
-  a.div_tasks = FastDiv((uint32_t)(plan.nacc * (plan.blocks_are_taps ? g.kw : plan.xblocks) * (plan.xr > 32 ? 2 : 1) + plan.bn / 32));
+  a.div_tasks = FastDiv((uint32_t)(plan.nacc * (plan.blocks_are_taps ? std::min(4, g.kw) : plan.xblocks) * (plan.xr > 32 ? 2 : 1) + plan.bn / 32));
   a.div_stages = FastDiv((uint32_t)plan.stages);
   a.out = plan.splits > 1 ? (float*)ws : dw;
   a.partial_layout = plan.splits > 1 ? 1 : 0;
   a.status = device_status_word();
   if (!a.status) return fail(B200_ECUDA, "device status word is not allocated");
-  const long long gx = (long long)plan.ci_tiles * g.kh * plan.co_tiles * g.groups;
+  const long long gx = (long long)plan.ci_tiles * g.kh * plan.kx_groups * plan.co_tiles * g.groups;
   if (gx > 2147483647ll) return fail(B200_ERANGE, "dWeight strip kernel: grid exceeds launch limits");
   // rows of dW that no CTA writes (channel blocks beyond kw taps) do not exist: every (co, ci, ky, kx)
-  // is covered because kx < kw <= 4 blocks and all ci tiles are enumerated
+  // is covered: four taps per CTA, ceil(kw / 4) tap groups, and all ci tiles are enumerated
   const dim3 grid((unsigned)gx, (unsigned)plan.splits);
   static unsigned long long* prof_buf = nullptr;
   const char* prof_env = getenv("B200_STRIP_PROFILE");

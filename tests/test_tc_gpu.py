@@ -138,6 +138,20 @@ def test_tc_strip_pads_ragged_channel_blocks(shape, channels_last):
     assert b200conv.last_kernel().startswith("tc_strip")
 
 
+@pytest.mark.parametrize("shape", [
+    ((2, 32, 14, 15), 32, (5, 5), dict(padding=(2, 2))),                      # two tap groups (4 + 1), strip arrangement
+    ((1, 64, 12, 12), 32, (7, 7), dict(padding=(3, 3))),                      # 4 + 3
+    ((2, 32, 20, 20), 48, (7, 7), dict(stride=(2, 2), padding=(3, 3))),       # stem-like: blocks arrangement
+    ((1, 32, 9, 16), 32, (1, 7), dict(padding=(0, 3))),
+    ((1, 32, 11, 11), 32, (3, 8), dict(padding=(1, 4))),                      # eight taps, output one column wider
+], ids=lambda s: "x".join(map(str, s[0])) + f"-k{s[2][0]}x{s[2][1]}" if isinstance(s, tuple) and len(s) == 4 else None)
+def test_tc_dweight_wide_filters(shape):
+    xshape, cout, kernel, kw = shape
+    errs = _run_case(xshape, cout, kernel, seed=sum(xshape) + cout, phases=("dw",), **kw)
+    assert errs["dw"] <= GATE
+    assert b200conv.last_kernel() == "tc_strip_dweight"
+
+
 def test_tc_dweight_four_accumulators_with_ragged_channel_blocks():
     # 136 and 200 input channels: the last 32-channel block of the last CTA is partly / wholly empty
     for cin, cout in ((136, 32), (200, 48)):

@@ -93,6 +93,7 @@ struct StripArgs {
   FastDiv img_div, row_div;
   int tiles_m, tiles_total;
   int unit, units;        // tiles per scheduling unit, number of units (tiles_total = unit * units)
+  int m_fastest;          // tile order (tile_coord)
   FastDiv div_tiles_n, div_tiles_m, div_tiles_pp, div_chunks, div_cblocks, div_cbpp, div_a_stages, div_unit;
   int halo, strip_rows;   // rows staged before the tile's first pixel; strip_rows is a multiple of 8
   int a_stages, w_stages;
@@ -134,6 +135,29 @@ struct TileIter {
   __device__ int tile() const { return u * unit + t; }
   __device__ void next() { if (++t == unit) { t = 0; u += step; } }
 };
+
+// tile index -> (pixel-row tile, column tile, group).  Column tile fastest when tiles are dealt in
+// units (see TileIter); otherwise the pixel-row tile runs fastest, so that the CTAs working at the same
+// time share their weight stages (the heavier operand: BN*256 bytes per stage against 16 KB of raw
+// activations) and L2 serves them as one stream.
+struct TileCoord {
+  int m_tile, n_tile, group;
+};
+__device__ __forceinline__ TileCoord tile_coord(const StripArgs& a, int tile) {
+  TileCoord c;
+  if (a.m_fastest) {
+    const int rest = (int)a.div_tiles_m.div((uint32_t)tile);
+    c.m_tile = tile - rest * a.tiles_m;
+    c.group = (int)a.div_tiles_n.div((uint32_t)rest);
+    c.n_tile = rest - c.group * a.tiles_n;
+  } else {
+    const int tn = (int)a.div_tiles_n.div((uint32_t)tile);
+    c.n_tile = tile - tn * a.tiles_n;
+    c.group = (int)a.div_tiles_m.div((uint32_t)tn);
+    c.m_tile = tn - c.group * a.tiles_m;
+  }
+  return c;
+}
 
 template <int BN>
 __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs a) {
@@ -208,7 +232,7 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
         if (!mbar_wait(smem_u32(&ctrl->acc_empty[ab]), ((t_count >> 1) & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_ACCUM)) break;
         PROF_ADD(pm, 0); }
         const uint32_t tmem_acc = tmem_base + ab * ACC_COLS;
-        const int n_tile = tile - (int)a.div_tiles_n.div((uint32_t)tile) * a.tiles_n;
+        const int n_tile = tile_coord(a, tile).n_tile;
         int phase = a.phase_on_n ? (int)a.div_tiles_pp.div((uint32_t)n_tile) : 0;  // dInput: the phase of this column tile
         int cbl = 0;
         uint32_t accumulate = 0;  // the tile's first MMA overwrites the accumulator
@@ -270,8 +294,9 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
       if (a.wait_for_images) asm volatile("griddepcontrol.wait;" ::: "memory");
       for (TileIter it(a); it.valid() && alive; it.next()) {
         const int tile = it.tile();
-        const int tn = (int)a.div_tiles_n.div((uint32_t)tile), n_tile = tile - tn * a.tiles_n;
-        const long long group = a.div_tiles_m.div((uint32_t)tn);
+        const TileCoord tc_ = tile_coord(a, tile);
+        const int n_tile = tc_.n_tile;
+        const long long group = tc_.group;
         long long first_image;
         int images;
         if (a.phase_on_n) {  // images of a group: [phase][tile of the phase][channel block][tap of the phase]
@@ -324,9 +349,8 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
       const int cb = (int)(a_count - tile_iter * a.cblocks);
       const uint32_t unit_iter = a.div_unit.div(tile_iter);
       const uint32_t tile = (blockIdx.x + unit_iter * gridDim.x) * a.unit + (tile_iter - unit_iter * a.unit);
-      const uint32_t tn = a.div_tiles_n.div(tile);
-      const int group = (int)a.div_tiles_m.div(tn);
-      const int m_tile = (int)tn - group * (int)a.tiles_m;
+      const TileCoord tc_ = tile_coord(a, (int)tile);
+      const int group = tc_.group, m_tile = tc_.m_tile;
       const uint32_t a_round = a.div_a_stages.div(a_count);
       const uint32_t as = a_count - a_round * a.a_stages;
       const bool pa = PROF_ON(threadIdx.x == EPI_WARPS * 32);
@@ -436,9 +460,8 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
     uint32_t t_count = 0;
     for (TileIter it(a); it.valid(); it.next(), ++t_count) {
       const int tile = it.tile();
-      const int tn = (int)a.div_tiles_n.div((uint32_t)tile), n_tile = tile - tn * a.tiles_n;
-      const int group = (int)a.div_tiles_m.div((uint32_t)tn);
-      const int m_tile = tn - group * (int)a.tiles_m;
+      const TileCoord tc_ = tile_coord(a, tile);
+      const int n_tile = tc_.n_tile, group = tc_.group, m_tile = tc_.m_tile;
       const int phase_n = (int)a.div_tiles_pp.div((uint32_t)n_tile);
       const int n0 = (n_tile - phase_n * a.tiles_pp) * BN;
       const int cols_valid = min(BN, a.nc - n0);
@@ -786,6 +809,7 @@ int strip_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* b
   // units of all column tiles of a pixel-row tile while that still leaves every SM two or more units
   a.unit = (tiles_total / a.tiles_n >= 2ll * sm_count()) ? a.tiles_n : 1;
   a.units = a.tiles_total / a.unit;
+  a.m_fastest = (a.unit == 1 && a.tiles_n > 1) ? 1 : 0;
   a.div_unit = FastDiv((uint32_t)a.unit);
   a.div_tiles_n = FastDiv((uint32_t)a.tiles_n); a.div_tiles_m = FastDiv((uint32_t)a.tiles_m);
   a.div_tiles_pp = FastDiv((uint32_t)a.tiles_pp); a.div_chunks = FastDiv((uint32_t)chunks);

@@ -139,6 +139,17 @@ size_t b200_conv2d_workspace(const b200_conv_params* p, int phase, int algo, siz
 int b200_conv2d_forward(const b200_conv_params* p, b200_view4 x, b200_view4 w, const float* bias,
                         int64_t bias_stride, float* y, void* workspace, size_t workspace_bytes,
                         int algo, void* stream);
+/* y = act(conv(x, w) + bias + residual), optionally written channels-last.  No single counterpart in
+ * the reference: it fuses the convolution with the add.Tensor / relu the reference registers as
+ * separate operators (csrc/ops/mm.cpp:1094-1097) and that follow it in ResNet / U-Net blocks.
+ * residual: view of the result's logical shape [n,cout,oh,ow] (any strides), ptr NULL = none.
+ * relu: 0 or 1.  y_channels_last = 0: y contiguous [n,cout,oh,ow]; 1: y contiguous [n,oh,ow,cout],
+ * available when the tcgen05 strip kernel takes the geometry (else B200_EUNSUPPORTED, "incompatible").
+ * With the strip kernel everything happens in its epilogue; other candidates run the plain forward
+ * followed by one elementwise pass.  Workspace and algo as for b200_conv2d_forward. */
+int b200_conv2d_forward_fused(const b200_conv_params* p, b200_view4 x, b200_view4 w, const float* bias,
+                              int64_t bias_stride, b200_view4 residual, int relu, float* y, int y_channels_last,
+                              void* workspace, size_t workspace_bytes, int algo, void* stream);
 /* dx = conv_transpose(dy, w).  Replaces dispatch(Input), csrc/ops/convolution.cpp:684-687 and
  * the conv2d_backward_input shaders.  dx: contiguous [n,cin,h,w]. */
 int b200_conv2d_dinput(const b200_conv_params* p, b200_view4 dy, b200_view4 w, float* dx,

@@ -78,6 +78,8 @@ SIGNATURES = {
     "b200_conv2d_workspace": (c_size_t, [POINTER(ConvParams), c_int, c_int, c_size_t]),
     "b200_conv2d_forward": (c_int, [POINTER(ConvParams), View4, View4, c_void_p, c_int64, c_void_p, c_void_p,
                                     c_size_t, c_int, c_void_p]),
+    "b200_conv2d_forward_fused": (c_int, [POINTER(ConvParams), View4, View4, c_void_p, c_int64, View4, c_int, c_void_p,
+                                          c_int, c_void_p, c_size_t, c_int, c_void_p]),
     "b200_conv2d_dinput": (c_int, [POINTER(ConvParams), View4, View4, c_void_p, c_void_p, c_size_t, c_int, c_void_p]),
     "b200_conv2d_dweight": (c_int, [POINTER(ConvParams), View4, View4, c_void_p, c_void_p, c_size_t, c_int, c_void_p]),
     "b200_conv2d_dweight_static": (c_int, [POINTER(ConvParams), View4, View4, c_void_p, c_void_p]),
@@ -239,6 +241,28 @@ def conv2d_forward(x, w, b=None, stride=(1, 1), padding=(0, 0), dilation=(1, 1),
     ws = DeviceBuffer(ws_n) if ws_n else None
     check(lib().b200_conv2d_forward(ctypes.byref(p), xv.view4(), wv.view4(), bv.ptr if bv else None,
                                     bv.strides[0] if bv else 0, y.ptr, ws.ptr if ws else None, ws_n, algo, None))
+    return y.to_numpy((p.n, p.cout, p.oh, p.ow))
+
+
+def conv2d_forward_fused(x, w, b=None, residual=None, relu=False, channels_last=False, stride=(1, 1), padding=(0, 0),
+                         dilation=(1, 1), groups=1, algo="auto", budget=DEFAULT_WORKSPACE):
+    """act(conv2d(x, w) + b + residual) on the device.  Returns the logical NCHW array; with
+    channels_last=True the device wrote it as contiguous [n, oh, ow, cout] and the result is a
+    channels-last strided view of that memory."""
+    algo = _algo(algo)
+    p = geometry(x.shape, w.shape[0], w.shape[2:], stride, padding, dilation, groups, wcin=w.shape[1])
+    xv, wv = DeviceView(x), DeviceView(w)
+    bv = DeviceView(b) if b is not None else None
+    rv = DeviceView(residual) if residual is not None else None
+    y = DeviceBuffer(4 * p.n * p.cout * p.oh * p.ow)
+    ws_n = workspace_bytes(p, PHASE_FORWARD, algo, budget)
+    ws = DeviceBuffer(ws_n) if ws_n else None
+    null_view = View4(None, (c_int64 * 4)(0, 0, 0, 0))
+    check(lib().b200_conv2d_forward_fused(ctypes.byref(p), xv.view4(), wv.view4(), bv.ptr if bv else None,
+                                          bv.strides[0] if bv else 0, rv.view4() if rv else null_view, int(bool(relu)),
+                                          y.ptr, int(bool(channels_last)), ws.ptr if ws else None, ws_n, algo, None))
+    if channels_last:
+        return y.to_numpy((p.n, p.oh, p.ow, p.cout)).transpose(0, 3, 1, 2)
     return y.to_numpy((p.n, p.cout, p.oh, p.ow))
 
 

@@ -102,9 +102,18 @@ int tc_gemm(long long M, long long N, long long K, const float* A, long long sa0
 
 // persistent strip kernel for stride-1 "same" convolutions (conv_tc_strip.cu)
 bool strip_supported(const ConvGeom& g, int phase);
+// What the strip kernel's epilogue may fuse behind alpha*acc + beta*bias: a residual tensor of the
+// output's logical shape [n][channels][h][w] (any strides) and a ReLU.
+struct StripPostOps {
+  View4 residual{nullptr, 0, 0, 0, 0};
+  int relu = 0;
+};
 int strip_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* bias, long long bias_stride, float* out,
                void* ws, size_t ws_bytes, cudaStream_t st, bool rowmajor = false, float alpha = 1.f, float beta = 1.f,
-               const float* staged_images = nullptr);  // images already written for strip_column_tile()
+               const float* staged_images = nullptr,  // images already written for strip_column_tile()
+               const StripPostOps* post = nullptr);
+// elementwise residual add / ReLU on a contiguous NCHW result (conv_simt.cu), for candidates without a fused epilogue
+int post_ops_nchw(float* y, const ConvGeom& g, const StripPostOps& post, cudaStream_t st);
 int strip_column_tile(const ConvGeom& g, bool is_dx);   // column tile the plan picks, 0 if unsupported
 size_t strip_workspace(const ConvGeom& g, int phase);  // bytes of the weight stage images
 

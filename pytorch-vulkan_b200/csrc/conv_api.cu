@@ -193,6 +193,37 @@ int b200_conv2d_forward(const b200_conv_params* p, b200_view4 x, b200_view4 w, c
   }
 }
 
+int b200_conv2d_forward_fused(const b200_conv_params* p, b200_view4 x, b200_view4 w, const float* bias,
+                              int64_t bias_stride, b200_view4 residual, int relu, float* y, int y_channels_last,
+                              void* workspace, size_t workspace_bytes, int algo, void* stream) {
+  if (int rc = check_params(p)) return rc;
+  if (int rc = ensure_init()) return rc;
+  if (!x.ptr || !w.ptr || !y) return fail(B200_EINVAL, "fused convolution forward: null tensor");
+  if ((relu != 0 && relu != 1) || (y_channels_last != 0 && y_channels_last != 1))
+    return fail(B200_EINVAL, "fused convolution forward: relu and y_channels_last must be 0 or 1");
+  const ConvGeom g = to_geom(*p);
+  const int chosen = select(g, B200_PHASE_FORWARD, algo, workspace ? workspace_bytes : 0);
+  if (chosen < 0) return chosen;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (!bias) bias_stride = 0;
+  StripPostOps post;
+  post.residual = to_view(residual);
+  post.relu = relu;
+  // the strip kernel applies everything in its epilogue and can write [pixel][channel] rows
+  if (chosen == B200_ALGO_TC && strip_supported(g, B200_PHASE_FORWARD)) {
+    note_kernel("tc_strip_forward_fused");
+    const int rc = strip_conv(g, false, to_view(x), to_view(w), bias, bias_stride, y, workspace, workspace_bytes, st,
+                              y_channels_last != 0, 1.f, 1.f, nullptr, &post);
+    if (rc != B200_EUNSUPPORTED) return rc;
+  }
+  if (y_channels_last)
+    return fail(B200_EUNSUPPORTED, "fused convolution forward: a channels-last result is incompatible with this "
+                                   "geometry's candidate (needs the tcgen05 strip kernel)");
+  // every other candidate: plain forward, then one elementwise pass over the contiguous result
+  if (int rc = b200_conv2d_forward(p, x, w, bias, bias_stride, y, workspace, workspace_bytes, algo, stream)) return rc;
+  return post_ops_nchw(y, g, post, st);
+}
+
 int b200_conv2d_dinput(const b200_conv_params* p, b200_view4 dy, b200_view4 w, float* dx, void* workspace,
                        size_t workspace_bytes, int algo, void* stream) {
   if (int rc = check_params(p)) return rc;

@@ -503,6 +503,29 @@ __global__ void __launch_bounds__(256) dbias_channels_kernel(ConvGeom g, View4 g
   }
 }
 
+// y (contiguous NCHW) += residual (any strides), then ReLU: the pass behind candidates whose kernels
+// have no fused epilogue.
+__global__ void __launch_bounds__(256) post_ops_kernel(float* __restrict__ y, ConvGeom g, View4 res, int relu, long long total) {
+  const long long i = blockIdx.x * 256ll + threadIdx.x;
+  if (i >= total) return;
+  float v = y[i];
+  if (res.ptr) {
+    const int x = (int)(i % g.ow), yy = (int)((i / g.ow) % g.oh);
+    const int c = (int)((i / ((long long)g.ow * g.oh)) % g.cout);
+    const long long n = i / ((long long)g.ow * g.oh * g.cout);
+    v += res.ptr[n * res.s0 + c * res.s1 + yy * res.s2 + x * res.s3];
+  }
+  if (relu) v = fmaxf(v, 0.f);
+  y[i] = v;
+}
+int post_ops_nchw(float* y, const ConvGeom& g, const StripPostOps& post, cudaStream_t st) {
+  if (!post.residual.ptr && !post.relu) return B200_OK;
+  const long long total = (long long)g.n * g.cout * g.oh * g.ow;
+  post_ops_kernel<<<(unsigned)div_up64(total, 256), 256, 0, st>>>(y, g, post.residual, post.relu, total);
+  count_launch();
+  return launch_check("post_ops_kernel");
+}
+
 int dbias_reduce(const ConvGeom& g, View4 dy, float* db, float* partial, int slabs, cudaStream_t st) {
   if (slabs < 1 || !partial) slabs = 1;
   float* out = slabs > 1 ? partial : db;

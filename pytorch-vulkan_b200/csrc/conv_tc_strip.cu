@@ -100,6 +100,8 @@ struct StripArgs {
   int out_rowmajor;       // 0: NCHW planes.  1: [pixel][channel] rows (channels-last / GEMM C)
   int out_vec4;           // row-major rows may be written with 16-byte stores
   float alpha, beta;      // out = alpha * acc + beta * bias
+  View4 res;              // optional residual added after the bias (logical shape of the output), ptr null = none
+  int relu;               // clamp at zero last
   int wait_for_images;    // launched with programmatic stream serialisation behind stage_weights_kernel
   int* status;
   unsigned long long* prof;  // optional cycle counters of CTA 0 (B200_STRIP_PROFILE=1), else null
@@ -471,7 +473,7 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
       const bool has_taps = !a.phase_on_n || ctrl->tap_start[phase_n + 1] > ctrl->tap_start[phase_n];
       const int q = m_tile * BLOCK_M + quarter * 32 + lane;
       bool ok = q < a.q_total;
-      long long obase = 0;
+      long long obase = 0, res_off = 0;
       if (ok) {
         const long long n = a.img_div.div((uint32_t)q);
         const int rem = q - (int)n * img_pitch;
@@ -479,6 +481,7 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
         ok = y < a.H && x < a.W;
         if (a.phase_on_n) { y = y * a.osh + ctrl->ph_a[phase_n]; x = x * a.osw + ctrl->ph_b[phase_n]; }
         ok = ok && y < a.out_h && x < a.out_w;
+        res_off = n * a.res.s0 + ((long long)group * a.nc + n0) * a.res.s1 + (long long)y * a.res.s2 + (long long)x * a.res.s3;
         obase = a.out_rowmajor ? (((n * a.out_h + y) * a.out_w + x) * (long long)a.out_channels + (long long)group * a.nc + n0)
                                : (((n * a.out_channels + (long long)group * a.nc + n0) * a.out_h + y) * a.out_w + x);
       }
@@ -520,6 +523,31 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
         } else if (a.alpha != 1.f) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] *= a.alpha;
+        }
+        if (a.res.ptr && ok) {
+          // all loads of the chunk are issued before the first add (one warp per scheduler runs at
+          // the latency of its dependent instructions)
+          const float* rp = a.res.ptr + res_off + c0 * a.res.s1;
+          float r[32];
+          if (nvalid == 32 && a.res.s1 == 1 && ((reinterpret_cast<uintptr_t>(rp) & 15) == 0)) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float4 f = __ldg(reinterpret_cast<const float4*>(rp) + j);
+              r[4 * j] = f.x; r[4 * j + 1] = f.y; r[4 * j + 2] = f.z; r[4 * j + 3] = f.w;
+            }
+          } else if (nvalid == 32) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = __ldg(rp + j * a.res.s1);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = j < nvalid ? __ldg(rp + j * a.res.s1) : 0.f;
+          }
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] += r[j];
+        }
+        if (a.relu) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
         }
         if (ok) {
           float* p = a.out + obase + c0 * col_stride;
@@ -751,7 +779,8 @@ static int launch_strip(const tcs::StripArgs& a, int grid, int smem, cudaStream_
 }
 
 int strip_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* bias, long long bias_stride, float* out,
-               void* ws, size_t ws_bytes, cudaStream_t st, bool rowmajor, float alpha, float beta, const float* staged_images) {
+               void* ws, size_t ws_bytes, cudaStream_t st, bool rowmajor, float alpha, float beta, const float* staged_images,
+               const StripPostOps* post) {
   using namespace tcs;
   const StripPlan plan = plan_strip(g, is_dx);
   if (!plan.ok) return fail(B200_EUNSUPPORTED, "strip kernel does not take this geometry");
@@ -816,6 +845,7 @@ int strip_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* b
   a.div_cblocks = FastDiv((uint32_t)a.cblocks); a.div_cbpp = FastDiv((uint32_t)a.cb_per_phase);
   a.div_a_stages = FastDiv((uint32_t)a.a_stages);
   a.wait_for_images = staged_here ? 1 : 0;
+  if (post && !is_dx) { a.res = post->residual; a.relu = post->relu; }
   a.out_rowmajor = rowmajor ? 1 : 0;
   a.alpha = alpha; a.beta = beta;
   a.out_vec4 = rowmajor && a.out_channels % 4 == 0 && plan.bn % 4 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 && a.nc % 4 == 0;

@@ -191,6 +191,47 @@ int b200_gemm(int64_t M, int64_t N, int64_t K, const float* A, int64_t sa0, int6
               const float* B, int64_t sb0, int64_t sb1, const float* bias, float alpha, float beta,
               float* C, int algo, void* stream);
 
+/* ---- BatchNorm (the normalisation either side of a convolution) --------------------------- */
+
+/* Memory layout of the FP32 tensors of a batch-norm call.  The logical shape is [n, c, s] with s the
+ * product of the trailing dimensions; the reference first packs every input to the contiguous form
+ * (csrc/ops/batch_norm.cpp:30, `packed(input)`), here a channels-last tensor is consumed as it is. */
+enum {
+  B200_BN_PLANAR = 0,      /* contiguous [n][c][s] (NCHW and its 1-D/3-D relatives) */
+  B200_BN_INTERLEAVED = 1  /* contiguous [n][s][c] (channels-last); y / dx are written the same way */
+};
+
+/* Bytes of workspace the two calls below need for this shape (0 on invalid shapes).  The workspace
+ * holds per-channel coefficients and the partial reductions; it must be 16-byte aligned. */
+size_t b200_batch_norm_workspace(int64_t n, int64_t c, int64_t s, int layout);
+
+/* y = (x - mean) * inv * weight + bias per channel.  Replaces batch_norm (csrc/ops/batch_norm.cpp:21-83)
+ * with the shaders batch_norm_forward.comp (training, and evaluation of small tensors) and
+ * batch_norm_eval.comp.
+ *  - training != 0: mean and biased variance over the n*s values of each channel; save_mean[c] and
+ *    save_inv[c] = 1/sqrt(var + eps) (0 when var == 0 and eps == 0) are written (contiguous);
+ *    running_mean / running_var, when not NULL, are updated in place with `momentum`, the variance
+ *    with the unbiased estimate (NaN for n*s == 1, as in the reference).
+ *  - training == 0: running_mean and running_var are required and read only; save_* are not touched.
+ *  weight, bias, running_* are channel vectors with an element stride each (NULL = absent).
+ *  Fails with B200_ERANGE above INT32_MAX elements (the reference stops at UINT32_MAX, :19). */
+int b200_batch_norm_forward(int64_t n, int64_t c, int64_t s, int layout, const float* x, const float* weight,
+                            int64_t weight_stride, const float* bias, int64_t bias_stride, float* running_mean,
+                            int64_t running_mean_stride, float* running_var, int64_t running_var_stride, int training,
+                            float momentum, float eps, float* y, float* save_mean, float* save_inv, void* workspace,
+                            size_t workspace_bytes, void* stream);
+
+/* Gradients of the call above.  Replaces batch_norm_backward (csrc/ops/batch_norm.cpp:84-113) and
+ * batch_norm_backward.comp.  dx, dw, db: NULL = not wanted (the reference's output mask).
+ *  - training != 0: mean / inv_or_var are save_mean / save_inv of the forward call;
+ *    db = sum g, dw = sum (x - mean) g * inv, dx = (g - db/m - (x - mean) * dw * inv / m) * inv * weight.
+ *    With two values per channel the algebraic form of batch_norm_backward.comp:24-37 is used.
+ *  - training == 0: mean / inv_or_var are the running mean and variance; dx = g * weight / sqrt(var + eps). */
+int b200_batch_norm_backward(int64_t n, int64_t c, int64_t s, int layout, const float* grad, const float* x,
+                             const float* weight, int64_t weight_stride, const float* mean, int64_t mean_stride,
+                             const float* inv_or_var, int64_t inv_stride, int training, float eps, float* dx, float* dw,
+                             float* db, void* workspace, size_t workspace_bytes, void* stream);
+
 /* Device-side health word.  The tcgen05 kernels bound every wait on an mbarrier; a wait that
  * gives up records (code << 24 | CTA index) here, frees its tensor memory and returns, so the
  * context stays usable.  *status = 0 means no wait ever gave up.  Synchronises the device.

@@ -24,6 +24,7 @@ PHASE_FORWARD, PHASE_DINPUT, PHASE_DWEIGHT, PHASE_DBIAS = 0, 1, 2, 3
 ALGO_AUTO, ALGO_DIRECT, ALGO_TILED, ALGO_TC, ALGO_WINOGRAD = 0, 1, 2, 3, 4
 ALGO_NAMES = {"auto": 0, "direct": 1, "tiled": 2, "tc": 3, "winograd": 4}
 H2D, D2H, D2D = 1, 2, 3
+BN_PLANAR, BN_INTERLEAVED = 0, 1
 DEFAULT_WORKSPACE = 64 << 20  # TORCH_VULKAN_CONV_WORKSPACE_MB default, convolution.cpp:239-247
 
 
@@ -86,6 +87,13 @@ SIGNATURES = {
     "b200_conv2d_dbias": (c_int, [POINTER(ConvParams), View4, c_void_p, c_void_p, c_size_t, c_void_p]),
     "b200_gemm": (c_int, [c_int64, c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64,
                           c_void_p, c_float, c_float, c_void_p, c_int, c_void_p]),
+    "b200_batch_norm_workspace": (c_size_t, [c_int64, c_int64, c_int64, c_int]),
+    "b200_batch_norm_forward": (c_int, [c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_int64,
+                                        c_void_p, c_int64, c_void_p, c_int64, c_int, c_float, c_float, c_void_p, c_void_p,
+                                        c_void_p, c_void_p, c_size_t, c_void_p]),
+    "b200_batch_norm_backward": (c_int, [c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_void_p,
+                                         c_int64, c_void_p, c_int64, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p,
+                                         c_size_t, c_void_p]),
     "b200_device_status": (c_int, [POINTER(c_int), c_int]),
     "b200_launch_count": (c_uint64, []),
     "b200_last_kernel": (c_char_p, []),
@@ -327,3 +335,80 @@ def gemm(a, b, bias=None, alpha=1.0, beta=0.0, algo="auto"):
         check(lib().b200_gemm(M, N, K, av.ptr, av.strides[0], av.strides[1], bv.ptr, bv.strides[0], bv.strides[1],
                               biasv.ptr if biasv else None, alpha, beta, out.ptr, _algo(algo), None))
     return out.to_numpy((M, N))
+
+
+def _bn_pack(a, channels_last):
+    """Contiguous device layout of a logical [n, c, *spatial] array: as it is (planar) or with the
+    channel axis last (interleaved)."""
+    a = np.asarray(a, np.float32)
+    return np.ascontiguousarray(np.moveaxis(a, 1, -1)) if channels_last else np.ascontiguousarray(a)
+
+
+def _bn_unpack(flat, shape, channels_last):
+    if not channels_last:
+        return flat.reshape(shape)
+    moved = (shape[0],) + tuple(shape[2:]) + (shape[1],)
+    return np.moveaxis(flat.reshape(moved), -1, 1)
+
+
+def _bn_dims(shape):
+    n, c = int(shape[0]), int(shape[1])
+    return n, c, int(np.prod(shape[2:], dtype=np.int64))
+
+
+def batch_norm_forward(x, weight=None, bias=None, running_mean=None, running_var=None, training=True, momentum=0.1,
+                       eps=1e-5, channels_last=False):
+    """aten::native_batch_norm on the device (csrc/ops/batch_norm.cpp:21-83).  x: logical [n, c, ...];
+    weight / bias / running_*: channel vectors (any strided float32 view) or None.  Returns
+    (y, save_mean, save_inv, running_mean, running_var): save_* are empty in evaluation mode, the
+    running statistics are the device's values after the call (None where not given)."""
+    n, c, s = _bn_dims(x.shape)
+    layout = BN_INTERLEAVED if channels_last else BN_PLANAR
+    xv = DeviceView(_bn_pack(x, channels_last))
+    vec = [DeviceView(v) if v is not None else None for v in (weight, bias, running_mean, running_var)]
+    arg = lambda v: (v.ptr if v else None, v.strides[0] if v else 0)
+    y = DeviceBuffer(4 * n * c * s)
+    sm, si = DeviceBuffer(4 * c), DeviceBuffer(4 * c)
+    ws_n = int(lib().b200_batch_norm_workspace(n, c, s, layout))
+    ws = DeviceBuffer(ws_n)
+    check(lib().b200_batch_norm_forward(n, c, s, layout, xv.ptr, *arg(vec[0]), *arg(vec[1]), *arg(vec[2]), *arg(vec[3]),
+                                        int(bool(training)), momentum, eps, y.ptr, sm.ptr, si.ptr, ws.ptr, ws_n, None))
+    out = _bn_unpack(y.to_numpy((n * c * s,)), x.shape, channels_last)
+
+    def back(view, like):  # the (possibly strided) vector as the device left it
+        if view is None:
+            return None
+        raw = np.empty(view.buf.nbytes // 4, np.float32)
+        check(lib().b200_memcpy(raw.ctypes.data, view.buf.ptr, raw.nbytes, D2H, None))
+        check(lib().b200_stream_sync(None))
+        first = (view.ptr - view.buf.ptr) // 4
+        return raw[first::view.strides[0] if view.strides[0] else 1][:c].copy()
+
+    empty = np.empty((0,), np.float32)
+    return (out, sm.to_numpy((c,)) if training else empty, si.to_numpy((c,)) if training else empty,
+            back(vec[2], running_mean), back(vec[3], running_var))
+
+
+def batch_norm_backward(grad, x, weight, mean, inv_or_var, training=True, eps=1e-5, mask=(True, True, True),
+                        channels_last=False):
+    """aten::native_batch_norm_backward on the device (csrc/ops/batch_norm.cpp:84-113): (dx, dw, db),
+    None where masked off.  mean / inv_or_var: save_mean / save_inv in training mode, the running
+    statistics in evaluation mode."""
+    if tuple(grad.shape) != tuple(x.shape):
+        raise ValueError("batch norm backward: gradient shape mismatch")
+    n, c, s = _bn_dims(x.shape)
+    layout = BN_INTERLEAVED if channels_last else BN_PLANAR
+    xv, gv = DeviceView(_bn_pack(x, channels_last)), DeviceView(_bn_pack(grad, channels_last))
+    wv = DeviceView(weight) if weight is not None else None
+    mv, iv = DeviceView(mean), DeviceView(inv_or_var)
+    dx = DeviceBuffer(4 * n * c * s) if mask[0] else None
+    dw = DeviceBuffer(4 * c) if mask[1] else None
+    db = DeviceBuffer(4 * c) if mask[2] else None
+    ws_n = int(lib().b200_batch_norm_workspace(n, c, s, layout))
+    ws = DeviceBuffer(ws_n)
+    check(lib().b200_batch_norm_backward(n, c, s, layout, gv.ptr, xv.ptr, wv.ptr if wv else None, wv.strides[0] if wv else 0,
+                                         mv.ptr, mv.strides[0], iv.ptr, iv.strides[0], int(bool(training)), eps,
+                                         dx.ptr if dx else None, dw.ptr if dw else None, db.ptr if db else None,
+                                         ws.ptr, ws_n, None))
+    return (_bn_unpack(dx.to_numpy((n * c * s,)), x.shape, channels_last) if dx else None,
+            dw.to_numpy((c,)) if dw else None, db.to_numpy((c,)) if db else None)

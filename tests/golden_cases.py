@@ -40,3 +40,28 @@ def gemm_cases():
                         outs=[z[f"g{i}_{j}_out"] for j in range(3)],
                         scalars=[(1.0, 1.0), (0.0, 1.0), (0.5, -2.0)]))
     return out
+
+
+_BN = None
+
+
+def batch_norm_cases():
+    """List of dicts: tag, training, momentum, eps, inputs x, g, w, b, rm, rv (None where absent) and
+    the PyTorch-CPU FP64 results y, mean, inv, dx, dw, db, rm_out, rv_out."""
+    global _BN
+    if _BN is None:
+        z = np.load(os.path.join(HERE, "golden", "batch_norm_cases.npz"))
+        cases = []
+        for i, tag in enumerate(z["tags"]):
+            training, momentum, eps = z[f"c{i}_cfg"]
+            case = dict(tag=str(tag), index=i, training=bool(training), momentum=float(momentum), eps=float(eps))
+            for k in ("x", "g", "w", "b", "rm", "rv", "y", "mean", "inv", "dx", "dw", "db", "rm_out", "rv_out"):
+                key = f"c{i}_{k}"
+                case[k] = z[key] if key in z.files else None
+            cases.append(case)
+        _BN = cases
+    return _BN
+
+
+def bn_case_id(case):
+    return f"{case['tag']}{case['index']}-" + "x".join(map(str, case["x"].shape)) + ("-train" if case["training"] else "-eval")

@@ -1,0 +1,110 @@
+#!/usr/bin/env python
+"""Times the BatchNorm kernels through the C ABI on one B200 and reports them against the HBM roofline.
+
+  python pytorch-vulkan_b200/bench_batch_norm.py [--reps R] [--shapes n,c,s;n,c,s...]
+
+Shapes default to the activations of the convolution benchmark's layer sweep (batch 64).  For each
+shape and layout (planar = NCHW, interleaved = channels-last) three calls are timed with CUDA events
+on the launching stream: training forward, evaluation forward, training backward (dx, dw, db).
+Algorithmic bytes per element: training forward 12 (statistics read, normalisation read, write),
+evaluation 8 (read, write), backward 20 (x and g read for the sums, x and g read again, dx written).
+`cold` rows write a 256 MB buffer (larger than L2) before every timed call; `warm` rows run the
+calls back to back, so tensors smaller than L2 are partly served from it.  One JSON line per row.
+"""
+import argparse
+import json
+import os
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, HERE)
+
+DEFAULT_SHAPES = [(64, 64, 3136), (64, 256, 3136), (64, 128, 784), (64, 256, 196), (64, 512, 49), (64, 1024, 3136)]
+BYTES_PER_ELEMENT = {"train_forward": 12, "eval_forward": 8, "train_backward": 20}
+
+
+def hbm_peak():
+    path = os.path.join(HERE, "..", "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        return json.load(open(path))["hbm_gbs"], "measured"
+    return 6650.0, "fallback"
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reps", type=int, default=10)
+    ap.add_argument("--shapes", default="")
+    args = ap.parse_args()
+    import torch
+    import b200conv
+    if not torch.cuda.is_available():
+        raise SystemExit("needs a CUDA device: the BatchNorm path has no CPU fallback")
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    b200conv.init(0)
+    L = b200conv.lib()
+    stream = torch.cuda.current_stream().cuda_stream
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    peak, peak_source = hbm_peak()
+    shapes = DEFAULT_SHAPES if not args.shapes else [tuple(int(v) for v in s.split(",")) for s in args.shapes.split(";")]
+
+    def timed(fn, cold):
+        for _ in range(3):
+            b200conv.check(fn())
+        if not cold:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(args.reps):
+                b200conv.check(fn())
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) / args.reps
+        total = 0.0
+        for _ in range(args.reps):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            b200conv.check(fn())
+            e1.record()
+            torch.cuda.synchronize()
+            total += e0.elapsed_time(e1)
+        return total / args.reps
+
+    for n, c, s in shapes:
+        for layout, layout_name in ((b200conv.BN_PLANAR, "planar"), (b200conv.BN_INTERLEAVED, "interleaved")):
+            gen = torch.Generator(device=dev).manual_seed(n + c + s)
+            x = torch.randn(n * c * s, device=dev, generator=gen)
+            g = torch.randn(n * c * s, device=dev, generator=gen)
+            y, dx = torch.empty_like(x), torch.empty_like(x)
+            w, b = torch.randn(c, device=dev, generator=gen), torch.randn(c, device=dev, generator=gen)
+            rm, rv = torch.zeros(c, device=dev), torch.ones(c, device=dev)
+            sm, si, dw, db = (torch.empty(c, device=dev) for _ in range(4))
+            ws_n = L.b200_batch_norm_workspace(n, c, s, layout)
+            ws = torch.empty(ws_n, dtype=torch.uint8, device=dev)
+            P = lambda t: t.data_ptr()
+            calls = {
+                "train_forward": lambda: L.b200_batch_norm_forward(n, c, s, layout, P(x), P(w), 1, P(b), 1, P(rm), 1, P(rv), 1, 1,
+                                                                   0.1, 1e-5, P(y), P(sm), P(si), P(ws), ws_n, stream),
+                "eval_forward": lambda: L.b200_batch_norm_forward(n, c, s, layout, P(x), P(w), 1, P(b), 1, P(rm), 1, P(rv), 1, 0,
+                                                                  0.1, 1e-5, P(y), P(sm), P(si), P(ws), ws_n, stream),
+                "train_backward": lambda: L.b200_batch_norm_backward(n, c, s, layout, P(g), P(x), P(w), 1, P(sm), 1, P(si), 1, 1,
+                                                                     1e-5, P(dx), P(dw), P(db), P(ws), ws_n, stream),
+            }
+            for name, fn in calls.items():
+                before = b200conv.launch_count()
+                b200conv.check(fn())
+                launches = b200conv.launch_count() - before
+                nbytes = BYTES_PER_ELEMENT[name] * n * c * s
+                for cold in (False, True):
+                    ms = timed(fn, cold)
+                    gbs = nbytes / ms / 1e6
+                    print(json.dumps({"op": name, "n": n, "c": c, "s": s, "layout": layout_name, "tensor_mb": round(4e-6 * n * c * s, 1),
+                                      "cache": "cold" if cold else "warm", "us": round(ms * 1e3, 1), "gpu_launches": launches,
+                                      "kernels": b200conv.last_kernel(),
+                                      "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peak, "unit": "GB/s",
+                                                   "frac": round(gbs / peak, 3), "peak_source": peak_source}}), flush=True)
+            del x, g, y, dx
+
+
+if __name__ == "__main__":
+    main()

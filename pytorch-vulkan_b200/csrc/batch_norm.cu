@@ -27,7 +27,7 @@ namespace {
 
 constexpr int kThreads = 256;
 constexpr int kRowsInnerMin = 256;  // planes at least this long use the rows arrangement
-constexpr int kSegment = 2048;      // floats of a plane one warp streams per unit
+constexpr int kSegment = 2048;      // most floats of a plane one warp streams per unit
 
 struct Moments {
   float n, mean, m2;
@@ -40,13 +40,13 @@ __device__ __forceinline__ Moments merge(Moments a, Moments b) {
   return {n, a.mean + d * f, a.m2 + b.m2 + d * d * a.n * f};
 }
 
+__device__ __forceinline__ Moments shfl_moments(Moments m, int o) {
+  return {__shfl_xor_sync(0xffffffffu, m.n, o), __shfl_xor_sync(0xffffffffu, m.mean, o), __shfl_xor_sync(0xffffffffu, m.m2, o)};
+}
+
 __device__ __forceinline__ Moments warp_merge(Moments m) {
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    Moments other = {__shfl_xor_sync(0xffffffffu, m.n, o), __shfl_xor_sync(0xffffffffu, m.mean, o),
-                     __shfl_xor_sync(0xffffffffu, m.m2, o)};
-    m = merge(m, other);
-  }
+  for (int o = 16; o > 0; o >>= 1) m = merge(m, shfl_moments(m, o));
   return m;
 }
 
@@ -72,7 +72,8 @@ struct BnShape {
   int outer, c, inner;  // logical [outer][c][inner]
   int cols;             // c * inner
   int slabs;            // partial results per column (columns) or per channel (rows)
-  int segs;             // rows: plane segments per plane
+  int per;              // units (rows arrangement) or rows (columns) per slab
+  int segs, seg_len;    // rows: segments per plane and their length (a multiple of 4)
   int part_inner;       // partial entries per channel and slab: inner (columns) or 1 (rows)
   float m;              // outer * inner, the reduction length
 };
@@ -80,14 +81,14 @@ struct BnShape {
 // ---- forward: statistics -----------------------------------------------------------------
 
 // rows arrangement: grid (c, slabs); part[slab * c + ch].
-__global__ void __launch_bounds__(kThreads) bn_stats_rows_kernel(const float* __restrict__ x, BnShape sh, Moments* part) {
+__global__ void __launch_bounds__(kThreads, 8) bn_stats_rows_kernel(const float* __restrict__ x, BnShape sh, Moments* part) {
   const int ch = blockIdx.x, slab = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int units = sh.outer * sh.segs, per = (units + sh.slabs - 1) / sh.slabs;
+  const int units = sh.outer * sh.segs, per = sh.per;
   const int u0 = slab * per, u1 = min(units, u0 + per);
   const float origin = __ldg(x + (size_t)ch * sh.inner);
   Moments acc = {0.f, 0.f, 0.f};
   for (int u = u0 + warp; u < u1; u += kThreads / 32) {
-    const int img = u / sh.segs, off = (u - img * sh.segs) * kSegment, len = min(kSegment, sh.inner - off);
+    const int img = u / sh.segs, off = (u - img * sh.segs) * sh.seg_len, len = min(sh.seg_len, sh.inner - off);
     const float* base = x + ((size_t)img * sh.c + ch) * sh.inner + off;
     const float k = __ldg(base + min(lane, len - 1));
     Shifted t;
@@ -127,10 +128,10 @@ __global__ void __launch_bounds__(kThreads) bn_stats_rows_kernel(const float* __
 // columns arrangement: grid (ceil(cols / (8 V)), slabs); V adjacent columns per thread (V = 4 needs
 // cols % 4 == 0 and a 16-byte aligned tensor); part[slab * cols + col].
 template <int V>
-__global__ void __launch_bounds__(kThreads) bn_stats_cols_kernel(const float* __restrict__ x, BnShape sh, Moments* part) {
+__global__ void __launch_bounds__(kThreads, 5) bn_stats_cols_kernel(const float* __restrict__ x, BnShape sh, Moments* part) {
   const int cl = (threadIdx.x & 7) * V, prow = threadIdx.x >> 3, slab = blockIdx.y;
   const int col0 = blockIdx.x * 8 * V + cl;
-  const int per = (sh.outer + sh.slabs - 1) / sh.slabs;
+  const int per = sh.per;
   const int r0 = slab * per, r1 = min(sh.outer, r0 + per);
   const bool live = col0 < sh.cols;  // V == 4: cols % 4 == 0, so a live quad is whole
   float origin[V];
@@ -182,16 +183,23 @@ __global__ void __launch_bounds__(kThreads) bn_stats_cols_kernel(const float* __
       for (int j = 0; j < V; ++j) acc[j] = merge(acc[j], t[j].moments(k[j], origin[j]));
     }
   }
-  // the 32 row-lanes of each column meet in shared memory
-  __shared__ Moments sm[32][8 * V + 1];
+  // the 32 row-lanes of a column: four share a warp (lanes l, l+8, l+16, l+24), the eight warps
+  // meet in shared memory
+  __shared__ Moments sm[kThreads / 32][8 * V + 1];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 #pragma unroll
-  for (int j = 0; j < V; ++j) sm[prow][cl + j] = acc[j];
+  for (int j = 0; j < V; ++j) {
+    acc[j] = merge(acc[j], shfl_moments(acc[j], 8));
+    acc[j] = merge(acc[j], shfl_moments(acc[j], 16));
+    if (lane < 8) sm[warp][cl + j] = acc[j];
+  }
   __syncthreads();
   if (threadIdx.x < 8 * V) {
     const int col = blockIdx.x * 8 * V + threadIdx.x;
     if (col < sh.cols) {
       Moments m = sm[0][threadIdx.x];
-      for (int p = 1; p < 32; ++p) m = merge(m, sm[p][threadIdx.x]);
+#pragma unroll
+      for (int w = 1; w < kThreads / 32; ++w) m = merge(m, sm[w][threadIdx.x]);
       part[(size_t)slab * sh.cols + col] = m;
     }
   }
@@ -291,6 +299,30 @@ __global__ void __launch_bounds__(kThreads) bn_apply_kernel(const float* __restr
   for (; q < quads; q += stride) one(q, __ldg(x4 + q));
 }
 
+// Channels-last with c % 4 == 0: a thread keeps one group of four channels, whose coefficients stay
+// in registers, and walks down the rows.  `lanes` (a multiple of c / 4) threads take part.
+__global__ void __launch_bounds__(kThreads) bn_apply_cols_kernel(const float* __restrict__ x, float* __restrict__ y,
+                                                                  const float4* __restrict__ coef, uint32_t rows, uint32_t c4,
+                                                                  uint32_t lanes) {
+  const uint32_t t = blockIdx.x * kThreads + threadIdx.x;
+  if (t >= lanes) return;
+  const uint32_t r0 = t / c4, j = t - r0 * c4;
+  const uint64_t rstep = lanes / c4;
+  const float4 k0 = __ldg(coef + 4 * j), k1 = __ldg(coef + 4 * j + 1), k2 = __ldg(coef + 4 * j + 2), k3 = __ldg(coef + 4 * j + 3);
+  const float4* x4 = reinterpret_cast<const float4*>(x) + j;
+  float4* y4 = reinterpret_cast<float4*>(y) + j;
+  auto one = [&](uint64_t row, float4 a) {
+    y4[row * c4] = make_float4(normalise(a.x, k0), normalise(a.y, k1), normalise(a.z, k2), normalise(a.w, k3));
+  };
+  uint64_t r = r0;
+  for (; r + 3 * rstep < rows; r += 4 * rstep) {
+    const float4 a0 = __ldg(x4 + r * c4), a1 = __ldg(x4 + (r + rstep) * c4), a2 = __ldg(x4 + (r + 2 * rstep) * c4),
+                 a3 = __ldg(x4 + (r + 3 * rstep) * c4);
+    one(r, a0), one(r + rstep, a1), one(r + 2 * rstep, a2), one(r + 3 * rstep, a3);
+  }
+  for (; r < rows; r += rstep) one(r, __ldg(x4 + r * c4));
+}
+
 // Scalar form: unaligned tensors and the last total % 4 elements ([first, total)).
 __global__ void __launch_bounds__(kThreads) bn_apply_scalar_kernel(const float* __restrict__ x, float* __restrict__ y,
                                                                     const float4* __restrict__ coef, uint32_t first, uint32_t total,
@@ -329,15 +361,15 @@ struct BnBackwardVectors {
   int training;
 };
 
-__global__ void __launch_bounds__(kThreads) bn_bwd_rows_kernel(const float* __restrict__ x, const float* __restrict__ g, BnShape sh,
+__global__ void __launch_bounds__(kThreads, 8) bn_bwd_rows_kernel(const float* __restrict__ x, const float* __restrict__ g, BnShape sh,
                                                                 BnBackwardVectors v, Sums* part) {
   const int ch = blockIdx.x, slab = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int units = sh.outer * sh.segs, per = (units + sh.slabs - 1) / sh.slabs;
+  const int units = sh.outer * sh.segs, per = sh.per;
   const int u0 = slab * per, u1 = min(units, u0 + per);
   const float mean = v.mean[ch * v.mean_stride];
   Sums t = {0.f, 0.f, 0.f};
   for (int u = u0 + warp; u < u1; u += kThreads / 32) {
-    const int img = u / sh.segs, off = (u - img * sh.segs) * kSegment, len = min(kSegment, sh.inner - off);
+    const int img = u / sh.segs, off = (u - img * sh.segs) * sh.seg_len, len = min(sh.seg_len, sh.inner - off);
     const size_t at = ((size_t)img * sh.c + ch) * sh.inner + off;
     const float *xb = x + at, *gb = g + at;
     int done = 0;
@@ -371,11 +403,11 @@ __global__ void __launch_bounds__(kThreads) bn_bwd_rows_kernel(const float* __re
 }
 
 template <int V>
-__global__ void __launch_bounds__(kThreads) bn_bwd_cols_kernel(const float* __restrict__ x, const float* __restrict__ g, BnShape sh,
+__global__ void __launch_bounds__(kThreads, 5) bn_bwd_cols_kernel(const float* __restrict__ x, const float* __restrict__ g, BnShape sh,
                                                                 BnBackwardVectors v, Sums* part) {
   const int cl = (threadIdx.x & 7) * V, prow = threadIdx.x >> 3, slab = blockIdx.y;
   const int col0 = blockIdx.x * 8 * V + cl;
-  const int per = (sh.outer + sh.slabs - 1) / sh.slabs;
+  const int per = sh.per;
   const int r0 = slab * per, r1 = min(sh.outer, r0 + per);
   float mean[V];
   Sums t[V];
@@ -408,15 +440,25 @@ __global__ void __launch_bounds__(kThreads) bn_bwd_cols_kernel(const float* __re
       for (; r < r1; r += 32, at += step) t[0].add(__ldg(x + at), __ldg(g + at), mean[0]);
     }
   }
-  __shared__ Sums sm[32][8 * V + 1];
+  __shared__ Sums sm[kThreads / 32][8 * V + 1];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 #pragma unroll
-  for (int j = 0; j < V; ++j) sm[prow][cl + j] = t[j];
+  for (int j = 0; j < V; ++j) {
+#pragma unroll
+    for (int o = 8; o <= 16; o <<= 1) {
+      t[j].a += __shfl_xor_sync(0xffffffffu, t[j].a, o);
+      t[j].b += __shfl_xor_sync(0xffffffffu, t[j].b, o);
+      t[j].r += __shfl_xor_sync(0xffffffffu, t[j].r, o);
+    }
+    if (lane < 8) sm[warp][cl + j] = t[j];
+  }
   __syncthreads();
   if (threadIdx.x < 8 * V) {
     const int col = blockIdx.x * 8 * V + threadIdx.x;
     if (col < sh.cols) {
       Sums s = sm[0][threadIdx.x];
-      for (int p = 1; p < 32; ++p) s.a += sm[p][threadIdx.x].a, s.b += sm[p][threadIdx.x].b, s.r += sm[p][threadIdx.x].r;
+#pragma unroll
+      for (int w = 1; w < kThreads / 32; ++w) s.a += sm[w][threadIdx.x].a, s.b += sm[w][threadIdx.x].b, s.r += sm[w][threadIdx.x].r;
       part[(size_t)slab * sh.cols + col] = s;
     }
   }
@@ -523,6 +565,35 @@ __global__ void __launch_bounds__(kThreads) bn_bwd_apply_kernel(const float* __r
   for (; q < quads; q += stride) one(q, TRAINING ? __ldg(x4 + q) : zero, __ldg(g4 + q));
 }
 
+// The channels-last form of the kernel above (c % 4 == 0): one group of four channels per thread.
+template <bool TRAINING>
+__global__ void __launch_bounds__(kThreads) bn_bwd_apply_cols_kernel(const float* __restrict__ x, const float* __restrict__ g,
+                                                                      float* __restrict__ dx, const float4* __restrict__ coef,
+                                                                      const float* __restrict__ scale, uint32_t rows, uint32_t c4,
+                                                                      uint32_t lanes) {
+  const uint32_t t = blockIdx.x * kThreads + threadIdx.x;
+  if (t >= lanes) return;
+  const uint32_t r0 = t / c4, j = t - r0 * c4;
+  const uint64_t rstep = lanes / c4;
+  const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+  const float4 k0 = TRAINING ? __ldg(coef + 4 * j) : zero, k1 = TRAINING ? __ldg(coef + 4 * j + 1) : zero,
+               k2 = TRAINING ? __ldg(coef + 4 * j + 2) : zero, k3 = TRAINING ? __ldg(coef + 4 * j + 3) : zero;
+  const float4 s = __ldg(reinterpret_cast<const float4*>(scale) + j);
+  const float4 *x4 = reinterpret_cast<const float4*>(x) + j, *g4 = reinterpret_cast<const float4*>(g) + j;
+  float4* d4 = reinterpret_cast<float4*>(dx) + j;
+  auto one = [&](uint64_t row, float4 a, float4 b) {
+    d4[row * c4] = make_float4(input_grad<TRAINING>(a.x, b.x, k0, s.x), input_grad<TRAINING>(a.y, b.y, k1, s.y),
+                               input_grad<TRAINING>(a.z, b.z, k2, s.z), input_grad<TRAINING>(a.w, b.w, k3, s.w));
+  };
+  uint64_t r = r0;
+  for (; r + rstep < rows; r += 2 * rstep) {
+    const float4 b0 = __ldg(g4 + r * c4), b1 = __ldg(g4 + (r + rstep) * c4);
+    const float4 a0 = TRAINING ? __ldg(x4 + r * c4) : zero, a1 = TRAINING ? __ldg(x4 + (r + rstep) * c4) : zero;
+    one(r, a0, b0), one(r + rstep, a1, b1);
+  }
+  for (; r < rows; r += rstep) one(r, TRAINING ? __ldg(x4 + r * c4) : zero, __ldg(g4 + r * c4));
+}
+
 template <bool TRAINING>
 __global__ void __launch_bounds__(kThreads) bn_bwd_apply_scalar_kernel(const float* __restrict__ x, const float* __restrict__ g,
                                                                         float* __restrict__ dx, const float4* __restrict__ coef,
@@ -555,21 +626,34 @@ int make_plan(int64_t n, int64_t c, int64_t s, int layout, BnPlan* out) {
   sh.cols = sh.c * sh.inner;
   sh.m = (float)((double)n * (double)s);
   p.rows = sh.inner >= kRowsInnerMin;
-  const int target = 4 * sm_count();  // CTAs wanted in flight
+  // CTAs wanted, from measurement: one wave of eight 32-register CTAs per SM for the rows kernels,
+  // four per SM for the column kernels (48 registers, a longer epilogue per CTA)
+  const int target = (p.rows ? 8 : 4) * sm_count();
+  const int kMinUnits = 8, kMinRows = 512;  // least units (rows kernels) / rows (column kernels) per CTA
   if (p.rows) {
     sh.segs = (sh.inner + kSegment - 1) / kSegment;
+    sh.seg_len = ((sh.inner + sh.segs - 1) / sh.segs + 3) & ~3;  // equal segments, 16-byte steps
     sh.part_inner = 1;
+    // a CTA takes a multiple of eight units (one per warp and round), so no warp idles while the
+    // others finish, and at least kMinUnits of them
     const int64_t units = (int64_t)sh.outer * sh.segs;
     int64_t slabs = (target + sh.c - 1) / sh.c;
-    const int64_t most = (units + 7) / 8;  // at least one unit per warp
-    sh.slabs = (int)(slabs < 1 ? 1 : (slabs > most ? most : slabs));
+    int64_t per = (units + slabs - 1) / slabs;
+    if (per < kMinUnits) per = kMinUnits;
+    per = (per + 7) / 8 * 8;
+    sh.slabs = (int)((units + per - 1) / per);
+    sh.per = (int)per;
   } else {
     sh.segs = 1;
+    sh.seg_len = sh.inner;
     sh.part_inner = sh.inner;
     const int col_blocks = (sh.cols + 31) / 32;
     int64_t slabs = (target + col_blocks - 1) / col_blocks;
-    const int64_t most = (sh.outer + 127) / 128;  // at least four rows per thread
-    sh.slabs = (int)(slabs < 1 ? 1 : (slabs > most ? most : slabs));
+    int64_t per = (sh.outer + slabs - 1) / slabs;
+    if (per < kMinRows) per = kMinRows;
+    per = (per + 127) / 128 * 128;  // whole passes of 32 row-lanes x 4 loads
+    sh.slabs = (int)((sh.outer + per - 1) / per);
+    sh.per = (int)per;
   }
   if (sh.slabs > 65535) sh.slabs = 65535;
   p.coef_bytes = ((size_t)sh.c * sizeof(float4) + 255) & ~(size_t)255;
@@ -657,7 +741,10 @@ int b200_batch_norm_forward(int64_t n, int64_t c, int64_t s, int layout, const f
     const uint32_t quads = total >> 2;
     if (quads) {
       const int grid = apply_grid((quads + 3) / 4);
-      if (uniform) bn_apply_kernel<true><<<grid, kThreads, 0, st>>>(x, y, coef, total, channel_of(sh, true));
+      const uint32_t c4 = (uint32_t)sh.c / 4, threads = (uint32_t)grid * kThreads;
+      if (sh.inner == 1 && sh.c % 4 == 0 && threads >= c4)
+        bn_apply_cols_kernel<<<grid, kThreads, 0, st>>>(x, y, coef, (uint32_t)sh.outer, c4, threads / c4 * c4);
+      else if (uniform) bn_apply_kernel<true><<<grid, kThreads, 0, st>>>(x, y, coef, total, channel_of(sh, true));
       else bn_apply_kernel<false><<<grid, kThreads, 0, st>>>(x, y, coef, total, channel_of(sh, false));
       count_launch();
       if (int rc = launch_check("bn_apply_kernel")) return rc;
@@ -723,7 +810,12 @@ int b200_batch_norm_backward(int64_t n, int64_t c, int64_t s, int layout, const 
   if (vec && (total >> 2)) {
     const int grid = apply_grid(((total >> 2) + 1) / 2);
     const ChannelOf ch = channel_of(sh, uniform);
-    if (training) {
+    const uint32_t c4 = (uint32_t)sh.c / 4, threads = (uint32_t)grid * kThreads;
+    if (sh.inner == 1 && sh.c % 4 == 0 && threads >= c4) {
+      const uint32_t lanes = threads / c4 * c4;
+      if (training) bn_bwd_apply_cols_kernel<true><<<grid, kThreads, 0, st>>>(x, grad, dx, coef, scale, (uint32_t)sh.outer, c4, lanes);
+      else bn_bwd_apply_cols_kernel<false><<<grid, kThreads, 0, st>>>(x, grad, dx, coef, scale, (uint32_t)sh.outer, c4, lanes);
+    } else if (training) {
       if (uniform) bn_bwd_apply_kernel<true, true><<<grid, kThreads, 0, st>>>(x, grad, dx, coef, scale, total, ch);
       else bn_bwd_apply_kernel<false, true><<<grid, kThreads, 0, st>>>(x, grad, dx, coef, scale, total, ch);
     } else {

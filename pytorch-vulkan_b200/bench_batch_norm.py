@@ -34,6 +34,8 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reps", type=int, default=10)
     ap.add_argument("--shapes", default="")
+    ap.add_argument("--cpu-baseline", action="store_true",
+                    help="also time PyTorch's CPU FP32 batch norm (the arithmetic the reference's tests compare with) on the host cores")
     args = ap.parse_args()
     import torch
     import b200conv
@@ -70,6 +72,23 @@ def main():
             total += e0.elapsed_time(e1)
         return total / args.reps
 
+    if args.cpu_baseline:
+        import time
+        n, c, s = shapes[0]
+        x, g = torch.randn(n, c, s), torch.randn(n, c, s)
+        w, b, rm, rv = torch.randn(c), torch.randn(c), torch.zeros(c), torch.ones(c)
+        for name, k in (("train_forward", 3), ("train_backward", 3)):
+            best = float("inf")
+            for _ in range(k + 1):
+                t0 = time.perf_counter()
+                if name == "train_forward":
+                    y, sm, si = torch.ops.aten.native_batch_norm(x, w, b, rm, rv, True, 0.1, 1e-5)
+                else:
+                    torch.ops.aten.native_batch_norm_backward(g, x, w, rm, rv, sm, si, True, 1e-5, [True, True, True])
+                best = min(best, time.perf_counter() - t0)
+            nbytes = BYTES_PER_ELEMENT[name] * n * c * s
+            print(json.dumps({"op": name, "n": n, "c": c, "s": s, "impl": "pytorch-cpu-fp32", "cores": torch.get_num_threads(),
+                              "us": round(best * 1e6, 1), "GB/s": round(nbytes / best / 1e9, 1)}), flush=True)
     for n, c, s in shapes:
         for layout, layout_name in ((b200conv.BN_PLANAR, "planar"), (b200conv.BN_INTERLEAVED, "interleaved")):
             gen = torch.Generator(device=dev).manual_seed(n + c + s)

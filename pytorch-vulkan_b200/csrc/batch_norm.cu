@@ -567,7 +567,7 @@ __global__ void __launch_bounds__(kThreads) bn_bwd_apply_kernel(const float* __r
 
 // The channels-last form of the kernel above (c % 4 == 0): one group of four channels per thread.
 template <bool TRAINING>
-__global__ void __launch_bounds__(kThreads) bn_bwd_apply_cols_kernel(const float* __restrict__ x, const float* __restrict__ g,
+__global__ void __launch_bounds__(kThreads, 5) bn_bwd_apply_cols_kernel(const float* __restrict__ x, const float* __restrict__ g,
                                                                       float* __restrict__ dx, const float4* __restrict__ coef,
                                                                       const float* __restrict__ scale, uint32_t rows, uint32_t c4,
                                                                       uint32_t lanes) {

@@ -232,6 +232,27 @@ int b200_batch_norm_backward(int64_t n, int64_t c, int64_t s, int layout, const 
                              const float* inv_or_var, int64_t inv_stride, int training, float eps, float* dx, float* dw,
                              float* db, void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---- GroupNorm ---------------------------------------------------------------------------------- */
+
+/* All tensors contiguous FP32: x, y, grad, dx [n][c][hw]; weight, bias, dw, db [c]; mean, rstd
+ * [n][groups] (the reference packs every operand first, csrc/ops/group_norm.cpp:97-99,134-135).
+ * Bytes of workspace the backward call needs when dw or db is asked for (0 on invalid shapes). */
+size_t b200_group_norm_workspace(int64_t n, int64_t c, int64_t hw, int64_t groups);
+
+/* y = (x - mean) * rstd * weight + bias with mean / rstd = 1/sqrt(var + eps) over each (sample,
+ * group) block of c/groups * hw values; mean and rstd are written.  weight / bias NULL = absent.
+ * Replaces forward (csrc/ops/group_norm.cpp:76-109) and group_norm_forward.comp.
+ * More than 4096 channels per group: B200_EUNSUPPORTED. */
+int b200_group_norm_forward(int64_t n, int64_t c, int64_t hw, int64_t groups, const float* x, const float* weight,
+                            const float* bias, float eps, float* y, float* mean, float* rstd, void* stream);
+
+/* dx, dw (weight gradient), db (bias gradient); NULL = not wanted.  Replaces backward
+ * (csrc/ops/group_norm.cpp:111-155) with group_norm_backward_input.comp and
+ * group_norm_backward_affine.comp; one pass over x and grad feeds all three results. */
+int b200_group_norm_backward(int64_t n, int64_t c, int64_t hw, int64_t groups, const float* grad, const float* x,
+                             const float* mean, const float* rstd, const float* weight, float* dx, float* dw, float* db,
+                             void* workspace, size_t workspace_bytes, void* stream);
+
 /* Device-side health word.  The tcgen05 kernels bound every wait on an mbarrier; a wait that
  * gives up records (code << 24 | CTA index) here, frees its tensor memory and returns, so the
  * context stays usable.  *status = 0 means no wait ever gave up.  Synchronises the device.

@@ -94,6 +94,11 @@ SIGNATURES = {
     "b200_batch_norm_backward": (c_int, [c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_void_p,
                                          c_int64, c_void_p, c_int64, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p,
                                          c_size_t, c_void_p]),
+    "b200_group_norm_workspace": (c_size_t, [c_int64, c_int64, c_int64, c_int64]),
+    "b200_group_norm_forward": (c_int, [c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_float, c_void_p,
+                                        c_void_p, c_void_p, c_void_p]),
+    "b200_group_norm_backward": (c_int, [c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                         c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
     "b200_device_status": (c_int, [POINTER(c_int), c_int]),
     "b200_launch_count": (c_uint64, []),
     "b200_last_kernel": (c_char_p, []),
@@ -412,3 +417,36 @@ def batch_norm_backward(grad, x, weight, mean, inv_or_var, training=True, eps=1e
                                          ws.ptr, ws_n, None))
     return (_bn_unpack(dx.to_numpy((n * c * s,)), x.shape, channels_last) if dx else None,
             dw.to_numpy((c,)) if dw else None, db.to_numpy((c,)) if db else None)
+
+
+def _dense(a):
+    return None if a is None else DeviceView(np.ascontiguousarray(a, np.float32))
+
+
+def group_norm_forward(x, groups, weight=None, bias=None, eps=1e-5):
+    """aten::native_group_norm on the device (csrc/ops/group_norm.cpp:76-109): (y, mean [n, groups],
+    rstd [n, groups]) for x of logical shape [n, c, ...]."""
+    n, c, hw = _bn_dims(x.shape)
+    xv, wv, bv = _dense(x), _dense(weight), _dense(bias)
+    y, mean, rstd = DeviceBuffer(4 * n * c * hw), DeviceBuffer(4 * n * groups), DeviceBuffer(4 * n * groups)
+    check(lib().b200_group_norm_forward(n, c, hw, groups, xv.ptr, wv.ptr if wv else None, bv.ptr if bv else None, eps,
+                                        y.ptr, mean.ptr, rstd.ptr, None))
+    return y.to_numpy(x.shape), mean.to_numpy((n, groups)), rstd.to_numpy((n, groups))
+
+
+def group_norm_backward(grad, x, mean, rstd, groups, weight=None, mask=(True, True, True)):
+    """aten::native_group_norm_backward on the device (csrc/ops/group_norm.cpp:111-155): (dx, dw, db),
+    None where masked off."""
+    if tuple(grad.shape) != tuple(x.shape):
+        raise ValueError("group norm backward: gradient shape mismatch")
+    n, c, hw = _bn_dims(x.shape)
+    gv, xv, mv, rv, wv = _dense(grad), _dense(x), _dense(mean), _dense(rstd), _dense(weight)
+    dx = DeviceBuffer(4 * n * c * hw) if mask[0] else None
+    dw = DeviceBuffer(4 * c) if mask[1] else None
+    db = DeviceBuffer(4 * c) if mask[2] else None
+    ws_n = int(lib().b200_group_norm_workspace(n, c, hw, groups))
+    ws = DeviceBuffer(ws_n)
+    check(lib().b200_group_norm_backward(n, c, hw, groups, gv.ptr, xv.ptr, mv.ptr, rv.ptr, wv.ptr if wv else None,
+                                         dx.ptr if dx else None, dw.ptr if dw else None, db.ptr if db else None,
+                                         ws.ptr, ws_n, None))
+    return (dx.to_numpy(x.shape) if dx else None, dw.to_numpy((c,)) if dw else None, db.to_numpy((c,)) if db else None)

@@ -1,0 +1,340 @@
+// GroupNorm forward and backward for contiguous FP32 [n][c][hw] tensors.  Replaces the
+// group_norm_forward / group_norm_backward_input / group_norm_backward_affine shaders of the
+// reference (csrc/shaders/group_norm_*.comp) and their host side (csrc/ops/group_norm.cpp:76-155).
+//
+// A (sample, group) block is c/groups adjacent planes, contiguous in memory.  As in the reference
+// one CTA owns one block, but it is a CTA of 16 warps that each stream whole plane segments with
+// 16-byte loads, and each kernel makes two passes over its block: the first reads it from HBM, the
+// second finds it in L2 (at most three CTAs of a few hundred KB per SM are in flight, far below the
+// 126 MB of L2).  HBM traffic is therefore one read and one write per tensor element:
+//   forward   statistics (pass 1), normalise and write (pass 2)                    8 B / element
+//   backward  the two group sums AND the per-(sample, channel) sums that the affine gradients
+//             need (pass 1), input gradient (pass 2); a small second kernel adds the
+//             per-sample sums over the batch                                     12 B / element
+// The reference reads x and dy a third time for the affine gradients (one thread per channel
+// walking the whole batch, group_norm_backward_affine.comp:16-29); here they fall out of pass 1.
+#include "common.cuh"
+
+namespace b200 {
+namespace {
+
+constexpr int kThreads = 512;
+constexpr int kWarps = kThreads / 32;
+constexpr int kSegment = 2048;   // most floats of a plane one warp streams per unit
+constexpr int kMaxUnits = 4096;  // per-unit partial sums of a block live in shared memory
+
+struct GnShape {
+  int n, c, hw, groups, cpg;  // cpg = channels per group
+  int segs, seg_len;          // a plane is cut into `segs` segments of `seg_len` floats (a multiple of 4)
+  int units;                  // cpg * segs
+  float count;                // cpg * hw
+};
+
+struct Moments {
+  float n, mean, m2;
+};
+__device__ __forceinline__ Moments merge(Moments a, Moments b) {
+  const float n = a.n + b.n;
+  if (!(n > 0.f)) return a;
+  const float d = b.mean - a.mean, f = b.n / n;
+  return {n, a.mean + d * f, a.m2 + b.m2 + d * d * a.n * f};
+}
+__device__ __forceinline__ Moments warp_merge(Moments m) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    Moments other = {__shfl_xor_sync(0xffffffffu, m.n, o), __shfl_xor_sync(0xffffffffu, m.mean, o),
+                     __shfl_xor_sync(0xffffffffu, m.m2, o)};
+    m = merge(m, other);
+  }
+  return m;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// The warp walks `len` floats at p (and at q when TWO): f(a) or f(a, b) per element, 16-byte loads
+// with four in flight per lane where both pointers are aligned.
+template <bool TWO, class F>
+__device__ __forceinline__ void warp_stream(const float* __restrict__ p, const float* __restrict__ q, int len, int lane, F&& f) {
+  int done = 0;
+  const uintptr_t bits = reinterpret_cast<uintptr_t>(p) | (TWO ? reinterpret_cast<uintptr_t>(q) : 0);
+  if ((bits & 15) == 0) {
+    const float4* p4 = reinterpret_cast<const float4*>(p);
+    const float4* q4 = reinterpret_cast<const float4*>(q);
+    const int quads = len >> 2;
+    int i = lane;
+    if (TWO) {
+      for (; i + 32 < quads; i += 64) {
+        const float4 a0 = __ldg(p4 + i), a1 = __ldg(p4 + i + 32), b0 = __ldg(q4 + i), b1 = __ldg(q4 + i + 32);
+        f(a0.x, b0.x), f(a0.y, b0.y), f(a0.z, b0.z), f(a0.w, b0.w);
+        f(a1.x, b1.x), f(a1.y, b1.y), f(a1.z, b1.z), f(a1.w, b1.w);
+      }
+      for (; i < quads; i += 32) {
+        const float4 a = __ldg(p4 + i), b = __ldg(q4 + i);
+        f(a.x, b.x), f(a.y, b.y), f(a.z, b.z), f(a.w, b.w);
+      }
+    } else {
+      for (; i + 96 < quads; i += 128) {
+        const float4 a0 = __ldg(p4 + i), a1 = __ldg(p4 + i + 32), a2 = __ldg(p4 + i + 64), a3 = __ldg(p4 + i + 96);
+        f(a0.x, 0.f), f(a0.y, 0.f), f(a0.z, 0.f), f(a0.w, 0.f);
+        f(a1.x, 0.f), f(a1.y, 0.f), f(a1.z, 0.f), f(a1.w, 0.f);
+        f(a2.x, 0.f), f(a2.y, 0.f), f(a2.z, 0.f), f(a2.w, 0.f);
+        f(a3.x, 0.f), f(a3.y, 0.f), f(a3.z, 0.f), f(a3.w, 0.f);
+      }
+      for (; i < quads; i += 32) {
+        const float4 a = __ldg(p4 + i);
+        f(a.x, 0.f), f(a.y, 0.f), f(a.z, 0.f), f(a.w, 0.f);
+      }
+    }
+    done = quads * 4;
+  }
+  for (int e = done + lane; e < len; e += 32) f(__ldg(p + e), TWO ? __ldg(q + e) : 0.f);
+}
+
+// The same walk producing one output value per element: out[e] = f(a, b).
+template <bool TWO, class F>
+__device__ __forceinline__ void warp_map(const float* __restrict__ p, const float* __restrict__ q, float* __restrict__ out, int len,
+                                         int lane, F&& f) {
+  int done = 0;
+  const uintptr_t bits = reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(out) | (TWO ? reinterpret_cast<uintptr_t>(q) : 0);
+  if ((bits & 15) == 0) {
+    const float4* p4 = reinterpret_cast<const float4*>(p);
+    const float4* q4 = reinterpret_cast<const float4*>(q);
+    float4* o4 = reinterpret_cast<float4*>(out);
+    const int quads = len >> 2;
+    const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+    int i = lane;
+    for (; i + 32 < quads; i += 64) {
+      const float4 a0 = __ldg(p4 + i), a1 = __ldg(p4 + i + 32);
+      const float4 b0 = TWO ? __ldg(q4 + i) : zero, b1 = TWO ? __ldg(q4 + i + 32) : zero;
+      o4[i] = make_float4(f(a0.x, b0.x), f(a0.y, b0.y), f(a0.z, b0.z), f(a0.w, b0.w));
+      o4[i + 32] = make_float4(f(a1.x, b1.x), f(a1.y, b1.y), f(a1.z, b1.z), f(a1.w, b1.w));
+    }
+    for (; i < quads; i += 32) {
+      const float4 a = __ldg(p4 + i), b = TWO ? __ldg(q4 + i) : zero;
+      o4[i] = make_float4(f(a.x, b.x), f(a.y, b.y), f(a.z, b.z), f(a.w, b.w));
+    }
+    done = quads * 4;
+  }
+  for (int e = done + lane; e < len; e += 32) out[e] = f(__ldg(p + e), TWO ? __ldg(q + e) : 0.f);
+}
+
+// Unit u of a block: plane (channel within the group) and the segment's offset and length in it.
+struct Unit {
+  int plane, off, len;
+};
+__device__ __forceinline__ Unit unit_of(const GnShape& sh, int u) {
+  const int plane = u / sh.segs, off = (u - plane * sh.segs) * sh.seg_len;
+  return {plane, off, min(sh.seg_len, sh.hw - off)};
+}
+
+// ---- forward -----------------------------------------------------------------------------------
+// grid = n * groups.  Mean and 1/sqrt(var + eps) per block (group_norm_forward.comp:24-47: shifted
+// first pass, centred second pass; here one pass of pairwise-merged moments, each thread summing
+// around a sample of its own segment), then y = (x - mean) * rstd * gamma[ch] + beta[ch] (:49-54).
+__global__ void __launch_bounds__(kThreads, 3) gn_forward_kernel(const float* __restrict__ x, const float* __restrict__ gamma,
+                                                                 const float* __restrict__ beta, GnShape sh, float eps,
+                                                                 float* __restrict__ y, float* __restrict__ means,
+                                                                 float* __restrict__ rstds) {
+  const int row = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int group = row % sh.groups;
+  const size_t base = ((size_t)(row / sh.groups) * sh.c + (size_t)group * sh.cpg) * sh.hw;
+  const float* xb = x + base;
+  const float origin = __ldg(xb);
+  Moments acc = {0.f, 0.f, 0.f};
+  for (int u = warp; u < sh.units; u += kWarps) {
+    const Unit un = unit_of(sh, u);
+    const float* p = xb + (size_t)un.plane * sh.hw + un.off;
+    const float k = __ldg(p + min(lane, un.len - 1));
+    float cnt = 0.f, s = 0.f, q = 0.f;
+    warp_stream<false>(p, nullptr, un.len, lane, [&](float v, float) {
+      const float d = v - k;
+      s += d;
+      q = fmaf(d, d, q);
+      cnt += 1.f;
+    });
+    if (cnt > 0.f) {
+      const float mean_d = s / cnt;
+      acc = merge(acc, Moments{cnt, (k - origin) + mean_d, fmaxf(q - s * mean_d, 0.f)});
+    }
+  }
+  __shared__ Moments warp_part[kWarps];
+  __shared__ float stat[2];
+  acc = warp_merge(acc);
+  if (lane == 0) warp_part[warp] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    Moments m = warp_part[0];
+#pragma unroll
+    for (int w = 1; w < kWarps; ++w) m = merge(m, warp_part[w]);
+    const float mean = origin + m.mean, rstd = 1.f / sqrtf(m.m2 / sh.count + eps);
+    means[row] = mean;
+    rstds[row] = rstd;
+    stat[0] = m.mean;  // relative to the origin: the low part of the mean stays in the subtraction below
+    stat[1] = rstd;
+  }
+  __syncthreads();
+  const float mean_rel = stat[0], rstd = stat[1];
+  for (int u = warp; u < sh.units; u += kWarps) {
+    const Unit un = unit_of(sh, u);
+    const int ch = group * sh.cpg + un.plane;
+    const float scale = rstd * (gamma ? __ldg(gamma + ch) : 1.f), shift = beta ? __ldg(beta + ch) : 0.f;
+    const size_t at = (size_t)un.plane * sh.hw + un.off;
+    warp_map<false>(xb + at, nullptr, y + base + at, un.len, lane,
+                    [&](float v, float) { return ((v - origin) - mean_rel) * scale + shift; });
+  }
+}
+
+// ---- backward ------------------------------------------------------------------------------------
+// grid = n * groups.  Pass 1: per unit s1 = sum dy, s2 = sum dy * z with z = (x - mean) * rstd.  The
+// units of a plane add up (in unit order) to the per-(sample, channel) sums the affine gradients
+// need; weighted by gamma they add up to the block's a and b (group_norm_backward_input.comp:26-37).
+// Pass 2: dx = rstd * (gamma dy - a / count - z * b / count) (:38-45).
+__global__ void __launch_bounds__(kThreads, 3) gn_backward_kernel(const float* __restrict__ dy, const float* __restrict__ x,
+                                                                  const float* __restrict__ means, const float* __restrict__ rstds,
+                                                                  const float* __restrict__ gamma, GnShape sh, float* __restrict__ dx,
+                                                                  float* __restrict__ plane_sums) {
+  extern __shared__ float unit_sums[];  // [units][2]
+  __shared__ float totals[2];
+  const int row = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int group = row % sh.groups, sample = row / sh.groups;
+  const size_t base = ((size_t)sample * sh.c + (size_t)group * sh.cpg) * sh.hw;
+  const float mean = __ldg(means + row), rstd = __ldg(rstds + row);
+  for (int u = warp; u < sh.units; u += kWarps) {
+    const Unit un = unit_of(sh, u);
+    const size_t at = base + (size_t)un.plane * sh.hw + un.off;
+    float s1 = 0.f, s2 = 0.f;
+    warp_stream<true>(x + at, dy + at, un.len, lane, [&](float xv, float gv) {
+      s1 += gv;
+      s2 = fmaf(gv, (xv - mean) * rstd, s2);
+    });
+    s1 = warp_sum(s1);
+    s2 = warp_sum(s2);
+    if (lane == 0) unit_sums[2 * u] = s1, unit_sums[2 * u + 1] = s2;
+  }
+  __syncthreads();
+  // per plane: add its segments in order; one warp then folds the planes into a and b
+  for (int pl = threadIdx.x; pl < sh.cpg; pl += kThreads) {
+    float s1 = 0.f, s2 = 0.f;
+    for (int sgi = 0; sgi < sh.segs; ++sgi) s1 += unit_sums[2 * (pl * sh.segs + sgi)], s2 += unit_sums[2 * (pl * sh.segs + sgi) + 1];
+    if (plane_sums) {
+      const size_t at = ((size_t)sample * sh.c + (size_t)group * sh.cpg + pl) * 2;
+      plane_sums[at] = s1, plane_sums[at + 1] = s2;
+    }
+    unit_sums[2 * pl * sh.segs] = s1, unit_sums[2 * pl * sh.segs + 1] = s2;  // the plane's first unit now holds its total
+  }
+  __syncthreads();
+  if (!dx) return;
+  if (warp == 0) {
+    float a = 0.f, b = 0.f;
+    for (int pl = lane; pl < sh.cpg; pl += 32) {
+      const float w = gamma ? __ldg(gamma + group * sh.cpg + pl) : 1.f;
+      a = fmaf(w, unit_sums[2 * pl * sh.segs], a);
+      b = fmaf(w, unit_sums[2 * pl * sh.segs + 1], b);
+    }
+    a = warp_sum(a);
+    b = warp_sum(b);
+    if (lane == 0) totals[0] = a / sh.count, totals[1] = b / sh.count;
+  }
+  __syncthreads();
+  const float avg = totals[0], avg_z = totals[1];
+  for (int u = warp; u < sh.units; u += kWarps) {
+    const Unit un = unit_of(sh, u);
+    const float w = gamma ? __ldg(gamma + group * sh.cpg + un.plane) : 1.f;
+    const size_t at = base + (size_t)un.plane * sh.hw + un.off;
+    warp_map<true>(x + at, dy + at, dx + at, un.len, lane, [&](float xv, float gv) {
+      const float z = (xv - mean) * rstd;
+      return rstd * (gv * w - avg - z * avg_z);
+    });
+  }
+}
+
+// dgamma[ch] = sum over samples of s2, dbeta[ch] = sum of s1, in sample order
+// (the result of group_norm_backward_affine.comp:16-31).
+__global__ void gn_affine_kernel(const float* __restrict__ plane_sums, int n, int c, float* __restrict__ dgamma,
+                                 float* __restrict__ dbeta) {
+  const int ch = blockIdx.x * blockDim.x + threadIdx.x;
+  if (ch >= c) return;
+  float s1 = 0.f, s2 = 0.f;
+  for (int b = 0; b < n; ++b) {
+    const float2 v = __ldg(reinterpret_cast<const float2*>(plane_sums) + (size_t)b * c + ch);
+    s1 += v.x, s2 += v.y;
+  }
+  if (dgamma) dgamma[ch] = s2;
+  if (dbeta) dbeta[ch] = s1;
+}
+
+int make_shape(int64_t n, int64_t c, int64_t hw, int64_t groups, GnShape* out) {
+  if (!(groups > 0 && n > 0 && c > 0 && hw > 0 && c % groups == 0))
+    return fail(B200_EINVAL, "native_group_norm: invalid batch, channel, group or spatial dimensions");
+  if (n * groups > INT32_MAX || c > INT32_MAX || hw > INT32_MAX || (c / groups) * hw > INT32_MAX)
+    return fail(B200_ERANGE, "native_group_norm: a (sample, group) block exceeds int32 indexing");
+  GnShape sh{};
+  sh.n = (int)n, sh.c = (int)c, sh.hw = (int)hw, sh.groups = (int)groups, sh.cpg = (int)(c / groups);
+  if (sh.cpg > kMaxUnits) return fail(B200_EUNSUPPORTED, "native_group_norm: more than %d channels per group", kMaxUnits);
+  int segs = (sh.hw + kSegment - 1) / kSegment;
+  const int most = kMaxUnits / sh.cpg;  // keep cpg * segs within the shared-memory table
+  if (segs > most) segs = most;
+  sh.segs = segs;
+  sh.seg_len = ((sh.hw + segs - 1) / segs + 3) & ~3;
+  sh.segs = (sh.hw + sh.seg_len - 1) / sh.seg_len;  // rounding the length up can save a segment
+  sh.units = sh.cpg * sh.segs;
+  sh.count = (float)((double)sh.cpg * (double)sh.hw);
+  *out = sh;
+  return B200_OK;
+}
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+size_t b200_group_norm_workspace(int64_t n, int64_t c, int64_t hw, int64_t groups) {
+  GnShape sh;
+  if (make_shape(n, c, hw, groups, &sh)) return 0;
+  return (size_t)n * (size_t)c * 2 * sizeof(float);
+}
+
+int b200_group_norm_forward(int64_t n, int64_t c, int64_t hw, int64_t groups, const float* x, const float* weight,
+                            const float* bias, float eps, float* y, float* mean, float* rstd, void* stream) {
+  if (int rc = ensure_init()) return rc;
+  GnShape sh;
+  if (int rc = make_shape(n, c, hw, groups, &sh)) return rc;
+  if (!x || !y || !mean || !rstd) return fail(B200_EINVAL, "native_group_norm: null tensor");
+  note_kernel("gn_forward");
+  gn_forward_kernel<<<(unsigned)(n * groups), kThreads, 0, (cudaStream_t)stream>>>(x, weight, bias, sh, eps, y, mean, rstd);
+  count_launch();
+  return launch_check("gn_forward_kernel");
+}
+
+int b200_group_norm_backward(int64_t n, int64_t c, int64_t hw, int64_t groups, const float* grad, const float* x,
+                             const float* mean, const float* rstd, const float* weight, float* dx, float* dw, float* db,
+                             void* workspace, size_t workspace_bytes, void* stream) {
+  if (int rc = ensure_init()) return rc;
+  GnShape sh;
+  if (int rc = make_shape(n, c, hw, groups, &sh)) return rc;
+  if (!grad || !x || !mean || !rstd) return fail(B200_EINVAL, "native_group_norm_backward: null tensor");
+  if (!dx && !dw && !db) return B200_OK;
+  const bool affine = dw || db;
+  if (affine && (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 7) || workspace_bytes < (size_t)n * c * 2 * sizeof(float)))
+    return fail(B200_EWORKSPACE, "native_group_norm_backward: workspace missing, unaligned or smaller than b200_group_norm_workspace()");
+  cudaStream_t st = (cudaStream_t)stream;
+  float* plane_sums = affine ? (float*)workspace : nullptr;
+  note_kernel(affine ? "gn_backward+affine" : "gn_backward");
+  gn_backward_kernel<<<(unsigned)(n * groups), kThreads, (size_t)sh.units * 2 * sizeof(float), st>>>(grad, x, mean, rstd, weight, sh,
+                                                                                                      dx, plane_sums);
+  count_launch();
+  if (int rc = launch_check("gn_backward_kernel")) return rc;
+  if (affine) {
+    gn_affine_kernel<<<(unsigned)((c + 127) / 128), 128, 0, st>>>(plane_sums, (int)n, (int)c, dw, db);
+    count_launch();
+    if (int rc = launch_check("gn_affine_kernel")) return rc;
+  }
+  return B200_OK;
+}
+
+}  // extern "C"

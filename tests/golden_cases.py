@@ -65,3 +65,27 @@ def batch_norm_cases():
 
 def bn_case_id(case):
     return f"{case['tag']}{case['index']}-" + "x".join(map(str, case["x"].shape)) + ("-train" if case["training"] else "-eval")
+
+
+_GN = None
+
+
+def group_norm_cases():
+    """List of dicts: tag, groups, inputs x, g, w, b (None where absent) and the PyTorch-CPU FP64
+    results y, mean, rstd, dx, dw, db."""
+    global _GN
+    if _GN is None:
+        z = np.load(os.path.join(HERE, "golden", "group_norm_cases.npz"))
+        cases = []
+        for i, tag in enumerate(z["tags"]):
+            case = dict(tag=str(tag), index=i, groups=int(z[f"c{i}_groups"]))
+            for k in ("x", "g", "w", "b", "y", "mean", "rstd", "dx", "dw", "db"):
+                key = f"c{i}_{k}"
+                case[k] = z[key] if key in z.files else None
+            cases.append(case)
+        _GN = cases
+    return _GN
+
+
+def gn_case_id(case):
+    return f"{case['tag']}{case['index']}-" + "x".join(map(str, case["x"].shape)) + f"-g{case['groups']}"

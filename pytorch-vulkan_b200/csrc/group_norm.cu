@@ -13,7 +13,11 @@
 //             per-sample sums over the batch                                     12 B / element
 // The reference reads x and dy a third time for the affine gradients (one thread per channel
 // walking the whole batch, group_norm_backward_affine.comp:16-29); here they fall out of pass 1.
+#include <algorithm>
+#include <mutex>
+
 #include "common.cuh"
+#include "tc_common.cuh"
 
 namespace b200 {
 namespace {
@@ -22,6 +26,9 @@ constexpr int kThreads = 512;
 constexpr int kWarps = kThreads / 32;
 constexpr int kSegment = 2048;   // most floats of a plane one warp streams per unit
 constexpr int kMaxUnits = 4096;  // per-unit partial sums of a block live in shared memory
+constexpr size_t kBulkSmemBytes = 200 * 1024;  // two resident blocks of the bulk-copy forward kernel
+constexpr int kBulkThreads = 1024;             // its CTA: the only one on its SM, so all the warps the SM holds
+constexpr int kBulkChannels = 256;             // most channels per group it takes
 
 struct GnShape {
   int n, c, hw, groups, cpg;  // cpg = channels per group
@@ -93,7 +100,9 @@ __device__ __forceinline__ void warp_stream(const float* __restrict__ p, const f
   for (int e = done + lane; e < len; e += 32) f(__ldg(p + e), TWO ? __ldg(q + e) : 0.f);
 }
 
-// The same walk producing one output value per element: out[e] = f(a, b).
+// The same walk producing one output value per element: out[e] = f(a, b).  This is the last use of
+// the inputs and the result is not read again here: streaming loads and stores (evict-first), so
+// that the lines other CTAs still wait to re-read stay in L2.
 template <bool TWO, class F>
 __device__ __forceinline__ void warp_map(const float* __restrict__ p, const float* __restrict__ q, float* __restrict__ out, int len,
                                          int lane, F&& f) {
@@ -107,18 +116,18 @@ __device__ __forceinline__ void warp_map(const float* __restrict__ p, const floa
     const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
     int i = lane;
     for (; i + 32 < quads; i += 64) {
-      const float4 a0 = __ldg(p4 + i), a1 = __ldg(p4 + i + 32);
-      const float4 b0 = TWO ? __ldg(q4 + i) : zero, b1 = TWO ? __ldg(q4 + i + 32) : zero;
-      o4[i] = make_float4(f(a0.x, b0.x), f(a0.y, b0.y), f(a0.z, b0.z), f(a0.w, b0.w));
-      o4[i + 32] = make_float4(f(a1.x, b1.x), f(a1.y, b1.y), f(a1.z, b1.z), f(a1.w, b1.w));
+      const float4 a0 = __ldcs(p4 + i), a1 = __ldcs(p4 + i + 32);
+      const float4 b0 = TWO ? __ldcs(q4 + i) : zero, b1 = TWO ? __ldcs(q4 + i + 32) : zero;
+      __stcs(o4 + i, make_float4(f(a0.x, b0.x), f(a0.y, b0.y), f(a0.z, b0.z), f(a0.w, b0.w)));
+      __stcs(o4 + i + 32, make_float4(f(a1.x, b1.x), f(a1.y, b1.y), f(a1.z, b1.z), f(a1.w, b1.w)));
     }
     for (; i < quads; i += 32) {
-      const float4 a = __ldg(p4 + i), b = TWO ? __ldg(q4 + i) : zero;
-      o4[i] = make_float4(f(a.x, b.x), f(a.y, b.y), f(a.z, b.z), f(a.w, b.w));
+      const float4 a = __ldcs(p4 + i), b = TWO ? __ldcs(q4 + i) : zero;
+      __stcs(o4 + i, make_float4(f(a.x, b.x), f(a.y, b.y), f(a.z, b.z), f(a.w, b.w)));
     }
     done = quads * 4;
   }
-  for (int e = done + lane; e < len; e += 32) out[e] = f(__ldg(p + e), TWO ? __ldg(q + e) : 0.f);
+  for (int e = done + lane; e < len; e += 32) __stcs(out + e, f(__ldcs(p + e), TWO ? __ldcs(q + e) : 0.f));
 }
 
 // Unit u of a block: plane (channel within the group) and the segment's offset and length in it.
@@ -160,23 +169,20 @@ __global__ void __launch_bounds__(kThreads, 3) gn_forward_kernel(const float* __
       acc = merge(acc, Moments{cnt, (k - origin) + mean_d, fmaxf(q - s * mean_d, 0.f)});
     }
   }
-  __shared__ Moments warp_part[kWarps];
-  __shared__ float stat[2];
+  __shared__ Moments warp_part[32];
   acc = warp_merge(acc);
+  if (threadIdx.x < 32) warp_part[threadIdx.x] = Moments{0.f, 0.f, 0.f};
+  __syncthreads();
   if (lane == 0) warp_part[warp] = acc;
   __syncthreads();
+  // every warp folds the partial results itself; the mean stays relative to the origin so that its
+  // low part survives in the subtraction below
+  const Moments total = warp_merge(warp_part[lane]);
+  const float mean_rel = total.mean, rstd = 1.f / sqrtf(total.m2 / sh.count + eps);
   if (threadIdx.x == 0) {
-    Moments m = warp_part[0];
-#pragma unroll
-    for (int w = 1; w < kWarps; ++w) m = merge(m, warp_part[w]);
-    const float mean = origin + m.mean, rstd = 1.f / sqrtf(m.m2 / sh.count + eps);
-    means[row] = mean;
+    means[row] = origin + mean_rel;
     rstds[row] = rstd;
-    stat[0] = m.mean;  // relative to the origin: the low part of the mean stays in the subtraction below
-    stat[1] = rstd;
   }
-  __syncthreads();
-  const float mean_rel = stat[0], rstd = stat[1];
   for (int u = warp; u < sh.units; u += kWarps) {
     const Unit un = unit_of(sh, u);
     const int ch = group * sh.cpg + un.plane;
@@ -185,6 +191,100 @@ __global__ void __launch_bounds__(kThreads, 3) gn_forward_kernel(const float* __
     warp_map<false>(xb + at, nullptr, y + base + at, un.len, lane,
                     [&](float v, float) { return ((v - origin) - mean_rel) * scale + shift; });
   }
+}
+
+// The same computation with the block resident in shared memory: one thread brings the block in
+// with bulk asynchronous copies (completion counted in bytes on an mbarrier), everybody computes
+// the statistics and the result from shared memory, and while they do the copy of the CTA's next
+// block is already in flight into the other buffer.  The block is read from HBM once and the
+// bytes in flight do not depend on how many warps are waiting.  Used when two blocks fit
+// but not four (100 KB < 2 * count * 4 bytes <= 200 KB: one CTA of 1024 threads per SM), planes are
+// multiples of four floats, x is 16-byte aligned and every CTA gets four blocks or more.
+// Every wait is bounded: a wait that gives up sets the status word and the CTA leaves.
+__global__ void __launch_bounds__(kBulkThreads, 1) gn_forward_bulk_kernel(const float* __restrict__ x, const float* __restrict__ gamma,
+                                                                      const float* __restrict__ beta, GnShape sh, float eps,
+                                                                      float* __restrict__ y, float* __restrict__ means,
+                                                                      float* __restrict__ rstds, int blocks, FastDiv plane_quads,
+                                                                      int* status) {
+  extern __shared__ __align__(128) unsigned char gn_smem[];
+  __shared__ __align__(8) unsigned long long full[2];
+  __shared__ int abort_flag;
+  __shared__ Moments warp_part[kBulkThreads / 32];
+  __shared__ float2 affine[kBulkChannels];  // per channel of the group: rstd * gamma, beta
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t block_bytes = (uint32_t)(sh.cpg * sh.hw) * 4u;
+  const int quads = (sh.cpg * sh.hw) >> 2;
+  const uint32_t bar[2] = {tc::smem_u32(&full[0]), tc::smem_u32(&full[1])};
+  if (threadIdx.x == 0) {
+    tc::mbar_init(bar[0], 1);
+    tc::mbar_init(bar[1], 1);
+    abort_flag = 0;
+    tc::fence_barrier_init();
+  }
+  __syncthreads();
+  auto block_base = [&](int blk) { return ((size_t)(blk / sh.groups) * sh.c + (size_t)(blk % sh.groups) * sh.cpg) * sh.hw; };
+  auto issue = [&](int blk, int b) {  // one thread: the whole block in pieces of at most 32 KB
+    const char* src = reinterpret_cast<const char*>(x + block_base(blk));
+    const uint32_t dst = tc::smem_u32(gn_smem) + (uint32_t)b * block_bytes;
+    tc::mbar_expect_tx(bar[b], block_bytes);
+    for (uint32_t off = 0; off < block_bytes; off += 32768u)
+      tc::bulk_g2s(dst + off, src + off, min(32768u, block_bytes - off), bar[b]);
+  };
+  int it = 0, pending = -1;  // pending: buffer with a copy in flight that nobody has waited for yet
+  if (threadIdx.x == 0 && (int)blockIdx.x < blocks) issue(blockIdx.x, 0);
+  for (int blk = blockIdx.x; blk < blocks; blk += gridDim.x, ++it) {
+    const int b = it & 1, next = blk + gridDim.x;
+    pending = -1;
+    if (next < blocks) {
+      if (threadIdx.x == 0) issue(next, b ^ 1);  // that buffer's readers passed the barrier ending the previous round
+      pending = b ^ 1;
+    }
+    if (!tc::mbar_wait(bar[b], (uint32_t)(it >> 1) & 1u, &abort_flag, status, tc::STATUS_TIMEOUT_TMA)) break;
+    const float4* s4 = reinterpret_cast<const float4*>(gn_smem + (size_t)b * block_bytes);
+    const float origin = reinterpret_cast<const float*>(s4)[0];
+    // statistics: every thread sums around its own first value
+    Moments acc = {0.f, 0.f, 0.f};
+    if ((int)threadIdx.x < quads) {
+      const float k = s4[threadIdx.x].x;
+      float cnt = 0.f, s = 0.f, q = 0.f;
+      for (int i = threadIdx.x; i < quads; i += kBulkThreads) {
+        const float4 v = s4[i];
+        const float d0 = v.x - k, d1 = v.y - k, d2 = v.z - k, d3 = v.w - k;
+        s += (d0 + d1) + (d2 + d3);
+        q = fmaf(d0, d0, fmaf(d1, d1, fmaf(d2, d2, fmaf(d3, d3, q))));
+        cnt += 4.f;
+      }
+      const float mean_d = s / cnt;
+      acc = Moments{cnt, (k - origin) + mean_d, fmaxf(q - s * mean_d, 0.f)};
+    }
+    acc = warp_merge(acc);
+    if (lane == 0) warp_part[warp] = acc;
+    __syncthreads();
+    // every warp folds the 32 partial results itself: no second barrier, no serial chain
+    const Moments total = warp_merge(warp_part[lane]);
+    const float mean_rel = total.mean, rstd = 1.f / sqrtf(total.m2 / sh.count + eps);
+    if (threadIdx.x == 0) {
+      means[blk] = origin + mean_rel;
+      rstds[blk] = rstd;
+    }
+    const int ch0 = (blk % sh.groups) * sh.cpg;
+    if ((int)threadIdx.x < sh.cpg)
+      affine[threadIdx.x] = make_float2(rstd * (gamma ? __ldg(gamma + ch0 + threadIdx.x) : 1.f), beta ? __ldg(beta + ch0 + threadIdx.x) : 0.f);
+    __syncthreads();
+    float4* y4 = reinterpret_cast<float4*>(y + block_base(blk));
+#pragma unroll 4
+    for (int i = threadIdx.x; i < quads; i += kBulkThreads) {
+      const float2 ab = affine[plane_quads.div((uint32_t)i)];
+      const float scale = ab.x, shift = ab.y;
+      const float4 v = s4[i];
+      __stcs(y4 + i, make_float4(((v.x - origin) - mean_rel) * scale + shift, ((v.y - origin) - mean_rel) * scale + shift,
+                                 ((v.z - origin) - mean_rel) * scale + shift, ((v.w - origin) - mean_rel) * scale + shift));
+    }
+    __syncthreads();  // the buffer may be overwritten by the copy issued in the next round
+  }
+  // after a wait that gave up: do not leave while a copy into this CTA's shared memory may still land
+  if (abort_flag && threadIdx.x == 0 && pending >= 0)
+    tc::mbar_wait(bar[pending], (uint32_t)((it + 1) >> 1) & 1u, nullptr, status, tc::STATUS_TIMEOUT_TMA);
 }
 
 // ---- backward ------------------------------------------------------------------------------------
@@ -305,8 +405,28 @@ int b200_group_norm_forward(int64_t n, int64_t c, int64_t hw, int64_t groups, co
   GnShape sh;
   if (int rc = make_shape(n, c, hw, groups, &sh)) return rc;
   if (!x || !y || !mean || !rstd) return fail(B200_EINVAL, "native_group_norm: null tensor");
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t block_bytes = (size_t)sh.cpg * sh.hw * sizeof(float);
+  const bool aligned = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0;
+  const int blocks = (int)(n * groups);
+  const int bulk_grid = std::min(blocks, sm_count());
+  // the resident form pays once the copy pipeline has rounds to overlap: four blocks or more per CTA
+  if (aligned && sh.hw % 4 == 0 && sh.cpg <= kBulkChannels && 2 * block_bytes > kBulkSmemBytes / 2 && 2 * block_bytes <= kBulkSmemBytes &&
+      blocks >= 4 * bulk_grid) {
+    static std::once_flag once;
+    static cudaError_t opt_in = cudaSuccess;
+    std::call_once(once, [] {
+      opt_in = cudaFuncSetAttribute(gn_forward_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kBulkSmemBytes);
+    });
+    B200_CUDA(opt_in);
+    note_kernel("gn_forward_bulk");
+    gn_forward_bulk_kernel<<<bulk_grid, kBulkThreads, 2 * block_bytes, st>>>(x, weight, bias, sh, eps, y, mean, rstd, blocks,
+                                                                            FastDiv((uint32_t)(sh.hw / 4)), device_status_word());
+    count_launch();
+    return launch_check("gn_forward_bulk_kernel");
+  }
   note_kernel("gn_forward");
-  gn_forward_kernel<<<(unsigned)(n * groups), kThreads, 0, (cudaStream_t)stream>>>(x, weight, bias, sh, eps, y, mean, rstd);
+  gn_forward_kernel<<<(unsigned)(n * groups), kThreads, 0, st>>>(x, weight, bias, sh, eps, y, mean, rstd);
   count_launch();
   return launch_check("gn_forward_kernel");
 }

@@ -222,6 +222,12 @@ __global__ void __launch_bounds__(kThreads) bn_stats_finalize_kernel(const float
   if (ch >= sh.c) return;
   const int entries = sh.slabs * sh.part_inner;
   const int pcols = sh.c * sh.part_inner;
+  // the channel's scalars first: their latency hides behind the merge
+  const float origin = __ldg(x + (size_t)ch * sh.inner);
+  const float gamma = v.weight ? v.weight[ch * v.w_stride] : 1.f;
+  const float beta = v.bias ? v.bias[ch * v.b_stride] : 0.f;
+  const float old_mean = v.running_mean ? v.running_mean[ch * v.rm_stride] : 0.f;
+  const float old_var = v.running_var ? v.running_var[ch * v.rv_stride] : 0.f;
   Moments m = {0.f, 0.f, 0.f};
   for (int t = lane; t < entries; t += 32) {
     const int slab = t / sh.part_inner, j = t - slab * sh.part_inner;
@@ -229,22 +235,13 @@ __global__ void __launch_bounds__(kThreads) bn_stats_finalize_kernel(const float
   }
   m = warp_merge(m);
   if (lane != 0) return;
-  const float origin = __ldg(x + (size_t)ch * sh.inner);
   const float variance = m.m2 / sh.m;
   const float inv = (variance == 0.f && v.eps == 0.f) ? 0.f : 1.f / sqrtf(variance + v.eps);
   const float mean = origin + m.mean;
   v.save_mean[ch] = mean;
   v.save_inv[ch] = inv;
-  if (v.running_mean) {
-    float* p = v.running_mean + ch * v.rm_stride;
-    *p = (1.f - v.momentum) * *p + v.momentum * mean;
-  }
-  if (v.running_var) {
-    float* p = v.running_var + ch * v.rv_stride;
-    *p = (1.f - v.momentum) * *p + v.momentum * (m.m2 / (sh.m - 1.f));
-  }
-  const float gamma = v.weight ? v.weight[ch * v.w_stride] : 1.f;
-  const float beta = v.bias ? v.bias[ch * v.b_stride] : 0.f;
+  if (v.running_mean) v.running_mean[ch * v.rm_stride] = (1.f - v.momentum) * old_mean + v.momentum * mean;
+  if (v.running_var) v.running_var[ch * v.rv_stride] = (1.f - v.momentum) * old_var + v.momentum * (m.m2 / (sh.m - 1.f));
   coef[ch] = make_float4(origin, m.mean, inv * gamma, beta);
 }
 

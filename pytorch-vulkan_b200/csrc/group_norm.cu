@@ -351,19 +351,24 @@ __global__ void __launch_bounds__(kThreads, 3) gn_backward_kernel(const float* _
   }
 }
 
-// dgamma[ch] = sum over samples of s2, dbeta[ch] = sum of s1, in sample order
-// (the result of group_norm_backward_affine.comp:16-31).
-__global__ void gn_affine_kernel(const float* __restrict__ plane_sums, int n, int c, float* __restrict__ dgamma,
-                                 float* __restrict__ dbeta) {
-  const int ch = blockIdx.x * blockDim.x + threadIdx.x;
+// dgamma[ch] = sum over samples of s2, dbeta[ch] = sum of s1 (the result of
+// group_norm_backward_affine.comp:16-31).  One warp per channel: lane l adds samples l, l + 32, ...
+// in order and the lanes are folded by shuffles, so the result does not depend on the launch.
+__global__ void __launch_bounds__(256) gn_affine_kernel(const float* __restrict__ plane_sums, int n, int c, float* __restrict__ dgamma,
+                                                        float* __restrict__ dbeta) {
+  const int ch = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (ch >= c) return;
   float s1 = 0.f, s2 = 0.f;
-  for (int b = 0; b < n; ++b) {
+  for (int b = lane; b < n; b += 32) {
     const float2 v = __ldg(reinterpret_cast<const float2*>(plane_sums) + (size_t)b * c + ch);
     s1 += v.x, s2 += v.y;
   }
-  if (dgamma) dgamma[ch] = s2;
-  if (dbeta) dbeta[ch] = s1;
+  s1 = warp_sum(s1);
+  s2 = warp_sum(s2);
+  if (lane == 0) {
+    if (dgamma) dgamma[ch] = s2;
+    if (dbeta) dbeta[ch] = s1;
+  }
 }
 
 int make_shape(int64_t n, int64_t c, int64_t hw, int64_t groups, GnShape* out) {
@@ -450,7 +455,7 @@ int b200_group_norm_backward(int64_t n, int64_t c, int64_t hw, int64_t groups, c
   count_launch();
   if (int rc = launch_check("gn_backward_kernel")) return rc;
   if (affine) {
-    gn_affine_kernel<<<(unsigned)((c + 127) / 128), 128, 0, st>>>(plane_sums, (int)n, (int)c, dw, db);
+    gn_affine_kernel<<<(unsigned)((c + 7) / 8), 256, 0, st>>>(plane_sums, (int)n, (int)c, dw, db);
     count_launch();
     if (int rc = launch_check("gn_affine_kernel")) return rc;
   }

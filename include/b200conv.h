@@ -154,6 +154,20 @@ int b200_conv2d_forward_fused(const b200_conv_params* p, b200_view4 x, b200_view
  * the conv2d_backward_input shaders.  dx: contiguous [n,cin,h,w]. */
 int b200_conv2d_dinput(const b200_conv_params* p, b200_view4 dy, b200_view4 w, float* dx,
                        void* workspace, size_t workspace_bytes, int algo, void* stream);
+/* y = conv_transpose2d(x, w) + bias: the transposed ("fractionally strided") convolution, which is
+ * the input gradient of an ordinary convolution.  `p` describes THAT convolution: p->n samples,
+ * (p->cin, p->h, p->w) are the channels and extent of the RESULT y, (p->cout, p->oh, p->ow) those of
+ * x, and w is [p->cout, p->cin / groups, kh, kw], the layout PyTorch gives a transposed convolution's
+ * weight.  An output_padding is expressed through p->h / p->w (b200_conv2d_geometry must map them
+ * back to x's extent).  bias: p->cin values or NULL.  y: contiguous [n, cin, h, w].
+ * Replaces the transposed branch of convolution_nd (csrc/ops/convolution_nd.cpp:46-56, shader
+ * convolution_nd.comp), to which the reference's convolution entry point delegates
+ * (csrc/ops/convolution.cpp:647).  Its gradients need no entry points of their own: with g the
+ * gradient of y, dx = b200_conv2d_forward(p, g, w), dw = b200_conv2d_dweight(p, g as x, x as dy),
+ * and db = b200_conv2d_dbias over g. */
+int b200_conv_transpose2d_forward(const b200_conv_params* p, b200_view4 x, b200_view4 w, const float* bias,
+                                  int64_t bias_stride, float* y, void* workspace, size_t workspace_bytes, int algo,
+                                  void* stream);
 /* dw = dy (*) x summed over batch and positions.  Replaces dispatch(Weight), :688-691,
  * the conv2d_backward_weight shaders (direct, reduce, tiled, finalize).  The split-K partials are summed in
  * ascending split order (no float atomics), so results are run-to-run identical.

@@ -82,6 +82,8 @@ SIGNATURES = {
     "b200_conv2d_forward_fused": (c_int, [POINTER(ConvParams), View4, View4, c_void_p, c_int64, View4, c_int, c_void_p,
                                           c_int, c_void_p, c_size_t, c_int, c_void_p]),
     "b200_conv2d_dinput": (c_int, [POINTER(ConvParams), View4, View4, c_void_p, c_void_p, c_size_t, c_int, c_void_p]),
+    "b200_conv_transpose2d_forward": (c_int, [POINTER(ConvParams), View4, View4, c_void_p, c_int64, c_void_p, c_void_p, c_size_t,
+                                              c_int, c_void_p]),
     "b200_conv2d_dweight": (c_int, [POINTER(ConvParams), View4, View4, c_void_p, c_void_p, c_size_t, c_int, c_void_p]),
     "b200_conv2d_dweight_static": (c_int, [POINTER(ConvParams), View4, View4, c_void_p, c_void_p]),
     "b200_conv2d_dbias": (c_int, [POINTER(ConvParams), View4, c_void_p, c_void_p, c_size_t, c_void_p]),
@@ -450,3 +452,27 @@ def group_norm_backward(grad, x, mean, rstd, groups, weight=None, mask=(True, Tr
                                          dx.ptr if dx else None, dw.ptr if dw else None, db.ptr if db else None,
                                          ws.ptr, ws_n, None))
     return (dx.to_numpy(x.shape) if dx else None, dw.to_numpy((c,)) if dw else None, db.to_numpy((c,)) if db else None)
+
+
+def conv_transpose2d_forward(x, w, b=None, stride=(1, 1), padding=(0, 0), output_padding=(0, 0), dilation=(1, 1), groups=1,
+                             algo="auto", budget=DEFAULT_WORKSPACE):
+    """y = conv_transpose2d(x, w) + b on the device; w is [cin, cout / groups, kh, kw] as in PyTorch."""
+    algo = _algo(algo)
+    pair = lambda v: (v, v) if isinstance(v, int) else tuple(v)
+    (sh, sw), (ph, pw), (oph, opw), (dh, dw) = pair(stride), pair(padding), pair(output_padding), pair(dilation)
+    n, cin, h, wd = x.shape
+    kh, kw = w.shape[2:]
+    oh = (h - 1) * sh - 2 * ph + dh * (kh - 1) + oph + 1
+    ow = (wd - 1) * sw - 2 * pw + dw * (kw - 1) + opw + 1
+    # the convolution whose input gradient this is: input [n, cout, oh, ow], output [n, cin, h, wd]
+    p = geometry((n, w.shape[1] * groups, oh, ow), cin, (kh, kw), (sh, sw), (ph, pw), (dh, dw), groups, wcin=w.shape[1])
+    if (p.oh, p.ow) != (h, wd) or w.shape[0] != cin:
+        raise ValueError("transposed convolution: output padding or weight shape does not match the input")
+    xv, wv = DeviceView(x), DeviceView(w)
+    bv = DeviceView(b) if b is not None else None
+    y = DeviceBuffer(4 * p.n * p.cin * p.h * p.w)
+    ws_n = workspace_bytes(p, PHASE_DINPUT, algo, budget)
+    ws = DeviceBuffer(ws_n) if ws_n else None
+    check(lib().b200_conv_transpose2d_forward(ctypes.byref(p), xv.view4(), wv.view4(), bv.ptr if bv else None,
+                                              bv.strides[0] if bv else 0, y.ptr, ws.ptr if ws else None, ws_n, algo, None))
+    return y.to_numpy((p.n, p.cin, p.h, p.w))

@@ -249,6 +249,19 @@ int b200_conv2d_dinput(const b200_conv_params* p, b200_view4 dy, b200_view4 w, f
   }
 }
 
+int b200_conv_transpose2d_forward(const b200_conv_params* p, b200_view4 x, b200_view4 w, const float* bias,
+                                  int64_t bias_stride, float* y, void* workspace, size_t workspace_bytes, int algo,
+                                  void* stream) {
+  // the transposed convolution of x is the input gradient of the convolution p describes
+  if (int rc = b200_conv2d_dinput(p, x, w, y, workspace, workspace_bytes, algo, stream)) return rc;
+  if (!bias) return B200_OK;
+  ConvGeom result = to_geom(*p);  // the result has p's input extent: address it as an "output" of that shape
+  result.cout = result.cin, result.oh = result.h, result.ow = result.w;
+  StripPostOps post{};
+  post.residual = View4{bias, 0, (long long)bias_stride, 0, 0};  // bias[c] broadcast over samples and pixels
+  return post_ops_nchw(y, result, post, (cudaStream_t)stream);
+}
+
 int b200_conv2d_dweight(const b200_conv_params* p, b200_view4 x, b200_view4 dy, float* dw, void* workspace,
                         size_t workspace_bytes, int algo, void* stream) {
   if (int rc = check_params(p)) return rc;

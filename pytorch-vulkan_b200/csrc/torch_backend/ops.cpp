@@ -385,49 +385,93 @@ static void plan_and_run(const b200_conv_params& p, int phase, const at::TensorO
 static b200_view4 view_of(const at::Tensor& t) {
   b200_view4 v{t.const_data_ptr<float>(), {0, 0, 0, 0}};
   for (int64_t d = 0; d < t.dim(); ++d) v.stride[d] = t.stride(d);
+  if (t.dim() == 3) v.stride[3] = t.stride(2), v.stride[2] = 0;  // [N, C, L] read as [N, C, 1, L]
   return v;
 }
 static void require_fp32_device(const at::Tensor& t) {
   TORCH_CHECK(on_device(t) && t.scalar_type() == at::kFloat, "Vulkan convolution requires FP32 Vulkan tensors");
 }
 
-static b200_conv_params conv_params(const at::Tensor& input, const at::Tensor& weight, c10::SymIntArrayRef stride,
-                                    c10::SymIntArrayRef padding, c10::SymIntArrayRef dilation, bool transposed,
-                                    c10::SymIntArrayRef output_padding, const c10::SymInt& groups) {
-  TORCH_CHECK(!transposed, "Vulkan ConvTranspose is not implemented yet");
-  TORCH_CHECK(input.dim() == 4 && weight.dim() == 4, "Vulkan convolution supports NCHW tensors only");
-  TORCH_CHECK(stride.size() == 2 && padding.size() == 2 && dilation.size() == 2 && output_padding.size() == 2,
-              "Vulkan convolution requires two spatial dimensions");
-  TORCH_CHECK(output_padding[0].expect_int() == 0 && output_padding[1].expect_int() == 0,
-              "Vulkan convolution: output_padding requires transposed convolution");
+// One convolution call resolved to the 2-D geometry the library computes with.  A 1-D convolution
+// is the 2-D one with a single row.  For a transposed convolution `p` describes the ordinary
+// convolution whose input gradient it is (its "input" is this call's result), as
+// b200_conv_transpose2d_forward expects; the reference routes both through convolution_nd
+// (csrc/ops/convolution.cpp:647,674; csrc/ops/convolution_nd.cpp:11-37).
+struct ConvCall {
+  b200_conv_params p;
+  bool transposed;
+  std::vector<int64_t> result_shape;  // of the forward result
+};
+
+static ConvCall conv_call(const at::Tensor& input, const at::Tensor& weight, c10::SymIntArrayRef stride,
+                          c10::SymIntArrayRef padding, c10::SymIntArrayRef dilation, bool transposed,
+                          c10::SymIntArrayRef output_padding, const c10::SymInt& groups_sym) {
+  TORCH_CHECK(input.dim() != 5 && input.scalar_type() != at::kLong,
+              "Vulkan convolution: only FP32 convolutions over one or two spatial dimensions are implemented by this backend build");
+  const int64_t rank = input.dim() - 2;
+  TORCH_CHECK((rank == 1 || rank == 2) && weight.dim() == input.dim(), "convolution: expected matching rank 3 or 4 tensors");
+  TORCH_CHECK((int64_t)stride.size() == rank && (int64_t)padding.size() == rank && (int64_t)dilation.size() == rank &&
+                  (int64_t)output_padding.size() == rank,
+              "convolution: spatial parameter rank mismatch");
   require_fp32_device(input);
   require_fp32_device(weight);
-  b200_conv_params p;
-  const int rc = b200_conv2d_geometry(&p, input.size(0), input.size(1), weight.size(0), input.size(2), input.size(3),
-                                      weight.size(1), weight.size(2), weight.size(3), stride[0].expect_int(),
-                                      stride[1].expect_int(), padding[0].expect_int(), padding[1].expect_int(),
-                                      dilation[0].expect_int(), dilation[1].expect_int(), groups.expect_int());
-  TORCH_CHECK(rc == 0, "Vulkan ", b200_last_error());
-  return p;
+  // spatial parameters as (row, column) pairs; the missing row of a 1-D call is the identity
+  auto pair = [&](c10::SymIntArrayRef v, int64_t fill) {
+    return rank == 2 ? std::array<int64_t, 2>{v[0].expect_int(), v[1].expect_int()} : std::array<int64_t, 2>{fill, v[0].expect_int()};
+  };
+  const auto s = pair(stride, 1), pad = pair(padding, 0), d = pair(dilation, 1), op = pair(output_padding, 0);
+  const int64_t groups = groups_sym.expect_int();
+  const int64_t h = rank == 2 ? input.size(2) : 1, w = input.size(rank + 1);
+  const int64_t kh = rank == 2 ? weight.size(2) : 1, kw = weight.size(rank + 1);
+  ConvCall call{};
+  call.transposed = transposed;
+  int rc;
+  if (!transposed) {
+    TORCH_CHECK(op[0] == 0 && op[1] == 0, "convolution: invalid output padding");
+    rc = b200_conv2d_geometry(&call.p, input.size(0), input.size(1), weight.size(0), h, w, weight.size(1), kh, kw, s[0], s[1],
+                              pad[0], pad[1], d[0], d[1], groups);
+    TORCH_CHECK(rc == 0, "Vulkan ", b200_last_error());
+    call.result_shape = {call.p.n, call.p.cout, call.p.oh, call.p.ow};
+  } else {
+    TORCH_CHECK(groups > 0 && weight.size(0) == input.size(1), "convolution: weight/channel/group mismatch");
+    for (int i = 0; i < 2; ++i)
+      TORCH_CHECK(op[i] >= 0 && (op[i] < s[i] || op[i] < d[i]), "convolution: invalid output padding");
+    const int64_t oh = (h - 1) * s[0] - 2 * pad[0] + d[0] * (kh - 1) + op[0] + 1;
+    const int64_t ow = (w - 1) * s[1] - 2 * pad[1] + d[1] * (kw - 1) + op[1] + 1;
+    TORCH_CHECK(oh > 0 && ow > 0, "convolution: invalid or oversized output shape");
+    rc = b200_conv2d_geometry(&call.p, input.size(0), weight.size(1) * groups, weight.size(0), oh, ow, weight.size(1), kh, kw,
+                              s[0], s[1], pad[0], pad[1], d[0], d[1], groups);
+    TORCH_CHECK(rc == 0, "Vulkan ", b200_last_error());
+    TORCH_CHECK(call.p.oh == h && call.p.ow == w, "convolution: invalid or oversized output shape");
+    call.result_shape = {call.p.n, call.p.cin, call.p.h, call.p.w};
+  }
+  if (rank == 1) call.result_shape.erase(call.result_shape.begin() + 2);
+  return call;
 }
 
 static at::Tensor convolution_overrideable(const at::Tensor& input, const at::Tensor& weight,
                                            const std::optional<at::Tensor>& bias, c10::SymIntArrayRef stride,
                                            c10::SymIntArrayRef padding, c10::SymIntArrayRef dilation, bool transposed,
                                            c10::SymIntArrayRef output_padding, c10::SymInt groups) {
-  TORCH_CHECK(input.dim() != 5 && input.scalar_type() != at::kLong,
-              "Vulkan convolution: only FP32 Conv2D is implemented by this backend build");
-  const auto p = conv_params(input, weight, stride, padding, dilation, transposed, output_padding, groups);
+  const ConvCall call = conv_call(input, weight, stride, padding, dilation, transposed, output_padding, groups);
+  const b200_conv_params& p = call.p;
   const float* bias_ptr = nullptr;
   int64_t bias_stride = 0;
   if (bias && bias->defined()) {
-    TORCH_CHECK(bias->numel() == p.cout && bias->scalar_type() == at::kFloat && on_device(*bias),
+    TORCH_CHECK(bias->numel() == call.result_shape[1] && bias->scalar_type() == at::kFloat && on_device(*bias),
                 "Vulkan convolution: bias shape/dtype mismatch");
     bias_ptr = bias->const_data_ptr<float>();
     bias_stride = bias->dim() ? bias->stride(bias->dim() - 1) : 0;
   }
-  auto result = at::empty({p.n, p.cout, p.oh, p.ow}, input.options());  // always contiguous NCHW
+  auto result = at::empty(call.result_shape, input.options());  // always contiguous, as in the reference
   const std::string layouts = std::to_string(layout_class(input)) + std::to_string(layout_class(weight));
+  if (call.transposed) {
+    plan_and_run(p, B200_PHASE_DINPUT, input.options(), layouts + "t", [&](int algo, void* ws, size_t ws_bytes) {
+      return b200_conv_transpose2d_forward(&p, view_of(input), view_of(weight), bias_ptr, bias_stride, result.data_ptr<float>(),
+                                           ws, ws_bytes, algo, backend_stream());
+    });
+    return result;
+  }
   plan_and_run(p, B200_PHASE_FORWARD, input.options(), layouts, [&](int algo, void* ws, size_t ws_bytes) {
     return b200_conv2d_forward(&p, view_of(input), view_of(weight), bias_ptr, bias_stride, result.data_ptr<float>(), ws,
                                ws_bytes, algo, backend_stream());
@@ -439,33 +483,49 @@ static std::tuple<at::Tensor, at::Tensor, at::Tensor> convolution_backward_overr
     const at::Tensor& grad_output, const at::Tensor& input, const at::Tensor& weight, c10::SymIntArrayRef stride,
     c10::SymIntArrayRef padding, c10::SymIntArrayRef dilation, bool transposed, c10::SymIntArrayRef output_padding,
     c10::SymInt groups, std::array<bool, 3> output_mask) {
-  TORCH_CHECK(input.dim() != 5, "Vulkan convolution: only FP32 Conv2D is implemented by this backend build");
-  const auto p = conv_params(input, weight, stride, padding, dilation, transposed, output_padding, groups);
-  TORCH_CHECK(grad_output.dim() == 4 && grad_output.size(0) == p.n && grad_output.size(1) == p.cout &&
-                  grad_output.size(2) == p.oh && grad_output.size(3) == p.ow,
-              "Vulkan convolution backward: output gradient shape mismatch");
+  const ConvCall call = conv_call(input, weight, stride, padding, dilation, transposed, output_padding, groups);
+  const b200_conv_params& p = call.p;
+  TORCH_CHECK(grad_output.sizes() == at::IntArrayRef(call.result_shape), "Vulkan convolution backward: output gradient shape mismatch");
   require_fp32_device(grad_output);
   const std::string layouts = std::to_string(layout_class(input)) + std::to_string(layout_class(weight)) +
-                              std::to_string(layout_class(grad_output));
+                              std::to_string(layout_class(grad_output)) + (call.transposed ? "t" : "");
+  // Ordinary convolution: dx = dInput(dy, w), dw = dWeight(x, dy).  Transposed: the roles swap,
+  // dx = forward(dy, w) and dw = dWeight(dy as the input, x as the output gradient).
+  const at::Tensor& conv_in = call.transposed ? grad_output : input;    // the tensor with p's input extent
+  const at::Tensor& conv_out = call.transposed ? input : grad_output;  // the tensor with p's output extent
   at::Tensor dx, dw, db;
   if (output_mask[0]) {
     dx = at::empty(input.sizes(), input.options().memory_format(at::MemoryFormat::Contiguous));
-    plan_and_run(p, B200_PHASE_DINPUT, input.options(), layouts, [&](int algo, void* ws, size_t ws_bytes) {
-      return b200_conv2d_dinput(&p, view_of(grad_output), view_of(weight), dx.data_ptr<float>(), ws, ws_bytes, algo,
-                                backend_stream());
-    });
+    if (call.transposed) {
+      plan_and_run(p, B200_PHASE_FORWARD, input.options(), layouts, [&](int algo, void* ws, size_t ws_bytes) {
+        return b200_conv2d_forward(&p, view_of(grad_output), view_of(weight), nullptr, 0, dx.data_ptr<float>(), ws, ws_bytes,
+                                   algo, backend_stream());
+      });
+    } else {
+      plan_and_run(p, B200_PHASE_DINPUT, input.options(), layouts, [&](int algo, void* ws, size_t ws_bytes) {
+        return b200_conv2d_dinput(&p, view_of(grad_output), view_of(weight), dx.data_ptr<float>(), ws, ws_bytes, algo,
+                                  backend_stream());
+      });
+    }
   }
   if (output_mask[1]) {
     dw = at::empty(weight.sizes(), weight.options().memory_format(at::MemoryFormat::Contiguous));
     plan_and_run(p, B200_PHASE_DWEIGHT, input.options(), layouts, [&](int algo, void* ws, size_t ws_bytes) {
-      return b200_conv2d_dweight(&p, view_of(input), view_of(grad_output), dw.data_ptr<float>(), ws, ws_bytes, algo,
+      return b200_conv2d_dweight(&p, view_of(conv_in), view_of(conv_out), dw.data_ptr<float>(), ws, ws_bytes, algo,
                                  backend_stream());
     });
   }
   if (output_mask[2]) {
-    db = at::empty({p.cout}, weight.options());
-    plan_and_run(p, B200_PHASE_DBIAS, input.options(), layouts, [&](int, void* ws, size_t ws_bytes) {
-      return b200_conv2d_dbias(&p, view_of(grad_output), db.data_ptr<float>(), ws, ws_bytes, backend_stream());
+    // the bias gradient sums grad_output over samples and positions; for a transposed call that
+    // tensor has p's input extent, described here as the output of a 1x1 convolution
+    b200_conv_params pb = p;
+    if (call.transposed) {
+      const int rc = b200_conv2d_geometry(&pb, p.n, p.cin, p.cin, p.h, p.w, p.cin, 1, 1, 1, 1, 0, 0, 1, 1, 1);
+      TORCH_CHECK(rc == 0, "Vulkan ", b200_last_error());
+    }
+    db = at::empty({pb.cout}, weight.options());
+    plan_and_run(pb, B200_PHASE_DBIAS, input.options(), layouts, [&](int, void* ws, size_t ws_bytes) {
+      return b200_conv2d_dbias(&pb, view_of(grad_output), db.data_ptr<float>(), ws, ws_bytes, backend_stream());
     });
   }
   return {dx, dw, db};

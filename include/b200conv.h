@@ -267,6 +267,13 @@ int b200_group_norm_backward(int64_t n, int64_t c, int64_t hw, int64_t groups, c
                              const float* mean, const float* rstd, const float* weight, float* dx, float* dw, float* db,
                              void* workspace, size_t workspace_bytes, void* stream);
 
+/* C[b] (contiguous [batch, M, N]) = A[b] * B[b]; A and B arbitrary 3-D element strides (a zero batch
+ * stride broadcasts one matrix).  Replaces bmm_impl (csrc/ops/bmm.cpp:16-68, shader bmm_strided.comp).
+ * K == 0 gives zeros, as there (:50-54).  One b200_gemm per batch, or a single product when the
+ * right-hand matrix is shared and the left-hand rows lie at one stride; there is no batched kernel. */
+int b200_bmm(int64_t batch, int64_t M, int64_t N, int64_t K, const float* A, int64_t sa_b, int64_t sa0, int64_t sa1,
+             const float* B, int64_t sb_b, int64_t sb0, int64_t sb1, float* C, int algo, void* stream);
+
 /* Device-side health word.  The tcgen05 kernels bound every wait on an mbarrier; a wait that
  * gives up records (code << 24 | CTA index) here, frees its tensor memory and returns, so the
  * context stays usable.  *status = 0 means no wait ever gave up.  Synchronises the device.

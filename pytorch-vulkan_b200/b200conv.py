@@ -101,6 +101,8 @@ SIGNATURES = {
                                         c_void_p, c_void_p, c_void_p]),
     "b200_group_norm_backward": (c_int, [c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                          c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "b200_bmm": (c_int, [c_int64] * 4 + [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64, c_void_p,
+                         c_int, c_void_p]),
     "b200_device_status": (c_int, [POINTER(c_int), c_int]),
     "b200_launch_count": (c_uint64, []),
     "b200_last_kernel": (c_char_p, []),
@@ -476,3 +478,15 @@ def conv_transpose2d_forward(x, w, b=None, stride=(1, 1), padding=(0, 0), output
     check(lib().b200_conv_transpose2d_forward(ctypes.byref(p), xv.view4(), wv.view4(), bv.ptr if bv else None,
                                               bv.strides[0] if bv else 0, y.ptr, ws.ptr if ws else None, ws_n, algo, None))
     return y.to_numpy((p.n, p.cin, p.h, p.w))
+
+
+def bmm(a, b, algo="auto"):
+    """C[i] = a[i] @ b[i] on the device; a [batch, M, K] and b [batch, K, N] any float32 views."""
+    batch, M, K = a.shape
+    batch2, K2, N = b.shape
+    if batch != batch2 or K != K2:
+        raise ValueError("bmm: expected matching batch dimensions and contraction size")
+    av, bv = DeviceView(a), DeviceView(b)
+    out = DeviceBuffer(4 * batch * M * N)
+    check(lib().b200_bmm(batch, M, N, K, av.ptr, *av.strides, bv.ptr, *bv.strides, out.ptr, _algo(algo), None))
+    return out.to_numpy((batch, M, N))

@@ -326,4 +326,20 @@ int b200_gemm(int64_t M, int64_t N, int64_t K, const float* A, int64_t sa0, int6
   return simt_gemm(M, N, K, A, sa0, sa1, B, sb0, sb1, bias, alpha, beta, C, st);
 }
 
+int b200_bmm(int64_t batch, int64_t M, int64_t N, int64_t K, const float* A, int64_t sa_b, int64_t sa0, int64_t sa1,
+             const float* B, int64_t sb_b, int64_t sb0, int64_t sb1, float* C, int algo, void* stream) {
+  if (batch < 0) return fail(B200_EINVAL, "bmm: negative batch");
+  if (batch == 0 || M == 0 || N == 0) return B200_OK;
+  if (batch * M > UINT32_MAX / N) return fail(B200_ERANGE, "bmm: result too large");
+  // one right-hand matrix for every batch and left-hand rows at one constant stride: a single
+  // product with batch * M rows
+  if ((sb_b == 0 || batch == 1) && (batch == 1 || sa_b == M * sa0))
+    return b200_gemm(batch * M, N, K, A, sa0, sa1, B, sb0, sb1, nullptr, 1.f, 0.f, C, algo, stream);
+  for (int64_t b = 0; b < batch; ++b)
+    if (int rc = b200_gemm(M, N, K, A ? A + b * sa_b : nullptr, sa0, sa1, B ? B + b * sb_b : nullptr, sb0, sb1, nullptr, 1.f, 0.f,
+                           C + b * M * N, algo, stream))
+      return rc;
+  return B200_OK;
+}
+
 }  // extern "C"

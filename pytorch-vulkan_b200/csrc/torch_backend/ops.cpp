@@ -587,6 +587,35 @@ static at::Tensor addmm(const at::Tensor& self, const at::Tensor& mat1, const at
   return out;
 }
 
+// ---- bmm -------------------------------------------------------------------------------------------
+// bmm / bmm.out of the reference (csrc/ops/bmm.cpp:16-110): rank-3 FP32 operands with arbitrary
+// strides (transposed, offset, batch-broadcast views are read in place), zeros for an empty
+// contraction.  Integer and complex operands, which the reference sends elsewhere, are not built.
+static at::Tensor bmm(const at::Tensor& a, const at::Tensor& b) {
+  TORCH_CHECK(a.device() == b.device() && a.dim() == 3 && b.dim() == 3 && a.size(0) == b.size(0) && a.size(2) == b.size(1),
+              "Vulkan bmm: expected matching batch dimensions and contraction size");
+  TORCH_CHECK(a.scalar_type() == b.scalar_type(), "Vulkan bmm: dtype mismatch");
+  TORCH_CHECK(on_device(a) && a.scalar_type() == at::kFloat, "Vulkan bmm supports FP32 Vulkan tensors only");
+  const int64_t batch = a.size(0), m = a.size(1), k = a.size(2), n = b.size(2);
+  auto out = at::empty({batch, m, n}, a.options());
+  if (!out.numel()) return out;
+  if (k == 0) return torch_vulkan::zero_(out);
+  B200_TORCH_CHECK(b200_bmm(batch, m, n, k, a.const_data_ptr<float>(), a.stride(0), a.stride(1), a.stride(2),
+                            b.const_data_ptr<float>(), b.stride(0), b.stride(1), b.stride(2), out.data_ptr<float>(),
+                            B200_ALGO_AUTO, backend_stream()));
+  return out;
+}
+static at::Tensor& bmm_out(const at::Tensor& a, const at::Tensor& b, at::Tensor& out) {
+  TORCH_CHECK(out.device() == a.device() && a.device() == b.device(), "Vulkan bmm.out: all tensors must be on the same device");
+  auto result = torch_vulkan::bmm(a, b);  // the destination may alias an operand or be a strided view
+  if (out.sizes() != result.sizes()) {
+    std::vector<c10::SymInt> sz(result.sizes().begin(), result.sizes().end());
+    resize_(out, sz, std::nullopt);
+  }
+  if (out.numel()) copy_from(result, out, false);
+  return out;
+}
+
 TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
   m.impl("empty.memory_format", &empty_memory_format);
   m.impl("empty_strided", &empty_strided);
@@ -604,6 +633,8 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
   m.impl("mm", &mm);
   m.impl("mm.out", &mm_out);
   m.impl("addmm", &addmm);
+  m.impl("bmm", &bmm);
+  m.impl("bmm.out", &bmm_out);
 }
 
 }  // namespace torch_vulkan

@@ -114,6 +114,8 @@ int strip_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* b
                const StripPostOps* post = nullptr);
 // elementwise residual add / ReLU on a contiguous NCHW result (conv_simt.cu), for candidates without a fused epilogue
 int post_ops_nchw(float* y, const ConvGeom& g, const StripPostOps& post, cudaStream_t st);
+// y[n][c][plane] += bias[c] on a contiguous result (conv_simt.cu)
+int bias_add_nchw(float* y, long long n, int channels, long long plane, const float* bias, long long bias_stride, cudaStream_t st);
 int strip_column_tile(const ConvGeom& g, bool is_dx);   // column tile the plan picks, 0 if unsupported
 size_t strip_workspace(const ConvGeom& g, int phase);  // bytes of the weight stage images
 

@@ -255,11 +255,8 @@ int b200_conv_transpose2d_forward(const b200_conv_params* p, b200_view4 x, b200_
   // the transposed convolution of x is the input gradient of the convolution p describes
   if (int rc = b200_conv2d_dinput(p, x, w, y, workspace, workspace_bytes, algo, stream)) return rc;
   if (!bias) return B200_OK;
-  ConvGeom result = to_geom(*p);  // the result has p's input extent: address it as an "output" of that shape
-  result.cout = result.cin, result.oh = result.h, result.ow = result.w;
-  StripPostOps post{};
-  post.residual = View4{bias, 0, (long long)bias_stride, 0, 0};  // bias[c] broadcast over samples and pixels
-  return post_ops_nchw(y, result, post, (cudaStream_t)stream);
+  // the result has p's input extent: [n, cin, h, w]
+  return bias_add_nchw(y, p->n, p->cin, (long long)p->h * p->w, bias, bias_stride, (cudaStream_t)stream);
 }
 
 int b200_conv2d_dweight(const b200_conv_params* p, b200_view4 x, b200_view4 dy, float* dw, void* workspace,

@@ -526,6 +526,36 @@ int post_ops_nchw(float* y, const ConvGeom& g, const StripPostOps& post, cudaStr
   return launch_check("post_ops_kernel");
 }
 
+// y[n][c][plane] += bias[c] on a contiguous result: one CTA per (sample, channel) plane at a time,
+// 16-byte accesses where the plane is aligned.  The bias pass of the transposed convolution.
+__global__ void __launch_bounds__(256) bias_planes_kernel(float* __restrict__ y, const float* __restrict__ bias, long long bias_stride,
+                                                          int channels, int plane, long long planes) {
+  for (long long pl = blockIdx.x; pl < planes; pl += gridDim.x) {
+    const float b = __ldg(bias + (pl % channels) * bias_stride);
+    float* p = y + pl * plane;
+    int done = 0;
+    if ((reinterpret_cast<uintptr_t>(p) & 15) == 0) {
+      float4* p4 = reinterpret_cast<float4*>(p);
+      const int quads = plane >> 2;
+      for (int i = threadIdx.x; i < quads; i += 256) {
+        float4 v = p4[i];
+        v.x += b, v.y += b, v.z += b, v.w += b;
+        p4[i] = v;
+      }
+      done = quads * 4;
+    }
+    for (int e = done + threadIdx.x; e < plane; e += 256) p[e] += b;
+  }
+}
+int bias_add_nchw(float* y, long long n, int channels, long long plane, const float* bias, long long bias_stride, cudaStream_t st) {
+  const long long planes = n * channels;
+  if (planes == 0 || plane == 0) return B200_OK;
+  const long long grid = planes < 8ll * sm_count() ? planes : 8ll * sm_count();
+  bias_planes_kernel<<<(unsigned)grid, 256, 0, st>>>(y, bias, bias_stride, channels, (int)plane, planes);
+  count_launch();
+  return launch_check("bias_planes_kernel");
+}
+
 int dbias_reduce(const ConvGeom& g, View4 dy, float* db, float* partial, int slabs, cudaStream_t st) {
   if (slabs < 1 || !partial) slabs = 1;
   float* out = slabs > 1 ? partial : db;

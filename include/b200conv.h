@@ -235,6 +235,17 @@ int b200_batch_norm_forward(int64_t n, int64_t c, int64_t s, int layout, const f
                             float momentum, float eps, float* y, float* save_mean, float* save_inv, void* workspace,
                             size_t workspace_bytes, void* stream);
 
+/* The call above followed by `+ residual` (a tensor of x's shape and layout, NULL = none) and a
+ * ReLU (relu != 0) in the same pass that writes y: the add.Tensor / relu pair that follows a BatchNorm
+ * in a residual block (csrc/ops/mm.cpp:1094-1097 registers them as separate elementwise operators;
+ * no fused counterpart exists in the reference).  save_mean / save_inv and the running statistics
+ * are those of the plain call. */
+int b200_batch_norm_forward_fused(int64_t n, int64_t c, int64_t s, int layout, const float* x, const float* weight,
+                                  int64_t weight_stride, const float* bias, int64_t bias_stride, float* running_mean,
+                                  int64_t running_mean_stride, float* running_var, int64_t running_var_stride, int training,
+                                  float momentum, float eps, const float* residual, int relu, float* y, float* save_mean,
+                                  float* save_inv, void* workspace, size_t workspace_bytes, void* stream);
+
 /* Gradients of the call above.  Replaces batch_norm_backward (csrc/ops/batch_norm.cpp:84-113) and
  * batch_norm_backward.comp.  dx, dw, db: NULL = not wanted (the reference's output mask).
  *  - training != 0: mean / inv_or_var are save_mean / save_inv of the forward call;

@@ -93,6 +93,9 @@ SIGNATURES = {
     "b200_batch_norm_forward": (c_int, [c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_int64,
                                         c_void_p, c_int64, c_void_p, c_int64, c_int, c_float, c_float, c_void_p, c_void_p,
                                         c_void_p, c_void_p, c_size_t, c_void_p]),
+    "b200_batch_norm_forward_fused": (c_int, [c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_int64,
+                                              c_void_p, c_int64, c_void_p, c_int64, c_int, c_float, c_float, c_void_p, c_int,
+                                              c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
     "b200_batch_norm_backward": (c_int, [c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_void_p,
                                          c_int64, c_void_p, c_int64, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p,
                                          c_size_t, c_void_p]),
@@ -366,7 +369,7 @@ def _bn_dims(shape):
 
 
 def batch_norm_forward(x, weight=None, bias=None, running_mean=None, running_var=None, training=True, momentum=0.1,
-                       eps=1e-5, channels_last=False):
+                       eps=1e-5, channels_last=False, residual=None, relu=False):
     """aten::native_batch_norm on the device (csrc/ops/batch_norm.cpp:21-83).  x: logical [n, c, ...];
     weight / bias / running_*: channel vectors (any strided float32 view) or None.  Returns
     (y, save_mean, save_inv, running_mean, running_var): save_* are empty in evaluation mode, the
@@ -380,8 +383,14 @@ def batch_norm_forward(x, weight=None, bias=None, running_mean=None, running_var
     sm, si = DeviceBuffer(4 * c), DeviceBuffer(4 * c)
     ws_n = int(lib().b200_batch_norm_workspace(n, c, s, layout))
     ws = DeviceBuffer(ws_n)
-    check(lib().b200_batch_norm_forward(n, c, s, layout, xv.ptr, *arg(vec[0]), *arg(vec[1]), *arg(vec[2]), *arg(vec[3]),
-                                        int(bool(training)), momentum, eps, y.ptr, sm.ptr, si.ptr, ws.ptr, ws_n, None))
+    if residual is None and not relu:
+        check(lib().b200_batch_norm_forward(n, c, s, layout, xv.ptr, *arg(vec[0]), *arg(vec[1]), *arg(vec[2]), *arg(vec[3]),
+                                            int(bool(training)), momentum, eps, y.ptr, sm.ptr, si.ptr, ws.ptr, ws_n, None))
+    else:  # y = relu(batch_norm(x) + residual) in the pass that writes y
+        rv = DeviceView(_bn_pack(residual, channels_last)) if residual is not None else None
+        check(lib().b200_batch_norm_forward_fused(n, c, s, layout, xv.ptr, *arg(vec[0]), *arg(vec[1]), *arg(vec[2]), *arg(vec[3]),
+                                                  int(bool(training)), momentum, eps, rv.ptr if rv else None, int(bool(relu)),
+                                                  y.ptr, sm.ptr, si.ptr, ws.ptr, ws_n, None))
     out = _bn_unpack(y.to_numpy((n * c * s,)), x.shape, channels_last)
 
     def back(view, like):  # the (possibly strided) vector as the device left it

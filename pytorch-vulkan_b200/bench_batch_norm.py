@@ -6,7 +6,8 @@
 Shapes default to the activations of the convolution benchmark's layer sweep (batch 64).  For each
 shape and layout (planar = NCHW, interleaved = channels-last) three calls are timed with CUDA events
 on the launching stream: training forward, evaluation forward, training backward (dx, dw, db).
-Algorithmic bytes per element: training forward 12 (statistics read, normalisation read, write),
+Algorithmic bytes per element: training forward 12 (statistics read, normalisation read, write; 16 with
+the fused residual add and ReLU, which reads one more tensor),
 evaluation 8 (read, write), backward 20 (x and g read for the sums, x and g read again, dx written).
 `cold` rows write a 256 MB buffer (larger than L2) before every timed call; `warm` rows run the
 calls back to back, so tensors smaller than L2 are partly served from it.  One JSON line per row.
@@ -20,7 +21,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, HERE)
 
 DEFAULT_SHAPES = [(64, 64, 3136), (64, 256, 3136), (64, 128, 784), (64, 256, 196), (64, 512, 49), (64, 1024, 3136)]
-BYTES_PER_ELEMENT = {"train_forward": 12, "eval_forward": 8, "train_backward": 20}
+BYTES_PER_ELEMENT = {"train_forward": 12, "train_forward_add_relu": 16, "eval_forward": 8, "train_backward": 20}
 
 
 def hbm_peak():
@@ -104,6 +105,9 @@ def main():
             calls = {
                 "train_forward": lambda: L.b200_batch_norm_forward(n, c, s, layout, P(x), P(w), 1, P(b), 1, P(rm), 1, P(rv), 1, 1,
                                                                    0.1, 1e-5, P(y), P(sm), P(si), P(ws), ws_n, stream),
+                "train_forward_add_relu": lambda: L.b200_batch_norm_forward_fused(n, c, s, layout, P(x), P(w), 1, P(b), 1, P(rm), 1,
+                                                                                  P(rv), 1, 1, 0.1, 1e-5, P(g), 1, P(y), P(sm), P(si),
+                                                                                  P(ws), ws_n, stream),
                 "eval_forward": lambda: L.b200_batch_norm_forward(n, c, s, layout, P(x), P(w), 1, P(b), 1, P(rm), 1, P(rv), 1, 0,
                                                                   0.1, 1e-5, P(y), P(sm), P(si), P(ws), ws_n, stream),
                 "train_backward": lambda: L.b200_batch_norm_backward(n, c, s, layout, P(g), P(x), P(w), 1, P(sm), 1, P(si), 1, 1,

@@ -271,13 +271,27 @@ __device__ __forceinline__ float normalise(float v, float4 k) { return ((v - k.x
 
 // y = ((x - origin) - mean_rel) * (inv * gamma) + beta over the flat tensor.  UNIFORM: the four
 // elements of a 16-byte group share a channel (inner % 4 == 0), `ch` then indexes groups.
-template <bool UNIFORM>
+// POST: add a residual tensor of the same layout (res may be null) and / or clamp at zero before the
+// store, the add + ReLU that follows a BatchNorm in a residual block.
+struct BnPost {
+  const float* res;
+  int relu;
+};
+__device__ __forceinline__ float4 post_ops(float4 r, float4 add, int relu) {
+  r.x += add.x, r.y += add.y, r.z += add.z, r.w += add.w;
+  if (relu) r = make_float4(fmaxf(r.x, 0.f), fmaxf(r.y, 0.f), fmaxf(r.z, 0.f), fmaxf(r.w, 0.f));
+  return r;
+}
+
+template <bool UNIFORM, bool POST>
 __global__ void __launch_bounds__(kThreads) bn_apply_kernel(const float* __restrict__ x, float* __restrict__ y,
-                                                             const float4* __restrict__ coef, uint32_t total, ChannelOf ch) {
+                                                             const float4* __restrict__ coef, uint32_t total, ChannelOf ch, BnPost post) {
   const uint32_t quads = total >> 2, stride = gridDim.x * kThreads;
   const float4* x4 = reinterpret_cast<const float4*>(x);
+  const float4* r4 = reinterpret_cast<const float4*>(post.res);
   float4* y4 = reinterpret_cast<float4*>(y);
-  auto one = [&](uint32_t q, float4 a) {
+  const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+  auto one = [&](uint32_t q, float4 a, float4 add) {
     float4 r;
     if (UNIFORM) {
       const float4 k = __ldg(coef + ch(q));
@@ -286,46 +300,57 @@ __global__ void __launch_bounds__(kThreads) bn_apply_kernel(const float* __restr
       r = make_float4(normalise(a.x, __ldg(coef + ch(4 * q))), normalise(a.y, __ldg(coef + ch(4 * q + 1))),
                       normalise(a.z, __ldg(coef + ch(4 * q + 2))), normalise(a.w, __ldg(coef + ch(4 * q + 3))));
     }
-    y4[q] = r;
+    y4[q] = POST ? post_ops(r, add, post.relu) : r;
   };
+  auto residual = [&](uint32_t q) { return POST && r4 ? __ldg(r4 + q) : zero; };
   uint32_t q = blockIdx.x * kThreads + threadIdx.x;
   for (; q < quads && q + 3 * (uint64_t)stride < quads; q += 4 * stride) {
     const float4 a0 = __ldg(x4 + q), a1 = __ldg(x4 + q + stride), a2 = __ldg(x4 + q + 2 * stride), a3 = __ldg(x4 + q + 3 * stride);
-    one(q, a0), one(q + stride, a1), one(q + 2 * stride, a2), one(q + 3 * stride, a3);
+    const float4 b0 = residual(q), b1 = residual(q + stride), b2 = residual(q + 2 * stride), b3 = residual(q + 3 * stride);
+    one(q, a0, b0), one(q + stride, a1, b1), one(q + 2 * stride, a2, b2), one(q + 3 * stride, a3, b3);
   }
-  for (; q < quads; q += stride) one(q, __ldg(x4 + q));
+  for (; q < quads; q += stride) one(q, __ldg(x4 + q), residual(q));
 }
 
 // Channels-last with c % 4 == 0: a thread keeps one group of four channels, whose coefficients stay
 // in registers, and walks down the rows.  `lanes` (a multiple of c / 4) threads take part.
+template <bool POST>
 __global__ void __launch_bounds__(kThreads) bn_apply_cols_kernel(const float* __restrict__ x, float* __restrict__ y,
                                                                   const float4* __restrict__ coef, uint32_t rows, uint32_t c4,
-                                                                  uint32_t lanes) {
+                                                                  uint32_t lanes, BnPost post) {
   const uint32_t t = blockIdx.x * kThreads + threadIdx.x;
   if (t >= lanes) return;
   const uint32_t r0 = t / c4, j = t - r0 * c4;
   const uint64_t rstep = lanes / c4;
   const float4 k0 = __ldg(coef + 4 * j), k1 = __ldg(coef + 4 * j + 1), k2 = __ldg(coef + 4 * j + 2), k3 = __ldg(coef + 4 * j + 3);
   const float4* x4 = reinterpret_cast<const float4*>(x) + j;
+  const float4* r4 = post.res ? reinterpret_cast<const float4*>(post.res) + j : nullptr;
   float4* y4 = reinterpret_cast<float4*>(y) + j;
-  auto one = [&](uint64_t row, float4 a) {
-    y4[row * c4] = make_float4(normalise(a.x, k0), normalise(a.y, k1), normalise(a.z, k2), normalise(a.w, k3));
+  const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+  auto one = [&](uint64_t row, float4 a, float4 add) {
+    const float4 r = make_float4(normalise(a.x, k0), normalise(a.y, k1), normalise(a.z, k2), normalise(a.w, k3));
+    y4[row * c4] = POST ? post_ops(r, add, post.relu) : r;
   };
+  auto residual = [&](uint64_t row) { return POST && r4 ? __ldg(r4 + row * c4) : zero; };
   uint64_t r = r0;
   for (; r + 3 * rstep < rows; r += 4 * rstep) {
     const float4 a0 = __ldg(x4 + r * c4), a1 = __ldg(x4 + (r + rstep) * c4), a2 = __ldg(x4 + (r + 2 * rstep) * c4),
                  a3 = __ldg(x4 + (r + 3 * rstep) * c4);
-    one(r, a0), one(r + rstep, a1), one(r + 2 * rstep, a2), one(r + 3 * rstep, a3);
+    const float4 b0 = residual(r), b1 = residual(r + rstep), b2 = residual(r + 2 * rstep), b3 = residual(r + 3 * rstep);
+    one(r, a0, b0), one(r + rstep, a1, b1), one(r + 2 * rstep, a2, b2), one(r + 3 * rstep, a3, b3);
   }
-  for (; r < rows; r += rstep) one(r, __ldg(x4 + r * c4));
+  for (; r < rows; r += rstep) one(r, __ldg(x4 + r * c4), residual(r));
 }
 
 // Scalar form: unaligned tensors and the last total % 4 elements ([first, total)).
 __global__ void __launch_bounds__(kThreads) bn_apply_scalar_kernel(const float* __restrict__ x, float* __restrict__ y,
                                                                     const float4* __restrict__ coef, uint32_t first, uint32_t total,
-                                                                    ChannelOf ch) {
-  for (uint64_t i = first + blockIdx.x * (uint64_t)kThreads + threadIdx.x; i < total; i += (uint64_t)gridDim.x * kThreads)
-    y[i] = normalise(__ldg(x + i), __ldg(coef + ch((uint32_t)i)));
+                                                                    ChannelOf ch, BnPost post) {
+  for (uint64_t i = first + blockIdx.x * (uint64_t)kThreads + threadIdx.x; i < total; i += (uint64_t)gridDim.x * kThreads) {
+    float v = normalise(__ldg(x + i), __ldg(coef + ch((uint32_t)i)));
+    if (post.res) v += __ldg(post.res + i);
+    y[i] = post.relu ? fmaxf(v, 0.f) : v;
+  }
 }
 
 // ---- backward: reductions -------------------------------------------------------------------
@@ -695,6 +720,16 @@ int b200_batch_norm_forward(int64_t n, int64_t c, int64_t s, int layout, const f
                             int64_t running_mean_stride, float* running_var, int64_t running_var_stride, int training,
                             float momentum, float eps, float* y, float* save_mean, float* save_inv, void* workspace,
                             size_t workspace_bytes, void* stream) {
+  return b200_batch_norm_forward_fused(n, c, s, layout, x, weight, weight_stride, bias, bias_stride, running_mean,
+                                       running_mean_stride, running_var, running_var_stride, training, momentum, eps, nullptr, 0, y,
+                                       save_mean, save_inv, workspace, workspace_bytes, stream);
+}
+
+int b200_batch_norm_forward_fused(int64_t n, int64_t c, int64_t s, int layout, const float* x, const float* weight,
+                                  int64_t weight_stride, const float* bias, int64_t bias_stride, float* running_mean,
+                                  int64_t running_mean_stride, float* running_var, int64_t running_var_stride, int training,
+                                  float momentum, float eps, const float* residual, int relu, float* y, float* save_mean,
+                                  float* save_inv, void* workspace, size_t workspace_bytes, void* stream) {
   if (int rc = ensure_init()) return rc;
   BnPlan p;
   if (int rc = make_plan(n, c, s, layout, &p)) return rc;
@@ -733,26 +768,36 @@ int b200_batch_norm_forward(int64_t n, int64_t c, int64_t s, int layout, const f
     count_launch();
     if (int rc = launch_check("bn_eval_coef_kernel")) return rc;
   }
-  if (aligned16(x) && aligned16(y)) {
+  const BnPost post{residual, relu ? 1 : 0};
+  const bool fused = residual || relu;
+  if (fused) note_kernel(training ? "bn_stats+finalize+apply_fused" : "bn_eval_coef+apply_fused");
+  if (aligned16(x) && aligned16(y) && aligned16(residual)) {
     const bool uniform = sh.inner % 4 == 0;
     const uint32_t quads = total >> 2;
     if (quads) {
       const int grid = apply_grid((quads + 3) / 4);
       const uint32_t c4 = (uint32_t)sh.c / 4, threads = (uint32_t)grid * kThreads;
-      if (sh.inner == 1 && sh.c % 4 == 0 && threads >= c4)
-        bn_apply_cols_kernel<<<grid, kThreads, 0, st>>>(x, y, coef, (uint32_t)sh.outer, c4, threads / c4 * c4);
-      else if (uniform) bn_apply_kernel<true><<<grid, kThreads, 0, st>>>(x, y, coef, total, channel_of(sh, true));
-      else bn_apply_kernel<false><<<grid, kThreads, 0, st>>>(x, y, coef, total, channel_of(sh, false));
+      const uint32_t lanes = c4 ? threads / c4 * c4 : 0;
+      if (sh.inner == 1 && sh.c % 4 == 0 && threads >= c4) {
+        if (fused) bn_apply_cols_kernel<true><<<grid, kThreads, 0, st>>>(x, y, coef, (uint32_t)sh.outer, c4, lanes, post);
+        else bn_apply_cols_kernel<false><<<grid, kThreads, 0, st>>>(x, y, coef, (uint32_t)sh.outer, c4, lanes, post);
+      } else if (uniform) {
+        if (fused) bn_apply_kernel<true, true><<<grid, kThreads, 0, st>>>(x, y, coef, total, channel_of(sh, true), post);
+        else bn_apply_kernel<true, false><<<grid, kThreads, 0, st>>>(x, y, coef, total, channel_of(sh, true), post);
+      } else {
+        if (fused) bn_apply_kernel<false, true><<<grid, kThreads, 0, st>>>(x, y, coef, total, channel_of(sh, false), post);
+        else bn_apply_kernel<false, false><<<grid, kThreads, 0, st>>>(x, y, coef, total, channel_of(sh, false), post);
+      }
       count_launch();
       if (int rc = launch_check("bn_apply_kernel")) return rc;
     }
     if (total & 3) {
-      bn_apply_scalar_kernel<<<1, kThreads, 0, st>>>(x, y, coef, total & ~3u, total, channel_of(sh, false));
+      bn_apply_scalar_kernel<<<1, kThreads, 0, st>>>(x, y, coef, total & ~3u, total, channel_of(sh, false), post);
       count_launch();
       if (int rc = launch_check("bn_apply_scalar_kernel")) return rc;
     }
   } else {
-    bn_apply_scalar_kernel<<<apply_grid(total), kThreads, 0, st>>>(x, y, coef, 0, total, channel_of(sh, false));
+    bn_apply_scalar_kernel<<<apply_grid(total), kThreads, 0, st>>>(x, y, coef, 0, total, channel_of(sh, false), post);
     count_launch();
     if (int rc = launch_check("bn_apply_scalar_kernel")) return rc;
   }

@@ -191,3 +191,31 @@ def test_invalid_arguments():
     with pytest.raises(ValueError, match="shape mismatch"):
         b200conv.batch_norm_backward(np.zeros((2, 3, 4), np.float32), np.zeros((2, 3, 5), np.float32), None,
                                      np.zeros(3, np.float32), np.ones(3, np.float32))
+
+
+@pytest.mark.parametrize("shape", [(4, 16, 32, 32), (3, 5, 33, 33), (16, 32, 7, 7), (300, 33), (8, 24, 14, 14)],
+                         ids=lambda s: "x".join(map(str, s)))
+@pytest.mark.parametrize("channels_last", [False, True], ids=["planar", "interleaved"])
+@pytest.mark.parametrize("training", [True, False], ids=["train", "eval"])
+@pytest.mark.parametrize("ops", ["relu", "residual", "residual_relu"])
+def test_fused_residual_and_relu(shape, channels_last, training, ops):
+    rng = np.random.default_rng(sum(shape) + len(ops))
+    c = shape[1]
+    x = (rng.standard_normal(shape) * 1.3 - 0.2).astype(np.float32)
+    res = rng.standard_normal(shape).astype(np.float32) if "residual" in ops else None
+    w, b = rng.standard_normal(c).astype(np.float32), rng.standard_normal(c).astype(np.float32)
+    rm, rv = rng.standard_normal(c).astype(np.float32), (rng.random(c) + 0.4).astype(np.float32)
+    relu = "relu" in ops
+    y, mean, inv, rm_out, rv_out = b200conv.batch_norm_forward(x, w, b, rm, rv, training, 0.1, 1e-5, channels_last=channels_last,
+                                                               residual=res, relu=relu)
+    assert b200conv.last_kernel().endswith("apply_fused")
+    want = bn.forward(x, w, b, rm, rv, training, 0.1, 1e-5, dtype=np.float64)
+    ref = want[0] + (res if res is not None else 0.0)
+    if relu:
+        ref = np.maximum(ref, 0.0)
+        assert (y >= 0).all()
+    assert oracle.rel_l2(y, ref) <= GATE
+    # the statistics are those of the plain call
+    plain = b200conv.batch_norm_forward(x, w, b, rm, rv, training, 0.1, 1e-5, channels_last=channels_last)
+    for a, e in zip((mean, inv, rm_out, rv_out), plain[1:]):
+        np.testing.assert_array_equal(a, e)

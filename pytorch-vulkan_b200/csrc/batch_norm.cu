@@ -20,6 +20,8 @@
 // deviations) and merged pairwise, the streaming form of the reference's shifted two-pass
 // reduction (batch_norm_forward.comp:27-38): no E[x^2]-E[x]^2 cancellation for data with a
 // large common offset, and the low part of the mean survives into the normalisation.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace b200 {
@@ -627,6 +629,159 @@ __global__ void __launch_bounds__(kThreads) bn_bwd_apply_scalar_kernel(const flo
   }
 }
 
+// ---- small tensors: one CTA per channel, one launch ------------------------------------------------
+// When a channel's values are a few hundred KB at most and there are enough channels to fill the
+// GPU, the three launches above cost more than the traffic.  Here one CTA owns a channel from the
+// first read to the last write, as the reference's workgroup does (batch_norm_forward.comp:18-55,
+// batch_norm_backward.comp:18-66), with a warp per image plane; the second pass finds the channel in
+// L1 / L2.  Planar layout only.
+
+// f(value) / f(x value, g value) over a plane of `len` floats, the warp's lanes striding it with
+// 16-byte loads where the plane is aligned.
+constexpr int kChannelThreads = 1024;  // 32 warps: a channel is spread over as many image planes at once as an SM holds
+
+template <bool TWO, class F>
+__device__ __forceinline__ void plane_stream(const float* __restrict__ p, const float* __restrict__ q, int len, int lane, F&& f) {
+  int done = 0;
+  if (((reinterpret_cast<uintptr_t>(p) | (TWO ? reinterpret_cast<uintptr_t>(q) : 0)) & 15) == 0) {
+    const float4* p4 = reinterpret_cast<const float4*>(p);
+    const float4* q4 = reinterpret_cast<const float4*>(q);
+    const int quads = len >> 2;
+    const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+    int i = lane;
+    for (; i + 32 < quads; i += 64) {
+      const float4 a0 = __ldg(p4 + i), a1 = __ldg(p4 + i + 32), b0 = TWO ? __ldg(q4 + i) : zero, b1 = TWO ? __ldg(q4 + i + 32) : zero;
+      f(a0.x, b0.x), f(a0.y, b0.y), f(a0.z, b0.z), f(a0.w, b0.w);
+      f(a1.x, b1.x), f(a1.y, b1.y), f(a1.z, b1.z), f(a1.w, b1.w);
+    }
+    for (; i < quads; i += 32) {
+      const float4 a = __ldg(p4 + i), b = TWO ? __ldg(q4 + i) : zero;
+      f(a.x, b.x), f(a.y, b.y), f(a.z, b.z), f(a.w, b.w);
+    }
+    done = quads * 4;
+  }
+  for (int e = done + lane; e < len; e += 32) f(__ldg(p + e), TWO ? __ldg(q + e) : 0.f);
+}
+// out[e] = f(a, b, r) over a plane; r is the residual value (0 when res is null).
+template <bool TWO, class F>
+__device__ __forceinline__ void plane_map(const float* __restrict__ p, const float* __restrict__ q, const float* __restrict__ res,
+                                          float* __restrict__ out, int len, int lane, F&& f) {
+  int done = 0;
+  const uintptr_t bits = reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(res) |
+                         (TWO ? reinterpret_cast<uintptr_t>(q) : 0);
+  if ((bits & 15) == 0) {
+    const float4* p4 = reinterpret_cast<const float4*>(p);
+    const float4* q4 = reinterpret_cast<const float4*>(q);
+    const float4* r4 = reinterpret_cast<const float4*>(res);
+    float4* o4 = reinterpret_cast<float4*>(out);
+    const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int i = lane; i < (len >> 2); i += 32) {
+      const float4 a = __ldg(p4 + i), b = TWO ? __ldg(q4 + i) : zero, r = res ? __ldg(r4 + i) : zero;
+      o4[i] = make_float4(f(a.x, b.x, r.x), f(a.y, b.y, r.y), f(a.z, b.z, r.z), f(a.w, b.w, r.w));
+    }
+    done = (len >> 2) * 4;
+  }
+  for (int e = done + lane; e < len; e += 32) out[e] = f(__ldg(p + e), TWO ? __ldg(q + e) : 0.f, res ? __ldg(res + e) : 0.f);
+}
+
+__global__ void __launch_bounds__(kChannelThreads) bn_forward_channel_kernel(const float* __restrict__ x, BnShape sh, BnForwardVectors v,
+                                                                       BnPost post, float* __restrict__ y) {
+  const int ch = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const float origin = __ldg(x + (size_t)ch * sh.inner);
+  const float gamma = v.weight ? v.weight[ch * v.w_stride] : 1.f;
+  const float beta = v.bias ? v.bias[ch * v.b_stride] : 0.f;
+  Moments acc = {0.f, 0.f, 0.f};
+  for (int img = warp; img < sh.outer; img += kChannelThreads / 32) {
+    const float* base = x + ((size_t)img * sh.c + ch) * sh.inner;
+    const float k = __ldg(base + min(lane, sh.inner - 1));
+    Shifted t;
+    plane_stream<false>(base, nullptr, sh.inner, lane, [&](float xv, float) { t.add(xv, k); });
+    acc = merge(acc, t.moments(k, origin));
+  }
+  __shared__ Moments warp_part[32];
+  acc = warp_merge(acc);
+  if (threadIdx.x < 32) warp_part[threadIdx.x] = Moments{0.f, 0.f, 0.f};
+  __syncthreads();
+  if (lane == 0) warp_part[warp] = acc;
+  __syncthreads();
+  const Moments m = warp_merge(warp_part[lane]);  // every warp folds the partial results itself
+  const float variance = m.m2 / sh.m;
+  const float inv = (variance == 0.f && v.eps == 0.f) ? 0.f : 1.f / sqrtf(variance + v.eps);
+  if (threadIdx.x == 0) {
+    const float mean = origin + m.mean;
+    v.save_mean[ch] = mean;
+    v.save_inv[ch] = inv;
+    if (v.running_mean) {
+      float* p = v.running_mean + ch * v.rm_stride;
+      *p = (1.f - v.momentum) * *p + v.momentum * mean;
+    }
+    if (v.running_var) {
+      float* p = v.running_var + ch * v.rv_stride;
+      *p = (1.f - v.momentum) * *p + v.momentum * (m.m2 / (sh.m - 1.f));
+    }
+  }
+  const float4 k4 = make_float4(origin, m.mean, inv * gamma, beta);
+  for (int img = warp; img < sh.outer; img += kChannelThreads / 32) {
+    const size_t at = ((size_t)img * sh.c + ch) * sh.inner;
+    plane_map<false>(x + at, nullptr, post.res ? post.res + at : nullptr, y + at, sh.inner, lane, [&](float xv, float, float r) {
+      const float o = normalise(xv, k4) + r;
+      return post.relu ? fmaxf(o, 0.f) : o;
+    });
+  }
+}
+
+__global__ void __launch_bounds__(kChannelThreads) bn_backward_channel_kernel(const float* __restrict__ x, const float* __restrict__ g,
+                                                                        BnShape sh, BnBackwardVectors v, float* __restrict__ dx) {
+  const int ch = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const float mean = v.mean[ch * v.mean_stride];
+  float inv = v.inv[ch * v.inv_stride];
+  if (!v.training) inv = 1.f / sqrtf(inv + v.eps);
+  const float gamma = v.weight ? v.weight[ch * v.w_stride] : 1.f;
+  Sums t = {0.f, 0.f, 0.f};
+  for (int img = warp; img < sh.outer; img += kChannelThreads / 32) {
+    const size_t at = ((size_t)img * sh.c + ch) * sh.inner;
+    plane_stream<true>(x + at, g + at, sh.inner, lane, [&](float xv, float gv) { t.add(xv, gv, mean); });
+  }
+  __shared__ Sums warp_part[32];
+  t = warp_sums(t);
+  if (threadIdx.x < 32) warp_part[threadIdx.x] = Sums{0.f, 0.f, 0.f};
+  __syncthreads();
+  if (lane == 0) warp_part[warp] = t;
+  __syncthreads();
+  const Sums s = warp_sums(warp_part[lane]);
+  float fa = s.a, fb = s.b, residual = 0.f;
+  if (v.training) {
+    residual = s.r / sh.m;
+    if (residual != 0.f) fb -= residual * fa;
+  }
+  if (threadIdx.x == 0) {
+    if (v.dw) v.dw[ch] = fb * inv;
+    if (v.db) v.db[ch] = fa;
+  }
+  if (!dx) return;
+  const float4 k4 = make_float4(mean, residual, fa / sh.m, (fb / sh.m) * inv * inv);
+  const float scale = inv * gamma;
+  const bool training = v.training != 0;
+  for (int img = warp; img < sh.outer; img += kChannelThreads / 32) {
+    const size_t at = ((size_t)img * sh.c + ch) * sh.inner;
+    plane_map<true>(x + at, g + at, nullptr, dx + at, sh.inner, lane, [&](float xv, float gv, float) {
+      return training ? input_grad<true>(xv, gv, k4, scale) : input_grad<false>(xv, gv, k4, scale);
+    });
+  }
+}
+
+// One launch pays when a channel is tens to hundreds of KB and the channels fill the GPU.  Measured
+// kernel times (64 images): 256 channels of 14x14 20 us against 26 us for the three launches, 128
+// channels of 28x28 18 against 27; 512 channels of 7x7 (12 KB each) 31 against 21, so short channels
+// keep the three-launch path.
+bool channel_kernel_fits(const BnShape& sh, int layout) {
+  static const bool enabled = !(getenv("B200_BN_ONE_LAUNCH") && getenv("B200_BN_ONE_LAUNCH")[0] == '0');  // testing aid
+  if (!enabled) return false;
+  const double channel_bytes = (double)sh.m * sizeof(float);
+  return layout == B200_BN_PLANAR && sh.c >= 64 && channel_bytes >= 32.0 * 1024 && channel_bytes <= 256.0 * 1024 &&
+         channel_bytes * sh.c <= 64.0 * 1024 * 1024;
+}
+
 // ---- host side ---------------------------------------------------------------------------------
 
 struct BnPlan {
@@ -746,6 +901,12 @@ int b200_batch_norm_forward_fused(int64_t n, int64_t c, int64_t s, int layout, c
   BnForwardVectors v{weight, bias, running_mean, running_var, weight_stride, bias_stride, running_mean_stride,
                      running_var_stride, save_mean, save_inv, eps, momentum};
   const uint32_t total = (uint32_t)((int64_t)sh.outer * sh.cols);
+  if (training && channel_kernel_fits(sh, layout)) {
+    note_kernel(residual || relu ? "bn_forward_channel_fused" : "bn_forward_channel");
+    bn_forward_channel_kernel<<<(unsigned)sh.c, kChannelThreads, 0, st>>>(x, sh, v, BnPost{residual, relu ? 1 : 0}, y);
+    count_launch();
+    return launch_check("bn_forward_channel_kernel");
+  }
   if (training) {
     if (p.rows) {
       note_kernel("bn_stats_rows+finalize+apply");
@@ -830,6 +991,12 @@ int b200_batch_norm_backward(int64_t n, int64_t c, int64_t s, int layout, const 
     return launch_check("bn_bwd_pair_kernel");
   }
   const int has_sums = training || dw || db;
+  if (has_sums && channel_kernel_fits(sh, layout)) {
+    note_kernel("bn_backward_channel");
+    bn_backward_channel_kernel<<<(unsigned)sh.c, kChannelThreads, 0, st>>>(x, grad, sh, v, dx);
+    count_launch();
+    return launch_check("bn_backward_channel_kernel");
+  }
   if (has_sums) {
     if (p.rows) {
       bn_bwd_rows_kernel<<<dim3((unsigned)sh.c, (unsigned)sh.slabs), kThreads, 0, st>>>(x, grad, sh, v, part);

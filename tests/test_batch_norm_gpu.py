@@ -59,6 +59,8 @@ def test_golden_cases(c, channels_last):
 SHAPES = [
     (4, 16, 32, 32), (3, 5, 33, 33), (1, 3, 96, 100), (2, 7, 20, 13), (8, 24, 14, 14), (16, 32, 7, 7),
     (5, 6, 7, 7), (64, 10), (300, 33), (2, 4, 3000), (1, 2, 5, 1000), (130, 8, 3, 3),
+    # 64 channels or more of 32 to 256 KB each: one CTA per channel, one launch (planar layout)
+    (32, 128, 7, 7), (16, 64, 28, 28), (12, 80, 33, 33), (64, 256, 14, 14), (3, 96, 5),
 ]
 
 
@@ -90,7 +92,10 @@ def test_against_the_fp64_oracle(shape, channels_last, training):
     assert oracle.rel_l2(dx, wdx) <= 2 * GATE
     assert oracle.rel_l2(dw, wdw) <= 2 * GATE
     assert oracle.rel_l2(db, wdb) <= 2 * GATE
-    assert b200conv.last_kernel().startswith("bn_bwd")
+    channel_bytes = 4 * x.size // c
+    one_launch = not channels_last and c >= 64 and 32 * 1024 <= channel_bytes <= 256 * 1024
+    assert b200conv.last_kernel() == ("bn_backward_channel" if one_launch else b200conv.last_kernel())
+    assert b200conv.last_kernel().startswith("bn_b")
 
 
 @pytest.mark.parametrize("mask", [(True, False, False), (False, True, False), (False, False, True), (False, True, True),
@@ -193,7 +198,7 @@ def test_invalid_arguments():
                                      np.zeros(3, np.float32), np.ones(3, np.float32))
 
 
-@pytest.mark.parametrize("shape", [(4, 16, 32, 32), (3, 5, 33, 33), (16, 32, 7, 7), (300, 33), (8, 24, 14, 14)],
+@pytest.mark.parametrize("shape", [(4, 16, 32, 32), (3, 5, 33, 33), (16, 32, 7, 7), (300, 33), (8, 24, 14, 14), (48, 64, 14, 14), (6, 72, 9, 7)],
                          ids=lambda s: "x".join(map(str, s)))
 @pytest.mark.parametrize("channels_last", [False, True], ids=["planar", "interleaved"])
 @pytest.mark.parametrize("training", [True, False], ids=["train", "eval"])
@@ -208,7 +213,7 @@ def test_fused_residual_and_relu(shape, channels_last, training, ops):
     relu = "relu" in ops
     y, mean, inv, rm_out, rv_out = b200conv.batch_norm_forward(x, w, b, rm, rv, training, 0.1, 1e-5, channels_last=channels_last,
                                                                residual=res, relu=relu)
-    assert b200conv.last_kernel().endswith("apply_fused")
+    assert "fused" in b200conv.last_kernel()
     want = bn.forward(x, w, b, rm, rv, training, 0.1, 1e-5, dtype=np.float64)
     ref = want[0] + (res if res is not None else 0.0)
     if relu:

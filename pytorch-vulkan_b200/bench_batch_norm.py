@@ -10,7 +10,9 @@ Algorithmic bytes per element: training forward 12 (statistics read, normalisati
 the fused residual add and ReLU, which reads one more tensor),
 evaluation 8 (read, write), backward 20 (x and g read for the sums, x and g read again, dx written).
 `cold` rows write a 256 MB buffer (larger than L2) before every timed call; `warm` rows run the
-calls back to back, so tensors smaller than L2 are partly served from it.  One JSON line per row.
+calls back to back, so tensors smaller than L2 are partly served from it; with --graph a third row
+times the calls inside one CUDA graph, which removes the host's launch cost (about 17 us per call from
+Python) that bounds the warm rows of small tensors.  One JSON line per row.
 """
 import argparse
 import json
@@ -35,6 +37,8 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reps", type=int, default=10)
     ap.add_argument("--shapes", default="")
+    ap.add_argument("--graph", action="store_true",
+                    help="also time each call as `reps` launches inside one CUDA graph (no host launch cost between calls)")
     ap.add_argument("--cpu-baseline", action="store_true",
                     help="also time PyTorch's CPU FP32 batch norm (the arithmetic the reference's tests compare with) on the host cores")
     args = ap.parse_args()
@@ -73,6 +77,23 @@ def main():
             total += e0.elapsed_time(e1)
         return total / args.reps
 
+    def timed_in_graph(fn):
+        """`reps` calls captured into one CUDA graph and replayed: device time per call without the
+        host's launch cost between calls."""
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            capture_stream = torch.cuda.current_stream().cuda_stream
+            for _ in range(args.reps):
+                b200conv.check(fn(capture_stream))
+        graph.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / args.reps
+
     if args.cpu_baseline:
         import time
         n, c, s = shapes[0]
@@ -103,26 +124,30 @@ def main():
             ws = torch.empty(ws_n, dtype=torch.uint8, device=dev)
             P = lambda t: t.data_ptr()
             calls = {
-                "train_forward": lambda: L.b200_batch_norm_forward(n, c, s, layout, P(x), P(w), 1, P(b), 1, P(rm), 1, P(rv), 1, 1,
-                                                                   0.1, 1e-5, P(y), P(sm), P(si), P(ws), ws_n, stream),
-                "train_forward_add_relu": lambda: L.b200_batch_norm_forward_fused(n, c, s, layout, P(x), P(w), 1, P(b), 1, P(rm), 1,
+                "train_forward": lambda st=stream: L.b200_batch_norm_forward(n, c, s, layout, P(x), P(w), 1, P(b), 1, P(rm), 1, P(rv), 1, 1,
+                                                                   0.1, 1e-5, P(y), P(sm), P(si), P(ws), ws_n, st),
+                "train_forward_add_relu": lambda st=stream: L.b200_batch_norm_forward_fused(n, c, s, layout, P(x), P(w), 1, P(b), 1, P(rm), 1,
                                                                                   P(rv), 1, 1, 0.1, 1e-5, P(g), 1, P(y), P(sm), P(si),
-                                                                                  P(ws), ws_n, stream),
-                "eval_forward": lambda: L.b200_batch_norm_forward(n, c, s, layout, P(x), P(w), 1, P(b), 1, P(rm), 1, P(rv), 1, 0,
-                                                                  0.1, 1e-5, P(y), P(sm), P(si), P(ws), ws_n, stream),
-                "train_backward": lambda: L.b200_batch_norm_backward(n, c, s, layout, P(g), P(x), P(w), 1, P(sm), 1, P(si), 1, 1,
-                                                                     1e-5, P(dx), P(dw), P(db), P(ws), ws_n, stream),
+                                                                                  P(ws), ws_n, st),
+                "eval_forward": lambda st=stream: L.b200_batch_norm_forward(n, c, s, layout, P(x), P(w), 1, P(b), 1, P(rm), 1, P(rv), 1, 0,
+                                                                  0.1, 1e-5, P(y), P(sm), P(si), P(ws), ws_n, st),
+                "train_backward": lambda st=stream: L.b200_batch_norm_backward(n, c, s, layout, P(g), P(x), P(w), 1, P(sm), 1, P(si), 1, 1,
+                                                                     1e-5, P(dx), P(dw), P(db), P(ws), ws_n, st),
             }
             for name, fn in calls.items():
                 before = b200conv.launch_count()
                 b200conv.check(fn())
                 launches = b200conv.launch_count() - before
                 nbytes = BYTES_PER_ELEMENT[name] * n * c * s
-                for cold in (False, True):
-                    ms = timed(fn, cold)
+                modes = [("warm", lambda: timed(fn, False)), ("cold", lambda: timed(fn, True))]
+                if args.graph:
+                    modes.append(("graph", lambda: timed_in_graph(fn)))
+                for cache, measure in modes:
+                    cold = cache == "cold"
+                    ms = measure()
                     gbs = nbytes / ms / 1e6
                     print(json.dumps({"op": name, "n": n, "c": c, "s": s, "layout": layout_name, "tensor_mb": round(4e-6 * n * c * s, 1),
-                                      "cache": "cold" if cold else "warm", "us": round(ms * 1e3, 1), "gpu_launches": launches,
+                                      "cache": cache, "us": round(ms * 1e3, 1), "gpu_launches": launches,
                                       "kernels": b200conv.last_kernel(),
                                       "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peak, "unit": "GB/s",
                                                    "frac": round(gbs / peak, 3), "peak_source": peak_source}}), flush=True)

@@ -285,6 +285,29 @@ int b200_group_norm_backward(int64_t n, int64_t c, int64_t hw, int64_t groups, c
 int b200_bmm(int64_t batch, int64_t M, int64_t N, int64_t K, const float* A, int64_t sa_b, int64_t sa0, int64_t sa1,
              const float* B, int64_t sb_b, int64_t sb0, int64_t sb1, float* C, int algo, void* stream);
 
+/* ---- scaled dot-product attention ---------------------------------------------------------------- */
+
+/* q [batch, tq, d], k [batch, tk, d], v [batch, tk, dv], out / grad [batch, tq, dv], lse [batch, tq],
+ * mask NULL or additive FP32 [batch, tq, tk]; all contiguous (the reference packs them,
+ * csrc/ops/attention.cpp:21,29).  causal != 0 hides keys j > i.  No dropout.
+ * Workspace: the score matrix (forward) or two of them (backward != 0). */
+size_t b200_attention_workspace(int64_t batch, int64_t tq, int64_t tk, int64_t d, int64_t dv, int backward);
+
+/* out = softmax(q k^T * scale + mask) v and the per-row log-sum-exp.  Replaces attention_forward
+ * (csrc/ops/attention.cpp:16-23, shader sdpa_training.comp mode 0).  Composed from b200_bmm and one
+ * row-softmax kernel; the scores are materialised in the workspace. */
+int b200_attention_forward(int64_t batch, int64_t tq, int64_t tk, int64_t d, int64_t dv, const float* q, const float* k,
+                           const float* v, const float* mask, int causal, float scale, float* out, float* lse, void* workspace,
+                           size_t workspace_bytes, void* stream);
+
+/* dq, dk, dvalue from the output gradient, the saved output and log-sum-exp.  Replaces
+ * attention_backward (csrc/ops/attention.cpp:24-34, sdpa_training.comp modes 1 and 2); the mask
+ * gradient the reference also returns is not produced. */
+int b200_attention_backward(int64_t batch, int64_t tq, int64_t tk, int64_t d, int64_t dv, const float* grad, const float* q,
+                            const float* k, const float* v, const float* mask, const float* out, const float* lse, int causal,
+                            float scale, float* dq, float* dk, float* dvalue, void* workspace, size_t workspace_bytes,
+                            void* stream);
+
 /* Device-side health word.  The tcgen05 kernels bound every wait on an mbarrier; a wait that
  * gives up records (code << 24 | CTA index) here, frees its tensor memory and returns, so the
  * context stays usable.  *status = 0 means no wait ever gave up.  Synchronises the device.

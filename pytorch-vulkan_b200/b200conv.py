@@ -106,6 +106,11 @@ SIGNATURES = {
                                          c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
     "b200_bmm": (c_int, [c_int64] * 4 + [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64, c_void_p,
                          c_int, c_void_p]),
+    "b200_attention_workspace": (c_size_t, [c_int64] * 5 + [c_int]),
+    "b200_attention_forward": (c_int, [c_int64] * 5 + [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p,
+                                       c_void_p, c_size_t, c_void_p]),
+    "b200_attention_backward": (c_int, [c_int64] * 5 + [c_void_p] * 7 + [c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p,
+                                        c_size_t, c_void_p]),
     "b200_device_status": (c_int, [POINTER(c_int), c_int]),
     "b200_launch_count": (c_uint64, []),
     "b200_last_kernel": (c_char_p, []),
@@ -499,3 +504,31 @@ def bmm(a, b, algo="auto"):
     out = DeviceBuffer(4 * batch * M * N)
     check(lib().b200_bmm(batch, M, N, K, av.ptr, *av.strides, bv.ptr, *bv.strides, out.ptr, _algo(algo), None))
     return out.to_numpy((batch, M, N))
+
+
+def attention_forward(q, k, v, mask=None, causal=False, scale=None):
+    """(out, lse) = softmax(q k^T * scale + mask) v for q [batch, tq, d], k [batch, tk, d], v [batch, tk, dv]."""
+    batch, tq, d = q.shape
+    tk, dv = k.shape[1], v.shape[2]
+    scale = float(scale) if scale is not None else 1.0 / float(np.sqrt(d))
+    qv, kv, vv, mv = _dense(q), _dense(k), _dense(v), _dense(mask)
+    out, lse = DeviceBuffer(4 * batch * tq * dv), DeviceBuffer(4 * batch * tq)
+    ws_n = int(lib().b200_attention_workspace(batch, tq, tk, d, dv, 0))
+    ws = DeviceBuffer(ws_n)
+    check(lib().b200_attention_forward(batch, tq, tk, d, dv, qv.ptr, kv.ptr, vv.ptr, mv.ptr if mv else None, int(bool(causal)),
+                                       scale, out.ptr, lse.ptr, ws.ptr, ws_n, None))
+    return out.to_numpy((batch, tq, dv)), lse.to_numpy((batch, tq))
+
+
+def attention_backward(grad, q, k, v, out, lse, mask=None, causal=False, scale=None):
+    """(dq, dk, dv) of attention_forward."""
+    batch, tq, d = q.shape
+    tk, dv = k.shape[1], v.shape[2]
+    scale = float(scale) if scale is not None else 1.0 / float(np.sqrt(d))
+    gv, qv, kv, vv, ov, lv, mv = (_dense(a) for a in (grad, q, k, v, out, lse, mask))
+    dq, dk, dvb = DeviceBuffer(4 * batch * tq * d), DeviceBuffer(4 * batch * tk * d), DeviceBuffer(4 * batch * tk * dv)
+    ws_n = int(lib().b200_attention_workspace(batch, tq, tk, d, dv, 1))
+    ws = DeviceBuffer(ws_n)
+    check(lib().b200_attention_backward(batch, tq, tk, d, dv, gv.ptr, qv.ptr, kv.ptr, vv.ptr, mv.ptr if mv else None, ov.ptr, lv.ptr,
+                                        int(bool(causal)), scale, dq.ptr, dk.ptr, dvb.ptr, ws.ptr, ws_n, None))
+    return dq.to_numpy((batch, tq, d)), dk.to_numpy((batch, tk, d)), dvb.to_numpy((batch, tk, dv))

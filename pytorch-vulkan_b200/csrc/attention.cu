@@ -1,0 +1,201 @@
+// Scaled dot-product attention, forward and backward, for contiguous FP32 [batch, tokens, dim]
+// operands.  Replaces attention_forward / attention_backward of the reference
+// (csrc/ops/attention.cpp:16-34) and its sdpa_training shader, without dropout.
+//
+// The products run on the GEMM kernels of this library (b200_bmm: tcgen05 from 128x64x32, CUDA
+// cores below); the score matrix is materialised in the caller's workspace, so this is the
+// composed form of attention, not a single fused pass:
+//   forward   S = Q K^T;  P = softmax(S * scale + mask) row by row, in place, with the
+//             log-sum-exp kept per row;  O = P V
+//   backward  P again from S and the saved log-sum-exp;  dV = P^T dO;  dP = dO V^T;
+//             dS = P (dP - rowsum(dO O)) * scale in place;  dQ = dS K;  dK = dS^T Q
+// The two elementwise kernels here are bound by HBM traffic over the [tokens, tokens] matrices.
+// Masking as in the shader (sdpa_training.comp:16): causal hides keys j > i; an additive float mask
+// of the scores' shape; a row with every key hidden has log-sum-exp -inf and probability 0.
+#include <cmath>
+
+#include "common.cuh"
+
+namespace b200 {
+namespace {
+
+constexpr int kThreads = 256;
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_add(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+// Block-wide reduction of one value per thread; every thread gets the result.
+template <bool MAX>
+__device__ __forceinline__ float block_reduce(float v, float* scratch) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  v = MAX ? warp_max(v) : warp_add(v);
+  __syncthreads();  // scratch may still be read from the previous reduction
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  v = lane < kThreads / 32 ? scratch[lane] : (MAX ? -INFINITY : 0.f);
+  return MAX ? warp_max(v) : warp_add(v);
+}
+
+__device__ __forceinline__ float masked_score(float s, float scale, const float* mask_row, int i, int j, int causal) {
+  if (causal && j > i) return -INFINITY;
+  s *= scale;
+  return mask_row ? s + __ldg(mask_row + j) : s;
+}
+
+// One CTA per score row: s[j] <- softmax_j(s[j] * scale + mask), lse[row] <- log sum exp.
+__global__ void __launch_bounds__(kThreads) softmax_rows_kernel(float* __restrict__ scores, const float* __restrict__ mask, int tq, int tk,
+                                                                 float scale, int causal, float* __restrict__ lse) {
+  __shared__ float scratch[kThreads / 32];
+  const long long row = blockIdx.x;
+  const int i = (int)(row % tq);
+  float* s = scores + row * tk;
+  const float* mrow = mask ? mask + row * tk : nullptr;
+  float mx = -INFINITY;
+  for (int j = threadIdx.x; j < tk; j += kThreads) mx = fmaxf(mx, masked_score(s[j], scale, mrow, i, j, causal));
+  mx = block_reduce<true>(mx, scratch);
+  float sum = 0.f;
+  if (mx > -INFINITY)
+    for (int j = threadIdx.x; j < tk; j += kThreads) sum += expf(masked_score(s[j], scale, mrow, i, j, causal) - mx);
+  sum = block_reduce<false>(sum, scratch);
+  const float logsum = sum > 0.f ? mx + logf(sum) : -INFINITY;
+  if (threadIdx.x == 0) lse[row] = logsum;
+  const bool dead = !(logsum > -INFINITY);
+  for (int j = threadIdx.x; j < tk; j += kThreads)
+    s[j] = dead ? 0.f : expf(masked_score(s[j], scale, mrow, i, j, causal) - logsum);
+}
+
+// Backward, first elementwise step: s[j] <- P[j] = exp(s[j] * scale + mask - lse[row]).
+__global__ void __launch_bounds__(kThreads) probabilities_kernel(float* __restrict__ scores, const float* __restrict__ mask, int tq, int tk,
+                                                                  float scale, int causal, const float* __restrict__ lse) {
+  const long long row = blockIdx.x;
+  const int i = (int)(row % tq);
+  float* s = scores + row * tk;
+  const float* mrow = mask ? mask + row * tk : nullptr;
+  const float logsum = __ldg(lse + row);
+  const bool dead = !(logsum > -INFINITY);
+  for (int j = threadIdx.x; j < tk; j += kThreads)
+    s[j] = dead ? 0.f : expf(masked_score(s[j], scale, mrow, i, j, causal) - logsum);
+}
+
+// Backward, second step: dp[j] <- dS[j] = P[j] * (dp[j] - delta) * scale with delta = sum_e dO[e] O[e]
+// of the row (sdpa_training.comp:38).
+__global__ void __launch_bounds__(kThreads) score_gradient_kernel(float* __restrict__ dp, const float* __restrict__ p,
+                                                                   const float* __restrict__ grad, const float* __restrict__ out, int tk,
+                                                                   int dv, float scale) {
+  __shared__ float scratch[kThreads / 32];
+  const long long row = blockIdx.x;
+  float delta = 0.f;
+  for (int e = threadIdx.x; e < dv; e += kThreads) delta = fmaf(__ldg(grad + row * dv + e), __ldg(out + row * dv + e), delta);
+  delta = block_reduce<false>(delta, scratch);
+  float* d = dp + row * tk;
+  const float* pr = p + row * tk;
+  for (int j = threadIdx.x; j < tk; j += kThreads) d[j] = pr[j] * (d[j] - delta) * scale;
+}
+
+__global__ void fill_kernel(float* p, float value, long long n) {
+  const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (i < n) p[i] = value;
+}
+
+struct AttentionShape {
+  int64_t batch, tq, tk, d, dv;
+  size_t score_bytes;
+};
+
+int make_shape(int64_t batch, int64_t tq, int64_t tk, int64_t d, int64_t dv, AttentionShape* out) {
+  if (batch < 0 || tq < 0 || tk < 0 || d < 0 || dv < 0) return fail(B200_EINVAL, "attention dimensions mismatch");
+  if (tk > INT32_MAX || tq > INT32_MAX || dv > INT32_MAX || (tk > 0 && batch * tq > (int64_t)UINT32_MAX / tk))
+    return fail(B200_ERANGE, "attention score indexing exceeds uint32");
+  *out = {batch, tq, tk, d, dv, ((size_t)(batch * tq * tk) * sizeof(float) + 255) & ~(size_t)255};
+  return B200_OK;
+}
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+size_t b200_attention_workspace(int64_t batch, int64_t tq, int64_t tk, int64_t d, int64_t dv, int backward) {
+  AttentionShape sh;
+  if (make_shape(batch, tq, tk, d, dv, &sh)) return 0;
+  return sh.score_bytes * (backward ? 2 : 1);
+}
+
+int b200_attention_forward(int64_t batch, int64_t tq, int64_t tk, int64_t d, int64_t dv, const float* q, const float* k,
+                           const float* v, const float* mask, int causal, float scale, float* out, float* lse, void* workspace,
+                           size_t workspace_bytes, void* stream) {
+  if (int rc = ensure_init()) return rc;
+  AttentionShape sh;
+  if (int rc = make_shape(batch, tq, tk, d, dv, &sh)) return rc;
+  const int64_t rows = batch * tq;
+  if (rows == 0) return B200_OK;
+  if (!q || !out || !lse || (tk > 0 && (!k || !v))) return fail(B200_EINVAL, "attention: null tensor");
+  cudaStream_t st = (cudaStream_t)stream;
+  if (tk == 0) {  // no keys at all: zero output, log-sum-exp of an empty set (attention.cpp:20)
+    if (dv) B200_CUDA(cudaMemsetAsync(out, 0, (size_t)rows * dv * sizeof(float), st));
+    fill_kernel<<<(unsigned)((rows + kThreads - 1) / kThreads), kThreads, 0, st>>>(lse, -INFINITY, rows);
+    count_launch();
+    return launch_check("fill_kernel");
+  }
+  if (!workspace || workspace_bytes < sh.score_bytes) return fail(B200_EWORKSPACE, "attention: workspace smaller than b200_attention_workspace()");
+  float* scores = (float*)workspace;
+  // S[b] = Q[b] K[b]^T: the right-hand matrix is K read with its strides swapped
+  if (int rc = b200_bmm(batch, tq, tk, d, q, tq * d, d, 1, k, tk * d, 1, d, scores, B200_ALGO_AUTO, stream)) return rc;
+  softmax_rows_kernel<<<(unsigned)rows, kThreads, 0, st>>>(scores, mask, (int)tq, (int)tk, scale, causal, lse);
+  count_launch();
+  if (int rc = launch_check("softmax_rows_kernel")) return rc;
+  if (dv == 0) return B200_OK;
+  const int rc = b200_bmm(batch, tq, dv, tk, scores, tq * tk, tk, 1, v, tk * dv, dv, 1, out, B200_ALGO_AUTO, stream);
+  note_kernel("attention_forward: bmm + softmax_rows + bmm");
+  return rc;
+}
+
+int b200_attention_backward(int64_t batch, int64_t tq, int64_t tk, int64_t d, int64_t dv, const float* grad, const float* q,
+                            const float* k, const float* v, const float* mask, const float* out, const float* lse, int causal,
+                            float scale, float* dq, float* dk, float* dvalue, void* workspace, size_t workspace_bytes,
+                            void* stream) {
+  if (int rc = ensure_init()) return rc;
+  AttentionShape sh;
+  if (int rc = make_shape(batch, tq, tk, d, dv, &sh)) return rc;
+  if (!dq || !dk || !dvalue) return fail(B200_EINVAL, "attention backward: null gradient");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t rows = batch * tq;
+  if (rows == 0 || tk == 0 || d == 0 || dv == 0) {  // nothing flows: all gradients are zero (attention.cpp:28)
+    if (batch * tq * d) B200_CUDA(cudaMemsetAsync(dq, 0, (size_t)(batch * tq * d) * sizeof(float), st));
+    if (batch * tk * d) B200_CUDA(cudaMemsetAsync(dk, 0, (size_t)(batch * tk * d) * sizeof(float), st));
+    if (batch * tk * dv) B200_CUDA(cudaMemsetAsync(dvalue, 0, (size_t)(batch * tk * dv) * sizeof(float), st));
+    return B200_OK;
+  }
+  if (!grad || !q || !k || !v || !out || !lse) return fail(B200_EINVAL, "attention backward: null tensor");
+  if (!workspace || workspace_bytes < 2 * sh.score_bytes)
+    return fail(B200_EWORKSPACE, "attention: workspace smaller than b200_attention_workspace()");
+  float* p = (float*)workspace;
+  float* dp = (float*)((char*)workspace + sh.score_bytes);
+  if (int rc = b200_bmm(batch, tq, tk, d, q, tq * d, d, 1, k, tk * d, 1, d, p, B200_ALGO_AUTO, stream)) return rc;
+  probabilities_kernel<<<(unsigned)rows, kThreads, 0, st>>>(p, mask, (int)tq, (int)tk, scale, causal, lse);
+  count_launch();
+  if (int rc = launch_check("probabilities_kernel")) return rc;
+  // dV[b] = P[b]^T dO[b]
+  if (int rc = b200_bmm(batch, tk, dv, tq, p, tq * tk, 1, tk, grad, tq * dv, dv, 1, dvalue, B200_ALGO_AUTO, stream)) return rc;
+  // dP[b] = dO[b] V[b]^T
+  if (int rc = b200_bmm(batch, tq, tk, dv, grad, tq * dv, dv, 1, v, tk * dv, 1, dv, dp, B200_ALGO_AUTO, stream)) return rc;
+  score_gradient_kernel<<<(unsigned)rows, kThreads, 0, st>>>(dp, p, grad, out, (int)tk, (int)dv, scale);
+  count_launch();
+  if (int rc = launch_check("score_gradient_kernel")) return rc;
+  // dQ[b] = dS[b] K[b];  dK[b] = dS[b]^T Q[b]
+  if (int rc = b200_bmm(batch, tq, d, tk, dp, tq * tk, tk, 1, k, tk * d, d, 1, dq, B200_ALGO_AUTO, stream)) return rc;
+  const int rc = b200_bmm(batch, tk, d, tq, dp, tq * tk, 1, tk, q, tq * d, d, 1, dk, B200_ALGO_AUTO, stream);
+  note_kernel("attention_backward: bmm x5 + probabilities + score_gradient");
+  return rc;
+}
+
+}  // extern "C"

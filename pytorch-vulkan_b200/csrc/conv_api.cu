@@ -328,6 +328,11 @@ int b200_bmm(int64_t batch, int64_t M, int64_t N, int64_t K, const float* A, int
   if (batch < 0) return fail(B200_EINVAL, "bmm: negative batch");
   if (batch == 0 || M == 0 || N == 0) return B200_OK;
   if (batch * M > UINT32_MAX / N) return fail(B200_ERANGE, "bmm: result too large");
+  if (K == 0) {  // empty contraction: zeros (bmm.cpp:50-54)
+    if (!C) return fail(B200_EINVAL, "bmm: null matrix");
+    B200_CUDA(cudaMemsetAsync(C, 0, (size_t)(batch * M * N) * sizeof(float), (cudaStream_t)stream));
+    return B200_OK;
+  }
   // one right-hand matrix for every batch and left-hand rows at one constant stride: a single
   // product with batch * M rows
   if ((sb_b == 0 || batch == 1) && (batch == 1 || sa_b == M * sa0))

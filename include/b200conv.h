@@ -280,8 +280,10 @@ int b200_group_norm_backward(int64_t n, int64_t c, int64_t hw, int64_t groups, c
 
 /* C[b] (contiguous [batch, M, N]) = A[b] * B[b]; A and B arbitrary 3-D element strides (a zero batch
  * stride broadcasts one matrix).  Replaces bmm_impl (csrc/ops/bmm.cpp:16-68, shader bmm_strided.comp).
- * K == 0 gives zeros, as there (:50-54).  One b200_gemm per batch, or a single product when the
- * right-hand matrix is shared and the left-hand rows lie at one stride; there is no batched kernel. */
+ * K == 0 gives zeros, as there (:50-54).  From 64 rows, 16 columns and a contraction of 16 every
+ * batch runs in ONE launch of the tcgen05 GEMM kernel (the batch rides on its group dimension); a
+ * right-hand matrix shared by all batches with left-hand rows at one stride folds into a single
+ * product; smaller shapes are one b200_gemm per batch. */
 int b200_bmm(int64_t batch, int64_t M, int64_t N, int64_t K, const float* A, int64_t sa_b, int64_t sa0, int64_t sa1,
              const float* B, int64_t sb_b, int64_t sb0, int64_t sb1, float* C, int algo, void* stream);
 

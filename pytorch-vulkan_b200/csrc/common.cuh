@@ -97,6 +97,8 @@ int tc_forward(const ConvGeom& g, View4 x, View4 w, const float* bias, long long
                void* ws, size_t ws_bytes, cudaStream_t st);
 int tc_dinput(const ConvGeom& g, View4 dy, View4 w, float* dx, void* ws, size_t ws_bytes, cudaStream_t st);
 int tc_dweight(const ConvGeom& g, View4 x, View4 dy, float* dw, void* ws, size_t ws_bytes, cudaStream_t st);
+int tc_bmm(long long batch, long long M, long long N, long long K, const float* A, long long sa_b, long long sa0, long long sa1,
+           const float* B, long long sb_b, long long sb0, long long sb1, float* C, cudaStream_t st);
 int tc_gemm(long long M, long long N, long long K, const float* A, long long sa0, long long sa1, const float* B,
             long long sb0, long long sb1, const float* bias, float alpha, float beta, float* C, cudaStream_t st);
 
@@ -108,10 +110,14 @@ struct StripPostOps {
   View4 residual{nullptr, 0, 0, 0, 0};
   int relu = 0;
 };
+// Per-group element offsets that turn the grouped 1x1 convolution into a batched GEMM (tc_bmm).
+struct StripBatch {
+  long long act_group_extra = 0, w_group_extra = 0, out_pitch = 0, out_group = 0;
+};
 int strip_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* bias, long long bias_stride, float* out,
                void* ws, size_t ws_bytes, cudaStream_t st, bool rowmajor = false, float alpha = 1.f, float beta = 1.f,
                const float* staged_images = nullptr,  // images already written for strip_column_tile()
-               const StripPostOps* post = nullptr);
+               const StripPostOps* post = nullptr, const StripBatch* batch = nullptr);
 // elementwise residual add / ReLU on a contiguous NCHW result (conv_simt.cu), for candidates without a fused epilogue
 int post_ops_nchw(float* y, const ConvGeom& g, const StripPostOps& post, cudaStream_t st);
 // y[n][c][plane] += bias[c] on a contiguous result (conv_simt.cu)

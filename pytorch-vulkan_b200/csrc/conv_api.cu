@@ -337,6 +337,13 @@ int b200_bmm(int64_t batch, int64_t M, int64_t N, int64_t K, const float* A, int
   // product with batch * M rows
   if ((sb_b == 0 || batch == 1) && (batch == 1 || sa_b == M * sa0))
     return b200_gemm(batch * M, N, K, A, sa0, sa1, B, sb0, sb1, nullptr, 1.f, 0.f, C, algo, stream);
+  // every batch in one launch pair on the tcgen05 kernel (the batch rides on its group dimension)
+  // (a loop of small products is the alternative, so the batched kernel is taken from smaller shapes than b200_gemm's)
+  if ((algo == B200_ALGO_TC || (algo == B200_ALGO_AUTO && M >= 64 && N >= 16 && K >= 16)) && A && B && C) {
+    note_kernel("tc_bmm");
+    const int rc = tc_bmm(batch, M, N, K, A, sa_b, sa0, sa1, B, sb_b, sb0, sb1, C, (cudaStream_t)stream);
+    if (rc != B200_EUNSUPPORTED) return rc;
+  }
   for (int64_t b = 0; b < batch; ++b)
     if (int rc = b200_gemm(M, N, K, A ? A + b * sa_b : nullptr, sa0, sa1, B ? B + b * sb_b : nullptr, sb0, sb1, nullptr, 1.f, 0.f,
                            C + b * M * N, algo, stream))

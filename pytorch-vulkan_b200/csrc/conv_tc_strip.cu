@@ -85,6 +85,9 @@ struct StripArgs {
   int phase_on_n;         // 1 in the dInput arrangement
   int tiles_pp;           // column tiles per phase (dInput), else tiles_n
   int kc, nc, out_channels;
+  // batched GEMM (groups used as the batch): extra element offsets per group on top of the grouped
+  // convolution's own (group * kc channels in, group * nc columns out); 0 / out_channels / nc otherwise
+  long long act_group_extra, out_pitch, out_group;
   int cb_per_phase;       // kc / 32
   int cblocks;            // strips per tile: forward n_phase * cb_per_phase, dInput cb_per_phase
   int images_per_tile;    // forward: weight stages per tile = cb_per_phase * taps_total
@@ -335,7 +338,7 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
     const int aw = warp - EPI_WARPS;
     const int chunks = (a.strip_rows + 31) / 32;
     const bool vec_layout = a.act.s1 == 1 && a.kc % 4 == 0 && ((reinterpret_cast<uintptr_t>(a.act.ptr) & 15) == 0) &&
-                        (a.act.s0 % 4 == 0) && (a.act.s2 % 4 == 0) && (a.act.s3 % 4 == 0);
+                        (a.act.s0 % 4 == 0) && (a.act.s2 % 4 == 0) && (a.act.s3 % 4 == 0) && (a.act_group_extra % 4 == 0);
     const bool chunked_layout = vec_layout && a.act.s3 < 256;  // eight lanes per pixel (see below)
     const int s1 = (int)a.act.s1;
     const int my_units = a.units > (int)blockIdx.x ? (a.units - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
@@ -372,7 +375,8 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
         const int y = (int)a.row_div.div((uint32_t)rem), x = rem - y * row_pitch;
         const int iy = a.phase_on_n ? y : y * a.sph + ctrl->ph_a[phase], ix = a.phase_on_n ? x : x * a.spw + ctrl->ph_b[phase];
         ok = y < a.H && x < a.W && iy < a.act_h && ix < a.act_w;
-        src += n * a.act.s0 + ((long long)group * a.kc + cbl * KBLK) * a.act.s1 + (long long)iy * a.act.s2 + (long long)ix * a.act.s3;
+        src += n * a.act.s0 + ((long long)group * a.kc + cbl * KBLK) * a.act.s1 + (long long)iy * a.act.s2 + (long long)ix * a.act.s3 +
+               (long long)group * a.act_group_extra;
       }
       float v[KBLK];
       if (chunked) {
@@ -482,7 +486,7 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
         if (a.phase_on_n) { y = y * a.osh + ctrl->ph_a[phase_n]; x = x * a.osw + ctrl->ph_b[phase_n]; }
         ok = ok && y < a.out_h && x < a.out_w;
         res_off = n * a.res.s0 + ((long long)group * a.nc + n0) * a.res.s1 + (long long)y * a.res.s2 + (long long)x * a.res.s3;
-        obase = a.out_rowmajor ? (((n * a.out_h + y) * a.out_w + x) * (long long)a.out_channels + (long long)group * a.nc + n0)
+        obase = a.out_rowmajor ? (((n * a.out_h + y) * a.out_w + x) * a.out_pitch + (long long)group * a.out_group + n0)
                                : (((n * a.out_channels + (long long)group * a.nc + n0) * a.out_h + y) * a.out_w + x);
       }
       const long long col_stride = a.out_rowmajor ? 1 : (long long)a.out_h * a.out_w;
@@ -594,7 +598,8 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
 // ordered as the main loop consumes them: [group][n_tile][phase][channel block][tap of the phase],
 // so a weight stage of the main kernel is one bulk copy from a running pointer.
 __global__ void __launch_bounds__(256) stage_weights_kernel(ConvGeom g, View4 w, int is_dx, int bn, int tiles_pp,
-                                                            TapTable tt, float* __restrict__ out, long long total) {
+                                                            TapTable tt, float* __restrict__ out, long long total,
+                                                            long long w_group_extra) {
   // let the convolution kernel behind this one start its prologue and its activation strips now
   asm volatile("griddepcontrol.launch_dependents;");
   const long long i = blockIdx.x * 256ll + threadIdx.x;
@@ -631,7 +636,7 @@ __global__ void __launch_bounds__(256) stage_weights_kernel(ConvGeom g, View4 w,
   float v = 0.f;
   if (r < nc && c < kc) {  // rows beyond the column count and channels beyond a ragged last block are zero
     const int co = is_dx ? c : r, ci = is_dx ? r : c;
-    v = w.ptr[((long long)grp * g.cog + co) * w.s0 + ci * w.s1 + tt.ky[tap] * w.s2 + tt.kx[tap] * w.s3];
+    v = w.ptr[((long long)grp * g.cog + co) * w.s0 + ci * w.s1 + tt.ky[tap] * w.s2 + tt.kx[tap] * w.s3 + grp * w_group_extra];
   }
   float hi, lo;
   split_tf32(v, hi, lo);
@@ -780,7 +785,7 @@ static int launch_strip(const tcs::StripArgs& a, int grid, int smem, cudaStream_
 
 int strip_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* bias, long long bias_stride, float* out,
                void* ws, size_t ws_bytes, cudaStream_t st, bool rowmajor, float alpha, float beta, const float* staged_images,
-               const StripPostOps* post) {
+               const StripPostOps* post, const StripBatch* batch) {
   using namespace tcs;
   const StripPlan plan = plan_strip(g, is_dx);
   if (!plan.ok) return fail(B200_EUNSUPPORTED, "strip kernel does not take this geometry");
@@ -795,7 +800,8 @@ int strip_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* b
     if (!ws || ws_bytes < 2 * sizeof(float) * (size_t)wcount || (reinterpret_cast<uintptr_t>(ws) & 15))
       return fail(B200_EWORKSPACE, "tcgen05 convolution needs a 16-byte aligned workspace of %zu bytes (got %zu)",
                   2 * sizeof(float) * (size_t)wcount, ws_bytes);
-    stage_weights_kernel<<<(unsigned)div_up64(wcount, 256), 256, 0, st>>>(g, w, is_dx ? 1 : 0, plan.bn, tiles_pp, plan.tt, (float*)ws, wcount);
+    stage_weights_kernel<<<(unsigned)div_up64(wcount, 256), 256, 0, st>>>(g, w, is_dx ? 1 : 0, plan.bn, tiles_pp, plan.tt, (float*)ws, wcount,
+                                                                          batch ? batch->w_group_extra : 0);
     count_launch();
     if (int rc = launch_check("stage_weights_kernel")) return rc;
     wp = (const float*)ws;
@@ -805,7 +811,8 @@ int strip_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* b
   {  // the kernel forms element offsets inside the activation tensor in 32 bits
     const long long an = g.n, ac = is_dx ? g.cout : g.cin, ah = is_dx ? g.oh : g.h, aw = is_dx ? g.ow : g.w;
     const long long span = (an - 1) * std::llabs(act.s0) + (ac - 1) * std::llabs(act.s1) +
-                           (ah - 1) * std::llabs(act.s2) + (aw - 1) * std::llabs(act.s3);
+                           (ah - 1) * std::llabs(act.s2) + (aw - 1) * std::llabs(act.s3) +
+                           (batch ? (g.groups - 1) * std::llabs(batch->act_group_extra) : 0);
     if (span > 2147483647ll - 64 * std::llabs(act.s1))
       return fail(B200_EUNSUPPORTED, "strip kernel: activation tensor too large for 32-bit element offsets");
   }
@@ -821,6 +828,9 @@ int strip_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* b
   a.kc = kc;
   a.nc = nc;
   a.out_channels = is_dx ? g.cin : g.cout;
+  a.act_group_extra = batch ? batch->act_group_extra : 0;
+  a.out_pitch = batch ? batch->out_pitch : a.out_channels;
+  a.out_group = batch ? batch->out_group : nc;
   a.cb_per_phase = cpp;
   a.cblocks = (is_dx ? 1 : plan.tt.n_phase) * a.cb_per_phase;
   a.images_per_tile = a.cb_per_phase * plan.tt.taps_total;
@@ -848,7 +858,8 @@ int strip_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* b
   if (post && !is_dx) { a.res = post->residual; a.relu = post->relu; }
   a.out_rowmajor = rowmajor ? 1 : 0;
   a.alpha = alpha; a.beta = beta;
-  a.out_vec4 = rowmajor && a.out_channels % 4 == 0 && plan.bn % 4 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 && a.nc % 4 == 0;
+  a.out_vec4 = rowmajor && a.out_pitch % 4 == 0 && a.out_group % 4 == 0 && plan.bn % 4 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 &&
+               a.nc % 4 == 0;
   a.status = device_status_word();
   if (!a.status) return fail(B200_ECUDA, "device status word is not allocated");
   static unsigned long long* prof_buf = nullptr;
@@ -897,6 +908,32 @@ int tc_gemm(long long M, long long N, long long K, const float* A, long long sa0
   if (int rc = b200_malloc(&ws, ws_bytes, st)) return rc;
   if (!bias || beta == 0.f) { bias = nullptr; beta = 0.f; }
   const int rc = strip_conv(g, false, act, wv, bias, 1, C, ws, ws_bytes, st, true, alpha, beta);
+  b200_free(ws, st);
+  return rc;
+}
+
+// C[b] = A[b] * B[b] for every batch in ONE launch pair: the batch rides on the kernel's group
+// dimension (each group has its own weight images and its own block of reduction channels), with the
+// three per-group offsets of StripBatch standing in for the grouped convolution's channel arithmetic.
+int tc_bmm(long long batch, long long M, long long N, long long K, const float* A, long long sa_b, long long sa0, long long sa1,
+           const float* B, long long sb_b, long long sb0, long long sb1, float* C, cudaStream_t st) {
+  if (K < 16 || N < 16 || M > 2147483647ll || batch * N > 2147483647ll || batch * K > 2147483647ll || batch > 65535)
+    return fail(B200_EUNSUPPORTED, "tcgen05 batched GEMM is incompatible with this shape (needs K >= 16 and N >= 16)");
+  ConvGeom g{};
+  g.n = 1; g.cin = (int)(batch * K); g.cout = (int)(batch * N); g.h = 1; g.w = (int)M; g.kh = g.kw = 1; g.oh = 1; g.ow = (int)M;
+  g.sh = g.sw = 1; g.ph = g.pw = 0; g.dh = g.dw = 1; g.groups = (int)batch; g.cig = (int)K; g.cog = (int)N;
+  if (!tcs::plan_strip(g, false).ok) return fail(B200_EUNSUPPORTED, "tcgen05 batched GEMM is incompatible with this shape");
+  const View4 act{A, 0, sa1, 0, sa0};   // [n=1][c=(b,k)][h=1][w=m]
+  const View4 wv{B, sb1, sb0, 0, 0};    // [co=(b,n)][ci=k][1][1]
+  StripBatch sb;
+  sb.act_group_extra = sa_b - K * sa1;  // group b starts b*K channels in: b*K*sa1 of the way to A[b]
+  sb.w_group_extra = sb_b - N * sb1;
+  sb.out_pitch = N;
+  sb.out_group = M * N;
+  void* ws = nullptr;
+  const size_t ws_bytes = strip_workspace(g, B200_PHASE_FORWARD);
+  if (int rc = b200_malloc(&ws, ws_bytes, st)) return rc;
+  const int rc = strip_conv(g, false, act, wv, nullptr, 1, C, ws, ws_bytes, st, true, 1.f, 0.f, nullptr, nullptr, &sb);
   b200_free(ws, st);
   return rc;
 }

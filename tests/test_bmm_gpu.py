@@ -47,6 +47,19 @@ def test_bmm_through_the_c_abi(shape, style):
     assert oracle.rel_l2(got, want) <= GATE
 
 
+@pytest.mark.parametrize("shape", [(2, 8, 16, 32), (4, 16, 32, 16), (8, 32, 32, 32), (3, 256, 96, 128), (16, 128, 64, 128),
+                                   (5, 130, 40, 72), (64, 128, 64, 64)], ids=lambda s: "x".join(map(str, s)))
+@pytest.mark.parametrize("style", STYLES)
+def test_batched_tensor_core_kernel(shape, style):
+    # every batch in one launch pair: forced onto the tcgen05 kernel, also for the strided views
+    batch, m, k, n = shape
+    a, b = _views(style, batch, m, k, n, 11 + sum(shape))
+    got = b200conv.bmm(a, b, algo="tc")
+    assert b200conv.last_kernel() in ("tc_bmm", "tc_gemm")   # tc_gemm: a shared right-hand matrix folds into one product
+    assert oracle.rel_l2(got, np.matmul(a.astype(np.float64), b.astype(np.float64))) <= GATE
+    assert b200conv.device_status() == 0
+
+
 def test_empty_contraction_gives_zeros():
     got = b200conv.bmm(np.zeros((3, 5, 0), np.float32), np.zeros((3, 0, 4), np.float32))
     np.testing.assert_array_equal(got, np.zeros((3, 5, 4), np.float32))

@@ -71,6 +71,56 @@ __global__ void __launch_bounds__(kThreads) softmax_rows_kernel(float* __restric
     s[j] = dead ? 0.f : expf(masked_score(s[j], scale, mrow, i, j, causal) - logsum);
 }
 
+// The same for rows of at most 4096 keys that are whole 16-byte groups: the row is read once into
+// registers (four groups of four per thread), reduced there and written once.
+__global__ void __launch_bounds__(kThreads) softmax_rows_resident_kernel(float* __restrict__ scores, const float* __restrict__ mask,
+                                                                          int tq, int tk, float scale, int causal,
+                                                                          float* __restrict__ lse) {
+  __shared__ float scratch[kThreads / 32];
+  const long long row = blockIdx.x;
+  const int i = (int)(row % tq), quads = tk >> 2;
+  float4* s4 = reinterpret_cast<float4*>(scores + row * tk);
+  const float4* m4 = mask ? reinterpret_cast<const float4*>(mask + row * tk) : nullptr;
+  float v[16];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int q = threadIdx.x + u * kThreads;
+    float4 a = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+    if (q < quads) {
+      a = s4[q];
+      const float4 m = m4 ? __ldg(m4 + q) : make_float4(0.f, 0.f, 0.f, 0.f);
+      const int j = 4 * q;
+      a.x = (causal && j > i) ? -INFINITY : a.x * scale + m.x;
+      a.y = (causal && j + 1 > i) ? -INFINITY : a.y * scale + m.y;
+      a.z = (causal && j + 2 > i) ? -INFINITY : a.z * scale + m.z;
+      a.w = (causal && j + 3 > i) ? -INFINITY : a.w * scale + m.w;
+    }
+    v[4 * u] = a.x, v[4 * u + 1] = a.y, v[4 * u + 2] = a.z, v[4 * u + 3] = a.w;
+    mx = fmaxf(fmaxf(mx, fmaxf(a.x, a.y)), fmaxf(a.z, a.w));
+  }
+  mx = block_reduce<true>(mx, scratch);
+  float sum = 0.f;
+  if (mx > -INFINITY) {
+#pragma unroll
+    for (int e = 0; e < 16; ++e) {
+      v[e] = expf(v[e] - mx);  // exp(-inf) = 0 for hidden keys and for the slots beyond the row
+      sum += v[e];
+    }
+  }
+  sum = block_reduce<false>(sum, scratch);
+  const bool dead = !(sum > 0.f);
+  if (threadIdx.x == 0) lse[row] = dead ? -INFINITY : mx + logf(sum);
+  const float inv = dead ? 0.f : 1.f / sum;
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int q = threadIdx.x + u * kThreads;
+    if (q < quads)
+      s4[q] = dead ? make_float4(0.f, 0.f, 0.f, 0.f)
+                   : make_float4(v[4 * u] * inv, v[4 * u + 1] * inv, v[4 * u + 2] * inv, v[4 * u + 3] * inv);
+  }
+}
+
 // Backward, first elementwise step: s[j] <- P[j] = exp(s[j] * scale + mask - lse[row]).
 __global__ void __launch_bounds__(kThreads) probabilities_kernel(float* __restrict__ scores, const float* __restrict__ mask, int tq, int tk,
                                                                   float scale, int causal, const float* __restrict__ lse) {
@@ -80,6 +130,21 @@ __global__ void __launch_bounds__(kThreads) probabilities_kernel(float* __restri
   const float* mrow = mask ? mask + row * tk : nullptr;
   const float logsum = __ldg(lse + row);
   const bool dead = !(logsum > -INFINITY);
+  if ((tk & 3) == 0 && ((reinterpret_cast<uintptr_t>(s) | reinterpret_cast<uintptr_t>(mrow)) & 15) == 0) {
+    float4* s4 = reinterpret_cast<float4*>(s);
+    const float4* m4 = reinterpret_cast<const float4*>(mrow);
+    for (int q = threadIdx.x; q < (tk >> 2); q += kThreads) {
+      const float4 a = s4[q], m = m4 ? __ldg(m4 + q) : make_float4(0.f, 0.f, 0.f, 0.f);
+      const int j = 4 * q;
+      float4 r;
+      r.x = (dead || (causal && j > i)) ? 0.f : expf(a.x * scale + m.x - logsum);
+      r.y = (dead || (causal && j + 1 > i)) ? 0.f : expf(a.y * scale + m.y - logsum);
+      r.z = (dead || (causal && j + 2 > i)) ? 0.f : expf(a.z * scale + m.z - logsum);
+      r.w = (dead || (causal && j + 3 > i)) ? 0.f : expf(a.w * scale + m.w - logsum);
+      s4[q] = r;
+    }
+    return;
+  }
   for (int j = threadIdx.x; j < tk; j += kThreads)
     s[j] = dead ? 0.f : expf(masked_score(s[j], scale, mrow, i, j, causal) - logsum);
 }
@@ -96,6 +161,16 @@ __global__ void __launch_bounds__(kThreads) score_gradient_kernel(float* __restr
   delta = block_reduce<false>(delta, scratch);
   float* d = dp + row * tk;
   const float* pr = p + row * tk;
+  if ((tk & 3) == 0 && ((reinterpret_cast<uintptr_t>(d) | reinterpret_cast<uintptr_t>(pr)) & 15) == 0) {
+    float4* d4 = reinterpret_cast<float4*>(d);
+    const float4* p4 = reinterpret_cast<const float4*>(pr);
+    for (int q = threadIdx.x; q < (tk >> 2); q += kThreads) {
+      const float4 a = d4[q], b = __ldg(p4 + q);
+      d4[q] = make_float4(b.x * (a.x - delta) * scale, b.y * (a.y - delta) * scale, b.z * (a.z - delta) * scale,
+                          b.w * (a.w - delta) * scale);
+    }
+    return;
+  }
   for (int j = threadIdx.x; j < tk; j += kThreads) d[j] = pr[j] * (d[j] - delta) * scale;
 }
 
@@ -150,7 +225,9 @@ int b200_attention_forward(int64_t batch, int64_t tq, int64_t tk, int64_t d, int
   float* scores = (float*)workspace;
   // S[b] = Q[b] K[b]^T: the right-hand matrix is K read with its strides swapped
   if (int rc = b200_bmm(batch, tq, tk, d, q, tq * d, d, 1, k, tk * d, 1, d, scores, B200_ALGO_AUTO, stream)) return rc;
-  softmax_rows_kernel<<<(unsigned)rows, kThreads, 0, st>>>(scores, mask, (int)tq, (int)tk, scale, causal, lse);
+  const bool resident = tk % 4 == 0 && tk <= 16 * kThreads && ((reinterpret_cast<uintptr_t>(scores) | reinterpret_cast<uintptr_t>(mask)) & 15) == 0;
+  if (resident) softmax_rows_resident_kernel<<<(unsigned)rows, kThreads, 0, st>>>(scores, mask, (int)tq, (int)tk, scale, causal, lse);
+  else softmax_rows_kernel<<<(unsigned)rows, kThreads, 0, st>>>(scores, mask, (int)tq, (int)tk, scale, causal, lse);
   count_launch();
   if (int rc = launch_check("softmax_rows_kernel")) return rc;
   if (dv == 0) return B200_OK;

@@ -606,9 +606,10 @@ __global__ void __launch_bounds__(256) stage_weights_kernel(ConvGeom g, View4 w,
   if (i >= total) return;
   const int kc = is_dx ? g.cog : g.cig, nc = is_dx ? g.cig : g.cog;
   const int cpp = (kc + KBLK - 1) / KBLK;
-  const int k = (int)(i % KBLK);
-  const int row = (int)((i / KBLK) % bn);
-  const long long image = i / ((long long)KBLK * bn);
+  // one thread per four adjacent reduction channels: a 16-byte piece of the swizzled row
+  const int k = (int)(i % (KBLK / 4)) * 4;
+  const int row = (int)((i / (KBLK / 4)) % bn);
+  const long long image = i / ((long long)(KBLK / 4) * bn);
   int grp, n_tile, cbl, tap;
   if (is_dx) {  // [group][phase][tile of the phase][channel block][tap of the phase]
     const int per_group = tiles_pp * cpp * tt.taps_total;
@@ -633,21 +634,27 @@ __global__ void __launch_bounds__(256) stage_weights_kernel(ConvGeom g, View4 w,
     tap = tt.start[phase] + rel % ntap;
   }
   const int r = n_tile * bn + row, c = cbl * KBLK + k;
-  float v = 0.f;
-  if (r < nc && c < kc) {  // rows beyond the column count and channels beyond a ragged last block are zero
-    const int co = is_dx ? c : r, ci = is_dx ? r : c;
-    v = w.ptr[((long long)grp * g.cog + co) * w.s0 + ci * w.s1 + tt.ky[tap] * w.s2 + tt.kx[tap] * w.s3 + grp * w_group_extra];
+  float v[4] = {0.f, 0.f, 0.f, 0.f};
+  if (r < nc) {  // rows beyond the column count and channels beyond a ragged last block are zero
+    // forward: r is the output channel, c the input channel; dInput: the other way round
+    const long long step = is_dx ? w.s0 : w.s1;
+    const float* src = w.ptr + ((long long)grp * g.cog + (is_dx ? c : r)) * w.s0 + (long long)(is_dx ? r : c) * w.s1 +
+                       tt.ky[tap] * w.s2 + tt.kx[tap] * w.s3 + grp * w_group_extra;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (c + j < kc) v[j] = __ldg(src + j * step);
   }
-  float hi, lo;
-  split_tf32(v, hi, lo);
+  float hi[4], lo[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) split_tf32(v[j], hi[j], lo[j]);
   float* plane = out + image * (bn * 64ll);
-  plane[sw128_offset(row, k) / 4] = hi;
+  *reinterpret_cast<float4*>(plane + sw128_offset(row, k) / 4) = make_float4(hi[0], hi[1], hi[2], hi[3]);
   if (CROSS_BF16) {  // second plane: [bf16(lo) x32 | bf16(hi) x32] per row, pairing with the activations' [hi | lo]
-    __nv_bfloat16* cross = reinterpret_cast<__nv_bfloat16*>(plane + bn * 32);
-    cross[sw128_offset_bf16(row, k) / 2] = __float2bfloat16_rn(lo);
-    cross[sw128_offset_bf16(row, 32 + k) / 2] = __float2bfloat16_rn(hi);
+    unsigned char* cross = reinterpret_cast<unsigned char*>(plane + bn * 32);
+    *reinterpret_cast<uint2*>(cross + sw128_offset_bf16(row, k)) = make_uint2(pack_bf16x2(lo[0], lo[1]), pack_bf16x2(lo[2], lo[3]));
+    *reinterpret_cast<uint2*>(cross + sw128_offset_bf16(row, 32 + k)) = make_uint2(pack_bf16x2(hi[0], hi[1]), pack_bf16x2(hi[2], hi[3]));
   } else {
-    plane[bn * 32 + sw128_offset(row, k) / 4] = lo;
+    *reinterpret_cast<float4*>(plane + bn * 32 + sw128_offset(row, k) / 4) = make_float4(lo[0], lo[1], lo[2], lo[3]);
   }
 }
 
@@ -800,7 +807,7 @@ int strip_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* b
     if (!ws || ws_bytes < 2 * sizeof(float) * (size_t)wcount || (reinterpret_cast<uintptr_t>(ws) & 15))
       return fail(B200_EWORKSPACE, "tcgen05 convolution needs a 16-byte aligned workspace of %zu bytes (got %zu)",
                   2 * sizeof(float) * (size_t)wcount, ws_bytes);
-    stage_weights_kernel<<<(unsigned)div_up64(wcount, 256), 256, 0, st>>>(g, w, is_dx ? 1 : 0, plan.bn, tiles_pp, plan.tt, (float*)ws, wcount,
+    stage_weights_kernel<<<(unsigned)div_up64(wcount / 4, 256), 256, 0, st>>>(g, w, is_dx ? 1 : 0, plan.bn, tiles_pp, plan.tt, (float*)ws, wcount / 4,
                                                                           batch ? batch->w_group_extra : 0);
     count_launch();
     if (int rc = launch_check("stage_weights_kernel")) return rc;

@@ -226,6 +226,9 @@ def main():
     if world > 1:
         import torch.distributed as dist_mod
         dist = dist_mod
+        # NCCL_DEBUG=VERSION makes NCCL print a banner on stdout, where only the JSON line belongs
+        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"
         dist.init_process_group("nccl", device_id=device)
     L = b200conv.lib()
     stream = torch.cuda.current_stream().cuda_stream

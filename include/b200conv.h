@@ -127,6 +127,13 @@ int b200_conv2d_geometry(b200_conv_params* out, int64_t n, int64_t cin, int64_t 
  * (AUTO resolves through the heuristic); <0 if the forced candidate is not applicable.
  * Replaces applicable/candidates/heuristic, csrc/ops/convolution.cpp:357-482. */
 int b200_conv2d_select(const b200_conv_params* p, int phase, int algo, size_t workspace_bytes);
+/* Which kernel a forward / dInput call of the tcgen05 candidate runs for this activation view (x for
+ * forward, dy for dInput; only the strides are read, the pointer is not dereferenced):
+ * 0 = strip kernel; 1 = per-tap gather kernel (views that span 2^31 elements or more, reduction
+ * channels in whole blocks of 32); 2 = CUDA-core implicit GEMM (such a view with a ragged channel
+ * count, which the gather kernel would truncate).  <0 if the candidate does not take the geometry.
+ * Part of execute_candidate's role, csrc/ops/convolution.cpp:483-520 (kernel choice per memory class). */
+int b200_conv2d_tc_route(const b200_conv_params* p, int phase, b200_view4 act);
 /* Scratch bytes the selected candidate wants (0 = none).  For dWeight this is the
  * split-K partial buffer of weight_split_plan, csrc/ops/convolution.cpp:204-238;
  * a smaller non-zero budget yields fewer, longer splits. */
@@ -301,6 +308,12 @@ size_t b200_attention_workspace(int64_t batch, int64_t tq, int64_t tk, int64_t d
 int b200_attention_forward(int64_t batch, int64_t tq, int64_t tk, int64_t d, int64_t dv, const float* q, const float* k,
                            const float* v, const float* mask, int causal, float scale, float* out, float* lse, void* workspace,
                            size_t workspace_bytes, void* stream);
+
+/* Replaces -inf by 0 in a log-sum-exp buffer, in place: what the reference's operator
+ * _scaled_dot_product_flash_attention_for_cpu returns for rows with every key hidden
+ * (csrc/ops/attention.cpp, cpu_flash_forward_native: at::where(isneginf(lse), 0, lse)).
+ * b200_attention_backward accepts either form: a hidden key's score is -inf, so its probability is 0. */
+int b200_attention_lse_finite(float* lse, int64_t count, void* stream);
 
 /* dq, dk, dvalue from the output gradient, the saved output and log-sum-exp.  Replaces
  * attention_backward (csrc/ops/attention.cpp:24-34, sdpa_training.comp modes 1 and 2); the mask

@@ -76,6 +76,7 @@ SIGNATURES = {
     "b200_event_elapsed_ms": (c_int, [c_void_p, c_void_p, POINTER(c_float)]),
     "b200_conv2d_geometry": (c_int, [POINTER(ConvParams)] + [c_int64] * 15),
     "b200_conv2d_select": (c_int, [POINTER(ConvParams), c_int, c_int, c_size_t]),
+    "b200_conv2d_tc_route": (c_int, [POINTER(ConvParams), c_int, View4]),
     "b200_conv2d_workspace": (c_size_t, [POINTER(ConvParams), c_int, c_int, c_size_t]),
     "b200_conv2d_forward": (c_int, [POINTER(ConvParams), View4, View4, c_void_p, c_int64, c_void_p, c_void_p,
                                     c_size_t, c_int, c_void_p]),
@@ -109,6 +110,7 @@ SIGNATURES = {
     "b200_attention_workspace": (c_size_t, [c_int64] * 5 + [c_int]),
     "b200_attention_forward": (c_int, [c_int64] * 5 + [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p,
                                        c_void_p, c_size_t, c_void_p]),
+    "b200_attention_lse_finite": (c_int, [c_void_p, c_int64, c_void_p]),
     "b200_attention_backward": (c_int, [c_int64] * 5 + [c_void_p] * 7 + [c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p,
                                         c_size_t, c_void_p]),
     "b200_device_status": (c_int, [POINTER(c_int), c_int]),
@@ -248,6 +250,12 @@ def workspace_bytes(p, phase, algo=ALGO_AUTO, budget=DEFAULT_WORKSPACE):
 
 def select(p, phase, algo=ALGO_AUTO, budget=DEFAULT_WORKSPACE):
     return check(lib().b200_conv2d_select(ctypes.byref(p), phase, algo, budget))
+
+
+def tc_route(p, phase, strides):
+    """0 strip kernel, 1 gather kernel, 2 CUDA-core implicit GEMM for a tcgen05 forward / dInput call on an
+    activation view with these element strides (host arithmetic only; no device memory is touched)."""
+    return check(lib().b200_conv2d_tc_route(ctypes.byref(p), phase, View4(None, (c_int64 * 4)(*strides))))
 
 
 def _algo(a):

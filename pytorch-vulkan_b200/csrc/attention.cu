@@ -192,6 +192,12 @@ int make_shape(int64_t batch, int64_t tq, int64_t tk, int64_t d, int64_t dv, Att
   return B200_OK;
 }
 
+// -inf -> 0 in place (rows with every key hidden)
+__global__ void __launch_bounds__(kThreads) lse_finite_kernel(float* __restrict__ lse, long long count) {
+  const long long i = blockIdx.x * (long long)kThreads + threadIdx.x;
+  if (i < count && lse[i] == -INFINITY) lse[i] = 0.f;
+}
+
 }  // namespace
 }  // namespace b200
 
@@ -234,6 +240,15 @@ int b200_attention_forward(int64_t batch, int64_t tq, int64_t tk, int64_t d, int
   const int rc = b200_bmm(batch, tq, dv, tk, scores, tq * tk, tk, 1, v, tk * dv, dv, 1, out, B200_ALGO_AUTO, stream);
   note_kernel("attention_forward: bmm + softmax_rows + bmm");
   return rc;
+}
+
+int b200_attention_lse_finite(float* lse, int64_t count, void* stream) {
+  if (int rc = ensure_init()) return rc;
+  if (count < 0 || (count > 0 && !lse)) return fail(B200_EINVAL, "attention: invalid log-sum-exp buffer");
+  if (count == 0) return B200_OK;
+  lse_finite_kernel<<<(unsigned)((count + kThreads - 1) / kThreads), kThreads, 0, (cudaStream_t)stream>>>(lse, count);
+  count_launch();
+  return launch_check("lse_finite_kernel");
 }
 
 int b200_attention_backward(int64_t batch, int64_t tq, int64_t tk, int64_t d, int64_t dv, const float* grad, const float* q,

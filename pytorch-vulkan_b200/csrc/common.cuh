@@ -122,6 +122,8 @@ int strip_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* b
 int post_ops_nchw(float* y, const ConvGeom& g, const StripPostOps& post, cudaStream_t st);
 // y[n][c][plane] += bias[c] on a contiguous result (conv_simt.cu)
 int bias_add_nchw(float* y, long long n, int channels, long long plane, const float* bias, long long bias_stride, cudaStream_t st);
+bool strip_view_addressable(const ConvGeom& g, bool is_dx, const View4& act, const StripBatch* batch);
+int tc_route(const ConvGeom& g, bool is_dx, const View4& act);  // 0 strip, 1 gather, 2 CUDA-core implicit GEMM (conv_tc.cu)
 int strip_column_tile(const ConvGeom& g, bool is_dx);   // column tile the plan picks, 0 if unsupported
 size_t strip_workspace(const ConvGeom& g, int phase);  // bytes of the weight stage images
 

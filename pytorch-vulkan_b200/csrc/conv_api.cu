@@ -96,7 +96,12 @@ static int select(const ConvGeom& g, int phase, int algo, size_t workspace) {
   if ((phase == B200_PHASE_FORWARD || phase == B200_PHASE_DINPUT) && g.cig >= 512 && g.cog >= 512 &&
       winograd_supported(g, phase) && winograd_workspace(g, phase, workspace) > 0)
     return B200_ALGO_WINOGRAD;
-  if (tc_supported(g, phase)) return B200_ALGO_TC;
+  // The tcgen05 forward / dInput kernels stage the split filter in the caller's workspace; a caller that
+  // brings none (or too little) gets the CUDA-core kernels, which need no scratch.  dWeight runs unsplit
+  // without a workspace.  (A forced B200_ALGO_TC keeps reporting the workspace error.)
+  if (tc_supported(g, phase) &&
+      (phase == B200_PHASE_DWEIGHT || tc_workspace(g, phase, workspace, nullptr, nullptr) <= workspace))
+    return B200_ALGO_TC;
   // Thresholds of the reference heuristic for leaving the one-thread-per-output kernels.
   if (phase == B200_PHASE_FORWARD) return (g.cog >= 8 && cols >= 16 && rows >= 32) ? B200_ALGO_TILED : B200_ALGO_DIRECT;
   if (phase == B200_PHASE_DINPUT)
@@ -145,6 +150,14 @@ int b200_conv2d_geometry(b200_conv_params* out, int64_t n, int64_t cin, int64_t 
 int b200_conv2d_select(const b200_conv_params* p, int phase, int algo, size_t workspace_bytes) {
   if (int rc = check_params(p)) return rc;
   return select(to_geom(*p), phase, algo, workspace_bytes);
+}
+
+int b200_conv2d_tc_route(const b200_conv_params* p, int phase, b200_view4 act) {
+  if (int rc = check_params(p)) return rc;
+  if (phase != B200_PHASE_FORWARD && phase != B200_PHASE_DINPUT) return fail(B200_EINVAL, "tc_route: forward or dInput only");
+  const ConvGeom g = to_geom(*p);
+  if (!tc_supported(g, phase)) return fail(B200_EUNSUPPORTED, "tcgen05 candidate is incompatible with this geometry");
+  return tc_route(g, phase == B200_PHASE_DINPUT, to_view(act));
 }
 
 size_t b200_conv2d_workspace(const b200_conv_params* p, int phase, int algo, size_t budget_bytes) {

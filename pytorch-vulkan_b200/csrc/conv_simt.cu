@@ -135,9 +135,9 @@ __device__ __forceinline__ void store_out(const IgemmArgs& p, int group, int spl
   const ConvGeom& g = p.g;
   if (m >= p.M || n >= p.N) return;
   if (PH == PH_GEMM) {
-    float r = p.alpha * v;
+    float r = p.alpha * v;  // alpha scales the product whether or not a bias follows
     if (p.bias && p.beta != 0.f) r += p.beta * p.bias[n * p.bias_stride];
-    p.out[m * p.N + n] = p.bias ? r : v;
+    p.out[m * p.N + n] = r;
   } else if (PH == PH_FWD) {
     const int spatial = g.oh * g.ow;
     const long long b = n / spatial, pos = n % spatial, oc = (long long)group * g.cog + m;

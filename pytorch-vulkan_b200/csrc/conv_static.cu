@@ -36,6 +36,9 @@ static __device__ __align__(256) float g_static_scratch[kStaticScratchBytes / si
 static std::mutex g_static_mutex;
 static float* g_static_address[64] = {};  // per device ordinal, filled on first use
 
+// The caller has run ensure_init() just before, which makes the library's device current on this
+// thread, so the ordinal read here is the library's own (one device per process); the address is
+// resolved with that device current, as cudaGetSymbolAddress requires.
 static int static_scratch_address(float** out) {
   int dev = -1;
   B200_CUDA(cudaGetDevice(&dev));

@@ -699,24 +699,51 @@ static int conv_tc_run(const ConvGeom& g, bool is_dx, View4 act, View4 w, const 
   return launch_conv_tc<256, false>(a, grid, st);
 }
 
+// Which kernel takes a forward / dInput call that asked for the tcgen05 candidate:
+//   0  the strip kernel (the normal case);
+//   1  the gather kernel: the strip kernel declines at run time (a view that spans more elements than its
+//      32-bit offsets address) and the reduction channels come in whole blocks of 32, which the gather
+//      kernel needs (it has no ragged-block padding);
+//   2  the CUDA-core implicit GEMM: everything else (a ragged channel count on such a view).
+// Pure host arithmetic on the geometry and the view's strides; nothing is dereferenced.
+int tc_route(const ConvGeom& g, bool is_dx, const View4& act) {
+  const int kc = is_dx ? g.cog : g.cig;
+  if (strip_allowed() && strip_supported(g, is_dx ? B200_PHASE_DINPUT : B200_PHASE_FORWARD) &&
+      strip_view_addressable(g, is_dx, act, nullptr))
+    return 0;
+  return kc % KBLK == 0 ? 1 : 2;
+}
+
 int tc_forward(const ConvGeom& g, View4 x, View4 w, const float* bias, long long bias_stride, float* y, void* ws,
                size_t ws_bytes, cudaStream_t st) {
-  if (strip_allowed() && strip_supported(g, B200_PHASE_FORWARD)) {
+  int route = tc_route(g, false, x);
+  if (route == 0) {
     note_kernel("tc_strip_forward");
     const int rc = strip_conv(g, false, x, w, bias, bias_stride, y, ws, ws_bytes, st);
-    if (rc != B200_EUNSUPPORTED) return rc;  // tensors beyond 32-bit element offsets take the gather kernel
-    note_kernel("tc_igemm_forward");
+    if (rc != B200_EUNSUPPORTED) return rc;  // e.g. more tiles than the kernel's 32-bit job indices
+    route = g.cig % KBLK == 0 ? 1 : 2;
   }
-  return conv_tc_run(g, false, x, w, bias, bias_stride, y, ws, ws_bytes, st);
+  if (route == 1) {
+    note_kernel("tc_igemm_forward");
+    return conv_tc_run(g, false, x, w, bias, bias_stride, y, ws, ws_bytes, st);
+  }
+  note_kernel("simt_igemm_forward");
+  return simt_igemm_forward(g, x, w, bias, bias_stride, y, st);
 }
 int tc_dinput(const ConvGeom& g, View4 dy, View4 w, float* dx, void* ws, size_t ws_bytes, cudaStream_t st) {
-  if (strip_allowed() && strip_supported(g, B200_PHASE_DINPUT)) {
+  int route = tc_route(g, true, dy);
+  if (route == 0) {
     note_kernel("tc_strip_dinput");
     const int rc = strip_conv(g, true, dy, w, nullptr, 0, dx, ws, ws_bytes, st);
     if (rc != B200_EUNSUPPORTED) return rc;
-    note_kernel("tc_igemm_dinput");
+    route = g.cog % KBLK == 0 ? 1 : 2;
   }
-  return conv_tc_run(g, true, dy, w, nullptr, 0, dx, ws, ws_bytes, st);
+  if (route == 1) {
+    note_kernel("tc_igemm_dinput");
+    return conv_tc_run(g, true, dy, w, nullptr, 0, dx, ws, ws_bytes, st);
+  }
+  note_kernel("simt_igemm_dinput");
+  return simt_igemm_dinput(g, dy, w, dx, st);
 }
 template <int BN>
 static int launch_dweight_tc(const DwTcArgs& a, dim3 grid, cudaStream_t st) {

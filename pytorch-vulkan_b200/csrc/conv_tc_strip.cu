@@ -790,6 +790,16 @@ static int launch_strip(const tcs::StripArgs& a, int grid, int smem, cudaStream_
   return launch_check("conv_strip_kernel");
 }
 
+// The kernel forms element offsets inside the activation tensor in 32 bits: true when the view's
+// extent (with the 64 channels a ragged block may look ahead) stays below 2^31 elements.
+bool strip_view_addressable(const ConvGeom& g, bool is_dx, const View4& act, const StripBatch* batch) {
+  const long long an = g.n, ac = is_dx ? g.cout : g.cin, ah = is_dx ? g.oh : g.h, aw = is_dx ? g.ow : g.w;
+  const long long span = (an - 1) * std::llabs(act.s0) + (ac - 1) * std::llabs(act.s1) +
+                         (ah - 1) * std::llabs(act.s2) + (aw - 1) * std::llabs(act.s3) +
+                         (batch ? (g.groups - 1) * std::llabs(batch->act_group_extra) : 0);
+  return span <= 2147483647ll - 64 * std::llabs(act.s1);
+}
+
 int strip_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* bias, long long bias_stride, float* out,
                void* ws, size_t ws_bytes, cudaStream_t st, bool rowmajor, float alpha, float beta, const float* staged_images,
                const StripPostOps* post, const StripBatch* batch) {
@@ -815,14 +825,8 @@ int strip_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* b
     staged_here = true;
   }
   if (reinterpret_cast<uintptr_t>(wp) & 15) return fail(B200_EINVAL, "weight stage images must be 16-byte aligned");
-  {  // the kernel forms element offsets inside the activation tensor in 32 bits
-    const long long an = g.n, ac = is_dx ? g.cout : g.cin, ah = is_dx ? g.oh : g.h, aw = is_dx ? g.ow : g.w;
-    const long long span = (an - 1) * std::llabs(act.s0) + (ac - 1) * std::llabs(act.s1) +
-                           (ah - 1) * std::llabs(act.s2) + (aw - 1) * std::llabs(act.s3) +
-                           (batch ? (g.groups - 1) * std::llabs(batch->act_group_extra) : 0);
-    if (span > 2147483647ll - 64 * std::llabs(act.s1))
-      return fail(B200_EUNSUPPORTED, "strip kernel: activation tensor too large for 32-bit element offsets");
-  }
+  if (!strip_view_addressable(g, is_dx, act, batch))
+    return fail(B200_EUNSUPPORTED, "strip kernel: activation tensor too large for 32-bit element offsets");
   StripArgs a{};
   a.g = g; a.act = act; a.wp = wp; a.bias = is_dx ? nullptr : bias; a.bias_stride = bias_stride; a.out = out;
   a.H = plan.gh; a.W = plan.gw; a.pr = plan.pr; a.pc = plan.pc;

@@ -29,7 +29,8 @@ void check(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, double
   TORCH_CHECK(q.scalar_type() == at::kFloat && k.scalar_type() == at::kFloat && v.scalar_type() == at::kFloat,
               "Vulkan attention requires FP32 input");
   TORCH_CHECK(dropout == 0, "scaled_dot_product_attention_flash_attention: Currently do not support dropout > 0");
-  TORCH_CHECK(q.size(3) == k.size(3), "scaled_dot_product_attention_flash_attention: Q/K should have the same head size");
+  TORCH_CHECK(q.size(3) == v.size(3) && k.size(3) == v.size(3),
+              "scaled_dot_product_attention_flash_attention: Q/K/V should have the same head size");
   TORCH_CHECK(q.sizes().slice(0, 2) == k.sizes().slice(0, 2) && q.sizes().slice(0, 2) == v.sizes().slice(0, 2) &&
                   k.size(2) == v.size(2),
               "attention batch/head/sequence mismatch");
@@ -66,6 +67,8 @@ std::tuple<at::Tensor, at::Tensor> attention_forward(const at::Tensor& q, const 
                                           vc.const_data_ptr<float>(), mc.defined() ? mc.const_data_ptr<float>() : nullptr,
                                           causal ? 1 : 0, (float)scale.value_or(1.0 / std::sqrt((double)d)), out.data_ptr<float>(),
                                           lse.data_ptr<float>(), ws.hold.data_ptr(), ws.bytes, backend_stream()));
+  // rows with every key hidden: the reference's operator returns 0 for them, not -inf (attention.cpp, cpu_flash_forward_native)
+  B200_TORCH_CHECK(b200_attention_lse_finite(lse.data_ptr<float>(), lse.numel(), backend_stream()));
   return {out, lse};
 }
 

@@ -74,3 +74,38 @@ def test_forced_candidates_resolve_or_fail_loudly():
         b200conv.select(p, b200conv.PHASE_FORWARD, b200conv.ALGO_WINOGRAD)
     # tiny geometry: the heuristic stays on the one-thread-per-output kernels (convolution.cpp:463-469)
     assert b200conv.select(p, b200conv.PHASE_FORWARD) == b200conv.ALGO_DIRECT
+
+
+def test_tcgen05_call_on_a_view_beyond_32_bit_offsets_never_truncates_channels():
+    """A view that spans 2^31 elements or more leaves the strip kernel; the gather kernel takes it only
+    when the reduction channels come in whole blocks of 32 (it has no ragged-block padding), anything
+    else goes to the CUDA-core implicit GEMM.  Host arithmetic only: no tensor is allocated."""
+    def strides(c, h, w):
+        return (c * h * w, h * w, w, 1)
+    small = b200conv.geometry((2, 48, 32, 32), 64, (3, 3), padding=(1, 1))
+    assert b200conv.tc_route(small, b200conv.PHASE_FORWARD, strides(48, 32, 32)) == 0
+    huge48 = b200conv.geometry((64, 48, 16384, 64), 32, (3, 3), padding=(1, 1))     # 3.2e9 elements, ragged block
+    assert b200conv.tc_route(huge48, b200conv.PHASE_FORWARD, strides(48, 16384, 64)) == 2
+    huge64 = b200conv.geometry((40, 64, 1024, 1024), 64, (3, 3), padding=(1, 1))    # whole blocks of 32
+    assert b200conv.tc_route(huge64, b200conv.PHASE_FORWARD, strides(64, 1024, 1024)) == 1
+    # dInput: the reduction runs over the output channels
+    dx80 = b200conv.geometry((40, 64, 1024, 1024), 80, (1, 1))
+    assert b200conv.tc_route(dx80, b200conv.PHASE_DINPUT, strides(80, 1024, 1024)) == 2
+    assert b200conv.tc_route(dx80, b200conv.PHASE_FORWARD, strides(64, 1024, 1024)) == 1
+    # a small tensor inside a huge parent (strides of the parent): still beyond 32-bit offsets
+    assert b200conv.tc_route(small, b200conv.PHASE_FORWARD, (2 ** 31, 32 * 32, 32, 1)) == 2
+
+
+def test_auto_selection_without_workspace_stays_off_the_tcgen05_forward_kernels():
+    p = b200conv.geometry((8, 64, 56, 56), 64, (3, 3), padding=(1, 1))
+    need = b200conv.workspace_bytes(p, b200conv.PHASE_FORWARD, b200conv.ALGO_TC)
+    assert need > 0
+    for phase in (b200conv.PHASE_FORWARD, b200conv.PHASE_DINPUT):
+        assert b200conv.select(p, phase, b200conv.ALGO_AUTO, budget=need) == b200conv.ALGO_TC
+        assert b200conv.select(p, phase, b200conv.ALGO_AUTO, budget=0) == b200conv.ALGO_TILED
+        assert b200conv.select(p, phase, b200conv.ALGO_AUTO, budget=need - 1) == b200conv.ALGO_TILED
+        assert b200conv.workspace_bytes(p, phase, b200conv.ALGO_AUTO, budget=0) == 0
+        # a forced candidate keeps asking for its workspace
+        assert b200conv.select(p, phase, b200conv.ALGO_TC, budget=0) == b200conv.ALGO_TC
+    # dWeight runs unsplit without scratch
+    assert b200conv.select(p, b200conv.PHASE_DWEIGHT, b200conv.ALGO_AUTO, budget=0) == b200conv.ALGO_TC

@@ -71,3 +71,27 @@ def test_flash_attention_operator_pair(causal, masked):
         torch.testing.assert_close(got.cpu(), want, rtol=3e-4, atol=3e-4)
     with pytest.raises(RuntimeError, match="do not support dropout"):
         torch.ops.aten._scaled_dot_product_flash_attention_for_cpu(q.to("vulkan"), k.to("vulkan"), v.to("vulkan"), 0.5, False)
+
+
+def test_operator_returns_zero_log_sum_exp_for_rows_with_every_key_hidden():
+    """The reference's operator replaces the -inf log-sum-exp of such rows with 0
+    (csrc/ops/attention.cpp, cpu_flash_forward_native); its backward then sees probability 0 there."""
+    torch.manual_seed(11)
+    q, k, v = torch.randn(1, 2, 6, 8), torch.randn(1, 2, 5, 8), torch.randn(1, 2, 5, 8)
+    mask = torch.zeros(1, 2, 6, 5)
+    mask[0, 1, 3] = float("-inf")
+    grad = torch.randn(1, 2, 6, 8)
+    dev = lambda t: t.to("vulkan")
+    out, lse = torch.ops.aten._scaled_dot_product_flash_attention_for_cpu(dev(q), dev(k), dev(v), 0.0, False, attn_mask=dev(mask))
+    lse_h, out_h = lse.cpu(), out.cpu()
+    assert torch.isfinite(lse_h).all() and lse_h[0, 1, 3] == 0 and (out_h[0, 1, 3] == 0).all()
+    dq, dk, dv = torch.ops.aten._scaled_dot_product_flash_attention_for_cpu_backward(dev(grad), dev(q), dev(k), dev(v), out, lse,
+                                                                                    0.0, False, attn_mask=dev(mask))
+    assert torch.isfinite(dq.cpu()).all() and (dq.cpu()[0, 1, 3] == 0).all()
+    # the visible rows agree with the oracle on the same inputs
+    wout, wlse = att.forward(q.reshape(2, 6, 8).numpy(), k.reshape(2, 5, 8).numpy(), v.reshape(2, 5, 8).numpy(),
+                             mask.reshape(2, 6, 5).numpy(), False)
+    keep = np.isfinite(wlse)
+    np.testing.assert_allclose(lse_h.reshape(2, 6).numpy()[keep], wlse[keep], rtol=1e-4, atol=1e-4)
+    with pytest.raises(RuntimeError, match="same head size"):
+        torch.ops.aten._scaled_dot_product_flash_attention_for_cpu(dev(q), dev(k), dev(torch.randn(1, 2, 5, 4)), 0.0, False)

@@ -1,5 +1,7 @@
 """Parity of the tcgen05 (split-precision FP32) kernels, forced through the C-ABI, against the FP64 oracle.
-Gate: per-output L2-normalised error <= 1e-4; in practice the split keeps it near 1e-6."""
+The contract's gate is a per-output L2-normalised error of 1e-4; these tests hold the kernels to what the
+split-precision arithmetic actually delivers (1e-6 to 6e-6 measured; Winograd up to 2e-5), so that losing
+the low-order plane or the cross terms (error near 5e-4) or most of their precision cannot pass."""
 import numpy as np
 import pytest
 
@@ -8,7 +10,8 @@ from golden_cases import conv_cases
 from oracle import oracle
 
 pytestmark = pytest.mark.gpu
-GATE = 1e-4
+GATE = 2e-5        # tcgen05 split-precision kernels
+GATE_WINOGRAD = 5e-5   # F(4x4,3x3): the transforms amplify rounding
 
 
 def _rand(shape, seed, scale=1.0):
@@ -226,4 +229,4 @@ def test_winograd_f4_forward_and_dinput(shape, budget):
         with pytest.raises(b200conv.B200Error, match="incompatible"):
             b200conv.conv2d_backward(go, x, w, mask=(True, False, False), algo="winograd", budget=budget, **args)
     assert b200conv.device_status() == 0
-    assert max(errs) <= GATE, errs
+    assert max(errs) <= GATE_WINOGRAD, errs

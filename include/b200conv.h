@@ -323,6 +323,28 @@ int b200_attention_backward(int64_t batch, int64_t tq, int64_t tk, int64_t d, in
                             float scale, float* dq, float* dk, float* dvalue, void* workspace, size_t workspace_bytes,
                             void* stream);
 
+/* ---- data-parallel exchange (batch sharded over GPUs, one process per GPU) ------------------------ */
+
+/* These entry points have no counterpart in the reference, which is single-device
+ * (csrc/torch_vulkan.cpp:105-107: deviceCount() == 1).  Forward and dInput are local to a rank; the
+ * weight and bias gradients of a layer are summed over ranks with one all-reduce (NCCL over NVLink),
+ * which the caller may issue on a second stream so that it runs under the next layer's kernels.
+ * NCCL is bound at run time (dlopen): a process that never calls these loads no communication library.
+ *
+ * b200_comm_unique_id: rank 0 fills 128 opaque bytes and hands them to every rank by its own means.
+ * b200_comm_init: every rank calls it with the same id after b200_init; returns once all nranks have
+ *   joined, or fails with B200_ECUDA after the timeout (default 60 s, b200_comm_set_timeout_ms) with the
+ *   half-built communicator aborted, so a rank that never joins cannot hang the others.
+ * b200_allreduce_sum_f32: in-place sum of `count` floats over all ranks, asynchronous on `stream`.
+ * b200_comm_destroy: releases the communicator (idempotent).  b200_comm_rank / _size: -1 / 0 before init. */
+int b200_comm_unique_id(void* out128);
+int b200_comm_set_timeout_ms(int timeout_ms);
+int b200_comm_init(int rank, int nranks, const void* unique_id128);
+int b200_comm_rank(void);
+int b200_comm_size(void);
+int b200_allreduce_sum_f32(float* buf, size_t count, void* stream);
+int b200_comm_destroy(void);
+
 /* Device-side health word.  The tcgen05 kernels bound every wait on an mbarrier; a wait that
  * gives up records (code << 24 | CTA index) here, frees its tensor memory and returns, so the
  * context stays usable.  *status = 0 means no wait ever gave up.  Synchronises the device.

@@ -113,6 +113,13 @@ SIGNATURES = {
     "b200_attention_lse_finite": (c_int, [c_void_p, c_int64, c_void_p]),
     "b200_attention_backward": (c_int, [c_int64] * 5 + [c_void_p] * 7 + [c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p,
                                         c_size_t, c_void_p]),
+    "b200_comm_unique_id": (c_int, [c_void_p]),
+    "b200_comm_set_timeout_ms": (c_int, [c_int]),
+    "b200_comm_init": (c_int, [c_int, c_int, c_void_p]),
+    "b200_comm_rank": (c_int, []),
+    "b200_comm_size": (c_int, []),
+    "b200_allreduce_sum_f32": (c_int, [c_void_p, c_size_t, c_void_p]),
+    "b200_comm_destroy": (c_int, []),
     "b200_device_status": (c_int, [POINTER(c_int), c_int]),
     "b200_launch_count": (c_uint64, []),
     "b200_last_kernel": (c_char_p, []),
@@ -159,6 +166,30 @@ def launch_count():
 
 def last_kernel():
     return lib().b200_last_kernel().decode()
+
+
+def comm_unique_id() -> bytes:
+    """128 opaque bytes that rank 0 creates and every rank passes to comm_init."""
+    buf = ctypes.create_string_buffer(128)
+    check(lib().b200_comm_unique_id(buf))
+    return buf.raw
+
+
+def comm_init(rank, nranks, unique_id: bytes, timeout_ms=None):
+    if len(unique_id) != 128:
+        raise ValueError("the communicator id is 128 bytes")
+    if timeout_ms is not None:
+        check(lib().b200_comm_set_timeout_ms(int(timeout_ms)))
+    check(lib().b200_comm_init(rank, nranks, ctypes.create_string_buffer(unique_id, 128)))
+
+
+def allreduce_sum_f32(ptr, count, stream=None):
+    """In-place sum over ranks of `count` floats at device address `ptr`, asynchronous on `stream`."""
+    check(lib().b200_allreduce_sum_f32(ptr, count, stream))
+
+
+def comm_destroy():
+    check(lib().b200_comm_destroy())
 
 
 class DeviceBuffer:

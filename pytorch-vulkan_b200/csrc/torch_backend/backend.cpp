@@ -266,6 +266,26 @@ PYBIND11_MODULE(_C, m) {
     B200_TORCH_CHECK(b200_device_status(&v, clear ? 1 : 0));
     return v;
   });
+  // data-parallel exchange: NCCL behind the C ABI, on the backend's current stream
+  m.def("_comm_unique_id", [] {
+    char id[128];
+    B200_TORCH_CHECK(b200_comm_unique_id(id));
+    return py::bytes(id, sizeof id);
+  });
+  m.def("_comm_init", [](int rank, int nranks, const std::string& id, int timeout_ms) {
+    TORCH_CHECK(id.size() == 128, "the communicator id is 128 bytes");
+    if (timeout_ms > 0) B200_TORCH_CHECK(b200_comm_set_timeout_ms(timeout_ms));
+    B200_TORCH_CHECK(b200_comm_init(rank, nranks, id.data()));
+  });
+  m.def("_comm_destroy", [] { B200_TORCH_CHECK(b200_comm_destroy()); });
+  m.def("_comm_size", [] { return b200_comm_size(); });
+  m.def("_all_reduce_", [](at::Tensor& t) {
+    TORCH_CHECK(t.device().type() == c10::DeviceType::PrivateUse1, "all_reduce_: expected a vulkan tensor");
+    TORCH_CHECK(t.scalar_type() == at::kFloat && t.is_contiguous(), "all_reduce_: expected a contiguous FP32 tensor");
+    if (t.numel())
+      B200_TORCH_CHECK(b200_allreduce_sum_f32(t.data_ptr<float>(), (size_t)t.numel(), backend_stream()));
+    return t;
+  });
   m.def("_launch_count", [] { return b200_launch_count(); });
   m.def("_last_kernel", [] { return std::string(b200_last_kernel()); });
 

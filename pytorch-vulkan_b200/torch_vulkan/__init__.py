@@ -40,10 +40,17 @@ def is_hardware_accelerated() -> bool:
 
 
 def _validate_device(value=None):
+    """The backend exposes exactly one logical device; anything else is refused, as in the reference."""
     if value is None:
         return
-    d = torch.device("vulkan", value) if isinstance(value, int) else torch.device(value)
-    if d.type != "vulkan" or d.index not in (None, 0):
+    if isinstance(value, torch.Stream):
+        value = value.device
+    if isinstance(value, int):
+        kind, index = "vulkan", value
+    else:
+        parsed = torch.device(value)
+        kind, index = parsed.type, parsed.index
+    if kind != "vulkan" or (index is not None and index != 0):
         raise RuntimeError("Vulkan backend supports logical device 0")
 
 
@@ -174,16 +181,47 @@ def stream(value):
 
 
 class Stream(torch.Stream):
+    """A stream of the one logical device (each is its own CUDA stream underneath)."""
+
     def __new__(cls, device="vulkan", priority=0):
         _validate_device(device)
-        return super().__new__(cls, device=device, priority=priority)
+        return torch.Stream.__new__(cls, device=device, priority=priority)
 
 
 class Event(torch.Event):
+    """An event of the one logical device; events cannot be shared between processes."""
+
     def __new__(cls, enable_timing=False, blocking=False, interprocess=False):
         if interprocess:
             raise RuntimeError("Interprocess Vulkan events are unsupported")
-        return torch.Event(device="vulkan", enable_timing=enable_timing, blocking=blocking)
+        options = dict(enable_timing=enable_timing, blocking=blocking)
+        return torch.Event(device="vulkan", **options)
+
+
+# ---- batch sharding over GPUs (one process per GPU; the reference is single-device) -------------------
+def comm_unique_id() -> bytes:
+    """Rank 0 creates the communicator id (128 opaque bytes) and sends it to every rank by any host channel."""
+    return _C._comm_unique_id()
+
+
+def comm_init(rank: int, nranks: int, unique_id: bytes, timeout_ms: int = 0) -> None:
+    """Join the communicator; raises after the timeout if a rank never joins."""
+    _C._comm_init(rank, nranks, unique_id, timeout_ms)
+
+
+def comm_destroy() -> None:
+    _C._comm_destroy()
+
+
+def comm_size() -> int:
+    """Number of ranks of the communicator, 0 before comm_init."""
+    return _C._comm_size()
+
+
+def all_reduce_(tensor: torch.Tensor) -> torch.Tensor:
+    """In-place sum of a contiguous FP32 vulkan tensor over all ranks (NCCL over NVLink), queued on the
+    current stream like any other operator."""
+    return _C._all_reduce_(tensor)
 
 
 def execution_stats():

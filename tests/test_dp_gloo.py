@@ -36,7 +36,12 @@ def _worker(rank, world, port, out_dir):
     dist.init_process_group("gloo", rank=rank, world_size=world)
     start, stop = dp.shard_range(GLOBAL_BATCH, rank, world)
     dw, db, _ = _shard_grads(start, stop)
-    rdw, rdb = dp.allreduce_grads(torch.from_numpy(dw), torch.from_numpy(db))
+    # the gradients live in one fused buffer dW || dB, as the kernels write them: ONE collective, no copy
+    flat, vdw, vdb = dp.fused_gradient_buffer(dw.shape, True, torch.empty(0))
+    vdw.copy_(torch.from_numpy(dw))
+    vdb.copy_(torch.from_numpy(db))
+    rdw, rdb = dp.allreduce_grads(vdw, vdb)
+    assert rdw.data_ptr() == flat.data_ptr() and rdb.data_ptr() == vdb.data_ptr()
     np.save(os.path.join(out_dir, f"dw{rank}.npy"), rdw.numpy())
     np.save(os.path.join(out_dir, f"db{rank}.npy"), rdb.numpy())
     dist.destroy_process_group()
@@ -68,3 +73,62 @@ def test_allreduce_is_identity_without_a_process_group():
     dw, db = torch.randn(4, 2, 3, 3), torch.randn(4)
     rdw, rdb = dp.allreduce_grads(dw, db)
     assert torch.equal(rdw, dw) and torch.equal(rdb, db)
+
+
+def test_fused_buffer_views_and_the_packing_fallback_agree():
+    dw, db = torch.randn(4, 2, 3, 3), torch.randn(4)
+    flat, vdw, vdb = dp.fused_gradient_buffer(dw.shape, True, dw)
+    assert flat.numel() == dw.numel() + db.numel() and vdw.shape == dw.shape and vdb.shape == db.shape
+    vdw.copy_(dw)
+    vdb.copy_(db)
+    assert torch.equal(flat, torch.cat([dw.reshape(-1), db]))
+    flat2, vdw2, none = dp.fused_gradient_buffer(dw.shape, False, dw)
+    assert none is None and flat2.numel() == dw.numel()
+    rdw, rdb = dp.allreduce_grads(dw, None)
+    assert torch.equal(rdw, dw) and rdb is None
+
+
+def _late_rank(port, hold_s):
+    """Rank 0 of a two-rank job that comes up but never publishes the communicator id."""
+    import datetime
+    import time
+    store = torch.distributed.TCPStore("127.0.0.1", port, 2, True, timeout=datetime.timedelta(seconds=30))
+    time.sleep(hold_s)
+    del store
+
+
+def test_a_rank_that_never_publishes_the_id_times_out_on_the_host():
+    """Failure detection stays on the host: the id travels through a key-value store with a bounded wait, so
+    a missing rank 0 is an exception on the others after the timeout, before any GPU work is queued."""
+    import datetime
+    import time
+    port = _free_port()
+    ctx = mp.get_context("spawn")
+    holder = ctx.Process(target=_late_rank, args=(port, 6.0))
+    holder.start()
+    try:
+        store = None
+        for _ in range(50):  # the server process needs a moment to listen
+            try:
+                store = torch.distributed.TCPStore("127.0.0.1", port, 2, False, timeout=datetime.timedelta(seconds=5))
+                break
+            except Exception:
+                time.sleep(0.1)
+        assert store is not None
+        t0 = time.time()
+        with pytest.raises(Exception):
+            dp.exchange_unique_id(store, 1, lambda: b"", timeout_s=1.0)
+        assert time.time() - t0 < 5.0
+    finally:
+        holder.join(timeout=15)
+        if holder.is_alive():
+            holder.terminate()
+
+
+def test_the_id_reaches_the_other_ranks_through_the_store():
+    import datetime
+    port = _free_port()
+    server = torch.distributed.TCPStore("127.0.0.1", port, 1, True, timeout=datetime.timedelta(seconds=10))
+    uid = bytes(range(128))
+    assert dp.exchange_unique_id(server, 0, lambda: uid) == uid
+    assert dp.exchange_unique_id(server, 1, lambda: b"unused", timeout_s=2.0) == uid

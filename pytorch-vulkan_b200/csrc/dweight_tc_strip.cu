@@ -52,6 +52,15 @@ constexpr int MMA_WARP = PRODUCER_WARPS;
 constexpr int THREADS = (PRODUCER_WARPS + 1) * 32;
 constexpr int MAX_STAGES = 6;
 constexpr int SMEM_LIMIT = 232448 - 2048;
+// The tensor core adds into its FP32 accumulator with truncation, so the error of one accumulation chain
+// grows linearly with its length (measured: 2e-4 relative after 32k pixels, i.e. 8k accumulation steps).
+// A CTA therefore keeps a chain to CHUNK_KB K blocks (3072 pixels, 768 steps: about 1.4e-5): after each
+// chunk the epilogue warps fold the accumulator into the CTA's slot of `out` with ordinary FP32 adds
+// (round to nearest; the first chunk is a store, later ones are global reductions with a single writer per
+// address) and the next chunk starts from zero.  A long reduction then costs one pass over the CTA's own
+// output tile every few thousand pixels (about 5 us per fold: the staging pipeline runs dry while the epilogue
+// warps, which are also producers, read the accumulator) instead of more splits and more scratch.
+constexpr int CHUNK_KB = 96;
 
 struct DwStripArgs {
   ConvGeom g;
@@ -74,6 +83,7 @@ struct DwStripArgs {
   int kx_groups;                 // filters wider than four taps take ceil(kw / 4) CTAs, four taps each
   int ci_tiles, co_tiles;
   int stages;
+  int chunk_kb;          // K blocks accumulated in tensor memory before the sum is folded into `out` (see CHUNK_KB)
   int* status;
   unsigned long long* prof;  // optional cycle counters of CTA (0,0) (B200_STRIP_PROFILE=1), else null
 };
@@ -87,7 +97,7 @@ struct DwStripArgs {
 #define DPROF_ADD(on, slot) do { if (on) atomicAdd(a.prof + (slot), (unsigned long long)(clock64() - prof_t0__)); } while (0)
 
 struct Ctrl {
-  unsigned long long full[MAX_STAGES], empty[MAX_STAGES], accum;
+  unsigned long long full[MAX_STAGES], empty[MAX_STAGES], accum[2], drained[2];
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -243,10 +253,75 @@ __device__ __forceinline__ void store_block(const float (&val)[32], int rows, in
   }
 }
 
+struct FoldArgs {
+  float* out;            // this thread's first output element
+  long long cols;        // element stride between output channels
+  uint32_t acc;          // tensor-memory address of this warp's accumulator rows (buffer 0)
+  uint32_t acc_buffer_cols, nbuf;  // column distance between the two accumulator buffers; 1 or 2 buffers
+  uint32_t accum_bar, drained_bar; // shared-memory addresses of accum[0] / drained[0] (buffer b: + 8 * b)
+  int cols_valid;
+  bool row_ok;
+  int* abort_flag;
+  int* status;
+};
+
+// Folds one warp's accumulator rows into `out` after chunk `c` of the reduction (see CHUNK_KB): the first chunk is
+// stored, later ones are added to what the same thread stored before.  Out of line on purpose: it runs once per
+// 2048 pixels, and inlined it costs the producers' loop registers (that loop runs at the 96-register limit of a
+// 17-warp CTA).
+template <int BN, bool FUSE_HILO>
+__device__ __noinline__ bool fold_accumulator(FoldArgs f, int c, bool more) {
+  // chunk c used accumulator buffer c % nbuf, for the (c / nbuf)-th time
+  const uint32_t buf = f.nbuf == 2 ? (uint32_t)c & 1u : 0u, use = f.nbuf == 2 ? (uint32_t)c >> 1 : (uint32_t)c;
+  if (!mbar_wait(f.accum_bar + 8u * buf, use & 1u, f.abort_flag, f.status, STATUS_TIMEOUT_ACCUM)) return false;
+  tc_fence_after();
+  const bool add = c > 0;
+  f.acc += buf * f.acc_buffer_cols;
+#pragma unroll 1
+  for (int c0 = 0; c0 < BN; c0 += 32) {
+    if (c0 >= f.cols_valid) break;
+    float v[32];
+    tmem_ld32(f.acc + (uint32_t)c0, v);
+    if (FUSE_HILO) {
+      float v2[32];
+      tmem_ld32(f.acc + (uint32_t)(BN + c0), v2);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] += v2[j];
+    }
+    if (f.row_ok) {
+      float* p = f.out + c0 * f.cols;
+      const int nvalid = f.cols_valid - c0;
+      if (add) {
+        // Reductions without a return value: the thread does not wait for the old values, so the accumulator is
+        // handed back after the tensor-memory reads alone.  Every address has exactly one writer (this thread,
+        // in program order), so the sums are the same from run to run.
+#pragma unroll
+        for (int j = 0; j < 32; ++j, p += f.cols)
+          if (j < nvalid) atomicAdd(p, v[j]);
+      } else if (nvalid >= 32) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j, p += f.cols) *p = v[j];
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j, p += f.cols)
+          if (j < nvalid) *p = v[j];
+      }
+    }
+  }
+  if (more) {  // the accumulator may be overwritten now
+    tc_fence_before();
+    __syncwarp();
+    if ((threadIdx.x & 31) == 0) mbar_arrive(f.drained_bar + 8u * buf);
+  }
+  return true;
+}
+
 template <int BN, bool DW_CROSS>
 __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStripArgs a) {
   extern __shared__ unsigned char smem_raw[];
   const unsigned long long prof_start = a.prof ? global_ns() : 0;
+  // the pass that sums the split partials may take its place on the SMs now (it waits for this grid to finish)
+  if (a.partial_layout) asm volatile("griddepcontrol.launch_dependents;");
   const ConvGeom& g = a.g;
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -267,14 +342,21 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
   // of 2*BN columns, so x_hi*[dy_hi | dy_lo] is a single MMA; the epilogue adds the two halves.
   constexpr bool FUSE_HILO = BN <= 128 && !DW_CROSS;
   constexpr uint32_t ACC_COLS = FUSE_HILO ? 2 * BN : BN;
-  const uint32_t tmem_cols = ACC_COLS * (uint32_t)a.nacc;  // 64..512, a power of two
+  // Two accumulator buffers where tensor memory has room (512 columns): the MMA thread then moves on to the
+  // other buffer at a chunk boundary while the epilogue warps fold the finished one, instead of waiting for them.
+  const uint32_t acc_buffer_cols = ACC_COLS * (uint32_t)a.nacc;   // 64..512, a power of two
+  const uint32_t nbuf = acc_buffer_cols <= 256 ? 2u : 1u;
+  const uint32_t tmem_cols = acc_buffer_cols * nbuf;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < MAX_STAGES; ++s) {
       mbar_init(smem_u32(&ctrl->full[s]), (uint32_t)tasks * 32u);
       mbar_init(smem_u32(&ctrl->empty[s]), 1);
     }
-    mbar_init(smem_u32(&ctrl->accum), 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&ctrl->accum[b]), 1);
+      mbar_init(smem_u32(&ctrl->drained[b]), (uint32_t)(4 * a.nacc));  // one arrival per epilogue warp
+    }
     ctrl->abort_flag = 0;
     fence_barrier_init();
   }
@@ -324,7 +406,22 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
       const uint64_t db16_base = make_mn_desc16(base + x_bytes + y_plane, KP * 64u);
       const bool pm = DPROF_ON(true);
       uint32_t s = 0, par = 0;
-      for (int kb = 0; kb < kblocks; ++kb) {
+      int kb_in_chunk = 0;
+      uint32_t chunk = 0, buf = 0;
+      for (int kb = 0; kb < kblocks; ++kb, ++kb_in_chunk) {
+        if (kb_in_chunk == a.chunk_kb) {
+          // chunk boundary: hand the accumulator to the epilogue warps; before the next buffer is overwritten its
+          // previous chunk (nbuf chunks back) must have been read
+          umma_commit(smem_u32(&ctrl->accum[buf]));
+          ++chunk;
+          kb_in_chunk = 0;
+          buf = nbuf == 2 ? chunk & 1u : 0u;
+          if (chunk >= nbuf) {
+            const uint32_t prev_use = (chunk - nbuf) / nbuf;
+            if (!mbar_wait(smem_u32(&ctrl->drained[buf]), prev_use & 1u, abort_flag, a.status, STATUS_TIMEOUT_ACCUM)) break;
+            tc_fence_after();
+          }
+        }
         { DPROF_T0(pm);
         if (!mbar_wait(smem_u32(&ctrl->full[s]), par, abort_flag, a.status, STATUS_TIMEOUT_FULL)) break;
         DPROF_ADD(pm, 0); }
@@ -333,11 +430,11 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
         const uint64_t da_hi = da_base + s * stage_d;
         const uint64_t db_hi = db_base + s * stage_d, db_lo = db_hi + y_plane_d;
         for (int u = 0; u < a.nacc; ++u) {  // channel blocks that share this dY block
-          const uint32_t acc = tmem_acc + (uint32_t)u * ACC_COLS;
+          const uint32_t acc = tmem_acc + buf * acc_buffer_cols + (uint32_t)u * ACC_COLS;
           const uint64_t ua_hi = da_hi + (uint64_t)u * (2 * x_plane_d), ua_lo = ua_hi + x_plane_d;
           if (DW_CROSS) {
 #pragma unroll
-            for (int kg = 0; kg < KP / 8; ++kg) umma_tf32(acc, ua_hi + kg * 64, db_hi + kg * 64, idesc, (kb | kg) != 0);
+            for (int kg = 0; kg < KP / 8; ++kg) umma_tf32(acc, ua_hi + kg * 64, db_hi + kg * 64, idesc, (kb_in_chunk | kg) != 0);
             const uint64_t a_h16 = da16_base + s * stage_d + (uint64_t)u * (2 * x_plane_d), a_l16 = a_h16 + (x_plane_d >> 1);
             const uint64_t b_l16 = db16_base + s * stage_d, b_h16 = b_l16 + (y_plane_d >> 1);
 #pragma unroll
@@ -349,10 +446,10 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
 #pragma unroll
           for (int kg = 0; kg < KP / 8; ++kg) {  // 8 pixels = 8 rows of 128 bytes per MMA
             if (FUSE_HILO) {
-              umma_tf32(acc, ua_hi + kg * 64, db_hi + kg * 64, idesc_wide, (kb | kg) != 0);
+              umma_tf32(acc, ua_hi + kg * 64, db_hi + kg * 64, idesc_wide, (kb_in_chunk | kg) != 0);
               umma_tf32(acc, ua_lo + kg * 64, db_hi + kg * 64, idesc, 1);
             } else {
-              umma_tf32(acc, ua_lo + kg * 64, db_hi + kg * 64, idesc, (kb | kg) != 0);
+              umma_tf32(acc, ua_lo + kg * 64, db_hi + kg * 64, idesc, (kb_in_chunk | kg) != 0);
               umma_tf32(acc, ua_hi + kg * 64, db_lo + kg * 64, idesc, 1);
               umma_tf32(acc, ua_hi + kg * 64, db_hi + kg * 64, idesc, 1);
             }
@@ -362,7 +459,7 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
         if (++s == (uint32_t)a.stages) { s = 0; par ^= 1; }
         DPROF_ADD(pm, 1);
       }
-      umma_commit(smem_u32(&ctrl->accum));
+      umma_commit(smem_u32(&ctrl->accum[buf]));
     }
   } else {
     // ---- producers: job j of K block kb goes to warp (kb*tasks + j) % 16 ----
@@ -371,11 +468,49 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
     const bool y_vec = a.dy.s1 == 1 && ((reinterpret_cast<uintptr_t>(a.dy.ptr) & 15) == 0) && a.dy.s0 % 4 == 0 &&
                        a.dy.s2 % 4 == 0 && a.dy.s3 % 4 == 0;
     const int total_jobs = kblocks * tasks;  // kblocks <= 2^26, tasks <= 16
+    // ---- folding the accumulator into `out` (warps 0 .. 4*nacc-1): lane = row of the accumulator = (block, channel) ----
+    // Chunk c of the reduction is complete when the MMA thread's commit flips `accum` for the c-th time.  The first
+    // chunk is stored, later ones are added to what this CTA stored before (same thread, same addresses: program order).
+    const int chunks_total = (kblocks + a.chunk_kb - 1) / a.chunk_kb;
+    const bool drains = warp < 4 * a.nacc;
+    // what the fold needs, as plain values (the call is out of line: see fold_accumulator)
+    FoldArgs fa;
+    {
+      const int taps = g.kh * g.kw;
+      const int quarter = warp & 3, u = warp >> 2;
+      // block index: horizontal tap (taps in M) or channel block (1x1 filter in the block arrangement)
+      const bool taps_in_m = a.xblocks == 1 || a.blocks_are_taps;
+      const int kx = taps_in_m ? kx0 + quarter : 0;
+      const int ci = ci0 + u * 32 + (taps_in_m ? lane : quarter * 32 + lane);
+      fa.cols = (long long)g.cig * taps;
+      fa.row_ok = kx < g.kw && ci < g.cig;
+      fa.out = a.out + ((long long)split * g.cout + (long long)group * g.cog + co0) * fa.cols +
+               (a.partial_layout ? (long long)(ky * g.kw + kx) * g.cig + ci : (long long)ci * taps + ky * g.kw + kx);
+      fa.acc = tmem_acc + (uint32_t)u * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
+      fa.cols_valid = cols_valid;
+      fa.acc_buffer_cols = acc_buffer_cols;
+      fa.nbuf = nbuf;
+      fa.accum_bar = smem_u32(&ctrl->accum[0]);
+      fa.drained_bar = smem_u32(&ctrl->drained[0]);
+      fa.abort_flag = &ctrl->abort_flag;
+      fa.status = a.status;
+    }
+    auto drain = [&](int c) -> bool { return fold_accumulator<BN, FUSE_HILO>(fa, c, c + (int)nbuf < chunks_total); };
     // consecutive jobs of a warp stay within `stages` K blocks of each other (a waiter that skipped
     // a whole phase of a stage's mbarrier would see the parity of an older phase and run ahead)
     const int warps_active = min(PRODUCER_WARPS, tasks * a.stages);
-    bool alive = warp < warps_active;
-    for (int job = warp; job < total_jobs && alive; job += warps_active) {
+    const bool produces = warp < warps_active;
+    bool alive = true;
+    int job = warp;
+    // chunk by chunk: this warp's staging jobs of the chunk (the inner loop is the hot one), then, for an
+    // epilogue warp, the fold of that chunk -- so a warp never stages blocks of a later chunk before it has
+    // folded the earlier one, and the MMA thread never waits for a fold that waits for this warp's blocks
+    for (int chunk = 0; chunk < chunks_total && alive; ++chunk) {
+    // ... except for the first `stages` K blocks of the next chunk, which it stages BEFORE folding: their slots
+    // were last used by blocks of this chunk, so staging them depends on nothing the fold waits for, and the
+    // MMA thread finds a full pipeline when the fold hands the accumulator back
+    const int job_end = chunk + 1 < chunks_total ? min(total_jobs, ((chunk + 1) * a.chunk_kb + a.stages) * tasks) : total_jobs;
+    for (; produces && job < job_end && alive; job += warps_active) {
       const int kb = (int)a.div_tasks.div((uint32_t)job), j = job - kb * tasks;
       const uint32_t round = a.div_stages.div((uint32_t)kb);
       const int s = kb - (int)round * a.stages;
@@ -439,49 +574,13 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
       mbar_arrive(smem_u32(&ctrl->full[s]));
       if (pp) { atomicAdd(a.prof + 4, (unsigned long long)(clock64() - tw)); atomicAdd(a.prof + 5, 1ull); } }
     }
-    // ---- epilogue (warps 0-3): lane = row of the accumulator = (block, channel) ----
-    const bool pe = DPROF_ON(threadIdx.x == 0);
-    DPROF_T0(pe);
-    // warp w reads TMEM lanes 32*(w & 3); warps 4-7 take the second accumulator
-    if (warp < 4 * a.nacc && mbar_wait(smem_u32(&ctrl->accum), 0, abort_flag, a.status, STATUS_TIMEOUT_ACCUM)) {
-      DPROF_ADD(pe, 6);
-      tc_fence_after();
-      const int taps = g.kh * g.kw;
-      const long long cols = (long long)g.cig * taps;
-      const int quarter = warp & 3, u = warp >> 2;
-      // block index: horizontal tap (taps in M) or channel block (1x1 filter in the block arrangement)
-      const bool taps_in_m = a.xblocks == 1 || a.blocks_are_taps;
-      const int kx = taps_in_m ? kx0 + quarter : 0;
-      const int ci = ci0 + u * 32 + (taps_in_m ? lane : quarter * 32 + lane);
-      const bool row_ok = kx < g.kw && ci < g.cig;
-      float* out = a.out + ((long long)split * g.cout + (long long)group * g.cog + co0) * cols +
-                   (a.partial_layout ? (long long)(ky * g.kw + kx) * g.cig + ci : (long long)ci * taps + ky * g.kw + kx);
-      const uint32_t acc = tmem_acc + (uint32_t)u * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        if (c0 >= cols_valid) break;
-        float v[32];
-        tmem_ld32(acc + (uint32_t)c0, v);
-        if (FUSE_HILO) {
-          float v2[32];
-          tmem_ld32(acc + (uint32_t)(BN + c0), v2);
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] += v2[j];
-        }
-        if (row_ok) {
-          float* p = out + c0 * cols;
-          const int nvalid = cols_valid - c0;
-          if (nvalid >= 32) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j, p += cols) *p = v[j];
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j, p += cols)
-              if (j < nvalid) *p = v[j];
-          }
-        }
-      }
+    if (drains && alive) {
+      const bool pe = DPROF_ON(threadIdx.x == 0);
+      DPROF_T0(pe);
+      alive = drain(chunk);
       DPROF_ADD(pe, 7);
+      if (pe) atomicAdd(a.prof + 8, 1ull);
+    }
     }
   }
   tc_fence_before();
@@ -505,6 +604,9 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
 // `splits` times the writes, are coalesced.
 __global__ void __launch_bounds__(256) finalize_partials_kernel(const float* __restrict__ partial, float* __restrict__ dw,
                                                                long long count, int splits, int cig, int taps) {
+  // launched with programmatic stream serialisation behind the kernel that writes the partials: its blocks may be
+  // resident before that kernel has finished, and wait here until it has (and its stores are visible)
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const long long i = blockIdx.x * 256ll + threadIdx.x;
   if (i >= count) return;
   float sum = 0.f;
@@ -564,8 +666,8 @@ static DwStripPlan plan_dw_strip(const ConvGeom& g, size_t budget) {
   // Several channel blocks per CTA share every staged dY block (one TMEM accumulator each): less dY
   // staging per MMA.  The column tile then stays at 128 (TMEM holds 512 columns).
   if (p.xblocks == 1 && g.cig >= 64) {
-    p.cross = g.cig >= 128;
-    p.nacc = p.cross ? 4 : 2;
+    p.cross = g.cig >= 128 || getenv("B200_DW_FORCE_CROSS") != nullptr;
+    p.nacc = p.cross && g.cig > 64 ? 4 : 2;
     p.bn = g.cog <= 64 ? 64 : 128;
   } else {
     p.bn = g.cog <= 64 ? 64 : (g.cog <= 128 ? 128 : 256);
@@ -650,6 +752,13 @@ int dweight_strip(const ConvGeom& g, View4 x, View4 dy, float* dw, void* ws, siz
   a.row_div = FastDiv((uint32_t)(a.W + a.pc));
   a.span = plan.span; a.splits = plan.splits; a.xblocks = plan.xblocks;
   a.ci_tiles = plan.ci_tiles; a.co_tiles = plan.co_tiles; a.stages = plan.stages;
+  {  // equal chunks of at most CHUNK_KB K blocks per CTA (a CTA reduces span / KP of them)
+    int limit = CHUNK_KB;
+    if (const char* e = getenv("B200_DW_CHUNK_KB")) limit = std::max(1, atoi(e));  // testing aid: chain length in K blocks
+    const int kblocks = plan.span / KP;
+    const int chunks = (kblocks + limit - 1) / limit;
+    a.chunk_kb = std::max(1, (kblocks + chunks - 1) / std::max(1, chunks));
+  }
   a.div_tasks = FastDiv((uint32_t)(plan.nacc * (plan.blocks_are_taps ? std::min(4, g.kw) : plan.xblocks) * (plan.xr > 32 ? 2 : 1) + plan.bn / 32));
   a.div_stages = FastDiv((uint32_t)plan.stages);
   a.out = plan.splits > 1 ? (float*)ws : dw;
@@ -680,13 +789,18 @@ int dweight_strip(const ConvGeom& g, View4 x, View4 dy, float* dw, void* ws, siz
     B200_CUDA(cudaStreamSynchronize(st));
     B200_CUDA(cudaMemcpy(h, prof_buf, sizeof h, cudaMemcpyDeviceToHost));
     fprintf(stderr, "[dweight strip profile, CTA 0, cycles] bn=%d xblocks=%d stages=%d grid=%lldx%d kblocks/cta=%d | mma: wait_full %llu issue %llu | "
-            "warp 0: jobs %llu load %llu wait_empty %llu store %llu | epilogue: wait_accum(total) %llu drain %llu | ns: last CTA start %llu, first start to last end %llu, CTA lifetime min %llu max %llu\n",
-            plan.bn, plan.xblocks, plan.stages, gx, plan.splits, plan.span / KP, h[0], h[1], h[5], h[2], h[3], h[4], h[6], h[7], h[12] - h[11], h[13] - h[11], h[14], h[15]);
+            "warp 0: jobs %llu load %llu wait_empty %llu store %llu | folds: %llu, cycles in them %llu (of which waiting for the accumulator %llu) | ns: last CTA start %llu, first start to last end %llu, CTA lifetime min %llu max %llu\n",
+            plan.bn, plan.xblocks, plan.stages, gx, plan.splits, plan.span / KP, h[0], h[1], h[5], h[2], h[3], h[4], h[8], h[7], h[6], h[12] - h[11], h[13] - h[11], h[14], h[15]);
   }
   if (plan.splits > 1) {
     const long long count = (long long)g.cout * g.cig * g.kh * g.kw;
-    finalize_partials_kernel<<<(unsigned)div_up64(count, 256), 256, 0, st>>>((const float*)ws, dw, count, plan.splits, g.cig,
-                                                                            g.kh * g.kw);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)div_up64(count, 256)); cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = 0; cfg.stream = st;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    if (!getenv("B200_DW_NO_PDL")) { cfg.attrs = &attr; cfg.numAttrs = 1; }
+    B200_CUDA(cudaLaunchKernelEx(&cfg, finalize_partials_kernel, (const float*)ws, dw, count, plan.splits, g.cig, g.kh * g.kw));
     count_launch();
     return launch_check("finalize_partials_kernel");
   }

@@ -37,6 +37,7 @@
 #include <cuda_bf16.h>
 
 #include "common.cuh"
+#include "strip_plan.cuh"
 #include "tc_common.cuh"
 
 #include <algorithm>
@@ -53,21 +54,8 @@ constexpr int BLOCK_M = 128, KBLK = 32;
 constexpr int EPI_WARPS = 4, A_WARPS = 8, W_WARPS = 1;
 constexpr int MMA_WARP = EPI_WARPS + A_WARPS + W_WARPS;
 constexpr int THREADS = (MMA_WARP + 1) * 32;
-constexpr int MAX_TAPS = 64, MAX_PHASES = 16;
 constexpr int MAX_STAGES = 4;
 constexpr int SMEM_LIMIT = 232448 - 2048;  // 227 KB per CTA minus the control block and alignment slack
-
-// Filter taps grouped by the input phase they read.  With stride s the input row of output row oy
-// and tap ky is s*oy + ky*d - pad = s*(oy + dr) + a with a = (ky*d - pad) mod s: tap ky reads the
-// sub-image made of rows = a (mod s) ("phase a") at the whole-pixel offset dr.  Channel blocks are
-// therefore enumerated per phase, and each phase runs only its own taps (stride 1: one phase, all taps).
-struct TapTable {
-  int n_phase = 0, taps_total = 0;
-  unsigned char a[MAX_PHASES], b[MAX_PHASES];  // row / column phase of active phase i
-  unsigned char start[MAX_PHASES + 1];         // taps of phase i: [start[i], start[i+1])
-  unsigned char ky[MAX_TAPS], kx[MAX_TAPS];    // filter position of tap t
-  int shift[MAX_TAPS];                         // strip row offset of tap t
-};
 
 struct StripArgs {
   ConvGeom g;
@@ -660,19 +648,12 @@ __global__ void __launch_bounds__(256) stage_weights_kernel(ConvGeom g, View4 w,
 
 static inline int floor_div(int a, int b) { return a >= 0 ? a / b : -((-a + b - 1) / b); }
 
-struct StripPlan {
-  bool ok = false;
-  int bn = 0, a_stages = 0, w_stages = 0, strip_rows = 0, halo = 0, smem = 0;
-  int gh = 0, gw = 0, pr = 0, pc = 0;  // pixel grid and its padding
-  int act_h = 0, act_w = 0, out_h = 0, out_w = 0, sph = 1, spw = 1;
-  TapTable tt;
-};
 
 // Any stride / padding / dilation in both directions; the reduction channels must come in blocks of
 // 32 and there must be at least 16 output columns.  Forward groups the taps by the phase of the
 // INPUT pixel they read; dInput by the phase of the OUTPUT (dX) pixel they contribute to: dX pixel
 // s*r + a receives tap ky iff (ky*d - pad) = a (mod s), from dY row r - floor((ky*d - pad) / s).
-static StripPlan plan_strip(const ConvGeom& g, bool is_dx) {
+StripPlan plan_strip_geometry(const ConvGeom& g, bool is_dx) {
   StripPlan p;
   const int kc = is_dx ? g.cog : g.cig, nc = is_dx ? g.cig : g.cog;
   // a ragged last channel block is padded with zeros; below 16 channels the padding would more than
@@ -720,8 +701,18 @@ static StripPlan plan_strip(const ConvGeom& g, bool is_dx) {
     tt.start[tt.n_phase + 1] = (unsigned char)tt.taps_total;
     ++tt.n_phase;
   }
+  p.shift_lo = lo; p.shift_hi = hi;
   p.halo = -lo;
-  p.strip_rows = (BLOCK_M + hi - lo + 7) / 8 * 8;
+  p.ok = true;
+  return p;
+}
+
+static StripPlan plan_strip(const ConvGeom& g, bool is_dx) {
+  StripPlan p = plan_strip_geometry(g, is_dx);
+  if (!p.ok) return p;
+  p.ok = false;
+  const int nc = is_dx ? g.cig : g.cog;
+  p.strip_rows = (BLOCK_M + p.shift_hi - p.shift_lo + 7) / 8 * 8;
   const int a_stage = p.strip_rows * 256;
   // Column tile: the widest tile makes the best use of shared-memory bandwidth per MMA, but a small
   // image gives few 128-pixel row tiles; pick the width with the lowest modelled time

@@ -131,7 +131,8 @@ int b200_conv2d_select(const b200_conv_params* p, int phase, int algo, size_t wo
  * forward, dy for dInput; only the strides are read, the pointer is not dereferenced):
  * 0 = strip kernel; 1 = per-tap gather kernel (views that span 2^31 elements or more, reduction
  * channels in whole blocks of 32); 2 = CUDA-core implicit GEMM (such a view with a ragged channel
- * count, which the gather kernel would truncate).  <0 if the candidate does not take the geometry.
+ * count, which the gather kernel would truncate); 3 = transposed strip kernel (filter on the M side, 65 or
+ * more output channels per group; 64-bit view offsets).  <0 if the candidate does not take the geometry.
  * Part of execute_candidate's role, csrc/ops/convolution.cpp:483-520 (kernel choice per memory class). */
 int b200_conv2d_tc_route(const b200_conv_params* p, int phase, b200_view4 act);
 /* Scratch bytes the selected candidate wants (0 = none).  For dWeight this is the

@@ -284,7 +284,7 @@ def select(p, phase, algo=ALGO_AUTO, budget=DEFAULT_WORKSPACE):
 
 
 def tc_route(p, phase, strides):
-    """0 strip kernel, 1 gather kernel, 2 CUDA-core implicit GEMM for a tcgen05 forward / dInput call on an
+    """0 strip kernel, 1 gather kernel, 2 CUDA-core implicit GEMM, 3 transposed strip kernel for a tcgen05 forward / dInput call on an
     activation view with these element strides (host arithmetic only; no device memory is touched)."""
     return check(lib().b200_conv2d_tc_route(ctypes.byref(p), phase, View4(None, (c_int64 * 4)(*strides))))
 

@@ -124,6 +124,11 @@ int post_ops_nchw(float* y, const ConvGeom& g, const StripPostOps& post, cudaStr
 int bias_add_nchw(float* y, long long n, int channels, long long plane, const float* bias, long long bias_stride, cudaStream_t st);
 bool strip_view_addressable(const ConvGeom& g, bool is_dx, const View4& act, const StripBatch* batch);
 int tc_route(const ConvGeom& g, bool is_dx, const View4& act);  // 0 strip, 1 gather, 2 CUDA-core implicit GEMM (conv_tc.cu)
+// transposed strip kernel (conv_tc_tstrip.cu): filter on M, up to 256 pixels on N; contiguous NCHW results
+bool tstrip_supported(const ConvGeom& g, int phase);
+size_t tstrip_workspace(const ConvGeom& g, int phase);
+int tstrip_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* bias, long long bias_stride, float* out,
+                void* ws, size_t ws_bytes, cudaStream_t st);
 int strip_column_tile(const ConvGeom& g, bool is_dx);   // column tile the plan picks, 0 if unsupported
 size_t strip_workspace(const ConvGeom& g, int phase);  // bytes of the weight stage images
 

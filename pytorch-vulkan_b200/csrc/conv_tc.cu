@@ -610,7 +610,9 @@ size_t tc_workspace(const ConvGeom& g, int phase, size_t budget, int* splits_out
   if (span_out) *span_out = 0;
   if (phase == B200_PHASE_FORWARD || phase == B200_PHASE_DINPUT) {
     const size_t planes = 2 * sizeof(float) * (size_t)g.cout * g.cig * g.kh * g.kw;  // hi + lo
-    return strip_allowed() && strip_supported(g, phase) ? std::max(planes, strip_workspace(g, phase)) : planes;
+    size_t need = strip_allowed() && strip_supported(g, phase) ? std::max(planes, strip_workspace(g, phase)) : planes;
+    if (strip_allowed() && tstrip_supported(g, phase)) need = std::max(need, tstrip_workspace(g, phase));
+    return need;
   }
   if (phase == B200_PHASE_DWEIGHT && strip_allowed() && dweight_strip_supported(g)) {
     if (splits_out) *splits_out = 0;
@@ -704,10 +706,13 @@ static int conv_tc_run(const ConvGeom& g, bool is_dx, View4 act, View4 w, const 
 //   1  the gather kernel: the strip kernel declines at run time (a view that spans more elements than its
 //      32-bit offsets address) and the reduction channels come in whole blocks of 32, which the gather
 //      kernel needs (it has no ragged-block padding);
-//   2  the CUDA-core implicit GEMM: everything else (a ragged channel count on such a view).
+//   2  the CUDA-core implicit GEMM: everything else (a ragged channel count on such a view);
+//   3  the transposed strip kernel, where most of a 128-channel tile is real output channels.
 // Pure host arithmetic on the geometry and the view's strides; nothing is dereferenced.
 int tc_route(const ConvGeom& g, bool is_dx, const View4& act) {
   const int kc = is_dx ? g.cog : g.cig;
+  // 3: the transposed strip kernel (filter on M), which addresses the view with 64-bit offsets
+  if (strip_allowed() && tstrip_supported(g, is_dx ? B200_PHASE_DINPUT : B200_PHASE_FORWARD)) return 3;
   if (strip_allowed() && strip_supported(g, is_dx ? B200_PHASE_DINPUT : B200_PHASE_FORWARD) &&
       strip_view_addressable(g, is_dx, act, nullptr))
     return 0;
@@ -717,6 +722,12 @@ int tc_route(const ConvGeom& g, bool is_dx, const View4& act) {
 int tc_forward(const ConvGeom& g, View4 x, View4 w, const float* bias, long long bias_stride, float* y, void* ws,
                size_t ws_bytes, cudaStream_t st) {
   int route = tc_route(g, false, x);
+  if (route == 3) {
+    note_kernel("tc_tstrip_forward");
+    const int rc = tstrip_conv(g, false, x, w, bias, bias_stride, y, ws, ws_bytes, st);
+    if (rc != B200_EUNSUPPORTED) return rc;
+    route = strip_supported(g, B200_PHASE_FORWARD) && strip_view_addressable(g, false, x, nullptr) ? 0 : (g.cig % KBLK == 0 ? 1 : 2);
+  }
   if (route == 0) {
     note_kernel("tc_strip_forward");
     const int rc = strip_conv(g, false, x, w, bias, bias_stride, y, ws, ws_bytes, st);
@@ -732,6 +743,12 @@ int tc_forward(const ConvGeom& g, View4 x, View4 w, const float* bias, long long
 }
 int tc_dinput(const ConvGeom& g, View4 dy, View4 w, float* dx, void* ws, size_t ws_bytes, cudaStream_t st) {
   int route = tc_route(g, true, dy);
+  if (route == 3) {
+    note_kernel("tc_tstrip_dinput");
+    const int rc = tstrip_conv(g, true, dy, w, nullptr, 0, dx, ws, ws_bytes, st);
+    if (rc != B200_EUNSUPPORTED) return rc;
+    route = strip_supported(g, B200_PHASE_DINPUT) && strip_view_addressable(g, true, dy, nullptr) ? 0 : (g.cog % KBLK == 0 ? 1 : 2);
+  }
   if (route == 0) {
     note_kernel("tc_strip_dinput");
     const int rc = strip_conv(g, true, dy, w, nullptr, 0, dx, ws, ws_bytes, st);

@@ -204,10 +204,13 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
 
   if (warp == MMA_WARP) {
     // ------------------------------ MMA issuer ------------------------------
-    // One thread.  The tensor pipe accepts only a few instructions ahead of the one it executes, so
-    // whatever this thread does between two tcgen05.mma shows up as idle tensor time: stage indices
-    // and parities are counted, not divided, and descriptors are the stage's base plus an offset.
-    if (lane == 0) {
+    // The whole warp runs the loop and waits on the barriers; one elected lane issues the tcgen05 instructions.
+    // With uniform control flow the descriptors live in uniform registers, which is where tcgen05.mma reads its
+    // operands (issued from one divergent thread, every operand crossed over from the vector registers first, and
+    // that crossing paced the kernel).  Stage indices and parities are counted, not divided, and descriptors are
+    // the stage's base plus an offset.
+    {
+      const bool leader = elect_one();
       constexpr uint32_t idesc = make_idesc_tf32(BLOCK_M, BN);
       constexpr uint32_t idesc_wide = make_idesc_tf32(BLOCK_M, FUSE_HILO ? 2 * BN : BN);
       constexpr uint32_t idesc_cross = make_idesc_bf16(BLOCK_M, BN);
@@ -216,14 +219,15 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
       const uint32_t a_stage_d = a_stage_bytes >> 4, a_plane_d = a_plane >> 4;
       constexpr uint32_t w_stage_d = w_stage_bytes >> 4, w_plane_d = w_plane >> 4;
       uint32_t as = 0, a_par = 0, ws = 0, w_par = 0, t_count = 0;
-      const bool pm = PROF_ON(true);
+      const bool pm = PROF_ON(lane == 0);
       bool alive = true;
       for (TileIter it(a); it.valid() && alive; it.next(), ++t_count) {
         const int tile = it.tile();
         const uint32_t ab = t_count & 1;
         { PROF_T0(pm);
-        if (!mbar_wait(smem_u32(&ctrl->acc_empty[ab]), ((t_count >> 1) & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_ACCUM)) break;
+        if (!warp_wait(smem_u32(&ctrl->acc_empty[ab]), ((t_count >> 1) & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_ACCUM)) break;
         PROF_ADD(pm, 0); }
+        tc_fence_after();
         const uint32_t tmem_acc = tmem_base + ab * ACC_COLS;
         const int n_tile = tile_coord(a, tile).n_tile;
         int phase = a.phase_on_n ? (int)a.div_tiles_pp.div((uint32_t)n_tile) : 0;  // dInput: the phase of this column tile
@@ -231,22 +235,22 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
         uint32_t accumulate = 0;  // the tile's first MMA overwrites the accumulator
         for (int cb = 0; cb < a.cblocks && alive; ++cb) {
           { PROF_T0(pm);
-          if (!mbar_wait(smem_u32(&ctrl->a_full[as]), a_par, abort_flag, a.status, STATUS_TIMEOUT_FULL)) { alive = false; break; }
+          if (!warp_wait(smem_u32(&ctrl->a_full[as]), a_par, abort_flag, a.status, STATUS_TIMEOUT_FULL)) { alive = false; break; }
           PROF_ADD(pm, 1); }
           const uint64_t da_strip = da_base + as * a_stage_d;
           const int tap_end = ctrl->tap_start[phase + 1];
           for (int tap = ctrl->tap_start[phase]; tap < tap_end; ++tap) {
             const int sh = ctrl->shift[tap];
             { PROF_T0(pm);
-            if (!mbar_wait(smem_u32(&ctrl->w_full[ws]), w_par, abort_flag, a.status, STATUS_TIMEOUT_FULL)) { alive = false; break; }
+            if (!warp_wait(smem_u32(&ctrl->w_full[ws]), w_par, abort_flag, a.status, STATUS_TIMEOUT_FULL)) { alive = false; break; }
             PROF_ADD(pm, 2); }
-            tc_fence_after();
             PROF_T0(pm);
             const uint64_t da_hi = da_strip + (uint64_t)(long long)(sh * 8), da_lo = da_hi + a_plane_d;
             const uint64_t db_hi = db_base + ws * w_stage_d, db_lo = db_hi + w_plane_d;
             const uint32_t first = accumulate;
             accumulate = 1;
-            if (CROSS_BF16) {  // hi x hi in TF32, then both cross terms as one BF16 product over the second planes
+            if (!leader) {
+            } else if (CROSS_BF16) {  // hi x hi in TF32, then both cross terms as one BF16 product over the second planes
 #pragma unroll
               for (int kk = 0; kk < 4; ++kk) umma_tf32(tmem_acc, da_hi + 2 * kk, db_hi + 2 * kk, idesc, first | (uint32_t)(kk != 0));
 #pragma unroll
@@ -264,15 +268,15 @@ __global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs 
 #pragma unroll
               for (int kk = 0; kk < 4; ++kk) umma_tf32(tmem_acc, da_hi + 2 * kk, db_hi + 2 * kk, idesc, 1);
             }
-            umma_commit(smem_u32(&ctrl->w_empty[ws]));
+            if (leader) umma_commit(smem_u32(&ctrl->w_empty[ws]));
             if (++ws == (uint32_t)a.w_stages) { ws = 0; w_par ^= 1; }
             PROF_ADD(pm, 3);
           }
-          if (alive) umma_commit(smem_u32(&ctrl->a_empty[as]));
+          if (alive && leader) umma_commit(smem_u32(&ctrl->a_empty[as]));
           if (++as == (uint32_t)a.a_stages) { as = 0; a_par ^= 1; }
           if (!a.phase_on_n && ++cbl == a.cb_per_phase) { cbl = 0; ++phase; }
         }
-        if (alive) umma_commit(smem_u32(&ctrl->acc_full[ab]));
+        if (alive && leader) umma_commit(smem_u32(&ctrl->acc_full[ab]));
       }
     }
   } else if (warp == EPI_WARPS + A_WARPS) {

@@ -387,9 +387,12 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
   const int yshift = dr * row_pitch;
 
   if (warp == MMA_WARP) {
-    // One thread; stage indices are counted and descriptors are base + offset, because everything
-    // this thread does between two tcgen05.mma is idle time of the tensor pipe.
-    if (lane == 0) {
+    // The whole warp runs the loop and waits on the barriers; one elected lane issues the tcgen05 instructions.  With
+    // uniform control flow the descriptors live in uniform registers, which is where tcgen05.mma reads its operands
+    // (issued from one divergent thread, every operand crossed over from the vector registers first, and that
+    // crossing, not the tensor pipe, paced the kernel).  Stage indices are counted and descriptors are base + offset.
+    {
+      const bool leader = elect_one();
       constexpr uint32_t idesc = make_idesc_tf32(128, BN) | (1u << 15) | (1u << 16);  // both operands MN-major
       constexpr uint32_t idesc_wide = make_idesc_tf32(128, FUSE_HILO ? 2 * BN : BN) | (1u << 15) | (1u << 16);
       const uint32_t a_lbo = a.xblocks == 1 ? (uint32_t)g.dw * 128u : 2u * x_plane;
@@ -404,7 +407,7 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
       const uint32_t a_lbo16 = a.xblocks == 1 ? (uint32_t)g.dw * 64u : 2u * x_plane;
       const uint64_t da16_base = make_mn_desc16(base + x_plane + (a.xblocks == 1 ? (uint32_t)(XOFF - g.pw + kx0 * g.dw) * 64u : 0u), a_lbo16);
       const uint64_t db16_base = make_mn_desc16(base + x_bytes + y_plane, KP * 64u);
-      const bool pm = DPROF_ON(true);
+      const bool pm = DPROF_ON(lane == 0);
       uint32_t s = 0, par = 0;
       int kb_in_chunk = 0;
       uint32_t chunk = 0, buf = 0;
@@ -412,23 +415,23 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
         if (kb_in_chunk == a.chunk_kb) {
           // chunk boundary: hand the accumulator to the epilogue warps; before the next buffer is overwritten its
           // previous chunk (nbuf chunks back) must have been read
-          umma_commit(smem_u32(&ctrl->accum[buf]));
+          if (leader) umma_commit(smem_u32(&ctrl->accum[buf]));
           ++chunk;
           kb_in_chunk = 0;
           buf = nbuf == 2 ? chunk & 1u : 0u;
           if (chunk >= nbuf) {
             const uint32_t prev_use = (chunk - nbuf) / nbuf;
-            if (!mbar_wait(smem_u32(&ctrl->drained[buf]), prev_use & 1u, abort_flag, a.status, STATUS_TIMEOUT_ACCUM)) break;
+            if (!warp_wait(smem_u32(&ctrl->drained[buf]), prev_use & 1u, abort_flag, a.status, STATUS_TIMEOUT_ACCUM)) break;
             tc_fence_after();
           }
         }
         { DPROF_T0(pm);
-        if (!mbar_wait(smem_u32(&ctrl->full[s]), par, abort_flag, a.status, STATUS_TIMEOUT_FULL)) break;
+        if (!warp_wait(smem_u32(&ctrl->full[s]), par, abort_flag, a.status, STATUS_TIMEOUT_FULL)) break;
         DPROF_ADD(pm, 0); }
-        tc_fence_after();
         DPROF_T0(pm);
         const uint64_t da_hi = da_base + s * stage_d;
         const uint64_t db_hi = db_base + s * stage_d, db_lo = db_hi + y_plane_d;
+        if (leader)
         for (int u = 0; u < a.nacc; ++u) {  // channel blocks that share this dY block
           const uint32_t acc = tmem_acc + buf * acc_buffer_cols + (uint32_t)u * ACC_COLS;
           const uint64_t ua_hi = da_hi + (uint64_t)u * (2 * x_plane_d), ua_lo = ua_hi + x_plane_d;
@@ -455,11 +458,11 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
             }
           }
         }
-        umma_commit(smem_u32(&ctrl->empty[s]));
+        if (leader) umma_commit(smem_u32(&ctrl->empty[s]));
         if (++s == (uint32_t)a.stages) { s = 0; par ^= 1; }
         DPROF_ADD(pm, 1);
       }
-      umma_commit(smem_u32(&ctrl->accum[buf]));
+      if (leader) umma_commit(smem_u32(&ctrl->accum[buf]));
     }
   } else {
     // ---- producers: job j of K block kb goes to warp (kb*tasks + j) % 16 ----

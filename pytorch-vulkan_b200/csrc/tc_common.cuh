@@ -88,6 +88,22 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
   return true;
 }
+// One lane of a converged warp (the same lane every time), for instructions that a single thread must issue
+// while the warp's control flow stays uniform.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t is_leader;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(is_leader));
+  return is_leader != 0;
+}
+// mbar_wait for a whole warp: every lane polls, and the warp leaves together with one answer.
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+  const bool ok = mbar_wait(bar, parity, abort_flag, status, code);
+  return __all_sync(0xffffffffu, ok);
+}
 // Bulk copy global -> shared memory of this CTA; completion is counted in bytes on `bar`
 // (pair it with mbar_expect_tx).  Both addresses 16-byte aligned, size a multiple of 16.
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {

@@ -95,11 +95,15 @@ def test_tc_matches_golden_layer64():
     ((2, 256, 6, 6), 96, (3, 3), dict(padding=(1, 1), groups=2)),  # ... per group
 ], ids=lambda s: "x".join(map(str, s[0])) + f"-co{s[1]}-k{s[2][0]}x{s[2][1]}" if isinstance(s, tuple) and len(s) == 4 else None)
 @pytest.mark.parametrize("channels_last", [False, True], ids=["nchw", "nhwc"])
-@pytest.mark.parametrize("variant", ["strip", "gather"])
+@pytest.mark.parametrize("variant", ["auto", "strip", "gather"])
 def test_tc_forward_and_dinput_shapes(shape, channels_last, variant, monkeypatch):
-    # "gather" pins the per-tap gather kernel; "strip" lets the persistent strip kernel take every
-    # geometry whose reduction channels come in blocks of 32 (the others run the gather kernel either way)
-    monkeypatch.setenv("B200_CONV_TC_VARIANT", variant)
+    # "gather" pins the per-tap gather kernel; "strip" the persistent strip kernel with pixels on the M side (every
+    # geometry whose reduction channels come in blocks of 32; the others run the gather kernel either way); "auto" is
+    # the library's own choice, which adds the transposed strip kernel from 65 output channels per group
+    if variant == "auto":
+        monkeypatch.delenv("B200_CONV_TC_VARIANT", raising=False)
+    else:
+        monkeypatch.setenv("B200_CONV_TC_VARIANT", variant)
     xshape, cout, kernel, kw = shape
     groups = kw.get("groups", 1)
     # the tcgen05 dInput kernel reduces over 32-channel blocks of Cout/groups
@@ -230,3 +234,37 @@ def test_winograd_f4_forward_and_dinput(shape, budget):
             b200conv.conv2d_backward(go, x, w, mask=(True, False, False), algo="winograd", budget=budget, **args)
     assert b200conv.device_status() == 0
     assert max(errs) <= GATE_WINOGRAD, errs
+
+
+@pytest.mark.parametrize("shape", [
+    # the transposed strip kernel: ragged channel tiles, ragged 16-channel blocks, several tiles per CTA, phases
+    ((2, 80, 19, 23), 96, (3, 3), dict(padding=(1, 1))),
+    ((3, 40, 30, 30), 200, (3, 3), dict(padding=(1, 1))),                 # two channel tiles, the second 72 wide
+    ((2, 72, 14, 14), 128, (1, 1), dict()),                               # no halo
+    ((8, 128, 28, 28), 128, (3, 3), dict(padding=(1, 1))),                # more tiles than SMs: both accumulators alternate
+    ((2, 128, 17, 17), 128, (3, 3), dict(stride=(2, 2), padding=(1, 1))), # input phases (forward), output phases (dInput)
+    ((2, 96, 16, 16), 192, (5, 5), dict(padding=(2, 2), groups=2)),       # 96 output channels per group
+    ((1, 128, 40, 120), 128, (3, 3), dict(padding=(1, 1))),               # wide rows: a long halo
+    ((2, 256, 9, 9), 256, (3, 3), dict(padding=(2, 2), dilation=(2, 2))),
+], ids=lambda s: "x".join(map(str, s[0])) + f"-co{s[1]}-k{s[2][0]}" if isinstance(s, tuple) and len(s) == 4 else None)
+@pytest.mark.parametrize("channels_last", [False, True], ids=["nchw", "nhwc"])
+def test_transposed_strip_kernel_shapes(shape, channels_last, monkeypatch):
+    monkeypatch.delenv("B200_CONV_TC_VARIANT", raising=False)
+    xshape, cout, kernel, kw = shape
+    groups = kw.get("groups", 1)
+    g = oracle.geometry(xshape, cout, kernel, **{k: v for k, v in kw.items()})
+    x, w = _rand(g.x_shape, 5), _rand(g.w_shape, 6, 0.1)
+    b, go = _rand((cout,), 7), _rand(g.y_shape, 8)
+    if channels_last:
+        x = np.ascontiguousarray(x.transpose(0, 2, 3, 1)).transpose(0, 3, 1, 2)
+        go = np.ascontiguousarray(go.transpose(0, 2, 3, 1)).transpose(0, 3, 1, 2)
+    args = dict(stride=kw.get("stride", (1, 1)), padding=kw.get("padding", (0, 0)), dilation=kw.get("dilation", (1, 1)), groups=groups)
+    want = _reference(x, w, b, go, args)
+    y = b200conv.conv2d_forward(x, w, b, algo="tc", **args)
+    assert b200conv.last_kernel() == "tc_tstrip_forward"
+    dx = b200conv.conv2d_backward(go, x, w, mask=(True, False, False), algo="tc", **args)[0]
+    if xshape[1] // groups >= 65:
+        assert b200conv.last_kernel() == "tc_tstrip_dinput"
+    assert b200conv.device_status() == 0
+    errs = [oracle.rel_l2(y, want[0]), oracle.rel_l2(dx, want[1])]
+    assert max(errs) <= GATE, errs

@@ -58,6 +58,8 @@ constexpr int W_WARP = EPI_WARPS + A_WARPS, MMA_WARP = W_WARP + 1;
 constexpr int THREADS = (MMA_WARP + 1) * 32;
 constexpr int MAX_A_STAGES = 4, MAX_W_STAGES = 8;
 constexpr uint32_t W_STAGE_BYTES = TM * ROWB * 2;   // hi plane + cross plane of one (tap, channel block)
+constexpr uint32_t W_RING_BYTES = 2 * W_STAGE_BYTES;  // a ring stage holds the images of two consecutive taps: one wait and one
+                                                      // commit per eight MMAs (the issuing warp is bound by its own instruction latencies)
 constexpr int TBUF_BYTES = EPI_WARPS * 32 * 33 * 4;  // the epilogue's transpose tiles
 constexpr int SMEM_LIMIT = 232448 - 2048;
 
@@ -143,7 +145,7 @@ __global__ void __launch_bounds__(THREADS, 1) conv_tstrip_kernel(const TArgs a) 
   const uint32_t a_plane = (uint32_t)a.strip_rows * ROWB, a_stage_bytes = 2u * a_plane;
   constexpr uint32_t w_plane = TM * ROWB;
   const uint32_t w_base = tiles_base + a.a_stages * a_stage_bytes;
-  const uint32_t tbuf_base = w_base + a.w_stages * W_STAGE_BYTES;
+  const uint32_t tbuf_base = w_base + a.w_stages * W_RING_BYTES;
   Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem_raw + (tbuf_base - raw) + TBUF_BYTES);
   volatile int* abort_flag = &ctrl->abort_flag;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -191,7 +193,7 @@ __global__ void __launch_bounds__(THREADS, 1) conv_tstrip_kernel(const TArgs a) 
     const uint64_t dx_base = make_kmajor_sw64_desc(tiles_base + (uint32_t)a.halo * ROWB);
     const uint64_t dw_base = make_kmajor_sw64_desc(w_base);
     const uint32_t a_stage_d = a_stage_bytes >> 4, a_plane_d = a_plane >> 4;
-    constexpr uint32_t w_stage_d = W_STAGE_BYTES >> 4, w_plane_d = w_plane >> 4;
+    constexpr uint32_t w_stage_d = W_STAGE_BYTES >> 4, w_plane_d = w_plane >> 4, w_ring_d = W_RING_BYTES >> 4;
     const bool leader = elect_one();
     uint32_t as = 0, a_par = 0, ws = 0, w_par = 0;
     bool alive = true;
@@ -209,16 +211,23 @@ __global__ void __launch_bounds__(THREADS, 1) conv_tstrip_kernel(const TArgs a) 
         if (!warp_wait(smem_u32(&ctrl->a_full[as]), a_par, abort_flag, a.status, STATUS_TIMEOUT_FULL)) { alive = false; break; }
         const uint64_t dx_strip = dx_base + as * a_stage_d;
         const int tap_end = ctrl->tap_start[phase + 1];
-        for (int tap = ctrl->tap_start[phase]; tap < tap_end; ++tap) {
-          const int sh = ctrl->shift[tap];
+        for (int tap = ctrl->tap_start[phase]; tap < tap_end; tap += 2) {
+          const int sh0 = ctrl->shift[tap], sh1 = ctrl->shift[tap + 1 < tap_end ? tap + 1 : tap];
+          const bool two = tap + 1 < tap_end;
           if (!warp_wait(smem_u32(&ctrl->w_full[ws]), w_par, abort_flag, a.status, STATUS_TIMEOUT_FULL)) { alive = false; break; }
-          const uint64_t x_hi = dx_strip + (uint64_t)(long long)(sh * (ROWB / 16)), x_cr = x_hi + a_plane_d;
-          const uint64_t w_hi = dw_base + ws * w_stage_d, w_cr = w_hi + w_plane_d;
+          const uint64_t x0 = dx_strip + (uint64_t)(long long)(sh0 * (ROWB / 16)), x1 = dx_strip + (uint64_t)(long long)(sh1 * (ROWB / 16));
+          const uint64_t w0 = dw_base + ws * w_ring_d, w1 = w0 + w_stage_d;
           if (leader) {
-            umma_tf32(tmem_acc, w_hi, x_hi, idesc, accumulate);
-            umma_tf32(tmem_acc, w_hi + 2, x_hi + 2, idesc, 1);
-            umma_bf16(tmem_acc, w_cr, x_cr, idesc_cross, 1);
-            umma_bf16(tmem_acc, w_cr + 2, x_cr + 2, idesc_cross, 1);
+            umma_tf32(tmem_acc, w0, x0, idesc, accumulate);
+            umma_tf32(tmem_acc, w0 + 2, x0 + 2, idesc, 1);
+            umma_bf16(tmem_acc, w0 + w_plane_d, x0 + a_plane_d, idesc_cross, 1);
+            umma_bf16(tmem_acc, w0 + w_plane_d + 2, x0 + a_plane_d + 2, idesc_cross, 1);
+            if (two) {
+              umma_tf32(tmem_acc, w1, x1, idesc, 1);
+              umma_tf32(tmem_acc, w1 + 2, x1 + 2, idesc, 1);
+              umma_bf16(tmem_acc, w1 + w_plane_d, x1 + a_plane_d, idesc_cross, 1);
+              umma_bf16(tmem_acc, w1 + w_plane_d + 2, x1 + a_plane_d + 2, idesc_cross, 1);
+            }
             umma_commit(smem_u32(&ctrl->w_empty[ws]));
           }
           accumulate = 1;
@@ -250,14 +259,24 @@ __global__ void __launch_bounds__(THREADS, 1) conv_tstrip_kernel(const TArgs a) 
           images = a.images_per_tile;
           first_image = (group * a.tiles_m + tc_.m_tile) * a.images_per_tile;
         }
+        // images are ordered [channel block][tap of the phase]: the two taps of a ring stage are adjacent in memory,
+        // and a block with an odd tap count ends with a stage of one image
         const unsigned char* img = reinterpret_cast<const unsigned char*>(a.wp) + first_image * (long long)W_STAGE_BYTES;
-        for (int i = 0; i < images; ++i, img += W_STAGE_BYTES) {
-          if (!mbar_wait(smem_u32(&ctrl->w_empty[ws]), w_par, abort_flag, a.status, STATUS_TIMEOUT_EMPTY)) { alive = false; break; }
-          const uint32_t full = smem_u32(&ctrl->w_full[ws]);
-          mbar_expect_tx(full, W_STAGE_BYTES);
-          bulk_g2s(w_base + ws * W_STAGE_BYTES, img, W_STAGE_BYTES, full);
-          ++issued;
-          if (++ws == (uint32_t)a.w_stages) { ws = 0; w_par ^= 1; }
+        (void)images;
+        int phase = a.phase_on_m ? (int)a.div_tiles_pp.div((uint32_t)tc_.m_tile) : 0, cbl = 0;
+        for (int cb = 0; cb < a.cblocks && alive; ++cb) {
+          const int ntap = ctrl->tap_start[phase + 1] - ctrl->tap_start[phase];
+          for (int tap = 0; tap < ntap; tap += 2) {
+            const uint32_t bytes = tap + 1 < ntap ? W_RING_BYTES : W_STAGE_BYTES;
+            if (!mbar_wait(smem_u32(&ctrl->w_empty[ws]), w_par, abort_flag, a.status, STATUS_TIMEOUT_EMPTY)) { alive = false; break; }
+            const uint32_t full = smem_u32(&ctrl->w_full[ws]);
+            mbar_expect_tx(full, bytes);
+            bulk_g2s(w_base + ws * W_RING_BYTES, img, bytes, full);
+            ++issued;
+            if (++ws == (uint32_t)a.w_stages) { ws = 0; w_par ^= 1; }
+            img += bytes;
+          }
+          if (!a.phase_on_m && ++cbl == a.cb_per_phase) { cbl = 0; ++phase; }
         }
       }
       // after an abort nobody consumes the stages: wait (bounded) for the copies still in flight
@@ -528,17 +547,17 @@ static TPlan plan_tstrip(const ConvGeom& g, bool is_dx) {
     int a_stages = 0, w_stages = 0;
     for (int as : {3, 2}) {
       const int left = SMEM_LIMIT - TBUF_BYTES - 1024 - (int)sizeof(Ctrl) - as * a_stage;
-      if (left >= 4 * (int)W_STAGE_BYTES) { a_stages = as; w_stages = std::min(MAX_W_STAGES, left / (int)W_STAGE_BYTES); break; }
+      if (left >= 2 * (int)W_RING_BYTES) { a_stages = as; w_stages = std::min(MAX_W_STAGES, left / (int)W_RING_BYTES); break; }
     }
     if (!a_stages) continue;
     const long long tiles = div_up64(q_total, pn) * p.tiles_m * g.groups;
-    const double cost = (double)div_up64(tiles, sm_count()) * (stages_per_tile * 4.0 * mma_clocks(pn) + 3000.0);
+    const double cost = (double)div_up64(tiles, sm_count()) * (stages_per_tile * (4.0 * mma_clocks(pn) + 120.0) + 3000.0);
     if (!p.ok || cost < best * 0.995) {   // ties go to the wider tile (fewer filter bytes per output)
       best = cost;
       p.ok = true;
       p.pn = pn; p.strip_rows = rows; p.a_stages = a_stages; p.w_stages = w_stages;
       p.tiles_p = (int)div_up64(q_total, pn);
-      p.smem = a_stages * a_stage + w_stages * (int)W_STAGE_BYTES + TBUF_BYTES + 1024 + (int)sizeof(Ctrl) + 64;
+      p.smem = a_stages * a_stage + w_stages * (int)W_RING_BYTES + TBUF_BYTES + 1024 + (int)sizeof(Ctrl) + 64;
     }
   }
   if (p.ok && (long long)p.tiles_p * p.tiles_m * g.groups * p.cpp * ((p.strip_rows + 31) / 32) > 2147483647ll - (1 << 20)) p.ok = false;

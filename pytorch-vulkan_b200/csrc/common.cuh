@@ -90,6 +90,12 @@ int dbias_reduce(const ConvGeom& g, View4 dy, float* db, float* partial, int sla
 int simt_gemm(long long M, long long N, long long K, const float* A, long long sa0, long long sa1, const float* B,
               long long sb0, long long sb1, const float* bias, float alpha, float beta, float* C, cudaStream_t st);
 
+// grouped 3x3 convolutions with 4 or 8 channels per group (conv_group_small.cu)
+bool group_small_supported(const ConvGeom& g);
+size_t group_small_dweight_workspace(const ConvGeom& g);
+int group_small_conv(const ConvGeom& g, bool is_dx, View4 in, View4 w, const float* bias, long long bias_stride, float* out, cudaStream_t st);
+int group_small_dweight(const ConvGeom& g, View4 x, View4 dy, float* dw, float* ws, size_t ws_bytes, cudaStream_t st);
+
 // tcgen05 paths (conv_tc.cu)
 bool tc_supported(const ConvGeom& g, int phase);
 size_t tc_workspace(const ConvGeom& g, int phase, size_t budget, int* splits_out, int* span_out);

@@ -102,6 +102,8 @@ static int select(const ConvGeom& g, int phase, int algo, size_t workspace) {
   if (tc_supported(g, phase) &&
       (phase == B200_PHASE_DWEIGHT || tc_workspace(g, phase, workspace, nullptr, nullptr) <= workspace))
     return B200_ALGO_TC;
+  // grouped 3x3 layers with 4 or 8 channels per group have kernels of their own behind the tiled candidate
+  if (group_small_supported(g) && phase != B200_PHASE_DBIAS) return B200_ALGO_TILED;
   // Thresholds of the reference heuristic for leaving the one-thread-per-output kernels.
   if (phase == B200_PHASE_FORWARD) return (g.cog >= 8 && cols >= 16 && rows >= 32) ? B200_ALGO_TILED : B200_ALGO_DIRECT;
   if (phase == B200_PHASE_DINPUT)
@@ -175,7 +177,10 @@ size_t b200_conv2d_workspace(const b200_conv_params* p, int phase, int algo, siz
   }
   if (chosen == B200_ALGO_TC) return tc_workspace(g, phase, budget_bytes, nullptr, nullptr);
   if (chosen == B200_ALGO_WINOGRAD) return winograd_workspace(g, phase, budget_bytes);
-  if (chosen == B200_ALGO_TILED && phase == B200_PHASE_DWEIGHT) return simt_dweight_plan(g, budget_bytes).bytes;
+  if (chosen == B200_ALGO_TILED && phase == B200_PHASE_DWEIGHT) {
+    if (group_small_supported(g) && group_small_dweight_workspace(g) <= budget_bytes) return group_small_dweight_workspace(g);
+    return simt_dweight_plan(g, budget_bytes).bytes;
+  }
   return 0;
 }
 
@@ -198,6 +203,10 @@ int b200_conv2d_forward(const b200_conv_params* p, b200_view4 x, b200_view4 w, c
       note_kernel("tc_igemm_forward");
       return tc_forward(g, to_view(x), to_view(w), bias, bias_stride, y, workspace, workspace_bytes, st);
     case B200_ALGO_TILED:
+      if (group_small_supported(g)) {   // few channels per group: the tile follows the group (conv_group_small.cu)
+        note_kernel("group_small_forward");
+        return group_small_conv(g, false, to_view(x), to_view(w), bias, bias_stride, y, st);
+      }
       note_kernel("simt_igemm_forward");
       return simt_igemm_forward(g, to_view(x), to_view(w), bias, bias_stride, y, st);
     default:
@@ -254,6 +263,10 @@ int b200_conv2d_dinput(const b200_conv_params* p, b200_view4 dy, b200_view4 w, f
       note_kernel("tc_igemm_dinput");
       return tc_dinput(g, to_view(dy), to_view(w), dx, workspace, workspace_bytes, st);
     case B200_ALGO_TILED:
+      if (group_small_supported(g)) {
+        note_kernel("group_small_dinput");
+        return group_small_conv(g, true, to_view(dy), to_view(w), nullptr, 0, dx, st);
+      }
       note_kernel("simt_igemm_dinput");
       return simt_igemm_dinput(g, to_view(dy), to_view(w), dx, st);
     default:
@@ -287,6 +300,10 @@ int b200_conv2d_dweight(const b200_conv_params* p, b200_view4 x, b200_view4 dy, 
       note_kernel("tc_igemm_dweight");
       return tc_dweight(g, to_view(x), to_view(dy), dw, workspace, workspace_bytes, st);
     case B200_ALGO_TILED: {
+      if (group_small_supported(g) && workspace_bytes >= group_small_dweight_workspace(g)) {
+        note_kernel("group_small_dweight");
+        return group_small_dweight(g, to_view(x), to_view(dy), dw, (float*)workspace, workspace_bytes, st);
+      }
       const SplitPlan plan = simt_dweight_plan(g, workspace_bytes);
       note_kernel(plan.splits > 1 ? "simt_igemm_dweight+finalize" : "simt_igemm_dweight");
       return simt_igemm_dweight(g, to_view(x), to_view(dy), dw, (float*)workspace, plan.splits, plan.span, st);

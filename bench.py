@@ -22,9 +22,9 @@ The line also carries
                 stream under the dInput kernel; strong scaling (the driver compares ms_per_step over N).
 
 N>1 (torchrun, one rank per GPU): every rank runs the same sweep on its own batch of 64 (weak scaling,
-global batch 64*N); the weight gradient of each layer is summed over ranks by b200_allreduce_sum_f32
-(NCCL behind the C ABI) on a second stream as soon as its dWeight kernel has finished, so the exchange
-runs under the following layers' kernels.  torch.distributed carries only the rendezvous, the barrier
+global batch 64*N); the weight gradients are summed over ranks by b200_allreduce_sum_f32 (NCCL behind the
+C ABI) on a second stream, in buckets of about 6 MB of consecutive layers, each issued as soon as its last
+dWeight kernel has finished, so the exchange runs under the following layers' kernels.  torch.distributed carries only the rendezvous, the barrier
 and the max-over-ranks of the timings.
 
 Other workloads (one JSON line per row; they feed the tables of BASELINE.md and profiles/):
@@ -451,6 +451,9 @@ def main():
         n = math.prod(l.w_shape)
         l.dw = grad_flat[off:off + n].view(l.w_shape)
         off += n
+        l.dw_end = off
+    pending = [0, 0]          # [start, end) of the gradients computed but not yet exchanged
+    BUCKET_FLOATS = (6 << 20) // 4
 
     families = {}  # kernel family -> [flops, [event pairs]]
 
@@ -475,9 +478,15 @@ def main():
                 fam[0] += l.p.flops()
                 fam[1].append((e0, e1))
         if comm is not None and exchange:
-            comm.all_reduce_after(main_stream, l.dw)   # runs under the next layer's kernels
+            # the gradients of consecutive layers are adjacent in grad_flat: exchange them in buckets of about 6 MB
+            # (fewer, larger all-reduces than one per layer), each under the kernels of the layers that follow
+            pending[1] = l.dw_end
+            if pending[1] - pending[0] >= BUCKET_FLOATS or l is layers[-1]:
+                comm.all_reduce_after(main_stream, grad_flat[pending[0]:pending[1]])
+                pending[0] = pending[1]
 
     def step(timed=False):
+        pending[0] = pending[1] = 0
         for l in layers:
             run_layer(l, timed)
         if comm is not None:
@@ -525,6 +534,7 @@ def main():
         ev_grads = torch.cuda.Event()
 
         def e2e_step():
+            pending[0] = pending[1] = 0
             for i, l in enumerate(layers):
                 with torch.cuda.stream(s_in):
                     s_in.wait_event(ev_comp[i])  # previous step's kernels have finished reading these inputs

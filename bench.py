@@ -218,12 +218,16 @@ class Layer:
 # (named in the note), from the ncu capture summarised in the strip-kernel summary under profiles/: bytes of
 # that capture, not a live measurement and not a figure for the whole family.
 NCU_TRAFFIC_ONE_LAYER = {
-    "tc_strip_dweight": {"bytes_per_launch": 53.7e6, "layer": "128->128 28x28 3x3 batch 64 NCHW",
-                         "note": "51.5 MB read + 2.2 MB written per launch against 51.9 MB algorithmic (x + dy + dW)"},
+    "tc_strip_dweight": {"bytes_per_launch": 54.4e6, "layer": "128->128 28x28 3x3 batch 64 NCHW",
+                         "note": "51.5 MB read + 2.9 MB written per launch against 51.9 MB algorithmic (x + dy + dW)"},
+    "tc_tstrip_forward": {"bytes_per_launch": 26.9e6, "layer": "128->128 28x28 3x3 batch 64 NCHW",
+                          "note": "26.9 MB read per launch (x + filter); the 25.7 MB output was still in L2 when the capture ended"},
+    "tc_tstrip_dinput": {"bytes_per_launch": 26.9e6, "layer": "128->128 28x28 3x3 batch 64 NCHW",
+                         "note": "26.9 MB read per launch (dy + filter)"},
     "tc_strip_forward": {"bytes_per_launch": 26.9e6, "layer": "128->128 28x28 3x3 batch 64 NCHW",
-                         "note": "26.9 MB read per launch (x + filter); the 25.7 MB output was still in L2 when the capture ended"},
+                         "note": "26.9 MB read per launch (x + filter), pixels-on-M arrangement of the same layer"},
     "tc_strip_dinput": {"bytes_per_launch": 26.9e6, "layer": "128->128 28x28 3x3 batch 64 NCHW",
-                        "note": "26.9 MB read per launch (dy + filter)"},
+                        "note": "26.9 MB read per launch (dy + filter), pixels-on-M arrangement of the same layer"},
 }
 
 

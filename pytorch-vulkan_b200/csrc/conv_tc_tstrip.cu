@@ -19,13 +19,14 @@
 // terms (tc_common.cuh).
 //
 // Shared-memory layout: channel blocks of 16 (64-byte rows, SWIZZLE_64B), so that a strip stage of 256 pixels
-// plus halo is about 40 KB and three of them fit beside a ring of 16 KB filter stages.  Per stage:
+// plus halo is about 40 KB and three of them fit beside a ring of 32 KB filter stages (two taps each).  Per stage:
 //   hi plane     rows x 64 B   TF32(x) for 16 channels
 //   cross plane  rows x 64 B   [bf16(x_hi) x16 | bf16(x_lo) x16]     (filter: [bf16(w_lo) x16 | bf16(w_hi) x16])
 //
 // CTA roles (448 threads, persistent over tiles): warps 0-3 epilogue (tcgen05.ld, transpose through shared
 // memory so that a warp stores 32 consecutive pixels of one channel, bias), warps 4-11 strip producers, warp 12
-// one thread streaming filter stages with cp.async.bulk, warp 13 tensor-memory allocation and the MMA thread.
+// one thread streaming filter stages with cp.async.bulk, warp 13 tensor-memory allocation and the MMA issue (the
+// whole warp runs the loop, one elected lane issues).
 // Two accumulators of 256 columns alternate, so the epilogue of a tile runs under the next tile's main loop.
 // All hand-offs are mbarriers with bounded waits.
 //

@@ -204,6 +204,37 @@ int b200_conv2d_dbias(const b200_conv_params* p, b200_view4 dy, float* db, void*
 int b200_conv2d_dweight_static(const b200_conv_params* p, b200_view4 x, b200_view4 dy, float* dw,
                                void* stream);
 
+/* ---- generic N-d convolution (3-D and integer tensors) ------------------------------------ */
+
+/* Geometry of a convolution with 1 to 3 spatial dimensions, ordinary or transposed.  Arrays hold
+ * depth, height, width; a lower rank fills the trailing entries and leaves the leading ones at
+ * extent 1 / stride 1 / padding 0.  Mirrors the reference's `geometry()` parameter block
+ * (csrc/ops/convolution_nd.cpp:7-43). */
+typedef struct b200_convnd_params {
+  int32_t rank, transposed;
+  int64_t n, cin, cout, groups;
+  int64_t in[3], out[3], k[3], stride[3], pad[3], dilation[3];
+} b200_convnd_params;
+
+/* Validates and fills `out`.  `in_sizes`, `kernel`, `stride`, `pad`, `dilation`, `output_pad` have
+ * `rank` entries; w0, w1 are the first two weight extents ([cout][cin/groups] ordinary,
+ * [cin][cout/groups] transposed).  Same checks and messages as csrc/ops/convolution_nd.cpp:13-40. */
+int b200_convnd_geometry(b200_convnd_params* out, int rank, int64_t n, int64_t cin,
+                         const int64_t* in_sizes, int64_t w0, int64_t w1, const int64_t* kernel,
+                         const int64_t* stride, const int64_t* pad, const int64_t* dilation,
+                         const int64_t* output_pad, int transposed, int64_t groups);
+
+/* y = conv(x, w) + bias on contiguous tensors; FP32 (is_int64 == 0) or int64 with wrapping
+ * arithmetic (is_int64 != 0; csrc/ops/convolution_nd.cpp:57-61, shader convolution_nd_int64).  bias may be
+ * NULL.  One thread per output element, like shader mode 0 (csrc/ops/convolution_nd.cpp:45-49,62). */
+int b200_convnd_forward(const b200_convnd_params* p, const void* x, const void* w,
+                        const void* bias, void* y, int is_int64, void* stream);
+
+/* FP32 gradients on contiguous tensors; a NULL result pointer skips that gradient (shader modes
+ * 1 dInput, 2 dWeight, 3 dBias; csrc/ops/convolution_nd.cpp:65-74). */
+int b200_convnd_backward(const b200_convnd_params* p, const float* grad, const float* x,
+                         const float* w, float* dx, float* dw, float* db, void* stream);
+
 /* ---- GEMM (nn.Linear neighbours of the conv path) -------------------------------------- */
 
 /* C[M,N] (contiguous) = alpha * A*B + (beta == 0 ? 0 : beta * bias[n]); A, B arbitrary 2-D
@@ -297,9 +328,13 @@ int b200_bmm(int64_t batch, int64_t M, int64_t N, int64_t K, const float* A, int
 
 /* ---- scaled dot-product attention ---------------------------------------------------------------- */
 
+/* Kinds of attention mask (masktype of csrc/ops/attention.cpp:12): none; additive FP32; one byte per
+ * score where zero hides the key (the storage of a bool tensor). */
+enum { B200_MASK_NONE = 0, B200_MASK_ADDITIVE = 1, B200_MASK_BYTES = 2 };
+
 /* q [batch, tq, d], k [batch, tk, d], v [batch, tk, dv], out / grad [batch, tq, dv], lse [batch, tq],
- * mask NULL or additive FP32 [batch, tq, tk]; all contiguous (the reference packs them,
- * csrc/ops/attention.cpp:21,29).  causal != 0 hides keys j > i.  No dropout.
+ * mask NULL (mask_type B200_MASK_NONE) or [batch, tq, tk] of the stated kind; all contiguous (the
+ * reference packs them, csrc/ops/attention.cpp:21,29).  causal != 0 hides keys j > i.  No dropout.
  * Workspace: the score matrix (forward) or two of them (backward != 0). */
 size_t b200_attention_workspace(int64_t batch, int64_t tq, int64_t tk, int64_t d, int64_t dv, int backward);
 
@@ -307,8 +342,8 @@ size_t b200_attention_workspace(int64_t batch, int64_t tq, int64_t tk, int64_t d
  * (csrc/ops/attention.cpp:16-23, shader sdpa_training.comp mode 0).  Composed from b200_bmm and one
  * row-softmax kernel; the scores are materialised in the workspace. */
 int b200_attention_forward(int64_t batch, int64_t tq, int64_t tk, int64_t d, int64_t dv, const float* q, const float* k,
-                           const float* v, const float* mask, int causal, float scale, float* out, float* lse, void* workspace,
-                           size_t workspace_bytes, void* stream);
+                           const float* v, const void* mask, int mask_type, int causal, float scale, float* out, float* lse,
+                           void* workspace, size_t workspace_bytes, void* stream);
 
 /* Replaces -inf by 0 in a log-sum-exp buffer, in place: what the reference's operator
  * _scaled_dot_product_flash_attention_for_cpu returns for rows with every key hidden
@@ -316,13 +351,14 @@ int b200_attention_forward(int64_t batch, int64_t tq, int64_t tk, int64_t d, int
  * b200_attention_backward accepts either form: a hidden key's score is -inf, so its probability is 0. */
 int b200_attention_lse_finite(float* lse, int64_t count, void* stream);
 
-/* dq, dk, dvalue from the output gradient, the saved output and log-sum-exp.  Replaces
- * attention_backward (csrc/ops/attention.cpp:24-34, sdpa_training.comp modes 1 and 2); the mask
- * gradient the reference also returns is not produced. */
+/* dq, dk, dvalue from the output gradient, the saved output and log-sum-exp, and, when dmask is not
+ * NULL, the gradient of an additive mask [batch, tq, tk]: P (dP - rowsum(dO O)), the score gradient
+ * before the scale.  Replaces attention_backward (csrc/ops/attention.cpp:24-34, sdpa_training.comp
+ * modes 1 and 2, whose mode 1 writes the same `dm`). */
 int b200_attention_backward(int64_t batch, int64_t tq, int64_t tk, int64_t d, int64_t dv, const float* grad, const float* q,
-                            const float* k, const float* v, const float* mask, const float* out, const float* lse, int causal,
-                            float scale, float* dq, float* dk, float* dvalue, void* workspace, size_t workspace_bytes,
-                            void* stream);
+                            const float* k, const float* v, const void* mask, int mask_type, const float* out, const float* lse,
+                            int causal, float scale, float* dq, float* dk, float* dvalue, float* dmask, void* workspace,
+                            size_t workspace_bytes, void* stream);
 
 /* ---- data-parallel exchange (batch sharded over GPUs, one process per GPU) ------------------------ */
 

@@ -2,7 +2,8 @@
 
 numpy FP64 (or FP32) restatement of csrc/shaders/sdpa_training.comp of the reference without
 dropout: scores q k^T * scale + mask with keys j > i hidden when causal (:16), the per-row
-log-sum-exp and probabilities (:21-30), and the three input gradients (:33-45).
+log-sum-exp and probabilities (:21-30), the three input gradients and the mask gradient (:33-45); masks are additive
+floats or booleans (False hides the key).
 
 Parity status: pinned against PyTorch CPU FP64 `scaled_dot_product_attention` and its autograd on
 seeded inputs in tests/test_attention_oracle.py (the reference's tests/test_attention.py compares
@@ -16,7 +17,9 @@ import numpy as np
 def _scores(q, k, mask, causal, scale, dtype):
     s = np.einsum("bid,bjd->bij", q.astype(dtype), k.astype(dtype)) * dtype(scale)
     if mask is not None:
-        s = s + np.asarray(mask).astype(dtype)
+        mask = np.asarray(mask)
+        # masktype 2 (bool): a zero byte hides the key; masktype 1: added to the scaled score (sdpa_training.comp:16)
+        s = np.where(mask, s, -np.inf) if mask.dtype == np.bool_ else s + mask.astype(dtype)
     if causal:
         i, j = np.arange(s.shape[1])[:, None], np.arange(s.shape[2])[None, :]
         s = np.where(j > i, -np.inf, s)
@@ -39,8 +42,8 @@ def forward(q, k, v, mask=None, causal=False, scale=None, dtype=np.float64):
     return out.astype(dtype), lse[:, :, 0].astype(dtype)
 
 
-def backward(grad, q, k, v, out, lse, mask=None, causal=False, scale=None, dtype=np.float64):
-    """(dq, dk, dv)."""
+def backward(grad, q, k, v, out, lse, mask=None, causal=False, scale=None, dtype=np.float64, mask_grad=False):
+    """(dq, dk, dv), and with mask_grad the gradient of the additive mask, `ds` before the scale (:38,40)."""
     dtype = np.dtype(dtype).type
     scale = 1.0 / np.sqrt(q.shape[2]) if scale is None else scale
     s = _scores(q, k, mask, causal, scale, dtype)
@@ -51,7 +54,9 @@ def backward(grad, q, k, v, out, lse, mask=None, causal=False, scale=None, dtype
     dv = np.einsum("bij,bie->bje", p, g)
     dp = np.einsum("bie,bje->bij", g, v.astype(dtype))
     delta = (g * np.asarray(out).astype(dtype)).sum(axis=2, keepdims=True)
-    ds = p * (dp - delta) * dtype(scale)
+    dm = p * (dp - delta)
+    ds = dm * dtype(scale)
     dq = np.einsum("bij,bjd->bid", ds, k.astype(dtype))
     dk = np.einsum("bij,bid->bjd", ds, q.astype(dtype))
-    return dq.astype(dtype), dk.astype(dtype), dv.astype(dtype)
+    grads = dq.astype(dtype), dk.astype(dtype), dv.astype(dtype)
+    return grads + (dm.astype(dtype),) if mask_grad else grads

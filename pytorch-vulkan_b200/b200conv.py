@@ -40,6 +40,12 @@ class View4(ctypes.Structure):
     _fields_ = [("ptr", c_void_p), ("stride", c_int64 * 4)]
 
 
+class ConvNdParams(ctypes.Structure):
+    """b200_convnd_params: depth/height/width arrays, lower ranks fill the trailing entries."""
+    _fields_ = [("rank", c_int32), ("transposed", c_int32), ("n", c_int64), ("cin", c_int64), ("cout", c_int64),
+                ("groups", c_int64)] + [(k, c_int64 * 3) for k in ("in_", "out", "k", "stride", "pad", "dilation")]
+
+
 class B200Error(RuntimeError):
     def __init__(self, code, text):
         super().__init__(f"b200conv error {code}: {text}")
@@ -108,11 +114,15 @@ SIGNATURES = {
     "b200_bmm": (c_int, [c_int64] * 4 + [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64, c_void_p,
                          c_int, c_void_p]),
     "b200_attention_workspace": (c_size_t, [c_int64] * 5 + [c_int]),
-    "b200_attention_forward": (c_int, [c_int64] * 5 + [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p,
+    "b200_attention_forward": (c_int, [c_int64] * 5 + [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p, c_void_p,
                                        c_void_p, c_size_t, c_void_p]),
     "b200_attention_lse_finite": (c_int, [c_void_p, c_int64, c_void_p]),
-    "b200_attention_backward": (c_int, [c_int64] * 5 + [c_void_p] * 7 + [c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p,
-                                        c_size_t, c_void_p]),
+    "b200_attention_backward": (c_int, [c_int64] * 5 + [c_void_p] * 5 + [c_int, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p,
+                                        c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "b200_convnd_geometry": (c_int, [POINTER(ConvNdParams), c_int, c_int64, c_int64, POINTER(c_int64), c_int64, c_int64]
+                             + [POINTER(c_int64)] * 5 + [c_int, c_int64]),
+    "b200_convnd_forward": (c_int, [POINTER(ConvNdParams), c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
+    "b200_convnd_backward": (c_int, [POINTER(ConvNdParams)] + [c_void_p] * 7),
     "b200_comm_unique_id": (c_int, [c_void_p]),
     "b200_comm_set_timeout_ms": (c_int, [c_int]),
     "b200_comm_init": (c_int, [c_int, c_int, c_void_p]),
@@ -533,6 +543,52 @@ def conv_transpose2d_forward(x, w, b=None, stride=(1, 1), padding=(0, 0), output
     return y.to_numpy((p.n, p.cin, p.h, p.w))
 
 
+def convnd_geometry(xshape, wshape, stride, padding, dilation, output_padding=None, transposed=False, groups=1):
+    """b200_convnd_params for x [n, cin, spatial...] and w ([cout, cin/g, k...] or transposed [cin, cout/g, k...])."""
+    rank = len(xshape) - 2
+    arr = lambda v: (c_int64 * 3)(*([v] * rank if isinstance(v, int) else list(v)))
+    p = ConvNdParams()
+    check(lib().b200_convnd_geometry(ctypes.byref(p), rank, xshape[0], xshape[1], arr(list(xshape[2:])), wshape[0], wshape[1],
+                                     arr(list(wshape[2:])), arr(stride), arr(padding), arr(dilation),
+                                     arr(output_padding if output_padding is not None else 0), int(transposed), groups))
+    return p, (p.n, p.cout) + tuple(p.out[3 - rank:])
+
+
+def _upload_dense(a, dtype):
+    a = np.ascontiguousarray(a, dtype=dtype)
+    buf = DeviceBuffer(a.nbytes)
+    if a.nbytes:
+        check(lib().b200_memcpy(buf.ptr, a.ctypes.data, a.nbytes, H2D, None))
+        check(lib().b200_stream_sync(None))
+    return buf
+
+
+def convnd_forward(x, w, b=None, stride=1, padding=0, dilation=1, output_padding=None, transposed=False, groups=1):
+    """Generic 1- to 3-D convolution (float32 or int64) through b200_convnd_forward; operands are packed first."""
+    dtype = np.int64 if x.dtype == np.int64 else np.float32
+    p, yshape = convnd_geometry(x.shape, w.shape, stride, padding, dilation, output_padding, transposed, groups)
+    xb, wb = _upload_dense(x, dtype), _upload_dense(w, dtype)
+    bb = _upload_dense(b, dtype) if b is not None else None
+    y = DeviceBuffer(int(np.prod(yshape)) * np.dtype(dtype).itemsize)
+    check(lib().b200_convnd_forward(ctypes.byref(p), xb.ptr, wb.ptr, bb.ptr if bb else None, y.ptr, int(dtype == np.int64), None))
+    return y.to_numpy(yshape, dtype)
+
+
+def convnd_backward(go, x, w, stride=1, padding=0, dilation=1, output_padding=None, transposed=False, groups=1,
+                    mask=(True, True, True)):
+    """(dx, dw, db) of the generic convolution through b200_convnd_backward; None where the mask is False."""
+    p, yshape = convnd_geometry(x.shape, w.shape, stride, padding, dilation, output_padding, transposed, groups)
+    if tuple(go.shape) != tuple(yshape):
+        raise ValueError("convolution backward: invalid gradient")
+    gb, xb, wb = _upload_dense(go, np.float32), _upload_dense(x, np.float32), _upload_dense(w, np.float32)
+    dx = DeviceBuffer(4 * x.size) if mask[0] else None
+    dw = DeviceBuffer(4 * w.size) if mask[1] else None
+    db = DeviceBuffer(4 * p.cout) if mask[2] else None
+    check(lib().b200_convnd_backward(ctypes.byref(p), gb.ptr, xb.ptr, wb.ptr, dx.ptr if dx else None, dw.ptr if dw else None,
+                                     db.ptr if db else None, None))
+    return (dx.to_numpy(x.shape) if dx else None, dw.to_numpy(w.shape) if dw else None, db.to_numpy((p.cout,)) if db else None)
+
+
 def bmm(a, b, algo="auto"):
     """C[i] = a[i] @ b[i] on the device; a [batch, M, K] and b [batch, K, N] any float32 views."""
     batch, M, K = a.shape
@@ -545,29 +601,47 @@ def bmm(a, b, algo="auto"):
     return out.to_numpy((batch, M, N))
 
 
+MASK_NONE, MASK_ADDITIVE, MASK_BYTES = 0, 1, 2
+
+
+def _upload_mask(mask):
+    """(buffer or None, mask kind): float32 masks are additive, bool masks hide the keys whose entry is False."""
+    if mask is None:
+        return None, MASK_NONE
+    mask = np.asarray(mask)
+    if mask.dtype == np.bool_:
+        return _upload_dense(mask.view(np.uint8), np.uint8), MASK_BYTES
+    return _upload_dense(mask, np.float32), MASK_ADDITIVE
+
+
 def attention_forward(q, k, v, mask=None, causal=False, scale=None):
     """(out, lse) = softmax(q k^T * scale + mask) v for q [batch, tq, d], k [batch, tk, d], v [batch, tk, dv]."""
     batch, tq, d = q.shape
     tk, dv = k.shape[1], v.shape[2]
     scale = float(scale) if scale is not None else 1.0 / float(np.sqrt(d))
-    qv, kv, vv, mv = _dense(q), _dense(k), _dense(v), _dense(mask)
+    qv, kv, vv = _dense(q), _dense(k), _dense(v)
+    mv, kind = _upload_mask(mask)
     out, lse = DeviceBuffer(4 * batch * tq * dv), DeviceBuffer(4 * batch * tq)
     ws_n = int(lib().b200_attention_workspace(batch, tq, tk, d, dv, 0))
     ws = DeviceBuffer(ws_n)
-    check(lib().b200_attention_forward(batch, tq, tk, d, dv, qv.ptr, kv.ptr, vv.ptr, mv.ptr if mv else None, int(bool(causal)),
+    check(lib().b200_attention_forward(batch, tq, tk, d, dv, qv.ptr, kv.ptr, vv.ptr, mv.ptr if mv else None, kind, int(bool(causal)),
                                        scale, out.ptr, lse.ptr, ws.ptr, ws_n, None))
     return out.to_numpy((batch, tq, dv)), lse.to_numpy((batch, tq))
 
 
-def attention_backward(grad, q, k, v, out, lse, mask=None, causal=False, scale=None):
-    """(dq, dk, dv) of attention_forward."""
+def attention_backward(grad, q, k, v, out, lse, mask=None, causal=False, scale=None, mask_grad=False):
+    """(dq, dk, dv) of attention_forward, plus the gradient of the additive mask when mask_grad is set."""
     batch, tq, d = q.shape
     tk, dv = k.shape[1], v.shape[2]
     scale = float(scale) if scale is not None else 1.0 / float(np.sqrt(d))
-    gv, qv, kv, vv, ov, lv, mv = (_dense(a) for a in (grad, q, k, v, out, lse, mask))
+    gv, qv, kv, vv, ov, lv = (_dense(a) for a in (grad, q, k, v, out, lse))
+    mv, kind = _upload_mask(mask)
     dq, dk, dvb = DeviceBuffer(4 * batch * tq * d), DeviceBuffer(4 * batch * tk * d), DeviceBuffer(4 * batch * tk * dv)
+    dm = DeviceBuffer(4 * batch * tq * tk) if mask_grad else None
     ws_n = int(lib().b200_attention_workspace(batch, tq, tk, d, dv, 1))
     ws = DeviceBuffer(ws_n)
-    check(lib().b200_attention_backward(batch, tq, tk, d, dv, gv.ptr, qv.ptr, kv.ptr, vv.ptr, mv.ptr if mv else None, ov.ptr, lv.ptr,
-                                        int(bool(causal)), scale, dq.ptr, dk.ptr, dvb.ptr, ws.ptr, ws_n, None))
-    return dq.to_numpy((batch, tq, d)), dk.to_numpy((batch, tk, d)), dvb.to_numpy((batch, tk, dv))
+    check(lib().b200_attention_backward(batch, tq, tk, d, dv, gv.ptr, qv.ptr, kv.ptr, vv.ptr, mv.ptr if mv else None, kind, ov.ptr,
+                                        lv.ptr, int(bool(causal)), scale, dq.ptr, dk.ptr, dvb.ptr, dm.ptr if dm else None, ws.ptr, ws_n,
+                                        None))
+    grads = dq.to_numpy((batch, tq, d)), dk.to_numpy((batch, tk, d)), dvb.to_numpy((batch, tk, dv))
+    return grads + (dm.to_numpy((batch, tq, tk)),) if mask_grad else grads

@@ -12,7 +12,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libb200conv.so")
-SOURCES = ["runtime.cu", "conv_simt.cu", "conv_group_small.cu", "conv_tc.cu", "conv_tc_strip.cu", "conv_tc_tstrip.cu", "dweight_tc_strip.cu", "winograd.cu", "conv_api.cu", "conv_static.cu", "batch_norm.cu", "group_norm.cu", "attention.cu", "comm.cu"]
+SOURCES = ["runtime.cu", "conv_simt.cu", "conv_group_small.cu", "conv_tc.cu", "conv_tc_strip.cu", "conv_tc_tstrip.cu", "dweight_tc_strip.cu", "winograd.cu", "conv_api.cu", "conv_static.cu", "conv_nd.cu", "batch_norm.cu", "group_norm.cu", "attention.cu", "comm.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-ccbin", "/usr/bin/g++", "--use_fast_math=false"]
 

@@ -10,8 +10,10 @@
 //   backward  P again from S and the saved log-sum-exp;  dV = P^T dO;  dP = dO V^T;
 //             dS = P (dP - rowsum(dO O)) * scale in place;  dQ = dS K;  dK = dS^T Q
 // The two elementwise kernels here are bound by HBM traffic over the [tokens, tokens] matrices.
-// Masking as in the shader (sdpa_training.comp:16): causal hides keys j > i; an additive float mask
-// of the scores' shape; a row with every key hidden has log-sum-exp -inf and probability 0.
+// Masking as in the shader (sdpa_training.comp:16): causal hides keys j > i; a mask of the scores' shape, either
+// additive FP32 or one byte per score where zero hides the key (a bool tensor); a row with every key hidden has
+// log-sum-exp -inf and probability 0.  The backward pass can also return the gradient of the additive mask,
+// dM = P (dP - rowsum(dO O)), the unscaled score gradient (sdpa_training.comp:38,40 `aux[index]=ds`).
 #include <cmath>
 
 #include "common.cuh"
@@ -43,20 +45,46 @@ __device__ __forceinline__ float block_reduce(float v, float* scratch) {
   return MAX ? warp_max(v) : warp_add(v);
 }
 
-__device__ __forceinline__ float masked_score(float s, float scale, const float* mask_row, int i, int j, int causal) {
+// One row of the mask: additive floats, or bytes of which zero hides the key; both null = no mask.
+struct MaskRow {
+  const float* f;
+  const unsigned char* b;
+  __device__ __forceinline__ float at(int j) const {
+    if (f) return __ldg(f + j);
+    if (b) return __ldg(b + j) ? 0.f : -INFINITY;
+    return 0.f;
+  }
+  // four consecutive entries from index 4*q; the caller has checked the 16-byte (float) / 4-byte (byte) alignment
+  __device__ __forceinline__ float4 at4(int q) const {
+    if (f) return __ldg(reinterpret_cast<const float4*>(f) + q);
+    if (b) {
+      const uchar4 m = __ldg(reinterpret_cast<const uchar4*>(b) + q);
+      return make_float4(m.x ? 0.f : -INFINITY, m.y ? 0.f : -INFINITY, m.z ? 0.f : -INFINITY, m.w ? 0.f : -INFINITY);
+    }
+    return make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  __device__ __forceinline__ bool aligned() const { return (reinterpret_cast<uintptr_t>(f) & 15) == 0 && (reinterpret_cast<uintptr_t>(b) & 3) == 0; }
+};
+__device__ __forceinline__ MaskRow mask_row(const void* mask, int mask_type, long long row, int tk) {
+  MaskRow m{nullptr, nullptr};
+  if (mask && mask_type == B200_MASK_ADDITIVE) m.f = static_cast<const float*>(mask) + row * tk;
+  if (mask && mask_type == B200_MASK_BYTES) m.b = static_cast<const unsigned char*>(mask) + row * tk;
+  return m;
+}
+
+__device__ __forceinline__ float masked_score(float s, float scale, const MaskRow& m, int i, int j, int causal) {
   if (causal && j > i) return -INFINITY;
-  s *= scale;
-  return mask_row ? s + __ldg(mask_row + j) : s;
+  return s * scale + m.at(j);
 }
 
 // One CTA per score row: s[j] <- softmax_j(s[j] * scale + mask), lse[row] <- log sum exp.
-__global__ void __launch_bounds__(kThreads) softmax_rows_kernel(float* __restrict__ scores, const float* __restrict__ mask, int tq, int tk,
-                                                                 float scale, int causal, float* __restrict__ lse) {
+__global__ void __launch_bounds__(kThreads) softmax_rows_kernel(float* __restrict__ scores, const void* __restrict__ mask, int mask_type, int tq,
+                                                                 int tk, float scale, int causal, float* __restrict__ lse) {
   __shared__ float scratch[kThreads / 32];
   const long long row = blockIdx.x;
   const int i = (int)(row % tq);
   float* s = scores + row * tk;
-  const float* mrow = mask ? mask + row * tk : nullptr;
+  const MaskRow mrow = mask_row(mask, mask_type, row, tk);
   float mx = -INFINITY;
   for (int j = threadIdx.x; j < tk; j += kThreads) mx = fmaxf(mx, masked_score(s[j], scale, mrow, i, j, causal));
   mx = block_reduce<true>(mx, scratch);
@@ -73,14 +101,14 @@ __global__ void __launch_bounds__(kThreads) softmax_rows_kernel(float* __restric
 
 // The same for rows of at most 4096 keys that are whole 16-byte groups: the row is read once into
 // registers (four groups of four per thread), reduced there and written once.
-__global__ void __launch_bounds__(kThreads) softmax_rows_resident_kernel(float* __restrict__ scores, const float* __restrict__ mask,
-                                                                          int tq, int tk, float scale, int causal,
+__global__ void __launch_bounds__(kThreads) softmax_rows_resident_kernel(float* __restrict__ scores, const void* __restrict__ mask,
+                                                                          int mask_type, int tq, int tk, float scale, int causal,
                                                                           float* __restrict__ lse) {
   __shared__ float scratch[kThreads / 32];
   const long long row = blockIdx.x;
   const int i = (int)(row % tq), quads = tk >> 2;
   float4* s4 = reinterpret_cast<float4*>(scores + row * tk);
-  const float4* m4 = mask ? reinterpret_cast<const float4*>(mask + row * tk) : nullptr;
+  const MaskRow mrow = mask_row(mask, mask_type, row, tk);
   float v[16];
   float mx = -INFINITY;
 #pragma unroll
@@ -89,7 +117,7 @@ __global__ void __launch_bounds__(kThreads) softmax_rows_resident_kernel(float* 
     float4 a = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
     if (q < quads) {
       a = s4[q];
-      const float4 m = m4 ? __ldg(m4 + q) : make_float4(0.f, 0.f, 0.f, 0.f);
+      const float4 m = mrow.at4(q);
       const int j = 4 * q;
       a.x = (causal && j > i) ? -INFINITY : a.x * scale + m.x;
       a.y = (causal && j + 1 > i) ? -INFINITY : a.y * scale + m.y;
@@ -122,19 +150,18 @@ __global__ void __launch_bounds__(kThreads) softmax_rows_resident_kernel(float* 
 }
 
 // Backward, first elementwise step: s[j] <- P[j] = exp(s[j] * scale + mask - lse[row]).
-__global__ void __launch_bounds__(kThreads) probabilities_kernel(float* __restrict__ scores, const float* __restrict__ mask, int tq, int tk,
-                                                                  float scale, int causal, const float* __restrict__ lse) {
+__global__ void __launch_bounds__(kThreads) probabilities_kernel(float* __restrict__ scores, const void* __restrict__ mask, int mask_type, int tq,
+                                                                  int tk, float scale, int causal, const float* __restrict__ lse) {
   const long long row = blockIdx.x;
   const int i = (int)(row % tq);
   float* s = scores + row * tk;
-  const float* mrow = mask ? mask + row * tk : nullptr;
+  const MaskRow mrow = mask_row(mask, mask_type, row, tk);
   const float logsum = __ldg(lse + row);
   const bool dead = !(logsum > -INFINITY);
-  if ((tk & 3) == 0 && ((reinterpret_cast<uintptr_t>(s) | reinterpret_cast<uintptr_t>(mrow)) & 15) == 0) {
+  if ((tk & 3) == 0 && (reinterpret_cast<uintptr_t>(s) & 15) == 0 && mrow.aligned()) {
     float4* s4 = reinterpret_cast<float4*>(s);
-    const float4* m4 = reinterpret_cast<const float4*>(mrow);
     for (int q = threadIdx.x; q < (tk >> 2); q += kThreads) {
-      const float4 a = s4[q], m = m4 ? __ldg(m4 + q) : make_float4(0.f, 0.f, 0.f, 0.f);
+      const float4 a = s4[q], m = mrow.at4(q);
       const int j = 4 * q;
       float4 r;
       r.x = (dead || (causal && j > i)) ? 0.f : expf(a.x * scale + m.x - logsum);
@@ -150,10 +177,10 @@ __global__ void __launch_bounds__(kThreads) probabilities_kernel(float* __restri
 }
 
 // Backward, second step: dp[j] <- dS[j] = P[j] * (dp[j] - delta) * scale with delta = sum_e dO[e] O[e]
-// of the row (sdpa_training.comp:38).
+// of the row (sdpa_training.comp:38); dmask[j] <- the same without the scale when the mask gradient is wanted.
 __global__ void __launch_bounds__(kThreads) score_gradient_kernel(float* __restrict__ dp, const float* __restrict__ p,
                                                                    const float* __restrict__ grad, const float* __restrict__ out, int tk,
-                                                                   int dv, float scale) {
+                                                                   int dv, float scale, float* __restrict__ dmask) {
   __shared__ float scratch[kThreads / 32];
   const long long row = blockIdx.x;
   float delta = 0.f;
@@ -161,17 +188,24 @@ __global__ void __launch_bounds__(kThreads) score_gradient_kernel(float* __restr
   delta = block_reduce<false>(delta, scratch);
   float* d = dp + row * tk;
   const float* pr = p + row * tk;
-  if ((tk & 3) == 0 && ((reinterpret_cast<uintptr_t>(d) | reinterpret_cast<uintptr_t>(pr)) & 15) == 0) {
+  float* dm = dmask ? dmask + row * tk : nullptr;
+  if ((tk & 3) == 0 && ((reinterpret_cast<uintptr_t>(d) | reinterpret_cast<uintptr_t>(pr) | reinterpret_cast<uintptr_t>(dm)) & 15) == 0) {
     float4* d4 = reinterpret_cast<float4*>(d);
+    float4* dm4 = reinterpret_cast<float4*>(dm);
     const float4* p4 = reinterpret_cast<const float4*>(pr);
     for (int q = threadIdx.x; q < (tk >> 2); q += kThreads) {
       const float4 a = d4[q], b = __ldg(p4 + q);
-      d4[q] = make_float4(b.x * (a.x - delta) * scale, b.y * (a.y - delta) * scale, b.z * (a.z - delta) * scale,
-                          b.w * (a.w - delta) * scale);
+      const float4 ds = make_float4(b.x * (a.x - delta), b.y * (a.y - delta), b.z * (a.z - delta), b.w * (a.w - delta));
+      if (dm4) dm4[q] = ds;
+      d4[q] = make_float4(ds.x * scale, ds.y * scale, ds.z * scale, ds.w * scale);
     }
     return;
   }
-  for (int j = threadIdx.x; j < tk; j += kThreads) d[j] = pr[j] * (d[j] - delta) * scale;
+  for (int j = threadIdx.x; j < tk; j += kThreads) {
+    const float ds = pr[j] * (d[j] - delta);
+    if (dm) dm[j] = ds;
+    d[j] = ds * scale;
+  }
 }
 
 __global__ void fill_kernel(float* p, float value, long long n) {
@@ -189,6 +223,13 @@ int make_shape(int64_t batch, int64_t tq, int64_t tk, int64_t d, int64_t dv, Att
   if (tk > INT32_MAX || tq > INT32_MAX || dv > INT32_MAX || (tk > 0 && batch * tq > (int64_t)UINT32_MAX / tk))
     return fail(B200_ERANGE, "attention score indexing exceeds uint32");
   *out = {batch, tq, tk, d, dv, ((size_t)(batch * tq * tk) * sizeof(float) + 255) & ~(size_t)255};
+  return B200_OK;
+}
+
+int check_mask(const void* mask, int mask_type) {
+  if (mask_type != B200_MASK_NONE && mask_type != B200_MASK_ADDITIVE && mask_type != B200_MASK_BYTES)
+    return fail(B200_EINVAL, "attention mask shape/dtype mismatch");
+  if ((mask_type != B200_MASK_NONE) != (mask != nullptr)) return fail(B200_EINVAL, "attention mask shape/dtype mismatch");
   return B200_OK;
 }
 
@@ -212,11 +253,12 @@ size_t b200_attention_workspace(int64_t batch, int64_t tq, int64_t tk, int64_t d
 }
 
 int b200_attention_forward(int64_t batch, int64_t tq, int64_t tk, int64_t d, int64_t dv, const float* q, const float* k,
-                           const float* v, const float* mask, int causal, float scale, float* out, float* lse, void* workspace,
-                           size_t workspace_bytes, void* stream) {
+                           const float* v, const void* mask, int mask_type, int causal, float scale, float* out, float* lse,
+                           void* workspace, size_t workspace_bytes, void* stream) {
   if (int rc = ensure_init()) return rc;
   AttentionShape sh;
   if (int rc = make_shape(batch, tq, tk, d, dv, &sh)) return rc;
+  if (int rc = check_mask(mask, mask_type)) return rc;
   const int64_t rows = batch * tq;
   if (rows == 0) return B200_OK;
   if (!q || !out || !lse || (tk > 0 && (!k || !v))) return fail(B200_EINVAL, "attention: null tensor");
@@ -231,9 +273,11 @@ int b200_attention_forward(int64_t batch, int64_t tq, int64_t tk, int64_t d, int
   float* scores = (float*)workspace;
   // S[b] = Q[b] K[b]^T: the right-hand matrix is K read with its strides swapped
   if (int rc = b200_bmm(batch, tq, tk, d, q, tq * d, d, 1, k, tk * d, 1, d, scores, B200_ALGO_AUTO, stream)) return rc;
-  const bool resident = tk % 4 == 0 && tk <= 16 * kThreads && ((reinterpret_cast<uintptr_t>(scores) | reinterpret_cast<uintptr_t>(mask)) & 15) == 0;
-  if (resident) softmax_rows_resident_kernel<<<(unsigned)rows, kThreads, 0, st>>>(scores, mask, (int)tq, (int)tk, scale, causal, lse);
-  else softmax_rows_kernel<<<(unsigned)rows, kThreads, 0, st>>>(scores, mask, (int)tq, (int)tk, scale, causal, lse);
+  const uintptr_t mask_align = mask_type == B200_MASK_BYTES ? 3 : 15;
+  const bool resident = tk % 4 == 0 && tk <= 16 * kThreads && (reinterpret_cast<uintptr_t>(scores) & 15) == 0 &&
+                        (reinterpret_cast<uintptr_t>(mask) & mask_align) == 0;
+  if (resident) softmax_rows_resident_kernel<<<(unsigned)rows, kThreads, 0, st>>>(scores, mask, mask_type, (int)tq, (int)tk, scale, causal, lse);
+  else softmax_rows_kernel<<<(unsigned)rows, kThreads, 0, st>>>(scores, mask, mask_type, (int)tq, (int)tk, scale, causal, lse);
   count_launch();
   if (int rc = launch_check("softmax_rows_kernel")) return rc;
   if (dv == 0) return B200_OK;
@@ -252,12 +296,13 @@ int b200_attention_lse_finite(float* lse, int64_t count, void* stream) {
 }
 
 int b200_attention_backward(int64_t batch, int64_t tq, int64_t tk, int64_t d, int64_t dv, const float* grad, const float* q,
-                            const float* k, const float* v, const float* mask, const float* out, const float* lse, int causal,
-                            float scale, float* dq, float* dk, float* dvalue, void* workspace, size_t workspace_bytes,
-                            void* stream) {
+                            const float* k, const float* v, const void* mask, int mask_type, const float* out, const float* lse,
+                            int causal, float scale, float* dq, float* dk, float* dvalue, float* dmask, void* workspace,
+                            size_t workspace_bytes, void* stream) {
   if (int rc = ensure_init()) return rc;
   AttentionShape sh;
   if (int rc = make_shape(batch, tq, tk, d, dv, &sh)) return rc;
+  if (int rc = check_mask(mask, mask_type)) return rc;
   if (!dq || !dk || !dvalue) return fail(B200_EINVAL, "attention backward: null gradient");
   cudaStream_t st = (cudaStream_t)stream;
   const int64_t rows = batch * tq;
@@ -265,6 +310,7 @@ int b200_attention_backward(int64_t batch, int64_t tq, int64_t tk, int64_t d, in
     if (batch * tq * d) B200_CUDA(cudaMemsetAsync(dq, 0, (size_t)(batch * tq * d) * sizeof(float), st));
     if (batch * tk * d) B200_CUDA(cudaMemsetAsync(dk, 0, (size_t)(batch * tk * d) * sizeof(float), st));
     if (batch * tk * dv) B200_CUDA(cudaMemsetAsync(dvalue, 0, (size_t)(batch * tk * dv) * sizeof(float), st));
+    if (dmask && rows * tk) B200_CUDA(cudaMemsetAsync(dmask, 0, (size_t)(rows * tk) * sizeof(float), st));
     return B200_OK;
   }
   if (!grad || !q || !k || !v || !out || !lse) return fail(B200_EINVAL, "attention backward: null tensor");
@@ -273,14 +319,14 @@ int b200_attention_backward(int64_t batch, int64_t tq, int64_t tk, int64_t d, in
   float* p = (float*)workspace;
   float* dp = (float*)((char*)workspace + sh.score_bytes);
   if (int rc = b200_bmm(batch, tq, tk, d, q, tq * d, d, 1, k, tk * d, 1, d, p, B200_ALGO_AUTO, stream)) return rc;
-  probabilities_kernel<<<(unsigned)rows, kThreads, 0, st>>>(p, mask, (int)tq, (int)tk, scale, causal, lse);
+  probabilities_kernel<<<(unsigned)rows, kThreads, 0, st>>>(p, mask, mask_type, (int)tq, (int)tk, scale, causal, lse);
   count_launch();
   if (int rc = launch_check("probabilities_kernel")) return rc;
   // dV[b] = P[b]^T dO[b]
   if (int rc = b200_bmm(batch, tk, dv, tq, p, tq * tk, 1, tk, grad, tq * dv, dv, 1, dvalue, B200_ALGO_AUTO, stream)) return rc;
   // dP[b] = dO[b] V[b]^T
   if (int rc = b200_bmm(batch, tq, tk, dv, grad, tq * dv, dv, 1, v, tk * dv, 1, dv, dp, B200_ALGO_AUTO, stream)) return rc;
-  score_gradient_kernel<<<(unsigned)rows, kThreads, 0, st>>>(dp, p, grad, out, (int)tk, (int)dv, scale);
+  score_gradient_kernel<<<(unsigned)rows, kThreads, 0, st>>>(dp, p, grad, out, (int)tk, (int)dv, scale, dmask);
   count_launch();
   if (int rc = launch_check("score_gradient_kernel")) return rc;
   // dQ[b] = dS[b] K[b];  dK[b] = dS[b]^T Q[b]

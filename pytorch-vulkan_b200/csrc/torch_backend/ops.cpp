@@ -403,11 +403,85 @@ struct ConvCall {
   std::vector<int64_t> result_shape;  // of the forward result
 };
 
+// ---- generic N-d branch: 3-D convolutions and int64 tensors --------------------------------------
+// The reference sends every rank and both dtypes through one generic shader (csrc/ops/convolution_nd.cpp:51-74);
+// here FP32 calls over one or two spatial dimensions take the Conv2D kernels below and only what those do not
+// cover (three spatial dimensions, int64) runs the generic kernel, on packed operands as in the reference.
+static bool takes_nd_branch(const at::Tensor& input) { return input.dim() == 5 || input.scalar_type() == at::kLong; }
+
+struct ConvNdCall {
+  b200_convnd_params p;
+  std::vector<int64_t> result_shape;
+};
+
+static ConvNdCall convnd_call(const at::Tensor& x, const at::Tensor& w, c10::SymIntArrayRef stride, c10::SymIntArrayRef pad,
+                              c10::SymIntArrayRef dilation, bool transposed, c10::SymIntArrayRef output_pad,
+                              const c10::SymInt& groups) {
+  const int rank = (int)x.dim() - 2;
+  TORCH_CHECK(rank >= 1 && rank <= 3 && w.dim() == x.dim(), "convolution: expected matching rank 3, 4 or 5 tensors");
+  TORCH_CHECK((x.scalar_type() == at::kFloat || x.scalar_type() == at::kLong) && w.scalar_type() == x.scalar_type() &&
+                  x.device() == w.device() && on_device(x),
+              "convolution: expected matching FP32/int64 tensors on the same device");
+  TORCH_CHECK((int)stride.size() == rank && (int)pad.size() == rank && (int)dilation.size() == rank && (int)output_pad.size() == rank,
+              "convolution: spatial parameter rank mismatch");
+  int64_t in[3], k[3], s[3], p[3], d[3], op[3];
+  for (int a = 0; a < rank; ++a) {
+    in[a] = x.size(a + 2), k[a] = w.size(a + 2), s[a] = stride[a].expect_int(), p[a] = pad[a].expect_int();
+    d[a] = dilation[a].expect_int(), op[a] = output_pad[a].expect_int();
+  }
+  ConvNdCall call{};
+  const int rc = b200_convnd_geometry(&call.p, rank, x.size(0), x.size(1), in, w.size(0), w.size(1), k, s, p, d, op, transposed,
+                                      groups.expect_int());
+  TORCH_CHECK(rc == 0, b200_last_error());
+  call.result_shape = {call.p.n, call.p.cout};
+  for (int a = 0; a < rank; ++a) call.result_shape.push_back(call.p.out[3 - rank + a]);
+  return call;
+}
+
+static at::Tensor convnd_forward(const at::Tensor& x, const at::Tensor& w, const std::optional<at::Tensor>& bias,
+                                 c10::SymIntArrayRef stride, c10::SymIntArrayRef pad, c10::SymIntArrayRef dilation, bool transposed,
+                                 c10::SymIntArrayRef output_pad, const c10::SymInt& groups) {
+  const ConvNdCall call = convnd_call(x, w, stride, pad, dilation, transposed, output_pad, groups);
+  auto out = at::empty(call.result_shape, x.options().memory_format(at::MemoryFormat::Contiguous));
+  at::Tensor b;
+  if (bias && bias->defined()) {
+    TORCH_CHECK(bias->dim() == 1 && bias->numel() == call.p.cout && bias->device() == x.device() &&
+                    bias->scalar_type() == x.scalar_type(),
+                "convolution: invalid bias");
+    b = device_contiguous(*bias);
+  }
+  if (!out.numel()) return out;
+  const at::Tensor xc = device_contiguous(x), wc = device_contiguous(w);
+  B200_TORCH_CHECK(b200_convnd_forward(&call.p, xc.const_data_ptr(), wc.const_data_ptr(), b.defined() ? b.const_data_ptr() : nullptr,
+                                       out.data_ptr(), x.scalar_type() == at::kLong, backend_stream()));
+  return out;
+}
+
+static std::tuple<at::Tensor, at::Tensor, at::Tensor> convnd_backward(const at::Tensor& grad, const at::Tensor& x, const at::Tensor& w,
+                                                                      c10::SymIntArrayRef stride, c10::SymIntArrayRef pad,
+                                                                      c10::SymIntArrayRef dilation, bool transposed,
+                                                                      c10::SymIntArrayRef output_pad, const c10::SymInt& groups,
+                                                                      std::array<bool, 3> mask) {
+  const ConvNdCall call = convnd_call(x, w, stride, pad, dilation, transposed, output_pad, groups);
+  TORCH_CHECK(grad.sizes() == at::IntArrayRef(call.result_shape) && grad.scalar_type() == at::kFloat && grad.device() == x.device() &&
+                  x.scalar_type() == at::kFloat,
+              "convolution backward: invalid gradient");
+  const at::Tensor xc = device_contiguous(x), wc = device_contiguous(w), gc = device_contiguous(grad);
+  const auto dense = [](const at::Tensor& like) { return like.options().memory_format(at::MemoryFormat::Contiguous); };
+  at::Tensor dx, dw, db;
+  if (mask[0]) dx = at::empty(x.sizes(), dense(x));
+  if (mask[1]) dw = at::empty(w.sizes(), dense(w));
+  if (mask[2]) db = at::empty({call.p.cout}, dense(w));
+  const auto ptr = [](const at::Tensor& t) { return t.defined() && t.numel() ? t.data_ptr<float>() : nullptr; };
+  B200_TORCH_CHECK(b200_convnd_backward(&call.p, gc.numel() ? gc.const_data_ptr<float>() : nullptr,
+                                        xc.numel() ? xc.const_data_ptr<float>() : nullptr, wc.const_data_ptr<float>(), ptr(dx), ptr(dw),
+                                        ptr(db), backend_stream()));
+  return {dx, dw, db};
+}
+
 static ConvCall conv_call(const at::Tensor& input, const at::Tensor& weight, c10::SymIntArrayRef stride,
                           c10::SymIntArrayRef padding, c10::SymIntArrayRef dilation, bool transposed,
                           c10::SymIntArrayRef output_padding, const c10::SymInt& groups_sym) {
-  TORCH_CHECK(input.dim() != 5 && input.scalar_type() != at::kLong,
-              "Vulkan convolution: only FP32 convolutions over one or two spatial dimensions are implemented by this backend build");
   const int64_t rank = input.dim() - 2;
   TORCH_CHECK((rank == 1 || rank == 2) && weight.dim() == input.dim(), "convolution: expected matching rank 3 or 4 tensors");
   TORCH_CHECK((int64_t)stride.size() == rank && (int64_t)padding.size() == rank && (int64_t)dilation.size() == rank &&
@@ -453,6 +527,7 @@ static at::Tensor convolution_overrideable(const at::Tensor& input, const at::Te
                                            const std::optional<at::Tensor>& bias, c10::SymIntArrayRef stride,
                                            c10::SymIntArrayRef padding, c10::SymIntArrayRef dilation, bool transposed,
                                            c10::SymIntArrayRef output_padding, c10::SymInt groups) {
+  if (takes_nd_branch(input)) return convnd_forward(input, weight, bias, stride, padding, dilation, transposed, output_padding, groups);
   const ConvCall call = conv_call(input, weight, stride, padding, dilation, transposed, output_padding, groups);
   const b200_conv_params& p = call.p;
   const float* bias_ptr = nullptr;
@@ -483,6 +558,8 @@ static std::tuple<at::Tensor, at::Tensor, at::Tensor> convolution_backward_overr
     const at::Tensor& grad_output, const at::Tensor& input, const at::Tensor& weight, c10::SymIntArrayRef stride,
     c10::SymIntArrayRef padding, c10::SymIntArrayRef dilation, bool transposed, c10::SymIntArrayRef output_padding,
     c10::SymInt groups, std::array<bool, 3> output_mask) {
+  if (takes_nd_branch(input))
+    return convnd_backward(grad_output, input, weight, stride, padding, dilation, transposed, output_padding, groups, output_mask);
   const ConvCall call = conv_call(input, weight, stride, padding, dilation, transposed, output_padding, groups);
   const b200_conv_params& p = call.p;
   TORCH_CHECK(grad_output.sizes() == at::IntArrayRef(call.result_shape), "Vulkan convolution backward: output gradient shape mismatch");
@@ -529,6 +606,63 @@ static std::tuple<at::Tensor, at::Tensor, at::Tensor> convolution_backward_overr
     });
   }
   return {dx, dw, db};
+}
+
+// ---- torch_vulkan::conv2d_fused ------------------------------------------------------------------------
+// y = act(conv2d(x, w) + bias + residual) in one call, optionally produced channels-last: the convolution
+// together with the add.Tensor / relu that follow it in a residual block, which the reference runs as
+// separate operators (csrc/ops/mm.cpp:1094-1097).  With the tcgen05 strip kernel all of it happens in the
+// kernel's epilogue and the channels-last result is written directly; other candidates compute the dense
+// result, apply one elementwise pass, and a channels-last request is then a strided copy.  Forward only:
+// the operator records no autograd graph.
+static at::Tensor conv2d_fused(const at::Tensor& input, const at::Tensor& weight, const std::optional<at::Tensor>& bias,
+                               const std::optional<at::Tensor>& residual, bool relu, at::IntArrayRef stride, at::IntArrayRef padding,
+                               at::IntArrayRef dilation, int64_t groups, bool channels_last_out) {
+  TORCH_CHECK(input.dim() == 4 && weight.dim() == 4, "conv2d_fused: expected 4-D input and weight");
+  TORCH_CHECK(stride.size() == 2 && padding.size() == 2 && dilation.size() == 2, "convolution: spatial parameter rank mismatch");
+  require_fp32_device(input);
+  require_fp32_device(weight);
+  b200_conv_params p;
+  const int rc = b200_conv2d_geometry(&p, input.size(0), input.size(1), weight.size(0), input.size(2), input.size(3), weight.size(1),
+                                      weight.size(2), weight.size(3), stride[0], stride[1], padding[0], padding[1], dilation[0],
+                                      dilation[1], groups);
+  TORCH_CHECK(rc == 0, "Vulkan ", b200_last_error());
+  const std::vector<int64_t> shape = {p.n, p.cout, p.oh, p.ow};
+  const float* bias_ptr = nullptr;
+  int64_t bias_stride = 0;
+  if (bias && bias->defined()) {
+    TORCH_CHECK(bias->numel() == p.cout && bias->scalar_type() == at::kFloat && on_device(*bias), "Vulkan convolution: bias shape/dtype mismatch");
+    bias_ptr = bias->const_data_ptr<float>();
+    bias_stride = bias->dim() ? bias->stride(bias->dim() - 1) : 0;
+  }
+  b200_view4 res{nullptr, {0, 0, 0, 0}};
+  if (residual && residual->defined()) {
+    require_fp32_device(*residual);
+    TORCH_CHECK(residual->sizes() == at::IntArrayRef(shape), "conv2d_fused: the residual must have the result's shape");
+    res = view_of(*residual);
+  }
+  // the channels-last epilogue belongs to the strip kernel; everything else produces the dense layout first
+  const bool strip = channels_last_out && b200_conv2d_select(&p, B200_PHASE_FORWARD, B200_ALGO_TC, workspace_limit()) == B200_ALGO_TC &&
+                     b200_conv2d_tc_route(&p, B200_PHASE_FORWARD, view_of(input)) == 0;
+  at::Tensor direct, dense;
+  bool last_cl = false;
+  const std::string layouts = std::to_string(layout_class(input)) + std::to_string(layout_class(weight)) + "f";
+  plan_and_run(p, B200_PHASE_FORWARD, input.options(), layouts, [&](int algo, void* ws, size_t ws_bytes) {
+    const int resolved = b200_conv2d_select(&p, B200_PHASE_FORWARD, algo, workspace_limit());
+    const bool cl_now = strip && resolved == B200_ALGO_TC && ws_bytes >= b200_conv2d_workspace(&p, B200_PHASE_FORWARD, B200_ALGO_TC, workspace_limit());
+    at::Tensor& target = cl_now ? direct : dense;
+    last_cl = cl_now;
+    if (!target.defined())
+      target = at::empty(shape, input.options().memory_format(cl_now ? at::MemoryFormat::ChannelsLast : at::MemoryFormat::Contiguous));
+    return b200_conv2d_forward_fused(&p, view_of(input), view_of(weight), bias_ptr, bias_stride, res, relu ? 1 : 0, target.data_ptr<float>(),
+                                     cl_now ? 1 : 0, ws, ws_bytes, algo, backend_stream());
+  });
+  // the last run is the recorded plan's (the tuner's trials come first): its target holds the result
+  if (last_cl) return direct;
+  if (!channels_last_out) return dense;
+  auto out = at::empty(shape, input.options().memory_format(at::MemoryFormat::ChannelsLast));
+  device_assign(out, dense);
+  return out;
 }
 
 // ---- mm / addmm ----------------------------------------------------------------------------------
@@ -636,5 +770,12 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
   m.impl("bmm", &bmm);
   m.impl("bmm.out", &bmm_out);
 }
+
+TORCH_LIBRARY_FRAGMENT(torch_vulkan, m) {
+  m.def("conv2d_fused(Tensor input, Tensor weight, Tensor? bias, Tensor? residual, bool relu, int[2] stride, int[2] padding, "
+        "int[2] dilation, int groups, bool channels_last_out) -> Tensor");
+}
+
+TORCH_LIBRARY_IMPL(torch_vulkan, PrivateUse1, m) { m.impl("conv2d_fused", &conv2d_fused); }
 
 }  // namespace torch_vulkan

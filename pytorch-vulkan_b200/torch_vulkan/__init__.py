@@ -237,3 +237,15 @@ def reset_execution_stats():
 def device_status(clear: bool = False) -> int:
     """0 unless a bounded device-side wait of a tcgen05 kernel gave up."""
     return _C._device_status(clear)
+
+
+def conv2d_fused(input, weight, bias=None, residual=None, relu=False, stride=1, padding=0, dilation=1, groups=1,
+                 channels_last_out=False):
+    """act(conv2d(input, weight) + bias + residual) in one device call (torch.ops.torch_vulkan.conv2d_fused), the result
+    optionally produced channels-last.  Forward only: no autograd graph is recorded."""
+    pair = lambda v: [v, v] if isinstance(v, int) else list(v)
+    return torch.ops.torch_vulkan.conv2d_fused(input, weight, bias, residual, bool(relu), pair(stride), pair(padding),
+                                               pair(dilation), int(groups), bool(channels_last_out))
+
+
+from torch_vulkan import attention as _attention  # noqa: E402,F401  (routes F.scaled_dot_product_attention to the device operators)

@@ -55,6 +55,35 @@ def test_geometry_rejections_carry_the_reference_messages():
         b200conv.geometry((70000, 1, 256, 256), 1, (1, 1))
 
 
+def test_nd_geometry_shapes_and_rejections():
+    """b200_convnd_geometry against the restatement's shape formulas and the reference's messages
+    (csrc/ops/convolution_nd.cpp:13-40 of the reference)."""
+    from oracle import convnd_oracle
+    cases = [((2, 4, 4, 5, 6), (8, 2, 2, 3, 2), (1, 2, 2), (1, 1, 0), (1, 1, 2), (0, 0, 0), False, 2),
+             ((2, 4, 4, 5, 6), (4, 4, 2, 3, 2), (1, 2, 2), (1, 1, 0), (1, 1, 2), (0, 1, 1), True, 2),
+             ((3, 6, 17), (4, 6, 5), (3,), (2,), (1,), (0,), False, 1),
+             ((1, 8, 9, 7), (8, 2, 3, 3), (2, 2), (1, 1), (1, 1), (1, 1), True, 4)]
+    for xs, ws, s, pd, d, op, tr, g in cases:
+        p, shape = b200conv.convnd_geometry(xs, ws, s, pd, d, op, tr, g)
+        assert shape == convnd_oracle.output_shape(xs, ws, s, pd, d, op, tr, g)
+        rank = len(xs) - 2
+        assert p.rank == rank and list(p.in_)[3 - rank:] == list(xs[2:]) and list(p.in_)[:3 - rank] == [1] * (3 - rank)
+    with pytest.raises(b200conv.B200Error, match="invalid groups/input channels"):
+        b200conv.convnd_geometry((1, 5, 4, 4, 4), (4, 2, 1, 1, 1), 1, 0, 1, groups=2)
+    with pytest.raises(b200conv.B200Error, match="weight/channel/group mismatch"):
+        b200conv.convnd_geometry((1, 4, 4, 4, 4), (4, 3, 1, 1, 1), 1, 0, 1, groups=2)
+    with pytest.raises(b200conv.B200Error, match="invalid output padding"):
+        b200conv.convnd_geometry((1, 4, 4, 4, 4), (4, 4, 1, 1, 1), 1, 0, 1, output_padding=1)
+    with pytest.raises(b200conv.B200Error, match="invalid output padding"):
+        b200conv.convnd_geometry((1, 4, 4, 4, 4), (4, 4, 2, 2, 2), 2, 0, 1, output_padding=2, transposed=True)
+    with pytest.raises(b200conv.B200Error, match="invalid or oversized output shape"):
+        b200conv.convnd_geometry((1, 4, 2, 4, 4), (4, 4, 3, 3, 3), 1, 0, 1)
+    with pytest.raises(b200conv.B200Error, match="spatial addressing exceeds int32"):
+        b200conv.convnd_geometry((1, 4, 4), (4, 4, 3), 2 ** 31, 0, 1)
+    with pytest.raises(b200conv.B200Error, match="invalid spatial parameters"):
+        b200conv.convnd_geometry((1, 4, 4), (4, 4, 3), 0, 0, 1)
+
+
 def test_workspace_plan_respects_budget_and_alignment():
     p = b200conv.geometry((64, 256, 56, 56), 256, (3, 3), padding=(1, 1))
     dw_bytes = 256 * 256 * 9 * 4
@@ -91,7 +120,9 @@ def test_tcgen05_call_on_a_view_beyond_32_bit_offsets_never_truncates_channels()
     # dInput: the reduction runs over the output channels
     dx80 = b200conv.geometry((40, 64, 1024, 1024), 80, (1, 1))
     assert b200conv.tc_route(dx80, b200conv.PHASE_DINPUT, strides(80, 1024, 1024)) == 2
-    assert b200conv.tc_route(dx80, b200conv.PHASE_FORWARD, strides(64, 1024, 1024)) == 3   # 80 output channels: transposed strip kernel
+    assert b200conv.tc_route(dx80, b200conv.PHASE_FORWARD, strides(64, 1024, 1024)) == 1   # 1x1 filters stay off the transposed strip kernel
+    fwd80 = b200conv.geometry((40, 64, 16384, 64), 80, (3, 3), padding=(1, 1))
+    assert b200conv.tc_route(fwd80, b200conv.PHASE_FORWARD, strides(64, 16384, 64)) == 3  # 80 output channels: transposed strip kernel (64-bit offsets)
     # a small tensor inside a huge parent (strides of the parent): still beyond 32-bit offsets
     assert b200conv.tc_route(small, b200conv.PHASE_FORWARD, (2 ** 31, 32 * 32, 32, 1)) == 2
 

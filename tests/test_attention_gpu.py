@@ -95,3 +95,96 @@ def test_operator_returns_zero_log_sum_exp_for_rows_with_every_key_hidden():
     np.testing.assert_allclose(lse_h.reshape(2, 6).numpy()[keep], wlse[keep], rtol=1e-4, atol=1e-4)
     with pytest.raises(RuntimeError, match="same head size"):
         torch.ops.aten._scaled_dot_product_flash_attention_for_cpu(dev(q), dev(k), dev(torch.randn(1, 2, 5, 4)), 0.0, False)
+
+
+@pytest.mark.parametrize("shape", [(2, 5, 7, 4, 6), (2, 137, 19, 8, 3), (2, 4, 141, 7, 129), (3, 128, 256, 64, 64)])
+@pytest.mark.parametrize("causal", [False, True])
+def test_bool_masks_and_the_mask_gradient_through_the_c_abi(shape, causal):
+    batch, tq, tk, d, dv = shape
+    rng = np.random.default_rng(432 + tq)
+    r = lambda *s: rng.standard_normal(s, dtype=np.float32)
+    q, k, v, grad = r(batch, tq, d), r(batch, tk, d), r(batch, tk, dv), r(batch, tq, dv)
+    keep = rng.random((batch, tq, tk)) > 0.3
+    keep[:, 0] = False                        # a row with every key hidden
+    out, lse = b200conv.attention_forward(q, k, v, keep, causal, scale=0.37)
+    wout, wlse = att.forward(q, k, v, keep, causal, scale=0.37)
+    assert oracle.rel_l2(out, wout) <= GATE and (out[:, 0] == 0).all() and np.isneginf(lse[:, 0]).all()
+    np.testing.assert_allclose(lse, wlse, rtol=1e-4, atol=1e-4)
+    for got, want in zip(b200conv.attention_backward(grad, q, k, v, out, lse, keep, causal, scale=0.37),
+                         att.backward(grad, q, k, v, wout, wlse, keep, causal, scale=0.37)):
+        assert np.isfinite(got).all() and oracle.rel_l2(got, want) <= 2 * GATE
+    add = r(batch, tq, tk)
+    out, lse = b200conv.attention_forward(q, k, v, add, causal, scale=0.37)
+    wout, wlse = att.forward(q, k, v, add, causal, scale=0.37)
+    got = b200conv.attention_backward(grad, q, k, v, out, lse, add, causal, scale=0.37, mask_grad=True)
+    want = att.backward(grad, q, k, v, wout, wlse, add, causal, scale=0.37, mask_grad=True)
+    assert len(got) == 4 and got[3].shape == (batch, tq, tk)
+    for a, e in zip(got, want):
+        assert oracle.rel_l2(a, e) <= 2 * GATE
+    # the mask gradient is the score gradient before the scale: hidden (causal) keys get exactly zero
+    if causal:
+        i, j = np.arange(tq)[:, None], np.arange(tk)[None, :]
+        assert (got[3][:, j > i] == 0).all()
+
+
+@pytest.mark.parametrize("shape", [(2, 3, 5, 7, 4, 6), (1, 2, 137, 19, 8, 3), (2, 1, 4, 141, 7, 129)])
+@pytest.mark.parametrize("kind", ["none", "causal", "bool", "float"])
+def test_scaled_dot_product_attention_forward_backward(shape, kind):
+    """The reference's tests/test_complete_attention.py:6-24 with its tolerances; the float mask has the scores' full
+    shape here (a broadcast mask's gradient needs a device reduction operator this backend does not register)."""
+    import torch.nn.functional as F
+    torch.manual_seed(432)
+    b, h, l, s, d, e = shape
+    q, k, v = [torch.randn(size, requires_grad=True) for size in [(b, h, l, d), (b, h, s, d), (b, h, s, e)]]
+    mask = None
+    if kind == "bool":
+        mask = torch.rand(l, s) > .3
+        mask[0] = False
+    if kind == "float":
+        mask = torch.randn(b, h, l, s, requires_grad=True)
+    inputs = [x.detach().to("vulkan").requires_grad_() for x in (q, k, v)]
+    mv = mask.detach().to("vulkan").requires_grad_(mask.requires_grad) if mask is not None else None
+    a = F.scaled_dot_product_attention(q, k, v, mask, is_causal=kind == "causal", scale=.37)
+    z = F.scaled_dot_product_attention(*inputs, mv, is_causal=kind == "causal", scale=.37)
+    assert z.device.type == "vulkan"
+    g = torch.randn_like(a)
+    a.backward(g)
+    z.backward(g.to("vulkan"))
+    # rows whose keys are all hidden: PyTorch's CPU math path returns NaN there, the device operator zeros, as the reference's
+    want = torch.nan_to_num(a.detach(), nan=0.0)
+    torch.testing.assert_close(z.detach().cpu(), want, rtol=4e-4, atol=4e-5)
+    for x, y in zip(inputs, (q, k, v)):
+        torch.testing.assert_close(x.grad.cpu(), torch.nan_to_num(y.grad, nan=0.0), rtol=6e-4, atol=7e-5)
+    if mask is not None and mask.requires_grad:
+        torch.testing.assert_close(mv.grad.cpu(), mask.grad, rtol=6e-4, atol=7e-5)
+
+
+def test_scaled_dot_product_attention_gqa_without_grad_and_rejections():
+    import torch.nn.functional as F
+    torch.manual_seed(3)
+    q, k, v = torch.randn(2, 4, 7, 5), torch.randn(2, 2, 9, 5), torch.randn(2, 2, 9, 3)
+    with torch.no_grad():
+        got = F.scaled_dot_product_attention(q.to("vulkan"), k.to("vulkan"), v.to("vulkan"), enable_gqa=True)
+    torch.testing.assert_close(got.cpu(), F.scaled_dot_product_attention(q, k, v, enable_gqa=True), rtol=3e-4, atol=3e-5)
+    with pytest.raises(RuntimeError, match="dropout is not implemented"):
+        F.scaled_dot_product_attention(q.to("vulkan"), q.to("vulkan"), q.to("vulkan"), dropout_p=0.5)
+    with pytest.raises(RuntimeError, match="Attention mask must be bool or FP32"):
+        F.scaled_dot_product_attention(q.to("vulkan"), q.to("vulkan"), q.to("vulkan"), attn_mask=torch.zeros(7, 7, dtype=torch.float64).to("vulkan"))
+    with pytest.raises(RuntimeError, match="attention mask shape/dtype mismatch"):
+        torch.ops.torch_vulkan.attention_forward(q[0].to("vulkan"), q[0].to("vulkan"), q[0].to("vulkan"), torch.zeros(4, 7, 6).to("vulkan"),
+                                                 0.0, False, 1.0)
+
+
+@pytest.mark.parametrize("batch,qlen,klen,dv", [(0, 3, 4, 5), (2, 0, 4, 5), (2, 3, 0, 5), (2, 3, 4, 0)])
+def test_attention_empty_dimensions(batch, qlen, klen, dv):
+    """tests/test_complete_attention.py:47-57 of the reference."""
+    import torch.nn.functional as F
+    q, k, v = torch.randn(batch, qlen, 7, requires_grad=True), torch.randn(batch, klen, 7, requires_grad=True), torch.randn(batch, klen, dv, requires_grad=True)
+    inputs = [x.detach().to("vulkan").requires_grad_() for x in (q, k, v)]
+    expected = F.scaled_dot_product_attention(q, k, v)
+    actual = F.scaled_dot_product_attention(*inputs)
+    expected.backward(torch.ones_like(expected))
+    actual.backward(torch.ones_like(expected).to("vulkan"))
+    torch.testing.assert_close(actual.cpu(), expected)
+    for a, b in zip(inputs, (q, k, v)):
+        torch.testing.assert_close(a.grad.cpu(), b.grad)

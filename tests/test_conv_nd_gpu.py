@@ -9,7 +9,7 @@ import torch.nn.functional as F
 
 import b200conv
 import torch_vulkan  # noqa: F401  (registers the device)
-from oracle import oracle
+from oracle import convnd_oracle, oracle
 
 pytestmark = pytest.mark.gpu
 GATE = 1e-4
@@ -97,5 +97,126 @@ def test_rejections():
     with pytest.raises(RuntimeError, match="weight/channel/group mismatch"):
         torch.ops.aten.convolution_overrideable(x, torch.randn(3, 2, 3, 3).to("vulkan"), None, [1, 1], [0, 0], [1, 1], True,
                                                 [0, 0], 1)
-    with pytest.raises(RuntimeError, match="one or two spatial dimensions"):
-        F.conv3d(torch.randn(1, 2, 4, 4, 4).to("vulkan"), torch.randn(2, 2, 3, 3, 3).to("vulkan"))
+    with pytest.raises(RuntimeError, match="matching FP32/int64 tensors"):
+        F.conv3d(torch.randn(1, 2, 4, 4, 4).to("vulkan"), torch.randn(2, 2, 3, 3, 3).double().to("vulkan"))
+    with pytest.raises(RuntimeError, match="weight/channel/group mismatch"):
+        F.conv3d(torch.randn(1, 3, 4, 4, 4).to("vulkan"), torch.randn(2, 2, 3, 3, 3).to("vulkan"))
+    with pytest.raises(RuntimeError, match="invalid bias"):
+        F.conv3d(torch.randn(1, 2, 4, 4, 4).to("vulkan"), torch.randn(2, 2, 3, 3, 3).to("vulkan"), torch.randn(3).to("vulkan"))
+    with pytest.raises(RuntimeError, match="invalid or oversized output shape"):
+        F.conv3d(torch.randn(1, 2, 2, 4, 4).to("vulkan"), torch.randn(2, 2, 3, 3, 3).to("vulkan"))
+
+
+# ---- three spatial dimensions and int64: the generic one-thread-per-output kernel ----------------------------------
+def _nd_case(rank, transposed, groups, seed=91):
+    """Shapes and parameters of the reference's own test of this path (tests/test_complete_spatial_recurrent.py:7-37)."""
+    gen = torch.Generator().manual_seed(seed)
+    spatial, kernel, co = (4, 5, 6)[-rank:], (2, 3, 2)[-rank:], 8
+    x = torch.randn((2, 4, *spatial), generator=gen)
+    w = torch.randn((4, co // groups, *kernel) if transposed else (co, 4 // groups, *kernel), generator=gen)
+    b = torch.randn(co, generator=gen)
+    kw = dict(stride=(1, 2, 2)[-rank:], padding=(1, 1, 0)[-rank:], dilation=(1, 1, 2)[-rank:], groups=groups)
+    if transposed:
+        kw["output_padding"] = (0, 1, 1)[-rank:]
+    return x, w, b, kw
+
+
+def _okw(kw, transposed):
+    return dict(stride=kw["stride"], padding=kw["padding"], dilation=kw["dilation"], output_padding=kw.get("output_padding", 0),
+                transposed=transposed, groups=kw["groups"])
+
+
+@pytest.mark.parametrize("rank,transposed", [(1, False), (2, False), (3, False), (1, True), (2, True), (3, True)])
+@pytest.mark.parametrize("groups", [1, 2, 4])
+def test_generic_kernel_through_the_c_abi(rank, transposed, groups):
+    x, w, b, kw = _nd_case(rank, transposed, groups)
+    okw = _okw(kw, transposed)
+    want = convnd_oracle.forward(x.numpy(), w.numpy(), b.numpy(), **okw)
+    got = b200conv.convnd_forward(x.numpy(), w.numpy(), b.numpy(), **okw)
+    assert got.shape == want.shape and oracle.rel_l2(got, want) <= 1e-6
+    assert b200conv.last_kernel() == "convnd_forward"
+    grad = torch.randn(want.shape, generator=torch.Generator().manual_seed(3)).numpy()
+    wdx, wdw, wdb = convnd_oracle.backward(grad, x.numpy(), w.numpy(), **okw)
+    dx, dw, db = b200conv.convnd_backward(grad, x.numpy(), w.numpy(), **okw)
+    assert oracle.rel_l2(dx, wdx) <= 1e-6 and oracle.rel_l2(dw, wdw) <= 1e-6 and oracle.rel_l2(db, wdb) <= 1e-6
+    only_dw = b200conv.convnd_backward(grad, x.numpy(), w.numpy(), mask=(False, True, False), **okw)
+    assert only_dw[0] is None and only_dw[2] is None and np.array_equal(only_dw[1], dw)
+
+
+def test_generic_kernel_on_a_video_sized_block():
+    """A 3-D residual block shape (16 frames of 56x56, 16 -> 32 channels, 3x3x3, stride (1,2,2)) against the restatement."""
+    gen = torch.Generator().manual_seed(11)
+    x = torch.randn(1, 16, 8, 28, 28, generator=gen).numpy()
+    w = (torch.randn(32, 16, 3, 3, 3, generator=gen) * 0.1).numpy()
+    b = torch.randn(32, generator=gen).numpy()
+    okw = dict(stride=(1, 2, 2), padding=1, dilation=1, groups=1)
+    want = convnd_oracle.forward(x, w, b, **okw)
+    got = b200conv.convnd_forward(x, w, b, **okw)
+    assert oracle.rel_l2(got, want) <= 1e-6
+    grad = torch.randn(want.shape, generator=gen).numpy()
+    for g, e in zip(b200conv.convnd_backward(grad, x, w, **okw), convnd_oracle.backward(grad, x, w, **okw)):
+        assert oracle.rel_l2(g, e) <= 2e-6
+
+
+@pytest.mark.parametrize("rank,transposed", [(1, False), (2, False), (3, False), (2, True), (3, True)])
+def test_int64_forward_is_bit_exact(rank, transposed):
+    gen = torch.Generator().manual_seed(7 + rank)
+    spatial, kernel = (4, 5, 6)[-rank:], (2, 3, 2)[-rank:]
+    x = torch.randint(-9, 9, (2, 4, *spatial), generator=gen, dtype=torch.int64)
+    w = torch.randint(-5, 5, (4, 4, *kernel) if transposed else (8, 2, *kernel), generator=gen, dtype=torch.int64)
+    b = torch.randint(-100, 100, (8,), generator=gen, dtype=torch.int64)
+    okw = dict(stride=(1, 2, 2)[-rank:], padding=(1, 1, 0)[-rank:], dilation=(1, 1, 2)[-rank:], groups=2, transposed=transposed,
+               output_padding=(0, 1, 1)[-rank:] if transposed else 0)
+    for xs, ws, bias in ((1, 1, b.numpy()), (1 << 40, 1 << 30, None)):       # the second pair wraps past 2^63
+        want = convnd_oracle.forward(x.numpy() * xs, w.numpy() * ws, bias, **okw)
+        got = b200conv.convnd_forward(x.numpy() * xs, w.numpy() * ws, bias, **okw)
+        assert got.dtype == np.int64 and np.array_equal(got, want)
+    assert b200conv.last_kernel() == "convnd_forward_int64"
+    # through the operator: an int64 tensor on the device takes the same kernel
+    fn = getattr(F, f"conv_transpose{rank}d" if transposed else f"conv{rank}d")
+    kw = {k: v for k, v in okw.items() if k != "transposed" and (transposed or k != "output_padding")}
+    dev = fn(x.to("vulkan"), w.to("vulkan"), b.to("vulkan"), **kw)
+    assert dev.dtype == torch.int64 and torch.equal(dev.cpu(), fn(x, w, b, **kw))
+
+
+@pytest.mark.parametrize("transposed", [False, True])
+@pytest.mark.parametrize("groups", [1, 2, 4])
+@pytest.mark.parametrize("layout", ["contiguous", "offset", "channels_last"])
+def test_conv3d_operator_and_gradients(transposed, groups, layout):
+    """The reference's own 3-D test (tests/test_complete_spatial_recurrent.py:7-37): same shapes, views and tolerances."""
+    x, w, b, kw = _nd_case(3, transposed, groups)
+    if layout == "offset":
+        def view(t):
+            base = torch.empty((*t.shape[:-1], t.shape[-1] * 2 + 1), device="vulkan")
+            out = base[..., 1::2]
+            out.copy_(t.to("vulkan"))
+            return out.detach().requires_grad_()
+        refs = [t.clone().requires_grad_() for t in (x, w, b)]
+        vals = [view(x), view(w), b.to("vulkan").requires_grad_()]
+    else:
+        if layout == "channels_last":
+            x = x.contiguous(memory_format=torch.channels_last_3d)
+        refs = [t.clone().requires_grad_() for t in (x, w, b)]
+        vals = [t.to("vulkan").requires_grad_() for t in (x, w, b)]
+    fn = F.conv_transpose3d if transposed else F.conv3d
+    expected, actual = fn(*refs, **kw), fn(*vals, **kw)
+    grad = torch.randn_like(expected)
+    expected.backward(grad)
+    actual.backward(grad.to("vulkan"))
+    torch.testing.assert_close(actual.cpu(), expected, rtol=3e-4, atol=1e-4)
+    for a, e in zip(vals, refs):
+        torch.testing.assert_close(a.grad.cpu(), e.grad, rtol=4e-4, atol=2e-4)
+
+
+@pytest.mark.parametrize("transposed", [False, True])
+def test_conv3d_empty_batch(transposed):
+    """tests/test_complete_spatial_recurrent.py:40-48 of the reference: an empty batch gives an empty result and a zero dW."""
+    x = torch.empty(0, 2, 3, 4, 5, requires_grad=True)
+    w = torch.randn((2, 3, 2, 2, 2) if transposed else (3, 2, 2, 2, 2), requires_grad=True)
+    fn = F.conv_transpose3d if transposed else F.conv3d
+    a, b = x.to("vulkan").detach().requires_grad_(), w.to("vulkan").detach().requires_grad_()
+    expected, actual = fn(x, w), fn(a, b)
+    expected.sum().backward()
+    actual.backward(torch.empty_like(actual))
+    torch.testing.assert_close(actual.cpu(), expected)
+    torch.testing.assert_close(b.grad.cpu(), w.grad)

@@ -80,3 +80,34 @@ def test_fused_forward_matches_the_plain_entry_point_bit_for_bit_without_post_op
     np.testing.assert_array_equal(plain, fused)
     fused_cl = b200conv.conv2d_forward_fused(x, w, b, channels_last=True, algo="tc", **args)
     np.testing.assert_array_equal(plain, fused_cl)
+
+
+@pytest.mark.parametrize("xshape,cout,kernel,kw", [
+    ((2, 64, 14, 14), 64, (3, 3), dict(padding=(1, 1))),                       # strip kernel: channels-last written by the epilogue
+    ((2, 64, 15, 15), 96, (3, 3), dict(stride=(2, 2), padding=(1, 1))),
+    ((2, 6, 9, 7), 5, (3, 2), dict(padding=(1, 0), dilation=(1, 2))),           # small: CUDA-core candidate plus one elementwise pass
+    ((1, 8, 10, 10), 8, (3, 3), dict(padding=(1, 1), groups=8)),
+])
+@pytest.mark.parametrize("channels_last_out", [False, True])
+def test_fused_operator_under_the_torch_vulkan_namespace(xshape, cout, kernel, kw, channels_last_out):
+    """torch.ops.torch_vulkan.conv2d_fused (and the torch_vulkan.conv2d_fused helper) against PyTorch CPU FP64."""
+    import torch_vulkan
+    gen = torch.Generator().manual_seed(sum(xshape) + cout)
+    groups = kw.get("groups", 1)
+    x = torch.randn(*xshape, generator=gen)
+    w = torch.randn(cout, xshape[1] // groups, *kernel, generator=gen) * 0.1
+    b = torch.randn(cout, generator=gen)
+    want_plain = F.conv2d(x.double(), w.double(), b.double(), **kw)
+    res = torch.randn(want_plain.shape, generator=gen)
+    want = torch.relu(want_plain + res.double())
+    xd = x.to("vulkan").contiguous(memory_format=torch.channels_last) if channels_last_out else x.to("vulkan")
+    got = torch_vulkan.conv2d_fused(xd, w.to("vulkan"), b.to("vulkan"), res.to("vulkan"), relu=True, channels_last_out=channels_last_out,
+                                    **kw)
+    assert got.device.type == "vulkan" and got.shape == want.shape
+    assert got.is_contiguous(memory_format=torch.channels_last if channels_last_out else torch.contiguous_format)
+    assert oracle.rel_l2(got.cpu().numpy(), want.numpy()) <= GATE
+    plain = torch.ops.torch_vulkan.conv2d_fused(x.to("vulkan"), w.to("vulkan"), None, None, False, list(kw.get("stride", (1, 1))),
+                                                list(kw.get("padding", (0, 0))), list(kw.get("dilation", (1, 1))), groups, False)
+    assert oracle.rel_l2(plain.cpu().numpy(), (want_plain - b.double().view(1, -1, 1, 1)).numpy()) <= GATE
+    with pytest.raises(RuntimeError, match="residual must have the result's shape"):
+        torch_vulkan.conv2d_fused(x.to("vulkan"), w.to("vulkan"), residual=x.to("vulkan")[:, :1], **kw)

@@ -67,6 +67,10 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> attention_forward3(const at::Tens
   auto out = at::empty({batch, tq, dv}, q.options().memory_format(at::MemoryFormat::Contiguous));
   auto lse = at::empty({batch, tq}, q.options().memory_format(at::MemoryFormat::Contiguous));
   if (!lse.numel()) return {out, lse, rng_metadata()};
+  if (!out.numel()) {  // no value features: nothing to weigh, the reference reports a zero log-sum-exp (attention.cpp:20)
+    lse.zero_();
+    return {out, lse, rng_metadata()};
+  }
   const at::Tensor qc = packed(q), kc = packed(k), vc = packed(v), mc = kind ? packed(mask) : at::Tensor();
   Workspace ws(batch, tq, tk, d, dv, false, q.options());
   B200_TORCH_CHECK(b200_attention_forward(batch, tq, tk, d, dv, qc.const_data_ptr<float>(), kc.const_data_ptr<float>(),

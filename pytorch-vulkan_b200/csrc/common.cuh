@@ -101,7 +101,10 @@ bool tc_supported(const ConvGeom& g, int phase);
 size_t tc_workspace(const ConvGeom& g, int phase, size_t budget, int* splits_out, int* span_out);
 int tc_forward(const ConvGeom& g, View4 x, View4 w, const float* bias, long long bias_stride, float* y,
                void* ws, size_t ws_bytes, cudaStream_t st);
-int tc_dinput(const ConvGeom& g, View4 dy, View4 w, float* dx, void* ws, size_t ws_bytes, cudaStream_t st);
+// bias (may be null) is indexed by the result's channel: the bias of a transposed convolution, whose forward pass this is.
+// *bias_applied tells whether the kernel that ran added it (the CUDA-core fallback does not).
+int tc_dinput(const ConvGeom& g, View4 dy, View4 w, const float* bias, long long bias_stride, float* dx, void* ws, size_t ws_bytes,
+              cudaStream_t st, bool* bias_applied = nullptr);
 int tc_dweight(const ConvGeom& g, View4 x, View4 dy, float* dw, void* ws, size_t ws_bytes, cudaStream_t st);
 int tc_bmm(long long batch, long long M, long long N, long long K, const float* A, long long sa_b, long long sa0, long long sa1,
            const float* B, long long sb_b, long long sb0, long long sb1, float* C, cudaStream_t st);

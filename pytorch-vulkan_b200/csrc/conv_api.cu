@@ -90,11 +90,19 @@ static int select(const ConvGeom& g, int phase, int algo, size_t workspace) {
     default:
       return fail(B200_EINVAL, "unknown algorithm id %d", algo);
   }
-  // Winograd F(4x4,3x3) pays for its transform passes once the channel contraction is long.
-  // Measured on 64 images: 256 -> 256 channels at 14x14 runs 86 us direct and 86-102 us Winograd;
-  // 512 -> 512 at 7x7 runs 116 us direct and 80 us Winograd.
+  // Winograd F(4x4,3x3) runs three passes (input transform, 36 plane GEMMs, output transform) for 2.25x fewer multiplies;
+  // it pays once both the channel contraction and the image are large.  Measured on 64 images, forward, microseconds,
+  // direct tcgen05 kernel vs Winograd (NCHW; channels-last in brackets):
+  //    512 ->  512 at  7x7     80 vs  78  (81 vs  83)     dInput  72 vs  85
+  //    512 ->  512 at 14x14   177 vs 190 (177 vs 223)
+  //    512 ->  512 at 28x28   697 vs 569 (704 vs 716)
+  //   1024 -> 1024 at  7x7    230 vs 204 (229 vs 213)     dInput 215 vs 231
+  //   1024 -> 1024 at 14x14   702 vs 550 (704 vs 639)
+  //    256 ->  256 at 28x28   171 vs 227;  at 56x56  628 vs 805
+  // so the rule is a product of both: 512 channels from 28x28, 1024 channels from 14x14.
   if ((phase == B200_PHASE_FORWARD || phase == B200_PHASE_DINPUT) && g.cig >= 512 && g.cog >= 512 &&
-      winograd_supported(g, phase) && winograd_workspace(g, phase, workspace) > 0)
+      (long long)g.cig * g.cog * g.oh * g.ow >= 512ll * 512 * 28 * 28 && winograd_supported(g, phase) &&
+      winograd_workspace(g, phase, workspace) > 0)
     return B200_ALGO_WINOGRAD;
   // The tcgen05 forward / dInput kernels stage the split filter in the caller's workspace; a caller that
   // brings none (or too little) gets the CUDA-core kernels, which need no scratch.  dWeight runs unsplit
@@ -246,8 +254,10 @@ int b200_conv2d_forward_fused(const b200_conv_params* p, b200_view4 x, b200_view
   return post_ops_nchw(y, g, post, st);
 }
 
-int b200_conv2d_dinput(const b200_conv_params* p, b200_view4 dy, b200_view4 w, float* dx, void* workspace,
-                       size_t workspace_bytes, int algo, void* stream) {
+// dInput with an optional per-channel bias on the result (the forward pass of a transposed convolution).  The tensor-core and
+// Winograd kernels add it in their epilogue; after the CUDA-core kernels it is one more pass over the result.
+static int dinput_with_bias(const b200_conv_params* p, b200_view4 dy, b200_view4 w, const float* bias, int64_t bias_stride, float* dx,
+                            void* workspace, size_t workspace_bytes, int algo, void* stream) {
   if (int rc = check_params(p)) return rc;
   if (int rc = ensure_init()) return rc;
   if (!dy.ptr || !w.ptr || !dx) return fail(B200_EINVAL, "convolution dInput: null tensor");
@@ -255,34 +265,46 @@ int b200_conv2d_dinput(const b200_conv_params* p, b200_view4 dy, b200_view4 w, f
   const int chosen = select(g, B200_PHASE_DINPUT, algo, workspace ? workspace_bytes : 0);
   if (chosen < 0) return chosen;
   cudaStream_t st = (cudaStream_t)stream;
+  bool bias_applied = false;
+  int rc;
   switch (chosen) {
     case B200_ALGO_WINOGRAD:
       note_kernel("winograd_f4_dinput");
-      return winograd_conv(g, true, to_view(dy), to_view(w), nullptr, 0, dx, workspace, workspace_bytes, st);
+      rc = winograd_conv(g, true, to_view(dy), to_view(w), bias, bias_stride, dx, workspace, workspace_bytes, st);
+      bias_applied = true;
+      break;
     case B200_ALGO_TC:
       note_kernel("tc_igemm_dinput");
-      return tc_dinput(g, to_view(dy), to_view(w), dx, workspace, workspace_bytes, st);
+      rc = tc_dinput(g, to_view(dy), to_view(w), bias, bias_stride, dx, workspace, workspace_bytes, st, &bias_applied);
+      break;
     case B200_ALGO_TILED:
       if (group_small_supported(g)) {
         note_kernel("group_small_dinput");
-        return group_small_conv(g, true, to_view(dy), to_view(w), nullptr, 0, dx, st);
+        rc = group_small_conv(g, true, to_view(dy), to_view(w), nullptr, 0, dx, st);
+      } else {
+        note_kernel("simt_igemm_dinput");
+        rc = simt_igemm_dinput(g, to_view(dy), to_view(w), dx, st);
       }
-      note_kernel("simt_igemm_dinput");
-      return simt_igemm_dinput(g, to_view(dy), to_view(w), dx, st);
+      break;
     default:
       note_kernel("direct_dinput");
-      return simt_direct(g, B200_PHASE_DINPUT, to_view(dy), to_view(w), nullptr, 0, dx, st);
+      rc = simt_direct(g, B200_PHASE_DINPUT, to_view(dy), to_view(w), nullptr, 0, dx, st);
   }
+  if (rc || !bias || bias_applied) return rc;
+  // the result has p's input extent: [n, cin, h, w]
+  return bias_add_nchw(dx, p->n, p->cin, (long long)p->h * p->w, bias, bias_stride, st);
+}
+
+int b200_conv2d_dinput(const b200_conv_params* p, b200_view4 dy, b200_view4 w, float* dx, void* workspace,
+                       size_t workspace_bytes, int algo, void* stream) {
+  return dinput_with_bias(p, dy, w, nullptr, 0, dx, workspace, workspace_bytes, algo, stream);
 }
 
 int b200_conv_transpose2d_forward(const b200_conv_params* p, b200_view4 x, b200_view4 w, const float* bias,
                                   int64_t bias_stride, float* y, void* workspace, size_t workspace_bytes, int algo,
                                   void* stream) {
   // the transposed convolution of x is the input gradient of the convolution p describes
-  if (int rc = b200_conv2d_dinput(p, x, w, y, workspace, workspace_bytes, algo, stream)) return rc;
-  if (!bias) return B200_OK;
-  // the result has p's input extent: [n, cin, h, w]
-  return bias_add_nchw(y, p->n, p->cin, (long long)p->h * p->w, bias, bias_stride, (cudaStream_t)stream);
+  return dinput_with_bias(p, x, w, bias, bias_stride, y, workspace, workspace_bytes, algo, stream);
 }
 
 int b200_conv2d_dweight(const b200_conv_params* p, b200_view4 x, b200_view4 dy, float* dw, void* workspace,

@@ -329,7 +329,7 @@ __global__ void __launch_bounds__(THREADS, 1) conv_tc_kernel(const ConvTcArgs a)
             const int col = col0 + j;
             if (col < cols_valid) {
               float r = kblocks > 0 ? v[j] : 0.f;  // a phase no tap reaches has a zero gradient
-              if (!IS_DX && a.bias) r += __ldg(a.bias + ((long long)group * a.nc + n0 + col) * a.bias_stride);
+              if (a.bias) r += __ldg(a.bias + ((long long)group * a.nc + n0 + col) * a.bias_stride);
               a.out[obase + (long long)(n0 + col) * a.out_hw] = r;
             }
           }
@@ -741,25 +741,28 @@ int tc_forward(const ConvGeom& g, View4 x, View4 w, const float* bias, long long
   note_kernel("simt_igemm_forward");
   return simt_igemm_forward(g, x, w, bias, bias_stride, y, st);
 }
-int tc_dinput(const ConvGeom& g, View4 dy, View4 w, float* dx, void* ws, size_t ws_bytes, cudaStream_t st) {
+int tc_dinput(const ConvGeom& g, View4 dy, View4 w, const float* bias, long long bias_stride, float* dx, void* ws, size_t ws_bytes,
+              cudaStream_t st, bool* bias_applied) {
+  if (bias_applied) *bias_applied = bias != nullptr;
   int route = tc_route(g, true, dy);
   if (route == 3) {
     note_kernel("tc_tstrip_dinput");
-    const int rc = tstrip_conv(g, true, dy, w, nullptr, 0, dx, ws, ws_bytes, st);
+    const int rc = tstrip_conv(g, true, dy, w, bias, bias_stride, dx, ws, ws_bytes, st);
     if (rc != B200_EUNSUPPORTED) return rc;
     route = strip_supported(g, B200_PHASE_DINPUT) && strip_view_addressable(g, true, dy, nullptr) ? 0 : (g.cog % KBLK == 0 ? 1 : 2);
   }
   if (route == 0) {
     note_kernel("tc_strip_dinput");
-    const int rc = strip_conv(g, true, dy, w, nullptr, 0, dx, ws, ws_bytes, st);
+    const int rc = strip_conv(g, true, dy, w, bias, bias_stride, dx, ws, ws_bytes, st);
     if (rc != B200_EUNSUPPORTED) return rc;
     route = g.cog % KBLK == 0 ? 1 : 2;
   }
   if (route == 1) {
     note_kernel("tc_igemm_dinput");
-    return conv_tc_run(g, true, dy, w, nullptr, 0, dx, ws, ws_bytes, st);
+    return conv_tc_run(g, true, dy, w, bias, bias_stride, dx, ws, ws_bytes, st);
   }
   note_kernel("simt_igemm_dinput");
+  if (bias_applied) *bias_applied = false;  // the CUDA-core kernel has no bias term: the caller adds it
   return simt_igemm_dinput(g, dy, w, dx, st);
 }
 template <int BN>

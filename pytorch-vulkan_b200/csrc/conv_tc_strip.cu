@@ -823,7 +823,7 @@ int strip_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* b
   if (!strip_view_addressable(g, is_dx, act, batch))
     return fail(B200_EUNSUPPORTED, "strip kernel: activation tensor too large for 32-bit element offsets");
   StripArgs a{};
-  a.g = g; a.act = act; a.wp = wp; a.bias = is_dx ? nullptr : bias; a.bias_stride = bias_stride; a.out = out;
+  a.g = g; a.act = act; a.wp = wp; a.bias = bias; a.bias_stride = bias_stride; a.out = out;
   a.H = plan.gh; a.W = plan.gw; a.pr = plan.pr; a.pc = plan.pc;
   a.act_h = plan.act_h; a.act_w = plan.act_w; a.out_h = plan.out_h; a.out_w = plan.out_w;
   a.sph = is_dx ? 1 : plan.sph; a.spw = is_dx ? 1 : plan.spw;

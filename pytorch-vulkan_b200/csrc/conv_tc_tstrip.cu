@@ -605,7 +605,7 @@ int tstrip_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* 
   if (int rc = launch_check("stage_filter16_kernel")) return rc;
 
   TArgs a{};
-  a.g = g; a.act = act; a.wp = (const float*)ws; a.bias = is_dx ? nullptr : bias; a.bias_stride = bias_stride; a.out = out;
+  a.g = g; a.act = act; a.wp = (const float*)ws; a.bias = bias; a.bias_stride = bias_stride; a.out = out;
   a.H = plan.geo.gh; a.W = plan.geo.gw; a.pr = plan.geo.pr; a.pc = plan.geo.pc;
   a.act_h = plan.geo.act_h; a.act_w = plan.geo.act_w; a.out_h = plan.geo.out_h; a.out_w = plan.geo.out_w;
   a.sph = is_dx ? 1 : plan.geo.sph; a.spw = is_dx ? 1 : plan.geo.spw;

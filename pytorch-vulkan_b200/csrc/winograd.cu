@@ -338,7 +338,7 @@ int winograd_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float
     const View4 vact{V, 0, 1, 0, 36ll * ctot_in};
     if (int rc = strip_conv(gg, false, vact, View4{}, nullptr, 0, M, nullptr, 0, st, true, 1.f, 0.f, U)) return rc;
     output_transform_kernel<<<dim3((unsigned)div_up64(cnt, 8), (unsigned)div_up64(ctot_out, 32)), 256, 0, st>>>(
-        tl, M, ctot_out, is_dx ? nullptr : bias, bias_stride, out, t0, t1);
+        tl, M, ctot_out, bias, bias_stride, out, t0, t1);
     count_launch();
     if (int rc = launch_check("output_transform_kernel")) return rc;
   }

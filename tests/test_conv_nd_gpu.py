@@ -221,3 +221,20 @@ def test_conv3d_empty_batch(transposed):
     assert y.shape == ((0, 3, 4, 5, 6) if transposed else (0, 3, 2, 3, 4))
     dx, dw, db = b200conv.convnd_backward(np.empty(y.shape, np.float32), x, w, transposed=transposed)
     assert dx.shape == x.shape and (dw == 0).all() and dw.shape == w.shape and (db == 0).all()
+
+
+@pytest.mark.parametrize("case", [TRANSPOSED[4], TRANSPOSED[5], ((2, 128, 12, 12), 128, (3, 3), (1, 1), (1, 1), (0, 0), (1, 1), 1)],
+                         ids=["up2x2", "up4x4s2", "3x3s1-128"])
+def test_transposed_bias_rides_in_the_tensor_core_epilogue(case):
+    """With a tcgen05 (or Winograd) kernel the bias of a transposed convolution costs no extra launch."""
+    x, w, b, kw = _transposed_inputs(case, 77)
+    b200conv.conv_transpose2d_forward(x.numpy(), w.numpy(), None, algo="tc", **kw)      # warm: one-time attribute calls
+    n0 = b200conv.launch_count()
+    plain = b200conv.conv_transpose2d_forward(x.numpy(), w.numpy(), None, algo="tc", **kw)
+    n1 = b200conv.launch_count()
+    biased = b200conv.conv_transpose2d_forward(x.numpy(), w.numpy(), b.numpy(), algo="tc", **kw)
+    n2 = b200conv.launch_count()
+    assert n2 - n1 == n1 - n0
+    want = F.conv_transpose2d(x.double(), w.double(), b.double(), **kw).numpy()
+    assert oracle.rel_l2(biased, want) <= GATE
+    np.testing.assert_allclose(biased - plain, np.broadcast_to(b.numpy()[None, :, None, None], plain.shape), atol=2e-5)

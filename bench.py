@@ -396,6 +396,11 @@ def main():
     ap.add_argument("--no-cfg5", action="store_true", help="skip the config-5 record (profiling runs)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
     ap.add_argument("--layers", default="", help="comma-separated layer indices (profiling runs)")
+    ap.add_argument("--bucket-mb", type=float, default=0.0,
+                    help="N > 1: 0 = one exchange of the fused gradient buffer after the last layer (measured fastest: a "
+                         "collective CTA and a compute CTA do not fit one SM's register file together, so an all-reduce under "
+                         "the persistent kernels delays them by about as much as it hides); > 0 = buckets of consecutive layers "
+                         "of at least this many MB, each exchanged under the following layers' kernels")
     ap.add_argument("--reps", type=int, default=10, help="timed repetitions per row of the per-layer workloads")
     ap.add_argument("--shapes", default="", help="shapes of the batch_norm / group_norm / attention workloads")
     ap.add_argument("--graph", action="store_true",
@@ -457,7 +462,7 @@ def main():
         off += n
         l.dw_end = off
     pending = [0, 0]          # [start, end) of the gradients computed but not yet exchanged
-    BUCKET_FLOATS = (6 << 20) // 4
+    BUCKET_FLOATS = int(args.bucket_mb * (1 << 20)) // 4 if args.bucket_mb > 0 else (1 << 62)
 
     families = {}  # kernel family -> [flops, [event pairs]]
 
@@ -482,8 +487,8 @@ def main():
                 fam[0] += l.p.flops()
                 fam[1].append((e0, e1))
         if comm is not None and exchange:
-            # the gradients of consecutive layers are adjacent in grad_flat: exchange them in buckets of about 6 MB
-            # (fewer, larger all-reduces than one per layer), each under the kernels of the layers that follow
+            # the gradients of consecutive layers are adjacent in grad_flat: one exchange after the last layer, or
+            # (--bucket-mb) buckets of consecutive layers, each under the kernels of the layers that follow
             pending[1] = l.dw_end
             if pending[1] - pending[0] >= BUCKET_FLOATS or l is layers[-1]:
                 comm.all_reduce_after(main_stream, grad_flat[pending[0]:pending[1]])

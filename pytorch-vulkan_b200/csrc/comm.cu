@@ -111,6 +111,12 @@ int b200_comm_init(int rank, int nranks, const void* unique_id128) {
   memcpy(&id, unique_id128, sizeof id);
   ncclConfig_t cfg = NCCL_CONFIG_INITIALIZER;
   cfg.blocking = 0;  // return at once; completion is polled below under a wall-clock bound
+  // The exchange usually runs under compute kernels whose CTAs fill an SM's register file, so every SM a collective CTA
+  // sits on delays one compute CTA: B200_COMM_MAX_CTAS bounds how many the all-reduce may use (unset: NCCL's choice).
+  if (const char* e = getenv("B200_COMM_MAX_CTAS")) {
+    const int ctas = atoi(e);
+    if (ctas >= 1 && ctas <= 64) { cfg.minCTAs = 1; cfg.maxCTAs = ctas; }
+  }
   ncclComm_t comm = nullptr;
   ncclResult_t r = g_nccl.init_rank_config(&comm, nranks, id, rank, &cfg);
   if (r != ncclSuccess && r != ncclInProgress) return nccl_fail(r, "ncclCommInitRankConfig");

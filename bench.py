@@ -27,8 +27,8 @@ C ABI) on a second stream, in buckets of about 6 MB of consecutive layers, each 
 dWeight kernel has finished, so the exchange runs under the following layers' kernels.  torch.distributed carries only the rendezvous, the barrier
 and the max-over-ranks of the timings.
 
-Other workloads (one JSON line per row; they feed the tables of BASELINE.md and profiles/):
-  cfg3 / cfg4   per-layer, per-phase times of BASELINE configs 3 and 4 (L2 flushed before every call)
+Other workloads (one JSON line per row: the per-layer, per-phase timing tables):
+  cfg3 / cfg4   per-layer, per-phase times of the U-Net-block and ResNeXt/dilated/strided configurations (configs 3 and 4) (L2 flushed before every call)
   cfg5          config 5 alone
   batch_norm / group_norm / attention   the kernels of the rows next to the convolution
 

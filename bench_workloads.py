@@ -1,7 +1,6 @@
 """Per-layer workloads of bench.py (`--workload cfg3|cfg4|batch_norm|group_norm|attention`).
 
-Each prints one JSON line per row; they produce the per-phase tables of BASELINE.md and the figures quoted in
-profiles/.  Everything is timed with CUDA events on the launching stream through the C ABI, one B200.
+Each prints one JSON line per row (the per-phase timing tables).  Everything is timed with CUDA events on the launching stream through the C ABI, one B200.
 `cold` rows (and every cfg3 / cfg4 row) write a 256 MB buffer, larger than the 126 MB L2, before each timed
 call; `warm` rows run the calls back to back.
 """
@@ -60,7 +59,7 @@ class Timer:
         return e0.elapsed_time(e1) / self.reps
 
 
-# ---- BASELINE configs 3 and 4: every layer kind, every phase -------------------------------------------------
+# ---- configs 3 and 4 (U-Net block; grouped, dilated, strided, 1x1): every layer kind, every phase ----------------
 CFG3 = [(32, c, c, hw, 3, dict(padding=(1, 1))) for c in (64, 128, 256, 512) for hw in (64, 32, 16, 33)]
 CFG4 = [
     (16, 128, 128, 64, 3, dict(padding=(1, 1))), (16, 256, 256, 32, 3, dict(padding=(1, 1))), (16, 512, 512, 16, 3, dict(padding=(1, 1))),

@@ -119,6 +119,17 @@ static int select(const ConvGeom& g, int phase, int algo, size_t workspace) {
   return rows >= 128 ? B200_ALGO_TILED : B200_ALGO_DIRECT;
 }
 
+// The automatic choice of Winograd is taken back for channels-last activations below 1024 channels: its input transform
+// reads 6x6 patches of whole pixels and is slower there (measured, 512 channels, batch 32, forward, Winograd vs direct:
+// 64x64 1869 vs ~1650 us, 33x33 599 vs ~485, 32x32 486 vs ~455; NCHW: 1322, 495, 374), while 1024 channels at 14x14 still
+// win (639 vs 704 us).  Only where the direct tcgen05 kernel's stage images fit the workspace the caller brought.
+static int reconsider_for_layout(const ConvGeom& g, int phase, int algo, int chosen, const b200_view4& act, size_t workspace) {
+  if (algo != B200_ALGO_AUTO || chosen != B200_ALGO_WINOGRAD) return chosen;
+  const bool channels_last = act.stride[1] == 1 && (long long)g.cig * g.groups > 1 && act.stride[3] != 1;
+  if (!channels_last || g.cig >= 1024 || !tc_supported(g, phase)) return chosen;
+  return tc_workspace(g, phase, workspace, nullptr, nullptr) <= workspace ? B200_ALGO_TC : chosen;
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -199,8 +210,9 @@ int b200_conv2d_forward(const b200_conv_params* p, b200_view4 x, b200_view4 w, c
   if (int rc = ensure_init()) return rc;
   if (!x.ptr || !w.ptr || !y) return fail(B200_EINVAL, "convolution forward: null tensor");
   const ConvGeom g = to_geom(*p);
-  const int chosen = select(g, B200_PHASE_FORWARD, algo, workspace ? workspace_bytes : 0);
+  int chosen = select(g, B200_PHASE_FORWARD, algo, workspace ? workspace_bytes : 0);
   if (chosen < 0) return chosen;
+  chosen = reconsider_for_layout(g, B200_PHASE_FORWARD, algo, chosen, x, workspace ? workspace_bytes : 0);
   cudaStream_t st = (cudaStream_t)stream;
   if (!bias) bias_stride = 0;
   switch (chosen) {
@@ -262,8 +274,9 @@ static int dinput_with_bias(const b200_conv_params* p, b200_view4 dy, b200_view4
   if (int rc = ensure_init()) return rc;
   if (!dy.ptr || !w.ptr || !dx) return fail(B200_EINVAL, "convolution dInput: null tensor");
   const ConvGeom g = to_geom(*p);
-  const int chosen = select(g, B200_PHASE_DINPUT, algo, workspace ? workspace_bytes : 0);
+  int chosen = select(g, B200_PHASE_DINPUT, algo, workspace ? workspace_bytes : 0);
   if (chosen < 0) return chosen;
+  chosen = reconsider_for_layout(g, B200_PHASE_DINPUT, algo, chosen, dy, workspace ? workspace_bytes : 0);
   cudaStream_t st = (cudaStream_t)stream;
   bool bias_applied = false;
   int rc;

@@ -51,9 +51,10 @@ namespace tcs {
 using namespace tc;
 
 constexpr int BLOCK_M = 128, KBLK = 32;
-constexpr int EPI_WARPS = 4, A_WARPS = 8, W_WARPS = 1;
-constexpr int MMA_WARP = EPI_WARPS + A_WARPS + W_WARPS;
-constexpr int THREADS = (MMA_WARP + 1) * 32;
+// Warp roles: 4 epilogue warps, AW strip producers, the weight-copy warp, the MMA warp.  AW is 8, or 16 for layers
+// whose producers set the pace (one tap per staged strip: 1x1 filters): twice the loads in flight per SM.
+constexpr int EPI_WARPS = 4, W_WARPS = 1;
+constexpr int strip_threads(int aw) { return (EPI_WARPS + aw + W_WARPS + 1) * 32; }
 constexpr int MAX_STAGES = 4;
 constexpr int SMEM_LIMIT = 232448 - 2048;  // 227 KB per CTA minus the control block and alignment slack
 
@@ -90,6 +91,7 @@ struct StripArgs {
   int a_stages, w_stages;
   int out_rowmajor;       // 0: NCHW planes.  1: [pixel][channel] rows (channels-last / GEMM C)
   int out_vec4;           // row-major rows may be written with 16-byte stores
+  int wide_producers;     // 1: the kernel instance with sixteen producer warps
   float alpha, beta;      // out = alpha * acc + beta * bias
   View4 res;              // optional residual added after the bias (logical shape of the output), ptr null = none
   int relu;               // clamp at zero last
@@ -152,8 +154,9 @@ __device__ __forceinline__ TileCoord tile_coord(const StripArgs& a, int tile) {
   return c;
 }
 
-template <int BN>
-__global__ void __launch_bounds__(THREADS, 1) conv_strip_kernel(const StripArgs a) {
+template <int BN, int AW>
+__global__ void __launch_bounds__(strip_threads(AW), 1) conv_strip_kernel(const StripArgs a) {
+  constexpr int A_WARPS = AW, MMA_WARP = EPI_WARPS + AW + W_WARPS;
   extern __shared__ unsigned char smem_raw[];
   const unsigned long long prof_start = a.prof ? global_ns() : 0;
   const uint32_t raw = smem_u32(smem_raw);
@@ -723,11 +726,14 @@ static StripPlan plan_strip(const ConvGeom& g, bool is_dx) {
   // waves(tiles / SMs) * width / efficiency(width).
   const long long tiles_m = div_up64((long long)g.n * (p.gh + p.pr) * (p.gw + p.pc), BLOCK_M);
   double best_cost = 0.0;
+  bool single_tap = true;  // no phase has more than one tap (1x1 filters): every staged strip feeds one tap's MMAs only
+  for (int ph = 0; ph < p.tt.n_phase; ++ph) single_tap = single_tap && p.tt.start[ph + 1] - p.tt.start[ph] <= 1;
   for (int bn : {256, 128, 64}) {
     if (bn > 64 && nc <= bn / 2) continue;  // do not pad the column tile by more than 2x
     const int w_stage = bn * 256;
     for (int a_stages : {4, 3, 2, 1}) {
-      if (a_stages > 2 && a_stages * a_stage > SMEM_LIMIT / 2) continue;  // deep strip pipelines only while cheap
+      if (a_stages > 2 && a_stages * a_stage > SMEM_LIMIT / 2 && !single_tap) continue;  // deep strip pipelines only while cheap
+                                                                                          // (or while the producers set the pace)
       const int left = SMEM_LIMIT - a_stages * a_stage;
       if (left < 2 * w_stage) continue;
       const long long tiles = tiles_m * ((nc + bn - 1) / bn) * g.groups * (is_dx ? p.sph * p.spw : 1);
@@ -767,22 +773,26 @@ size_t strip_workspace(const ConvGeom& g, int phase) {
   return 2 * sizeof(float) * (size_t)g.groups * cols * ((kc + 31) / 32 * 32) * g.kh * g.kw;  // ragged last channel block padded
 }
 
-template <int BN>
-static int launch_strip(const tcs::StripArgs& a, int grid, int smem, cudaStream_t st) {
+template <int BN, int AW>
+static int launch_strip_aw(const tcs::StripArgs& a, int grid, int smem, cudaStream_t st) {
   // opt in once (thread-safe) to the full 227 KB of dynamic shared memory for this instantiation
   static std::once_flag once;
   static cudaError_t opt_in = cudaSuccess;
-  std::call_once(once, [] { opt_in = cudaFuncSetAttribute(tcs::conv_strip_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448); });
+  std::call_once(once, [] { opt_in = cudaFuncSetAttribute(tcs::conv_strip_kernel<BN, AW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448); });
   B200_CUDA(opt_in);
   cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3((unsigned)grid); cfg.blockDim = dim3(tcs::THREADS); cfg.dynamicSmemBytes = (size_t)smem; cfg.stream = st;
+  cfg.gridDim = dim3((unsigned)grid); cfg.blockDim = dim3(tcs::strip_threads(AW)); cfg.dynamicSmemBytes = (size_t)smem; cfg.stream = st;
   cudaLaunchAttribute attr{};
   attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr.val.programmaticStreamSerializationAllowed = 1;
   if (a.wait_for_images) { cfg.attrs = &attr; cfg.numAttrs = 1; }
-  B200_CUDA(cudaLaunchKernelEx(&cfg, tcs::conv_strip_kernel<BN>, a));
+  B200_CUDA(cudaLaunchKernelEx(&cfg, tcs::conv_strip_kernel<BN, AW>, a));
   count_launch();
   return launch_check("conv_strip_kernel");
+}
+template <int BN>
+static int launch_strip(const tcs::StripArgs& a, int grid, int smem, cudaStream_t st) {
+  return a.wide_producers ? launch_strip_aw<BN, 16>(a, grid, smem, st) : launch_strip_aw<BN, 8>(a, grid, smem, st);
 }
 
 // The kernel forms element offsets inside the activation tensor in 32 bits: true when the view's
@@ -846,6 +856,16 @@ int strip_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* b
   a.row_div = FastDiv((uint32_t)(a.W + a.pc));
   a.tiles_m = (int)div_up64(a.q_total, BLOCK_M);
   a.halo = plan.halo; a.strip_rows = plan.strip_rows; a.a_stages = plan.a_stages; a.w_stages = plan.w_stages;
+  {
+    // one tap per staged strip (1x1 filters): the MMAs wait for the producers, so sixteen of them run (testing aid:
+    // B200_STRIP_PRODUCERS=8|16 pins either)
+    int most = 0;
+    for (int ph = 0; ph < plan.tt.n_phase; ++ph) most = std::max(most, (int)plan.tt.start[ph + 1] - (int)plan.tt.start[ph]);
+    // ... and only while the reduction side is the larger one (256 -> 64 channels forward: 90 -> 69 us); with more output
+    // than input (its dInput) the epilogue's stores set the pace and the extra warps only take registers from it (61 -> 80 us)
+    a.wide_producers = most <= 1 && kc > nc ? 1 : 0;
+    if (const char* e = getenv("B200_STRIP_PRODUCERS")) a.wide_producers = atoi(e) == 16 ? 1 : 0;
+  }
   const int chunks = (a.strip_rows + 31) / 32;
   const long long tiles_total = (long long)a.tiles_m * a.tiles_n * g.groups;
   if (tiles_total * a.cblocks * chunks > 2147483647ll - (1 << 20))

@@ -54,9 +54,8 @@ using tcs::MAX_TAPS;
 constexpr int TM = 128;          // filter rows (output channels) per tile
 constexpr int KB = 16;           // reduction channels per stage
 constexpr int ROWB = 64;         // bytes per plane row
-constexpr int EPI_WARPS = 4, A_WARPS = 8;
-constexpr int W_WARP = EPI_WARPS + A_WARPS, MMA_WARP = W_WARP + 1;
-constexpr int THREADS = (MMA_WARP + 1) * 32;
+constexpr int EPI_WARPS = 4;   // then AW strip producers (8, or 16 where the producers set the pace), the filter warp, the MMA warp
+constexpr int tstrip_threads(int aw) { return (EPI_WARPS + aw + 2) * 32; }
 constexpr int MAX_A_STAGES = 4, MAX_W_STAGES = 8;
 constexpr uint32_t W_STAGE_BYTES = TM * ROWB * 2;   // hi plane + cross plane of one (tap, channel block)
 constexpr uint32_t W_RING_BYTES = 2 * W_STAGE_BYTES;  // a ring stage holds the images of two consecutive taps: one wait and one
@@ -139,7 +138,9 @@ __device__ __forceinline__ TileCoord tile_coord(const TArgs& a, int tile) {
   return c;
 }
 
-__global__ void __launch_bounds__(THREADS, 1) conv_tstrip_kernel(const TArgs a) {
+template <int AW>
+__global__ void __launch_bounds__(tstrip_threads(AW), 1) conv_tstrip_kernel(const TArgs a) {
+  constexpr int A_WARPS = AW, W_WARP = EPI_WARPS + AW, MMA_WARP = W_WARP + 1;
   extern __shared__ unsigned char smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t tiles_base = (raw + 1023u) & ~1023u;
@@ -644,16 +645,25 @@ int tstrip_conv(const ConvGeom& g, bool is_dx, View4 act, View4 w, const float* 
 
   static std::once_flag once;
   static cudaError_t opt_in = cudaSuccess;
-  std::call_once(once, [] { opt_in = cudaFuncSetAttribute(conv_tstrip_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448); });
+  std::call_once(once, [] {
+    opt_in = cudaFuncSetAttribute(conv_tstrip_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448);
+    if (opt_in == cudaSuccess) opt_in = cudaFuncSetAttribute(conv_tstrip_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448);
+  });
   B200_CUDA(opt_in);
+  // A strided forward pass stages one strip per input phase and gets only one to four taps of MMAs out of it (a
+  // stride-1 strip feeds all nine): the producers set the pace, so sixteen run (128 -> 128 channels, 56x56 stride 2:
+  // 87 -> 81 us NCHW, 94 -> 73 us channels-last; stride-1 layers are unchanged either way).  B200_TSTRIP_PRODUCERS=8|16 pins it.
+  bool wide = !is_dx && (g.sh > 1 || g.sw > 1);
+  if (const char* e = getenv("B200_TSTRIP_PRODUCERS")) wide = atoi(e) == 16;
   cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3((unsigned)std::min(a.tiles_total, sm_count())); cfg.blockDim = dim3(THREADS);
+  cfg.gridDim = dim3((unsigned)std::min(a.tiles_total, sm_count())); cfg.blockDim = dim3(tstrip_threads(wide ? 16 : 8));
   cfg.dynamicSmemBytes = (size_t)plan.smem; cfg.stream = st;
   cudaLaunchAttribute attr{};
   attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr.val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = &attr; cfg.numAttrs = 1;
-  B200_CUDA(cudaLaunchKernelEx(&cfg, conv_tstrip_kernel, a));
+  if (wide) B200_CUDA(cudaLaunchKernelEx(&cfg, conv_tstrip_kernel<16>, a));
+  else B200_CUDA(cudaLaunchKernelEx(&cfg, conv_tstrip_kernel<8>, a));
   count_launch();
   if (profiling) {
     unsigned long long h[16];

@@ -24,8 +24,8 @@
 namespace b200 {
 namespace gcs {
 
-constexpr int TH = 16, TW = 64;          // output tile
-constexpr int IH = TH + 2, IW = TW + 4;  // input tile with halo; rows padded to 68 floats (16-byte aligned strips)
+constexpr int TH = 16;                   // rows of a dWeight tile (forward / dInput tiles come from the SX template parameter)
+constexpr int IH = TH + 2;               // its input rows with halo
 constexpr int THREADS = 256;
 
 struct GArgs {

@@ -167,7 +167,6 @@ __global__ void __launch_bounds__(strip_threads(AW), 1) conv_strip_kernel(const 
   Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem_raw + (w_base - raw) + a.w_stages * w_stage_bytes);
   volatile int* abort_flag = &ctrl->abort_flag;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const ConvGeom& g = a.g;
   // For BN <= 128 the weight stage's hi and lo planes (adjacent in shared memory) are fed to the
   // tensor core as ONE operand of 2*BN rows: a single MMA of width 2*BN yields a_hi*b_hi in columns
   // [0,BN) and a_hi*b_lo in [BN,2BN), a second one of width BN adds a_lo*b_hi to [0,BN); the epilogue

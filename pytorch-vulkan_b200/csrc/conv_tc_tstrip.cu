@@ -251,20 +251,16 @@ __global__ void __launch_bounds__(tstrip_threads(AW), 1) conv_tstrip_kernel(cons
         const TileCoord tc_ = tile_coord(a, (int)blockIdx.x + t * (int)gridDim.x);
         const long long group = tc_.group;
         long long first_image;
-        int images;
         if (a.phase_on_m) {  // images of a group: [phase][tile of the phase][channel block][tap of the phase]
           const int phase = (int)a.div_tiles_pp.div((uint32_t)tc_.m_tile), in_phase = tc_.m_tile - phase * a.tiles_pp;
           const int t0 = ctrl->tap_start[phase], ntap = ctrl->tap_start[phase + 1] - t0;
-          images = a.cb_per_phase * ntap;
           first_image = ((group * a.tt.taps_total + t0) * a.tiles_pp + (long long)in_phase * ntap) * a.cb_per_phase;
         } else {
-          images = a.images_per_tile;
           first_image = (group * a.tiles_m + tc_.m_tile) * a.images_per_tile;
         }
         // images are ordered [channel block][tap of the phase]: the two taps of a ring stage are adjacent in memory,
         // and a block with an odd tap count ends with a stage of one image
         const unsigned char* img = reinterpret_cast<const unsigned char*>(a.wp) + first_image * (long long)W_STAGE_BYTES;
-        (void)images;
         int phase = a.phase_on_m ? (int)a.div_tiles_pp.div((uint32_t)tc_.m_tile) : 0, cbl = 0;
         for (int cb = 0; cb < a.cblocks && alive; ++cb) {
           const int ntap = ctrl->tap_start[phase + 1] - ctrl->tap_start[phase];

@@ -435,7 +435,7 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
         for (int u = 0; u < a.nacc; ++u) {  // channel blocks that share this dY block
           const uint32_t acc = tmem_acc + buf * acc_buffer_cols + (uint32_t)u * ACC_COLS;
           const uint64_t ua_hi = da_hi + (uint64_t)u * (2 * x_plane_d), ua_lo = ua_hi + x_plane_d;
-          if (DW_CROSS) {
+          if constexpr (DW_CROSS) {
 #pragma unroll
             for (int kg = 0; kg < KP / 8; ++kg) umma_tf32(acc, ua_hi + kg * 64, db_hi + kg * 64, idesc, (kb_in_chunk | kg) != 0);
             const uint64_t a_h16 = da16_base + s * stage_d + (uint64_t)u * (2 * x_plane_d), a_l16 = a_h16 + (x_plane_d >> 1);
@@ -444,17 +444,17 @@ __global__ void __launch_bounds__(THREADS, 1) dweight_strip_kernel(const DwStrip
             for (int kg = 0; kg < KP / 16; ++kg) umma_bf16(acc, a_h16 + kg * 64, b_l16 + kg * 64, idesc16, 1);  // 16 rows of 64 bytes
 #pragma unroll
             for (int kg = 0; kg < KP / 16; ++kg) umma_bf16(acc, a_l16 + kg * 64, b_h16 + kg * 64, idesc16, 1);
-            continue;
-          }
+          } else {
 #pragma unroll
-          for (int kg = 0; kg < KP / 8; ++kg) {  // 8 pixels = 8 rows of 128 bytes per MMA
-            if (FUSE_HILO) {
-              umma_tf32(acc, ua_hi + kg * 64, db_hi + kg * 64, idesc_wide, (kb_in_chunk | kg) != 0);
-              umma_tf32(acc, ua_lo + kg * 64, db_hi + kg * 64, idesc, 1);
-            } else {
-              umma_tf32(acc, ua_lo + kg * 64, db_hi + kg * 64, idesc, (kb_in_chunk | kg) != 0);
-              umma_tf32(acc, ua_hi + kg * 64, db_lo + kg * 64, idesc, 1);
-              umma_tf32(acc, ua_hi + kg * 64, db_hi + kg * 64, idesc, 1);
+            for (int kg = 0; kg < KP / 8; ++kg) {  // 8 pixels = 8 rows of 128 bytes per MMA
+              if (FUSE_HILO) {
+                umma_tf32(acc, ua_hi + kg * 64, db_hi + kg * 64, idesc_wide, (kb_in_chunk | kg) != 0);
+                umma_tf32(acc, ua_lo + kg * 64, db_hi + kg * 64, idesc, 1);
+              } else {
+                umma_tf32(acc, ua_lo + kg * 64, db_hi + kg * 64, idesc, (kb_in_chunk | kg) != 0);
+                umma_tf32(acc, ua_hi + kg * 64, db_lo + kg * 64, idesc, 1);
+                umma_tf32(acc, ua_hi + kg * 64, db_hi + kg * 64, idesc, 1);
+              }
             }
           }
         }

@@ -54,7 +54,9 @@ void check3(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const
   TORCH_CHECK(q.device() == k.device() && k.device() == v.device() && (!mask.defined() || !mask.numel() || mask.device() == q.device()),
               "attention devices mismatch");
   TORCH_CHECK(dropout >= 0 && dropout <= 1, "invalid attention dropout");
-  TORCH_CHECK(dropout == 0, "Vulkan attention: dropout is not implemented by this backend build");
+  // 0 keeps every probability, 1 drops every one (sdpa_training.comp:17 `dropped`); anything between draws from the
+  // reference's device Philox stream, which this build does not have
+  TORCH_CHECK(dropout == 0 || dropout == 1, "Vulkan attention: dropout is not implemented by this backend build");
 }
 
 at::Tensor rng_metadata() { return at::zeros({4}, at::TensorOptions().dtype(at::kLong).device(at::kCPU)); }
@@ -77,6 +79,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> attention_forward3(const at::Tens
                                           vc.const_data_ptr<float>(), kind ? mc.const_data_ptr() : nullptr, kind, causal ? 1 : 0,
                                           (float)scale, out.data_ptr<float>(), lse.data_ptr<float>(), ws.hold.data_ptr(), ws.bytes,
                                           backend_stream()));
+  if (dropout == 1) out.zero_();  // every probability dropped: the log-sum-exp stands, the weighted sum is empty
   return {out, lse, rng_metadata()};
 }
 
@@ -96,6 +99,11 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> attention_backward3(c
   const auto dense = [](const at::Tensor& like) { return like.options().memory_format(at::MemoryFormat::Contiguous); };
   auto dq = at::empty(q.sizes(), dense(q)), dk = at::empty(k.sizes(), dense(k)), dvalue = at::empty(v.sizes(), dense(v));
   auto dm = at::empty({batch, tq, tk}, dense(q));
+  if (dropout == 1) {  // nothing reached the output, so nothing flows back (ds = P (0 - 0), dv = P * 0 * dO)
+    for (at::Tensor* t : {&dq, &dk, &dvalue, &dm})
+      if (t->numel()) t->zero_();
+    return {dq, dk, dvalue, dm};
+  }
   const at::Tensor gc = packed(grad), qc = packed(q), kc = packed(k), vc = packed(v), oc = packed(out), lc = packed(lse),
                    mc = kind ? packed(mask) : at::Tensor();
   Workspace ws(batch, tq, tk, d, dv, true, q.options());

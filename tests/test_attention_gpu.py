@@ -168,6 +168,11 @@ def test_scaled_dot_product_attention_gqa_without_grad_and_rejections():
     torch.testing.assert_close(got.cpu(), F.scaled_dot_product_attention(q, k, v, enable_gqa=True), rtol=3e-4, atol=3e-5)
     with pytest.raises(RuntimeError, match="dropout is not implemented"):
         F.scaled_dot_product_attention(q.to("vulkan"), q.to("vulkan"), q.to("vulkan"), dropout_p=0.5)
+    # dropout_p = 1 drops every probability: zero output and zero gradients (tests/test_complete_attention.py:36-45 there)
+    qd = q.to("vulkan").requires_grad_()
+    full = F.scaled_dot_product_attention(qd, qd.detach(), qd.detach(), dropout_p=1.0)
+    full.backward(torch.ones_like(full))
+    assert (full.detach().cpu() == 0).all() and (qd.grad.cpu() == 0).all()
     with pytest.raises(RuntimeError, match="Attention mask must be bool or FP32"):
         F.scaled_dot_product_attention(q.to("vulkan"), q.to("vulkan"), q.to("vulkan"), attn_mask=torch.zeros(7, 7, dtype=torch.float64).to("vulkan"))
     with pytest.raises(RuntimeError, match="attention mask shape/dtype mismatch"):

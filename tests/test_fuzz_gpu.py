@@ -72,3 +72,44 @@ def test_random_geometry_all_phases(case):
     assert b200conv.device_status() == 0
     errs = [oracle.rel_l2(a, e) for a, e in zip((y, dx, dw, db), want)]
     assert max(errs) <= GATE, (fwd_kernel, errs)
+
+
+def _draw_wide(rng):
+    """Layers of tensor-core size: 64 to 512 channels, images up to 48x48, batches up to 8."""
+    while True:
+        groups = int(rng.choice((1, 1, 1, 2)))
+        cin, cout = int(rng.choice((64, 80, 128, 160, 256, 320, 512))), int(rng.choice((64, 80, 128, 160, 256, 320, 512)))
+        k = int(rng.choice((1, 2, 3, 3, 3)))
+        s = int(rng.choice((1, 1, 2)))
+        d = int(rng.choice((1, 1, 2)))
+        p = int(rng.integers(0, d * (k - 1) // 2 + 2))
+        h, w = int(rng.integers(7, 49)), int(rng.integers(7, 49))
+        n = int(rng.integers(2, 9))
+        if h + 2 * p < d * (k - 1) + 1 or w + 2 * p < d * (k - 1) + 1 or n * max(cin, cout) * h * w > 3 << 21:
+            continue
+        return dict(xshape=(n, cin, h, w), cout=cout, kernel=(k, k), stride=(s, s), padding=(p, p), dilation=(d, d), groups=groups,
+                    layout=str(rng.choice(("nchw", "nhwc"))))
+
+
+@pytest.mark.parametrize("case", [_draw_wide(r) for r in [np.random.default_rng(77)] for _ in range(48)],
+                         ids=lambda c: "{}-co{}-k{}-s{}-p{}-d{}-g{}-{}".format("x".join(map(str, c["xshape"])), c["cout"], c["kernel"][0],
+                                                                              c["stride"][0], c["padding"][0], c["dilation"][0],
+                                                                              c["groups"], c["layout"]))
+def test_random_tensor_core_layers(case):
+    """The tcgen05 candidates forced on random wide layers (strip, transposed strip, their 16-producer instances, the
+    chunked dWeight): 2.5e-5, the split-precision kernels' own bound, not the contract's 1e-4."""
+    args = dict(stride=case["stride"], padding=case["padding"], dilation=case["dilation"], groups=case["groups"])
+    g = oracle.geometry(case["xshape"], case["cout"], case["kernel"], **args)
+    rng = np.random.default_rng(sum(case["xshape"]) + 31 * case["cout"])
+    x = rng.standard_normal(g.x_shape, dtype=np.float32)
+    w = (rng.standard_normal(g.w_shape, dtype=np.float32) / np.sqrt(np.prod(g.w_shape[1:]))).astype(np.float32)
+    b = rng.standard_normal(case["cout"], dtype=np.float32)
+    go = rng.standard_normal(g.y_shape, dtype=np.float32)
+    want = oracle.torch_conv_all(x, w, b, go, args["stride"], args["padding"], args["dilation"], args["groups"])
+    xv, gov = _as_layout(x, case["layout"]), _as_layout(go, case["layout"])
+    y = b200conv.conv2d_forward(xv, w, b, algo="tc", budget=1 << 30, **args)
+    assert b200conv.last_kernel().startswith("tc_")
+    dx, dw, db = b200conv.conv2d_backward(gov, xv, w, algo="tc", budget=1 << 30, **args)
+    assert b200conv.device_status() == 0
+    errs = [oracle.rel_l2(a, e) for a, e in zip((y, dx, dw, db), want)]
+    assert max(errs) <= 2.5e-5, errs

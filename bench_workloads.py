@@ -290,10 +290,10 @@ def run_attention(args, torch, b200conv, device, pk):
         calls = [
             ("bmm_q_kt", product, lambda: L.b200_bmm(heads, t, t, d, P(q), t * d, d, 1, P(k), t * d, 1, d, P(scores), 0, stream)),
             ("bmm_p_v", product, lambda: L.b200_bmm(heads, t, d, t, P(scores), t * t, t, 1, P(v), t * d, d, 1, P(out), 0, stream)),
-            ("attention_forward", 2 * product, lambda: L.b200_attention_forward(heads, t, t, d, d, P(q), P(k), P(v), None, 0, 0, scale, P(out),
+            ("attention_forward", 2 * product, lambda: L.b200_attention_forward(heads, t, t, d, d, P(q), P(k), P(v), None, 0, 0, scale, 0.0, None, P(out),
                                                                                 P(lse), P(ws), n_f, stream)),
             ("attention_backward", 5 * product, lambda: L.b200_attention_backward(heads, t, t, d, d, P(g), P(q), P(k), P(v), None, 0, P(out),
-                                                                                  P(lse), 0, scale, P(dq), P(dk), P(dv), None, P(ws), n_b,
+                                                                                  P(lse), 0, scale, 0.0, None, P(dq), P(dk), P(dv), None, P(ws), n_b,
                                                                                   stream)),
         ]
         for name, flops, fn in calls:

@@ -334,7 +334,12 @@ enum { B200_MASK_NONE = 0, B200_MASK_ADDITIVE = 1, B200_MASK_BYTES = 2 };
 
 /* q [batch, tq, d], k [batch, tk, d], v [batch, tk, dv], out / grad [batch, tq, dv], lse [batch, tq],
  * mask NULL (mask_type B200_MASK_NONE) or [batch, tq, tk] of the stated kind; all contiguous (the
- * reference packs them, csrc/ops/attention.cpp:21,29).  causal != 0 hides keys j > i.  No dropout.
+ * reference packs them, csrc/ops/attention.cpp:21,29).  causal != 0 hides keys j > i.
+ * dropout in [0, 1]: probability of dropping a (query, key) probability; kept ones are scaled by 1 / (1 - dropout).
+ * For 0 < dropout < 1, rng points to four host words {seed low, seed high, offset low, offset high}: the
+ * Philox4x32-10 stream of the reference (csrc/shaders/philox.glsl; state layout of VulkanGenerator::reserve,
+ * csrc/vulkan_generator.cpp:17-20), element (row, key) drawing word (row * tk + key) % 4 of block
+ * offset + (row * tk + key) / 4.  The backward call must get the same dropout and rng as its forward call.
  * Workspace: the score matrix (forward) or two of them (backward != 0). */
 size_t b200_attention_workspace(int64_t batch, int64_t tq, int64_t tk, int64_t d, int64_t dv, int backward);
 
@@ -342,8 +347,8 @@ size_t b200_attention_workspace(int64_t batch, int64_t tq, int64_t tk, int64_t d
  * (csrc/ops/attention.cpp:16-23, shader sdpa_training.comp mode 0).  Composed from b200_bmm and one
  * row-softmax kernel; the scores are materialised in the workspace. */
 int b200_attention_forward(int64_t batch, int64_t tq, int64_t tk, int64_t d, int64_t dv, const float* q, const float* k,
-                           const float* v, const void* mask, int mask_type, int causal, float scale, float* out, float* lse,
-                           void* workspace, size_t workspace_bytes, void* stream);
+                           const float* v, const void* mask, int mask_type, int causal, float scale, float dropout,
+                           const uint32_t* rng, float* out, float* lse, void* workspace, size_t workspace_bytes, void* stream);
 
 /* Replaces -inf by 0 in a log-sum-exp buffer, in place: what the reference's operator
  * _scaled_dot_product_flash_attention_for_cpu returns for rows with every key hidden
@@ -357,8 +362,8 @@ int b200_attention_lse_finite(float* lse, int64_t count, void* stream);
  * modes 1 and 2, whose mode 1 writes the same `dm`). */
 int b200_attention_backward(int64_t batch, int64_t tq, int64_t tk, int64_t d, int64_t dv, const float* grad, const float* q,
                             const float* k, const float* v, const void* mask, int mask_type, const float* out, const float* lse,
-                            int causal, float scale, float* dq, float* dk, float* dvalue, float* dmask, void* workspace,
-                            size_t workspace_bytes, void* stream);
+                            int causal, float scale, float dropout, const uint32_t* rng, float* dq, float* dk, float* dvalue,
+                            float* dmask, void* workspace, size_t workspace_bytes, void* stream);
 
 /* ---- data-parallel exchange (batch sharded over GPUs, one process per GPU) ------------------------ */
 

@@ -114,11 +114,11 @@ SIGNATURES = {
     "b200_bmm": (c_int, [c_int64] * 4 + [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64, c_void_p,
                          c_int, c_void_p]),
     "b200_attention_workspace": (c_size_t, [c_int64] * 5 + [c_int]),
-    "b200_attention_forward": (c_int, [c_int64] * 5 + [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p, c_void_p,
-                                       c_void_p, c_size_t, c_void_p]),
+    "b200_attention_forward": (c_int, [c_int64] * 5 + [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_void_p,
+                                       c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
     "b200_attention_lse_finite": (c_int, [c_void_p, c_int64, c_void_p]),
-    "b200_attention_backward": (c_int, [c_int64] * 5 + [c_void_p] * 5 + [c_int, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p,
-                                        c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "b200_attention_backward": (c_int, [c_int64] * 5 + [c_void_p] * 5 + [c_int, c_void_p, c_void_p, c_int, c_float, c_float, c_void_p,
+                                        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
     "b200_convnd_geometry": (c_int, [POINTER(ConvNdParams), c_int, c_int64, c_int64, POINTER(c_int64), c_int64, c_int64]
                              + [POINTER(c_int64)] * 5 + [c_int, c_int64]),
     "b200_convnd_forward": (c_int, [POINTER(ConvNdParams), c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
@@ -614,8 +614,17 @@ def _upload_mask(mask):
     return _upload_dense(mask, np.float32), MASK_ADDITIVE
 
 
-def attention_forward(q, k, v, mask=None, causal=False, scale=None):
-    """(out, lse) = softmax(q k^T * scale + mask) v for q [batch, tq, d], k [batch, tk, d], v [batch, tk, dv]."""
+def _rng_words(rng):
+    """(seed, offset) -> the four uint32 words the library takes, or None."""
+    if rng is None:
+        return None
+    seed, offset = (int(v) & ((1 << 64) - 1) for v in rng)
+    return (ctypes.c_uint32 * 4)(seed & 0xFFFFFFFF, seed >> 32, offset & 0xFFFFFFFF, offset >> 32)
+
+
+def attention_forward(q, k, v, mask=None, causal=False, scale=None, dropout=0.0, rng=None):
+    """(out, lse) = dropout(softmax(q k^T * scale + mask)) v for q [batch, tq, d], k [batch, tk, d], v [batch, tk, dv];
+    rng = (seed, offset) of the Philox stream when 0 < dropout < 1."""
     batch, tq, d = q.shape
     tk, dv = k.shape[1], v.shape[2]
     scale = float(scale) if scale is not None else 1.0 / float(np.sqrt(d))
@@ -625,11 +634,11 @@ def attention_forward(q, k, v, mask=None, causal=False, scale=None):
     ws_n = int(lib().b200_attention_workspace(batch, tq, tk, d, dv, 0))
     ws = DeviceBuffer(ws_n)
     check(lib().b200_attention_forward(batch, tq, tk, d, dv, qv.ptr, kv.ptr, vv.ptr, mv.ptr if mv else None, kind, int(bool(causal)),
-                                       scale, out.ptr, lse.ptr, ws.ptr, ws_n, None))
+                                       scale, float(dropout), _rng_words(rng), out.ptr, lse.ptr, ws.ptr, ws_n, None))
     return out.to_numpy((batch, tq, dv)), lse.to_numpy((batch, tq))
 
 
-def attention_backward(grad, q, k, v, out, lse, mask=None, causal=False, scale=None, mask_grad=False):
+def attention_backward(grad, q, k, v, out, lse, mask=None, causal=False, scale=None, mask_grad=False, dropout=0.0, rng=None):
     """(dq, dk, dv) of attention_forward, plus the gradient of the additive mask when mask_grad is set."""
     batch, tq, d = q.shape
     tk, dv = k.shape[1], v.shape[2]
@@ -641,7 +650,7 @@ def attention_backward(grad, q, k, v, out, lse, mask=None, causal=False, scale=N
     ws_n = int(lib().b200_attention_workspace(batch, tq, tk, d, dv, 1))
     ws = DeviceBuffer(ws_n)
     check(lib().b200_attention_backward(batch, tq, tk, d, dv, gv.ptr, qv.ptr, kv.ptr, vv.ptr, mv.ptr if mv else None, kind, ov.ptr,
-                                        lv.ptr, int(bool(causal)), scale, dq.ptr, dk.ptr, dvb.ptr, dm.ptr if dm else None, ws.ptr, ws_n,
-                                        None))
+                                        lv.ptr, int(bool(causal)), scale, float(dropout), _rng_words(rng), dq.ptr, dk.ptr, dvb.ptr,
+                                        dm.ptr if dm else None, ws.ptr, ws_n, None))
     grads = dq.to_numpy((batch, tq, d)), dk.to_numpy((batch, tk, d)), dvb.to_numpy((batch, tk, dv))
     return grads + (dm.to_numpy((batch, tq, tk)),) if mask_grad else grads

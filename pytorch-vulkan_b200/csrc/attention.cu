@@ -1,14 +1,14 @@
 // Scaled dot-product attention, forward and backward, for contiguous FP32 [batch, tokens, dim]
 // operands.  Replaces attention_forward / attention_backward of the reference
-// (csrc/ops/attention.cpp:16-34) and its sdpa_training shader, without dropout.
+// (csrc/ops/attention.cpp:16-34) and its sdpa_training shader, dropout included (the same counter-based stream).
 //
 // The products run on the GEMM kernels of this library (b200_bmm: tcgen05 from 128x64x32, CUDA
 // cores below); the score matrix is materialised in the caller's workspace, so this is the
 // composed form of attention, not a single fused pass:
 //   forward   S = Q K^T;  P = softmax(S * scale + mask) row by row, in place, with the
 //             log-sum-exp kept per row;  O = P V
-//   backward  P again from S and the saved log-sum-exp;  dV = P^T dO;  dP = dO V^T;
-//             dS = P (dP - rowsum(dO O)) * scale in place;  dQ = dS K;  dK = dS^T Q
+//   backward  P again from S and the saved log-sum-exp;  dP = dO V^T;
+//             dS = P (dP w - rowsum(dO O)) * scale in place (w: dropout weights);  dV = (P w)^T dO;  dQ = dS K;  dK = dS^T Q
 // The two elementwise kernels here are bound by HBM traffic over the [tokens, tokens] matrices.
 // Masking as in the shader (sdpa_training.comp:16): causal hides keys j > i; a mask of the scores' shape, either
 // additive FP32 or one byte per score where zero hides the key (a bool tensor); a row with every key hidden has
@@ -77,9 +77,53 @@ __device__ __forceinline__ float masked_score(float s, float scale, const MaskRo
   return s * scale + m.at(j);
 }
 
+// ---- dropout: the reference's counter-based stream (csrc/shaders/philox.glsl; sdpa_training.comp:17) ------------------
+// Philox4x32-10 (Salmon et al., "Parallel random numbers: as easy as 1, 2, 3") keyed by the 64-bit seed; the counter
+// is the 64-bit offset reserved for the call plus the element's block (four elements per block, one output word
+// each).  An element is kept when its uniform in [0, 1) (top 24 bits of the word) is at least the dropout probability,
+// and kept probabilities are scaled by 1 / (1 - p).
+struct DropState {
+  float p, keep_scale;   // dropout probability; 1 / (1 - p) (0 when p == 1)
+  uint2 seed, offset;
+};
+__device__ __forceinline__ uint4 philox4x32_10(uint2 key, uint4 c) {
+#pragma unroll
+  for (int round = 0; round < 10; ++round) {
+    const uint32_t hi0 = __umulhi(0xD2511F53u, c.x), lo0 = 0xD2511F53u * c.x;
+    const uint32_t hi1 = __umulhi(0xCD9E8D57u, c.z), lo1 = 0xCD9E8D57u * c.z;
+    c = make_uint4(hi1 ^ c.y ^ key.x, lo1, hi0 ^ c.w ^ key.y, lo0);
+    key.x += 0x9E3779B9u;
+    key.y += 0xBB67AE85u;
+  }
+  return c;
+}
+__device__ __forceinline__ uint4 drop_words(const DropState& d, uint32_t block) {
+  const uint32_t low = d.offset.x + block;
+  return philox4x32_10(d.seed, make_uint4(low, d.offset.y + (low < d.offset.x ? 1u : 0u), 0u, 0u));
+}
+__device__ __forceinline__ float keep_weight(const DropState& d, uint32_t word) {
+  return (float)(word >> 8) * 0.000000059604644775390625f >= d.p ? d.keep_scale : 0.f;
+}
+// weight of element `index` (0 when dropped)
+__device__ __forceinline__ float drop_weight(const DropState& d, uint32_t index) {
+  if (d.p == 0.f) return 1.f;
+  if (d.p >= 1.f) return 0.f;
+  const uint4 r = drop_words(d, index >> 2);
+  const uint32_t w = (index & 3u) == 0 ? r.x : (index & 3u) == 1 ? r.y : (index & 3u) == 2 ? r.z : r.w;
+  return keep_weight(d, w);
+}
+// weights of the four elements of block `block` (index = 4 * block + i)
+__device__ __forceinline__ float4 drop_weight4(const DropState& d, uint32_t block) {
+  if (d.p == 0.f) return make_float4(1.f, 1.f, 1.f, 1.f);
+  if (d.p >= 1.f) return make_float4(0.f, 0.f, 0.f, 0.f);
+  const uint4 r = drop_words(d, block);
+  return make_float4(keep_weight(d, r.x), keep_weight(d, r.y), keep_weight(d, r.z), keep_weight(d, r.w));
+}
+
 // One CTA per score row: s[j] <- softmax_j(s[j] * scale + mask), lse[row] <- log sum exp.
 __global__ void __launch_bounds__(kThreads) softmax_rows_kernel(float* __restrict__ scores, const void* __restrict__ mask, int mask_type, int tq,
-                                                                 int tk, float scale, int causal, float* __restrict__ lse) {
+                                                                 int tk, float scale, int causal, float* __restrict__ lse,
+                                                                 DropState drop) {
   __shared__ float scratch[kThreads / 32];
   const long long row = blockIdx.x;
   const int i = (int)(row % tq);
@@ -96,14 +140,14 @@ __global__ void __launch_bounds__(kThreads) softmax_rows_kernel(float* __restric
   if (threadIdx.x == 0) lse[row] = logsum;
   const bool dead = !(logsum > -INFINITY);
   for (int j = threadIdx.x; j < tk; j += kThreads)
-    s[j] = dead ? 0.f : expf(masked_score(s[j], scale, mrow, i, j, causal) - logsum);
+    s[j] = dead ? 0.f : expf(masked_score(s[j], scale, mrow, i, j, causal) - logsum) * drop_weight(drop, (uint32_t)(row * tk + j));
 }
 
 // The same for rows of at most 4096 keys that are whole 16-byte groups: the row is read once into
 // registers (four groups of four per thread), reduced there and written once.
 __global__ void __launch_bounds__(kThreads) softmax_rows_resident_kernel(float* __restrict__ scores, const void* __restrict__ mask,
                                                                           int mask_type, int tq, int tk, float scale, int causal,
-                                                                          float* __restrict__ lse) {
+                                                                          float* __restrict__ lse, DropState drop) {
   __shared__ float scratch[kThreads / 32];
   const long long row = blockIdx.x;
   const int i = (int)(row % tq), quads = tk >> 2;
@@ -143,9 +187,12 @@ __global__ void __launch_bounds__(kThreads) softmax_rows_resident_kernel(float* 
 #pragma unroll
   for (int u = 0; u < 4; ++u) {
     const int q = threadIdx.x + u * kThreads;
-    if (q < quads)
-      s4[q] = dead ? make_float4(0.f, 0.f, 0.f, 0.f)
-                   : make_float4(v[4 * u] * inv, v[4 * u + 1] * inv, v[4 * u + 2] * inv, v[4 * u + 3] * inv);
+    if (q < quads) {
+      // tk is a multiple of 4 here, so the four elements are one Philox block
+      const float4 w = drop_weight4(drop, (uint32_t)((row * tk) >> 2) + (uint32_t)q);
+      s4[q] = dead ? make_float4(0.f, 0.f, 0.f, 0.f)   // (the row's values are still -inf: no arithmetic on them)
+                   : make_float4(v[4 * u] * inv * w.x, v[4 * u + 1] * inv * w.y, v[4 * u + 2] * inv * w.z, v[4 * u + 3] * inv * w.w);
+    }
   }
 }
 
@@ -176,35 +223,41 @@ __global__ void __launch_bounds__(kThreads) probabilities_kernel(float* __restri
     s[j] = dead ? 0.f : expf(masked_score(s[j], scale, mrow, i, j, causal) - logsum);
 }
 
-// Backward, second step: dp[j] <- dS[j] = P[j] * (dp[j] - delta) * scale with delta = sum_e dO[e] O[e]
-// of the row (sdpa_training.comp:38); dmask[j] <- the same without the scale when the mask gradient is wanted.
-__global__ void __launch_bounds__(kThreads) score_gradient_kernel(float* __restrict__ dp, const float* __restrict__ p,
+// Backward, second step: dp[j] <- dS[j] = P[j] * (dp[j] * w[j] - delta) * scale with delta = sum_e dO[e] O[e]
+// of the row and w the dropout weight (sdpa_training.comp:38); dmask[j] <- the same without the scale when the mask
+// gradient is wanted; with dropout p[j] <- P[j] * w[j], which is what dV = (P w)^T dO contracts afterwards.
+__global__ void __launch_bounds__(kThreads) score_gradient_kernel(float* __restrict__ dp, float* __restrict__ p,
                                                                    const float* __restrict__ grad, const float* __restrict__ out, int tk,
-                                                                   int dv, float scale, float* __restrict__ dmask) {
+                                                                   int dv, float scale, float* __restrict__ dmask, DropState drop) {
   __shared__ float scratch[kThreads / 32];
   const long long row = blockIdx.x;
   float delta = 0.f;
   for (int e = threadIdx.x; e < dv; e += kThreads) delta = fmaf(__ldg(grad + row * dv + e), __ldg(out + row * dv + e), delta);
   delta = block_reduce<false>(delta, scratch);
   float* d = dp + row * tk;
-  const float* pr = p + row * tk;
+  float* pr = p + row * tk;
   float* dm = dmask ? dmask + row * tk : nullptr;
+  const bool dropping = drop.p != 0.f;
   if ((tk & 3) == 0 && ((reinterpret_cast<uintptr_t>(d) | reinterpret_cast<uintptr_t>(pr) | reinterpret_cast<uintptr_t>(dm)) & 15) == 0) {
     float4* d4 = reinterpret_cast<float4*>(d);
     float4* dm4 = reinterpret_cast<float4*>(dm);
-    const float4* p4 = reinterpret_cast<const float4*>(pr);
+    float4* p4 = reinterpret_cast<float4*>(pr);
     for (int q = threadIdx.x; q < (tk >> 2); q += kThreads) {
-      const float4 a = d4[q], b = __ldg(p4 + q);
-      const float4 ds = make_float4(b.x * (a.x - delta), b.y * (a.y - delta), b.z * (a.z - delta), b.w * (a.w - delta));
+      const float4 a = d4[q], b = p4[q];
+      const float4 w = drop_weight4(drop, (uint32_t)((row * tk) >> 2) + (uint32_t)q);
+      const float4 ds = make_float4(b.x * (a.x * w.x - delta), b.y * (a.y * w.y - delta), b.z * (a.z * w.z - delta), b.w * (a.w * w.w - delta));
       if (dm4) dm4[q] = ds;
       d4[q] = make_float4(ds.x * scale, ds.y * scale, ds.z * scale, ds.w * scale);
+      if (dropping) p4[q] = make_float4(b.x * w.x, b.y * w.y, b.z * w.z, b.w * w.w);
     }
     return;
   }
   for (int j = threadIdx.x; j < tk; j += kThreads) {
-    const float ds = pr[j] * (d[j] - delta);
+    const float w = drop_weight(drop, (uint32_t)(row * tk + j));
+    const float pj = pr[j], ds = pj * (d[j] * w - delta);
     if (dm) dm[j] = ds;
     d[j] = ds * scale;
+    if (dropping) pr[j] = pj * w;
   }
 }
 
@@ -223,6 +276,17 @@ int make_shape(int64_t batch, int64_t tq, int64_t tk, int64_t d, int64_t dv, Att
   if (tk > INT32_MAX || tq > INT32_MAX || dv > INT32_MAX || (tk > 0 && batch * tq > (int64_t)UINT32_MAX / tk))
     return fail(B200_ERANGE, "attention score indexing exceeds uint32");
   *out = {batch, tq, tk, d, dv, ((size_t)(batch * tq * tk) * sizeof(float) + 255) & ~(size_t)255};
+  return B200_OK;
+}
+
+int make_drop(float dropout, const uint32_t* rng, DropState* d) {
+  if (!(dropout >= 0.f && dropout <= 1.f)) return fail(B200_EINVAL, "invalid attention dropout");
+  *d = DropState{dropout, dropout < 1.f ? 1.f / (1.f - dropout) : 0.f, make_uint2(0u, 0u), make_uint2(0u, 0u)};
+  if (dropout > 0.f && dropout < 1.f) {
+    if (!rng) return fail(B200_EINVAL, "attention dropout needs the four words of the random stream (seed, offset)");
+    d->seed = make_uint2(rng[0], rng[1]);
+    d->offset = make_uint2(rng[2], rng[3]);
+  }
   return B200_OK;
 }
 
@@ -253,12 +317,14 @@ size_t b200_attention_workspace(int64_t batch, int64_t tq, int64_t tk, int64_t d
 }
 
 int b200_attention_forward(int64_t batch, int64_t tq, int64_t tk, int64_t d, int64_t dv, const float* q, const float* k,
-                           const float* v, const void* mask, int mask_type, int causal, float scale, float* out, float* lse,
-                           void* workspace, size_t workspace_bytes, void* stream) {
+                           const float* v, const void* mask, int mask_type, int causal, float scale, float dropout,
+                           const uint32_t* rng, float* out, float* lse, void* workspace, size_t workspace_bytes, void* stream) {
   if (int rc = ensure_init()) return rc;
   AttentionShape sh;
   if (int rc = make_shape(batch, tq, tk, d, dv, &sh)) return rc;
   if (int rc = check_mask(mask, mask_type)) return rc;
+  DropState drop;
+  if (int rc = make_drop(dropout, rng, &drop)) return rc;
   const int64_t rows = batch * tq;
   if (rows == 0) return B200_OK;
   if (!q || !out || !lse || (tk > 0 && (!k || !v))) return fail(B200_EINVAL, "attention: null tensor");
@@ -276,8 +342,8 @@ int b200_attention_forward(int64_t batch, int64_t tq, int64_t tk, int64_t d, int
   const uintptr_t mask_align = mask_type == B200_MASK_BYTES ? 3 : 15;
   const bool resident = tk % 4 == 0 && tk <= 16 * kThreads && (reinterpret_cast<uintptr_t>(scores) & 15) == 0 &&
                         (reinterpret_cast<uintptr_t>(mask) & mask_align) == 0;
-  if (resident) softmax_rows_resident_kernel<<<(unsigned)rows, kThreads, 0, st>>>(scores, mask, mask_type, (int)tq, (int)tk, scale, causal, lse);
-  else softmax_rows_kernel<<<(unsigned)rows, kThreads, 0, st>>>(scores, mask, mask_type, (int)tq, (int)tk, scale, causal, lse);
+  if (resident) softmax_rows_resident_kernel<<<(unsigned)rows, kThreads, 0, st>>>(scores, mask, mask_type, (int)tq, (int)tk, scale, causal, lse, drop);
+  else softmax_rows_kernel<<<(unsigned)rows, kThreads, 0, st>>>(scores, mask, mask_type, (int)tq, (int)tk, scale, causal, lse, drop);
   count_launch();
   if (int rc = launch_check("softmax_rows_kernel")) return rc;
   if (dv == 0) return B200_OK;
@@ -297,12 +363,14 @@ int b200_attention_lse_finite(float* lse, int64_t count, void* stream) {
 
 int b200_attention_backward(int64_t batch, int64_t tq, int64_t tk, int64_t d, int64_t dv, const float* grad, const float* q,
                             const float* k, const float* v, const void* mask, int mask_type, const float* out, const float* lse,
-                            int causal, float scale, float* dq, float* dk, float* dvalue, float* dmask, void* workspace,
-                            size_t workspace_bytes, void* stream) {
+                            int causal, float scale, float dropout, const uint32_t* rng, float* dq, float* dk, float* dvalue,
+                            float* dmask, void* workspace, size_t workspace_bytes, void* stream) {
   if (int rc = ensure_init()) return rc;
   AttentionShape sh;
   if (int rc = make_shape(batch, tq, tk, d, dv, &sh)) return rc;
   if (int rc = check_mask(mask, mask_type)) return rc;
+  DropState drop;
+  if (int rc = make_drop(dropout, rng, &drop)) return rc;
   if (!dq || !dk || !dvalue) return fail(B200_EINVAL, "attention backward: null gradient");
   cudaStream_t st = (cudaStream_t)stream;
   const int64_t rows = batch * tq;
@@ -322,13 +390,14 @@ int b200_attention_backward(int64_t batch, int64_t tq, int64_t tk, int64_t d, in
   probabilities_kernel<<<(unsigned)rows, kThreads, 0, st>>>(p, mask, mask_type, (int)tq, (int)tk, scale, causal, lse);
   count_launch();
   if (int rc = launch_check("probabilities_kernel")) return rc;
-  // dV[b] = P[b]^T dO[b]
-  if (int rc = b200_bmm(batch, tk, dv, tq, p, tq * tk, 1, tk, grad, tq * dv, dv, 1, dvalue, B200_ALGO_AUTO, stream)) return rc;
   // dP[b] = dO[b] V[b]^T
   if (int rc = b200_bmm(batch, tq, tk, dv, grad, tq * dv, dv, 1, v, tk * dv, 1, dv, dp, B200_ALGO_AUTO, stream)) return rc;
-  score_gradient_kernel<<<(unsigned)rows, kThreads, 0, st>>>(dp, p, grad, out, (int)tk, (int)dv, scale, dmask);
+  // dS in place of dP; with dropout P becomes P w for the product below
+  score_gradient_kernel<<<(unsigned)rows, kThreads, 0, st>>>(dp, p, grad, out, (int)tk, (int)dv, scale, dmask, drop);
   count_launch();
   if (int rc = launch_check("score_gradient_kernel")) return rc;
+  // dV[b] = (P w)[b]^T dO[b]
+  if (int rc = b200_bmm(batch, tk, dv, tq, p, tq * tk, 1, tk, grad, tq * dv, dv, 1, dvalue, B200_ALGO_AUTO, stream)) return rc;
   // dQ[b] = dS[b] K[b];  dK[b] = dS[b]^T Q[b]
   if (int rc = b200_bmm(batch, tq, d, tk, dp, tq * tk, tk, 1, k, tk * d, d, 1, dq, B200_ALGO_AUTO, stream)) return rc;
   const int rc = b200_bmm(batch, tk, d, tq, dp, tq * tk, 1, tk, q, tq * d, d, 1, dk, B200_ALGO_AUTO, stream);

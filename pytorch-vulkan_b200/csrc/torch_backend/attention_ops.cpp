@@ -5,10 +5,12 @@
 //     F.scaled_dot_product_attention here.
 //   aten::_scaled_dot_product_flash_attention_for_cpu and its backward (:36-43), with their shape checks and messages:
 //     [B, H, T, D] operands reshaped to B*H batches, a 2-D or 4-D additive FP32 mask expanded to the scores' shape (:38).
-// Operands are made contiguous and handed to b200_attention_forward / _backward.  Dropout strictly between 0 and 1 is not
-// supported (the reference draws it from a Philox stream, sdpa_training.comp:17); 0 is the identity.
+// Operands are made contiguous and handed to b200_attention_forward / _backward.  Dropout draws from the backend's
+// Philox stream (seed from torch_vulkan.manual_seed, offset advanced per call), whose four state words travel from
+// the forward to the backward operator as a CPU tensor, as in the reference (attention.cpp:17-18,25).
 #include <torch/library.h>
 
+#include <array>
 #include <cmath>
 #include <optional>
 #include <tuple>
@@ -54,12 +56,15 @@ void check3(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const
   TORCH_CHECK(q.device() == k.device() && k.device() == v.device() && (!mask.defined() || !mask.numel() || mask.device() == q.device()),
               "attention devices mismatch");
   TORCH_CHECK(dropout >= 0 && dropout <= 1, "invalid attention dropout");
-  // 0 keeps every probability, 1 drops every one (sdpa_training.comp:17 `dropped`); anything between draws from the
-  // reference's device Philox stream, which this build does not have
-  TORCH_CHECK(dropout == 0 || dropout == 1, "Vulkan attention: dropout is not implemented by this backend build");
 }
 
-at::Tensor rng_metadata() { return at::zeros({4}, at::TensorOptions().dtype(at::kLong).device(at::kCPU)); }
+// The four words of the random stream as the CPU int64 tensor the operator pair hands from forward to backward
+// (attention.cpp:18 of the reference); zeros when no stream is drawn from.
+at::Tensor rng_metadata(const std::array<uint32_t, 4>& state = {0, 0, 0, 0}) {
+  auto t = at::empty({4}, at::TensorOptions().dtype(at::kLong).device(at::kCPU));
+  for (int i = 0; i < 4; ++i) t.data_ptr<int64_t>()[i] = state[i];
+  return t;
+}
 
 std::tuple<at::Tensor, at::Tensor, at::Tensor> attention_forward3(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
                                                                   const at::Tensor& mask, double dropout, bool causal, double scale) {
@@ -68,19 +73,21 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> attention_forward3(const at::Tens
   const int64_t batch = q.size(0), tq = q.size(1), tk = k.size(1), d = q.size(2), dv = v.size(2);
   auto out = at::empty({batch, tq, dv}, q.options().memory_format(at::MemoryFormat::Contiguous));
   auto lse = at::empty({batch, tq}, q.options().memory_format(at::MemoryFormat::Contiguous));
-  if (!lse.numel()) return {out, lse, rng_metadata()};
+  // a stream is reserved exactly when the reference reserves one (attention.cpp:17): a quarter block per score
+  std::array<uint32_t, 4> state = {0, 0, 0, 0};
+  if (dropout > 0 && dropout < 1) state = reserve_random_blocks(((uint64_t)batch * tq * tk + 3) / 4);
+  if (!lse.numel()) return {out, lse, rng_metadata(state)};
   if (!out.numel()) {  // no value features: nothing to weigh, the reference reports a zero log-sum-exp (attention.cpp:20)
     lse.zero_();
-    return {out, lse, rng_metadata()};
+    return {out, lse, rng_metadata(state)};
   }
   const at::Tensor qc = packed(q), kc = packed(k), vc = packed(v), mc = kind ? packed(mask) : at::Tensor();
   Workspace ws(batch, tq, tk, d, dv, false, q.options());
   B200_TORCH_CHECK(b200_attention_forward(batch, tq, tk, d, dv, qc.const_data_ptr<float>(), kc.const_data_ptr<float>(),
                                           vc.const_data_ptr<float>(), kind ? mc.const_data_ptr() : nullptr, kind, causal ? 1 : 0,
-                                          (float)scale, out.data_ptr<float>(), lse.data_ptr<float>(), ws.hold.data_ptr(), ws.bytes,
-                                          backend_stream()));
-  if (dropout == 1) out.zero_();  // every probability dropped: the log-sum-exp stands, the weighted sum is empty
-  return {out, lse, rng_metadata()};
+                                          (float)scale, (float)dropout, state.data(), out.data_ptr<float>(), lse.data_ptr<float>(),
+                                          ws.hold.data_ptr(), ws.bytes, backend_stream()));
+  return {out, lse, rng_metadata(state)};
 }
 
 std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> attention_backward3(const at::Tensor& grad, const at::Tensor& q,
@@ -99,11 +106,8 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> attention_backward3(c
   const auto dense = [](const at::Tensor& like) { return like.options().memory_format(at::MemoryFormat::Contiguous); };
   auto dq = at::empty(q.sizes(), dense(q)), dk = at::empty(k.sizes(), dense(k)), dvalue = at::empty(v.sizes(), dense(v));
   auto dm = at::empty({batch, tq, tk}, dense(q));
-  if (dropout == 1) {  // nothing reached the output, so nothing flows back (ds = P (0 - 0), dv = P * 0 * dO)
-    for (at::Tensor* t : {&dq, &dk, &dvalue, &dm})
-      if (t->numel()) t->zero_();
-    return {dq, dk, dvalue, dm};
-  }
+  std::array<uint32_t, 4> state;
+  for (int i = 0; i < 4; ++i) state[i] = (uint32_t)rng.const_data_ptr<int64_t>()[i];
   const at::Tensor gc = packed(grad), qc = packed(q), kc = packed(k), vc = packed(v), oc = packed(out), lc = packed(lse),
                    mc = kind ? packed(mask) : at::Tensor();
   Workspace ws(batch, tq, tk, d, dv, true, q.options());
@@ -113,8 +117,8 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> attention_backward3(c
   static float placeholder;
   const auto want = [&](at::Tensor& t) { float* p = out_ptr(t); return p ? p : &placeholder; };
   B200_TORCH_CHECK(b200_attention_backward(batch, tq, tk, d, dv, ptr(gc), ptr(qc), ptr(kc), ptr(vc), kind ? mc.const_data_ptr() : nullptr,
-                                           kind, ptr(oc), ptr(lc), causal ? 1 : 0, (float)scale, want(dq), want(dk), want(dvalue),
-                                           out_ptr(dm), ws.hold.data_ptr(), ws.bytes, backend_stream()));
+                                           kind, ptr(oc), ptr(lc), causal ? 1 : 0, (float)scale, (float)dropout, state.data(), want(dq),
+                                           want(dk), want(dvalue), out_ptr(dm), ws.hold.data_ptr(), ws.bytes, backend_stream()));
   return {dq, dk, dvalue, dm};
 }
 

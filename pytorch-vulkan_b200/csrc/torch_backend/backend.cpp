@@ -40,6 +40,27 @@ ExecutionStats& execution_stats() {
   static ExecutionStats s;
   return s;
 }
+
+namespace {
+std::mutex rng_mutex;
+uint64_t rng_seed = 67280421310721ull, rng_offset = 0;   // PyTorch's default seed value until manual_seed is called
+}  // namespace
+void set_random_seed(uint64_t seed) {
+  std::lock_guard<std::mutex> lock(rng_mutex);
+  rng_seed = seed;
+  rng_offset = 0;
+}
+uint64_t random_seed() {
+  std::lock_guard<std::mutex> lock(rng_mutex);
+  return rng_seed;
+}
+std::array<uint32_t, 4> reserve_random_blocks(uint64_t blocks) {
+  std::lock_guard<std::mutex> lock(rng_mutex);
+  TORCH_CHECK(blocks <= UINT64_MAX - rng_offset, "Vulkan RNG counter exhausted");
+  const std::array<uint32_t, 4> state = {uint32_t(rng_seed), uint32_t(rng_seed >> 32), uint32_t(rng_offset), uint32_t(rng_offset >> 32)};
+  rng_offset += blocks;
+  return state;
+}
 static std::mutex stats_mutex;
 void note_host_read(size_t bytes) {
   std::lock_guard<std::mutex> lock(stats_mutex);
@@ -219,6 +240,8 @@ PYBIND11_MODULE(_C, m) {
     return d;
   });
   m.def("_reset_execution_stats", [] { execution_stats() = ExecutionStats(); });
+  m.def("_manual_seed", [](uint64_t seed) { set_random_seed(seed); });
+  m.def("_initial_seed", [] { return random_seed(); });
   m.def("_current_stream", [] {
     return py::reinterpret_steal<py::object>(THPStream_Wrap(
         c10::Stream(c10::Stream::UNSAFE, c10::Device(c10::DeviceType::PrivateUse1, 0), current_stream_id)));

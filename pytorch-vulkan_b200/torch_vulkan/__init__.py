@@ -106,13 +106,10 @@ def _is_in_bad_fork() -> bool:
     return False
 
 
-# Device RNG is outside the convolution path: the seed is kept so that the module satisfies
-# torch.manual_seed's device-module protocol, and tensors are drawn on the host and moved.
-_seed_state = {"seed": 0}
-
-
+# The backend keeps one counter-based random stream (64-bit seed, 64-bit offset; the reference's VulkanGenerator):
+# attention dropout draws from it.  Random tensor factories are outside this build: tensors are drawn on the host.
 def manual_seed_all(seed: int) -> None:
-    _seed_state["seed"] = int(seed)
+    _C._manual_seed(int(seed) & ((1 << 64) - 1))
 
 
 def manual_seed(seed: int) -> None:
@@ -120,7 +117,7 @@ def manual_seed(seed: int) -> None:
 
 
 def initial_seed() -> int:
-    return _seed_state["seed"]
+    return _C._initial_seed()
 
 
 def seed() -> None:
@@ -133,12 +130,12 @@ def seed_all() -> None:
 
 def get_rng_state(device="vulkan"):
     _validate_device(device)
-    return torch.tensor([_seed_state["seed"]], dtype=torch.int64)
+    return torch.tensor([_C._initial_seed() & ((1 << 63) - 1)], dtype=torch.int64)   # the seed; the offset restarts at 0
 
 
 def set_rng_state(state, device="vulkan"):
     _validate_device(device)
-    _seed_state["seed"] = int(state.reshape(-1)[0])
+    manual_seed_all(int(state.reshape(-1)[0]))
 
 
 torch._register_device_module("vulkan", sys.modules[__name__])

@@ -7,7 +7,7 @@ attention_backward (csrc/torch_backend/attention_ops.cpp here, csrc/ops/attentio
 instead of the softmax/matmul decomposition.  Operands of any leading shape are flattened to
 [batch, tokens, dim]; masks may be bool (False hides the key) or float32 (added to the scores; its
 gradient is returned when it requires one); grouped-query attention repeats the key/value heads.
-Dropout between 0 and 1 is refused by the device operator.
+Dropout draws from the backend's counter-based stream (torch_vulkan.manual_seed).
 """
 import math
 

@@ -166,8 +166,8 @@ def test_scaled_dot_product_attention_gqa_without_grad_and_rejections():
     with torch.no_grad():
         got = F.scaled_dot_product_attention(q.to("vulkan"), k.to("vulkan"), v.to("vulkan"), enable_gqa=True)
     torch.testing.assert_close(got.cpu(), F.scaled_dot_product_attention(q, k, v, enable_gqa=True), rtol=3e-4, atol=3e-5)
-    with pytest.raises(RuntimeError, match="dropout is not implemented"):
-        F.scaled_dot_product_attention(q.to("vulkan"), q.to("vulkan"), q.to("vulkan"), dropout_p=0.5)
+    with pytest.raises(RuntimeError, match="invalid attention dropout"):
+        torch.ops.torch_vulkan.attention_forward(q[0].to("vulkan"), q[0].to("vulkan"), q[0].to("vulkan"), torch.empty(0).to("vulkan"), 1.5, False, 1.0)
     # dropout_p = 1 drops every probability: zero output and zero gradients (tests/test_complete_attention.py:36-45 there)
     qd = q.to("vulkan").requires_grad_()
     full = F.scaled_dot_product_attention(qd, qd.detach(), qd.detach(), dropout_p=1.0)
@@ -193,3 +193,48 @@ def test_attention_empty_dimensions(batch, qlen, klen, dv):
     torch.testing.assert_close(actual.cpu(), expected)
     for a, b in zip(inputs, (q, k, v)):
         torch.testing.assert_close(a.grad.cpu(), b.grad)
+
+
+@pytest.mark.parametrize("shape", [(2, 5, 7, 4, 6), (2, 137, 19, 8, 3), (3, 128, 256, 64, 64)])
+@pytest.mark.parametrize("p", [0.1, 0.35, 0.9])
+def test_dropout_stream_through_the_c_abi(shape, p):
+    """Forward and all gradients with dropout against the oracle drawing the same Philox stream (seed, offset)."""
+    batch, tq, tk, d, dv = shape
+    rng = np.random.default_rng(tq + tk)
+    r = lambda *s: rng.standard_normal(s, dtype=np.float32)
+    q, k, v, grad, add = r(batch, tq, d), r(batch, tk, d), r(batch, tk, dv), r(batch, tq, dv), r(batch, tq, tk)
+    stream = (0x1234567887654321, 0xFFFFFFF0)       # the block counter carries into the high offset word
+    out, lse = b200conv.attention_forward(q, k, v, add, True, scale=0.37, dropout=p, rng=stream)
+    wout, wlse = att.forward(q, k, v, add, True, scale=0.37, dropout=p, rng=stream)
+    assert oracle.rel_l2(out, wout) <= GATE
+    np.testing.assert_allclose(lse, wlse, rtol=1e-4, atol=1e-4)
+    got = b200conv.attention_backward(grad, q, k, v, out, lse, add, True, scale=0.37, mask_grad=True, dropout=p, rng=stream)
+    want = att.backward(grad, q, k, v, wout, wlse, add, True, scale=0.37, mask_grad=True, dropout=p, rng=stream)
+    for a, e in zip(got, want):
+        assert oracle.rel_l2(a, e) <= 2 * GATE
+    other, _ = b200conv.attention_forward(q, k, v, add, True, scale=0.37, dropout=p, rng=(stream[0], stream[1] + 1))
+    assert not np.array_equal(other, out)
+
+
+def test_scaled_dot_product_attention_with_dropout_is_seeded_and_consistent():
+    """tests/test_complete_attention.py:36-45 of the reference: the same seed gives the same mask, and the gradient agrees
+    with finite differences taken under that mask; here also with the oracle drawing the stream from offset 0."""
+    import torch.nn.functional as F
+    import torch_vulkan
+    torch.manual_seed(1)
+    q, k, v = (torch.randn(1, 2, 9, 8) for _ in range(3))
+    dev = [t.to("vulkan").requires_grad_() for t in (q, k, v)]
+    torch_vulkan.manual_seed(42)
+    out = F.scaled_dot_product_attention(*dev, dropout_p=0.35)
+    out.backward(torch.ones_like(out))
+    torch_vulkan.manual_seed(42)
+    again = F.scaled_dot_product_attention(*[t.detach() for t in dev], dropout_p=0.35)
+    assert torch.equal(again.cpu(), out.detach().cpu())
+    later = F.scaled_dot_product_attention(*[t.detach() for t in dev], dropout_p=0.35)        # the offset has advanced
+    assert not torch.equal(later.cpu(), out.detach().cpu())
+    n = lambda t: t.reshape(2, 9, 8).numpy()
+    want, wlse = att.forward(n(q), n(k), n(v), dropout=0.35, rng=(42, 0))
+    assert oracle.rel_l2(out.detach().cpu().reshape(2, 9, 8).numpy(), want) <= GATE
+    grads = att.backward(np.ones((2, 9, 8), np.float32), n(q), n(k), n(v), want, wlse, dropout=0.35, rng=(42, 0))
+    for g, e in zip(dev, grads):
+        assert oracle.rel_l2(g.grad.cpu().reshape(2, 9, 8).numpy(), e) <= 2 * GATE

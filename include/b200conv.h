@@ -100,6 +100,13 @@ int b200_gather_strided(void* dst, const void* src, int ndim, const int64_t* siz
 int b200_scatter_strided(void* dst, const void* src, int ndim, const int64_t* sizes,
                          const int64_t* strides, int elem_bytes, void* stream);
 
+/* dst (contiguous over the dimensions that are kept, in their order) <- sum of the FP32 strided view over the
+ * dimensions with reduce[i] != 0.  The reduction the autograd graph of a broadcast operand needs (expand's backward,
+ * `sum_to_size`): a broadcast attention mask, grouped-query key / value heads.  Stands for the reference's reduction
+ * operator on this one signature (sum_dim, csrc/ops/reduce.cpp:24-35); one warp per result. */
+int b200_sum_strided(float* dst, const float* src, int ndim, const int64_t* sizes, const int64_t* strides,
+                     const unsigned char* reduce, void* stream);
+
 /* Streams and events: replaces the single in-order queue and event sequences of
  * csrc/torch_vulkan.cpp:34-103 and csrc/vulkan_context.cpp:493-523. */
 int b200_stream_create(void** stream);

@@ -395,6 +395,68 @@ static int strided_copy(void* dst, const void* src, int ndim, const int64_t* siz
 }
 }  // namespace b200
 
+// ---- strided sum over a subset of the dimensions --------------------------------------------------------------------
+namespace b200 {
+struct ReduceDesc {
+  int kept_dims, reduced_dims;
+  long long kept_size[8], kept_stride[8], red_size[8], red_stride[8];
+  long long red_total;
+};
+// One warp per result element: its lanes stride over the reduced elements (FP32 partial sums of at most
+// red_total / 32 terms each), then a shuffle tree in a fixed order.
+__global__ void __launch_bounds__(256) sum_strided_kernel(float* __restrict__ dst, const float* __restrict__ src, ReduceDesc d,
+                                                          long long outputs) {
+  const long long out = blockIdx.x * 8ll + (threadIdx.x >> 5);
+  if (out >= outputs) return;
+  const int lane = threadIdx.x & 31;
+  long long r = out, base = 0;
+  for (int k = d.kept_dims - 1; k >= 0; --k) {
+    const long long q = r / d.kept_size[k];
+    base += (r - q * d.kept_size[k]) * d.kept_stride[k];
+    r = q;
+  }
+  float acc = 0.f;
+  for (long long e = lane; e < d.red_total; e += 32) {
+    long long t = e, off = base;
+    for (int k = d.reduced_dims - 1; k >= 0; --k) {
+      const long long q = t / d.red_size[k];
+      off += (t - q * d.red_size[k]) * d.red_stride[k];
+      t = q;
+    }
+    acc += src[off];
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (lane == 0) dst[out] = acc;
+}
+}  // namespace b200
+
+extern "C" int b200_sum_strided(float* dst, const float* src, int ndim, const int64_t* sizes, const int64_t* strides,
+                                const unsigned char* reduce, void* stream) {
+  using namespace b200;
+  if (int rc = ensure_init()) return rc;
+  if (ndim < 0 || ndim > 8 || (ndim > 0 && (!sizes || !strides || !reduce))) return fail(B200_EINVAL, "strided sum supports at most 8 dimensions (got %d)", ndim);
+  ReduceDesc d{};
+  d.red_total = 1;
+  long long outputs = 1;
+  for (int i = 0; i < ndim; ++i) {
+    if (sizes[i] < 0) return fail(B200_EINVAL, "strided sum: negative extent");
+    if (reduce[i]) {
+      d.red_size[d.reduced_dims] = sizes[i]; d.red_stride[d.reduced_dims++] = strides[i];
+      d.red_total *= sizes[i];
+    } else {
+      d.kept_size[d.kept_dims] = sizes[i]; d.kept_stride[d.kept_dims++] = strides[i];
+      outputs *= sizes[i];
+    }
+  }
+  if (outputs == 0) return B200_OK;
+  if (!dst || (!src && d.red_total > 0)) return fail(B200_EINVAL, "strided sum: null tensor");
+  if (outputs > 8ll * 2147483647ll) return fail(B200_ERANGE, "strided sum: too many results");
+  sum_strided_kernel<<<(unsigned)((outputs + 7) / 8), 256, 0, (cudaStream_t)stream>>>(dst, src, d, outputs);
+  count_launch();
+  return launch_check("sum_strided_kernel");
+}
+
 extern "C" int b200_gather_strided(void* dst, const void* src, int ndim, const int64_t* sizes,
                                    const int64_t* strides, int elem_bytes, void* stream) {
   return b200::strided_copy<false>(dst, src, ndim, sizes, strides, elem_bytes, (cudaStream_t)stream);

@@ -665,6 +665,33 @@ static at::Tensor conv2d_fused(const at::Tensor& input, const at::Tensor& weight
   return out;
 }
 
+// ---- sum over a dimension list -------------------------------------------------------------------------
+// The one reduction the autograd graphs of this backend's operators need: expand's backward (`sum_to_size`) for a
+// broadcast attention mask or grouped-query key / value heads, and `.sum()` of a result.  FP32 only, any strides
+// (reference: sum_dim / sum_all, csrc/ops/reduce.cpp:24-35; its integer and fallback branches are not built).
+static at::Tensor sum_dim(const at::Tensor& x, at::OptionalIntArrayRef dim, bool keepdim, std::optional<at::ScalarType> dtype) {
+  TORCH_CHECK(on_device(x) && x.scalar_type() == at::kFloat && dtype.value_or(at::kFloat) == at::kFloat,
+              "Vulkan sum: only FP32 tensors are implemented by this backend build");
+  TORCH_CHECK(x.dim() <= 8, "Vulkan sum: at most 8 dimensions");
+  std::array<unsigned char, 8> reduce{};
+  if (!dim.has_value() || dim->empty()) {
+    for (int64_t d = 0; d < x.dim(); ++d) reduce[d] = 1;
+  } else {
+    for (int64_t d : *dim) reduce[at::maybe_wrap_dim(d, x.dim())] = 1;
+  }
+  std::vector<int64_t> shape;
+  for (int64_t d = 0; d < x.dim(); ++d) {
+    if (!reduce[d]) shape.push_back(x.size(d));
+    else if (keepdim) shape.push_back(1);
+  }
+  auto out = at::empty(shape, x.options().memory_format(at::MemoryFormat::Contiguous));
+  if (out.numel())
+    B200_TORCH_CHECK(b200_sum_strided(out.data_ptr<float>(), x.numel() ? x.const_data_ptr<float>() : nullptr, (int)x.dim(),
+                                      x.sizes().data(), x.strides().data(), reduce.data(), backend_stream()));
+  return out;
+}
+static at::Tensor sum_all(const at::Tensor& x, std::optional<at::ScalarType> dtype) { return sum_dim(x, std::nullopt, false, dtype); }
+
 // ---- mm / addmm ----------------------------------------------------------------------------------
 static void gemm_into(const at::Tensor& a, const at::Tensor& b, const float* bias, float alpha, float beta,
                       at::Tensor& out) {
@@ -764,6 +791,8 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
   m.impl("_reshape_alias", &reshape_alias);
   m.impl("convolution_overrideable", &convolution_overrideable);
   m.impl("convolution_backward_overrideable", &convolution_backward_overrideable);
+  m.impl("sum.dim_IntList", &sum_dim);
+  m.impl("sum", &sum_all);
   m.impl("mm", &mm);
   m.impl("mm.out", &mm_out);
   m.impl("addmm", &addmm);

@@ -131,7 +131,7 @@ def test_bool_masks_and_the_mask_gradient_through_the_c_abi(shape, causal):
 @pytest.mark.parametrize("kind", ["none", "causal", "bool", "float"])
 def test_scaled_dot_product_attention_forward_backward(shape, kind):
     """The reference's tests/test_complete_attention.py:6-24 with its tolerances; the float mask has the scores' full
-    shape here (a broadcast mask's gradient needs a device reduction operator this backend does not register)."""
+    shape here, the broadcast [1, 1, L, S] form is test_broadcast_float_mask_receives_its_gradient below."""
     import torch.nn.functional as F
     torch.manual_seed(432)
     b, h, l, s, d, e = shape
@@ -238,3 +238,59 @@ def test_scaled_dot_product_attention_with_dropout_is_seeded_and_consistent():
     grads = att.backward(np.ones((2, 9, 8), np.float32), n(q), n(k), n(v), want, wlse, dropout=0.35, rng=(42, 0))
     for g, e in zip(dev, grads):
         assert oracle.rel_l2(g.grad.cpu().reshape(2, 9, 8).numpy(), e) <= 2 * GATE
+
+
+@pytest.mark.parametrize("shape,dims,keepdim", [((4, 5, 6), (1,), False), ((4, 5, 6), (0, 2), True), ((3, 1, 7, 9), None, False),
+                                               ((2, 3, 4, 5, 6), (0, 1, 3), False), ((64, 300), (0,), False), ((5000,), (0,), False)])
+def test_sum_over_a_dimension_list(shape, dims, keepdim):
+    torch.manual_seed(3)
+    x = torch.randn(*shape)
+    want = x.double().sum() if dims is None else x.double().sum(dim=dims, keepdim=keepdim)
+    xd = x.to("vulkan")
+    got = xd.sum() if dims is None else xd.sum(dim=dims, keepdim=keepdim)
+    assert got.device.type == "vulkan" and got.shape == want.shape
+    torch.testing.assert_close(got.cpu().double(), want, rtol=1e-5, atol=1e-5)
+    if len(shape) >= 2:        # a transposed (strided) view sums the same
+        xt = xd.transpose(0, -1)
+        torch.testing.assert_close(xt.sum(dim=0).cpu().double(), x.transpose(0, -1).double().sum(dim=0), rtol=1e-5, atol=1e-5)
+    with pytest.raises(RuntimeError, match="only FP32"):
+        torch.ones(3, dtype=torch.int64).to("vulkan").sum()
+
+
+@pytest.mark.parametrize("gqa", [False, True])
+def test_attention_broadcast_and_gqa_with_gradients(gqa):
+    """tests/test_complete_attention.py:26-33 of the reference: broadcast batch, grouped-query heads, `.sum().backward()`."""
+    import torch.nn.functional as F
+    torch.manual_seed(8)
+    q = torch.randn(2, 4, 7, 5, requires_grad=True)
+    k = torch.randn(1, 2 if gqa else 4, 9, 5, requires_grad=True)
+    v = torch.randn(2, 2 if gqa else 4, 9, 3, requires_grad=True)
+    vs = [x.detach().to("vulkan").requires_grad_() for x in (q, k, v)]
+    a = F.scaled_dot_product_attention(q, k, v, enable_gqa=gqa)
+    b = F.scaled_dot_product_attention(*vs, enable_gqa=gqa)
+    a.sum().backward()
+    b.sum().backward()
+    torch.testing.assert_close(b.detach().cpu(), a.detach(), rtol=3e-4, atol=3e-5)
+    for x, y in zip(vs, (q, k, v)):
+        torch.testing.assert_close(x.grad.cpu(), y.grad, rtol=5e-4, atol=5e-5)
+
+
+def test_broadcast_float_mask_receives_its_gradient():
+    """The float-mask case of tests/test_complete_attention.py:6-24 as the reference writes it: a [1, 1, L, S] mask that
+    requires a gradient, broadcast over batch and heads."""
+    import torch.nn.functional as F
+    torch.manual_seed(432)
+    b, h, l, s, d, e = 2, 3, 5, 7, 4, 6
+    q, k, v = [torch.randn(size, requires_grad=True) for size in [(b, h, l, d), (b, h, s, d), (b, h, s, e)]]
+    mask = torch.randn(1, 1, l, s, requires_grad=True)
+    inputs = [x.detach().to("vulkan").requires_grad_() for x in (q, k, v)]
+    mv = mask.detach().to("vulkan").requires_grad_()
+    a = F.scaled_dot_product_attention(q, k, v, mask, scale=.37)
+    z = F.scaled_dot_product_attention(*inputs, mv, scale=.37)
+    g = torch.randn_like(a)
+    a.backward(g)
+    z.backward(g.to("vulkan"))
+    torch.testing.assert_close(z.detach().cpu(), a.detach(), rtol=4e-4, atol=4e-5)
+    for x, y in zip(inputs, (q, k, v)):
+        torch.testing.assert_close(x.grad.cpu(), y.grad, rtol=6e-4, atol=7e-5)
+    torch.testing.assert_close(mv.grad.cpu(), mask.grad, rtol=6e-4, atol=7e-5)

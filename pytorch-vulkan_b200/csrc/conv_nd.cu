@@ -4,10 +4,19 @@
 // shaders convolution_nd.comp / convolution_nd_int64.comp, also one invocation per output element).  The 2-D and
 // 1-D FP32 cases never come here: they run the Conv2D kernels; what remains is 3-D convolution and integer tensors.
 //
+// Three-dimensional FP32 convolutions with at least 16 channels per group on both sides do not run that kernel: they
+// are decomposed over the depth taps into 2-D convolutions on the tcgen05 kernels (conv3d_* below), each depth tap a
+// batch of depth slices read through a strided view, the partial results accumulated through the fused epilogue's
+// residual input.  The generic kernel remains for everything else (and as the fallback when a step declines).
+//
 //   ordinary     y[n, co, o]  = b[co] + sum_{ci in group, k} x[n, ci, o*s - p + k*d] * w[co, ci_local, k]
 //   transposed   y[n, co, o]  = b[co] + sum_{ci in group, k : (o + p - k*d) = i*s} x[n, ci, i] * w[ci, co_local, k]
 // and the three gradients of either (mode 1: dx, 2: dw, 3: db), each again one thread per result element.
 #include "common.cuh"
+
+#include <algorithm>
+#include <cstdlib>
+#include <vector>
 
 namespace b200 {
 namespace cnd {
@@ -130,6 +139,12 @@ __global__ void __launch_bounds__(256) convnd_db_kernel(Nd g, const float* __res
   if (lane == 0) db[co] = acc;
 }
 
+// rows[r][c] = bias[c] (or 0): the start value of the channels-last accumulation buffer
+__global__ void __launch_bounds__(256) fill_rows_kernel(float* __restrict__ dst, const float* __restrict__ bias, long long rows, int c) {
+  const long long i = blockIdx.x * 256ll + threadIdx.x;
+  if (i < rows * c) dst[i] = bias ? __ldg(bias + (int)(i % c)) : 0.f;
+}
+
 static Nd to_nd(const b200_convnd_params& p) {
   Nd g{};
   g.n = p.n; g.cin = p.cin; g.cout = p.cout; g.groups = p.groups; g.transposed = p.transposed;
@@ -138,6 +153,170 @@ static Nd to_nd(const b200_convnd_params& p) {
     g.s[a] = (int)p.stride[a]; g.p[a] = (int)p.pad[a]; g.d[a] = (int)p.dilation[a];
   }
   return g;
+}
+
+// ---- 3-D convolution on the 2-D tensor-core kernels ------------------------------------------------------------------
+// y[n, :, od] = bias + sum_kd conv2d(x[n, :, od*sd - pd + kd*dd], w[:, :, kd]): for every depth tap kd and sample n ONE 2-D
+// call whose batch is the range of output depths that tap reaches inside the input (view with batch stride sd * plane
+// pitch, no copy).  The calls accumulate in a channels-last buffer [n][od][oh][ow][cout] through
+// b200_conv2d_forward_fused (residual = the buffer itself), which starts as the bias rows and is transposed into the
+// contiguous result at the end.  dInput (stride 1, one group) is the same with the filter view flipped and transposed
+// (negative strides); dWeight runs the 2-D dWeight per (kd, n) into a scratch [n][kd][cout][cin/g][kh][kw], summed over
+// n and scattered into dW.
+struct Scratch {   // blocks of the library's stream-ordered allocator, released on scope exit
+  cudaStream_t st;
+  std::vector<void*> blocks;
+  explicit Scratch(cudaStream_t s) : st(s) {}
+  ~Scratch() { for (void* p : blocks) b200_free(p, st); }
+  int get(void** out, size_t bytes) {
+    if (int rc = b200_malloc(out, bytes ? bytes : 16, st)) return rc;
+    blocks.push_back(*out);
+    return B200_OK;
+  }
+};
+
+static bool conv3d_takes(const b200_convnd_params& p) {
+  if (getenv("B200_CONV3D_GENERIC")) return false;   // testing aid: pins the generic kernel
+  if (p.rank != 3 || p.transposed || p.n <= 0) return false;
+  if (p.cin / p.groups < 16 || p.cout / p.groups < 16) return false;
+  const long long plane = p.out[1] * p.out[2];
+  return p.in[0] * p.in[1] * p.in[2] > 0 && plane > 0 && p.n * p.out[0] * plane * std::max(p.cin, p.cout) < (1ll << 40);
+}
+// output depths [lo, hi] that tap kd reads inside the input: 0 <= od*sd - pd + kd*dd < D
+static void depth_range(const b200_convnd_params& p, long long kd, long long* lo, long long* hi) {
+  const long long off = kd * p.dilation[0] - p.pad[0], sd = p.stride[0];
+  *lo = off >= 0 ? 0 : (-off + sd - 1) / sd;
+  *hi = std::min<long long>(p.out[0] - 1, (p.in[0] - 1 - off) >= 0 ? (p.in[0] - 1 - off) / sd : -1);
+}
+
+static int conv3d_forward(const b200_convnd_params& p, const float* x, const float* w, const float* bias, float* y, cudaStream_t st) {
+  const long long D = p.in[0], H = p.in[1], W = p.in[2], OD = p.out[0], OH = p.out[1], OW = p.out[2], cig = p.cin / p.groups;
+  const long long kvol2 = p.k[1] * p.k[2];
+  Scratch scratch(st);
+  float* acc = nullptr;   // [n][od][oh][ow][cout]
+  const long long rows = p.n * OD * OH * OW;
+  if (int rc = scratch.get((void**)&acc, (size_t)rows * p.cout * sizeof(float))) return rc;
+  fill_rows_kernel<<<(unsigned)div_up64(rows * p.cout, 256), 256, 0, st>>>(acc, bias, rows, (int)p.cout);
+  count_launch();
+  if (int rc = launch_check("fill_rows_kernel")) return rc;
+  size_t ws_bytes = 0;
+  void* ws = nullptr;
+  for (long long kd = 0; kd < p.k[0]; ++kd) {
+    long long lo, hi;
+    depth_range(p, kd, &lo, &hi);
+    if (hi < lo) continue;
+    b200_conv_params p2;
+    if (int rc = b200_conv2d_geometry(&p2, hi - lo + 1, p.cin, p.cout, H, W, cig, p.k[1], p.k[2], p.stride[1], p.stride[2], p.pad[1], p.pad[2],
+                                      p.dilation[1], p.dilation[2], p.groups))
+      return rc;
+    if (p2.oh != OH || p2.ow != OW) return fail(B200_EINVAL, "convolution: invalid or oversized output shape");
+    if (b200_conv2d_select(&p2, B200_PHASE_FORWARD, B200_ALGO_TC, (size_t)1 << 40) != B200_ALGO_TC) return B200_EUNSUPPORTED;
+    const size_t need = b200_conv2d_workspace(&p2, B200_PHASE_FORWARD, B200_ALGO_TC, (size_t)1 << 40);
+    if (need > ws_bytes) {
+      if (int rc = scratch.get(&ws, need)) return rc;
+      ws_bytes = need;
+    }
+    const b200_view4 wv{w + kd * kvol2, {cig * p.k[0] * kvol2, p.k[0] * kvol2, p.k[2], 1}};
+    for (long long n = 0; n < p.n; ++n) {
+      const long long d0 = lo * p.stride[0] - p.pad[0] + kd * p.dilation[0];
+      const b200_view4 xv{x + (n * p.cin * D + d0) * H * W, {p.stride[0] * H * W, D * H * W, W, 1}};
+      float* block = acc + (n * OD + lo) * OH * OW * p.cout;
+      const b200_view4 res{block, {OH * OW * p.cout, 1, OW * p.cout, p.cout}};
+      const int rc = b200_conv2d_forward_fused(&p2, xv, wv, nullptr, 0, res, 0, block, 1, ws, ws_bytes, B200_ALGO_TC, st);
+      if (rc) return rc;   // B200_EUNSUPPORTED from the first call: the caller runs the generic kernel instead
+    }
+  }
+  // [n][od][oh][ow][cout] -> contiguous [n][cout][od][oh][ow]
+  const int64_t sizes[5] = {p.n, p.cout, OD, OH, OW};
+  const int64_t strides[5] = {OD * OH * OW * p.cout, 1, OH * OW * p.cout, OW * p.cout, p.cout};
+  return b200_gather_strided(y, acc, 5, sizes, strides, 4, st);
+}
+
+// dx[n, :, id] = sum_kd conv2d(dy[n, :, id + pd - kd*dd], flip(w[:, :, kd])^T), stride 1 in all three dimensions, one group
+static int conv3d_dinput(const b200_convnd_params& p, const float* grad, const float* w, float* dx, cudaStream_t st) {
+  if (p.groups != 1 || p.stride[0] != 1 || p.stride[1] != 1 || p.stride[2] != 1) return B200_EUNSUPPORTED;
+  const long long D = p.in[0], H = p.in[1], W = p.in[2], OD = p.out[0], OH = p.out[1], OW = p.out[2];
+  const long long kvol2 = p.k[1] * p.k[2];
+  const long long ph2 = p.dilation[1] * (p.k[1] - 1) - p.pad[1], pw2 = p.dilation[2] * (p.k[2] - 1) - p.pad[2];
+  if (ph2 < 0 || pw2 < 0) return B200_EUNSUPPORTED;   // padding beyond the filter reach: left to the generic kernel
+  Scratch scratch(st);
+  float* acc = nullptr;   // [n][d][h][w][cin]
+  const long long rows = p.n * D * H * W;
+  if (int rc = scratch.get((void**)&acc, (size_t)rows * p.cin * sizeof(float))) return rc;
+  fill_rows_kernel<<<(unsigned)div_up64(rows * p.cin, 256), 256, 0, st>>>(acc, nullptr, rows, (int)p.cin);
+  count_launch();
+  if (int rc = launch_check("fill_rows_kernel")) return rc;
+  size_t ws_bytes = 0;
+  void* ws = nullptr;
+  for (long long kd = 0; kd < p.k[0]; ++kd) {
+    // input depths id with 0 <= id + pd - kd*dd < OD
+    const long long off = p.pad[0] - kd * p.dilation[0];
+    const long long lo = std::max<long long>(0, -off), hi = std::min<long long>(D - 1, OD - 1 - off);
+    if (hi < lo) continue;
+    b200_conv_params p2;   // the 2-D convolution dy -> dx: cout input channels, cin output channels, flipped filter
+    if (int rc = b200_conv2d_geometry(&p2, hi - lo + 1, p.cout, p.cin, OH, OW, p.cout, p.k[1], p.k[2], 1, 1, ph2, pw2, p.dilation[1],
+                                      p.dilation[2], 1))
+      return rc;
+    if (p2.oh != H || p2.ow != W) return B200_EUNSUPPORTED;
+    if (b200_conv2d_select(&p2, B200_PHASE_FORWARD, B200_ALGO_TC, (size_t)1 << 40) != B200_ALGO_TC) return B200_EUNSUPPORTED;
+    const size_t need = b200_conv2d_workspace(&p2, B200_PHASE_FORWARD, B200_ALGO_TC, (size_t)1 << 40);
+    if (need > ws_bytes) {
+      if (int rc = scratch.get(&ws, need)) return rc;
+      ws_bytes = need;
+    }
+    // filter of that convolution: [cin][cout][kh][kw] = w[co][ci][kd][kh-1-ky][kw-1-kx]
+    const b200_view4 wv{w + kd * kvol2 + (kvol2 - 1), {p.k[0] * kvol2, p.cin * p.k[0] * kvol2, -p.k[2], -1}};
+    for (long long n = 0; n < p.n; ++n) {
+      const b200_view4 gv{grad + (n * p.cout * OD + (lo + off)) * OH * OW, {OH * OW, OD * OH * OW, OW, 1}};
+      float* block = acc + (n * D + lo) * H * W * p.cin;
+      const b200_view4 res{block, {H * W * p.cin, 1, W * p.cin, p.cin}};
+      if (int rc = b200_conv2d_forward_fused(&p2, gv, wv, nullptr, 0, res, 0, block, 1, ws, ws_bytes, B200_ALGO_TC, st)) return rc;
+    }
+  }
+  const int64_t sizes[5] = {p.n, p.cin, D, H, W};
+  const int64_t strides[5] = {D * H * W * p.cin, 1, H * W * p.cin, W * p.cin, p.cin};
+  return b200_gather_strided(dx, acc, 5, sizes, strides, 4, st);
+}
+
+// dw[:, :, kd] = sum_n dWeight2d(x[n, :, od*sd - pd + kd*dd], dy[n, :, od])
+static int conv3d_dweight(const b200_convnd_params& p, const float* grad, const float* x, float* dw, cudaStream_t st) {
+  const long long D = p.in[0], H = p.in[1], W = p.in[2], OD = p.out[0], OH = p.out[1], OW = p.out[2], cig = p.cin / p.groups;
+  const long long kvol2 = p.k[1] * p.k[2], slice = p.cout * cig * kvol2;
+  Scratch scratch(st);
+  float* parts = nullptr;   // [n][kd][cout][cin/g][kh][kw]
+  float* sums = nullptr;    // [kd][cout][cin/g][kh][kw]
+  if (int rc = scratch.get((void**)&parts, (size_t)(p.n * p.k[0] * slice) * sizeof(float))) return rc;
+  if (int rc = scratch.get((void**)&sums, (size_t)(p.k[0] * slice) * sizeof(float))) return rc;
+  B200_CUDA(cudaMemsetAsync(parts, 0, (size_t)(p.n * p.k[0] * slice) * sizeof(float), st));   // taps that reach no depth stay zero
+  size_t ws_bytes = 0;
+  void* ws = nullptr;
+  for (long long kd = 0; kd < p.k[0]; ++kd) {
+    long long lo, hi;
+    depth_range(p, kd, &lo, &hi);
+    if (hi < lo) continue;
+    b200_conv_params p2;
+    if (int rc = b200_conv2d_geometry(&p2, hi - lo + 1, p.cin, p.cout, H, W, cig, p.k[1], p.k[2], p.stride[1], p.stride[2], p.pad[1], p.pad[2],
+                                      p.dilation[1], p.dilation[2], p.groups))
+      return rc;
+    if (b200_conv2d_select(&p2, B200_PHASE_DWEIGHT, B200_ALGO_TC, (size_t)1 << 40) != B200_ALGO_TC) return B200_EUNSUPPORTED;
+    const size_t need = b200_conv2d_workspace(&p2, B200_PHASE_DWEIGHT, B200_ALGO_TC, (size_t)256 << 20);
+    if (need > ws_bytes) {
+      if (int rc = scratch.get(&ws, need)) return rc;
+      ws_bytes = need;
+    }
+    for (long long n = 0; n < p.n; ++n) {
+      const long long d0 = lo * p.stride[0] - p.pad[0] + kd * p.dilation[0];
+      const b200_view4 xv{x + (n * p.cin * D + d0) * H * W, {p.stride[0] * H * W, D * H * W, W, 1}};
+      const b200_view4 gv{grad + (n * p.cout * OD + lo) * OH * OW, {OH * OW, OD * OH * OW, OW, 1}};
+      if (int rc = b200_conv2d_dweight(&p2, xv, gv, parts + (n * p.k[0] + kd) * slice, need ? ws : nullptr, need, B200_ALGO_TC, st)) return rc;
+    }
+  }
+  // sum over n, then [kd][cout][cin/g][kh*kw] -> dw[cout][cin/g][kd][kh*kw]
+  const int64_t psizes[2] = {p.n, p.k[0] * slice}, pstrides[2] = {p.k[0] * slice, 1};
+  const unsigned char reduce[2] = {1, 0};
+  if (int rc = b200_sum_strided(sums, parts, 2, psizes, pstrides, reduce, st)) return rc;
+  const int64_t sizes[3] = {p.k[0], p.cout * cig, kvol2}, strides[3] = {kvol2, p.k[0] * kvol2, 1};
+  return b200_scatter_strided(dw, sums, 3, sizes, strides, 4, st);
 }
 
 }  // namespace cnd
@@ -189,6 +368,13 @@ int b200_convnd_forward(const b200_convnd_params* p, const void* x, const void* 
   if (!x || !w || !y) return fail(B200_EINVAL, "convolution: null tensor");
   const unsigned blocks = (unsigned)div_up64(total, 256);
   cudaStream_t st = (cudaStream_t)stream;
+  if (!is_int64 && cnd::conv3d_takes(*p)) {
+    const int rc = cnd::conv3d_forward(*p, (const float*)x, (const float*)w, (const float*)bias, (float*)y, st);
+    if (rc != B200_EUNSUPPORTED) {
+      note_kernel("conv3d_forward: depth taps on the 2-D tcgen05 kernels");
+      return rc;
+    }
+  }
   if (is_int64)
     cnd::convnd_map_kernel<long long><<<blocks, 256, 0, st>>>(g, 0, (const long long*)x, (const long long*)w, (const long long*)bias,
                                                              (long long*)y, total);
@@ -209,6 +395,21 @@ int b200_convnd_backward(const b200_convnd_params* p, const float* grad, const f
   const long long w_total = (p->transposed ? p->cin * (p->cout / p->groups) : p->cout * (p->cin / p->groups)) * p->k[0] * p->k[1] * p->k[2];
   const long long out_total = p->n * p->cout * p->out[0] * p->out[1] * p->out[2];
   if ((dx || dw || db) && out_total && !grad) return fail(B200_EINVAL, "convolution backward: null gradient");
+  const bool on_2d = cnd::conv3d_takes(*p) && out_total > 0;
+  if (dx && in_total && on_2d && w) {
+    const int rc = cnd::conv3d_dinput(*p, grad, w, dx, st);
+    if (rc != B200_EUNSUPPORTED) {
+      if (rc) return rc;
+      dx = nullptr;   // done
+    }
+  }
+  if (dw && w_total && on_2d && x) {
+    const int rc = cnd::conv3d_dweight(*p, grad, x, dw, st);
+    if (rc != B200_EUNSUPPORTED) {
+      if (rc) return rc;
+      dw = nullptr;
+    }
+  }
   if (dx && in_total) {
     if (!w) return fail(B200_EINVAL, "convolution backward: null weight");
     cnd::convnd_map_kernel<float><<<(unsigned)div_up64(in_total, 256), 256, 0, st>>>(g, 1, grad, w, nullptr, dx, in_total);

@@ -145,8 +145,13 @@ def test_generic_kernel_through_the_c_abi(rank, transposed, groups):
     assert only_dw[0] is None and only_dw[2] is None and np.array_equal(only_dw[1], dw)
 
 
-def test_generic_kernel_on_a_video_sized_block():
-    """A 3-D residual block shape (16 frames of 56x56, 16 -> 32 channels, 3x3x3, stride (1,2,2)) against the restatement."""
+@pytest.mark.parametrize("generic", [True, False], ids=["generic-kernel", "tensor-core-decomposition"])
+def test_generic_kernel_on_a_video_sized_block(generic, monkeypatch):
+    """A 3-D residual block shape (16 frames of 56x56, 16 -> 32 channels, 3x3x3, stride (1,2,2)) against the restatement,
+    through the one-thread-per-output kernel (pinned by B200_CONV3D_GENERIC) and through the decomposition."""
+    if generic:
+        monkeypatch.setenv("B200_CONV3D_GENERIC", "1")
+    gate = 2e-6 if generic else 2e-5
     gen = torch.Generator().manual_seed(11)
     x = torch.randn(1, 16, 8, 28, 28, generator=gen).numpy()
     w = (torch.randn(32, 16, 3, 3, 3, generator=gen) * 0.1).numpy()
@@ -154,10 +159,11 @@ def test_generic_kernel_on_a_video_sized_block():
     okw = dict(stride=(1, 2, 2), padding=1, dilation=1, groups=1)
     want = convnd_oracle.forward(x, w, b, **okw)
     got = b200conv.convnd_forward(x, w, b, **okw)
-    assert oracle.rel_l2(got, want) <= 1e-6
+    assert b200conv.last_kernel().startswith("convnd_forward" if generic else "conv3d_forward")
+    assert oracle.rel_l2(got, want) <= gate
     grad = torch.randn(want.shape, generator=gen).numpy()
     for g, e in zip(b200conv.convnd_backward(grad, x, w, **okw), convnd_oracle.backward(grad, x, w, **okw)):
-        assert oracle.rel_l2(g, e) <= 2e-6
+        assert oracle.rel_l2(g, e) <= gate
 
 
 @pytest.mark.parametrize("rank,transposed", [(1, False), (2, False), (3, False), (2, True), (3, True)])
@@ -238,3 +244,45 @@ def test_transposed_bias_rides_in_the_tensor_core_epilogue(case):
     want = F.conv_transpose2d(x.double(), w.double(), b.double(), **kw).numpy()
     assert oracle.rel_l2(biased, want) <= GATE
     np.testing.assert_allclose(biased - plain, np.broadcast_to(b.numpy()[None, :, None, None], plain.shape), atol=2e-5)
+
+
+# ---- 3-D convolutions with 16 or more channels per group: depth taps on the 2-D tensor-core kernels ----------------
+WIDE3D = [  # (x shape, cout, kernel, stride, padding, dilation, groups)
+    ((2, 32, 6, 10, 9), 48, (3, 3, 3), (1, 1, 1), (1, 1, 1), (1, 1, 1), 1),
+    ((1, 64, 5, 12, 12), 64, (3, 3, 3), (1, 1, 1), (1, 1, 1), (1, 1, 1), 1),
+    ((2, 32, 7, 9, 8), 32, (2, 3, 2), (2, 1, 2), (1, 1, 0), (1, 1, 2), 1),       # strides and dilation: dInput stays generic
+    ((2, 64, 6, 8, 8), 64, (3, 3, 3), (1, 1, 1), (1, 1, 1), (1, 1, 1), 2),       # two groups of 32: dInput stays generic
+    ((1, 32, 4, 7, 7), 32, (5, 3, 3), (1, 1, 1), (1, 1, 1), (1, 1, 1), 1),       # depth taps that reach no input depth at all
+    ((2, 48, 8, 6, 6), 32, (3, 1, 1), (1, 1, 1), (0, 0, 0), (2, 1, 1), 1),       # "valid" in depth with dilation 2
+]
+
+
+@pytest.mark.parametrize("case", WIDE3D, ids=lambda c: "x".join(map(str, c[0])) + f"-co{c[1]}-k{'x'.join(map(str, c[2]))}-g{c[6]}")
+def test_conv3d_on_the_tensor_core_kernels(case):
+    xshape, cout, kernel, stride, padding, dilation, groups = case
+    gen = torch.Generator().manual_seed(sum(xshape) + cout)
+    x = torch.randn(*xshape, generator=gen).numpy()
+    w = (torch.randn(cout, xshape[1] // groups, *kernel, generator=gen) / np.sqrt(xshape[1] // groups * np.prod(kernel))).numpy()
+    b = torch.randn(cout, generator=gen).numpy()
+    okw = dict(stride=stride, padding=padding, dilation=dilation, groups=groups)
+    want = convnd_oracle.forward(x, w, b, **okw)
+    got = b200conv.convnd_forward(x, w, b, **okw)
+    assert b200conv.last_kernel().startswith("conv3d_forward")
+    assert got.shape == want.shape and oracle.rel_l2(got, want) <= 2e-5
+    assert oracle.rel_l2(b200conv.convnd_forward(x, w, None, **okw), convnd_oracle.forward(x, w, None, **okw)) <= 2e-5
+    grad = torch.randn(want.shape, generator=gen).numpy()
+    for g, e in zip(b200conv.convnd_backward(grad, x, w, **okw), convnd_oracle.backward(grad, x, w, **okw)):
+        assert oracle.rel_l2(g, e) <= 2e-5
+    assert b200conv.device_status() == 0
+
+
+def test_conv3d_wide_operator_and_gradients(monkeypatch):
+    """The operator on a wide 3-D layer (tensor-core decomposition) agrees with the generic kernel and with PyTorch CPU."""
+    torch.manual_seed(14)
+    x, w, b = torch.randn(2, 32, 5, 9, 9), torch.randn(32, 32, 3, 3, 3) * 0.05, torch.randn(32)
+    fn = lambda xx, ww, bb: F.conv3d(xx, ww, bb, padding=1)
+    _check_autograd(fn, (x, w, b))
+    fast = fn(x.to("vulkan"), w.to("vulkan"), b.to("vulkan")).cpu()
+    monkeypatch.setenv("B200_CONV3D_GENERIC", "1")
+    slow = fn(x.to("vulkan"), w.to("vulkan"), b.to("vulkan")).cpu()
+    torch.testing.assert_close(fast, slow, rtol=2e-4, atol=2e-4)

@@ -100,6 +100,10 @@ int b200_gather_strided(void* dst, const void* src, int ndim, const int64_t* siz
 int b200_scatter_strided(void* dst, const void* src, int ndim, const int64_t* sizes,
                          const int64_t* strides, int elem_bytes, void* stream);
 
+/* strided dst += contiguous src (FP32; the view must not alias itself): partial results accumulated into a slice of a
+ * larger tensor (the depth taps of a 3-D dInput).  No counterpart in the reference. */
+int b200_scatter_add_strided(float* dst, const float* src, int ndim, const int64_t* sizes, const int64_t* strides, void* stream);
+
 /* dst (contiguous over the dimensions that are kept, in their order) <- sum of the FP32 strided view over the
  * dimensions with reduce[i] != 0.  The reduction the autograd graph of a broadcast operand needs (expand's backward,
  * `sum_to_size`): a broadcast attention mask, grouped-query key / value heads.  Stands for the reference's reduction
@@ -241,7 +245,7 @@ int b200_convnd_forward(const b200_convnd_params* p, const void* x, const void* 
 
 /* FP32 gradients on contiguous tensors; a NULL result pointer skips that gradient (shader modes
  * 1 dInput, 2 dWeight, 3 dBias; csrc/ops/convolution_nd.cpp:65-74).  Wide 3-D calls run the 2-D tcgen05 kernels per
- * depth tap as in the forward call (dInput: stride 1 and one group; dWeight: always). */
+ * depth tap as in the forward call. */
 int b200_convnd_backward(const b200_convnd_params* p, const float* grad, const float* x,
                          const float* w, float* dx, float* dw, float* db, void* stream);
 

@@ -68,6 +68,7 @@ SIGNATURES = {
     "b200_memset": (c_int, [c_void_p, c_int, c_size_t, c_void_p]),
     "b200_gather_strided": (c_int, [c_void_p, c_void_p, c_int, POINTER(c_int64), POINTER(c_int64), c_int, c_void_p]),
     "b200_scatter_strided": (c_int, [c_void_p, c_void_p, c_int, POINTER(c_int64), POINTER(c_int64), c_int, c_void_p]),
+    "b200_scatter_add_strided": (c_int, [c_void_p, c_void_p, c_int, POINTER(c_int64), POINTER(c_int64), c_void_p]),
     "b200_sum_strided": (c_int, [c_void_p, c_void_p, c_int, POINTER(c_int64), POINTER(c_int64), c_void_p, c_void_p]),
     "b200_stream_create": (c_int, [POINTER(c_void_p)]),
     "b200_stream_destroy": (c_int, [c_void_p]),

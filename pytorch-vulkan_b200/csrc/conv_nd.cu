@@ -233,12 +233,51 @@ static int conv3d_forward(const b200_convnd_params& p, const float* x, const flo
 }
 
 // dx[n, :, id] = sum_kd conv2d(dy[n, :, id + pd - kd*dd], flip(w[:, :, kd])^T), stride 1 in all three dimensions, one group
+// The general form (strides, groups): the 2-D dInput kernels per (kd, n) into a contiguous scratch [depths][cin][h][w],
+// added into the slice of dx those depths are (dx starts as zeros).  An input depth id receives tap kd from the output
+// depth od with od*sd = id + pd - kd*dd: for sd > 1 those id are every sd-th depth.
+static int conv3d_dinput_general(const b200_convnd_params& p, const float* grad, const float* w, float* dx, cudaStream_t st) {
+  const long long D = p.in[0], H = p.in[1], W = p.in[2], OD = p.out[0], OH = p.out[1], OW = p.out[2], cig = p.cin / p.groups;
+  const long long kvol2 = p.k[1] * p.k[2];
+  Scratch scratch(st);
+  B200_CUDA(cudaMemsetAsync(dx, 0, (size_t)(p.n * p.cin * D * H * W) * sizeof(float), st));
+  float* part = nullptr;
+  if (int rc = scratch.get((void**)&part, (size_t)(OD * p.cin * H * W) * sizeof(float))) return rc;
+  size_t ws_bytes = 0;
+  void* ws = nullptr;
+  for (long long kd = 0; kd < p.k[0]; ++kd) {
+    long long lo, hi;
+    depth_range(p, kd, &lo, &hi);   // output depths whose tap kd lies inside the input
+    if (hi < lo) continue;
+    b200_conv_params p2;
+    if (int rc = b200_conv2d_geometry(&p2, hi - lo + 1, p.cin, p.cout, H, W, cig, p.k[1], p.k[2], p.stride[1], p.stride[2], p.pad[1], p.pad[2],
+                                      p.dilation[1], p.dilation[2], p.groups))
+      return rc;
+    if (p2.oh != OH || p2.ow != OW) return B200_EUNSUPPORTED;
+    const size_t need = b200_conv2d_workspace(&p2, B200_PHASE_DINPUT, B200_ALGO_AUTO, (size_t)1 << 40);
+    if (need > ws_bytes) {
+      if (int rc = scratch.get(&ws, need)) return rc;
+      ws_bytes = need;
+    }
+    const b200_view4 wv{w + kd * kvol2, {cig * p.k[0] * kvol2, p.k[0] * kvol2, p.k[2], 1}};
+    const long long d0 = lo * p.stride[0] - p.pad[0] + kd * p.dilation[0];   // input depth of the first of them
+    for (long long n = 0; n < p.n; ++n) {
+      const b200_view4 gv{grad + (n * p.cout * OD + lo) * OH * OW, {OH * OW, OD * OH * OW, OW, 1}};
+      if (int rc = b200_conv2d_dinput(&p2, gv, wv, part, need ? ws : nullptr, need, B200_ALGO_AUTO, st)) return rc;
+      const int64_t sizes[4] = {hi - lo + 1, p.cin, H, W};
+      const int64_t strides[4] = {p.stride[0] * H * W, D * H * W, W, 1};
+      if (int rc = b200_scatter_add_strided(dx + (n * p.cin * D + d0) * H * W, part, 4, sizes, strides, st)) return rc;
+    }
+  }
+  return B200_OK;
+}
+
 static int conv3d_dinput(const b200_convnd_params& p, const float* grad, const float* w, float* dx, cudaStream_t st) {
-  if (p.groups != 1 || p.stride[0] != 1 || p.stride[1] != 1 || p.stride[2] != 1) return B200_EUNSUPPORTED;
+  if (p.groups != 1 || p.stride[0] != 1 || p.stride[1] != 1 || p.stride[2] != 1) return conv3d_dinput_general(p, grad, w, dx, st);
   const long long D = p.in[0], H = p.in[1], W = p.in[2], OD = p.out[0], OH = p.out[1], OW = p.out[2];
   const long long kvol2 = p.k[1] * p.k[2];
   const long long ph2 = p.dilation[1] * (p.k[1] - 1) - p.pad[1], pw2 = p.dilation[2] * (p.k[2] - 1) - p.pad[2];
-  if (ph2 < 0 || pw2 < 0) return B200_EUNSUPPORTED;   // padding beyond the filter reach: left to the generic kernel
+  if (ph2 < 0 || pw2 < 0) return conv3d_dinput_general(p, grad, w, dx, st);   // padding beyond the filter reach
   Scratch scratch(st);
   float* acc = nullptr;   // [n][d][h][w][cin]
   const long long rows = p.n * D * H * W;

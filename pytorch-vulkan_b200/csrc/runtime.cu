@@ -461,6 +461,37 @@ extern "C" int b200_gather_strided(void* dst, const void* src, int ndim, const i
                                    const int64_t* strides, int elem_bytes, void* stream) {
   return b200::strided_copy<false>(dst, src, ndim, sizes, strides, elem_bytes, (cudaStream_t)stream);
 }
+// strided dst += contiguous src (FP32): accumulation of partial results into a view of a larger tensor
+namespace b200 {
+__global__ void __launch_bounds__(256) strided_add_kernel(float* __restrict__ dst, const float* __restrict__ src, StridedDesc d, long long total) {
+  for (long long i = blockIdx.x * 256ll + threadIdx.x; i < total; i += (long long)gridDim.x * 256) {
+    long long r = i, addr = 0;
+#pragma unroll 1
+    for (int k = d.ndim - 1; k >= 0; --k) {
+      const long long q = r / d.size[k];
+      addr += (r - q * d.size[k]) * d.stride[k];
+      r = q;
+    }
+    dst[addr] += src[i];
+  }
+}
+}  // namespace b200
+extern "C" int b200_scatter_add_strided(float* dst, const float* src, int ndim, const int64_t* sizes, const int64_t* strides, void* stream) {
+  using namespace b200;
+  if (int rc = ensure_init()) return rc;
+  if (ndim < 0 || ndim > 8) return fail(B200_EINVAL, "strided copy supports at most 8 dimensions (got %d)", ndim);
+  StridedDesc d;
+  d.ndim = ndim;
+  long long total = 1;
+  for (int i = 0; i < ndim; ++i) { d.size[i] = sizes[i]; d.stride[i] = strides[i]; total *= sizes[i]; }
+  if (total == 0) return B200_OK;
+  if (!dst || !src) return fail(B200_EINVAL, "strided add: null tensor");
+  const int grid = (int)std::min<long long>((total + 255) / 256, (long long)sm_count() * 16);
+  strided_add_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(dst, src, d, total);
+  count_launch();
+  return launch_check("strided_add_kernel");
+}
+
 extern "C" int b200_scatter_strided(void* dst, const void* src, int ndim, const int64_t* sizes,
                                     const int64_t* strides, int elem_bytes, void* stream) {
   return b200::strided_copy<true>(dst, src, ndim, sizes, strides, elem_bytes, (cudaStream_t)stream);

@@ -250,10 +250,12 @@ def test_transposed_bias_rides_in_the_tensor_core_epilogue(case):
 WIDE3D = [  # (x shape, cout, kernel, stride, padding, dilation, groups)
     ((2, 32, 6, 10, 9), 48, (3, 3, 3), (1, 1, 1), (1, 1, 1), (1, 1, 1), 1),
     ((1, 64, 5, 12, 12), 64, (3, 3, 3), (1, 1, 1), (1, 1, 1), (1, 1, 1), 1),
-    ((2, 32, 7, 9, 8), 32, (2, 3, 2), (2, 1, 2), (1, 1, 0), (1, 1, 2), 1),       # strides and dilation: dInput stays generic
-    ((2, 64, 6, 8, 8), 64, (3, 3, 3), (1, 1, 1), (1, 1, 1), (1, 1, 1), 2),       # two groups of 32: dInput stays generic
+    ((2, 32, 7, 9, 8), 32, (2, 3, 2), (2, 1, 2), (1, 1, 0), (1, 1, 2), 1),       # strides and dilation: dInput through the 2-D dInput kernels + strided add
+    ((2, 64, 6, 8, 8), 64, (3, 3, 3), (1, 1, 1), (1, 1, 1), (1, 1, 1), 2),       # two groups of 32: likewise
     ((1, 32, 4, 7, 7), 32, (5, 3, 3), (1, 1, 1), (1, 1, 1), (1, 1, 1), 1),       # depth taps that reach no input depth at all
     ((2, 48, 8, 6, 6), 32, (3, 1, 1), (1, 1, 1), (0, 0, 0), (2, 1, 1), 1),       # "valid" in depth with dilation 2
+    ((2, 32, 9, 11, 10), 64, (3, 3, 3), (2, 2, 2), (1, 1, 1), (1, 1, 1), 1),     # stride 2 everywhere (a video stem's shape)
+    ((1, 32, 6, 8, 8), 32, (3, 3, 3), (1, 1, 1), (3, 3, 3), (1, 1, 1), 1),       # padding beyond the filter reach
 ]
 
 

@@ -175,6 +175,16 @@ struct Scratch {   // blocks of the library's stream-ordered allocator, released
   }
 };
 
+// A transposed convolution is the input gradient of the ordinary convolution with the same weight whose input is the
+// transposed call's result: that convolution's parameters (input and output extents and channel counts swapped).
+static b200_convnd_params mirrored(const b200_convnd_params& p) {
+  b200_convnd_params m = p;
+  m.transposed = 0;
+  m.cin = p.cout; m.cout = p.cin;
+  for (int a = 0; a < 3; ++a) { m.in[a] = p.out[a]; m.out[a] = p.in[a]; }
+  return m;
+}
+
 static bool conv3d_takes(const b200_convnd_params& p) {
   if (getenv("B200_CONV3D_GENERIC")) return false;   // testing aid: pins the generic kernel
   if (p.rank != 3 || p.transposed || p.n <= 0) return false;
@@ -414,6 +424,18 @@ int b200_convnd_forward(const b200_convnd_params* p, const void* x, const void* 
       return rc;
     }
   }
+  if (!is_int64 && p->transposed && p->rank == 3) {   // the input gradient of the mirrored convolution, plus the bias
+    const b200_convnd_params m = cnd::mirrored(*p);
+    if (cnd::conv3d_takes(m)) {
+      int rc = cnd::conv3d_dinput(m, (const float*)x, (const float*)w, (float*)y, st);
+      if (rc == B200_OK && bias)
+        rc = bias_add_nchw((float*)y, p->n, (int)p->cout, (long long)(p->out[0] * p->out[1] * p->out[2]), (const float*)bias, 1, st);
+      if (rc != B200_EUNSUPPORTED) {
+        note_kernel("conv_transpose3d_forward: depth taps on the 2-D tcgen05 kernels");
+        return rc;
+      }
+    }
+  }
   if (is_int64)
     cnd::convnd_map_kernel<long long><<<blocks, 256, 0, st>>>(g, 0, (const long long*)x, (const long long*)w, (const long long*)bias,
                                                              (long long*)y, total);
@@ -434,6 +456,21 @@ int b200_convnd_backward(const b200_convnd_params* p, const float* grad, const f
   const long long w_total = (p->transposed ? p->cin * (p->cout / p->groups) : p->cout * (p->cin / p->groups)) * p->k[0] * p->k[1] * p->k[2];
   const long long out_total = p->n * p->cout * p->out[0] * p->out[1] * p->out[2];
   if ((dx || dw || db) && out_total && !grad) return fail(B200_EINVAL, "convolution backward: null gradient");
+  if (p->transposed && p->rank == 3 && out_total > 0 && in_total > 0) {
+    // gradients of a transposed call through the mirrored convolution: dx = its forward pass over grad, dw = its
+    // dWeight with grad as the input and x as the output gradient
+    const b200_convnd_params m = cnd::mirrored(*p);
+    if (cnd::conv3d_takes(m)) {
+      if (dx && w) {
+        const int rc = cnd::conv3d_forward(m, grad, w, nullptr, dx, st);
+        if (rc != B200_EUNSUPPORTED) { if (rc) return rc; dx = nullptr; }
+      }
+      if (dw && w_total && x) {
+        const int rc = cnd::conv3d_dweight(m, x, grad, dw, st);
+        if (rc != B200_EUNSUPPORTED) { if (rc) return rc; dw = nullptr; }
+      }
+    }
+  }
   const bool on_2d = cnd::conv3d_takes(*p) && out_total > 0;
   if (dx && in_total && on_2d && w) {
     const int rc = cnd::conv3d_dinput(*p, grad, w, dx, st);

@@ -288,3 +288,28 @@ def test_conv3d_wide_operator_and_gradients(monkeypatch):
     monkeypatch.setenv("B200_CONV3D_GENERIC", "1")
     slow = fn(x.to("vulkan"), w.to("vulkan"), b.to("vulkan")).cpu()
     torch.testing.assert_close(fast, slow, rtol=2e-4, atol=2e-4)
+
+
+@pytest.mark.parametrize("xshape,cout,kernel,stride,padding,output_padding,groups", [
+    ((2, 32, 4, 5, 6), 32, (2, 2, 2), (2, 2, 2), (0, 0, 0), (0, 0, 0), 1),       # the x2 up-convolution of a 3-D U-Net
+    ((1, 64, 3, 6, 6), 32, (3, 3, 3), (1, 1, 1), (1, 1, 1), (0, 0, 0), 1),
+    ((2, 32, 4, 5, 5), 48, (3, 3, 2), (2, 1, 2), (1, 1, 0), (1, 0, 1), 1),       # output padding, mixed strides
+    ((1, 64, 3, 5, 5), 64, (2, 3, 3), (1, 2, 1), (0, 1, 1), (0, 1, 0), 2),       # two groups
+])
+def test_conv_transpose3d_on_the_tensor_core_kernels(xshape, cout, kernel, stride, padding, output_padding, groups):
+    gen = torch.Generator().manual_seed(sum(xshape) + cout + 5)
+    x = torch.randn(*xshape, generator=gen).numpy()
+    w = (torch.randn(xshape[1], cout // groups, *kernel, generator=gen) / np.sqrt(xshape[1] // groups * np.prod(kernel))).numpy()
+    b = torch.randn(cout, generator=gen).numpy()
+    okw = dict(stride=stride, padding=padding, dilation=1, output_padding=output_padding, transposed=True, groups=groups)
+    want = convnd_oracle.forward(x, w, b, **okw)
+    got = b200conv.convnd_forward(x, w, b, **okw)
+    assert b200conv.last_kernel().startswith("conv_transpose3d_forward")
+    assert got.shape == want.shape and oracle.rel_l2(got, want) <= 2e-5
+    grad = torch.randn(want.shape, generator=gen).numpy()
+    for g, e in zip(b200conv.convnd_backward(grad, x, w, **okw), convnd_oracle.backward(grad, x, w, **okw)):
+        assert oracle.rel_l2(g, e) <= 2e-5
+    assert b200conv.device_status() == 0
+    # and through the operator with autograd
+    tkw = dict(stride=stride, padding=padding, output_padding=output_padding, groups=groups)
+    _check_autograd(lambda xx, ww, bb: F.conv_transpose3d(xx, ww, bb, **tkw), (torch.from_numpy(x), torch.from_numpy(w), torch.from_numpy(b)))

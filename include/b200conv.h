@@ -238,8 +238,8 @@ int b200_convnd_geometry(b200_convnd_params* out, int rank, int64_t n, int64_t c
 /* y = conv(x, w) + bias on contiguous tensors; FP32 (is_int64 == 0) or int64 with wrapping
  * arithmetic (is_int64 != 0; csrc/ops/convolution_nd.cpp:57-61, shader convolution_nd_int64).  bias may be
  * NULL.  One thread per output element, like shader mode 0 (csrc/ops/convolution_nd.cpp:45-49,62) -- except FP32 calls
- * over three spatial dimensions with 16 or more channels per group on both sides, which are decomposed over the depth
- * taps into calls of the 2-D tcgen05 kernels (scratch comes from b200_malloc on `stream`). */
+ * over three spatial dimensions of 2^24 multiply-adds or more, which are decomposed over the depth taps into calls of the
+ * 2-D kernels (tcgen05 from 16 channels per group; scratch comes from b200_malloc on `stream`). */
 int b200_convnd_forward(const b200_convnd_params* p, const void* x, const void* w,
                         const void* bias, void* y, int is_int64, void* stream);
 

@@ -188,10 +188,14 @@ static b200_convnd_params mirrored(const b200_convnd_params& p) {
 static bool conv3d_takes(const b200_convnd_params& p) {
   if (getenv("B200_CONV3D_GENERIC")) return false;   // testing aid: pins the generic kernel
   if (p.rank != 3 || p.transposed || p.n <= 0) return false;
-  if (p.cin / p.groups < 16 || p.cout / p.groups < 16) return false;
   const long long plane = p.out[1] * p.out[2];
-  return p.in[0] * p.in[1] * p.in[2] > 0 && plane > 0 && p.n * p.out[0] * plane * std::max(p.cin, p.cout) < (1ll << 40);
+  if (!(p.in[0] * p.in[1] * p.in[2] > 0 && plane > 0 && p.n * p.out[0] * plane * std::max(p.cin, p.cout) < (1ll << 40))) return false;
+  // small problems stay on the single launch of the generic kernel: the decomposition costs a few launches per depth tap and sample
+  const long long macs = p.n * p.out[0] * plane * p.cout * (p.cin / p.groups) * p.k[0] * p.k[1] * p.k[2];
+  return macs >= (1ll << 24) || getenv("B200_CONV3D_DECOMPOSE") != nullptr;   // (testing aid: decompose whatever the size)
 }
+// the fused channels-last accumulation needs the tcgen05 strip kernel: 16 or more channels per group on both sides
+static bool conv3d_wide(const b200_convnd_params& p) { return p.cin / p.groups >= 16 && p.cout / p.groups >= 16; }
 // output depths [lo, hi] that tap kd reads inside the input: 0 <= od*sd - pd + kd*dd < D
 static void depth_range(const b200_convnd_params& p, long long kd, long long* lo, long long* hi) {
   const long long off = kd * p.dilation[0] - p.pad[0], sd = p.stride[0];
@@ -199,7 +203,48 @@ static void depth_range(const b200_convnd_params& p, long long kd, long long* lo
   *hi = std::min<long long>(p.out[0] - 1, (p.in[0] - 1 - off) >= 0 ? (p.in[0] - 1 - off) / sd : -1);
 }
 
+// Narrow layers (fewer than 16 channels per group on a side): the 2-D forward candidates per (kd, n) into a contiguous
+// scratch [depths][cout][oh][ow], added into the slice of y those depths are (y starts as the bias planes).
+static int conv3d_forward_general(const b200_convnd_params& p, const float* x, const float* w, const float* bias, float* y, cudaStream_t st) {
+  const long long D = p.in[0], H = p.in[1], W = p.in[2], OD = p.out[0], OH = p.out[1], OW = p.out[2], cig = p.cin / p.groups;
+  const long long kvol2 = p.k[1] * p.k[2];
+  Scratch scratch(st);
+  B200_CUDA(cudaMemsetAsync(y, 0, (size_t)(p.n * p.cout * OD * OH * OW) * sizeof(float), st));
+  if (bias)
+    if (int rc = bias_add_nchw(y, p.n, (int)p.cout, OD * OH * OW, bias, 1, st)) return rc;
+  float* part = nullptr;
+  if (int rc = scratch.get((void**)&part, (size_t)(OD * p.cout * OH * OW) * sizeof(float))) return rc;
+  size_t ws_bytes = 0;
+  void* ws = nullptr;
+  for (long long kd = 0; kd < p.k[0]; ++kd) {
+    long long lo, hi;
+    depth_range(p, kd, &lo, &hi);
+    if (hi < lo) continue;
+    b200_conv_params p2;
+    if (int rc = b200_conv2d_geometry(&p2, hi - lo + 1, p.cin, p.cout, H, W, cig, p.k[1], p.k[2], p.stride[1], p.stride[2], p.pad[1], p.pad[2],
+                                      p.dilation[1], p.dilation[2], p.groups))
+      return rc;
+    if (p2.oh != OH || p2.ow != OW) return fail(B200_EINVAL, "convolution: invalid or oversized output shape");
+    const size_t need = b200_conv2d_workspace(&p2, B200_PHASE_FORWARD, B200_ALGO_AUTO, (size_t)1 << 40);
+    if (need > ws_bytes) {
+      if (int rc = scratch.get(&ws, need)) return rc;
+      ws_bytes = need;
+    }
+    const b200_view4 wv{w + kd * kvol2, {cig * p.k[0] * kvol2, p.k[0] * kvol2, p.k[2], 1}};
+    const long long d0 = lo * p.stride[0] - p.pad[0] + kd * p.dilation[0];
+    for (long long n = 0; n < p.n; ++n) {
+      const b200_view4 xv{x + (n * p.cin * D + d0) * H * W, {p.stride[0] * H * W, D * H * W, W, 1}};
+      if (int rc = b200_conv2d_forward(&p2, xv, wv, nullptr, 0, part, need ? ws : nullptr, need, B200_ALGO_AUTO, st)) return rc;
+      const int64_t sizes[4] = {hi - lo + 1, p.cout, OH, OW};
+      const int64_t strides[4] = {OH * OW, OD * OH * OW, OW, 1};
+      if (int rc = b200_scatter_add_strided(y + (n * p.cout * OD + lo) * OH * OW, part, 4, sizes, strides, st)) return rc;
+    }
+  }
+  return B200_OK;
+}
+
 static int conv3d_forward(const b200_convnd_params& p, const float* x, const float* w, const float* bias, float* y, cudaStream_t st) {
+  if (!conv3d_wide(p)) return conv3d_forward_general(p, x, w, bias, y, st);
   const long long D = p.in[0], H = p.in[1], W = p.in[2], OD = p.out[0], OH = p.out[1], OW = p.out[2], cig = p.cin / p.groups;
   const long long kvol2 = p.k[1] * p.k[2];
   Scratch scratch(st);
@@ -220,7 +265,8 @@ static int conv3d_forward(const b200_convnd_params& p, const float* x, const flo
                                       p.dilation[1], p.dilation[2], p.groups))
       return rc;
     if (p2.oh != OH || p2.ow != OW) return fail(B200_EINVAL, "convolution: invalid or oversized output shape");
-    if (b200_conv2d_select(&p2, B200_PHASE_FORWARD, B200_ALGO_TC, (size_t)1 << 40) != B200_ALGO_TC) return B200_EUNSUPPORTED;
+    if (b200_conv2d_select(&p2, B200_PHASE_FORWARD, B200_ALGO_TC, (size_t)1 << 40) != B200_ALGO_TC)
+      return conv3d_forward_general(p, x, w, bias, y, st);   // y has not been touched yet
     const size_t need = b200_conv2d_workspace(&p2, B200_PHASE_FORWARD, B200_ALGO_TC, (size_t)1 << 40);
     if (need > ws_bytes) {
       if (int rc = scratch.get(&ws, need)) return rc;
@@ -283,7 +329,7 @@ static int conv3d_dinput_general(const b200_convnd_params& p, const float* grad,
 }
 
 static int conv3d_dinput(const b200_convnd_params& p, const float* grad, const float* w, float* dx, cudaStream_t st) {
-  if (p.groups != 1 || p.stride[0] != 1 || p.stride[1] != 1 || p.stride[2] != 1) return conv3d_dinput_general(p, grad, w, dx, st);
+  if (p.groups != 1 || p.stride[0] != 1 || p.stride[1] != 1 || p.stride[2] != 1 || !conv3d_wide(p)) return conv3d_dinput_general(p, grad, w, dx, st);
   const long long D = p.in[0], H = p.in[1], W = p.in[2], OD = p.out[0], OH = p.out[1], OW = p.out[2];
   const long long kvol2 = p.k[1] * p.k[2];
   const long long ph2 = p.dilation[1] * (p.k[1] - 1) - p.pad[1], pw2 = p.dilation[2] * (p.k[2] - 1) - p.pad[2];
@@ -307,7 +353,7 @@ static int conv3d_dinput(const b200_convnd_params& p, const float* grad, const f
                                       p.dilation[2], 1))
       return rc;
     if (p2.oh != H || p2.ow != W) return B200_EUNSUPPORTED;
-    if (b200_conv2d_select(&p2, B200_PHASE_FORWARD, B200_ALGO_TC, (size_t)1 << 40) != B200_ALGO_TC) return B200_EUNSUPPORTED;
+    if (b200_conv2d_select(&p2, B200_PHASE_FORWARD, B200_ALGO_TC, (size_t)1 << 40) != B200_ALGO_TC) return conv3d_dinput_general(p, grad, w, dx, st);
     const size_t need = b200_conv2d_workspace(&p2, B200_PHASE_FORWARD, B200_ALGO_TC, (size_t)1 << 40);
     if (need > ws_bytes) {
       if (int rc = scratch.get(&ws, need)) return rc;
@@ -347,8 +393,7 @@ static int conv3d_dweight(const b200_convnd_params& p, const float* grad, const 
     if (int rc = b200_conv2d_geometry(&p2, hi - lo + 1, p.cin, p.cout, H, W, cig, p.k[1], p.k[2], p.stride[1], p.stride[2], p.pad[1], p.pad[2],
                                       p.dilation[1], p.dilation[2], p.groups))
       return rc;
-    if (b200_conv2d_select(&p2, B200_PHASE_DWEIGHT, B200_ALGO_TC, (size_t)1 << 40) != B200_ALGO_TC) return B200_EUNSUPPORTED;
-    const size_t need = b200_conv2d_workspace(&p2, B200_PHASE_DWEIGHT, B200_ALGO_TC, (size_t)256 << 20);
+    const size_t need = b200_conv2d_workspace(&p2, B200_PHASE_DWEIGHT, B200_ALGO_AUTO, (size_t)256 << 20);
     if (need > ws_bytes) {
       if (int rc = scratch.get(&ws, need)) return rc;
       ws_bytes = need;
@@ -357,7 +402,7 @@ static int conv3d_dweight(const b200_convnd_params& p, const float* grad, const 
       const long long d0 = lo * p.stride[0] - p.pad[0] + kd * p.dilation[0];
       const b200_view4 xv{x + (n * p.cin * D + d0) * H * W, {p.stride[0] * H * W, D * H * W, W, 1}};
       const b200_view4 gv{grad + (n * p.cout * OD + lo) * OH * OW, {OH * OW, OD * OH * OW, OW, 1}};
-      if (int rc = b200_conv2d_dweight(&p2, xv, gv, parts + (n * p.k[0] + kd) * slice, need ? ws : nullptr, need, B200_ALGO_TC, st)) return rc;
+      if (int rc = b200_conv2d_dweight(&p2, xv, gv, parts + (n * p.k[0] + kd) * slice, need ? ws : nullptr, need, B200_ALGO_AUTO, st)) return rc;
     }
   }
   // sum over n, then [kd][cout][cin/g][kh*kw] -> dw[cout][cin/g][kd][kh*kw]

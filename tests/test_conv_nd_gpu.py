@@ -151,6 +151,8 @@ def test_generic_kernel_on_a_video_sized_block(generic, monkeypatch):
     through the one-thread-per-output kernel (pinned by B200_CONV3D_GENERIC) and through the decomposition."""
     if generic:
         monkeypatch.setenv("B200_CONV3D_GENERIC", "1")
+    else:
+        monkeypatch.setenv("B200_CONV3D_DECOMPOSE", "1")
     gate = 2e-6 if generic else 2e-5
     gen = torch.Generator().manual_seed(11)
     x = torch.randn(1, 16, 8, 28, 28, generator=gen).numpy()
@@ -260,7 +262,8 @@ WIDE3D = [  # (x shape, cout, kernel, stride, padding, dilation, groups)
 
 
 @pytest.mark.parametrize("case", WIDE3D, ids=lambda c: "x".join(map(str, c[0])) + f"-co{c[1]}-k{'x'.join(map(str, c[2]))}-g{c[6]}")
-def test_conv3d_on_the_tensor_core_kernels(case):
+def test_conv3d_on_the_tensor_core_kernels(case, monkeypatch):
+    monkeypatch.setenv("B200_CONV3D_DECOMPOSE", "1")      # these shapes are below the size from which it is chosen
     xshape, cout, kernel, stride, padding, dilation, groups = case
     gen = torch.Generator().manual_seed(sum(xshape) + cout)
     x = torch.randn(*xshape, generator=gen).numpy()
@@ -280,6 +283,7 @@ def test_conv3d_on_the_tensor_core_kernels(case):
 
 def test_conv3d_wide_operator_and_gradients(monkeypatch):
     """The operator on a wide 3-D layer (tensor-core decomposition) agrees with the generic kernel and with PyTorch CPU."""
+    monkeypatch.setenv("B200_CONV3D_DECOMPOSE", "1")
     torch.manual_seed(14)
     x, w, b = torch.randn(2, 32, 5, 9, 9), torch.randn(32, 32, 3, 3, 3) * 0.05, torch.randn(32)
     fn = lambda xx, ww, bb: F.conv3d(xx, ww, bb, padding=1)
@@ -296,7 +300,8 @@ def test_conv3d_wide_operator_and_gradients(monkeypatch):
     ((2, 32, 4, 5, 5), 48, (3, 3, 2), (2, 1, 2), (1, 1, 0), (1, 0, 1), 1),       # output padding, mixed strides
     ((1, 64, 3, 5, 5), 64, (2, 3, 3), (1, 2, 1), (0, 1, 1), (0, 1, 0), 2),       # two groups
 ])
-def test_conv_transpose3d_on_the_tensor_core_kernels(xshape, cout, kernel, stride, padding, output_padding, groups):
+def test_conv_transpose3d_on_the_tensor_core_kernels(xshape, cout, kernel, stride, padding, output_padding, groups, monkeypatch):
+    monkeypatch.setenv("B200_CONV3D_DECOMPOSE", "1")
     gen = torch.Generator().manual_seed(sum(xshape) + cout + 5)
     x = torch.randn(*xshape, generator=gen).numpy()
     w = (torch.randn(xshape[1], cout // groups, *kernel, generator=gen) / np.sqrt(xshape[1] // groups * np.prod(kernel))).numpy()
@@ -313,3 +318,24 @@ def test_conv_transpose3d_on_the_tensor_core_kernels(xshape, cout, kernel, strid
     # and through the operator with autograd
     tkw = dict(stride=stride, padding=padding, output_padding=output_padding, groups=groups)
     _check_autograd(lambda xx, ww, bb: F.conv_transpose3d(xx, ww, bb, **tkw), (torch.from_numpy(x), torch.from_numpy(w), torch.from_numpy(b)))
+
+
+@pytest.mark.parametrize("xshape,cout,kernel,stride,padding,groups", [
+    ((2, 3, 6, 20, 20), 24, (3, 5, 5), (1, 2, 2), (1, 2, 2), 1),      # a video stem: three input channels
+    ((2, 8, 5, 12, 12), 8, (3, 3, 3), (1, 1, 1), (1, 1, 1), 2),       # four channels per group
+    ((1, 12, 4, 9, 9), 40, (2, 3, 3), (2, 1, 1), (0, 1, 1), 1),
+])
+def test_conv3d_narrow_layers_through_the_decomposition(xshape, cout, kernel, stride, padding, groups, monkeypatch):
+    """Fewer than 16 channels per group: the 2-D candidates per depth tap into a scratch, added into the result."""
+    monkeypatch.setenv("B200_CONV3D_DECOMPOSE", "1")
+    gen = torch.Generator().manual_seed(sum(xshape) + cout)
+    x = torch.randn(*xshape, generator=gen).numpy()
+    w = (torch.randn(cout, xshape[1] // groups, *kernel, generator=gen) * 0.1).numpy()
+    b = torch.randn(cout, generator=gen).numpy()
+    okw = dict(stride=stride, padding=padding, dilation=1, groups=groups)
+    want = convnd_oracle.forward(x, w, b, **okw)
+    got = b200conv.convnd_forward(x, w, b, **okw)
+    assert b200conv.last_kernel().startswith("conv3d_forward") and oracle.rel_l2(got, want) <= 2e-5
+    grad = torch.randn(want.shape, generator=gen).numpy()
+    for g, e in zip(b200conv.convnd_backward(grad, x, w, **okw), convnd_oracle.backward(grad, x, w, **okw)):
+        assert oracle.rel_l2(g, e) <= 2e-5

@@ -31,6 +31,7 @@ Other workloads (one JSON line per row: the per-layer, per-phase timing tables):
   cfg3 / cfg4   per-layer, per-phase times of the U-Net-block and ResNeXt/dilated/strided configurations (configs 3 and 4) (L2 flushed before every call)
   cfg5          config 5 alone
   batch_norm / group_norm / attention   the kernels of the rows next to the convolution
+  conv3d        3-D layers through the depth-tap decomposition and through the generic kernel
 
 `--impl reference` times the reference's CPU path (PyTorch's CPU convolution, which is what the reference
 falls back to and tests against) on the same sweep.  `--layers`, `--no-cpu`, `--no-cfg5`, `--no-e2e` exist
@@ -425,7 +426,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--workload", default="sweep",
-                    choices=["sweep", "cfg3", "cfg4", "cfg5", "batch_norm", "group_norm", "attention"])
+                    choices=["sweep", "cfg3", "cfg4", "cfg5", "batch_norm", "group_norm", "attention", "conv3d"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling runs)")
     ap.add_argument("--no-cfg5", action="store_true", help="skip the config-5 record (profiling runs)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
@@ -456,7 +457,7 @@ def main():
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
     b200conv.init(local)
-    if args.workload in ("cfg3", "cfg4", "batch_norm", "group_norm", "attention"):
+    if args.workload in ("cfg3", "cfg4", "batch_norm", "group_norm", "attention", "conv3d"):
         import bench_workloads
         return getattr(bench_workloads, "run_" + args.workload)(args, torch, b200conv, device, peaks())
     dist, comm = None, None

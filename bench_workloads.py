@@ -1,4 +1,4 @@
-"""Per-layer workloads of bench.py (`--workload cfg3|cfg4|batch_norm|group_norm|attention`).
+"""Per-layer workloads of bench.py (`--workload cfg3|cfg4|batch_norm|group_norm|attention|conv3d`).
 
 Each prints one JSON line per row (the per-phase timing tables).  Everything is timed with CUDA events on the launching stream through the C ABI, one B200.
 `cold` rows (and every cfg3 / cfg4 row) write a 256 MB buffer, larger than the 126 MB L2, before each timed
@@ -7,6 +7,7 @@ call; `warm` rows run the calls back to back.
 import ctypes
 import json
 import math
+import os
 
 FLUSH_BYTES = 256 << 20
 
@@ -305,3 +306,44 @@ def run_attention(args, torch, b200conv, device, pk):
                               "scores_mb": round(4e-6 * heads * t * t, 1), "us": round(ms * 1e3, 1),
                               "tflops": round(flops / ms / 1e9, 1), "gpu_launches": launches, "kernels": b200conv.last_kernel()}), flush=True)
         del q, k, v, g, scores, ws
+
+
+# ---- 3-D convolution: the decomposition over depth taps against the one-thread-per-output kernel ---------------------
+CONV3D_SHAPES = [(4, 64, 16, 56), (2, 128, 8, 28), (1, 32, 32, 64)]   # (batch, channels, depth, height = width); 3x3x3, padding 1
+
+
+def run_conv3d(args, torch, b200conv, device, pk):
+    """b200_convnd_forward / _backward on video-sized 3-D layers, once through the decomposition onto the 2-D kernels and
+    once with the generic kernel pinned (B200_CONV3D_GENERIC).  FLOPs: 2 * N * D * H * W * Cout * Cin * 27 per phase."""
+    L = b200conv.lib()
+    stream = torch.cuda.current_stream().cuda_stream
+    for n, c, d, hw in _shapes(args, CONV3D_SHAPES):
+        gen = torch.Generator(device=device).manual_seed(n + c + d + hw)
+        x = torch.randn(n, c, d, hw, hw, device=device, generator=gen)
+        w = torch.randn(c, c, 3, 3, 3, device=device, generator=gen) * 0.05
+        p, yshape = b200conv.convnd_geometry(tuple(x.shape), tuple(w.shape), 1, 1, 1)
+        y, g = torch.empty(yshape, device=device), torch.randn(yshape, device=device, generator=gen)
+        dx, dw = torch.empty_like(x), torch.empty_like(w)
+        flops = 2.0 * y.numel() * c * 27
+        P = lambda t: t.data_ptr()
+        calls = [
+            ("forward", lambda: L.b200_convnd_forward(ctypes.byref(p), P(x), P(w), None, P(y), 0, stream)),
+            ("dinput", lambda: L.b200_convnd_backward(ctypes.byref(p), P(g), P(x), P(w), P(dx), None, None, stream)),
+            ("dweight", lambda: L.b200_convnd_backward(ctypes.byref(p), P(g), P(x), P(w), None, P(dw), None, stream)),
+        ]
+        for path in ("decomposed", "generic"):
+            if path == "generic":
+                os.environ["B200_CONV3D_GENERIC"] = "1"
+            else:
+                os.environ.pop("B200_CONV3D_GENERIC", None)
+            timer = Timer(torch, b200conv, device, args.reps if path == "decomposed" else 2)
+            for name, fn in calls:
+                before = b200conv.launch_count()
+                b200conv.check(fn())
+                launches = b200conv.launch_count() - before
+                ms = timer.time(fn, cold=False)
+                print(json.dumps({"workload": "conv3d", "path": path, "phase": name, "n": n, "channels": c, "depth": d, "hw": hw,
+                                  "kernel": [3, 3, 3], "us": round(ms * 1e3, 1), "tflops": round(flops / ms / 1e9, 1),
+                                  "gpu_launches": launches}), flush=True)
+        os.environ.pop("B200_CONV3D_GENERIC", None)
+        del x, w, y, g, dx, dw

@@ -94,6 +94,7 @@ class ClockSampler:
             self.handle = pynvml.nvmlDeviceGetHandleByIndex(phys)
             self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
             self.nvml = pynvml
+            self.period = max(0.001, float(os.environ.get("B200_BENCH_CLOCK_PERIOD_MS", "2")) / 1000.0)
             self.running = True
             self.thread = threading.Thread(target=self._poll, daemon=True)
             self.thread.start()
@@ -120,7 +121,7 @@ class ClockSampler:
                 self.rows.append([str(mhz), str(self.max_mhz)] + ["Active" if mask & bit else "Not Active" for _, bit in bits])
             except Exception:
                 pass
-            time.sleep(0.002)
+            time.sleep(self.period)
 
     def _read(self):
         for line in self.proc.stdout:
@@ -431,6 +432,9 @@ def main():
     ap.add_argument("--no-cfg5", action="store_true", help="skip the config-5 record (profiling runs)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
     ap.add_argument("--layers", default="", help="comma-separated layer indices (profiling runs)")
+    ap.add_argument("--eager", action="store_true",
+                    help="launch every kernel of every step from the host instead of replaying one CUDA graph of a step "
+                         "(the graph is the default: kernel-to-kernel gaps of 1-2 us instead of 3-9 us)")
     ap.add_argument("--bucket-mb", type=float, default=0.0,
                     help="N > 1: 0 = one exchange of the fused gradient buffer after the last layer (measured fastest: a "
                          "collective CTA and a compute CTA do not fit one SM's register file together, so an all-reduce under "
@@ -500,16 +504,17 @@ def main():
     BUCKET_FLOATS = int(args.bucket_mb * (1 << 20)) // 4 if args.bucket_mb > 0 else (1 << 62)
 
     families = {}  # kernel family -> [flops, [event pairs]]
+    issue_stream = [stream]   # the stream the library calls are issued on (the capture stream while a graph is recorded)
 
     def run_layer(l, timed, exchange=True):
         xv, wv, gv = l.views(b200conv)
         calls = (
             ("forward", lambda: L.b200_conv2d_forward(ctypes.byref(l.p), xv, wv, None, 0, l.y.data_ptr(),
-                                                      ws.data_ptr(), ws_bytes, 0, stream)),
+                                                      ws.data_ptr(), ws_bytes, 0, issue_stream[0])),
             ("dinput", lambda: L.b200_conv2d_dinput(ctypes.byref(l.p), gv, wv, l.dx.data_ptr(), ws.data_ptr(),
-                                                    ws_bytes, 0, stream)),
+                                                    ws_bytes, 0, issue_stream[0])),
             ("dweight", lambda: L.b200_conv2d_dweight(ctypes.byref(l.p), xv, gv, l.dw.data_ptr(), ws.data_ptr(),
-                                                      ws_bytes, 0, stream)),
+                                                      ws_bytes, 0, issue_stream[0])),
         )
         for name, fn in calls:
             if timed:
@@ -545,17 +550,56 @@ def main():
     for _ in range(args.warmup):
         step()
     barrier()
+
+    # One step's library calls recorded once into a CUDA graph (same entry points, same kernels, same buffers) and replayed
+    # per step: the host then costs one launch per step instead of one per kernel.  The gradient exchange stays outside.
+    graph, graph_launches = None, 0
+    if not args.eager and not args.layers:
+        try:
+            before = b200conv.launch_count()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                issue_stream[0] = torch.cuda.current_stream().cuda_stream
+                for l in layers:
+                    run_layer(l, False, exchange=False)
+            graph_launches = b200conv.launch_count() - before
+        except Exception as exc:   # capture not possible here: every kernel is launched from the host, as with --eager
+            print(f"bench.py: CUDA graph capture of a step failed ({exc}); running eagerly", file=sys.stderr)
+            graph = None
+        issue_stream[0] = stream
+        if graph is not None:
+            for _ in range(2):
+                graph.replay()
+        barrier()
+
+    def graph_step():
+        graph.replay()
+        if comm is not None:
+            comm.all_reduce_after(main_stream, grad_flat)
+            comm.join(main_stream)
+
+    # the sampler starts BEFORE the barrier: opening NVML takes milliseconds, and a rank 0 that entered the timed region
+    # late would make every other rank wait for it in the first exchange
     sampler = ClockSampler(local) if rank == 0 else None
+    barrier()
     launches0 = b200conv.launch_count()
     t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t_start.record()
     for _ in range(args.steps):
-        step(timed=True)
+        if graph is not None:
+            graph_step()
+        else:
+            step(timed=True)
     t_end.record()
     barrier()
-    launches = b200conv.launch_count() - launches0
+    launches = b200conv.launch_count() - launches0 + (graph_launches * args.steps if graph is not None else 0)
     clocks = sampler.stop() if sampler else None
     ms = t_start.elapsed_time(t_end) / args.steps
+    if graph is not None:
+        # the per-kernel-family times of the roofline object: the same steps once more with an event pair around every call
+        for _ in range(args.steps):
+            step(timed=True)
+        barrier()
     status = b200conv.device_status()
     if status != 0:
         raise SystemExit(f"device status word is {status:#x}: a bounded wait gave up; numbers are invalid")
@@ -663,7 +707,10 @@ def main():
                     "peak_source": f"{pk['source']}: sustained bf16 {pk['bf16_sustained']} TFLOP/s / 2 (TF32 rate); the split-precision "
                                    "scheme issues one TF32 and one BF16 pass of equal duration per algorithmic MAC (ceiling = peak/2), "
                                    "three TF32 passes where the dWeight plan keeps 3xTF32 (peak/3)",
-                    "families": fam_stats}
+                    "families": fam_stats,
+                    "families_timed": ("an event pair around every library call in an eager pass of the same steps right after the "
+                                       "timed region (the timed region replays a CUDA graph)") if graph is not None
+                                      else "an event pair around every library call inside the timed region"}
         line = {
             "metric": "conv2d_fwd_bwd_tflops", "value": world * step_flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
@@ -676,6 +723,8 @@ def main():
             "e2e": {"value": world * step_flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                     "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes, "ms_per_step": e2e_ms},
             "gpu_launches": int(launches),
+            "launch_mode": (f"one CUDA graph of a step ({graph_launches} kernel launches recorded through the C ABI) replayed per step"
+                            if graph is not None else "every kernel launched from the host"),
             "roofline": roofline,
         }
         if cpu:

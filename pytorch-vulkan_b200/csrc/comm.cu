@@ -117,6 +117,12 @@ int b200_comm_init(int rank, int nranks, const void* unique_id128) {
     const int ctas = atoi(e);
     if (ctas >= 1 && ctas <= 64) { cfg.minCTAs = 1; cfg.maxCTAs = ctas; }
   }
+  // ... and B200_COMM_MIN_CTAS how few: an exchange that nothing overlaps (the default of the benchmark's sweep) is
+  // served best by many
+  if (const char* e = getenv("B200_COMM_MIN_CTAS")) {
+    const int ctas = atoi(e);
+    if (ctas >= 1 && ctas <= 64) { cfg.minCTAs = ctas; if (cfg.maxCTAs != NCCL_CONFIG_UNDEF_INT && cfg.maxCTAs < ctas) cfg.maxCTAs = ctas; }
+  }
   ncclComm_t comm = nullptr;
   ncclResult_t r = g_nccl.init_rank_config(&comm, nranks, id, rank, &cfg);
   if (r != ncclSuccess && r != ncclInProgress) return nccl_fail(r, "ncclCommInitRankConfig");
@@ -165,7 +171,10 @@ int b200_allreduce_sum_f32(float* buf, size_t count, void* stream) {
       g_comm = nullptr;
       return fail(B200_ECUDA, "comm: all-reduce did not enqueue within %d ms (communicator aborted)", g_timeout_ms);
     }
-    if (r == ncclInProgress) std::this_thread::sleep_for(std::chrono::microseconds(50));
+    if (r == ncclInProgress) {
+      if (getenv("B200_COMM_POLL_SLEEP")) std::this_thread::sleep_for(std::chrono::microseconds(50));
+      else std::this_thread::yield();   // the enqueue takes tens of microseconds: sleeping through it doubles the call's latency
+    }
   }
   if (r != ncclSuccess) return nccl_fail(r, "ncclAllReduce");
   count_launch();

@@ -21,10 +21,16 @@ The line also carries
                 the fused dW || dB buffer (2.36 MB) issued through the library's communicator on a second
                 stream under the dInput kernel; strong scaling (the driver compares ms_per_step over N).
 
+The timed steps replay ONE CUDA graph of a step (its 72 kernel launches are recorded through the C ABI on the
+benchmark's stream after the warm-up steps; `launch_mode` says so, `gpu_launches` counts the recorded launches
+times the replays plus what is launched outside the graph); `--eager` issues every call separately instead.  The
+per-family times of `roofline` come from an extra eager pass with events around every call, outside the timed region.
+
 N>1 (torchrun, one rank per GPU): every rank runs the same sweep on its own batch of 64 (weak scaling,
-global batch 64*N); the weight gradients are summed over ranks by b200_allreduce_sum_f32 (NCCL behind the
-C ABI) on a second stream, in buckets of about 6 MB of consecutive layers, each issued as soon as its last
-dWeight kernel has finished, so the exchange runs under the following layers' kernels.  torch.distributed carries only the rendezvous, the barrier
+global batch 64*N); the dWeight kernels write into one fused gradient buffer (26 MB), which b200_allreduce_sum_f32
+(NCCL behind the C ABI) sums over the ranks once per step after the last layer, on a second stream.
+`--bucket-mb M` exchanges buckets of about M MB of consecutive layers under the following layers' kernels instead
+(eager mode only; measured slower on this workload).  torch.distributed carries only the rendezvous, the barrier
 and the max-over-ranks of the timings.
 
 Other workloads (one JSON line per row: the per-layer, per-phase timing tables):
@@ -554,7 +560,7 @@ def main():
     # One step's library calls recorded once into a CUDA graph (same entry points, same kernels, same buffers) and replayed
     # per step: the host then costs one launch per step instead of one per kernel.  The gradient exchange stays outside.
     graph, graph_launches = None, 0
-    if not args.eager and not args.layers:
+    if not args.eager and not args.layers and args.bucket_mb <= 0:   # buckets are issued between the layers' calls
         try:
             before = b200conv.launch_count()
             graph = torch.cuda.CUDAGraph()

@@ -24,7 +24,7 @@ The line also carries
 The timed steps replay ONE CUDA graph of a step (its 72 kernel launches are recorded through the C ABI on the
 benchmark's stream after the warm-up steps; `launch_mode` says so, `gpu_launches` counts the recorded launches
 times the replays plus what is launched outside the graph); `--eager` issues every call separately instead.  The
-per-family times of `roofline` come from an extra eager pass with events around every call, outside the timed region.
+per-family times of `roofline` come from an extra eager pass with events around every call, before the timed region.
 
 N>1 (torchrun, one rank per GPU): every rank runs the same sweep on its own batch of 64 (weak scaling,
 global batch 64*N); the dWeight kernels write into one fused gradient buffer (26 MB), which b200_allreduce_sum_f32
@@ -561,6 +561,11 @@ def main():
     # per step: the host then costs one launch per step instead of one per kernel.  The gradient exchange stays outside.
     graph, graph_launches = None, 0
     if not args.eager and not args.layers and args.bucket_mb <= 0:   # buckets are issued between the layers' calls
+        # the per-kernel-family times of the roofline object: the same steps with an event pair around every call, BEFORE
+        # the timed region, so that the buffers checked afterwards are the ones the timed replays wrote
+        for _ in range(args.steps):
+            step(timed=True)
+        barrier()
         try:
             before = b200conv.launch_count()
             graph = torch.cuda.CUDAGraph()
@@ -572,6 +577,7 @@ def main():
         except Exception as exc:   # capture not possible here: every kernel is launched from the host, as with --eager
             print(f"bench.py: CUDA graph capture of a step failed ({exc}); running eagerly", file=sys.stderr)
             graph = None
+            families.clear()
         issue_stream[0] = stream
         if graph is not None:
             for _ in range(2):
@@ -601,11 +607,6 @@ def main():
     launches = b200conv.launch_count() - launches0 + (graph_launches * args.steps if graph is not None else 0)
     clocks = sampler.stop() if sampler else None
     ms = t_start.elapsed_time(t_end) / args.steps
-    if graph is not None:
-        # the per-kernel-family times of the roofline object: the same steps once more with an event pair around every call
-        for _ in range(args.steps):
-            step(timed=True)
-        barrier()
     status = b200conv.device_status()
     if status != 0:
         raise SystemExit(f"device status word is {status:#x}: a bounded wait gave up; numbers are invalid")
@@ -714,7 +715,7 @@ def main():
                                    "scheme issues one TF32 and one BF16 pass of equal duration per algorithmic MAC (ceiling = peak/2), "
                                    "three TF32 passes where the dWeight plan keeps 3xTF32 (peak/3)",
                     "families": fam_stats,
-                    "families_timed": ("an event pair around every library call in an eager pass of the same steps right after the "
+                    "families_timed": ("an event pair around every library call in an eager pass of the same steps right before the "
                                        "timed region (the timed region replays a CUDA graph)") if graph is not None
                                       else "an event pair around every library call inside the timed region"}
         line = {

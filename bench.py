@@ -728,7 +728,8 @@ def main():
                                   + ("" if world == 1 else ": skipped at N>1, where dW holds the sum over ranks") + "), PyTorch CPU FP64",
             "clocks": clocks,
             "e2e": {"value": world * step_flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
-                    "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes, "ms_per_step": e2e_ms},
+                    "h2d_bytes_per_step": world * h2d_bytes, "d2h_bytes_per_step": world * d2h_bytes, "ms_per_step": e2e_ms,
+                    "bytes_are": "whole job (every rank copies its own batch: per rank 1/n_gpus of these)"},
             "gpu_launches": int(launches),
             "launch_mode": (f"one CUDA graph of a step ({graph_launches} kernel launches recorded through the C ABI) replayed per step"
                             if graph is not None else "every kernel launched from the host"),

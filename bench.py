@@ -30,7 +30,7 @@ N>1 (torchrun, one rank per GPU): every rank runs the same sweep on its own batc
 global batch 64*N); the dWeight kernels write into one fused gradient buffer (26 MB), which b200_allreduce_sum_f32
 (NCCL behind the C ABI) sums over the ranks once per step after the last layer, on a second stream.
 `--bucket-mb M` exchanges buckets of about M MB of consecutive layers under the following layers' kernels instead
-(eager mode only; measured slower on this workload).  torch.distributed carries only the rendezvous, the barrier
+(the step is then cut into one graph per bucket).  torch.distributed carries only the rendezvous, the barrier
 and the max-over-ranks of the timings.
 
 Other workloads (one JSON line per row: the per-layer, per-phase timing tables):
@@ -559,20 +559,33 @@ def main():
 
     # One step's library calls recorded once into a CUDA graph (same entry points, same kernels, same buffers) and replayed
     # per step: the host then costs one launch per step instead of one per kernel.  The gradient exchange stays outside.
-    graph, graph_launches = None, 0
-    if not args.eager and not args.layers and args.bucket_mb <= 0:   # buckets are issued between the layers' calls
+    graph, graph_launches = None, 0      # graph: [(CUDAGraph, end of its layers' gradients in grad_flat)], one per bucket
+    if not args.eager and not args.layers:
         # the per-kernel-family times of the roofline object: the same steps with an event pair around every call, BEFORE
         # the timed region, so that the buffers checked afterwards are the ones the timed replays wrote
         for _ in range(args.steps):
             step(timed=True)
         barrier()
+        # with --bucket-mb the step is cut where a bucket of gradients is complete: one graph per bucket, its exchange
+        # issued behind it on the second stream while the next graph runs
+        parts, first = [], 0
+        for l in layers:
+            if comm is not None and (l.dw_end - first >= BUCKET_FLOATS) and l is not layers[-1]:
+                parts.append(l)
+                first = l.dw_end
+        parts.append(layers[-1])
         try:
             before = b200conv.launch_count()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                issue_stream[0] = torch.cuda.current_stream().cuda_stream
-                for l in layers:
-                    run_layer(l, False, exchange=False)
+            graph, it = [], iter(layers)
+            for last in parts:
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    issue_stream[0] = torch.cuda.current_stream().cuda_stream
+                    for l in it:
+                        run_layer(l, False, exchange=False)
+                        if l is last:
+                            break
+                graph.append((g, last.dw_end))
             graph_launches = b200conv.launch_count() - before
         except Exception as exc:   # capture not possible here: every kernel is launched from the host, as with --eager
             print(f"bench.py: CUDA graph capture of a step failed ({exc}); running eagerly", file=sys.stderr)
@@ -581,13 +594,18 @@ def main():
         issue_stream[0] = stream
         if graph is not None:
             for _ in range(2):
-                graph.replay()
+                for g, _end in graph:
+                    g.replay()
         barrier()
 
     def graph_step():
-        graph.replay()
+        start = 0
+        for g, end in graph:
+            g.replay()
+            if comm is not None:
+                comm.all_reduce_after(main_stream, grad_flat[start:end])
+            start = end
         if comm is not None:
-            comm.all_reduce_after(main_stream, grad_flat)
             comm.join(main_stream)
 
     # the sampler starts BEFORE the barrier: opening NVML takes milliseconds, and a rank 0 that entered the timed region
@@ -731,7 +749,7 @@ def main():
                     "h2d_bytes_per_step": world * h2d_bytes, "d2h_bytes_per_step": world * d2h_bytes, "ms_per_step": e2e_ms,
                     "bytes_are": "whole job (every rank copies its own batch: per rank 1/n_gpus of these)"},
             "gpu_launches": int(launches),
-            "launch_mode": (f"one CUDA graph of a step ({graph_launches} kernel launches recorded through the C ABI) replayed per step"
+            "launch_mode": (f"{len(graph)} CUDA graph(s) of a step ({graph_launches} kernel launches recorded through the C ABI) replayed per step"
                             if graph is not None else "every kernel launched from the host"),
             "roofline": roofline,
         }

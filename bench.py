@@ -90,7 +90,7 @@ class ClockSampler:
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
-        self.rows, self.proc, self.nvml, self.running = [], None, None, False
+        self.rows, self.proc, self.nvml, self.running, self.counting = [], None, None, False, False
         try:
             import pynvml
             pynvml.nvmlInit()
@@ -124,14 +124,20 @@ class ClockSampler:
             try:
                 mhz = float(n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM))
                 mask = int(n.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle))
-                self.rows.append([str(mhz), str(self.max_mhz)] + ["Active" if mask & bit else "Not Active" for _, bit in bits])
+                if self.counting:
+                    self.rows.append([str(mhz), str(self.max_mhz)] + ["Active" if mask & bit else "Not Active" for _, bit in bits])
             except Exception:
                 pass
             time.sleep(self.period)
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            if self.counting:
+                self.rows.append([c.strip() for c in line.split(",")])
+
+    def mark(self):
+        """The timed region starts now: samples taken before this call (while the ranks met at the barrier) are not kept."""
+        self.counting = True
 
     def stop(self):
         if self.nvml:
@@ -615,6 +621,8 @@ def main():
     launches0 = b200conv.launch_count()
     t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t_start.record()
+    if sampler:
+        sampler.mark()
     for _ in range(args.steps):
         if graph is not None:
             graph_step()
